@@ -1,0 +1,172 @@
+/* kn_b200.h -- C ABI of the B200-native executor for Kyanite's graph IR.
+ *
+ * The entry points below are what a host binding (Rust FFI, ctypes, cgo ...) binds in place of the
+ * reference's CUDA stack for this path: the `CudaExecutor` of kn-cuda-eval together with the
+ * kn-cuda-sys bindings underneath it (cuDNN, cuBLAS, NVRTC, cudart).  Each declaration cites the
+ * reference interface it replaces as `path:line` inside the reference project.
+ *
+ * Conventions
+ *  - every function returns a `kn_status`; on failure `kn_last_error()` holds a message for the
+ *    calling thread.  Nothing aborts the process (the reference panics instead:
+ *    kn-cuda-sys/src/wrapper/status.rs:17-32; a binding that wants that behaviour panics on a
+ *    non-zero status).
+ *  - an executor is used by one thread at a time but may move between threads; different
+ *    executors (devices) may run concurrently (kn-cuda-eval/src/executor.rs:39-41).
+ *  - the library selects the executor's device itself on every entry.
+ *  - all tensors crossing the boundary are dense, row-major ("standard layout") host arrays of the
+ *    dtype reported by `kn_executor_io_info`.
+ */
+#ifndef KN_B200_H
+#define KN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define KN_API __attribute__((visibility("default")))
+#else
+#define KN_API
+#endif
+
+typedef enum kn_status {
+    KN_OK = 0,
+    KN_ERR_INVALID_ARG = 1, /* null pointer, index out of range, wrong struct size */
+    KN_ERR_BAD_GRAPH = 2,   /* malformed graph blob */
+    KN_ERR_UNSUPPORTED = 3, /* valid graph the executor cannot run (rank / dtype limits) */
+    KN_ERR_CUDA = 4,        /* a CUDA runtime or driver call failed; message holds the CUDA error */
+    KN_ERR_SHAPE = 5,       /* shapes inconsistent for the given batch size */
+    KN_ERR_NO_DEVICE = 6,   /* requested device does not exist (CudaDeviceNotAvailable) */
+    KN_ERR_INTERNAL = 7
+} kn_status;
+
+/* dtype tags: the reference's `DType` in declaration order (kn-graph/src/dtype.rs:25-37) plus F16 */
+typedef enum kn_dtype {
+    KN_F32 = 0, KN_F64, KN_I8, KN_I16, KN_I32, KN_I64, KN_U8, KN_U16, KN_U32, KN_U64, KN_BOOL, KN_F16
+} kn_dtype;
+
+/* how f32 contractions (MatMul, Conv) are computed */
+typedef enum kn_math_mode {
+    KN_MATH_TF32 = 0, /* tcgen05 tensor cores, TF32 operands, f32 accumulate (default).  This is what
+                         the reference's cuDNN convolutions use on Ampere-and-later GPUs. */
+    KN_MATH_F32 = 1   /* exact f32 FMA on the SIMT pipes (what the reference's cublasSgemm uses) */
+} kn_math_mode;
+
+typedef struct kn_options {
+    uint32_t struct_size;   /* = sizeof(kn_options) */
+    int32_t math_mode;      /* kn_math_mode */
+    int32_t use_cuda_graph; /* 1: capture the step list once and replay it (default), 0: launch steps */
+    int32_t reserved;
+} kn_options;
+
+#define KN_MAX_RANK 8
+
+typedef struct kn_tensor_info {
+    int32_t dtype; /* kn_dtype */
+    int32_t rank;
+    int64_t dims[KN_MAX_RANK];
+    uint64_t bytes;
+} kn_tensor_info;
+
+/* kn-cuda-eval/src/planner.rs:67-81 `MemoryUsage` */
+typedef struct kn_mem_usage {
+    uint64_t dedicated_bytes;  /* constants */
+    uint64_t shared_bytes;     /* the activation arena actually allocated */
+    uint64_t zero_bytes;
+    uint64_t hypo_peak_bytes;  /* lower bound: largest sum of simultaneously live buffers */
+    uint64_t hypo_total_bytes; /* sum of all shared buffers if nothing were reused */
+} kn_mem_usage;
+
+typedef struct kn_graph kn_graph;
+typedef struct kn_executor kn_executor;
+
+/* Message of the last failure on this thread; never NULL. */
+KN_API const char* kn_last_error(void);
+
+/* Library ABI version (major * 1000 + minor). */
+KN_API int kn_version(void);
+
+/* Fills a default option block. */
+KN_API int kn_options_default(kn_options* opts);
+
+/* Number of CUDA devices.  Replaces `CudaDevice::all` / `cudaGetDeviceCount`
+ * (kn-cuda-sys/src/wrapper/handle.rs:38-48). */
+KN_API int kn_device_count(int* count);
+
+/* Builds the graph from its serialised form (see kyanite_b200/graph.py `Graph.to_bytes` for the
+ * layout).  The reference passes `&Graph` by reference inside one Rust process
+ * (kn-cuda-eval/src/executor.rs:61); a Rust value cannot cross a C boundary, so the binding walks
+ * `graph.values()` (kn-graph/src/graph.rs:391-394) and serialises each `ValueInfo`.
+ * The blob is copied; the caller may free it afterwards. */
+KN_API int kn_graph_from_blob(const void* bytes, size_t len, kn_graph** out);
+KN_API void kn_graph_destroy(kn_graph* graph);
+KN_API int kn_graph_io_count(const kn_graph* graph, int* n_inputs, int* n_outputs, int* n_values);
+
+/* Host-only: lowers the graph for `batch_size` and writes a text description of the step list and
+ * memory plan into `buf` (NUL-terminated, truncated to `cap`); `*needed` receives the full length.
+ * Touches no CUDA API.  Mirrors the reference's `Debug` dump of a `CudaExecutor`
+ * (kn-cuda-eval/src/executor.rs:269-289). */
+KN_API int kn_plan_describe(const kn_graph* graph, size_t batch_size, const kn_options* opts, char* buf, size_t cap,
+                     size_t* needed);
+
+/* `CudaExecutor::new(device, &graph, batch_size)` (kn-cuda-eval/src/executor.rs:61-110): plans the
+ * graph, allocates the arena, uploads constants, allocates pinned staging for inputs and outputs.
+ * The graph handle may be destroyed afterwards. */
+KN_API int kn_executor_create(int device, const kn_graph* graph, size_t batch_size, const kn_options* opts,
+                       kn_executor** out);
+KN_API void kn_executor_destroy(kn_executor* exec);
+
+KN_API int kn_executor_io_count(const kn_executor* exec, int* n_inputs, int* n_outputs);
+/* Shape and dtype of input/output `index` at this executor's batch size
+ * (`graph.input_shapes()` / `output_shapes()` evaluated, kn-cuda-eval/src/executor.rs:118-127). */
+KN_API int kn_executor_io_info(const kn_executor* exec, int is_output, int index, kn_tensor_info* info);
+
+/* `CudaExecutor::evaluate(&inputs) -> &[DTensor]` (kn-cuda-eval/src/executor.rs:117-195):
+ * copies every input to the device, runs all steps, copies every output back and waits.
+ * `inputs[i]` / `outputs[i]` are host buffers of `kn_executor_io_info(..).bytes` bytes.  Passing
+ * the executor's own staging pointer (kn_executor_host_buffer) for an entry skips the extra host
+ * copy for it.  Bool outputs are validated to be 0/1 (executor.rs:181-189). */
+KN_API int kn_executor_evaluate(kn_executor* exec, const void* const* inputs, void* const* outputs);
+
+/* `CudaExecutor::run_async` (kn-cuda-eval/src/executor.rs:199-258): enqueues the steps on the
+ * executor's stream without touching host memory; inputs are whatever the device input buffers hold. */
+KN_API int kn_executor_run_async(kn_executor* exec);
+/* `stream().synchronize()` (kn-cuda-sys/src/wrapper/handle.rs:128-132) */
+KN_API int kn_executor_synchronize(kn_executor* exec);
+/* The `cudaStream_t` the steps run on, as an opaque pointer (`CudaExecutor::stream`, executor.rs:263-265). */
+KN_API int kn_executor_stream(kn_executor* exec, void** stream);
+
+/* Pinned host staging buffer of input/output `index` (the reference keeps these private:
+ * kn-cuda-eval/src/executor.rs:74-95). */
+KN_API int kn_executor_host_buffer(kn_executor* exec, int is_output, int index, void** ptr, uint64_t* bytes);
+/* Device buffer of input/output `index` (`device_inputs` / `device_outputs`, executor.rs:27-28).
+ * Outputs may be strided views in the reference; here they are always dense. */
+KN_API int kn_executor_device_buffer(kn_executor* exec, int is_output, int index, void** ptr, uint64_t* bytes);
+/* Asynchronous halves of `evaluate`: staging -> device for all inputs, device -> staging for all outputs. */
+KN_API int kn_executor_upload_inputs(kn_executor* exec);
+KN_API int kn_executor_download_outputs(kn_executor* exec);
+
+/* `executor.mem_usage` (kn-cuda-eval/src/executor.rs:33, planner.rs:67-81) */
+KN_API int kn_executor_mem_usage(const kn_executor* exec, kn_mem_usage* usage);
+/* Number of steps and of kernel launches one `run_async` issues. */
+KN_API int kn_executor_step_count(const kn_executor* exec, int* steps, int* launches);
+
+/* `set_profile` / `last_profile` (kn-cuda-eval/src/executor.rs:43-58, 208-257, 291-325): with
+ * profiling on, the next `run_async`/`evaluate` launches step by step (no graph replay) with a CUDA
+ * event pair around each step.  `kn_executor_last_profile` writes one line per step
+ * (`index kind microseconds algorithmic_bytes flops description`) followed by per-kind totals. */
+KN_API int kn_executor_set_profile(kn_executor* exec, int enable);
+KN_API int kn_executor_last_profile(kn_executor* exec, char* buf, size_t cap, size_t* needed);
+
+/* Host-only element semantics, exported so the scalar rules can be tested without a device:
+ * applies one unary / binary operation to 64-bit canonical element patterns. */
+KN_API int kn_scalar_unary(int unary_op, int from_dtype, int to_dtype, uint64_t x, uint64_t* out);
+KN_API int kn_scalar_binary(int binary_op, int dtype, uint64_t a, uint64_t b, uint64_t* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KN_B200_H */

@@ -1,0 +1,545 @@
+// The executor and the C ABI.  Counterpart of `CudaExecutor` (kn-cuda-eval/src/executor.rs:20-325):
+// owns the arena, the uploaded constants, pinned staging for inputs and outputs, the stream and the
+// captured CUDA graph of the step list.
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+#include <memory>
+#include <sstream>
+#include <string>
+#include <vector>
+
+#include "ir.h"
+#include "kernels.h"
+#include "kn_b200.h"
+#include "plan.h"
+#include "scalar_ops.h"
+#include "tc.h"
+
+namespace kn {
+
+namespace {
+
+thread_local std::string g_last_error;
+
+#define KN_CUDA(expr)                                                                                   \
+    do {                                                                                                \
+        cudaError_t err__ = (expr);                                                                     \
+        if (err__ != cudaSuccess)                                                                       \
+            ::kn::fail(KN_ERR_CUDA, std::string(#expr) + " failed: " + cudaGetErrorString(err__));      \
+    } while (0)
+
+struct DeviceGuard {
+    int prev = -1;
+    explicit DeviceGuard(int device) {
+        cudaGetDevice(&prev);
+        KN_CUDA(cudaSetDevice(device));
+    }
+    ~DeviceGuard() {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
+
+}  // namespace
+
+struct Executor {
+    int device = 0;
+    std::unique_ptr<Plan> plan;
+    cudaStream_t stream = nullptr;
+    uint8_t* arena = nullptr;
+    uint8_t* consts = nullptr;
+    std::vector<void*> pinned_in, pinned_out;
+    std::vector<size_t> bytes_in, bytes_out;
+    std::vector<DType> dtype_in, dtype_out;
+    cudaGraphExec_t graph_exec = nullptr;
+    bool profile = false;
+    std::vector<float> step_us;
+    int launches = 0;
+
+    ~Executor() {
+        cudaSetDevice(device);
+        if (stream) cudaStreamSynchronize(stream);
+        if (graph_exec) cudaGraphExecDestroy(graph_exec);
+        for (void* p : pinned_in) if (p) cudaFreeHost(p);
+        for (void* p : pinned_out) if (p) cudaFreeHost(p);
+        if (arena) cudaFree(arena);
+        if (consts) cudaFree(consts);
+        if (stream) cudaStreamDestroy(stream);
+    }
+
+    uint8_t* device_ptr(const PlanTensor& t) const {
+        const BufferInfo& b = plan->buffers[t.buf];
+        uint8_t* base = b.kind == BufKind::Const ? consts : arena;
+        return base + b.arena_offset + t.offset * dtype_size(t.dtype);
+    }
+
+    void patch_pointers() {
+        launches = 0;
+        for (Step& s : plan->steps) {
+            std::vector<void*> ptr;
+            for (auto& t : s.operands) ptr.push_back(device_ptr(t));
+            switch (s.kind) {
+                case StepKind::Scalar:
+                    for (size_t i = 0; i < ptr.size(); i++) s.scalar.ptr[i] = ptr[i];
+                    break;
+                case StepKind::Reduce:
+                    s.reduce.in = ptr[0];
+                    s.reduce.out = ptr[1];
+                    break;
+                case StepKind::Softmax:
+                    s.row.in0 = (const float*)ptr[0];
+                    s.row.in1 = nullptr;
+                    s.row.out = (float*)ptr[1];
+                    break;
+                case StepKind::Layernorm:
+                    s.row.in0 = (const float*)ptr[0];
+                    s.row.out = (float*)ptr[1];
+                    s.row.in1 = ptr.size() > 2 ? (const float*)ptr[2] : nullptr;
+                    break;
+                case StepKind::Gather:
+                    s.gather.in = ptr[0];
+                    s.gather.idx = ptr[1];
+                    s.gather.out = ptr[2];
+                    break;
+                case StepKind::Gemm:
+                    s.gemm.a = (const float*)ptr[0];
+                    s.gemm.b = (const float*)ptr[1];
+                    s.gemm.c = (float*)ptr[2];
+                    s.gemm.add1 = ptr.size() > 3 ? (const float*)ptr[3] : nullptr;
+                    s.gemm.add2 = ptr.size() > 4 ? (const float*)ptr[4] : nullptr;
+                    break;
+                case StepKind::Conv:
+                    s.conv.in = (const float*)ptr[0];
+                    s.conv.filter = (const float*)ptr[1];
+                    s.conv.out = (float*)ptr[2];
+                    s.conv.add1 = ptr.size() > 3 ? (const float*)ptr[3] : nullptr;
+                    s.conv.add2 = ptr.size() > 4 ? (const float*)ptr[4] : nullptr;
+                    break;
+                default: fail(KN_ERR_INTERNAL, "unknown step kind");
+            }
+            if (s.tensor_core) tc_prepare_step(s);
+            launches += s.launches;
+        }
+    }
+
+    void launch_step(const Step& s) {
+        int err = 0;
+        switch (s.kind) {
+            case StepKind::Scalar: err = launch_scalar(s.scalar, stream); break;
+            case StepKind::Reduce: err = launch_reduce(s.reduce, stream); break;
+            case StepKind::Softmax: err = launch_softmax(s.row, stream); break;
+            case StepKind::Layernorm: err = launch_layernorm(s.row, stream); break;
+            case StepKind::Gather: err = launch_gather(s.gather, stream); break;
+            case StepKind::Gemm: err = s.tensor_core ? tc_launch_step(s, stream) : launch_gemm_simt(s.gemm, stream); break;
+            case StepKind::Conv: err = s.tensor_core ? tc_launch_step(s, stream) : launch_conv_simt(s.conv, stream); break;
+            default: fail(KN_ERR_INTERNAL, "unknown step kind");
+        }
+        if (err != 0)
+            fail(KN_ERR_CUDA, std::string("launch of step ") + step_kind_name(s.kind) + " (" + s.desc + ") failed: " +
+                                  cudaGetErrorString((cudaError_t)err));
+    }
+
+    void run_async() {
+        if (plan->steps.empty()) return;
+        if (profile) {
+            std::vector<cudaEvent_t> ev(plan->steps.size() + 1);
+            for (auto& e : ev) KN_CUDA(cudaEventCreate(&e));
+            KN_CUDA(cudaEventRecord(ev[0], stream));
+            for (size_t i = 0; i < plan->steps.size(); i++) {
+                launch_step(plan->steps[i]);
+                KN_CUDA(cudaEventRecord(ev[i + 1], stream));
+            }
+            KN_CUDA(cudaStreamSynchronize(stream));
+            step_us.assign(plan->steps.size(), 0.f);
+            for (size_t i = 0; i < plan->steps.size(); i++) {
+                float ms = 0;
+                KN_CUDA(cudaEventElapsedTime(&ms, ev[i], ev[i + 1]));
+                step_us[i] = ms * 1000.f;
+            }
+            for (auto& e : ev) cudaEventDestroy(e);
+            return;
+        }
+        if (plan->opts.use_cuda_graph) {
+            if (!graph_exec) {
+                cudaGraph_t graph = nullptr;
+                KN_CUDA(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
+                try {
+                    for (const Step& s : plan->steps) launch_step(s);
+                } catch (...) {
+                    cudaStreamEndCapture(stream, &graph);
+                    if (graph) cudaGraphDestroy(graph);
+                    throw;
+                }
+                KN_CUDA(cudaStreamEndCapture(stream, &graph));
+                cudaError_t err = cudaGraphInstantiate(&graph_exec, graph, 0);
+                cudaGraphDestroy(graph);
+                KN_CUDA(err);
+            }
+            KN_CUDA(cudaGraphLaunch(graph_exec, stream));
+        } else {
+            for (const Step& s : plan->steps) launch_step(s);
+        }
+    }
+
+    void upload_inputs() {
+        for (size_t i = 0; i < pinned_in.size(); i++)
+            if (bytes_in[i])
+                KN_CUDA(cudaMemcpyAsync(device_ptr(plan->inputs[i]), pinned_in[i], bytes_in[i], cudaMemcpyHostToDevice, stream));
+    }
+    void download_outputs() {
+        for (size_t i = 0; i < pinned_out.size(); i++)
+            if (bytes_out[i])
+                KN_CUDA(cudaMemcpyAsync(pinned_out[i], device_ptr(plan->outputs[i]), bytes_out[i], cudaMemcpyDeviceToHost, stream));
+    }
+
+    void evaluate(const void* const* inputs, void* const* outputs) {
+        KN_CUDA(cudaStreamSynchronize(stream));
+        for (size_t i = 0; i < pinned_in.size(); i++) {
+            KN_CHECK(inputs != nullptr && (inputs[i] != nullptr || bytes_in[i] == 0), KN_ERR_INVALID_ARG, "null input buffer");
+            if (bytes_in[i] && inputs[i] != pinned_in[i]) memcpy(pinned_in[i], inputs[i], bytes_in[i]);
+        }
+        upload_inputs();
+        run_async();
+        download_outputs();
+        KN_CUDA(cudaStreamSynchronize(stream));
+        for (size_t i = 0; i < pinned_out.size(); i++) {
+            KN_CHECK(outputs != nullptr && (outputs[i] != nullptr || bytes_out[i] == 0), KN_ERR_INVALID_ARG, "null output buffer");
+            if (dtype_out[i] == DType::Bool) {
+                const uint8_t* b = (const uint8_t*)pinned_out[i];
+                for (size_t k = 0; k < bytes_out[i]; k++)
+                    KN_CHECK(b[k] <= 1, KN_ERR_INTERNAL, "bool output holds a value other than 0 or 1");
+            }
+            if (bytes_out[i] && outputs[i] != pinned_out[i]) memcpy(outputs[i], pinned_out[i], bytes_out[i]);
+        }
+    }
+};
+
+static std::unique_ptr<Executor> create_executor(int device, const Graph& graph, size_t batch, const kn_options& opts) {
+    int count = 0;
+    cudaError_t cerr = cudaGetDeviceCount(&count);
+    if (cerr != cudaSuccess || count == 0)
+        fail(KN_ERR_NO_DEVICE, std::string("no CUDA device available: ") + cudaGetErrorString(cerr));
+    KN_CHECK(device >= 0 && device < count, KN_ERR_NO_DEVICE, "CUDA device " + std::to_string(device) + " not available");
+
+    auto ex = std::make_unique<Executor>();
+    ex->device = device;
+    DeviceGuard guard(device);
+    ex->plan = make_plan(graph, (int64_t)batch, opts);
+    Plan& plan = *ex->plan;
+    KN_CUDA(cudaStreamCreateWithFlags(&ex->stream, cudaStreamNonBlocking));
+    KN_CUDA(cudaMalloc((void**)&ex->arena, std::max<size_t>(plan.arena_bytes, 256)));
+    KN_CUDA(cudaMalloc((void**)&ex->consts, std::max<size_t>(plan.const_bytes, 256)));
+    if (plan.const_bytes) {
+        // constants cross to the device once, here (kn-cuda-eval/src/planner.rs:331-344)
+        std::vector<uint8_t> staging(plan.const_bytes, 0);
+        for (auto& b : plan.buffers)
+            if (b.kind == BufKind::Const && b.bytes) memcpy(staging.data() + b.arena_offset, b.host_data, b.bytes);
+        KN_CUDA(cudaMemcpy(ex->consts, staging.data(), plan.const_bytes, cudaMemcpyHostToDevice));
+    }
+    for (auto& b : plan.buffers) {   // host copies are no longer needed
+        b.host_data = nullptr;
+        b.owned.reset();
+    }
+    for (size_t i = 0; i < plan.inputs.size(); i++) {
+        size_t bytes = (size_t)plan.inputs[i].ss.size() * dtype_size(plan.inputs[i].dtype);
+        void* p = nullptr;
+        KN_CUDA(cudaHostAlloc(&p, std::max<size_t>(bytes, 16), cudaHostAllocDefault));
+        memset(p, 0, std::max<size_t>(bytes, 16));
+        ex->pinned_in.push_back(p);
+        ex->bytes_in.push_back(bytes);
+        ex->dtype_in.push_back(plan.inputs[i].dtype);
+    }
+    for (size_t i = 0; i < plan.outputs.size(); i++) {
+        size_t bytes = (size_t)plan.outputs[i].ss.size() * dtype_size(plan.outputs[i].dtype);
+        void* p = nullptr;
+        KN_CUDA(cudaHostAlloc(&p, std::max<size_t>(bytes, 16), cudaHostAllocDefault));
+        memset(p, 0, std::max<size_t>(bytes, 16));
+        ex->pinned_out.push_back(p);
+        ex->bytes_out.push_back(bytes);
+        ex->dtype_out.push_back(plan.outputs[i].dtype);
+    }
+    KN_CUDA(cudaMemsetAsync(ex->arena, 0, std::max<size_t>(plan.arena_bytes, 256), ex->stream));
+    ex->patch_pointers();
+    KN_CUDA(cudaStreamSynchronize(ex->stream));
+    return ex;
+}
+
+}  // namespace kn
+
+// ------------------------------------------------------------------------------------------------
+// C ABI
+// ------------------------------------------------------------------------------------------------
+struct kn_graph {
+    std::unique_ptr<kn::Graph> g;
+};
+struct kn_executor {
+    std::unique_ptr<kn::Executor> e;
+};
+
+namespace {
+
+template <typename F>
+int guarded(F&& f) {
+    try {
+        f();
+        return KN_OK;
+    } catch (const kn::Error& e) {
+        kn::g_last_error = e.what();
+        return e.code;
+    } catch (const std::bad_alloc&) {
+        kn::g_last_error = "out of host memory";
+        return KN_ERR_INTERNAL;
+    } catch (const std::exception& e) {
+        kn::g_last_error = e.what();
+        return KN_ERR_INTERNAL;
+    }
+}
+
+kn_options resolve_options(const kn_options* opts) {
+    kn_options o;
+    kn_options_default(&o);
+    if (opts) {
+        KN_CHECK(opts->struct_size == sizeof(kn_options), KN_ERR_INVALID_ARG, "kn_options.struct_size does not match this library");
+        KN_CHECK(opts->math_mode == KN_MATH_TF32 || opts->math_mode == KN_MATH_F32, KN_ERR_INVALID_ARG, "unknown math mode");
+        o = *opts;
+    }
+    return o;
+}
+
+int write_text(const std::string& text, char* buf, size_t cap, size_t* needed) {
+    if (needed) *needed = text.size();
+    if (buf && cap) {
+        size_t n = std::min(cap - 1, text.size());
+        memcpy(buf, text.data(), n);
+        buf[n] = 0;
+    }
+    return KN_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* kn_last_error(void) { return kn::g_last_error.c_str(); }
+
+int kn_version(void) { return 1000; }
+
+int kn_options_default(kn_options* opts) {
+    if (!opts) return KN_ERR_INVALID_ARG;
+    opts->struct_size = sizeof(kn_options);
+    opts->math_mode = KN_MATH_TF32;
+    opts->use_cuda_graph = 1;
+    opts->reserved = 0;
+    return KN_OK;
+}
+
+int kn_device_count(int* count) {
+    return guarded([&] {
+        KN_CHECK(count != nullptr, KN_ERR_INVALID_ARG, "null count");
+        int n = 0;
+        cudaError_t err = cudaGetDeviceCount(&n);
+        if (err != cudaSuccess) {
+            cudaGetLastError();
+            n = 0;
+        }
+        *count = n;
+    });
+}
+
+int kn_graph_from_blob(const void* bytes, size_t len, kn_graph** out) {
+    return guarded([&] {
+        KN_CHECK(out != nullptr, KN_ERR_INVALID_ARG, "null out pointer");
+        *out = nullptr;
+        auto g = kn::Graph::parse(bytes, len);
+        *out = new kn_graph{std::move(g)};
+    });
+}
+
+void kn_graph_destroy(kn_graph* graph) { delete graph; }
+
+int kn_graph_io_count(const kn_graph* graph, int* n_inputs, int* n_outputs, int* n_values) {
+    return guarded([&] {
+        KN_CHECK(graph != nullptr, KN_ERR_INVALID_ARG, "null graph");
+        if (n_inputs) *n_inputs = (int)graph->g->inputs.size();
+        if (n_outputs) *n_outputs = (int)graph->g->outputs.size();
+        if (n_values) *n_values = (int)graph->g->values.size();
+    });
+}
+
+int kn_plan_describe(const kn_graph* graph, size_t batch_size, const kn_options* opts, char* buf, size_t cap, size_t* needed) {
+    return guarded([&] {
+        KN_CHECK(graph != nullptr, KN_ERR_INVALID_ARG, "null graph");
+        kn_options o = resolve_options(opts);
+        auto plan = kn::make_plan(*graph->g, (int64_t)batch_size, o);
+        write_text(plan->describe(), buf, cap, needed);
+    });
+}
+
+int kn_executor_create(int device, const kn_graph* graph, size_t batch_size, const kn_options* opts, kn_executor** out) {
+    return guarded([&] {
+        KN_CHECK(out != nullptr, KN_ERR_INVALID_ARG, "null out pointer");
+        *out = nullptr;
+        KN_CHECK(graph != nullptr, KN_ERR_INVALID_ARG, "null graph");
+        kn_options o = resolve_options(opts);
+        auto e = kn::create_executor(device, *graph->g, batch_size, o);
+        *out = new kn_executor{std::move(e)};
+    });
+}
+
+void kn_executor_destroy(kn_executor* exec) { delete exec; }
+
+int kn_executor_io_count(const kn_executor* exec, int* n_inputs, int* n_outputs) {
+    return guarded([&] {
+        KN_CHECK(exec != nullptr, KN_ERR_INVALID_ARG, "null executor");
+        if (n_inputs) *n_inputs = (int)exec->e->plan->inputs.size();
+        if (n_outputs) *n_outputs = (int)exec->e->plan->outputs.size();
+    });
+}
+
+static const kn::PlanTensor& io_tensor(const kn_executor* exec, int is_output, int index) {
+    KN_CHECK(exec != nullptr, KN_ERR_INVALID_ARG, "null executor");
+    const auto& list = is_output ? exec->e->plan->outputs : exec->e->plan->inputs;
+    KN_CHECK(index >= 0 && (size_t)index < list.size(), KN_ERR_INVALID_ARG, "input/output index out of range");
+    return list[index];
+}
+
+int kn_executor_io_info(const kn_executor* exec, int is_output, int index, kn_tensor_info* info) {
+    return guarded([&] {
+        KN_CHECK(info != nullptr, KN_ERR_INVALID_ARG, "null info");
+        const kn::PlanTensor& t = io_tensor(exec, is_output, index);
+        KN_CHECK(t.ss.rank() <= KN_MAX_RANK, KN_ERR_UNSUPPORTED, "input/output rank above 8");
+        info->dtype = (int32_t)t.dtype;
+        info->rank = t.ss.rank();
+        for (int d = 0; d < KN_MAX_RANK; d++) info->dims[d] = d < t.ss.rank() ? t.ss.shape[d] : 1;
+        info->bytes = (uint64_t)t.ss.size() * kn::dtype_size(t.dtype);
+    });
+}
+
+int kn_executor_evaluate(kn_executor* exec, const void* const* inputs, void* const* outputs) {
+    return guarded([&] {
+        KN_CHECK(exec != nullptr, KN_ERR_INVALID_ARG, "null executor");
+        kn::DeviceGuard guard(exec->e->device);
+        exec->e->evaluate(inputs, outputs);
+    });
+}
+
+int kn_executor_run_async(kn_executor* exec) {
+    return guarded([&] {
+        KN_CHECK(exec != nullptr, KN_ERR_INVALID_ARG, "null executor");
+        kn::DeviceGuard guard(exec->e->device);
+        exec->e->run_async();
+    });
+}
+
+int kn_executor_synchronize(kn_executor* exec) {
+    return guarded([&] {
+        KN_CHECK(exec != nullptr, KN_ERR_INVALID_ARG, "null executor");
+        kn::DeviceGuard guard(exec->e->device);
+        KN_CUDA(cudaStreamSynchronize(exec->e->stream));
+    });
+}
+
+int kn_executor_stream(kn_executor* exec, void** stream) {
+    return guarded([&] {
+        KN_CHECK(exec != nullptr && stream != nullptr, KN_ERR_INVALID_ARG, "null argument");
+        *stream = (void*)exec->e->stream;
+    });
+}
+
+int kn_executor_host_buffer(kn_executor* exec, int is_output, int index, void** ptr, uint64_t* bytes) {
+    return guarded([&] {
+        io_tensor(exec, is_output, index);
+        if (ptr) *ptr = is_output ? exec->e->pinned_out[index] : exec->e->pinned_in[index];
+        if (bytes) *bytes = is_output ? exec->e->bytes_out[index] : exec->e->bytes_in[index];
+    });
+}
+
+int kn_executor_device_buffer(kn_executor* exec, int is_output, int index, void** ptr, uint64_t* bytes) {
+    return guarded([&] {
+        const kn::PlanTensor& t = io_tensor(exec, is_output, index);
+        if (ptr) *ptr = exec->e->device_ptr(t);
+        if (bytes) *bytes = is_output ? exec->e->bytes_out[index] : exec->e->bytes_in[index];
+    });
+}
+
+int kn_executor_upload_inputs(kn_executor* exec) {
+    return guarded([&] {
+        KN_CHECK(exec != nullptr, KN_ERR_INVALID_ARG, "null executor");
+        kn::DeviceGuard guard(exec->e->device);
+        exec->e->upload_inputs();
+    });
+}
+
+int kn_executor_download_outputs(kn_executor* exec) {
+    return guarded([&] {
+        KN_CHECK(exec != nullptr, KN_ERR_INVALID_ARG, "null executor");
+        kn::DeviceGuard guard(exec->e->device);
+        exec->e->download_outputs();
+    });
+}
+
+int kn_executor_mem_usage(const kn_executor* exec, kn_mem_usage* usage) {
+    return guarded([&] {
+        KN_CHECK(exec != nullptr && usage != nullptr, KN_ERR_INVALID_ARG, "null argument");
+        *usage = exec->e->plan->mem;
+    });
+}
+
+int kn_executor_step_count(const kn_executor* exec, int* steps, int* launches) {
+    return guarded([&] {
+        KN_CHECK(exec != nullptr, KN_ERR_INVALID_ARG, "null executor");
+        if (steps) *steps = (int)exec->e->plan->steps.size();
+        if (launches) *launches = exec->e->launches;
+    });
+}
+
+int kn_executor_set_profile(kn_executor* exec, int enable) {
+    return guarded([&] {
+        KN_CHECK(exec != nullptr, KN_ERR_INVALID_ARG, "null executor");
+        exec->e->profile = enable != 0;
+    });
+}
+
+int kn_executor_last_profile(kn_executor* exec, char* buf, size_t cap, size_t* needed) {
+    return guarded([&] {
+        KN_CHECK(exec != nullptr, KN_ERR_INVALID_ARG, "null executor");
+        const kn::Plan& plan = *exec->e->plan;
+        std::ostringstream os;
+        double total[(int)kn::StepKind::COUNT] = {0};
+        double total_tc = 0;
+        const auto& us = exec->e->step_us;
+        for (size_t i = 0; i < plan.steps.size() && i < us.size(); i++) {
+            const kn::Step& s = plan.steps[i];
+            os << i << " " << kn::step_kind_name(s.kind) << (s.tensor_core ? "/tc" : "") << " " << us[i] << " "
+               << (uint64_t)s.alg_bytes << " " << (uint64_t)s.flops << " " << s.desc << "\n";
+            total[(int)s.kind] += us[i];
+            if (s.tensor_core) total_tc += us[i];
+        }
+        for (int k = 0; k < (int)kn::StepKind::COUNT; k++)
+            os << "total " << kn::step_kind_name((kn::StepKind)k) << " " << total[k] << "\n";
+        os << "total tensor_core " << total_tc << "\n";
+        write_text(os.str(), buf, cap, needed);
+    });
+}
+
+int kn_scalar_unary(int unary_op, int from_dtype, int to_dtype, uint64_t x, uint64_t* out) {
+    return guarded([&] {
+        KN_CHECK(out != nullptr, KN_ERR_INVALID_ARG, "null out");
+        KN_CHECK(unary_op >= 0 && unary_op <= (int)kn::UnaryOp::BitCast, KN_ERR_INVALID_ARG, "unknown unary op");
+        KN_CHECK(from_dtype >= 0 && from_dtype < (int)kn::DType::COUNT && to_dtype >= 0 && to_dtype < (int)kn::DType::COUNT,
+                 KN_ERR_INVALID_ARG, "unknown dtype");
+        *out = kn::unary_bits((kn::UnaryOp)unary_op, (kn::DType)from_dtype, (kn::DType)to_dtype, x);
+    });
+}
+
+int kn_scalar_binary(int binary_op, int dtype, uint64_t a, uint64_t b, uint64_t* out) {
+    return guarded([&] {
+        KN_CHECK(out != nullptr, KN_ERR_INVALID_ARG, "null out");
+        KN_CHECK(binary_op >= 0 && binary_op <= (int)kn::BinaryOp::Pow, KN_ERR_INVALID_ARG, "unknown binary op");
+        KN_CHECK(dtype >= 0 && dtype < (int)kn::DType::COUNT, KN_ERR_INVALID_ARG, "unknown dtype");
+        *out = kn::binary_bits((kn::BinaryOp)binary_op, (kn::DType)dtype, a, b);
+    });
+}
+
+}  // extern "C"

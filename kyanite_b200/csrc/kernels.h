@@ -1,0 +1,129 @@
+// Launch-parameter blocks of the executor's kernels and their host launchers.
+//
+// A parameter block is plain data: the planner fills it without touching CUDA, the executor patches
+// the device pointers in once the arena exists, and the launcher passes it by value as a
+// `__grid_constant__` kernel argument (so it is also baked into a captured CUDA graph node).
+// Strides are in elements and may be zero or negative.  Every tensor of rank > KN_DEV_MAX_RANK
+// after axis merging is rejected by the planner.
+#pragma once
+#include <cstdint>
+
+#include "common.h"
+
+struct CUstream_st;
+typedef CUstream_st* cudaStream_t;
+
+namespace kn {
+
+constexpr int DEV_MAX_RANK = 8;
+constexpr int SCALAR_MAX_OPERANDS = 10;
+constexpr int SCALAR_MAX_INSTR = 40;
+
+enum class Activation : int32_t { None = 0, Relu = 1 };
+
+// ---- fused elementwise ("scalar") kernel: replaces kn-cuda-eval/src/autokernel/scalar.{rs,cu}.
+// The body is a small register program instead of generated C source: slot i < n_loads holds the
+// element loaded from operand load_operand[i]; instruction k writes slot n_loads + k.
+struct ScalarInstr {
+    uint8_t kind;    // 0 = constant, 1 = unary, 2 = binary
+    uint8_t op;      // UnaryOp / BinaryOp
+    uint8_t dtype;   // result dtype
+    uint8_t from;    // operand dtype (differs from `dtype` only for casts)
+    uint8_t a, b;    // operand slots
+    uint16_t pad;
+    uint64_t imm;    // constant: canonical element pattern
+};
+
+struct ScalarParams {
+    int32_t rank, n_operands, n_loads, n_instr, n_stores;
+    int32_t vec4;    // 1: every operand is f32 with innermost stride 1 (or 0) and 16-byte aligned rows
+    int64_t total;   // element count
+    int64_t dims[DEV_MAX_RANK];
+    void* ptr[SCALAR_MAX_OPERANDS];
+    int64_t strides[SCALAR_MAX_OPERANDS][DEV_MAX_RANK];
+    uint8_t dtype[SCALAR_MAX_OPERANDS];
+    uint8_t load_operand[SCALAR_MAX_OPERANDS];
+    uint8_t store_operand[SCALAR_MAX_OPERANDS];
+    uint8_t store_slot[SCALAR_MAX_OPERANDS];
+    ScalarInstr instr[SCALAR_MAX_INSTR];
+};
+
+// ---- reduce: replaces autokernel/reduce.{rs,cu}
+struct ReduceParams {
+    const void* in;
+    void* out;
+    uint8_t dtype, op;       // DType, ReduceOp
+    int32_t kept_rank, red_rank;
+    int64_t n_out, n_red;
+    int64_t kept_dims[DEV_MAX_RANK], kept_in_strides[DEV_MAX_RANK], kept_out_strides[DEV_MAX_RANK];
+    int64_t red_dims[DEV_MAX_RANK], red_strides[DEV_MAX_RANK];
+    float mean_scale;        // Mean: the divisor, n_red as float (sum / count like the CPU path)
+};
+
+// ---- softmax / layernorm over one axis: replace autokernel/{softmax,layernorm}.{rs,cu}
+struct RowParams {
+    const float* in0;
+    const float* in1;        // layernorm only, may be null; same strides as in0
+    float* out;
+    int32_t outer_rank;
+    int64_t rows, len;
+    int64_t outer_dims[DEV_MAX_RANK], in_strides[DEV_MAX_RANK], out_strides[DEV_MAX_RANK];
+    int64_t in_axis_stride, out_axis_stride;
+    float scale;             // softmax: input scale folded in
+    float alpha0, alpha1;    // layernorm: x = alpha0 * in0 + alpha1 * in1
+    float eps;
+};
+
+// ---- gather along one axis with rank-1 indices: replaces autokernel/gather.{rs,cu}
+struct GatherParams {
+    const void* in;
+    const void* idx;
+    void* out;
+    int32_t rank, axis, elem_size;
+    uint8_t idx_dtype;
+    int64_t total;           // output elements
+    int64_t axis_in_size;    // valid index range; anything else writes 0
+    int64_t idx_stride;
+    int64_t out_dims[DEV_MAX_RANK], in_strides[DEV_MAX_RANK], out_strides[DEV_MAX_RANK];
+};
+
+// ---- batched matrix multiply with fused epilogue  C = act(A.B + add1 + add2)
+// replaces cublasSgemmStridedBatched (kn-cuda-sys/src/wrapper/group.rs:120-171) plus the scalar
+// kernel that followed it for bias / activation.
+struct GemmParams {
+    const float* a;
+    const float* b;
+    float* c;
+    const float* add1;       // optional addends with their own (broadcastable) strides
+    const float* add2;
+    int64_t batch, m, n, k;
+    int64_t sa[3], sb[3], sc[3], s1[3], s2[3];   // (batch, row, col) strides
+    int32_t act;
+    int32_t round_tf32;      // round outputs to TF32 (they only feed tensor-core contractions)
+};
+
+// ---- 2D convolution (cross-correlation, zero padding) with fused epilogue
+// out = act(conv(in, filter) + add1 + add2); replaces cudnnConvolutionBiasActivationForward
+// (kn-cuda-sys/src/wrapper/operation.rs:162-240).
+struct ConvParams {
+    const float* in;
+    const float* filter;
+    float* out;
+    const float* add1;
+    const float* add2;
+    int32_t n, c, h, w, k, r, s, oh, ow, stride_y, stride_x, pad_y, pad_x;
+    int64_t s_in[4], s_f[4], s_out[4], s1[4], s2[4];
+    int32_t act;
+    int32_t round_tf32;
+};
+
+// All launchers enqueue on `stream` and return the cudaError_t of the launch as int.
+int launch_scalar(const ScalarParams& p, cudaStream_t stream);
+int launch_reduce(const ReduceParams& p, cudaStream_t stream);
+int launch_softmax(const RowParams& p, cudaStream_t stream);
+int launch_layernorm(const RowParams& p, cudaStream_t stream);
+int launch_gather(const GatherParams& p, cudaStream_t stream);
+int launch_gemm_simt(const GemmParams& p, cudaStream_t stream);
+int launch_conv_simt(const ConvParams& p, cudaStream_t stream);
+
+}  // namespace kn

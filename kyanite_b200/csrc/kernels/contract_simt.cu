@@ -1,0 +1,161 @@
+// Exact-f32 contraction kernels on the SIMT pipes: batched matrix multiply and 2D convolution
+// (as an implicit GEMM) with the fused `act(x + add1 + add2)` epilogue.
+//
+// These serve KN_MATH_F32 and every contraction shape the tensor-core kernels do not take
+// (arbitrary operand strides, stride/padding combinations, tiny extents).  Operands are addressed
+// through their element strides, so transposed, sliced, flipped or broadcast inputs need no copy.
+#include <cuda_runtime.h>
+
+#include "../kernels.h"
+
+namespace kn {
+
+namespace {
+
+constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
+
+__device__ __forceinline__ float apply_epilogue(float v, int act, int round_tf32) {
+    if (act == (int)Activation::Relu) v = fmaxf(v, 0.0f);
+    if (round_tf32) {
+        uint32_t u;
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v));
+        v = __uint_as_float(u);
+    }
+    return v;
+}
+
+struct GemmProblem {
+    GemmParams p;
+    __device__ int64_t M() const { return p.m; }
+    __device__ int64_t N() const { return p.n; }
+    __device__ int64_t K() const { return p.k; }
+    __device__ bool a_k_fast() const { return p.sa[2] == 1; }
+    __device__ bool b_k_fast() const { return p.sb[1] == 1; }
+    __device__ float load_a(int64_t b, int64_t m, int64_t k) const { return p.a[b * p.sa[0] + m * p.sa[1] + k * p.sa[2]]; }
+    __device__ float load_b(int64_t b, int64_t k, int64_t n) const { return p.b[b * p.sb[0] + k * p.sb[1] + n * p.sb[2]]; }
+    __device__ void store(int64_t b, int64_t m, int64_t n, float acc) const {
+        if (p.add1) acc += p.add1[b * p.s1[0] + m * p.s1[1] + n * p.s1[2]];
+        if (p.add2) acc += p.add2[b * p.s2[0] + m * p.s2[1] + n * p.s2[2]];
+        p.c[b * p.sc[0] + m * p.sc[1] + n * p.sc[2]] = apply_epilogue(acc, p.act, p.round_tf32);
+    }
+};
+
+struct ConvProblem {
+    ConvParams p;
+    __device__ int64_t M() const { return (int64_t)p.n * p.oh * p.ow; }
+    __device__ int64_t N() const { return p.k; }
+    __device__ int64_t K() const { return (int64_t)p.c * p.r * p.s; }
+    __device__ bool a_k_fast() const { return false; }
+    __device__ bool b_k_fast() const { return true; }
+    __device__ float load_a(int64_t, int64_t m, int64_t kk) const {
+        const int ox = (int)(m % p.ow);
+        const int64_t t = m / p.ow;
+        const int oy = (int)(t % p.oh);
+        const int64_t img = t / p.oh;
+        const int fx = (int)(kk % p.s);
+        const int64_t u = kk / p.s;
+        const int fy = (int)(u % p.r);
+        const int64_t ci = u / p.r;
+        const int iy = oy * p.stride_y + fy - p.pad_y;
+        const int ix = ox * p.stride_x + fx - p.pad_x;
+        if (iy < 0 || iy >= p.h || ix < 0 || ix >= p.w) return 0.0f;
+        return p.in[img * p.s_in[0] + ci * p.s_in[1] + iy * p.s_in[2] + ix * p.s_in[3]];
+    }
+    __device__ float load_b(int64_t, int64_t kk, int64_t n) const {
+        const int fx = (int)(kk % p.s);
+        const int64_t u = kk / p.s;
+        const int fy = (int)(u % p.r);
+        const int64_t ci = u / p.r;
+        return p.filter[n * p.s_f[0] + ci * p.s_f[1] + fy * p.s_f[2] + fx * p.s_f[3]];
+    }
+    __device__ void store(int64_t, int64_t m, int64_t n, float acc) const {
+        const int64_t ox = m % p.ow;
+        const int64_t t = m / p.ow;
+        const int64_t oy = t % p.oh;
+        const int64_t img = t / p.oh;
+        if (p.add1) acc += p.add1[img * p.s1[0] + n * p.s1[1] + oy * p.s1[2] + ox * p.s1[3]];
+        if (p.add2) acc += p.add2[img * p.s2[0] + n * p.s2[1] + oy * p.s2[2] + ox * p.s2[3]];
+        p.out[img * p.s_out[0] + n * p.s_out[1] + oy * p.s_out[2] + ox * p.s_out[3]] = apply_epilogue(acc, p.act, p.round_tf32);
+    }
+};
+
+template <class Problem>
+__global__ void __launch_bounds__(256) contract_simt_kernel(const __grid_constant__ Problem prob) {
+    __shared__ float As[BK][BM + 4];
+    __shared__ float Bs[BK][BN + 4];
+    const int64_t M = prob.M(), N = prob.N(), K = prob.K();
+    const int64_t batch = blockIdx.z;
+    const int64_t m0 = (int64_t)blockIdx.x * BM, n0 = (int64_t)blockIdx.y * BN;
+    const int tid = threadIdx.x;
+    const int tx = tid % (BN / TN), ty = tid / (BN / TN);
+    const bool a_k_fast = prob.a_k_fast(), b_k_fast = prob.b_k_fast();
+
+    float acc[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; i++)
+#pragma unroll
+        for (int j = 0; j < TN; j++) acc[i][j] = 0.0f;
+
+    for (int64_t k0 = 0; k0 < K; k0 += BK) {
+#pragma unroll
+        for (int i = 0; i < (BM * BK) / 256; i++) {
+            const int e = tid + i * 256;
+            const int mm = a_k_fast ? e / BK : e % BM;
+            const int kk = a_k_fast ? e % BK : e / BM;
+            const int64_t m = m0 + mm, k = k0 + kk;
+            As[kk][mm] = (m < M && k < K) ? prob.load_a(batch, m, k) : 0.0f;
+        }
+#pragma unroll
+        for (int i = 0; i < (BN * BK) / 256; i++) {
+            const int e = tid + i * 256;
+            const int nn = b_k_fast ? e / BK : e % BN;
+            const int kk = b_k_fast ? e % BK : e / BN;
+            const int64_t n = n0 + nn, k = k0 + kk;
+            Bs[kk][nn] = (n < N && k < K) ? prob.load_b(batch, k, n) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BK; kk++) {
+            float a[TM], b[TN];
+#pragma unroll
+            for (int i = 0; i < TM; i++) a[i] = As[kk][ty * TM + i];
+#pragma unroll
+            for (int j = 0; j < TN; j++) b[j] = Bs[kk][tx * TN + j];
+#pragma unroll
+            for (int i = 0; i < TM; i++)
+#pragma unroll
+                for (int j = 0; j < TN; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < TM; i++) {
+        const int64_t m = m0 + ty * TM + i;
+        if (m >= M) continue;
+#pragma unroll
+        for (int j = 0; j < TN; j++) {
+            const int64_t n = n0 + tx * TN + j;
+            if (n < N) prob.store(batch, m, n, acc[i][j]);
+        }
+    }
+}
+
+template <class Problem>
+int launch(const Problem& prob, int64_t M, int64_t N, int64_t batch, cudaStream_t stream) {
+    if (M == 0 || N == 0 || batch == 0) return 0;
+    const int64_t gx = (M + BM - 1) / BM, gy = (N + BN - 1) / BN;
+    if (gy > 65535 || batch > 65535 || gx > 0x7FFFFFFFll) return (int)cudaErrorInvalidValue;
+    dim3 grid((unsigned)gx, (unsigned)gy, (unsigned)batch);
+    contract_simt_kernel<Problem><<<grid, 256, 0, stream>>>(prob);
+    return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+int launch_gemm_simt(const GemmParams& p, cudaStream_t stream) { return launch(GemmProblem{p}, p.m, p.n, p.batch, stream); }
+
+int launch_conv_simt(const ConvParams& p, cudaStream_t stream) {
+    return launch(ConvProblem{p}, (int64_t)p.n * p.oh * p.ow, p.k, 1, stream);
+}
+
+}  // namespace kn

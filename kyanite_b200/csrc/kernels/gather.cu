@@ -1,0 +1,57 @@
+// Gather along one axis with rank-1 indices of any integer type:
+//   out[..., j, ...] = in[..., idx[j], ...]
+// Elements move as raw 1/2/4/8-byte words, so the result is bit-exact for every dtype.  An index
+// outside [0, axis size) writes zero, like the reference's `gather_kernel`
+// (kn-cuda-eval/src/autokernel/gather.cu:46-49); its CPU path rejects such indices instead.
+#include <cuda_runtime.h>
+
+#include "../kernels.h"
+#include "../scalar_ops.h"
+
+namespace kn {
+
+namespace {
+
+template <typename W>
+__global__ void __launch_bounds__(256) gather_kernel(const __grid_constant__ GatherParams p) {
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < p.total; idx += step) {
+        int64_t rem = idx, in_off = 0, out_off = 0;
+        bool valid = true;
+        for (int d = p.rank - 1; d >= 0; d--) {
+            const int64_t dim = p.out_dims[d];
+            const int64_t q = rem / dim;
+            int64_t i = rem - q * dim;
+            rem = q;
+            out_off += i * p.out_strides[d];
+            if (d == p.axis) {
+                const uint64_t raw = load_bits(p.idx, (DType)p.idx_dtype, i * p.idx_stride);
+                // signed types arrive sign-extended, so a negative index is a huge unsigned value
+                valid = raw < (uint64_t)p.axis_in_size;
+                i = valid ? (int64_t)raw : 0;
+            }
+            in_off += i * p.in_strides[d];
+        }
+        W v = valid ? ((const W*)p.in)[in_off] : W(0);
+        ((W*)p.out)[out_off] = v;
+    }
+}
+
+}  // namespace
+
+int launch_gather(const GatherParams& p, cudaStream_t stream) {
+    if (p.total == 0) return 0;
+    int64_t blocks = (p.total + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    const unsigned grid = (unsigned)blocks;
+    switch (p.elem_size) {
+        case 1: gather_kernel<uint8_t><<<grid, 256, 0, stream>>>(p); break;
+        case 2: gather_kernel<uint16_t><<<grid, 256, 0, stream>>>(p); break;
+        case 4: gather_kernel<uint32_t><<<grid, 256, 0, stream>>>(p); break;
+        case 8: gather_kernel<uint64_t><<<grid, 256, 0, stream>>>(p); break;
+        default: return (int)cudaErrorInvalidValue;
+    }
+    return (int)cudaGetLastError();
+}
+
+}  // namespace kn

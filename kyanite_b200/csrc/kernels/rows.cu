@@ -1,0 +1,299 @@
+// Row-wise kernels: reduce, softmax, layernorm.  They take the place of the reference's
+// `reduce_kernel`, `softmax_kernel` and `layernorm_kernel` templates
+// (kn-cuda-eval/src/autokernel/{reduce,softmax,layernorm}.cu).
+//
+// softmax / layernorm keep the whole row in registers between the statistics pass and the
+// normalising pass, so global memory is read once and written once (the reference kernels re-read
+// the row two or three times).  A row is owned by a warp (len <= 1024) or by a block
+// (len <= 8192); longer rows fall back to a block that re-reads the row from L2 / HBM.
+#include <cuda_runtime.h>
+
+#include "../kernels.h"
+#include "../scalar_ops.h"
+
+namespace kn {
+
+namespace {
+
+constexpr unsigned kFull = 0xFFFFFFFFu;
+
+__device__ __forceinline__ void decode_offsets(int64_t idx, int rank, const int64_t* dims, const int64_t* s0,
+                                                const int64_t* s1, int64_t& o0, int64_t& o1) {
+    o0 = 0;
+    o1 = 0;
+    for (int d = rank - 1; d >= 0; d--) {
+        const int64_t dim = dims[d];
+        const int64_t q = idx / dim;
+        const int64_t i = idx - q * dim;
+        idx = q;
+        o0 += i * s0[d];
+        o1 += i * s1[d];
+    }
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(kFull, v, o));
+    return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(kFull, v, o);
+    return v;
+}
+
+// Reduction across the `TPR` threads that own one row.  TPR == 32: a warp.  TPR == blockDim.x: the
+// whole block through shared memory.
+template <int TPR, bool IS_MAX>
+__device__ __forceinline__ float row_reduce(float v, float* smem) {
+    v = IS_MAX ? warp_max(v) : warp_sum(v);
+    if (TPR == 32) return v;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();   // protect smem reuse between consecutive reductions
+    if (lane == 0) smem[warp] = v;
+    __syncthreads();
+    float r = lane < (TPR >> 5) ? smem[lane] : (IS_MAX ? -INFINITY : 0.0f);
+    return IS_MAX ? warp_max(r) : warp_sum(r);
+}
+
+// ------------------------------------------------------------------ softmax
+template <int TPR, int ITEMS>
+__global__ void __launch_bounds__(256) softmax_cached_kernel(const __grid_constant__ RowParams p) {
+    __shared__ float smem[8];
+    const int rows_per_block = blockDim.x / TPR;
+    const int64_t row = (int64_t)blockIdx.x * rows_per_block + threadIdx.x / TPR;
+    const int t = threadIdx.x % TPR;
+    const bool active = row < p.rows;   // whole warps / blocks share `row`, so reductions stay converged
+    int64_t oi = 0, oo = 0;
+    if (active) decode_offsets(row, p.outer_rank, p.outer_dims, p.in_strides, p.out_strides, oi, oo);
+    const float* in = p.in0 + oi;
+    float* out = p.out + oo;
+
+    float v[ITEMS];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < ITEMS; i++) {
+        const int64_t e = (int64_t)i * TPR + t;
+        v[i] = (active && e < p.len) ? in[e * p.in_axis_stride] * p.scale : -INFINITY;
+        mx = fmaxf(mx, v[i]);
+    }
+    mx = row_reduce<TPR, true>(mx, smem);
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < ITEMS; i++) {
+        const int64_t e = (int64_t)i * TPR + t;
+        v[i] = expf(v[i] - mx);
+        if (e < p.len) sum += v[i];
+    }
+    sum = row_reduce<TPR, false>(sum, smem);
+    if (!active) return;
+#pragma unroll
+    for (int i = 0; i < ITEMS; i++) {
+        const int64_t e = (int64_t)i * TPR + t;
+        if (e < p.len) out[e * p.out_axis_stride] = v[i] / sum;
+    }
+}
+
+// rows longer than a block can keep in registers: three sweeps over global memory
+__global__ void __launch_bounds__(256) softmax_streaming_kernel(const __grid_constant__ RowParams p) {
+    __shared__ float smem[8];
+    const int64_t row = blockIdx.x;
+    int64_t oi, oo;
+    decode_offsets(row, p.outer_rank, p.outer_dims, p.in_strides, p.out_strides, oi, oo);
+    const float* in = p.in0 + oi;
+    float* out = p.out + oo;
+    float mx = -INFINITY;
+    for (int64_t e = threadIdx.x; e < p.len; e += 256) mx = fmaxf(mx, in[e * p.in_axis_stride] * p.scale);
+    mx = row_reduce<256, true>(mx, smem);
+    float sum = 0.f;
+    for (int64_t e = threadIdx.x; e < p.len; e += 256) sum += expf(in[e * p.in_axis_stride] * p.scale - mx);
+    sum = row_reduce<256, false>(sum, smem);
+    for (int64_t e = threadIdx.x; e < p.len; e += 256)
+        out[e * p.out_axis_stride] = expf(in[e * p.in_axis_stride] * p.scale - mx) / sum;
+}
+
+// ------------------------------------------------------------------ layernorm
+__device__ __forceinline__ float ln_load(const RowParams& p, const float* in0, const float* in1, int64_t e) {
+    float x = p.alpha0 * in0[e * p.in_axis_stride];
+    if (in1 != nullptr) x += p.alpha1 * in1[e * p.in_axis_stride];
+    return x;
+}
+
+template <int TPR, int ITEMS>
+__global__ void __launch_bounds__(256) layernorm_cached_kernel(const __grid_constant__ RowParams p) {
+    __shared__ float smem[8];
+    const int rows_per_block = blockDim.x / TPR;
+    const int64_t row = (int64_t)blockIdx.x * rows_per_block + threadIdx.x / TPR;
+    const int t = threadIdx.x % TPR;
+    const bool active = row < p.rows;
+    int64_t oi = 0, oo = 0;
+    if (active) decode_offsets(row, p.outer_rank, p.outer_dims, p.in_strides, p.out_strides, oi, oo);
+    const float* in0 = p.in0 + oi;
+    const float* in1 = p.in1 ? p.in1 + oi : nullptr;
+    float* out = p.out + oo;
+
+    float v[ITEMS];
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < ITEMS; i++) {
+        const int64_t e = (int64_t)i * TPR + t;
+        v[i] = (active && e < p.len) ? ln_load(p, in0, in1, e) : 0.f;
+        sum += v[i];
+    }
+    const float n = (float)p.len;
+    const float mean = row_reduce<TPR, false>(sum, smem) / n;
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < ITEMS; i++) {
+        const int64_t e = (int64_t)i * TPR + t;
+        v[i] -= mean;
+        if (e < p.len) sq += v[i] * v[i];
+    }
+    const float var = row_reduce<TPR, false>(sq, smem) / n;
+    const float denom = sqrtf(var + p.eps);
+    if (!active) return;
+#pragma unroll
+    for (int i = 0; i < ITEMS; i++) {
+        const int64_t e = (int64_t)i * TPR + t;
+        if (e < p.len) out[e * p.out_axis_stride] = v[i] / denom;
+    }
+}
+
+__global__ void __launch_bounds__(256) layernorm_streaming_kernel(const __grid_constant__ RowParams p) {
+    __shared__ float smem[8];
+    const int64_t row = blockIdx.x;
+    int64_t oi, oo;
+    decode_offsets(row, p.outer_rank, p.outer_dims, p.in_strides, p.out_strides, oi, oo);
+    const float* in0 = p.in0 + oi;
+    const float* in1 = p.in1 ? p.in1 + oi : nullptr;
+    float* out = p.out + oo;
+    const float n = (float)p.len;
+    float sum = 0.f;
+    for (int64_t e = threadIdx.x; e < p.len; e += 256) sum += ln_load(p, in0, in1, e);
+    const float mean = row_reduce<256, false>(sum, smem) / n;
+    float sq = 0.f;
+    for (int64_t e = threadIdx.x; e < p.len; e += 256) {
+        const float d = ln_load(p, in0, in1, e) - mean;
+        sq += d * d;
+    }
+    const float var = row_reduce<256, false>(sq, smem) / n;
+    const float denom = sqrtf(var + p.eps);
+    for (int64_t e = threadIdx.x; e < p.len; e += 256) out[e * p.out_axis_stride] = (ln_load(p, in0, in1, e) - mean) / denom;
+}
+
+// ------------------------------------------------------------------ reduce
+__device__ __forceinline__ uint64_t reduce_identity(ReduceOp op, DType d) {
+    const bool is_float = d == DType::F32 || d == DType::F64 || d == DType::F16;
+    switch (op) {
+        case ReduceOp::Sum: case ReduceOp::Mean: return is_float ? float_pattern(d, 0.0) : 0ull;
+        case ReduceOp::Prod: return is_float ? float_pattern(d, 1.0) : 1ull;
+        default: break;
+    }
+    const bool want_max_value = op == ReduceOp::Min;   // identity of min is the largest value
+    if (is_float) return float_pattern(d, want_max_value ? (double)INFINITY : -(double)INFINITY);
+    switch (d) {
+        case DType::I8: return (uint64_t)(int64_t)(want_max_value ? INT8_MAX : INT8_MIN);
+        case DType::I16: return (uint64_t)(int64_t)(want_max_value ? INT16_MAX : INT16_MIN);
+        case DType::I32: return (uint64_t)(int64_t)(want_max_value ? INT32_MAX : INT32_MIN);
+        case DType::I64: return (uint64_t)(want_max_value ? INT64_MAX : INT64_MIN);
+        case DType::U8: return want_max_value ? 0xFFull : 0ull;
+        case DType::U16: return want_max_value ? 0xFFFFull : 0ull;
+        case DType::U32: return want_max_value ? 0xFFFFFFFFull : 0ull;
+        case DType::U64: return want_max_value ? ~0ull : 0ull;
+        default: return want_max_value ? 1ull : 0ull;   // Bool
+    }
+}
+
+__device__ __forceinline__ BinaryOp reduce_binary(ReduceOp op) {
+    switch (op) {
+        case ReduceOp::Sum: case ReduceOp::Mean: return BinaryOp::Add;
+        case ReduceOp::Prod: return BinaryOp::Mul;
+        case ReduceOp::Max: return BinaryOp::Max;
+        default: return BinaryOp::Min;
+    }
+}
+
+// TPO threads cooperate on one output element.
+template <int TPO>
+__global__ void __launch_bounds__(256) reduce_kernel(const __grid_constant__ ReduceParams p) {
+    __shared__ uint64_t smem[8];
+    const int outs_per_block = 256 / TPO;
+    const int64_t o = (int64_t)blockIdx.x * outs_per_block + threadIdx.x / TPO;
+    const int t = threadIdx.x % TPO;
+    const bool active = o < p.n_out;
+    const DType d = (DType)p.dtype;
+    const ReduceOp rop = (ReduceOp)p.op;
+    const BinaryOp bop = reduce_binary(rop);
+
+    int64_t oi = 0, oo = 0;
+    if (active) decode_offsets(o, p.kept_rank, p.kept_dims, p.kept_in_strides, p.kept_out_strides, oi, oo);
+
+    uint64_t acc = reduce_identity(rop, d);
+    if (active) {
+        for (int64_t r = t; r < p.n_red; r += TPO) {
+            int64_t ri = 0, dummy = 0;
+            decode_offsets(r, p.red_rank, p.red_dims, p.red_strides, p.red_strides, ri, dummy);
+            acc = binary_bits(bop, d, acc, load_bits(p.in, d, oi + ri));
+        }
+    }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) acc = binary_bits(bop, d, acc, __shfl_xor_sync(kFull, acc, s));
+    if (TPO > 32) {
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        if (lane == 0) smem[warp] = acc;
+        __syncthreads();
+        acc = lane < (TPO >> 5) ? smem[lane] : reduce_identity(rop, d);
+#pragma unroll
+        for (int s = 16; s > 0; s >>= 1) acc = binary_bits(bop, d, acc, __shfl_xor_sync(kFull, acc, s));
+    }
+    if (active && t == 0) {
+        if (rop == ReduceOp::Mean) acc = f32_to_bits(bits_to_f32(acc) / p.mean_scale);
+        store_bits(p.out, d, oo, acc);
+    }
+}
+
+}  // namespace
+
+#define KN_ROW_DISPATCH(KERNEL, STREAMING)                                                                     \
+    if (p.rows == 0 || p.len == 0) return 0;                                                                   \
+    if (p.rows > 0x7FFFFFFFll) return (int)cudaErrorInvalidValue;                                              \
+    const int64_t len = p.len;                                                                                 \
+    if (len <= 1024) {                                                                                         \
+        const int rows_per_block = 8;                                                                          \
+        const unsigned grid = (unsigned)((p.rows + rows_per_block - 1) / rows_per_block);                      \
+        if (len <= 32) KERNEL<32, 1><<<grid, 256, 0, stream>>>(p);                                             \
+        else if (len <= 64) KERNEL<32, 2><<<grid, 256, 0, stream>>>(p);                                        \
+        else if (len <= 128) KERNEL<32, 4><<<grid, 256, 0, stream>>>(p);                                       \
+        else if (len <= 256) KERNEL<32, 8><<<grid, 256, 0, stream>>>(p);                                       \
+        else if (len <= 512) KERNEL<32, 16><<<grid, 256, 0, stream>>>(p);                                      \
+        else KERNEL<32, 32><<<grid, 256, 0, stream>>>(p);                                                      \
+    } else if (len <= 8192) {                                                                                  \
+        const unsigned grid = (unsigned)p.rows;                                                                \
+        if (len <= 2048) KERNEL<256, 8><<<grid, 256, 0, stream>>>(p);                                          \
+        else if (len <= 4096) KERNEL<256, 16><<<grid, 256, 0, stream>>>(p);                                    \
+        else KERNEL<256, 32><<<grid, 256, 0, stream>>>(p);                                                     \
+    } else {                                                                                                   \
+        STREAMING<<<(unsigned)p.rows, 256, 0, stream>>>(p);                                                    \
+    }                                                                                                          \
+    return (int)cudaGetLastError();
+
+int launch_softmax(const RowParams& p, cudaStream_t stream) { KN_ROW_DISPATCH(softmax_cached_kernel, softmax_streaming_kernel) }
+
+int launch_layernorm(const RowParams& p, cudaStream_t stream) {
+    KN_ROW_DISPATCH(layernorm_cached_kernel, layernorm_streaming_kernel)
+}
+
+int launch_reduce(const ReduceParams& p, cudaStream_t stream) {
+    if (p.n_out == 0) return 0;
+    if (p.n_red >= 2048) {
+        if (p.n_out > 0x7FFFFFFFll) return (int)cudaErrorInvalidValue;
+        reduce_kernel<256><<<(unsigned)p.n_out, 256, 0, stream>>>(p);
+    } else {
+        const int64_t grid = (p.n_out + 7) / 8;
+        if (grid > 0x7FFFFFFFll) return (int)cudaErrorInvalidValue;
+        reduce_kernel<32><<<(unsigned)grid, 256, 0, stream>>>(p);
+    }
+    return (int)cudaGetLastError();
+}
+
+}  // namespace kn

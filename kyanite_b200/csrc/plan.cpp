@@ -1,0 +1,965 @@
+#include "plan.h"
+
+#include <pthread.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <map>
+#include <optional>
+#include <sstream>
+
+#include "scalar_ops.h"
+
+namespace kn {
+
+const char* step_kind_name(StepKind k) {
+    static const char* names[] = {"Scalar", "Reduce", "Softmax", "Layernorm", "Gather", "Gemm", "Conv"};
+    return (int)k < 7 ? names[(int)k] : "?";
+}
+
+// ------------------------------------------------------------------------------------------------
+// PlanTensor
+// ------------------------------------------------------------------------------------------------
+PlanTensor PlanTensor::with(StridedShape s, int64_t extra_offset) const {
+    PlanTensor r = *this;
+    r.ss = std::move(s);
+    r.offset += extra_offset;
+    return r;
+}
+
+PlanTensor PlanTensor::slice(int axis, int64_t start, int64_t end, int64_t step) const {
+    StridedShape s = ss.slice(axis, start, end, step);
+    // an empty slice addresses nothing; keep the offset inside the buffer
+    int64_t extra = s.shape[axis] == 0 ? 0 : start * ss.strides[axis];
+    return with(std::move(s), extra);
+}
+
+PlanTensor PlanTensor::flip(int axis) const {
+    StridedShape s = ss.flip(axis);
+    int64_t len = ss.shape[axis];
+    int64_t extra = len == 0 ? 0 : (len - 1) * ss.strides[axis];
+    return with(std::move(s), extra);
+}
+
+std::string PlanTensor::str() const {
+    return std::string(dtype_name(dtype)) + "@b" + std::to_string(buf) + "+" + std::to_string(offset) + ss.str();
+}
+
+namespace {
+
+double touched_bytes(const PlanTensor& t) {
+    double n = 1;
+    for (int i = 0; i < t.ss.rank(); i++)
+        if (t.ss.strides[i] != 0 || t.ss.shape[i] == 0) n *= (double)t.ss.shape[i];
+    return n * dtype_size(t.dtype);
+}
+
+// Merge axes that are contiguous for every operand and drop unit axes, so kernels decode as few
+// coordinates per element as possible.  `strides[o]` are per-operand strides over `dims`.
+void coalesce_axes(std::vector<int64_t>& dims, std::vector<std::vector<int64_t>>& strides) {
+    std::vector<int64_t> nd;
+    std::vector<std::vector<int64_t>> ns(strides.size());
+    for (size_t d = 0; d < dims.size(); d++) {
+        if (dims[d] == 1) continue;
+        bool merged = false;
+        if (!nd.empty()) {
+            bool can = true;
+            for (size_t o = 0; o < strides.size(); o++)
+                if (ns[o].back() != strides[o][d] * dims[d]) { can = false; break; }
+            if (can) {
+                nd.back() *= dims[d];
+                for (size_t o = 0; o < strides.size(); o++) ns[o].back() = strides[o][d];
+                merged = true;
+            }
+        }
+        if (!merged) {
+            nd.push_back(dims[d]);
+            for (size_t o = 0; o < strides.size(); o++) ns[o].push_back(strides[o][d]);
+        }
+    }
+    if (nd.empty()) {
+        nd.push_back(1);
+        for (auto& s : ns) s.push_back(0);
+    }
+    dims = std::move(nd);
+    strides = std::move(ns);
+}
+
+// slot reference while a scalar program is being built: loads and instructions are numbered
+// separately and merged into one slot space at the end
+struct Ref {
+    bool is_load = false;
+    int index = -1;
+};
+
+struct ScalarBlock {
+    std::vector<PlanTensor> loads;
+    struct PendingInstr {
+        ScalarInstr in;
+        Ref a, b;
+    };
+    std::vector<PendingInstr> instrs;
+    std::map<int, Ref> value_ref;   // graph value -> slot (common sub-expressions evaluate once)
+
+    Ref load(const PlanTensor& t) {
+        for (size_t i = 0; i < loads.size(); i++)
+            if (loads[i].same_storage(t)) return Ref{true, (int)i};
+        loads.push_back(t);
+        return Ref{true, (int)loads.size() - 1};
+    }
+    Ref constant(Scalar c) {
+        PendingInstr p{};
+        p.in.kind = 0;
+        p.in.dtype = (uint8_t)c.dtype;
+        p.in.from = (uint8_t)c.dtype;
+        p.in.imm = c.bits;
+        instrs.push_back(p);
+        return Ref{false, (int)instrs.size() - 1};
+    }
+    Ref unary(UnaryOp op, DType from, DType to, Ref a) {
+        PendingInstr p{};
+        p.in.kind = 1;
+        p.in.op = (uint8_t)op;
+        p.in.dtype = (uint8_t)to;
+        p.in.from = (uint8_t)from;
+        p.a = a;
+        instrs.push_back(p);
+        return Ref{false, (int)instrs.size() - 1};
+    }
+    Ref binary(BinaryOp op, DType d, Ref a, Ref b) {
+        PendingInstr p{};
+        p.in.kind = 2;
+        p.in.op = (uint8_t)op;
+        p.in.dtype = (uint8_t)d;
+        p.in.from = (uint8_t)d;
+        p.a = a;
+        p.b = b;
+        instrs.push_back(p);
+        return Ref{false, (int)instrs.size() - 1};
+    }
+};
+
+class Planner {
+   public:
+    Planner(const Graph& g, int64_t batch, const kn_options& opts, Plan& plan)
+        : g_(g), batch_(batch), opts_(opts), plan_(plan), map_(g.values.size()), chain_cache_(g.values.size(), -2) {}
+
+    void run() {
+        plan_.batch = batch_;
+        plan_.opts = opts_;
+        plan_.inputs.resize(g_.inputs.size());
+        // every graph input gets a buffer, used or not (planner.rs:117-121)
+        for (int v : g_.inputs) visit(v);
+        for (int v : g_.outputs) {
+            PlanTensor t = ensure_simple(visit(v), v);
+            buffer(t.buf).always_live = true;
+            plan_.outputs.push_back(t);
+            plan_.output_shapes.push_back(t.ss.shape);
+        }
+        for (auto& t : plan_.inputs) plan_.input_shapes.push_back(t.ss.shape);
+        assign_memory();
+    }
+
+   private:
+    const Graph& g_;
+    int64_t batch_;
+    kn_options opts_;
+    Plan& plan_;
+    std::vector<std::optional<PlanTensor>> map_;
+    std::vector<int> chain_cache_;
+
+    BufferInfo& buffer(int b) { return plan_.buffers[b]; }
+
+    std::vector<int64_t> shape_of(int v) const {
+        std::vector<int64_t> s = g_.eval_shape(v, batch_);
+        for (int64_t d : s) KN_CHECK(d >= 0, KN_ERR_SHAPE, "negative dimension");
+        return s;
+    }
+
+    // ---------------------------------------------------------------- buffers
+    PlanTensor alloc_shared(const std::vector<int64_t>& shape, DType dtype, int value) {
+        BufferInfo b;
+        b.kind = BufKind::Shared;
+        int64_t n = 1;
+        for (int64_t d : shape) n *= d;
+        b.bytes = (size_t)n * dtype_size(dtype);
+        b.value = value;
+        plan_.buffers.push_back(b);
+        PlanTensor t;
+        t.buf = (int)plan_.buffers.size() - 1;
+        t.dtype = dtype;
+        t.ss = StridedShape::simple(shape);
+        return t;
+    }
+
+    PlanTensor alloc_const(const std::vector<int64_t>& shape, DType dtype, int value, const uint8_t* data,
+                           std::shared_ptr<std::vector<uint8_t>> owned) {
+        BufferInfo b;
+        b.kind = BufKind::Const;
+        int64_t n = 1;
+        for (int64_t d : shape) n *= d;
+        b.bytes = (size_t)n * dtype_size(dtype);
+        b.value = value;
+        b.host_data = owned ? owned->data() : data;
+        b.owned = std::move(owned);
+        plan_.buffers.push_back(b);
+        PlanTensor t;
+        t.buf = (int)plan_.buffers.size() - 1;
+        t.dtype = dtype;
+        t.ss = StridedShape::simple(shape);
+        return t;
+    }
+
+    // ---------------------------------------------------------------- steps
+    void push_step(Step&& s) {
+        for (auto& t : s.operands) KN_CHECK(t.ss.rank() <= 64, KN_ERR_INTERNAL, "operand rank");
+        s.alg_bytes = 0;
+        for (size_t i = 0; i < s.operands.size(); i++) {
+            bool dup = false;
+            for (size_t j = 0; j < i; j++) dup = dup || s.operands[j].same_storage(s.operands[i]);
+            if (!dup) s.alg_bytes += touched_bytes(s.operands[i]);
+        }
+        plan_.steps.push_back(std::move(s));
+    }
+
+    // Emit one fused elementwise kernel.  `stores` pairs a destination tensor with the slot to write.
+    void emit_scalar(ScalarBlock& block, const std::vector<std::pair<PlanTensor, Ref>>& stores, int value,
+                     const std::string& desc) {
+        KN_CHECK(!stores.empty(), KN_ERR_INTERNAL, "scalar step without a store");
+        const std::vector<int64_t>& shape = stores[0].first.ss.shape;
+        int64_t total = 1;
+        for (int64_t d : shape) total *= d;
+        if (total == 0) return;
+
+        Step s;
+        s.kind = StepKind::Scalar;
+        s.value = value;
+        s.desc = desc;
+        for (auto& t : block.loads) {
+            KN_CHECK(t.ss.shape == shape, KN_ERR_INTERNAL, "scalar operand shape mismatch");
+            s.operands.push_back(t);
+            s.writes.push_back(0);
+        }
+        for (auto& st : stores) {
+            KN_CHECK(st.first.ss.shape == shape, KN_ERR_INTERNAL, "scalar store shape mismatch");
+            s.operands.push_back(st.first);
+            s.writes.push_back(1);
+        }
+        KN_CHECK((int)s.operands.size() <= SCALAR_MAX_OPERANDS, KN_ERR_UNSUPPORTED, "too many operands in one fused elementwise step");
+        KN_CHECK((int)block.instrs.size() <= SCALAR_MAX_INSTR, KN_ERR_UNSUPPORTED, "fused elementwise program too long");
+
+        std::vector<int64_t> dims = shape;
+        std::vector<std::vector<int64_t>> strides;
+        for (auto& t : s.operands) strides.push_back(t.ss.strides);
+        coalesce_axes(dims, strides);
+        KN_CHECK((int)dims.size() <= DEV_MAX_RANK, KN_ERR_UNSUPPORTED,
+                 "elementwise step needs more than 8 non-mergeable axes");
+
+        ScalarParams& p = s.scalar;
+        p.rank = (int)dims.size();
+        p.n_operands = (int)s.operands.size();
+        p.n_loads = (int)block.loads.size();
+        p.n_instr = (int)block.instrs.size();
+        p.n_stores = (int)stores.size();
+        p.total = total;
+        for (int d = 0; d < p.rank; d++) p.dims[d] = dims[d];
+        for (int o = 0; o < p.n_operands; o++) {
+            p.dtype[o] = (uint8_t)s.operands[o].dtype;
+            for (int d = 0; d < p.rank; d++) p.strides[o][d] = strides[o][d];
+        }
+        auto slot_of = [&](Ref r) { return r.is_load ? r.index : p.n_loads + r.index; };
+        for (int l = 0; l < p.n_loads; l++) p.load_operand[l] = (uint8_t)l;
+        for (int k = 0; k < p.n_instr; k++) {
+            ScalarInstr in = block.instrs[k].in;
+            if (in.kind >= 1) in.a = (uint8_t)slot_of(block.instrs[k].a);
+            if (in.kind == 2) in.b = (uint8_t)slot_of(block.instrs[k].b);
+            p.instr[k] = in;
+        }
+        for (int st = 0; st < p.n_stores; st++) {
+            p.store_operand[st] = (uint8_t)(p.n_loads + st);
+            p.store_slot[st] = (uint8_t)slot_of(stores[st].second);
+        }
+
+        // 128-bit path: all f32, innermost axis contiguous (or broadcast for loads), 16-byte aligned
+        bool vec = dims.back() % 4 == 0;
+        for (int k = 0; k < p.n_instr && vec; k++)
+            vec = p.instr[k].dtype == (uint8_t)DType::F32 && p.instr[k].from == (uint8_t)DType::F32;
+        for (int o = 0; o < p.n_operands && vec; o++) {
+            const PlanTensor& t = s.operands[o];
+            int64_t inner = strides[o].back();
+            bool is_store = o >= p.n_loads;
+            if (t.dtype != DType::F32 || !(inner == 1 || (inner == 0 && !is_store))) { vec = false; break; }
+            if (inner == 1) {
+                if (t.offset % 4 != 0) vec = false;
+                for (int d = 0; d + 1 < p.rank; d++)
+                    if (strides[o][d] % 4 != 0) vec = false;
+            }
+        }
+        p.vec4 = vec ? 1 : 0;
+        push_step(std::move(s));
+    }
+
+    void emit_copy(const PlanTensor& src, const PlanTensor& dst, int value) {
+        ScalarBlock block;
+        Ref r = block.load(src);
+        emit_scalar(block, {{dst, r}}, value, "copy");
+    }
+
+    PlanTensor ensure_simple(const PlanTensor& t, int value) {
+        if (t.ss.has_simple_strides()) return t;
+        PlanTensor dense = alloc_shared(t.ss.shape, t.dtype, value);
+        emit_copy(t, dense, value);
+        return dense;
+    }
+
+    // ---------------------------------------------------------------- visiting
+    PlanTensor visit(int v) {
+        if (map_[v]) return *map_[v];
+        PlanTensor t = visit_new(v);
+        KN_CHECK(t.ss.shape == shape_of(v), KN_ERR_INTERNAL, "planned shape differs from graph shape");
+        KN_CHECK(t.dtype == g_.values[v].dtype, KN_ERR_INTERNAL, "planned dtype differs from graph dtype");
+        map_[v] = t;
+        return t;
+    }
+
+    PlanTensor visit_new(int v) {
+        if (auto fused = try_fused_contraction(v)) return *fused;
+        const ValueInfo& info = g_.values[v];
+        std::vector<int64_t> shape = shape_of(v);
+        switch (info.op) {
+            case OpKind::Input: {
+                PlanTensor t = alloc_shared(shape, info.dtype, v);
+                buffer(t.buf).always_live = true;
+                plan_.inputs[info.input_index] = t;
+                return t;
+            }
+            case OpKind::Constant:
+                return alloc_const(shape, info.dtype, v, info.const_data, nullptr);
+            case OpKind::View: {
+                PlanTensor in = visit(info.inputs[0]);
+                if (auto s = in.ss.view(shape)) return in.with(*s);
+                PlanTensor dense = alloc_shared(in.ss.shape, in.dtype, v);
+                emit_copy(in, dense, v);
+                auto s = dense.ss.view(shape);
+                KN_CHECK(s.has_value(), KN_ERR_INTERNAL, "view of a dense tensor failed");
+                return dense.with(*s);
+            }
+            case OpKind::Broadcast: {
+                PlanTensor in = visit(info.inputs[0]);
+                return in.with(in.ss.broadcast(shape));
+            }
+            case OpKind::Permute: {
+                PlanTensor in = visit(info.inputs[0]);
+                return in.with(in.ss.permute(info.permutation));
+            }
+            case OpKind::Slice: {
+                PlanTensor in = visit(info.inputs[0]);
+                return in.slice(info.axis, info.slice_start, info.slice_end, info.slice_step);
+            }
+            case OpKind::Flip: {
+                PlanTensor in = visit(info.inputs[0]);
+                return in.flip(info.axis);
+            }
+            case OpKind::Gather: return visit_gather(v);
+            case OpKind::Concat: {
+                std::vector<PlanTensor> ins;
+                for (int i : info.inputs) ins.push_back(visit(i));
+                PlanTensor out = alloc_shared(shape, info.dtype, v);
+                int64_t start = 0;
+                for (auto& in : ins) {
+                    int64_t n = in.ss.shape[info.axis];
+                    emit_copy(in, out.slice(info.axis, start, start + n, 1), v);
+                    start += n;
+                }
+                KN_CHECK(start == shape[info.axis], KN_ERR_SHAPE, "concat sizes do not add up");
+                return out;
+            }
+            case OpKind::Conv: case OpKind::MatMul:
+                fail(KN_ERR_UNSUPPORTED, std::string(op_name(info.op)) + " is only supported for f32 operands");
+            case OpKind::Unary: case OpKind::Binary: return visit_scalar(v);
+            case OpKind::Softmax: return visit_softmax(v);
+            case OpKind::Layernorm: return visit_layernorm(v);
+            case OpKind::Reduce: return visit_reduce(v);
+            default: fail(KN_ERR_INTERNAL, "unknown operation");
+        }
+    }
+
+    // ---------------------------------------------------------------- elementwise fusion
+    // (kn-cuda-eval/src/planner.rs:835-923.)  Differences from the reference: a value whose users
+    // are not all inside this expression is materialised once and loaded instead of being
+    // recomputed per user, shared sub-expressions inside the block evaluate once, and a block that
+    // outgrows the kernel's program size is split at a sub-expression.
+    PlanTensor visit_scalar(int root) {
+        // count edges from Unary/Binary nodes reachable from the root, to find values used only here
+        std::map<int, int> tree_uses;
+        {
+            std::vector<int> stack{root};
+            std::map<int, bool> seen;
+            while (!stack.empty()) {
+                int x = stack.back();
+                stack.pop_back();
+                if (seen[x]) continue;
+                seen[x] = true;
+                const ValueInfo& xi = g_.values[x];
+                if (xi.op != OpKind::Unary && xi.op != OpKind::Binary) continue;
+                for (int in : xi.inputs) {
+                    tree_uses[in]++;
+                    stack.push_back(in);
+                }
+            }
+        }
+        // Inline as deep as the kernel's program and operand limits allow; on overflow retry with a
+        // shallower cut (operands materialised by a failed attempt stay planned and are reused).
+        static const int kDepths[] = {1 << 20, 12, 6, 3, 1, 0};
+        for (int max_depth : kDepths) {
+            ScalarBlock block;
+            Ref r = build_scalar(root, 0, max_depth, block, tree_uses);
+            if ((int)block.loads.size() + 1 > SCALAR_MAX_OPERANDS || (int)block.instrs.size() > SCALAR_MAX_INSTR) continue;
+            PlanTensor out = alloc_shared(shape_of(root), g_.values[root].dtype, root);
+            emit_scalar(block, {{out, r}}, root, "fused");
+            return out;
+        }
+        fail(KN_ERR_INTERNAL, "elementwise operation does not fit one kernel");
+    }
+
+    Ref build_scalar(int v, int depth, int max_depth, ScalarBlock& block, const std::map<int, int>& tree_uses) {
+        const bool is_root = depth == 0;
+        if (!is_root) {
+            auto cached = block.value_ref.find(v);
+            if (cached != block.value_ref.end()) return cached->second;
+            if (map_[v]) return block.load(*map_[v]);
+        }
+        const ValueInfo& info = g_.values[v];
+        bool is_scalar_op = info.op == OpKind::Unary || info.op == OpKind::Binary;
+        Ref result;
+        if (!is_root && !is_scalar_op) {
+            if (auto c = g_.as_single_const(v)) result = block.constant(*c);
+            else result = block.load(visit(v));
+        } else if (!is_root && (depth > max_depth || !can_inline(v, tree_uses))) {
+            if (auto c = g_.as_single_const(v)) result = block.constant(*c);
+            else result = block.load(visit(v));
+        } else if (info.op == OpKind::Unary) {
+            Ref a = build_scalar(info.inputs[0], depth + 1, max_depth, block, tree_uses);
+            result = block.unary(info.unary_op, info.cast_from, info.dtype, a);
+        } else {
+            Ref a = build_scalar(info.inputs[0], depth + 1, max_depth, block, tree_uses);
+            Ref b = build_scalar(info.inputs[1], depth + 1, max_depth, block, tree_uses);
+            result = block.binary(info.binary_op, info.dtype, a, b);
+        }
+        block.value_ref[v] = result;
+        return result;
+    }
+
+    bool can_inline(int v, const std::map<int, int>& tree_uses) {
+        if (!g_.is_hidden(v)) return false;
+        auto it = tree_uses.find(v);
+        int in_tree = it == tree_uses.end() ? 0 : it->second;
+        if (g_.values[v].non_output_uses != in_tree) return false;
+        // a contraction epilogue takes precedence over inlining (planner.rs:881-893)
+        if (match_epilogue(v).has_value()) return false;
+        return true;
+    }
+
+    // ---------------------------------------------------------------- contraction + epilogue
+    bool is_contraction(int v) const {
+        const ValueInfo& info = g_.values[v];
+        if (info.dtype != DType::F32) return false;
+        if (info.op == OpKind::Conv) return info.shape.size() == 4;
+        if (info.op == OpKind::MatMul) return true;
+        return false;
+    }
+    bool fusable(int v) const { return g_.is_hidden_with_uses(v, 1); }
+
+    // The contraction a chain of single-use Add / View nodes ends in, or -1.
+    int chain_end(int v) {
+        if (chain_cache_[v] != -2) return chain_cache_[v];
+        const ValueInfo& info = g_.values[v];
+        int r = -1;
+        if (is_contraction(v)) {
+            r = v;
+        } else if (info.dtype == DType::F32 && info.op == OpKind::View) {
+            int in = info.inputs[0];
+            if (fusable(in)) r = chain_end(in);
+        } else if (info.dtype == DType::F32 && info.op == OpKind::Binary && info.binary_op == BinaryOp::Add) {
+            for (int side : info.inputs) {
+                if (fusable(side)) {
+                    int e = chain_end(side);
+                    if (e >= 0) { r = e; break; }
+                }
+            }
+        }
+        chain_cache_[v] = r;
+        return r;
+    }
+
+    struct Epilogue {
+        int contraction = -1;
+        Activation act = Activation::None;
+        std::vector<int> addends;
+    };
+
+    // Matches  relu?( add*( view?( conv | matmul ) ) )  rooted at `root`
+    // (generalises try_visit_fused_conv, kn-cuda-eval/src/planner.rs:669-833, to MatMul and to
+    // addends of any broadcast shape).
+    std::optional<Epilogue> match_epilogue(int root) {
+        const ValueInfo& ri = g_.values[root];
+        if (ri.dtype != DType::F32) return std::nullopt;
+        Epilogue e;
+        int curr = root;
+        if (ri.op == OpKind::Binary && ri.binary_op == BinaryOp::Max) {
+            int l = ri.inputs[0], r = ri.inputs[1];
+            if (g_.is_const_zero(r) && fusable(l) && chain_end(l) >= 0) { curr = l; e.act = Activation::Relu; }
+            else if (g_.is_const_zero(l) && fusable(r) && chain_end(r) >= 0) { curr = r; e.act = Activation::Relu; }
+            else return std::nullopt;
+        }
+        if (chain_end(curr) < 0) return std::nullopt;
+        while (!is_contraction(curr)) {
+            const ValueInfo& ci = g_.values[curr];
+            if (ci.op == OpKind::View) {
+                curr = ci.inputs[0];
+            } else {   // Add: continue on the side that reaches the contraction
+                int l = ci.inputs[0], r = ci.inputs[1];
+                int cont, other;
+                if (fusable(l) && chain_end(l) >= 0) { cont = l; other = r; }
+                else { cont = r; other = l; }
+                if (e.addends.size() == 2) return std::nullopt;
+                e.addends.push_back(other);
+                curr = cont;
+            }
+        }
+        e.contraction = curr;
+        return e;
+    }
+
+    std::optional<PlanTensor> try_fused_contraction(int root) {
+        auto m = match_epilogue(root);
+        if (!m) return std::nullopt;
+        const ValueInfo& ci = g_.values[m->contraction];
+        std::vector<int64_t> native = shape_of(m->contraction);
+        std::vector<int64_t> root_shape = shape_of(root);
+
+        // operands first (they may emit steps of their own), then this step
+        PlanTensor x = visit(ci.inputs[0]);
+        PlanTensor w = visit(ci.inputs[1]);
+        std::vector<PlanTensor> addends;
+        for (int a : m->addends) {
+            PlanTensor t = visit(a);
+            auto s = t.ss.view(native);
+            if (!s) {
+                if (m->contraction == root) fail(KN_ERR_INTERNAL, "bare contraction with addends");
+                return std::nullopt;   // planned unfused instead
+            }
+            addends.push_back(t.with(*s));
+        }
+        PlanTensor out = alloc_shared(native, DType::F32, root);
+
+        Step s;
+        s.value = root;
+        s.operands = {x, w, out};
+        s.writes = {0, 0, 1};
+        for (auto& a : addends) {
+            s.operands.push_back(a);
+            s.writes.push_back(0);
+        }
+        if (ci.op == OpKind::MatMul) {
+            KN_CHECK(x.ss.rank() == 3 && w.ss.rank() == 3, KN_ERR_SHAPE, "matmul operands must have rank 3");
+            s.kind = StepKind::Gemm;
+            GemmParams& p = s.gemm;
+            p.batch = x.ss.shape[0];
+            p.m = x.ss.shape[1];
+            p.k = x.ss.shape[2];
+            p.n = w.ss.shape[2];
+            KN_CHECK(w.ss.shape[0] == p.batch && w.ss.shape[1] == p.k, KN_ERR_SHAPE, "matmul operand shapes differ");
+            for (int i = 0; i < 3; i++) {
+                p.sa[i] = x.ss.strides[i];
+                p.sb[i] = w.ss.strides[i];
+                p.sc[i] = out.ss.strides[i];
+                if (addends.size() > 0) p.s1[i] = addends[0].ss.strides[i];
+                if (addends.size() > 1) p.s2[i] = addends[1].ss.strides[i];
+            }
+            p.act = (int32_t)m->act;
+            s.flops = 2.0 * (double)p.batch * (double)p.m * (double)p.n * (double)p.k;
+            s.desc = "matmul b=" + std::to_string(p.batch) + " m=" + std::to_string(p.m) + " n=" + std::to_string(p.n) +
+                     " k=" + std::to_string(p.k);
+        } else {
+            KN_CHECK(x.ss.rank() == 4 && w.ss.rank() == 4, KN_ERR_SHAPE, "conv operands must have rank 4");
+            s.kind = StepKind::Conv;
+            ConvParams& p = s.conv;
+            p.n = (int32_t)x.ss.shape[0];
+            p.c = (int32_t)x.ss.shape[1];
+            p.h = (int32_t)x.ss.shape[2];
+            p.w = (int32_t)x.ss.shape[3];
+            p.k = (int32_t)w.ss.shape[0];
+            p.r = (int32_t)w.ss.shape[2];
+            p.s = (int32_t)w.ss.shape[3];
+            KN_CHECK(w.ss.shape[1] == p.c, KN_ERR_SHAPE, "conv channel mismatch");
+            p.stride_y = ci.stride_y;
+            p.stride_x = ci.stride_x;
+            p.pad_y = ci.pad_y;
+            p.pad_x = ci.pad_x;
+            p.oh = (int32_t)native[2];
+            p.ow = (int32_t)native[3];
+            KN_CHECK(native[0] == p.n && native[1] == p.k, KN_ERR_SHAPE, "conv output shape mismatch");
+            KN_CHECK((p.h + 2 * p.pad_y - p.r) / p.stride_y + 1 == p.oh && (p.w + 2 * p.pad_x - p.s) / p.stride_x + 1 == p.ow,
+                     KN_ERR_SHAPE, "conv output extent does not match stride and padding");
+            for (int i = 0; i < 4; i++) {
+                p.s_in[i] = x.ss.strides[i];
+                p.s_f[i] = w.ss.strides[i];
+                p.s_out[i] = out.ss.strides[i];
+                if (addends.size() > 0) p.s1[i] = addends[0].ss.strides[i];
+                if (addends.size() > 1) p.s2[i] = addends[1].ss.strides[i];
+            }
+            p.act = (int32_t)m->act;
+            s.flops = 2.0 * (double)p.n * p.k * p.c * p.r * p.s * p.oh * p.ow;
+            s.desc = "conv n=" + std::to_string(p.n) + " c=" + std::to_string(p.c) + " hw=" + std::to_string(p.h) + "x" +
+                     std::to_string(p.w) + " k=" + std::to_string(p.k) + " rs=" + std::to_string(p.r) + "x" + std::to_string(p.s);
+        }
+        s.desc += std::string(" +") + std::to_string(addends.size()) + (m->act == Activation::Relu ? " relu" : "");
+        int64_t total = 1;
+        for (int64_t d : native) total *= d;
+        if (total != 0) push_step(std::move(s));
+
+        auto rs = out.ss.view(root_shape);
+        KN_CHECK(rs.has_value(), KN_ERR_INTERNAL, "view of a dense contraction output failed");
+        return out.with(*rs);
+    }
+
+    // ---------------------------------------------------------------- gather
+    PlanTensor visit_gather(int v) {
+        const ValueInfo& info = g_.values[v];
+        PlanTensor in = visit(info.inputs[0]);
+        PlanTensor idx = visit(info.inputs[1]);
+        KN_CHECK(idx.ss.rank() == 1 && dtype_is_int(idx.dtype), KN_ERR_BAD_GRAPH, "gather indices must be a rank-1 integer tensor");
+        PlanTensor out = alloc_shared(shape_of(v), info.dtype, v);
+        KN_CHECK(out.ss.rank() <= DEV_MAX_RANK, KN_ERR_UNSUPPORTED, "gather rank above 8");
+        Step s;
+        s.kind = StepKind::Gather;
+        s.value = v;
+        s.operands = {in, idx, out};
+        s.writes = {0, 0, 1};
+        GatherParams& p = s.gather;
+        p.rank = out.ss.rank();
+        p.axis = info.axis;
+        p.elem_size = dtype_size(info.dtype);
+        p.idx_dtype = (uint8_t)idx.dtype;
+        p.total = out.ss.size();
+        p.axis_in_size = in.ss.shape[info.axis];
+        p.idx_stride = idx.ss.strides[0];
+        for (int d = 0; d < p.rank; d++) {
+            p.out_dims[d] = out.ss.shape[d];
+            p.in_strides[d] = in.ss.strides[d];
+            p.out_strides[d] = out.ss.strides[d];
+        }
+        s.desc = "gather axis=" + std::to_string(info.axis);
+        if (p.total != 0) push_step(std::move(s));
+        return out;
+    }
+
+    // ---------------------------------------------------------------- scale / sum peeling
+    // `const * x` -> (const, x)   (kn-cuda-eval/src/planner.rs:584-604)
+    std::pair<float, PlanTensor> visit_scalable(int v) {
+        const ValueInfo& info = g_.values[v];
+        if (info.op == OpKind::Binary && info.binary_op == BinaryOp::Mul && info.dtype == DType::F32 && !map_[v]) {
+            if (auto c = g_.as_single_const(info.inputs[0])) return {c->as_f32(), visit(info.inputs[1])};
+            if (auto c = g_.as_single_const(info.inputs[1])) return {c->as_f32(), visit(info.inputs[0])};
+        }
+        return {1.0f, visit(v)};
+    }
+
+    void fill_rows(RowParams& p, const PlanTensor& in, const PlanTensor& out, int axis) {
+        KN_CHECK(in.ss.rank() - 1 <= DEV_MAX_RANK, KN_ERR_UNSUPPORTED, "row kernel rank above 9");
+        p.outer_rank = 0;
+        p.rows = 1;
+        for (int d = 0; d < in.ss.rank(); d++) {
+            if (d == axis) continue;
+            if (in.ss.shape[d] == 1) continue;
+            p.outer_dims[p.outer_rank] = in.ss.shape[d];
+            p.in_strides[p.outer_rank] = in.ss.strides[d];
+            p.out_strides[p.outer_rank] = out.ss.strides[d];
+            p.outer_rank++;
+            p.rows *= in.ss.shape[d];
+        }
+        p.len = in.ss.shape[axis];
+        p.in_axis_stride = in.ss.strides[axis];
+        p.out_axis_stride = out.ss.strides[axis];
+    }
+
+    PlanTensor visit_softmax(int v) {
+        const ValueInfo& info = g_.values[v];
+        KN_CHECK(info.dtype == DType::F32, KN_ERR_UNSUPPORTED, "softmax needs f32");
+        auto [scale, in] = visit_scalable(info.inputs[0]);
+        PlanTensor out = alloc_shared(shape_of(v), DType::F32, v);
+        Step s;
+        s.kind = StepKind::Softmax;
+        s.value = v;
+        s.operands = {in, out};
+        s.writes = {0, 1};
+        fill_rows(s.row, in, out, info.axis);
+        s.row.scale = scale;
+        s.desc = "softmax rows=" + std::to_string(s.row.rows) + " len=" + std::to_string(s.row.len);
+        if (out.ss.size() != 0) push_step(std::move(s));
+        return out;
+    }
+
+    // `a*x + b*y` -> the layernorm kernel's two inputs (kn-cuda-eval/src/planner.rs:522-552)
+    PlanTensor visit_layernorm(int v) {
+        const ValueInfo& info = g_.values[v];
+        KN_CHECK(info.dtype == DType::F32, KN_ERR_UNSUPPORTED, "layernorm needs f32");
+        int input = info.inputs[0];
+        const ValueInfo& ii = g_.values[input];
+        float a0 = 1.f, a1 = 0.f;
+        PlanTensor x0;
+        std::optional<PlanTensor> x1;
+        if (ii.op == OpKind::Binary && ii.binary_op == BinaryOp::Add && !map_[input]) {
+            auto [s0, t0] = visit_scalable(ii.inputs[0]);
+            auto [s1, t1] = visit_scalable(ii.inputs[1]);
+            if (t0.ss == t1.ss) {
+                a0 = s0; a1 = s1; x0 = t0; x1 = t1;
+            } else {
+                x0 = visit(input);
+            }
+        } else {
+            auto [s0, t0] = visit_scalable(input);
+            a0 = s0;
+            x0 = t0;
+        }
+        PlanTensor out = alloc_shared(shape_of(v), DType::F32, v);
+        Step s;
+        s.kind = StepKind::Layernorm;
+        s.value = v;
+        s.operands = {x0, out};
+        s.writes = {0, 1};
+        if (x1) {
+            s.operands.push_back(*x1);
+            s.writes.push_back(0);
+        }
+        fill_rows(s.row, x0, out, info.axis);
+        s.row.alpha0 = a0;
+        s.row.alpha1 = a1;
+        s.row.eps = info.eps;
+        s.desc = "layernorm rows=" + std::to_string(s.row.rows) + " len=" + std::to_string(s.row.len) + (x1 ? " +res" : "");
+        if (out.ss.size() != 0) push_step(std::move(s));
+        return out;
+    }
+
+    PlanTensor visit_reduce(int v) {
+        const ValueInfo& info = g_.values[v];
+        PlanTensor in = visit(info.inputs[0]);
+        PlanTensor out = alloc_shared(shape_of(v), info.dtype, v);
+        Step s;
+        s.kind = StepKind::Reduce;
+        s.value = v;
+        s.operands = {in, out};
+        s.writes = {0, 1};
+        ReduceParams& p = s.reduce;
+        p.dtype = (uint8_t)info.dtype;
+        p.op = (uint8_t)info.reduce_op;
+        if (info.reduce_op == ReduceOp::Mean) KN_CHECK(info.dtype == DType::F32, KN_ERR_UNSUPPORTED, "mean needs f32");
+        std::vector<int64_t> kd, ki, ko, rd, rs;
+        int out_axis = 0;
+        for (int d = 0; d < in.ss.rank(); d++) {
+            bool reduced = std::find(info.axes.begin(), info.axes.end(), d) != info.axes.end();
+            if (reduced) {
+                rd.push_back(in.ss.shape[d]);
+                rs.push_back(in.ss.strides[d]);
+            } else {
+                kd.push_back(in.ss.shape[d]);
+                ki.push_back(in.ss.strides[d]);
+                ko.push_back(out.ss.strides[out_axis++]);
+            }
+        }
+        {
+            std::vector<std::vector<int64_t>> st{ki, ko};
+            coalesce_axes(kd, st);
+            ki = st[0];
+            ko = st[1];
+            std::vector<std::vector<int64_t>> rt{rs};
+            coalesce_axes(rd, rt);
+            rs = rt[0];
+        }
+        KN_CHECK((int)kd.size() <= DEV_MAX_RANK && (int)rd.size() <= DEV_MAX_RANK, KN_ERR_UNSUPPORTED, "reduce rank above 8");
+        p.kept_rank = (int)kd.size();
+        p.red_rank = (int)rd.size();
+        p.n_out = 1;
+        p.n_red = 1;
+        for (int d = 0; d < p.kept_rank; d++) {
+            p.kept_dims[d] = kd[d];
+            p.kept_in_strides[d] = ki[d];
+            p.kept_out_strides[d] = ko[d];
+            p.n_out *= kd[d];
+        }
+        for (int d = 0; d < p.red_rank; d++) {
+            p.red_dims[d] = rd[d];
+            p.red_strides[d] = rs[d];
+            p.n_red *= rd[d];
+        }
+        p.mean_scale = (float)p.n_red;
+        s.desc = "reduce out=" + std::to_string(p.n_out) + " red=" + std::to_string(p.n_red);
+        if (out.ss.size() != 0) push_step(std::move(s));
+        return out;
+    }
+
+    // ---------------------------------------------------------------- memory
+    // Live ranges over step indices, then offsets inside one arena: buffers are placed largest
+    // first at the lowest offset that does not collide with an already placed buffer whose live
+    // range overlaps.  (The reference reuses only buffers of identical size and gives each its own
+    // cudaMalloc: kn-cuda-eval/src/planner.rs:134-228.)
+    void assign_memory() {
+        auto& bufs = plan_.buffers;
+        for (size_t i = 0; i < plan_.steps.size(); i++) {
+            for (auto& t : plan_.steps[i].operands) {
+                BufferInfo& b = bufs[t.buf];
+                b.first_step = std::min(b.first_step, (int)i);
+                b.last_step = std::max(b.last_step, (int)i);
+            }
+        }
+        const int n_steps = (int)plan_.steps.size();
+        for (auto& b : bufs) {
+            if (b.always_live) {
+                b.first_step = -1;
+                b.last_step = n_steps;
+            }
+        }
+        auto align = [](size_t x) { return (x + 255) & ~(size_t)255; };
+
+        // constants: packed back to back
+        size_t coff = 0;
+        for (auto& b : bufs) {
+            if (b.kind != BufKind::Const) continue;
+            b.arena_offset = (int64_t)coff;
+            coff += align(std::max<size_t>(b.bytes, 1));
+            plan_.mem.dedicated_bytes += b.bytes;
+        }
+        plan_.const_bytes = coff;
+
+        std::vector<int> order;
+        for (size_t i = 0; i < bufs.size(); i++) {
+            BufferInfo& b = bufs[i];
+            if (b.kind != BufKind::Shared) continue;
+            plan_.mem.hypo_total_bytes += b.bytes;
+            if (b.last_step < b.first_step) {   // never touched by a step
+                if (!b.always_live) { b.arena_offset = 0; continue; }
+            }
+            order.push_back((int)i);
+        }
+        std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return bufs[a].bytes > bufs[b].bytes; });
+        std::vector<int> placed;
+        size_t arena = 0;
+        for (int bi : order) {
+            BufferInfo& b = bufs[bi];
+            size_t size = align(std::max<size_t>(b.bytes, 1));
+            std::vector<std::pair<size_t, size_t>> busy;
+            for (int pj : placed) {
+                BufferInfo& o = bufs[pj];
+                if (o.last_step < b.first_step || b.last_step < o.first_step) continue;
+                busy.push_back({(size_t)o.arena_offset, (size_t)o.arena_offset + align(std::max<size_t>(o.bytes, 1))});
+            }
+            std::sort(busy.begin(), busy.end());
+            size_t off = 0;
+            for (auto& iv : busy) {
+                if (off + size <= iv.first) break;
+                off = std::max(off, iv.second);
+            }
+            b.arena_offset = (int64_t)off;
+            arena = std::max(arena, off + size);
+            placed.push_back(bi);
+        }
+        plan_.arena_bytes = arena;
+        plan_.mem.shared_bytes = arena;
+
+        // lower bound on the arena: the largest set of simultaneously live buffers
+        std::vector<int64_t> delta(n_steps + 3, 0);
+        for (int bi : order) {
+            BufferInfo& b = bufs[bi];
+            delta[b.first_step + 1] += (int64_t)b.bytes;
+            delta[b.last_step + 2] -= (int64_t)b.bytes;
+        }
+        int64_t live = 0, peak = 0;
+        for (int64_t d : delta) {
+            live += d;
+            peak = std::max(peak, live);
+        }
+        plan_.mem.hypo_peak_bytes = (uint64_t)peak;
+        plan_.mem.zero_bytes = 0;
+
+        // every operand must stay inside its buffer
+        for (auto& s : plan_.steps) {
+            for (auto& t : s.operands) {
+                int64_t lo, hi;
+                t.ss.extent(&lo, &hi);
+                if (t.ss.size() == 0) continue;
+                int64_t es = dtype_size(t.dtype);
+                KN_CHECK(t.offset + lo >= 0 && (t.offset + hi + 1) * es <= (int64_t)bufs[t.buf].bytes, KN_ERR_INTERNAL,
+                         "operand reaches outside its buffer: " + t.str());
+            }
+        }
+    }
+};
+
+struct PlanJob {
+    const Graph* g;
+    int64_t batch;
+    kn_options opts;
+    Plan* plan;
+    int code = 0;
+    std::string msg;
+};
+
+void* plan_thread(void* arg) {
+    PlanJob* job = (PlanJob*)arg;
+    try {
+        Planner p(*job->g, job->batch, job->opts, *job->plan);
+        p.run();
+    } catch (const Error& e) {
+        job->code = e.code;
+        job->msg = e.what();
+    } catch (const std::exception& e) {
+        job->code = KN_ERR_INTERNAL;
+        job->msg = e.what();
+    }
+    return nullptr;
+}
+
+}  // namespace
+
+std::unique_ptr<Plan> make_plan(const Graph& graph, int64_t batch, const kn_options& opts) {
+    KN_CHECK(batch >= 0, KN_ERR_INVALID_ARG, "negative batch size");
+    auto plan = std::make_unique<Plan>();
+    PlanJob job{&graph, batch, opts, plan.get()};
+    // The lowering recurses along operand chains; deep graphs (thousands of values in a chain) need
+    // more stack than a caller's thread may have, so it runs on a thread with a large stack.
+    pthread_attr_t attr;
+    pthread_attr_init(&attr);
+    pthread_attr_setstacksize(&attr, (size_t)512 << 20);
+    pthread_t th;
+    int rc = pthread_create(&th, &attr, plan_thread, &job);
+    pthread_attr_destroy(&attr);
+    if (rc != 0) {
+        plan_thread(&job);
+    } else {
+        pthread_join(th, nullptr);
+    }
+    if (job.code != 0) fail(job.code, job.msg);
+    return plan;
+}
+
+std::string Plan::describe() const {
+    std::ostringstream os;
+    os << "plan batch=" << batch << " steps=" << steps.size() << " buffers=" << buffers.size() << " arena_bytes=" << arena_bytes
+       << " const_bytes=" << const_bytes << " hypo_peak=" << mem.hypo_peak_bytes << " hypo_total=" << mem.hypo_total_bytes << "\n";
+    for (size_t i = 0; i < steps.size(); i++) {
+        const Step& s = steps[i];
+        os << "step " << i << " " << step_kind_name(s.kind) << (s.tensor_core ? "/tc" : "") << " value=" << s.value << " " << s.desc;
+        if (s.kind == StepKind::Scalar)
+            os << " loads=" << s.scalar.n_loads << " instr=" << s.scalar.n_instr << " rank=" << s.scalar.rank
+               << (s.scalar.vec4 ? " vec4" : "");
+        os << " bytes=" << (uint64_t)s.alg_bytes << " flops=" << (uint64_t)s.flops << " [";
+        for (size_t o = 0; o < s.operands.size(); o++) os << (o ? " " : "") << (s.writes[o] ? "w:" : "r:") << s.operands[o].str();
+        os << "]\n";
+    }
+    for (size_t i = 0; i < inputs.size(); i++) os << "input " << i << " " << inputs[i].str() << "\n";
+    for (size_t i = 0; i < outputs.size(); i++) os << "output " << i << " " << outputs[i].str() << "\n";
+    return os.str();
+}
+
+}  // namespace kn

@@ -1,0 +1,281 @@
+"""Host-side mirror of the reference's executor interface, over the C ABI.
+
+    CudaDevice(0)                                   kn-cuda-sys/src/wrapper/handle.rs:38-48
+    CudaExecutor(device, graph, batch_size)         kn-cuda-eval/src/executor.rs:61
+    executor.evaluate(inputs) -> outputs            kn-cuda-eval/src/executor.rs:117
+    executor.run_async()                            kn-cuda-eval/src/executor.rs:199
+    Device.cuda(0).prepare(graph, batch).eval(...)  kn-runtime/src/lib.rs:85,120
+
+Same names, argument meaning and error behaviour: wrong input count, shape or dtype raises
+(the reference asserts, executor.rs:118-127); a missing device raises `CudaDeviceNotAvailable`.
+Everything numerical happens inside `libkn_b200.so`; numpy only carries host buffers.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import byref, c_int, c_size_t, c_uint64, c_void_p
+from dataclasses import dataclass
+from typing import List, Optional, Sequence
+
+import numpy as np
+
+from . import _lib
+from ._lib import KnError, KnMemUsage, KnOptions, KnTensorInfo, check
+from .graph import DType, Graph
+
+__all__ = ["CudaDevice", "CudaDeviceNotAvailable", "CudaExecutor", "Device", "PreparedGraph", "MemoryUsage",
+           "plan_describe", "KnError", "MATH_TF32", "MATH_F32"]
+
+MATH_TF32 = _lib.KN_MATH_TF32
+MATH_F32 = _lib.KN_MATH_F32
+
+
+class CudaDeviceNotAvailable(RuntimeError):
+    pass
+
+
+def _options(math_mode: Optional[int], use_cuda_graph: Optional[bool]) -> KnOptions:
+    opts = KnOptions()
+    check(_lib.load().kn_options_default(byref(opts)))
+    if math_mode is not None:
+        opts.math_mode = int(math_mode)
+    if use_cuda_graph is not None:
+        opts.use_cuda_graph = 1 if use_cuda_graph else 0
+    return opts
+
+
+class _GraphHandle:
+    def __init__(self, graph):
+        blob = graph if isinstance(graph, (bytes, bytearray)) else graph.to_bytes()
+        self.ptr = c_void_p()
+        buf = (ctypes.c_char * len(blob)).from_buffer_copy(blob)
+        check(_lib.load().kn_graph_from_blob(ctypes.cast(buf, c_void_p), len(blob), byref(self.ptr)))
+
+    def close(self):
+        if self.ptr:
+            _lib.load().kn_graph_destroy(self.ptr)
+            self.ptr = c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def plan_describe(graph, batch_size: int, math_mode: Optional[int] = None) -> str:
+    """Text dump of the planned step list; needs no GPU."""
+    lib = _lib.load()
+    h = _GraphHandle(graph)
+    try:
+        opts = _options(math_mode, None)
+        needed = c_size_t()
+        check(lib.kn_plan_describe(h.ptr, batch_size, byref(opts), None, 0, byref(needed)))
+        buf = ctypes.create_string_buffer(needed.value + 1)
+        check(lib.kn_plan_describe(h.ptr, batch_size, byref(opts), buf, needed.value + 1, byref(needed)))
+        return buf.value.decode()
+    finally:
+        h.close()
+
+
+@dataclass(frozen=True)
+class CudaDevice:
+    index: int = 0
+
+    def __post_init__(self):
+        if not (0 <= self.index < CudaDevice.device_count()):
+            raise CudaDeviceNotAvailable(f"CUDA device {self.index} not available")
+
+    @staticmethod
+    def device_count() -> int:
+        n = c_int()
+        check(_lib.load().kn_device_count(byref(n)))
+        return n.value
+
+    @staticmethod
+    def all() -> List["CudaDevice"]:
+        return [CudaDevice(i) for i in range(CudaDevice.device_count())]
+
+
+@dataclass
+class MemoryUsage:
+    dedicated_bytes: int
+    shared_bytes: int
+    zero_bytes: int
+    hypo_peak_bytes: int
+    hypo_total_bytes: int
+
+
+class CudaExecutor:
+    def __init__(self, device, graph, batch_size: int, math_mode: Optional[int] = None,
+                 use_cuda_graph: Optional[bool] = None):
+        self._lib = _lib.load()
+        self._ptr = c_void_p()
+        index = device.index if isinstance(device, CudaDevice) else int(device)
+        self.device = index
+        self.batch_size = int(batch_size)
+        h = _GraphHandle(graph)
+        try:
+            opts = _options(math_mode, use_cuda_graph)
+            status = self._lib.kn_executor_create(index, h.ptr, self.batch_size, byref(opts), byref(self._ptr))
+            if status == 6:
+                raise CudaDeviceNotAvailable(self._lib.kn_last_error().decode())
+            check(status)
+        finally:
+            h.close()
+        n_in, n_out = c_int(), c_int()
+        check(self._lib.kn_executor_io_count(self._ptr, byref(n_in), byref(n_out)))
+        self._in_info = [self._io_info(0, i) for i in range(n_in.value)]
+        self._out_info = [self._io_info(1, i) for i in range(n_out.value)]
+        self.host_inputs = [self._host_array(0, i) for i in range(n_in.value)]
+        self.host_outputs = [self._host_array(1, i) for i in range(n_out.value)]
+
+    # ---------------------------------------------------------------- info
+    def _io_info(self, is_output: int, index: int):
+        info = KnTensorInfo()
+        check(self._lib.kn_executor_io_info(self._ptr, is_output, index, byref(info)))
+        shape = tuple(info.dims[d] for d in range(info.rank))
+        return shape, DType(info.dtype), int(info.bytes)
+
+    def _host_array(self, is_output: int, index: int) -> np.ndarray:
+        """numpy view of the pinned staging buffer (no copy)."""
+        shape, dtype, nbytes = (self._out_info if is_output else self._in_info)[index]
+        ptr, size = c_void_p(), c_uint64()
+        check(self._lib.kn_executor_host_buffer(self._ptr, is_output, index, byref(ptr), byref(size)))
+        if nbytes == 0:
+            return np.zeros(shape, dtype=dtype.np)
+        raw = (ctypes.c_uint8 * nbytes).from_address(ptr.value)
+        return np.frombuffer(raw, dtype=dtype.np).reshape(shape)
+
+    @property
+    def input_shapes(self):
+        return [s for s, _, _ in self._in_info]
+
+    @property
+    def output_shapes(self):
+        return [s for s, _, _ in self._out_info]
+
+    @property
+    def mem_usage(self) -> MemoryUsage:
+        u = KnMemUsage()
+        check(self._lib.kn_executor_mem_usage(self._ptr, byref(u)))
+        return MemoryUsage(u.dedicated_bytes, u.shared_bytes, u.zero_bytes, u.hypo_peak_bytes, u.hypo_total_bytes)
+
+    def step_count(self):
+        steps, launches = c_int(), c_int()
+        check(self._lib.kn_executor_step_count(self._ptr, byref(steps), byref(launches)))
+        return steps.value, launches.value
+
+    def device_buffer(self, is_output: bool, index: int):
+        ptr, size = c_void_p(), c_uint64()
+        check(self._lib.kn_executor_device_buffer(self._ptr, int(is_output), index, byref(ptr), byref(size)))
+        return ptr.value, size.value
+
+    def stream(self) -> int:
+        s = c_void_p()
+        check(self._lib.kn_executor_stream(self._ptr, byref(s)))
+        return s.value or 0
+
+    # ---------------------------------------------------------------- running
+    def evaluate(self, inputs: Sequence[np.ndarray]) -> List[np.ndarray]:
+        """Copies inputs to the device, runs the graph, returns fresh host arrays."""
+        if len(inputs) != len(self._in_info):
+            raise ValueError(f"Wrong input count, expected {len(self._in_info)} but got {len(inputs)}")
+        arrays = []
+        for i, (x, (shape, dtype, _)) in enumerate(zip(inputs, self._in_info)):
+            x = np.asarray(x)
+            if tuple(x.shape) != shape:
+                raise ValueError(f"Wrong shape for input {i}: expected {shape}, got {tuple(x.shape)}")
+            if x.dtype != dtype.np:
+                raise ValueError(f"Wrong dtype for input {i}: expected {dtype.np}, got {x.dtype}")
+            if not x.flags.c_contiguous:
+                x = x.copy(order="C")   # `as_standard_layout` (executor.rs:135)
+            arrays.append(x)
+        outs = [np.empty(shape, dtype=dtype.np) for shape, dtype, _ in self._out_info]
+        in_ptrs = (c_void_p * max(1, len(arrays)))(*[a.ctypes.data for a in arrays])
+        out_ptrs = (c_void_p * max(1, len(outs)))(*[o.ctypes.data for o in outs])
+        check(self._lib.kn_executor_evaluate(self._ptr, in_ptrs, out_ptrs))
+        return outs
+
+    def evaluate_staged(self) -> List[np.ndarray]:
+        """`evaluate` on the pinned staging buffers: the caller has filled `host_inputs` and reads
+        `host_outputs` (valid until the next call); no extra host copies."""
+        in_ptrs = (c_void_p * max(1, len(self.host_inputs)))(
+            *[a.ctypes.data if a.size else None for a in self.host_inputs])
+        out_ptrs = (c_void_p * max(1, len(self.host_outputs)))(
+            *[a.ctypes.data if a.size else None for a in self.host_outputs])
+        check(self._lib.kn_executor_evaluate(self._ptr, in_ptrs, out_ptrs))
+        return self.host_outputs
+
+    def upload_inputs(self):
+        check(self._lib.kn_executor_upload_inputs(self._ptr))
+
+    def download_outputs(self):
+        check(self._lib.kn_executor_download_outputs(self._ptr))
+
+    def run_async(self):
+        check(self._lib.kn_executor_run_async(self._ptr))
+
+    def synchronize(self):
+        check(self._lib.kn_executor_synchronize(self._ptr))
+
+    # ---------------------------------------------------------------- profiling
+    def set_profile(self, enable: bool):
+        check(self._lib.kn_executor_set_profile(self._ptr, int(enable)))
+
+    def last_profile(self) -> str:
+        needed = c_size_t()
+        check(self._lib.kn_executor_last_profile(self._ptr, None, 0, byref(needed)))
+        buf = ctypes.create_string_buffer(needed.value + 1)
+        check(self._lib.kn_executor_last_profile(self._ptr, buf, needed.value + 1, byref(needed)))
+        return buf.value.decode()
+
+    def close(self):
+        if getattr(self, "_ptr", None):
+            self.host_inputs = []
+            self.host_outputs = []
+            self._lib.kn_executor_destroy(self._ptr)
+            self._ptr = c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+
+class PreparedGraph:
+    """kn-runtime/src/lib.rs:48-51,120-126"""
+
+    def __init__(self, executor: CudaExecutor):
+        self.executor = executor
+
+    def eval(self, inputs: Sequence[np.ndarray]) -> List[np.ndarray]:
+        return self.executor.evaluate(inputs)
+
+
+class Device:
+    """kn-runtime/src/lib.rs:68-93.  Only the CUDA variant exists here: the CPU executor of the
+    reference is not part of this library."""
+
+    def __init__(self, cuda_device: CudaDevice):
+        self.cuda_device = cuda_device
+
+    @staticmethod
+    def cuda(index: int = 0) -> "Device":
+        return Device(CudaDevice(index))
+
+    @staticmethod
+    def best() -> "Device":
+        if CudaDevice.device_count() == 0:
+            raise CudaDeviceNotAvailable("no CUDA device; this library has no CPU executor")
+        return Device(CudaDevice(0))
+
+    def prepare(self, graph: Graph, batch_size: int, **kwargs) -> PreparedGraph:
+        return PreparedGraph(CudaExecutor(self.cuda_device, graph, batch_size, **kwargs))

@@ -1,0 +1,81 @@
+"""Host-only checks of the planner: every reference graph lowers, fusion produces the step counts
+the design promises, and the memory plan reuses buffers."""
+import re
+
+import pytest
+
+import ref_graphs
+from kyanite_b200.configs import mlp, resnet_tower
+from kyanite_b200.executor import KnError, plan_describe
+from kyanite_b200.graph import BATCH, DType, Graph, shape
+
+CASES = ref_graphs.all_cases()
+
+
+def steps_of(text):
+    return [l for l in text.splitlines() if l.startswith("step ")]
+
+
+@pytest.mark.parametrize("case", CASES, ids=[c.name for c in CASES])
+def test_lowers(case):
+    text = plan_describe(case.graph, case.batch_size)
+    assert text.startswith("plan batch=")
+
+
+def test_conv_bias_res_relu_is_one_step():
+    by = {c.name: c for c in CASES}
+    assert len(steps_of(plan_describe(by["fuse_res"].graph, 0))) == 1       # relu(conv + res)
+    assert len(steps_of(plan_describe(by["fused_all"].graph, 0))) == 1      # conv + bias + res
+    assert len(steps_of(plan_describe(by["affine_padding"].graph, 0))) == 2  # pre-add, then conv + bias
+
+
+def test_mlp_is_three_gemms_and_a_softmax():
+    g, _ = mlp()
+    kinds = [s.split()[2] for s in steps_of(plan_describe(g, 8))]
+    assert kinds == ["Gemm", "Gemm", "Gemm", "Softmax"]   # the reference plans 7 steps here
+
+
+def test_resnet_tower_step_list():
+    g, _ = resnet_tower(channels=16, blocks=2)
+    kinds = [s.split()[2].split("/")[0] for s in steps_of(plan_describe(g, 4))]
+    assert kinds.count("Conv") == 1 + 2 * 2 + 2
+    assert kinds.count("Gemm") == 2
+    assert kinds.count("Softmax") == 2
+    assert kinds.count("Scalar") <= 2   # at most the layout copies of the two heads
+
+
+def test_arena_reuses_buffers():
+    g, _ = resnet_tower(channels=16, blocks=6)
+    head = plan_describe(g, 8).splitlines()[0]
+    arena = int(re.search(r"arena_bytes=(\d+)", head).group(1))
+    total = int(re.search(r"hypo_total=(\d+)", head).group(1))
+    peak = int(re.search(r"hypo_peak=(\d+)", head).group(1))
+    assert peak <= arena < total / 2
+
+
+def test_softmax_scale_and_layernorm_residual_fold():
+    by = {c.name: c for c in CASES}
+    text = plan_describe(by["softmax"].graph, 0)
+    assert len(steps_of(text)) == 3                       # the scaled softmax needs no separate multiply
+    text = plan_describe(by["layernorm_residual_scaled"].graph, 3)
+    assert len(steps_of(text)) == 1 and "+res" in text
+
+
+def test_unsupported_contraction_dtype_is_reported():
+    g = Graph()
+    a = g.input(shape(1, 2, 2), DType.I32)
+    g.output(g.batched_mat_mul(a, a))
+    with pytest.raises(KnError) as e:
+        plan_describe(g, 0)
+    assert e.value.status == 3
+
+
+def test_deep_chain_plans():
+    # thousands of values in one chain: planning must not depend on the caller's stack size
+    g = Graph()
+    x = g.input(shape(BATCH, 4))
+    cur = x
+    for i in range(3000):
+        cur = g.softmax(g.add(cur, g.scalar(float(i % 3) + 0.5)), 1)
+    g.output(cur)
+    assert len(steps_of(plan_describe(g, 2))) == 6000
