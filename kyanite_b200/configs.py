@@ -65,26 +65,28 @@ def resnet_tower(channels: int = 128, blocks: int = 16, board: int = 8, in_plane
     """ResNet-style board-game tower, f32.  Stem conv3x3 + bias + ReLU; `blocks` residual blocks of
     conv3x3 + bias, ReLU, conv3x3 + bias, + residual, ReLU (batch-norm already folded into the
     bias); policy head conv1x1 -> flatten -> softmax; value head conv1x1 -> flatten -> linear + ReLU
-    -> linear -> softmax.  Kaiming-normal weights."""
+    -> linear -> softmax.  Kaiming-normal weights; the second convolution of every block is scaled by
+    1/sqrt(2 * blocks), standing in for the folded batch-norm gain, so that activations stay O(1)
+    through the residual stream instead of doubling in variance per block."""
     g = Graph()
     seeds = _Seeds(seed)
 
-    def conv_w(cout, cin, k):
-        std = math.sqrt(2.0 / (cin * k * k))
+    def conv_w(cout, cin, k, gain=1.0):
+        std = gain * math.sqrt(2.0 / (cin * k * k))
         return (_rng(seeds.take()).standard_normal((cout, cin, k, k)) * std).astype(np.float32)
 
     def bias(c):
         return (0.1 * _rng(seeds.take()).standard_normal((1, c, 1, 1))).astype(np.float32)
 
-    def conv_bias(x, cout, cin, k):
-        y = g.conv(x, g.constant_tensor(conv_w(cout, cin, k)), 1, 1, k // 2, k // 2)
+    def conv_bias(x, cout, cin, k, gain=1.0):
+        y = g.conv(x, g.constant_tensor(conv_w(cout, cin, k, gain)), 1, 1, k // 2, k // 2)
         return g.add(y, g.constant_tensor(bias(cout)))
 
     x = g.input(shape(BATCH, in_planes, board, board))
     cur = g.relu(conv_bias(x, channels, in_planes, 3))
     for _ in range(blocks):
         y = g.relu(conv_bias(cur, channels, channels, 3))
-        y = conv_bias(y, channels, channels, 3)
+        y = conv_bias(y, channels, channels, 3, gain=1.0 / math.sqrt(2.0 * blocks))
         cur = g.relu(g.add(y, cur))
 
     policy = conv_bias(cur, policy_channels, channels, 1)

@@ -49,6 +49,8 @@ struct Executor {
     cudaStream_t stream = nullptr;
     uint8_t* arena = nullptr;
     uint8_t* consts = nullptr;
+    uint32_t* status_dev = nullptr;    // raised by a kernel whose bounded wait expired
+    uint32_t* status_host = nullptr;   // pinned mirror
     std::vector<void*> pinned_in, pinned_out;
     std::vector<size_t> bytes_in, bytes_out;
     std::vector<DType> dtype_in, dtype_out;
@@ -65,6 +67,8 @@ struct Executor {
         for (void* p : pinned_out) if (p) cudaFreeHost(p);
         if (arena) cudaFree(arena);
         if (consts) cudaFree(consts);
+        if (status_dev) cudaFree(status_dev);
+        if (status_host) cudaFreeHost(status_host);
         if (stream) cudaStreamDestroy(stream);
     }
 
@@ -118,7 +122,7 @@ struct Executor {
                     break;
                 default: fail(KN_ERR_INTERNAL, "unknown step kind");
             }
-            if (s.tensor_core) tc_prepare_step(s);
+            if (s.tensor_core) tc_prepare_step(s, status_dev);
             launches += s.launches;
         }
     }
@@ -191,6 +195,15 @@ struct Executor {
         for (size_t i = 0; i < pinned_out.size(); i++)
             if (bytes_out[i])
                 KN_CUDA(cudaMemcpyAsync(pinned_out[i], device_ptr(plan->outputs[i]), bytes_out[i], cudaMemcpyDeviceToHost, stream));
+        KN_CUDA(cudaMemcpyAsync(status_host, status_dev, 4, cudaMemcpyDeviceToHost, stream));
+    }
+    void check_status() {
+        if (*status_host != 0) {
+            uint32_t code = *status_host;
+            *status_host = 0;
+            cudaMemsetAsync(status_dev, 0, 4, stream);
+            fail(KN_ERR_INTERNAL, "a kernel gave up waiting on a barrier (code " + std::to_string(code) + ")");
+        }
     }
 
     void evaluate(const void* const* inputs, void* const* outputs) {
@@ -203,6 +216,7 @@ struct Executor {
         run_async();
         download_outputs();
         KN_CUDA(cudaStreamSynchronize(stream));
+        check_status();
         for (size_t i = 0; i < pinned_out.size(); i++) {
             KN_CHECK(outputs != nullptr && (outputs[i] != nullptr || bytes_out[i] == 0), KN_ERR_INVALID_ARG, "null output buffer");
             if (dtype_out[i] == DType::Bool) {
@@ -230,6 +244,10 @@ static std::unique_ptr<Executor> create_executor(int device, const Graph& graph,
     KN_CUDA(cudaStreamCreateWithFlags(&ex->stream, cudaStreamNonBlocking));
     KN_CUDA(cudaMalloc((void**)&ex->arena, std::max<size_t>(plan.arena_bytes, 256)));
     KN_CUDA(cudaMalloc((void**)&ex->consts, std::max<size_t>(plan.const_bytes, 256)));
+    KN_CUDA(cudaMalloc((void**)&ex->status_dev, 256));
+    KN_CUDA(cudaMemset(ex->status_dev, 0, 256));
+    KN_CUDA(cudaHostAlloc((void**)&ex->status_host, 16, cudaHostAllocDefault));
+    *ex->status_host = 0;
     if (plan.const_bytes) {
         // constants cross to the device once, here (kn-cuda-eval/src/planner.rs:331-344)
         std::vector<uint8_t> staging(plan.const_bytes, 0);
@@ -436,7 +454,9 @@ int kn_executor_synchronize(kn_executor* exec) {
     return guarded([&] {
         KN_CHECK(exec != nullptr, KN_ERR_INVALID_ARG, "null executor");
         kn::DeviceGuard guard(exec->e->device);
+        KN_CUDA(cudaMemcpyAsync(exec->e->status_host, exec->e->status_dev, 4, cudaMemcpyDeviceToHost, exec->e->stream));
         KN_CUDA(cudaStreamSynchronize(exec->e->stream));
+        exec->e->check_status();
     });
 }
 

@@ -1,11 +1,567 @@
-// placeholder until the tcgen05 kernels land: no step is marked tensor_core yet
+// Tensor-core contractions for sm_100a: batched matrix multiply and stride-1 2D convolution as an
+// implicit GEMM, TF32 operands, f32 accumulation in tensor memory, fused epilogue
+// act(acc + add1 + add2).
+//
+// One CTA computes one 128 x BN output tile:
+//   warp 0 / lane 0   TMA producer: per K block one `cp.async.bulk.tensor` for the 128 x 32 A tile and
+//                     one for the BN x 32 B tile, both K-major with the 128-byte swizzle, into a
+//                     ring of shared-memory stages guarded by full/empty mbarriers
+//   warp 1 / lane 0   MMA issuer: four `tcgen05.mma.kind::tf32` (K = 8 each) per stage into a
+//                     128-lane x BN-column f32 accumulator in TMEM; `tcgen05.commit` frees the stage
+//   warps 2..5        epilogue: `tcgen05.ld` the accumulator (one output row per thread), add the
+//                     optional addends, activation, store through the output's element strides
+//
+// Convolution needs no im2col buffer: the input is read as a 4-D (C, W, H, N) tensor, an M tile is
+// a box of nb x hb x wb output positions, and filter tap (r, s) is the same box shifted by
+// (r - pad_y, s - pad_x); positions outside the image are zero-filled by the TMA unit, which is
+// exactly the zero padding of the convolution.  Channel and K tails are zero-filled the same way.
+//
+// Every mbarrier wait is bounded: on expiry the kernel records a code in the executor's status word,
+// all roles leave their loops, TMEM is released and the kernel returns.
+#include <cuda.h>
 #include <cuda_runtime.h>
+
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
 
 #include "../tc.h"
 
 namespace kn {
 
-void tc_prepare_step(Step&) { fail(KN_ERR_INTERNAL, "tensor-core step without a tensor-core kernel"); }
-int tc_launch_step(const Step&, cudaStream_t) { return (int)cudaErrorNotSupported; }
+namespace {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockK = 32;                     // floats: one 128-byte swizzle row
+constexpr int kATileBytes = kBlockM * 128;
+constexpr int kThreads = 192;
+constexpr long long kWaitCycles = 4000000000ll;   // ~2 s at 2 GHz
+
+struct TcParams {
+    int32_t mode;   // 0 = matmul, 1 = conv
+    int32_t bn, tmem_cols, k_iters, stages;
+    // conv tiling
+    int32_t cblocks, kernel_w, pad_y, pad_x, wb, hb, nb, tiles_w, tiles_h;
+    int32_t wb_shift, hb_shift;   // log2 of wb, hb
+    int32_t n_img, oh, ow;
+    int64_t m, n;           // matmul rows / columns (conv: n = output channels)
+    float* out;
+    const float* add1;
+    const float* add2;
+    int64_t so[4], s1[4], s2[4];   // conv: (n, c, h, w) strides; matmul: (batch, row, col, -)
+    int32_t act, round_tf32;
+    int32_t staged;         // epilogue goes through shared memory (output columns are unit-stride)
+    int32_t vec4;           // staged epilogue may use 128-bit accesses
+    int32_t add1_mode, add2_mode;   // vec4 path: 0 absent, 1 one value per column (bias), 2 full tensor
+    uint32_t* status;
+};
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false if the kernel is being abandoned.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abandon, uint32_t* status,
+                                          uint32_t code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long start = clock64();
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abandon) return false;
+        if (clock64() - start > kWaitCycles) {
+            *abandon = 1;
+            atomicMax(status, code);
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// K-major operand tile, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);   // start address
+    d |= (uint64_t)1 << 16;                    // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;          // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                    // descriptor version of this architecture
+    d |= (uint64_t)2 << 61;                    // 128-byte swizzle
+    return d;
+}
+
+__device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ float finish(float v, int act, int round_tf32) {
+    if (act == (int)Activation::Relu) v = fmaxf(v, 0.0f);
+    if (round_tf32) {
+        uint32_t u;
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v));
+        v = __uint_as_float(u);
+    }
+    return v;
+}
+
+// ---------------------------------------------------------------- the kernel
+__global__ void __launch_bounds__(kThreads, 1)
+tc_contract_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                   const __grid_constant__ TcParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const int stages = p.stages;
+    const uint32_t b_tile_bytes = (uint32_t)p.bn * 128u;
+    const uint32_t a_base = base;
+    const uint32_t b_base = base + (uint32_t)stages * kATileBytes;
+    const uint32_t bar_base = b_base + (uint32_t)stages * b_tile_bytes;   // 8-byte aligned
+    const uint32_t full_bar = bar_base, empty_bar = bar_base + 8u * stages, accum_bar = bar_base + 16u * stages;
+    const uint32_t slot_addr = accum_bar + 8u;
+    // generic pointers to the same words
+    uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+    volatile uint32_t* tmem_slot = (volatile uint32_t*)(gen_base + (slot_addr - base));
+    volatile int* abandon = (volatile int*)(gen_base + (slot_addr + 4u - base));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; s++) {
+            mbar_init(full_bar + 8u * s, 1);
+            mbar_init(empty_bar + 8u * s, 1);
+        }
+        mbar_init(accum_bar, 1);
+        *abandon = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_addr), "r"((uint32_t)p.tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    // tile coordinates
+    int m0 = 0, n0_img = 0, h0 = 0, w0 = 0;
+    const int ncol0 = blockIdx.y * p.bn;
+    const int batch = blockIdx.z;
+    if (p.mode == 0) {
+        m0 = blockIdx.x * kBlockM;
+    } else {
+        const int tw = blockIdx.x % p.tiles_w;
+        const int th = (blockIdx.x / p.tiles_w) % p.tiles_h;
+        const int tn = blockIdx.x / (p.tiles_w * p.tiles_h);
+        w0 = tw * p.wb;
+        h0 = th * p.hb;
+        n0_img = tn * p.nb;
+    }
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- producer
+        for (int it = 0; it < p.k_iters; it++) {
+            const int s = it % stages;
+            const uint32_t parity = ((it / stages) & 1) ^ 1;
+            if (!mbar_wait(empty_bar + 8u * s, parity, abandon, p.status, 1)) break;
+            mbar_expect_tx(full_bar + 8u * s, kATileBytes + b_tile_bytes);
+            if (p.mode == 0) {
+                tma_load_4d(a_base + s * kATileBytes, &map_a, full_bar + 8u * s, it * kBlockK, m0, batch, 0);
+                tma_load_3d(b_base + s * b_tile_bytes, &map_b, full_bar + 8u * s, it * kBlockK, ncol0, batch);
+            } else {
+                const int tap = it / p.cblocks, cb = it - tap * p.cblocks;
+                const int r = tap / p.kernel_w, sx = tap - r * p.kernel_w;
+                tma_load_4d(a_base + s * kATileBytes, &map_a, full_bar + 8u * s, cb * kBlockK, w0 + sx - p.pad_x,
+                            h0 + r - p.pad_y, n0_img);
+                tma_load_3d(b_base + s * b_tile_bytes, &map_b, full_bar + 8u * s, cb * kBlockK, ncol0, tap);
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---------------- MMA issuer
+        // instruction descriptor: f32 accumulate, tf32 x tf32, both K-major, M = 128, N = bn
+        const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(p.bn >> 3) << 17) | ((uint32_t)(kBlockM >> 4) << 24);
+        bool ok = true;
+        for (int it = 0; it < p.k_iters && ok; it++) {
+            const int s = it % stages;
+            const uint32_t parity = (it / stages) & 1;
+            ok = mbar_wait(full_bar + 8u * s, parity, abandon, p.status, 2);
+            if (!ok) break;
+            tc_fence_after();
+            const uint64_t da = smem_desc_sw128(a_base + s * kATileBytes);
+            const uint64_t db = smem_desc_sw128(b_base + s * b_tile_bytes);
+#pragma unroll
+            for (int j = 0; j < kBlockK / 8; j++)   // 8 tf32 = 32 bytes per instruction: advance the start address by 2 units
+                mma_tf32(tmem_base, da + 2u * j, db + 2u * j, idesc, (it | j) != 0 ? 1u : 0u);
+            mma_commit(empty_bar + 8u * s);
+        }
+        if (ok) mma_commit(accum_bar);
+    } else if (warp >= 2) {
+        // ---------------- epilogue: thread <-> accumulator lane <-> output row
+        const int q = warp & 3;
+        const bool ok = mbar_wait(accum_bar, 0, abandon, p.status, 3);
+        tc_fence_after();
+        const int64_t sn_o = p.mode == 0 ? p.so[2] : p.so[1];
+        const int64_t sn_1 = p.mode == 0 ? p.s1[2] : p.s1[1];
+        const int64_t sn_2 = p.mode == 0 ? p.s2[2] : p.s2[1];
+        // offsets of output row `row` of this tile in the output and the two addends
+        auto row_offsets = [&](int row, int64_t& off_o, int64_t& off_1, int64_t& off_2) -> bool {
+            if (p.mode == 0) {
+                const int64_t m = (int64_t)m0 + row;
+                off_o = batch * p.so[0] + m * p.so[1];
+                off_1 = batch * p.s1[0] + m * p.s1[1];
+                off_2 = batch * p.s2[0] + m * p.s2[1];
+                return m < p.m;
+            }
+            // wb and hb are powers of two: no integer division on this path
+            const int wi = row & (p.wb - 1);
+            const int hi = (row >> p.wb_shift) & (p.hb - 1);
+            const int ni = row >> (p.wb_shift + p.hb_shift);
+            const int64_t img = n0_img + ni, oy = h0 + hi, ox = w0 + wi;
+            off_o = img * p.so[0] + oy * p.so[2] + ox * p.so[3];
+            off_1 = img * p.s1[0] + oy * p.s1[2] + ox * p.s1[3];
+            off_2 = img * p.s2[0] + oy * p.s2[2] + ox * p.s2[3];
+            return img < p.n_img && oy < p.oh && ox < p.ow;
+        };
+        if (ok && !p.staged) {
+            // Output rows are the unit-stride direction (e.g. NCHW): the 32 lanes of a warp hold 32
+            // consecutive rows, so storing straight from registers is already coalesced.
+            int64_t off_o, off_1, off_2;
+            const bool row_valid = row_offsets(q * 32 + lane, off_o, off_1, off_2);
+            for (int c0 = 0; c0 < p.bn; c0 += 32) {
+                uint32_t v[32];
+                tmem_load_32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+                if (!row_valid) continue;
+#pragma unroll
+                for (int j = 0; j < 32; j++) {
+                    const int64_t n = (int64_t)ncol0 + c0 + j;
+                    if (c0 + j < p.bn && n < p.n) {
+                        float acc = __uint_as_float(v[j]);
+                        if (p.add1) acc += p.add1[off_1 + n * sn_1];
+                        if (p.add2) acc += p.add2[off_2 + n * sn_2];
+                        p.out[off_o + n * sn_o] = finish(acc, p.act, p.round_tf32);
+                    }
+                }
+            }
+        } else if (ok) {
+            // Output columns are the unit-stride direction (channels-last, row-major C): transpose
+            // through shared memory (the operand stages are all consumed by now) so that a warp
+            // writes one output row's consecutive columns per instruction.
+            float* tile = (float*)gen_base;
+            const int ld = p.bn + 4;
+            const int row = q * 32 + lane;
+            for (int c0 = 0; c0 < p.bn; c0 += 32) {
+                uint32_t v[32];
+                tmem_load_32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+#pragma unroll
+                for (int j = 0; j < 32; j += 4) {
+                    if (c0 + j < p.bn)
+                        *(float4*)(tile + row * ld + c0 + j) = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                                                                           __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+                }
+            }
+            __syncwarp();   // each warp reads back only the 32 rows it staged itself
+            if (p.vec4) {
+                // 128-bit path: a lane owns four consecutive columns; eight rows are in flight at a
+                // time so the addend loads overlap instead of serialising on memory latency
+                for (int c = 4 * lane; c < p.bn; c += 128) {
+                    const int64_t n = (int64_t)ncol0 + c;
+                    if (n >= p.n) continue;
+                    float4 col_add = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (p.add1_mode == 1) col_add = *(const float4*)(p.add1 + n);
+                    if (p.add2_mode == 1) {
+                        const float4 t = *(const float4*)(p.add2 + n);
+                        col_add.x += t.x; col_add.y += t.y; col_add.z += t.z; col_add.w += t.w;
+                    }
+#pragma unroll 1
+                    for (int rr = 0; rr < 32; rr += 8) {
+                        float4 extra[8];
+                        int64_t off_out[8];
+                        bool valid[8];
+#pragma unroll
+                        for (int u = 0; u < 8; u++) {
+                            int64_t off_1, off_2;
+                            valid[u] = row_offsets(q * 32 + rr + u, off_out[u], off_1, off_2);
+                            extra[u] = col_add;
+                            if (valid[u] && p.add1_mode == 2) {
+                                const float4 t = *(const float4*)(p.add1 + off_1 + n);
+                                extra[u].x += t.x; extra[u].y += t.y; extra[u].z += t.z; extra[u].w += t.w;
+                            }
+                            if (valid[u] && p.add2_mode == 2) {
+                                const float4 t = *(const float4*)(p.add2 + off_2 + n);
+                                extra[u].x += t.x; extra[u].y += t.y; extra[u].z += t.z; extra[u].w += t.w;
+                            }
+                        }
+#pragma unroll
+                        for (int u = 0; u < 8; u++) {
+                            if (!valid[u]) continue;
+                            const float4 a = *(const float4*)(tile + (q * 32 + rr + u) * ld + c);
+                            float4 o;
+                            o.x = finish(a.x + extra[u].x, p.act, p.round_tf32);
+                            o.y = finish(a.y + extra[u].y, p.act, p.round_tf32);
+                            o.z = finish(a.z + extra[u].z, p.act, p.round_tf32);
+                            o.w = finish(a.w + extra[u].w, p.act, p.round_tf32);
+                            *(float4*)(p.out + off_out[u] + n) = o;
+                        }
+                    }
+                }
+            } else {
+                for (int r = q * 32; r < q * 32 + 32; r++) {
+                    int64_t off_o, off_1, off_2;
+                    if (!row_offsets(r, off_o, off_1, off_2)) continue;
+                    for (int c = lane; c < p.bn; c += 32) {
+                        const int64_t n = (int64_t)ncol0 + c;
+                        if (n < p.n) {
+                            float acc = tile[r * ld + c];
+                            if (p.add1) acc += p.add1[off_1 + n * sn_1];
+                            if (p.add2) acc += p.add2[off_2 + n * sn_2];
+                            p.out[off_o + n * sn_o] = finish(acc, p.act, p.round_tf32);
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)p.tmem_cols) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    KN_CHECK(fn != nullptr, KN_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    return fn;
+}
+
+// dims / strides innermost first; strides in elements (dims[0] has stride 1)
+CUtensorMap make_map(const void* base, int rank, const int64_t* dims, const int64_t* strides, const int* box) {
+    KN_CHECK(((uintptr_t)base & 15) == 0, KN_ERR_INTERNAL, "TMA base address is not 16-byte aligned");
+    cuuint64_t gdim[5], gstride[4];
+    cuuint32_t gbox[5], estride[5];
+    for (int i = 0; i < rank; i++) {
+        gdim[i] = (cuuint64_t)std::max<int64_t>(dims[i], 1);
+        gbox[i] = (cuuint32_t)box[i];
+        estride[i] = 1;
+        if (i > 0) {
+            int64_t bytes = strides[i] * 4;
+            if (dims[i] <= 1 && (bytes <= 0 || bytes % 16 != 0)) bytes = 16;   // never stepped: any legal value
+            KN_CHECK(bytes > 0 && bytes % 16 == 0, KN_ERR_INTERNAL, "TMA stride is not a positive multiple of 16 bytes");
+            gstride[i - 1] = (cuuint64_t)bytes;
+        }
+    }
+    CUtensorMap map;
+    // TFLOAT32: the copy engine rounds each f32 to TF32 on its way into shared memory, so operands
+    // are rounded to nearest instead of being truncated by the tensor core
+    CUresult res = encode_tiled_fn()(&map, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, (cuuint32_t)rank, const_cast<void*>(base), gdim,
+                                     gstride, gbox, estride, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    KN_CHECK(res == CUDA_SUCCESS, KN_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)res));
+    return map;
+}
+
+int round_up(int x, int to) { return (x + to - 1) / to * to; }
+int pow2_ceil(int x) {
+    int p = 1;
+    while (p < x) p <<= 1;
+    return p;
+}
+
+}  // namespace
+
+struct TcLaunch {
+    CUtensorMap map_a, map_b;
+    TcParams p;
+    dim3 grid;
+    int smem_bytes;
+};
+
+bool tc_conv_tile(int oh, int ow, int* wb, int* hb, int* nb) {
+    int w = std::min(pow2_ceil(ow), kBlockM);
+    int h = std::min(pow2_ceil(oh), kBlockM / w);
+    *wb = w;
+    *hb = h;
+    *nb = kBlockM / (w * h);
+    return true;
+}
+
+void tc_prepare_step(Step& step, uint32_t* status_word) {
+    auto launch = std::make_shared<TcLaunch>();
+    TcParams& p = launch->p;
+    memset(&p, 0, sizeof(p));
+    p.status = status_word;
+    int64_t n_cols;
+    if (step.kind == StepKind::Gemm) {
+        const GemmParams& g = step.gemm;
+        p.mode = 0;
+        n_cols = g.n;
+        p.m = g.m;
+        p.n = g.n;
+        p.k_iters = (int)((g.k + kBlockK - 1) / kBlockK);
+        p.out = g.c;
+        p.add1 = g.add1;
+        p.add2 = g.add2;
+        for (int i = 0; i < 3; i++) {
+            p.so[i] = g.sc[i];
+            p.s1[i] = g.s1[i];
+            p.s2[i] = g.s2[i];
+        }
+        p.act = g.act;
+        p.round_tf32 = g.round_tf32;
+        // A: [batch, m, k] with k contiguous; B: [batch, k, n] with k contiguous
+        int64_t adims[4] = {g.k, g.m, g.batch, 1}, astr[4] = {1, g.sa[1], g.sa[0], 4};
+        int abox[4] = {kBlockK, kBlockM, 1, 1};
+        launch->map_a = make_map(g.a, 4, adims, astr, abox);
+        p.bn = (int)std::min<int64_t>(round_up((int)std::min<int64_t>(n_cols, 256), 16), 256);
+        if (n_cols > 256) p.bn = 128;
+        int64_t bdims[3] = {g.k, g.n, g.batch}, bstr[3] = {1, g.sb[2], g.sb[0]};
+        int bbox[3] = {kBlockK, p.bn, 1};
+        launch->map_b = make_map(g.b, 3, bdims, bstr, bbox);
+        launch->grid = dim3((unsigned)((g.m + kBlockM - 1) / kBlockM), (unsigned)((n_cols + p.bn - 1) / p.bn), (unsigned)g.batch);
+    } else {
+        const ConvParams& c = step.conv;
+        p.mode = 1;
+        n_cols = c.k;
+        p.n = c.k;
+        p.cblocks = (c.c + kBlockK - 1) / kBlockK;
+        p.k_iters = c.r * c.s * p.cblocks;
+        p.kernel_w = c.s;
+        p.pad_y = c.pad_y;
+        p.pad_x = c.pad_x;
+        tc_conv_tile(c.oh, c.ow, &p.wb, &p.hb, &p.nb);
+        while ((1 << p.wb_shift) < p.wb) p.wb_shift++;
+        while ((1 << p.hb_shift) < p.hb) p.hb_shift++;
+        p.tiles_w = (c.ow + p.wb - 1) / p.wb;
+        p.tiles_h = (c.oh + p.hb - 1) / p.hb;
+        const int tiles_n = (c.n + p.nb - 1) / p.nb;
+        p.n_img = c.n;
+        p.oh = c.oh;
+        p.ow = c.ow;
+        p.out = c.out;
+        p.add1 = c.add1;
+        p.add2 = c.add2;
+        for (int i = 0; i < 4; i++) {
+            p.so[i] = c.s_out[i];
+            p.s1[i] = c.s1[i];
+            p.s2[i] = c.s2[i];
+        }
+        p.act = c.act;
+        p.round_tf32 = c.round_tf32;
+        // input viewed as (C, W, H, N), channels contiguous
+        int64_t adims[4] = {c.c, c.w, c.h, c.n}, astr[4] = {1, c.s_in[3], c.s_in[2], c.s_in[0]};
+        int abox[4] = {kBlockK, p.wb, p.hb, p.nb};
+        launch->map_a = make_map(c.in, 4, adims, astr, abox);
+        p.bn = (int)std::min<int64_t>(round_up((int)std::min<int64_t>(n_cols, 256), 16), 256);
+        if (n_cols > 256) p.bn = 128;
+        // filter stored as (tap, out channel, in channel) with in-channel rows padded to a multiple of 4
+        const int64_t c_pad = round_up(c.c, 4);
+        int64_t bdims[3] = {c.c, c.k, (int64_t)c.r * c.s}, bstr[3] = {1, c_pad, c_pad * c.k};
+        int bbox[3] = {kBlockK, p.bn, 1};
+        launch->map_b = make_map(c.filter, 3, bdims, bstr, bbox);
+        launch->grid = dim3((unsigned)(p.tiles_w * p.tiles_h * tiles_n), (unsigned)((n_cols + p.bn - 1) / p.bn), 1);
+    }
+    p.tmem_cols = std::max(32, pow2_ceil(p.bn));
+    const int stage_bytes = kATileBytes + p.bn * 128;
+    p.stages = std::max(2, std::min(6, (200 * 1024) / stage_bytes));
+    p.stages = std::min(p.stages, std::max(2, p.k_iters));
+    p.staged = (p.mode == 0 ? p.so[2] : p.so[1]) == 1 ? 1 : 0;
+    {
+        // rows are (batch, row) for matmul and (image, y, x) for conv; columns are the remaining stride
+        auto classify = [&](const float* ptr, const int64_t* st) -> int {
+            if (ptr == nullptr) return 0;
+            const int64_t col = p.mode == 0 ? st[2] : st[1];
+            const int64_t r0 = st[0], r1 = p.mode == 0 ? st[1] : st[2], r2 = p.mode == 0 ? 0 : st[3];
+            if (col != 1 || ((uintptr_t)ptr & 15) != 0) return 3;
+            if (r0 == 0 && r1 == 0 && r2 == 0) return 1;
+            if (r0 % 4 == 0 && r1 % 4 == 0 && r2 % 4 == 0) return 2;
+            return 3;
+        };
+        p.add1_mode = classify(p.add1, p.s1);
+        p.add2_mode = classify(p.add2, p.s2);
+        const int out_mode = classify(p.out, p.so);
+        p.vec4 = p.staged && p.n % 4 == 0 && out_mode == 2 && p.add1_mode != 3 && p.add2_mode != 3;
+    }
+    const int staging_bytes = p.staged ? kBlockM * (p.bn + 4) * 4 : 0;
+    launch->smem_bytes = std::max(p.stages * stage_bytes + 16 * p.stages + 64, staging_bytes) + 1024;
+    step.tc = launch;
+}
+
+int tc_launch_step(const Step& step, cudaStream_t stream) {
+    const TcLaunch& l = *step.tc;
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [] {
+        attr_err = cudaFuncSetAttribute(tc_contract_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    });
+    if (attr_err != cudaSuccess) return (int)attr_err;
+    if (l.grid.x == 0 || l.grid.y == 0 || l.grid.z == 0) return 0;
+    tc_contract_kernel<<<l.grid, kThreads, l.smem_bytes, stream>>>(l.map_a, l.map_b, l.p);
+    return (int)cudaGetLastError();
+}
 
 }  // namespace kn

@@ -142,7 +142,11 @@ struct ScalarBlock {
 class Planner {
    public:
     Planner(const Graph& g, int64_t batch, const kn_options& opts, Plan& plan)
-        : g_(g), batch_(batch), opts_(opts), plan_(plan), map_(g.values.size()), chain_cache_(g.values.size(), -2) {}
+        : g_(g), batch_(batch), opts_(opts), plan_(plan), map_(g.values.size()), chain_cache_(g.values.size(), -2),
+          users_(g.values.size()) {
+        for (size_t v = 0; v < g.values.size(); v++)
+            for (int in : g.values[v].inputs) users_[in].push_back((int)v);
+    }
 
     void run() {
         plan_.batch = batch_;
@@ -167,6 +171,7 @@ class Planner {
     Plan& plan_;
     std::vector<std::optional<PlanTensor>> map_;
     std::vector<int> chain_cache_;
+    std::vector<std::vector<int>> users_;
 
     BufferInfo& buffer(int b) { return plan_.buffers[b]; }
 
@@ -551,10 +556,26 @@ class Planner {
             }
             addends.push_back(t.with(*s));
         }
-        PlanTensor out = alloc_shared(native, DType::F32, root);
+        PlanTensor out;
+        bool tensor_core = false;
+        if (opts_.math_mode == KN_MATH_TF32) {
+            if (ci.op == OpKind::MatMul) tensor_core = gemm_fits_tensor_core(x, w);
+            else tensor_core = conv_fits_tensor_core(ci, x, w, native);
+        }
+        if (tensor_core && ci.op == OpKind::Conv) {
+            x = channels_last(x, ci.inputs[0]);
+            w = tap_major_filter(w, ci.inputs[1]);
+            // keep the activation channels-last while it flows from convolution to convolution
+            if (root_shape == native && native[1] % 4 == 0 && feeds_tensor_core_conv(root)) {
+                out = alloc_shared({native[0], native[2], native[3], native[1]}, DType::F32, root);
+                out = out.with(out.ss.permute({0, 3, 1, 2}));
+            }
+        }
+        if (out.buf < 0) out = alloc_shared(native, DType::F32, root);
 
         Step s;
         s.value = root;
+        s.tensor_core = tensor_core;
         s.operands = {x, w, out};
         s.writes = {0, 0, 1};
         for (auto& a : addends) {
@@ -615,6 +636,7 @@ class Planner {
                      std::to_string(p.w) + " k=" + std::to_string(p.k) + " rs=" + std::to_string(p.r) + "x" + std::to_string(p.s);
         }
         s.desc += std::string(" +") + std::to_string(addends.size()) + (m->act == Activation::Relu ? " relu" : "");
+        if (tensor_core) s.desc += " tf32";
         int64_t total = 1;
         for (int64_t d : native) total *= d;
         if (total != 0) push_step(std::move(s));
@@ -622,6 +644,88 @@ class Planner {
         auto rs = out.ss.view(root_shape);
         KN_CHECK(rs.has_value(), KN_ERR_INTERNAL, "view of a dense contraction output failed");
         return out.with(*rs);
+    }
+
+    // ---------------------------------------------------------------- tensor-core eligibility
+    static bool tma_stride_ok(int64_t dim, int64_t stride) { return dim <= 1 || (stride > 0 && stride % 4 == 0); }
+
+    // A [b, m, k] and B [b, k, n] both contiguous along k, every other stride a multiple of 16 bytes
+    bool gemm_fits_tensor_core(const PlanTensor& a, const PlanTensor& b) const {
+        if (a.ss.rank() != 3 || b.ss.rank() != 3) return false;
+        const int64_t batch = a.ss.shape[0], m = a.ss.shape[1], k = a.ss.shape[2], n = b.ss.shape[2];
+        if (batch < 1 || batch > 65535 || m < 64 || n < 8 || k < 8) return false;
+        if (k > 1 && (a.ss.strides[2] != 1 || b.ss.strides[1] != 1)) return false;
+        if (!tma_stride_ok(m, a.ss.strides[1]) || !tma_stride_ok(batch, a.ss.strides[0])) return false;
+        if (!tma_stride_ok(n, b.ss.strides[2]) || !tma_stride_ok(batch, b.ss.strides[0])) return false;
+        if (a.offset % 4 != 0 || b.offset % 4 != 0) return false;
+        if (m > (1ll << 30) || n > (1ll << 30) || k > (1ll << 30)) return false;
+        return true;
+    }
+
+    bool conv_fits_tensor_core(const ValueInfo& ci, const PlanTensor& x, const PlanTensor& w, const std::vector<int64_t>& out) const {
+        if (ci.stride_y != 1 || ci.stride_x != 1) return false;
+        if (x.ss.rank() != 4 || w.ss.rank() != 4) return false;
+        const int64_t positions = out[0] * out[2] * out[3];
+        if (positions < 128 || out[1] < 4 || x.ss.shape[1] < 1) return false;
+        if (out[2] > 32768 || out[3] > 32768 || out[0] > (1 << 24) || w.ss.shape[2] * w.ss.shape[3] > 1024) return false;
+        return true;
+    }
+
+    bool value_is_tensor_core_conv_input(int conv, int input) {
+        const ValueInfo& ci = g_.values[conv];
+        if (ci.op != OpKind::Conv || ci.inputs[0] != input || ci.dtype != DType::F32) return false;
+        if (ci.stride_y != 1 || ci.stride_x != 1) return false;
+        std::vector<int64_t> o = shape_of(conv);
+        return o[0] * o[2] * o[3] >= 128 && o[1] >= 4;
+    }
+    bool feeds_tensor_core_conv(int v) {
+        for (int u : users_[v])
+            if (value_is_tensor_core_conv_input(u, v)) return true;
+        return false;
+    }
+
+    // The convolution kernel reads its input as (C, W, H, N) with channels contiguous.  A tensor that
+    // already is channels-last (the output of a previous tensor-core convolution) is used in place.
+    PlanTensor channels_last(const PlanTensor& x, int value) {
+        const auto& sh = x.ss.shape;
+        const auto& st = x.ss.strides;
+        bool ok = (sh[1] <= 1 || st[1] == 1) && tma_stride_ok(sh[3], st[3]) && tma_stride_ok(sh[2], st[2]) &&
+                  tma_stride_ok(sh[0], st[0]) && x.offset % 4 == 0;
+        if (ok) return x;
+        const int64_t c_pad = (sh[1] + 3) / 4 * 4;
+        PlanTensor dense = alloc_shared({sh[0], sh[2], sh[3], c_pad}, DType::F32, value);
+        PlanTensor nhwc = dense.with(dense.ss.permute({0, 3, 1, 2}));   // logical [N, C_pad, H, W]
+        PlanTensor dst = nhwc.slice(1, 0, sh[1], 1);                    // the real channels; pad lanes are never read
+        emit_copy(x, dst, value);
+        return dst;
+    }
+
+    // Filter [K, C, R, S] -> [R*S][K][C_pad] rounded to TF32 (round to nearest, ties away).  Constant
+    // filters are rearranged here on the host, once; computed filters get a strided copy step.
+    PlanTensor tap_major_filter(const PlanTensor& w, int value) {
+        const int64_t K = w.ss.shape[0], C = w.ss.shape[1], R = w.ss.shape[2], S = w.ss.shape[3];
+        const int64_t c_pad = (C + 3) / 4 * 4;
+        const ValueInfo& wi = g_.values[value];
+        if (wi.op == OpKind::Constant && w.ss.has_simple_strides() && w.offset == 0) {
+            auto data = std::make_shared<std::vector<uint8_t>>((size_t)(R * S * K * c_pad) * 4, 0);
+            const uint32_t* src = (const uint32_t*)wi.const_data;
+            uint32_t* dst = (uint32_t*)data->data();
+            for (int64_t k = 0; k < K; k++)
+                for (int64_t c = 0; c < C; c++)
+                    for (int64_t r = 0; r < R; r++)
+                        for (int64_t s2 = 0; s2 < S; s2++) {
+                            uint32_t bits;
+                            memcpy(&bits, (const uint8_t*)src + 4 * (((k * C + c) * R + r) * S + s2), 4);
+                            if ((bits & 0x7F800000u) != 0x7F800000u) bits = (bits + 0x1000u) & 0xFFFFE000u;
+                            dst[((r * S + s2) * K + k) * c_pad + c] = bits;
+                        }
+            PlanTensor t = alloc_const({R, S, K, c_pad}, DType::F32, value, nullptr, data);
+            return t.with(t.ss.permute({2, 3, 0, 1})).slice(1, 0, C, 1);   // logical [K, C, R, S]
+        }
+        PlanTensor dense = alloc_shared({R, S, K, c_pad}, DType::F32, value);
+        PlanTensor dst = dense.with(dense.ss.permute({2, 3, 0, 1})).slice(1, 0, C, 1);
+        emit_copy(w, dst, value);
+        return dst;
     }
 
     // ---------------------------------------------------------------- gather

@@ -44,6 +44,8 @@ struct PlanTensor {
     std::string str() const;
 };
 
+struct TcLaunch;   // tensor maps and launch geometry of a tensor-core step (kernels/contract_tc.cu)
+
 enum class StepKind : uint8_t { Scalar = 0, Reduce, Softmax, Layernorm, Gather, Gemm, Conv, COUNT };
 const char* step_kind_name(StepKind k);
 
@@ -53,6 +55,7 @@ struct Step {
     std::vector<PlanTensor> operands;   // in the order the kernel's pointers are patched
     std::vector<uint8_t> writes;        // per operand: 1 if the step writes it
     bool tensor_core = false;           // Gemm / Conv: tcgen05 kernel instead of the SIMT one
+    std::shared_ptr<TcLaunch> tc;       // built by tc_prepare_step once device pointers exist
     int launches = 1;
     double alg_bytes = 0;               // distinct operand bytes touched once (roofline numerator)
     double flops = 0;

@@ -6,8 +6,12 @@
 namespace kn {
 
 // Builds the TMA tensor maps of a step marked `tensor_core` (needs the patched device pointers).
-void tc_prepare_step(Step& step);
+// `status_word` is a device word the kernel raises when one of its bounded waits expires.
+void tc_prepare_step(Step& step, uint32_t* status_word);
 // Launches a step marked `tensor_core`; returns a cudaError_t as int.
 int tc_launch_step(const Step& step, cudaStream_t stream);
+
+// Output tile of the convolution kernel: wb x hb x nb output positions (product 128).
+bool tc_conv_tile(int oh, int ow, int* wb, int* hb, int* nb);
 
 }  // namespace kn

@@ -480,10 +480,13 @@ def cpu_eval_graph(blob, batch_size: int, inputs: Sequence[np.ndarray], keep_all
 
 
 def assert_tensors_match(expected: Sequence[np.ndarray], actual: Sequence[np.ndarray], tol_abs=1e-3,
-                         tol_rel=1e-3) -> Tuple[float, float]:
+                         tol_rel=1e-3, abs_scaled=False) -> Tuple[float, float]:
     """The reference's comparison rule (kn-cuda-eval/src/tester.rs:28-29,216-302): floats mismatch
     iff abs_diff >= tol_abs AND rel_diff >= tol_rel, NaN positions must agree, non-floats must be
-    exactly equal.  Returns the (max abs, max rel) float error seen."""
+    exactly equal.  With `abs_scaled` the absolute threshold of each tensor is
+    tol_abs * max(1, largest finite |expected|), for reduced-precision operands whose rounding error
+    is relative to the summed magnitudes rather than to the (possibly cancelled) result.
+    Returns the (max abs, max rel) float error seen."""
     assert len(expected) == len(actual), f"wrong number of tensors: {len(expected)} vs {len(actual)}"
     max_abs = 0.0
     max_rel = 0.0
@@ -505,7 +508,11 @@ def assert_tensors_match(expected: Sequence[np.ndarray], actual: Sequence[np.nda
             d = np.where(same, 0.0, np.abs(e64 - a64))
             rel = np.where(same, 0.0, d / np.abs(e64))
         rel = np.where(np.isnan(rel), np.inf, rel)
-        bad = (d >= tol_abs) & (rel >= tol_rel)
+        tensor_abs = tol_abs
+        if abs_scaled:
+            finite = np.abs(e64[np.isfinite(e64)])
+            tensor_abs = tol_abs * max(1.0, float(finite.max()) if finite.size else 1.0)
+        bad = (d >= tensor_abs) & (rel >= tol_rel)
         if bad.any():
             idx = np.argwhere(bad)[:5]
             msg = ", ".join(f"{tuple(j)}: expected {e[tuple(j)]}, got {a[tuple(j)]}" for j in idx)

@@ -6,7 +6,7 @@ import pytest
 
 import ref_graphs
 from kyanite_b200.configs import mlp, resnet_tower
-from kyanite_b200.executor import KnError, plan_describe
+from kyanite_b200.executor import MATH_F32, MATH_TF32, KnError, plan_describe
 from kyanite_b200.graph import BATCH, DType, Graph, shape
 
 CASES = ref_graphs.all_cases()
@@ -24,9 +24,13 @@ def test_lowers(case):
 
 def test_conv_bias_res_relu_is_one_step():
     by = {c.name: c for c in CASES}
-    assert len(steps_of(plan_describe(by["fuse_res"].graph, 0))) == 1       # relu(conv + res)
-    assert len(steps_of(plan_describe(by["fused_all"].graph, 0))) == 1      # conv + bias + res
-    assert len(steps_of(plan_describe(by["affine_padding"].graph, 0))) == 2  # pre-add, then conv + bias
+    assert len(steps_of(plan_describe(by["fuse_res"].graph, 0, MATH_F32))) == 1       # relu(conv + res)
+    assert len(steps_of(plan_describe(by["fused_all"].graph, 0, MATH_F32))) == 1      # conv + bias + res
+    assert len(steps_of(plan_describe(by["affine_padding"].graph, 0, MATH_F32))) == 2  # pre-add, then conv + bias
+    # on the tensor cores the convolution keeps its fused epilogue; the only extra step is the
+    # channels-last copy of an input that is not channels-last yet
+    tc = steps_of(plan_describe(by["fuse_res"].graph, 0, MATH_TF32))
+    assert [s.split()[2] for s in tc] == ["Scalar", "Conv/tc"] and "+1 relu" in tc[1]
 
 
 def test_mlp_is_three_gemms_and_a_softmax():
@@ -37,11 +41,16 @@ def test_mlp_is_three_gemms_and_a_softmax():
 
 def test_resnet_tower_step_list():
     g, _ = resnet_tower(channels=16, blocks=2)
-    kinds = [s.split()[2].split("/")[0] for s in steps_of(plan_describe(g, 4))]
-    assert kinds.count("Conv") == 1 + 2 * 2 + 2
-    assert kinds.count("Gemm") == 2
-    assert kinds.count("Softmax") == 2
-    assert kinds.count("Scalar") <= 2   # at most the layout copies of the two heads
+    for mode in (MATH_F32, MATH_TF32):
+        kinds = [s.split()[2] for s in steps_of(plan_describe(g, 4, mode))]
+        assert sum(k.startswith("Conv") for k in kinds) == 1 + 2 * 2 + 2
+        assert sum(k.startswith("Gemm") for k in kinds) == 2
+        assert kinds.count("Softmax") == 2
+        # f32: nothing but contractions and softmax; tf32: one channels-last copy of the network input,
+        # after which activations stay channels-last from convolution to convolution
+        assert kinds.count("Scalar") == (0 if mode == MATH_F32 else 1)
+    kinds = [s.split()[2] for s in steps_of(plan_describe(g, 4, MATH_TF32))]
+    assert kinds.count("Conv/tc") == 7
 
 
 def test_arena_reuses_buffers():
