@@ -380,6 +380,234 @@ tc_contract_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     }
 }
 
+// ---------------------------------------------------------------- channels-last convolution kernel
+//
+// Same pipeline, operands swapped: the accumulator holds output channels on its 128 lanes and
+// output pixels on its columns, D[k][pixel] = sum_{r,s,c} W[k][c][r][s] * X[pixel + (r, s)][c].
+//   A operand  the filter: for one horizontal tap s and one block of 32 input channels, the R
+//              vertical taps arrive as R tiles of [128 output channels x 32] in ONE bulk copy
+//   B operand  the activations: a sub-tile is hb rows x 8 columns of one image; its input window
+//              for horizontal tap s, (hb + R - 1) rows x 8 pixels x 32 channels, is loaded ONCE and
+//              vertical tap r reads it at a row offset of r * 1024 bytes (8 pixels x 128 bytes),
+//              which keeps every operand descriptor 1024-byte aligned
+// so the activations cross from L2 S times instead of R*S times, and a CTA that owns `per_cta`
+// sub-tiles loads the filter once for all of them.  (An SM pulls a bounded number of bytes per
+// clock from L2; at TF32 that, not the tensor pipe, limits a 128x128 tile that re-fetches both
+// operands per tap.)
+//
+// With channels-last output a warp's 32 lanes are 32 consecutive channels of one pixel, so the
+// epilogue stores straight from registers, coalesced.
+struct ConvClParams {
+    int32_t k_out, c_blocks, kernel_h, kernel_w, pad_y, pad_x;
+    int32_t hb, hb_shift, ncols;        // sub-tile rows (power of two), columns = 8 * hb
+    int32_t per_cta, tmem_cols, stages;
+    int32_t tiles_w, tiles_h, subtiles; // sub-tile grid per image and in total
+    int32_t n_img, oh, ow;
+    int32_t iters;                      // kernel_w * c_blocks
+    float* out;
+    const float* add1;
+    const float* add2;
+    int64_t so[4], s1[4], s2[4];        // (n, c, h, w) strides
+    int32_t act, round_tf32;
+    // bulk-copy epilogue: the residual tile is prefetched into shared memory by the copy engine while
+    // the mainloop runs and the finished tile leaves through a bulk tensor store
+    int32_t tma_io, has_res;
+    const float* bias;                  // tma_io: one value per output channel (or null)
+    int64_t bias_stride;
+    uint32_t* status;
+};
+
+constexpr int kMaxPerCta = 8;
+
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                 ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+tc_conv_cl_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                  const __grid_constant__ CUtensorMap map_res, const __grid_constant__ CUtensorMap map_out,
+                  const __grid_constant__ ConvClParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const int stages = p.stages;
+    const uint32_t w_bytes = (uint32_t)p.kernel_h * kATileBytes;                 // R tiles of 128 x 128 B
+    const uint32_t x_tile_bytes = (uint32_t)(p.hb + p.kernel_h - 1) * 1024u;     // one sub-tile window
+    const uint32_t stage_bytes = w_bytes + (uint32_t)p.per_cta * x_tile_bytes;
+    const uint32_t io_base = base + (uint32_t)stages * stage_bytes;              // [sub-tile][pixel][128 channels] f32
+    const uint32_t io_tile_bytes = p.tma_io ? (uint32_t)p.ncols * 512u : 0u;
+    const uint32_t bar_base = io_base + (uint32_t)p.per_cta * io_tile_bytes;
+    const uint32_t full_bar = bar_base, empty_bar = bar_base + 8u * stages, accum_bar = bar_base + 16u * stages;
+    const uint32_t res_bar = accum_bar + 8u;
+    const uint32_t slot_addr = res_bar + 8u;
+    uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+    volatile uint32_t* tmem_slot = (volatile uint32_t*)(gen_base + (slot_addr - base));
+    volatile int* abandon = (volatile int*)(gen_base + (slot_addr + 4u - base));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; s++) {
+            mbar_init(full_bar + 8u * s, 1);
+            mbar_init(empty_bar + 8u * s, 1);
+        }
+        mbar_init(accum_bar, 1);
+        mbar_init(res_bar, 1);
+        *abandon = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_addr), "r"((uint32_t)p.tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int k0 = blockIdx.y * kBlockM;             // first output channel of this CTA
+    const int first_subtile = blockIdx.x * p.per_cta;
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- producer
+        if (p.tma_io && p.has_res) {
+            int valid = p.subtiles - first_subtile;
+            if (valid > p.per_cta) valid = p.per_cta;
+            mbar_expect_tx(res_bar, (uint32_t)valid * io_tile_bytes);
+            for (int i = 0; i < valid; i++) {
+                const int sub = first_subtile + i;
+                const int tw = sub % p.tiles_w;
+                const int th = (sub / p.tiles_w) % p.tiles_h;
+                const int img = sub / (p.tiles_w * p.tiles_h);
+                tma_load_4d(io_base + (uint32_t)i * io_tile_bytes, &map_res, res_bar, k0, tw * 8, th * p.hb, img);
+            }
+        }
+        for (int it = 0; it < p.iters; it++) {
+            const int st = it % stages;
+            const uint32_t parity = ((it / stages) & 1) ^ 1;
+            if (!mbar_wait(empty_bar + 8u * st, parity, abandon, p.status, 1)) break;
+            const uint32_t bar = full_bar + 8u * st;
+            mbar_expect_tx(bar, stage_bytes);
+            const int sx = it / p.c_blocks, cb = it - sx * p.c_blocks;
+            const uint32_t stage_addr = base + (uint32_t)st * stage_bytes;
+            tma_load_4d(stage_addr, &map_w, bar, cb * kBlockK, k0, sx, 0);
+            for (int i = 0; i < p.per_cta; i++) {
+                const int sub = first_subtile + i;       // past the end: every coordinate is out of range, zero fill
+                const int tw = sub % p.tiles_w;
+                const int th = (sub / p.tiles_w) % p.tiles_h;
+                const int img = sub / (p.tiles_w * p.tiles_h);
+                tma_load_4d(stage_addr + w_bytes + (uint32_t)i * x_tile_bytes, &map_x, bar, cb * kBlockK,
+                            tw * 8 + sx - p.pad_x, th * p.hb - p.pad_y, img);
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---------------- MMA issuer: M = 128 output channels, N = 8 * hb pixels of one sub-tile
+        const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(p.ncols >> 3) << 17) | ((uint32_t)(kBlockM >> 4) << 24);
+        bool ok = true;
+        for (int it = 0; it < p.iters && ok; it++) {
+            const int st = it % stages;
+            const uint32_t parity = (it / stages) & 1;
+            ok = mbar_wait(full_bar + 8u * st, parity, abandon, p.status, 2);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t stage_addr = base + (uint32_t)st * stage_bytes;
+            for (int r = 0; r < p.kernel_h; r++) {
+                const uint64_t dw = smem_desc_sw128(stage_addr + (uint32_t)r * kATileBytes);
+                for (int i = 0; i < p.per_cta; i++) {
+                    const uint64_t dx = smem_desc_sw128(stage_addr + w_bytes + (uint32_t)i * x_tile_bytes + (uint32_t)r * 1024u);
+#pragma unroll
+                    for (int j = 0; j < kBlockK / 8; j++)
+                        mma_tf32(tmem_base + (uint32_t)(i * p.ncols), dw + 2u * j, dx + 2u * j, idesc, (it | r | j) != 0 ? 1u : 0u);
+                }
+            }
+            mma_commit(empty_bar + 8u * st);
+        }
+        if (ok) mma_commit(accum_bar);
+    } else if (warp >= 2) {
+        // ---------------- epilogue: thread <-> accumulator lane <-> output channel
+        const int q = warp & 3;
+        const int64_t k = (int64_t)k0 + q * 32 + lane;
+        const bool ok = mbar_wait(accum_bar, 0, abandon, p.status, 3);
+        tc_fence_after();
+        const bool k_valid = k < p.k_out;
+        if (ok && p.tma_io) {
+            const float bias = (p.bias != nullptr && k_valid) ? p.bias[k * p.bias_stride] : 0.f;
+            bool res_ok = true;
+            if (p.has_res) res_ok = mbar_wait(res_bar, 0, abandon, p.status, 4);
+            float* io = (float*)(gen_base + (io_base - base));
+            if (res_ok) {
+                for (int i = 0; i < p.per_cta; i++) {
+                    if (first_subtile + i >= p.subtiles) break;
+                    for (int c0 = 0; c0 < p.ncols; c0 += 32) {
+                        uint32_t v[32];
+                        tmem_load_32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(i * p.ncols + c0), v);
+                        float* cell = io + ((size_t)(i * p.ncols + c0) * kBlockM) + q * 32 + lane;
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            float val = __uint_as_float(v[j]) + bias;
+                            if (p.has_res) val += cell[j * kBlockM];
+                            cell[j * kBlockM] = finish(val, p.act, p.round_tf32);
+                        }
+                    }
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the bulk store
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (threadIdx.x == 64 && res_ok) {
+                for (int i = 0; i < p.per_cta; i++) {
+                    const int sub = first_subtile + i;
+                    if (sub >= p.subtiles) break;
+                    const int tw = sub % p.tiles_w;
+                    const int th = (sub / p.tiles_w) % p.tiles_h;
+                    const int img = sub / (p.tiles_w * p.tiles_h);
+                    tma_store_4d(&map_out, io_base + (uint32_t)i * io_tile_bytes, k0, tw * 8, th * p.hb, img);
+                }
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // shared memory must outlive the read
+            }
+        } else if (ok) {
+            for (int i = 0; i < p.per_cta; i++) {
+                const int sub = first_subtile + i;
+                if (sub >= p.subtiles) break;
+                const int tw = sub % p.tiles_w;
+                const int th = (sub / p.tiles_w) % p.tiles_h;
+                const int64_t img = sub / (p.tiles_w * p.tiles_h);
+                const int64_t base_o = img * p.so[0] + k * p.so[1];
+                const int64_t base_1 = img * p.s1[0] + k * p.s1[1];
+                const int64_t base_2 = img * p.s2[0] + k * p.s2[1];
+                for (int c0 = 0; c0 < p.ncols; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_load_32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(i * p.ncols + c0), v);
+                    if (!k_valid) continue;
+                    float extra[32];
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const int oy = th * p.hb + ((c0 + j) >> 3), ox = tw * 8 + ((c0 + j) & 7);
+                        const bool valid = oy < p.oh && ox < p.ow;
+                        float e = 0.f;
+                        if (valid && p.add1) e += p.add1[base_1 + oy * p.s1[2] + ox * p.s1[3]];
+                        if (valid && p.add2) e += p.add2[base_2 + oy * p.s2[2] + ox * p.s2[3]];
+                        extra[j] = e;
+                    }
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const int oy = th * p.hb + ((c0 + j) >> 3), ox = tw * 8 + ((c0 + j) & 7);
+                        if (oy < p.oh && ox < p.ow)
+                            p.out[base_o + oy * p.so[2] + ox * p.so[3]] = finish(__uint_as_float(v[j]) + extra[j], p.act, p.round_tf32);
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)p.tmem_cols) : "memory");
+    }
+}
+
 // ---------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -400,7 +628,8 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 // dims / strides innermost first; strides in elements (dims[0] has stride 1)
-CUtensorMap make_map(const void* base, int rank, const int64_t* dims, const int64_t* strides, const int* box) {
+CUtensorMap make_map(const void* base, int rank, const int64_t* dims, const int64_t* strides, const int* box,
+                     bool operand = true) {
     KN_CHECK(((uintptr_t)base & 15) == 0, KN_ERR_INTERNAL, "TMA base address is not 16-byte aligned");
     cuuint64_t gdim[5], gstride[4];
     cuuint32_t gbox[5], estride[5];
@@ -418,8 +647,10 @@ CUtensorMap make_map(const void* base, int rank, const int64_t* dims, const int6
     CUtensorMap map;
     // TFLOAT32: the copy engine rounds each f32 to TF32 on its way into shared memory, so operands
     // are rounded to nearest instead of being truncated by the tensor core
-    CUresult res = encode_tiled_fn()(&map, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, (cuuint32_t)rank, const_cast<void*>(base), gdim,
-                                     gstride, gbox, estride, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+    // (epilogue tiles, `operand == false`, are plain f32 rows without swizzle)
+    CUresult res = encode_tiled_fn()(&map, operand ? CU_TENSOR_MAP_DATA_TYPE_TFLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                                     (cuuint32_t)rank, const_cast<void*>(base), gdim, gstride, gbox, estride,
+                                     CU_TENSOR_MAP_INTERLEAVE_NONE, operand ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     KN_CHECK(res == CUDA_SUCCESS, KN_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)res));
     return map;
@@ -435,11 +666,129 @@ int pow2_ceil(int x) {
 }  // namespace
 
 struct TcLaunch {
-    CUtensorMap map_a, map_b;
+    CUtensorMap map_a, map_b, map_res, map_out;
     TcParams p;
+    bool channels_last = false;   // tc_conv_cl_kernel with `cl` instead of tc_contract_kernel with `p`
+    ConvClParams cl;
     dim3 grid;
     int smem_bytes;
 };
+
+static bool tma_stride_ok_host(int64_t dim, int64_t stride) { return dim <= 1 || (stride > 0 && stride % 4 == 0); }
+
+// Fills the channels-last convolution launch if the step qualifies: channels-last output, at least
+// four output rows, and two pipeline stages of its filter taps fit in shared memory.
+static bool prepare_conv_channels_last(const ConvParams& c, uint32_t* status_word, TcLaunch& launch) {
+    if (c.s_out[1] != 1 || c.oh < 4) return false;
+    ConvClParams& p = launch.cl;
+    memset(&p, 0, sizeof(p));
+    p.hb = std::min(32, pow2_ceil(c.oh));
+    while ((1 << p.hb_shift) < p.hb) p.hb_shift++;
+    p.ncols = 8 * p.hb;
+    const int w_bytes = c.r * kATileBytes;
+    const int x_bytes = (p.hb + c.r - 1) * 1024;
+    const int smem_budget = 220 * 1024;
+    // bulk-copy epilogue: needs a channels-last output and residual the copy engine can address, and at
+    // most one per-channel addend (bias) besides
+    auto tile_ok = [&](const float* ptr, const int64_t* st) {
+        return ((uintptr_t)ptr & 15) == 0 && st[1] == 1 && tma_stride_ok_host(c.ow, st[3]) && tma_stride_ok_host(c.oh, st[2]) &&
+               tma_stride_ok_host(c.n, st[0]);
+    };
+    auto per_channel = [&](const int64_t* st) { return st[0] == 0 && st[2] == 0 && st[3] == 0; };
+    const float* bias = nullptr;
+    const float* res = nullptr;
+    const int64_t* res_strides = nullptr;
+    int64_t bias_stride = 0;
+    bool tma_io = tile_ok(c.out, c.s_out);
+    const float* adds[2] = {c.add1, c.add2};
+    const int64_t* add_strides[2] = {c.s1, c.s2};
+    for (int a = 0; a < 2 && tma_io; a++) {
+        if (adds[a] == nullptr) continue;
+        if (per_channel(add_strides[a]) && bias == nullptr) {
+            bias = adds[a];
+            bias_stride = add_strides[a][1];
+        } else if (tile_ok(adds[a], add_strides[a]) && res == nullptr) {
+            res = adds[a];
+            res_strides = add_strides[a];
+        } else {
+            tma_io = false;
+        }
+    }
+    const int io_bytes = tma_io ? p.ncols * 512 : 0;
+    if (2 * (w_bytes + x_bytes) + io_bytes > smem_budget) return false;
+    p.tiles_w = (c.ow + 7) / 8;
+    p.tiles_h = (c.oh + p.hb - 1) / p.hb;
+    const int64_t subtiles = (int64_t)c.n * p.tiles_w * p.tiles_h;
+    if (subtiles > (1ll << 30)) return false;
+    p.subtiles = (int)subtiles;
+    // sub-tiles per CTA: the filter is fetched once per CTA, the windows once per sub-tile; pick the
+    // count that moves the fewest bytes per SM over all waves of a 148-SM device
+    const int k_blocks = (c.k + kBlockM - 1) / kBlockM;
+    int best = 1;
+    double best_cost = 1e300;
+    for (int per = 1; per <= kMaxPerCta; per++) {
+        if (per * p.ncols > 512 || 2 * (w_bytes + per * x_bytes) + per * io_bytes > smem_budget) break;
+        const int64_t ctas = ((subtiles + per - 1) / per) * k_blocks;
+        const double waves = (double)((ctas + 147) / 148);
+        const double cost = waves * (w_bytes + (double)per * x_bytes);
+        if (cost < best_cost) { best_cost = cost; best = per; }
+    }
+    p.per_cta = best;
+    p.tmem_cols = std::max(32, pow2_ceil(p.per_cta * p.ncols));
+    const int stage_bytes = w_bytes + p.per_cta * x_bytes;
+    p.stages = std::max(2, std::min(4, (smem_budget - p.per_cta * io_bytes) / stage_bytes));
+    p.k_out = c.k;
+    p.c_blocks = (c.c + kBlockK - 1) / kBlockK;
+    p.kernel_h = c.r;
+    p.kernel_w = c.s;
+    p.pad_y = c.pad_y;
+    p.pad_x = c.pad_x;
+    p.iters = c.s * p.c_blocks;
+    p.stages = std::min(p.stages, std::max(2, p.iters));
+    p.n_img = c.n;
+    p.oh = c.oh;
+    p.ow = c.ow;
+    p.out = c.out;
+    p.add1 = c.add1;
+    p.add2 = c.add2;
+    for (int i = 0; i < 4; i++) {
+        p.so[i] = c.s_out[i];
+        p.s1[i] = c.s1[i];
+        p.s2[i] = c.s2[i];
+    }
+    p.act = c.act;
+    p.round_tf32 = c.round_tf32;
+    p.status = status_word;
+    // filter memory is [tap = r * S + s][out channel][in channel padded to 4]; viewed as (c, k, s, r)
+    const int64_t c_pad = round_up(c.c, 4);
+    int64_t wdims[4] = {c.c, c.k, c.s, c.r}, wstr[4] = {1, c_pad, c_pad * c.k, c_pad * c.k * c.s};
+    int wbox[4] = {kBlockK, kBlockM, 1, c.r};
+    launch.map_a = make_map(c.filter, 4, wdims, wstr, wbox);
+    int64_t xdims[4] = {c.c, c.w, c.h, c.n}, xstr[4] = {1, c.s_in[3], c.s_in[2], c.s_in[0]};
+    int xbox[4] = {kBlockK, 8, p.hb + c.r - 1, 1};
+    launch.map_b = make_map(c.in, 4, xdims, xstr, xbox);
+    launch.grid = dim3((unsigned)((subtiles + p.per_cta - 1) / p.per_cta), (unsigned)k_blocks, 1);
+    p.tma_io = tma_io ? 1 : 0;
+    p.has_res = res != nullptr ? 1 : 0;
+    p.bias = bias;
+    p.bias_stride = bias_stride;
+    if (tma_io) {
+        int64_t odims[4] = {c.k, c.ow, c.oh, c.n}, ostr[4] = {1, c.s_out[3], c.s_out[2], c.s_out[0]};
+        int obox[4] = {kBlockM, 8, p.hb, 1};
+        launch.map_out = make_map(c.out, 4, odims, ostr, obox, false);
+        launch.map_res = launch.map_out;
+        if (res != nullptr) {
+            int64_t rstr[4] = {1, res_strides[3], res_strides[2], res_strides[0]};
+            launch.map_res = make_map(res, 4, odims, rstr, obox, false);
+        }
+    } else {
+        launch.map_res = launch.map_a;
+        launch.map_out = launch.map_a;
+    }
+    launch.smem_bytes = p.stages * stage_bytes + p.per_cta * io_bytes + 16 * p.stages + 64 + 1024;
+    launch.channels_last = true;
+    return true;
+}
 
 bool tc_conv_tile(int oh, int ow, int* wb, int* hb, int* nb) {
     int w = std::min(pow2_ceil(ow), kBlockM);
@@ -485,6 +834,10 @@ void tc_prepare_step(Step& step, uint32_t* status_word) {
         launch->grid = dim3((unsigned)((g.m + kBlockM - 1) / kBlockM), (unsigned)((n_cols + p.bn - 1) / p.bn), (unsigned)g.batch);
     } else {
         const ConvParams& c = step.conv;
+        if (prepare_conv_channels_last(c, status_word, *launch)) {
+            step.tc = launch;
+            return;
+        }
         p.mode = 1;
         n_cols = c.k;
         p.n = c.k;
@@ -553,14 +906,24 @@ void tc_prepare_step(Step& step, uint32_t* status_word) {
 
 int tc_launch_step(const Step& step, cudaStream_t stream) {
     const TcLaunch& l = *step.tc;
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [] {
-        attr_err = cudaFuncSetAttribute(tc_contract_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-    });
-    if (attr_err != cudaSuccess) return (int)attr_err;
+    // the opt-in to large dynamic shared memory is per device
+    static std::mutex mu;
+    static bool done[64] = {false};
+    int device = 0;
+    cudaGetDevice(&device);
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (device >= 0 && device < 64 && !done[device]) {
+            cudaError_t e1 = cudaFuncSetAttribute(tc_contract_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            cudaError_t e2 = cudaFuncSetAttribute(tc_conv_cl_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            if (e1 != cudaSuccess) return (int)e1;
+            if (e2 != cudaSuccess) return (int)e2;
+            done[device] = true;
+        }
+    }
     if (l.grid.x == 0 || l.grid.y == 0 || l.grid.z == 0) return 0;
-    tc_contract_kernel<<<l.grid, kThreads, l.smem_bytes, stream>>>(l.map_a, l.map_b, l.p);
+    if (l.channels_last) tc_conv_cl_kernel<<<l.grid, kThreads, l.smem_bytes, stream>>>(l.map_a, l.map_b, l.map_res, l.map_out, l.cl);
+    else tc_contract_kernel<<<l.grid, kThreads, l.smem_bytes, stream>>>(l.map_a, l.map_b, l.p);
     return (int)cudaGetLastError();
 }
 
