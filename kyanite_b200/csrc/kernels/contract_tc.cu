@@ -401,6 +401,7 @@ struct ConvClParams {
     int32_t k_out, c_blocks, kernel_h, kernel_w, pad_y, pad_x;
     int32_t hb, hb_shift, ncols;        // sub-tile rows (power of two), columns = 8 * hb
     int32_t per_cta, tmem_cols, stages;
+    int32_t n_mma, col_stride;          // one MMA spans all sub-tiles of the CTA: N columns, columns between sub-tiles
     int32_t tiles_w, tiles_h, subtiles; // sub-tile grid per image and in total
     int32_t n_img, oh, ow;
     int32_t iters;                      // kernel_w * c_blocks
@@ -502,8 +503,13 @@ tc_conv_cl_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             }
         }
     } else if (warp == 1 && lane == 0) {
-        // ---------------- MMA issuer: M = 128 output channels, N = 8 * hb pixels of one sub-tile
-        const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(p.ncols >> 3) << 17) | ((uint32_t)(kBlockM >> 4) << 24);
+        // ---------------- MMA issuer: M = 128 output channels.  The windows of the CTA's sub-tiles lie
+        // back to back in the stage, (hb + R - 1) groups of 8 pixels each, so ONE instruction per tap and
+        // K step covers all of them: its N spans per_cta * hb + (per_cta - 1) * (R - 1) groups, and the
+        // (R - 1) groups between two sub-tiles accumulate values nobody reads.  (An instruction costs
+        // about the same for N = 64 as for N = 128, so narrow per-sub-tile instructions would halve
+        // the tensor throughput.)
+        const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(p.n_mma >> 3) << 17) | ((uint32_t)(kBlockM >> 4) << 24);
         bool ok = true;
         for (int it = 0; it < p.iters && ok; it++) {
             const int st = it % stages;
@@ -514,12 +520,10 @@ tc_conv_cl_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             const uint32_t stage_addr = base + (uint32_t)st * stage_bytes;
             for (int r = 0; r < p.kernel_h; r++) {
                 const uint64_t dw = smem_desc_sw128(stage_addr + (uint32_t)r * kATileBytes);
-                for (int i = 0; i < p.per_cta; i++) {
-                    const uint64_t dx = smem_desc_sw128(stage_addr + w_bytes + (uint32_t)i * x_tile_bytes + (uint32_t)r * 1024u);
+                const uint64_t dx = smem_desc_sw128(stage_addr + w_bytes + (uint32_t)r * 1024u);
 #pragma unroll
-                    for (int j = 0; j < kBlockK / 8; j++)
-                        mma_tf32(tmem_base + (uint32_t)(i * p.ncols), dw + 2u * j, dx + 2u * j, idesc, (it | r | j) != 0 ? 1u : 0u);
-                }
+                for (int j = 0; j < kBlockK / 8; j++)
+                    mma_tf32(tmem_base, dw + 2u * j, dx + 2u * j, idesc, (it | r | j) != 0 ? 1u : 0u);
             }
             mma_commit(empty_bar + 8u * st);
         }
@@ -541,7 +545,7 @@ tc_conv_cl_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                     if (first_subtile + i >= p.subtiles) break;
                     for (int c0 = 0; c0 < p.ncols; c0 += 32) {
                         uint32_t v[32];
-                        tmem_load_32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(i * p.ncols + c0), v);
+                        tmem_load_32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(i * p.col_stride + c0), v);
                         float* cell = io + ((size_t)(i * p.ncols + c0) * kBlockM) + q * 32 + lane;
 #pragma unroll
                         for (int j = 0; j < 32; j++) {
@@ -578,7 +582,7 @@ tc_conv_cl_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 const int64_t base_2 = img * p.s2[0] + k * p.s2[1];
                 for (int c0 = 0; c0 < p.ncols; c0 += 32) {
                     uint32_t v[32];
-                    tmem_load_32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(i * p.ncols + c0), v);
+                    tmem_load_32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(i * p.col_stride + c0), v);
                     if (!k_valid) continue;
                     float extra[32];
 #pragma unroll
@@ -727,14 +731,16 @@ static bool prepare_conv_channels_last(const ConvParams& c, uint32_t* status_wor
     int best = 1;
     double best_cost = 1e300;
     for (int per = 1; per <= kMaxPerCta; per++) {
-        if (per * p.ncols > 512 || 2 * (w_bytes + per * x_bytes) + per * io_bytes > smem_budget) break;
+        if (8 * (per * p.hb + (per - 1) * (c.r - 1)) > 256 || 2 * (w_bytes + per * x_bytes) + per * io_bytes > smem_budget) break;
         const int64_t ctas = ((subtiles + per - 1) / per) * k_blocks;
         const double waves = (double)((ctas + 147) / 148);
         const double cost = waves * (w_bytes + (double)per * x_bytes);
         if (cost < best_cost) { best_cost = cost; best = per; }
     }
     p.per_cta = best;
-    p.tmem_cols = std::max(32, pow2_ceil(p.per_cta * p.ncols));
+    p.col_stride = 8 * (p.hb + c.r - 1);
+    p.n_mma = 8 * (p.per_cta * p.hb + (p.per_cta - 1) * (c.r - 1));
+    p.tmem_cols = std::max(32, pow2_ceil(p.n_mma));
     const int stage_bytes = w_bytes + p.per_cta * x_bytes;
     p.stages = std::max(2, std::min(4, (smem_budget - p.per_cta * io_bytes) / stage_bytes));
     p.k_out = c.k;
