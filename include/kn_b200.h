@@ -160,6 +160,11 @@ KN_API int kn_executor_step_count(const kn_executor* exec, int* steps, int* laun
  * (`index kind microseconds algorithmic_bytes flops description`) followed by per-kind totals. */
 KN_API int kn_executor_set_profile(kn_executor* exec, int enable);
 KN_API int kn_executor_last_profile(kn_executor* exec, char* buf, size_t cap, size_t* needed);
+/* Launches step `step` alone `launches` times back to back between one pair of CUDA events on the
+ * executor's stream and returns the average duration of one launch in microseconds.  The step reads
+ * and rewrites whatever its buffers currently hold.  (The per-step figures of `last_profile` include
+ * the event and launch gaps of a one-by-one run; this one does not.)  No reference counterpart. */
+KN_API int kn_executor_time_step(kn_executor* exec, int step, int launches, float* microseconds);
 
 /* Host-only element semantics, exported so the scalar rules can be tested without a device:
  * applies one unary / binary operation to 64-bit canonical element patterns. */

@@ -543,6 +543,35 @@ int kn_executor_last_profile(kn_executor* exec, char* buf, size_t cap, size_t* n
     });
 }
 
+int kn_executor_time_step(kn_executor* exec, int step, int launches, float* microseconds) {
+    return guarded([&] {
+        KN_CHECK(exec != nullptr && microseconds != nullptr, KN_ERR_INVALID_ARG, "null argument");
+        kn::Executor& e = *exec->e;
+        KN_CHECK(step >= 0 && (size_t)step < e.plan->steps.size(), KN_ERR_INVALID_ARG, "step index out of range");
+        KN_CHECK(launches >= 1 && launches <= 100000, KN_ERR_INVALID_ARG, "launch count out of range");
+        kn::DeviceGuard guard(e.device);
+        cudaEvent_t a, b;
+        KN_CUDA(cudaEventCreate(&a));
+        KN_CUDA(cudaEventCreate(&b));
+        try {
+            e.launch_step(e.plan->steps[step]);   // warm
+            KN_CUDA(cudaEventRecord(a, e.stream));
+            for (int i = 0; i < launches; i++) e.launch_step(e.plan->steps[step]);
+            KN_CUDA(cudaEventRecord(b, e.stream));
+            KN_CUDA(cudaStreamSynchronize(e.stream));
+            float ms = 0;
+            KN_CUDA(cudaEventElapsedTime(&ms, a, b));
+            *microseconds = ms * 1000.f / (float)launches;
+        } catch (...) {
+            cudaEventDestroy(a);
+            cudaEventDestroy(b);
+            throw;
+        }
+        cudaEventDestroy(a);
+        cudaEventDestroy(b);
+    });
+}
+
 int kn_scalar_unary(int unary_op, int from_dtype, int to_dtype, uint64_t x, uint64_t* out) {
     return guarded([&] {
         KN_CHECK(out != nullptr, KN_ERR_INVALID_ARG, "null out");

@@ -230,6 +230,12 @@ class CudaExecutor:
         check(self._lib.kn_executor_last_profile(self._ptr, buf, needed.value + 1, byref(needed)))
         return buf.value.decode()
 
+    def time_step(self, step: int, launches: int = 20) -> float:
+        """Average microseconds of one launch of step `step`, launched `launches` times back to back."""
+        us = ctypes.c_float()
+        check(self._lib.kn_executor_time_step(self._ptr, step, launches, byref(us)))
+        return us.value
+
     def close(self):
         if getattr(self, "_ptr", None):
             self.host_inputs = []
