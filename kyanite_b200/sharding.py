@@ -1,0 +1,68 @@
+"""Batch sharding across devices: the executor's only multi-GPU mode.
+
+Every per-sample tensor of a graph carries the batch size in its shape (`Size(factor, exp)` with
+exp > 0), samples never interact in the operations the executor runs, and the reference has no
+collective at all (it can only run one executor per device).  So a global batch is split on the host
+along each input's batch axis, every rank evaluates its shard with its own executor, and outputs are
+concatenated along their batch axis.  Inputs without a batch axis are replicated.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import numpy as np
+
+from .graph import Graph
+
+
+def batch_axis(shape) -> Optional[int]:
+    """Index of the (single) axis proportional to the batch size, or None."""
+    axes = [i for i, d in enumerate(shape) if d.exp > 0]
+    if not axes:
+        return None
+    if len(axes) > 1 or shape[axes[0]].exp != 1:
+        raise ValueError(f"shape {shape} is not linear in the batch size along one axis; cannot shard it")
+    return axes[0]
+
+
+def shard_sizes(global_batch: int, world: int) -> List[int]:
+    """Per-rank batch sizes: as even as possible, earlier ranks take the remainder."""
+    base, rem = divmod(global_batch, world)
+    return [base + (1 if r < rem else 0) for r in range(world)]
+
+
+def split_inputs(graph: Graph, inputs: Sequence[np.ndarray], global_batch: int, rank: int, world: int) -> List[np.ndarray]:
+    sizes = shard_sizes(global_batch, world)
+    start = sum(sizes[:rank])
+    out = []
+    for v, x in zip(graph.inputs, inputs):
+        shape = graph[v].shape
+        axis = batch_axis(shape)
+        if axis is None:
+            out.append(x)
+            continue
+        f = shape[axis].factor
+        sl = [slice(None)] * x.ndim
+        sl[axis] = slice(start * f, (start + sizes[rank]) * f)
+        out.append(np.ascontiguousarray(x[tuple(sl)]))
+    return out
+
+
+def merge_outputs(graph: Graph, per_rank_outputs: Sequence[Sequence[np.ndarray]]) -> List[np.ndarray]:
+    merged = []
+    for i, v in enumerate(graph.outputs):
+        axis = batch_axis(graph[v].shape)
+        parts = [outs[i] for outs in per_rank_outputs]
+        if axis is None:
+            for p in parts[1:]:
+                if not np.array_equal(p, parts[0], equal_nan=True):
+                    raise ValueError(f"output {i} has no batch axis but differs between ranks")
+            merged.append(parts[0])
+        else:
+            merged.append(np.concatenate(parts, axis=axis))
+    return merged
+
+
+def aggregate_throughput(units_per_rank: Sequence[int], ms_per_rank: Sequence[float]) -> float:
+    """Whole-job units per second: all units over the slowest rank's time."""
+    return sum(units_per_rank) / (max(ms_per_rank) / 1000.0)

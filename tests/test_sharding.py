@@ -1,0 +1,72 @@
+"""Batch sharding on CPU with two gloo ranks: each rank evaluates its shard of a global batch (with
+the CPU oracle standing in for a device), rank 0 merges and compares with the unsharded result."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from kyanite_b200.configs import resnet_tower
+from kyanite_b200.graph import BATCH, DType, Graph, shape
+from kyanite_b200.sharding import aggregate_throughput, batch_axis, merge_outputs, shard_sizes, split_inputs
+from oracle.cpu_eval import cpu_eval_graph
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, global_batch, result_path):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        graph, make_inputs = resnet_tower(channels=8, blocks=1)
+        inputs = make_inputs(global_batch, 3)
+        mine = split_inputs(graph, inputs, global_batch, rank, world)
+        sizes = shard_sizes(global_batch, world)
+        outs = cpu_eval_graph(graph.to_bytes(), sizes[rank], mine)
+        gathered = [None] * world
+        dist.all_gather_object(gathered, outs)
+        times = [None] * world
+        dist.all_gather_object(times, 1.0 + rank)   # pretend rank r took (1 + r) ms
+        if rank == 0:
+            merged = merge_outputs(graph, gathered)
+            full = cpu_eval_graph(graph.to_bytes(), global_batch, inputs)
+            ok = all(np.allclose(a, b, rtol=1e-5, atol=1e-6) for a, b in zip(merged, full))
+            rate = aggregate_throughput(sizes, times)
+            with open(result_path, "w") as f:
+                f.write(f"{int(ok)} {rate}")
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("global_batch", [8, 7])
+def test_two_rank_batch_sharding(tmp_path, global_batch):
+    result = tmp_path / "result.txt"
+    mp.spawn(_worker, args=(2, _free_port(), global_batch, str(result)), nprocs=2, join=True)
+    ok, rate = result.read_text().split()
+    assert ok == "1"
+    assert float(rate) == pytest.approx(global_batch / 0.002)   # slowest rank: 2 ms
+
+
+def test_shard_helpers():
+    assert shard_sizes(10, 4) == [3, 3, 2, 2]
+    assert batch_axis(shape(BATCH, 3)) == 0
+    assert batch_axis(shape(4, 3)) is None
+    g = Graph()
+    a = g.input(shape(BATCH, 2))
+    t = g.input(shape(3))
+    g.output(g.add(a, g.view(g.slice(t, 0, (0, 2, 1)), shape(1, 2))))
+    x = np.arange(8, dtype=np.float32).reshape(4, 2)
+    tt = np.ones(3, np.float32)
+    s0 = split_inputs(g, [x, tt], 4, 0, 2)
+    s1 = split_inputs(g, [x, tt], 4, 1, 2)
+    assert np.array_equal(s0[0], x[:2]) and np.array_equal(s1[0], x[2:]) and s0[1] is tt
+    with pytest.raises(ValueError):
+        batch_axis((BATCH * BATCH,))
