@@ -413,6 +413,7 @@ struct ConvClParams {
     // bulk-copy epilogue: the residual tile is prefetched into shared memory by the copy engine while
     // the mainloop runs and the finished tile leaves through a bulk tensor store
     int32_t tma_io, has_res;
+    int32_t io_alias;                   // the in/out tile reuses a retired pipeline slot instead of its own region
     const float* bias;                  // tma_io: one value per output channel (or null)
     int64_t bias_stride;
     uint32_t* status;
@@ -436,9 +437,11 @@ tc_conv_cl_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     const uint32_t w_bytes = (uint32_t)p.kernel_h * kATileBytes;                 // R tiles of 128 x 128 B
     const uint32_t x_tile_bytes = (uint32_t)(p.hb + p.kernel_h - 1) * 1024u;     // one sub-tile window
     const uint32_t stage_bytes = w_bytes + (uint32_t)p.per_cta * x_tile_bytes;
-    const uint32_t io_base = base + (uint32_t)stages * stage_bytes;              // [sub-tile][pixel][128 channels] f32
+    // in/out tile [sub-tile][pixel][128 channels] f32: its own region behind the stages, or (io_alias)
+    // the pipeline slot that retires first
     const uint32_t io_tile_bytes = p.tma_io ? (uint32_t)p.ncols * 512u : 0u;
-    const uint32_t bar_base = io_base + (uint32_t)p.per_cta * io_tile_bytes;
+    const uint32_t io_base = p.io_alias ? base + (uint32_t)(p.iters % stages) * stage_bytes : base + (uint32_t)stages * stage_bytes;
+    const uint32_t bar_base = base + (uint32_t)stages * stage_bytes + (p.io_alias ? 0u : (uint32_t)p.per_cta * io_tile_bytes);
     const uint32_t full_bar = bar_base, empty_bar = bar_base + 8u * stages, accum_bar = bar_base + 16u * stages;
     const uint32_t res_bar = accum_bar + 8u;
     const uint32_t slot_addr = res_bar + 8u;
@@ -470,9 +473,32 @@ tc_conv_cl_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     const int k0 = blockIdx.y * kBlockM;             // first output channel of this CTA
     const int first_subtile = blockIdx.x * p.per_cta;
 
+    // Programmatic dependent launch: let the next kernel of the step list be scheduled onto SMs as
+    // this grid's CTAs retire (its prologue then overlaps our tail) ...
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
     if (warp == 0 && lane == 0) {
         // ---------------- producer
-        if (p.tma_io && p.has_res) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+        if (p.tma_io) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_res) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_out) : "memory");
+        }
+        // ... and, being such a dependent ourselves, touch nothing the previous kernel wrote before it
+        // has completed.  Every load is issued by this thread; MMAs and the epilogue follow from them.
+        // The filter is a constant of the plan, not an output of the previous kernel: its tiles for the
+        // first round of stages are requested before the wait, so their latency overlaps the
+        // previous kernel's tail.
+        const int early = p.iters < stages ? p.iters : stages;
+        for (int it = 0; it < early; it++) {
+            const uint32_t bar = full_bar + 8u * it;
+            mbar_expect_tx(bar, stage_bytes);
+            const int sx = it / p.c_blocks, cb = it - sx * p.c_blocks;
+            tma_load_4d(base + (uint32_t)it * stage_bytes, &map_w, bar, cb * kBlockK, k0, sx, 0);
+        }
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        auto prefetch_residual = [&]() {
             int valid = p.subtiles - first_subtile;
             if (valid > p.per_cta) valid = p.per_cta;
             mbar_expect_tx(res_bar, (uint32_t)valid * io_tile_bytes);
@@ -483,16 +509,19 @@ tc_conv_cl_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 const int img = sub / (p.tiles_w * p.tiles_h);
                 tma_load_4d(io_base + (uint32_t)i * io_tile_bytes, &map_res, res_bar, k0, tw * 8, th * p.hb, img);
             }
-        }
+        };
+        if (p.tma_io && p.has_res && !p.io_alias) prefetch_residual();   // own region: as early as possible
         for (int it = 0; it < p.iters; it++) {
             const int st = it % stages;
             const uint32_t parity = ((it / stages) & 1) ^ 1;
-            if (!mbar_wait(empty_bar + 8u * st, parity, abandon, p.status, 1)) break;
             const uint32_t bar = full_bar + 8u * st;
-            mbar_expect_tx(bar, stage_bytes);
             const int sx = it / p.c_blocks, cb = it - sx * p.c_blocks;
             const uint32_t stage_addr = base + (uint32_t)st * stage_bytes;
-            tma_load_4d(stage_addr, &map_w, bar, cb * kBlockK, k0, sx, 0);
+            if (it >= early) {
+                if (!mbar_wait(empty_bar + 8u * st, parity, abandon, p.status, 1)) break;
+                mbar_expect_tx(bar, stage_bytes);
+                tma_load_4d(stage_addr, &map_w, bar, cb * kBlockK, k0, sx, 0);
+            }
             for (int i = 0; i < p.per_cta; i++) {
                 const int sub = first_subtile + i;       // past the end: every coordinate is out of range, zero fill
                 const int tw = sub % p.tiles_w;
@@ -501,6 +530,14 @@ tc_conv_cl_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 tma_load_4d(stage_addr + w_bytes + (uint32_t)i * x_tile_bytes, &map_x, bar, cb * kBlockK,
                             tw * 8 + sx - p.pad_x, th * p.hb - p.pad_y, img);
             }
+        }
+        if (p.tma_io && p.has_res && p.io_alias) {
+            // The in/out tile lives in the pipeline slot that retires first: slot iters % stages, which
+            // the next iteration would have refilled.  Wait for its last MMA like any refill, then
+            // fetch the residual there; it lands while the remaining stages are still being consumed.
+            const int it = p.iters, st = it % stages;
+            const uint32_t parity = ((it / stages) & 1) ^ 1;
+            if (mbar_wait(empty_bar + 8u * st, parity, abandon, p.status, 1)) prefetch_residual();
         }
     } else if (warp == 1 && lane == 0) {
         // ---------------- MMA issuer: M = 128 output channels.  The windows of the CTA's sub-tiles lie
@@ -535,14 +572,26 @@ tc_conv_cl_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         const bool ok = mbar_wait(accum_bar, 0, abandon, p.status, 3);
         tc_fence_after();
         const bool k_valid = k < p.k_out;
-        if (ok && p.tma_io) {
+        if (p.tma_io) {
             const float bias = (p.bias != nullptr && k_valid) ? p.bias[k * p.bias_stride] : 0.f;
-            bool res_ok = true;
-            if (p.has_res) res_ok = mbar_wait(res_bar, 0, abandon, p.status, 4);
+            bool res_ok = ok;
+            if (ok && p.has_res) res_ok = mbar_wait(res_bar, 0, abandon, p.status, 4);
             float* io = (float*)(gen_base + (io_base - base));
-            if (res_ok) {
+            // the loop below synchronises the four epilogue warps, so they must agree on entering it:
+            // vote (every epilogue thread gets here, its waits being bounded)
+            uint32_t all_ok;
+            asm volatile(
+                "{\n\t.reg .pred p, q;\n\t"
+                "setp.ne.u32 p, %1, 0;\n\t"
+                "bar.red.and.pred q, 2, 128, p;\n\t"
+                "selp.u32 %0, 1, 0, q;\n\t}"
+                : "=r"(all_ok)
+                : "r"((uint32_t)res_ok)
+                : "memory");
+            if (all_ok) {
                 for (int i = 0; i < p.per_cta; i++) {
-                    if (first_subtile + i >= p.subtiles) break;
+                    const int sub = first_subtile + i;
+                    if (sub >= p.subtiles) break;
                     for (int c0 = 0; c0 < p.ncols; c0 += 32) {
                         uint32_t v[32];
                         tmem_load_32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(i * p.col_stride + c0), v);
@@ -554,22 +603,19 @@ tc_conv_cl_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                             cell[j * kBlockM] = finish(val, p.act, p.round_tf32);
                         }
                     }
+                    // this sub-tile is complete: hand it to the copy engine while the next one is computed
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> bulk store
+                    asm volatile("bar.sync 1, 128;" ::: "memory");                 // the four epilogue warps
+                    if (threadIdx.x == 64) {
+                        const int tw = sub % p.tiles_w;
+                        const int th = (sub / p.tiles_w) % p.tiles_h;
+                        const int img = sub / (p.tiles_w * p.tiles_h);
+                        tma_store_4d(&map_out, io_base + (uint32_t)i * io_tile_bytes, k0, tw * 8, th * p.hb, img);
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
                 }
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the bulk store
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (threadIdx.x == 64 && res_ok) {
-                for (int i = 0; i < p.per_cta; i++) {
-                    const int sub = first_subtile + i;
-                    if (sub >= p.subtiles) break;
-                    const int tw = sub % p.tiles_w;
-                    const int th = (sub / p.tiles_w) % p.tiles_h;
-                    const int img = sub / (p.tiles_w * p.tiles_h);
-                    tma_store_4d(&map_out, io_base + (uint32_t)i * io_tile_bytes, k0, tw * 8, th * p.hb, img);
-                }
-                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // shared memory must outlive the read
-            }
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // shared memory must outlive the reads
         } else if (ok) {
             for (int i = 0; i < p.per_cta; i++) {
                 const int sub = first_subtile + i;
@@ -719,7 +765,7 @@ static bool prepare_conv_channels_last(const ConvParams& c, uint32_t* status_wor
         }
     }
     const int io_bytes = tma_io ? p.ncols * 512 : 0;
-    if (2 * (w_bytes + x_bytes) + io_bytes > smem_budget) return false;
+    if (2 * (w_bytes + x_bytes) + (io_bytes <= w_bytes + x_bytes ? 0 : io_bytes) > smem_budget) return false;
     p.tiles_w = (c.ow + 7) / 8;
     p.tiles_h = (c.oh + p.hb - 1) / p.hb;
     const int64_t subtiles = (int64_t)c.n * p.tiles_w * p.tiles_h;
@@ -731,7 +777,9 @@ static bool prepare_conv_channels_last(const ConvParams& c, uint32_t* status_wor
     int best = 1;
     double best_cost = 1e300;
     for (int per = 1; per <= kMaxPerCta; per++) {
-        if (8 * (per * p.hb + (per - 1) * (c.r - 1)) > 256 || 2 * (w_bytes + per * x_bytes) + per * io_bytes > smem_budget) break;
+        const int stage = w_bytes + per * x_bytes;
+        const int io_extra = per * io_bytes <= stage ? 0 : per * io_bytes;   // fits a retired slot, or needs its own region
+        if (8 * (per * p.hb + (per - 1) * (c.r - 1)) > 256 || 2 * stage + io_extra > smem_budget) break;
         const int64_t ctas = ((subtiles + per - 1) / per) * k_blocks;
         const double waves = (double)((ctas + 147) / 148);
         const double cost = waves * (w_bytes + (double)per * x_bytes);
@@ -742,7 +790,10 @@ static bool prepare_conv_channels_last(const ConvParams& c, uint32_t* status_wor
     p.n_mma = 8 * (p.per_cta * p.hb + (p.per_cta - 1) * (c.r - 1));
     p.tmem_cols = std::max(32, pow2_ceil(p.n_mma));
     const int stage_bytes = w_bytes + p.per_cta * x_bytes;
-    p.stages = std::max(2, std::min(4, (smem_budget - p.per_cta * io_bytes) / stage_bytes));
+    // the in/out tile may reuse the first pipeline slot to retire when it fits into one slot
+    const bool io_alias = tma_io && p.per_cta * io_bytes <= stage_bytes;
+    p.io_alias = io_alias ? 1 : 0;
+    p.stages = std::max(2, std::min(4, (smem_budget - (io_alias ? 0 : p.per_cta * io_bytes)) / stage_bytes));
     p.k_out = c.k;
     p.c_blocks = (c.c + kBlockK - 1) / kBlockK;
     p.kernel_h = c.r;
@@ -791,7 +842,7 @@ static bool prepare_conv_channels_last(const ConvParams& c, uint32_t* status_wor
         launch.map_res = launch.map_a;
         launch.map_out = launch.map_a;
     }
-    launch.smem_bytes = p.stages * stage_bytes + p.per_cta * io_bytes + 16 * p.stages + 64 + 1024;
+    launch.smem_bytes = p.stages * stage_bytes + (p.io_alias ? 0 : p.per_cta * io_bytes) + 16 * p.stages + 64 + 1024;
     launch.channels_last = true;
     return true;
 }
@@ -928,7 +979,20 @@ int tc_launch_step(const Step& step, cudaStream_t stream) {
         }
     }
     if (l.grid.x == 0 || l.grid.y == 0 || l.grid.z == 0) return 0;
-    if (l.channels_last) tc_conv_cl_kernel<<<l.grid, kThreads, l.smem_bytes, stream>>>(l.map_a, l.map_b, l.map_res, l.map_out, l.cl);
+    if (l.channels_last) {
+        // may start while the previous kernel of the stream drains (see griddepcontrol in the kernel)
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = l.grid;
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = (size_t)l.smem_bytes;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        return (int)cudaLaunchKernelEx(&cfg, tc_conv_cl_kernel, l.map_a, l.map_b, l.map_res, l.map_out, l.cl);
+    }
     else tc_contract_kernel<<<l.grid, kThreads, l.smem_bytes, stream>>>(l.map_a, l.map_b, l.p);
     return (int)cudaGetLastError();
 }
