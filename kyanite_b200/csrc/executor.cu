@@ -110,6 +110,11 @@ struct Executor {
                     s.gemm.a = (const float*)ptr[0];
                     s.gemm.b = (const float*)ptr[1];
                     s.gemm.c = (float*)ptr[2];
+                    s.gemm.scratch = nullptr;
+                    if (s.gemm.splits > 1) {   // the split-K scratch buffer is the last operand
+                        s.gemm.scratch = (float*)ptr.back();
+                        ptr.pop_back();
+                    }
                     s.gemm.add1 = ptr.size() > 3 ? (const float*)ptr[3] : nullptr;
                     s.gemm.add2 = ptr.size() > 4 ? (const float*)ptr[4] : nullptr;
                     break;

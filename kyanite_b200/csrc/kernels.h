@@ -100,6 +100,10 @@ struct GemmParams {
     int64_t sa[3], sb[3], sc[3], s1[3], s2[3];   // (batch, row, col) strides
     int32_t act;
     int32_t round_tf32;      // round outputs to TF32 (they only feed tensor-core contractions)
+    // tensor-core path only: K is cut into `splits` slices whose partial tiles go to `scratch`
+    // ([batch][slice][m][n] f32) and are summed by a second kernel; 1 = no split
+    int32_t splits;
+    float* scratch;
 };
 
 // ---- 2D convolution (cross-correlation, zero padding) with fused epilogue

@@ -40,6 +40,7 @@ constexpr long long kWaitCycles = 4000000000ll;   // ~2 s at 2 GHz
 struct TcParams {
     int32_t mode;   // 0 = matmul, 1 = conv
     int32_t bn, tmem_cols, k_iters, stages;
+    int32_t splits, k_iters_total;   // matmul split K: slices per batch entry, K blocks overall (k_iters = per slice)
     // conv tiling
     int32_t cblocks, kernel_w, pad_y, pad_x, wb, hb, nb, tiles_w, tiles_h;
     int32_t wb_shift, hb_shift;   // log2 of wb, hb
@@ -197,7 +198,11 @@ tc_contract_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     // tile coordinates
     int m0 = 0, n0_img = 0, h0 = 0, w0 = 0;
     const int ncol0 = blockIdx.y * p.bn;
-    const int batch = blockIdx.z;
+    // matmul with split K: blockIdx.z enumerates (batch, K slice); each slice writes its own partial tile
+    const int zb = blockIdx.z;
+    const int batch = p.mode == 0 ? zb / p.splits : 0;
+    const int k_first = p.mode == 0 ? (zb - batch * p.splits) * p.k_iters : 0;   // first K block of this slice
+    const int k_count = p.mode == 0 ? min(p.k_iters, p.k_iters_total - k_first) : p.k_iters;
     if (p.mode == 0) {
         m0 = blockIdx.x * kBlockM;
     } else {
@@ -211,14 +216,14 @@ tc_contract_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 
     if (warp == 0 && lane == 0) {
         // ---------------- producer
-        for (int it = 0; it < p.k_iters; it++) {
+        for (int it = 0; it < k_count; it++) {
             const int s = it % stages;
             const uint32_t parity = ((it / stages) & 1) ^ 1;
             if (!mbar_wait(empty_bar + 8u * s, parity, abandon, p.status, 1)) break;
             mbar_expect_tx(full_bar + 8u * s, kATileBytes + b_tile_bytes);
             if (p.mode == 0) {
-                tma_load_4d(a_base + s * kATileBytes, &map_a, full_bar + 8u * s, it * kBlockK, m0, batch, 0);
-                tma_load_3d(b_base + s * b_tile_bytes, &map_b, full_bar + 8u * s, it * kBlockK, ncol0, batch);
+                tma_load_4d(a_base + s * kATileBytes, &map_a, full_bar + 8u * s, (k_first + it) * kBlockK, m0, batch, 0);
+                tma_load_3d(b_base + s * b_tile_bytes, &map_b, full_bar + 8u * s, (k_first + it) * kBlockK, ncol0, batch);
             } else {
                 const int tap = it / p.cblocks, cb = it - tap * p.cblocks;
                 const int r = tap / p.kernel_w, sx = tap - r * p.kernel_w;
@@ -232,7 +237,7 @@ tc_contract_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         // instruction descriptor: f32 accumulate, tf32 x tf32, both K-major, M = 128, N = bn
         const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(p.bn >> 3) << 17) | ((uint32_t)(kBlockM >> 4) << 24);
         bool ok = true;
-        for (int it = 0; it < p.k_iters && ok; it++) {
+        for (int it = 0; it < k_count && ok; it++) {
             const int s = it % stages;
             const uint32_t parity = (it / stages) & 1;
             ok = mbar_wait(full_bar + 8u * s, parity, abandon, p.status, 2);
@@ -258,7 +263,7 @@ tc_contract_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         auto row_offsets = [&](int row, int64_t& off_o, int64_t& off_1, int64_t& off_2) -> bool {
             if (p.mode == 0) {
                 const int64_t m = (int64_t)m0 + row;
-                off_o = batch * p.so[0] + m * p.so[1];
+                off_o = zb * p.so[0] + m * p.so[1];   // (with split K the output is the slice's partial tile)
                 off_1 = batch * p.s1[0] + m * p.s1[1];
                 off_2 = batch * p.s2[0] + m * p.s2[1];
                 return m < p.m;
@@ -377,6 +382,35 @@ tc_contract_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     __syncthreads();
     if (warp == 0) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)p.tmem_cols) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------- split-K reduction
+// Sums the per-slice partial tiles [batch][slice][M][N] of a split-K matmul and applies the epilogue.
+struct SplitKReduceParams {
+    const float* partial;
+    int32_t splits;
+    int64_t batch, m, n;
+    float* out;
+    const float* add1;
+    const float* add2;
+    int64_t so[3], s1[3], s2[3];
+    int32_t act, round_tf32;
+};
+
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const __grid_constant__ SplitKReduceParams p) {
+    const int64_t total = p.batch * p.m * p.n;
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += step) {
+        const int64_t n = idx % p.n;
+        const int64_t m = (idx / p.n) % p.m;
+        const int64_t b = idx / (p.n * p.m);
+        const float* src = p.partial + (b * p.splits * p.m + m) * p.n + n;
+        float acc = 0.f;
+        for (int s = 0; s < p.splits; s++) acc += src[(int64_t)s * p.m * p.n];
+        if (p.add1) acc += p.add1[b * p.s1[0] + m * p.s1[1] + n * p.s1[2]];
+        if (p.add2) acc += p.add2[b * p.s2[0] + m * p.s2[1] + n * p.s2[2]];
+        p.out[b * p.so[0] + m * p.so[1] + n * p.so[2]] = finish(acc, p.act, p.round_tf32);
     }
 }
 
@@ -719,6 +753,8 @@ struct TcLaunch {
     CUtensorMap map_a, map_b, map_res, map_out;
     TcParams p;
     bool channels_last = false;   // tc_conv_cl_kernel with `cl` instead of tc_contract_kernel with `p`
+    bool split_k = false;         // tc_contract_kernel writes partial tiles, splitk_reduce_kernel finishes
+    SplitKReduceParams reduce;
     ConvClParams cl;
     dim3 grid;
     int smem_bytes;
@@ -889,6 +925,42 @@ void tc_prepare_step(Step& step, uint32_t* status_word) {
         int bbox[3] = {kBlockK, p.bn, 1};
         launch->map_b = make_map(g.b, 3, bdims, bstr, bbox);
         launch->grid = dim3((unsigned)((g.m + kBlockM - 1) / kBlockM), (unsigned)((n_cols + p.bn - 1) / p.bn), (unsigned)g.batch);
+        p.k_iters_total = p.k_iters;
+        p.splits = 1;
+        if (g.splits > 1) {
+            // split K: every slice writes a dense [m][n] partial tile into the step's scratch buffer,
+            // splitk_reduce_kernel sums the slices and applies the epilogue
+            const int per_slice = (p.k_iters_total + g.splits - 1) / g.splits;
+            p.k_iters = per_slice;
+            p.splits = (p.k_iters_total + per_slice - 1) / per_slice;   // no empty slice
+            SplitKReduceParams& r = launch->reduce;
+            memset(&r, 0, sizeof(r));
+            r.partial = g.scratch;
+            r.splits = p.splits;
+            r.batch = g.batch;
+            r.m = g.m;
+            r.n = g.n;
+            r.out = g.c;
+            r.add1 = g.add1;
+            r.add2 = g.add2;
+            for (int i = 0; i < 3; i++) {
+                r.so[i] = g.sc[i];
+                r.s1[i] = g.s1[i];
+                r.s2[i] = g.s2[i];
+            }
+            r.act = g.act;
+            r.round_tf32 = g.round_tf32;
+            p.out = g.scratch;
+            p.add1 = nullptr;
+            p.add2 = nullptr;
+            p.act = 0;
+            p.round_tf32 = 0;
+            p.so[0] = g.m * g.n;   // per (batch, slice)
+            p.so[1] = g.n;
+            p.so[2] = 1;
+            launch->grid.z = (unsigned)(g.batch * p.splits);
+            launch->split_k = true;
+        }
     } else {
         const ConvParams& c = step.conv;
         if (prepare_conv_channels_last(c, status_word, *launch)) {
@@ -900,6 +972,8 @@ void tc_prepare_step(Step& step, uint32_t* status_word) {
         p.n = c.k;
         p.cblocks = (c.c + kBlockK - 1) / kBlockK;
         p.k_iters = c.r * c.s * p.cblocks;
+        p.k_iters_total = p.k_iters;
+        p.splits = 1;
         p.kernel_w = c.s;
         p.pad_y = c.pad_y;
         p.pad_x = c.pad_x;
@@ -993,7 +1067,12 @@ int tc_launch_step(const Step& step, cudaStream_t stream) {
         cfg.numAttrs = 1;
         return (int)cudaLaunchKernelEx(&cfg, tc_conv_cl_kernel, l.map_a, l.map_b, l.map_res, l.map_out, l.cl);
     }
-    else tc_contract_kernel<<<l.grid, kThreads, l.smem_bytes, stream>>>(l.map_a, l.map_b, l.p);
+    tc_contract_kernel<<<l.grid, kThreads, l.smem_bytes, stream>>>(l.map_a, l.map_b, l.p);
+    if (l.split_k) {
+        const int64_t total = l.reduce.batch * l.reduce.m * l.reduce.n;
+        const unsigned blocks = (unsigned)std::min<int64_t>((total + 255) / 256, 148 * 8);
+        splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(l.reduce);
+    }
     return (int)cudaGetLastError();
 }
 

@@ -599,6 +599,27 @@ class Planner {
                 if (addends.size() > 1) p.s2[i] = addends[1].ss.strides[i];
             }
             p.act = (int32_t)m->act;
+            p.splits = 1;
+            if (tensor_core) {
+                // A contraction with few output tiles but a long K would leave most SMs idle: cut K into
+                // slices computed by separate CTAs.  Their partial tiles go to a scratch buffer of the
+                // arena (live only during this step) and a second small kernel sums them.
+                const int64_t bn = p.n > 256 ? 128 : std::min<int64_t>((std::min<int64_t>(p.n, 256) + 15) / 16 * 16, 256);
+                const int64_t tiles = ((p.m + 127) / 128) * ((p.n + bn - 1) / bn) * p.batch;
+                const int64_t k_blocks = (p.k + 31) / 32;
+                if (tiles < 48 && k_blocks >= 16) {
+                    int64_t splits = std::min<int64_t>(std::min<int64_t>(k_blocks / 4, (96 + tiles - 1) / tiles), 32);
+                    if (splits > 1) {
+                        const int64_t per = (k_blocks + splits - 1) / splits;
+                        splits = (k_blocks + per - 1) / per;
+                        p.splits = (int32_t)splits;
+                        PlanTensor scratch = alloc_shared({p.batch, splits, p.m, p.n}, DType::F32, root);
+                        s.operands.push_back(scratch);
+                        s.writes.push_back(1);
+                        s.launches = 2;
+                    }
+                }
+            }
             s.flops = 2.0 * (double)p.batch * (double)p.m * (double)p.n * (double)p.k;
             s.desc = "matmul b=" + std::to_string(p.batch) + " m=" + std::to_string(p.m) + " n=" + std::to_string(p.n) +
                      " k=" + std::to_string(p.k);
@@ -637,6 +658,7 @@ class Planner {
         }
         s.desc += std::string(" +") + std::to_string(addends.size()) + (m->act == Activation::Relu ? " relu" : "");
         if (tensor_core) s.desc += " tf32";
+        if (s.kind == StepKind::Gemm && s.gemm.splits > 1) s.desc += " splitk=" + std::to_string(s.gemm.splits);
         int64_t total = 1;
         for (int64_t d : native) total *= d;
         if (total != 0) push_step(std::move(s));

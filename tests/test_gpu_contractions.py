@@ -1,0 +1,83 @@
+"""Tensor-core contraction kernels against the CPU oracle on shapes the reference suite does not
+reach: tiles with ragged edges, channel tails, boards that are not a power of two, 5x5 filters, split-K
+matmuls (partial tiles through the step's scratch buffer), channels-last chains with a residual.
+Tolerance for TF32 operands: abs >= 4e-3 * max(1, largest |expected|) AND rel >= 4e-3 is a mismatch."""
+import numpy as np
+import pytest
+
+from kyanite_b200.configs import resnet_tower
+from kyanite_b200.executor import MATH_F32, MATH_TF32, CudaExecutor, plan_describe
+from kyanite_b200.graph import BATCH, Graph, shape
+from oracle.cpu_eval import assert_tensors_match, cpu_eval_graph
+
+pytestmark = pytest.mark.gpu
+
+
+def rng(seed, *s):
+    return np.random.Generator(np.random.PCG64(seed)).standard_normal(s).astype(np.float32)
+
+
+def check(g, batch, ins, mode=MATH_TF32, expect=None):
+    blob = g.to_bytes()
+    if expect is not None:
+        assert expect in plan_describe(blob, batch, math_mode=mode)
+    want = cpu_eval_graph(blob, batch, ins)
+    with CudaExecutor(0, blob, batch, math_mode=mode) as ex:
+        for _ in range(2):
+            got = ex.evaluate(ins)
+            assert_tensors_match(want, got, tol_abs=4e-3, tol_rel=4e-3, abs_scaled=True)
+
+
+@pytest.mark.parametrize("b,m,n,k", [(1, 256, 128, 64), (1, 128, 16, 32), (3, 200, 72, 100), (1, 1000, 300, 36)])
+def test_matmul_tiles(b, m, n, k):
+    g = Graph()
+    a = g.input(shape(b, m, k))
+    w = g.input(shape(b, n, k))
+    g.output(g.batched_mat_mul(a, g.permute(w, [0, 2, 1])))
+    check(g, 0, [rng(1, b, m, k), rng(2, b, n, k)], expect="Gemm/tc")
+
+
+@pytest.mark.parametrize("b,m,n,k", [(1, 256, 256, 2048), (1, 128, 64, 4096), (2, 130, 40, 1000), (1, 64, 16, 512)])
+def test_matmul_split_k(b, m, n, k):
+    g = Graph()
+    a = g.input(shape(b, m, k))
+    w = g.input(shape(b, n, k))
+    bias = g.input(shape(1, 1, n))
+    g.output(g.relu(g.add(g.batched_mat_mul(a, g.permute(w, [0, 2, 1])), bias)))
+    check(g, 0, [rng(1, b, m, k), rng(2, b, n, k), rng(3, 1, 1, n)], expect="splitk=")
+
+
+@pytest.mark.parametrize("n,c,h,w,k,r,pad", [(4, 32, 8, 8, 128, 3, 1), (8, 3, 8, 8, 5, 3, 1), (2, 21, 8, 8, 16, 1, 0),
+                                              (3, 8, 16, 16, 24, 3, 1), (5, 12, 9, 9, 20, 3, 1), (2, 16, 64, 64, 16, 3, 1),
+                                              (2, 4, 8, 8, 8, 5, 2), (3, 130, 8, 8, 136, 3, 1)])
+def test_conv_shapes(n, c, h, w, k, r, pad):
+    g = Graph()
+    x = g.input(shape(n, c, h, w))
+    wt = g.constant(shape(k, c, r, r), rng(3, k, c, r, r) * 0.1)
+    bias = g.constant(shape(1, k, 1, 1), rng(4, k))
+    g.output(g.relu(g.add(g.conv(x, wt, 1, 1, pad, pad), bias)))
+    check(g, 0, [rng(5, n, c, h, w)], expect="Conv/tc")
+
+
+def test_channels_last_chain_with_residual_and_runtime_filter():
+    # conv -> conv (+ residual) stays channels-last; the second filter is a graph input, so it is
+    # rearranged by a copy step instead of on the host
+    g = Graph()
+    x = g.input(shape(BATCH, 16, 8, 8))
+    w2 = g.input(shape(16, 16, 3, 3))
+    w1 = g.constant(shape(16, 16, 3, 3), rng(1, 16, 16, 3, 3) * 0.1)
+    b1 = g.constant(shape(1, 16, 1, 1), rng(2, 16))
+    y = g.relu(g.add(g.conv(x, w1, 1, 1, 1, 1), b1))
+    z = g.relu(g.add(g.conv(y, w2, 1, 1, 1, 1), y))
+    g.output_all([z, g.flatten(z, 1)])
+    check(g, 5, [rng(3, 5, 16, 8, 8), rng(4, 16, 16, 3, 3) * 0.1], expect="Conv/tc")
+
+
+@pytest.mark.parametrize("mode,tol", [(MATH_F32, 1e-4), (MATH_TF32, 4e-3)])
+def test_full_tower(mode, tol):
+    g, make_inputs = resnet_tower()
+    ins = make_inputs(16, 7)
+    want = cpu_eval_graph(g.to_bytes(), 16, ins)
+    with CudaExecutor(0, g, 16, math_mode=mode) as ex:
+        got = ex.evaluate(ins)
+    assert_tensors_match(want, got, tol_abs=tol, tol_rel=tol)
