@@ -166,6 +166,33 @@ KN_API int kn_executor_last_profile(kn_executor* exec, char* buf, size_t cap, si
  * the event and launch gaps of a one-by-one run; this one does not.)  No reference counterpart. */
 KN_API int kn_executor_time_step(kn_executor* exec, int step, int launches, float* microseconds);
 
+/* Matrix multiply that allocates nothing.  No counterpart in the reference.
+ *
+ *     C[m][n] = sum_k A[m][k] * B[n][k]        (A, B, C dense row-major f32 in DEVICE memory)
+ *
+ * For callers that cannot allocate device memory: a serving loop with a fixed memory footprint, a
+ * plugin callback inside a runtime that owns every byte of the device, a context whose pool is
+ * already handed out.  It runs the executor's split-K tensor-core matmul (TF32 operands rounded to
+ * nearest, f32 accumulation) with the per-slice partial sums kept in a fixed array inside the
+ * library's device module instead of an allocated buffer; it calls no cudaMalloc / cudaFree and no
+ * allocating library routine.  The kernels are enqueued on `stream` (a cudaStream_t, may be NULL for
+ * the default stream) of the CURRENT device and the call returns without waiting.
+ *
+ *  - Limit: slices * m * n * 4 bytes <= KN_STATIC_SCRATCH_BYTES, where slices (1..32) grows with k
+ *    and shrinks with the number of 128-row output tiles; larger problems are rejected with
+ *    KN_ERR_UNSUPPORTED and a message that states the need.  k must be a multiple of 4; A and B
+ *    16-byte aligned.
+ *  - The array costs KN_STATIC_SCRATCH_BYTES of device memory on every GPU that loads the library, for
+ *    the life of the process.
+ *  - The first call on a device looks up the array's device address and opts the kernel in to large
+ *    shared memory; make that first call outside any stream capture.
+ *  - All calls share the one array (it keeps the previous call's partial sums; every element a call
+ *    reads it has written first, so nothing needs clearing).  Two calls whose kernels may overlap on
+ *    the GPU (different streams, or different threads) race on it: serialise them. */
+#define KN_STATIC_SCRATCH_BYTES (8u << 20)
+KN_API int kn_matmul_tf32_static(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k,
+                                 void* stream);
+
 /* Host-only element semantics, exported so the scalar rules can be tested without a device:
  * applies one unary / binary operation to 64-bit canonical element patterns. */
 KN_API int kn_scalar_unary(int unary_op, int from_dtype, int to_dtype, uint64_t x, uint64_t* out);

@@ -43,6 +43,8 @@ struct DeviceGuard {
 
 }  // namespace
 
+void set_last_error(const std::string& message) { g_last_error = message; }
+
 struct Executor {
     int device = 0;
     std::unique_ptr<Plan> plan;

@@ -1077,3 +1077,158 @@ int tc_launch_step(const Step& step, cudaStream_t stream) {
 }
 
 }  // namespace kn
+
+// ------------------------------------------------------------------------------------------------
+// Matrix multiply for callers that must not allocate
+// ------------------------------------------------------------------------------------------------
+// Some hosts of this library run where device allocation is off the table: inside a latency-critical
+// serving loop that has promised its allocator a fixed footprint, from a plugin callback of a runtime
+// that owns all device memory, or on a context whose memory pool is already carved up.  The executor's
+// split-K matmul keeps its partial tiles in the arena it allocated; this entry point runs the same two
+// kernels with the partial tiles in a fixed array that is part of the loaded module instead, so a call
+// allocates nothing (no cudaMalloc / cudaFree, no allocating library routine).  The price: the array
+// occupies KN_STATIC_SCRATCH_BYTES on every GPU that loads the library until the process exits, and it
+// caps the problem size.
+namespace kn {
+namespace {
+
+constexpr size_t kStaticScratchFloats = (size_t)KN_STATIC_SCRATCH_BYTES / 4;
+
+// Device-resident scratch.  In host code these names are host-side stand-ins, NOT device addresses:
+// the device addresses are fetched once per device with cudaGetSymbolAddress (below).
+static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
+static __device__ __align__(256) uint32_t g_static_status[64];
+
+struct StaticDevice {
+    bool ready = false;
+    float* scratch = nullptr;
+    uint32_t* status = nullptr;
+};
+std::mutex g_static_mu;
+StaticDevice g_static_dev[64];
+
+// One-time set-up for the current device: resolve the device addresses of the two arrays and opt the
+// kernel in to large dynamic shared memory.  None of this allocates device memory.
+const StaticDevice& static_device_setup() {
+    int device = -1;
+    cudaError_t err = cudaGetDevice(&device);
+    KN_CHECK(err == cudaSuccess, KN_ERR_CUDA, std::string("cudaGetDevice failed: ") + cudaGetErrorString(err));
+    KN_CHECK(device >= 0 && device < 64, KN_ERR_UNSUPPORTED, "device index above 63");
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    StaticDevice& d = g_static_dev[device];
+    if (!d.ready) {
+        void* scratch = nullptr;
+        void* status = nullptr;
+        err = cudaGetSymbolAddress(&scratch, g_static_scratch);
+        KN_CHECK(err == cudaSuccess && scratch != nullptr, KN_ERR_CUDA,
+                 std::string("cudaGetSymbolAddress(scratch) failed: ") + cudaGetErrorString(err));
+        err = cudaGetSymbolAddress(&status, g_static_status);
+        KN_CHECK(err == cudaSuccess && status != nullptr, KN_ERR_CUDA,
+                 std::string("cudaGetSymbolAddress(status) failed: ") + cudaGetErrorString(err));
+        err = cudaFuncSetAttribute(tc_contract_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        KN_CHECK(err == cudaSuccess, KN_ERR_CUDA, std::string("cudaFuncSetAttribute failed: ") + cudaGetErrorString(err));
+        d.scratch = (float*)scratch;
+        d.status = (uint32_t*)status;
+        d.ready = true;
+    }
+    return d;
+}
+
+void matmul_static(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k, cudaStream_t stream) {
+    KN_CHECK(a != nullptr && b != nullptr && c != nullptr, KN_ERR_INVALID_ARG, "null operand");
+    KN_CHECK(m >= 1 && n >= 1 && k >= 1 && m <= (1ll << 30) && n <= (1ll << 30) && k <= (1ll << 30), KN_ERR_INVALID_ARG,
+             "matrix extent out of range");
+    KN_CHECK(k % 4 == 0, KN_ERR_UNSUPPORTED, "k must be a multiple of 4 (rows of A and B must be 16-byte aligned)");
+    KN_CHECK(((uintptr_t)a & 15) == 0 && ((uintptr_t)b & 15) == 0 && ((uintptr_t)c & 3) == 0, KN_ERR_INVALID_ARG,
+             "A and B must be 16-byte aligned, C 4-byte aligned");
+
+    // same slicing rule as the planner: aim at ~96 CTAs, at least 4 K blocks per slice, at most 32 slices
+    const int bn = n > 256 ? 128 : (int)std::min<int64_t>(round_up((int)std::min<int64_t>(n, 256), 16), 256);
+    const int64_t tiles = ((m + kBlockM - 1) / kBlockM) * ((n + bn - 1) / bn);
+    const int64_t k_blocks = (k + kBlockK - 1) / kBlockK;
+    int64_t splits = std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>(k_blocks / 4, (96 + tiles - 1) / tiles), 32));
+    const int64_t per_slice = (k_blocks + splits - 1) / splits;
+    splits = (k_blocks + per_slice - 1) / per_slice;
+    const size_t need = (size_t)splits * (size_t)m * (size_t)n;
+    KN_CHECK(need <= kStaticScratchFloats, KN_ERR_UNSUPPORTED,
+             "problem too large for the static scratch: " + std::to_string(splits) + " K slices x " + std::to_string(m) + " x " +
+                 std::to_string(n) + " partial sums need " + std::to_string(need * 4) + " bytes, the limit is " +
+                 std::to_string((size_t)KN_STATIC_SCRATCH_BYTES));
+    KN_CHECK((m + kBlockM - 1) / kBlockM <= 0x7FFFFFFFll && (n + bn - 1) / bn <= 65535, KN_ERR_UNSUPPORTED, "grid too large");
+
+    const StaticDevice& dev = static_device_setup();
+
+    TcParams p;
+    memset(&p, 0, sizeof(p));
+    p.mode = 0;
+    p.m = m;
+    p.n = n;
+    p.bn = bn;
+    p.tmem_cols = std::max(32, pow2_ceil(bn));
+    p.k_iters_total = (int)k_blocks;
+    p.k_iters = (int)per_slice;
+    p.splits = (int)splits;
+    p.out = dev.scratch;            // every (slice, row, column) below m x n is overwritten: nothing to clear
+    p.so[0] = m * n;
+    p.so[1] = n;
+    p.so[2] = 1;
+    p.status = dev.status;
+    const int stage_bytes = kATileBytes + bn * 128;
+    p.stages = std::max(2, std::min(6, (200 * 1024) / stage_bytes));
+    p.stages = std::min(p.stages, std::max(2, p.k_iters));
+    {
+        auto classify_out = [&]() { return ((uintptr_t)p.out & 15) == 0 && n % 4 == 0; };
+        p.staged = 1;
+        p.vec4 = classify_out() ? 1 : 0;
+        p.add1_mode = 0;
+        p.add2_mode = 0;
+    }
+    const int staging_bytes = kBlockM * (bn + 4) * 4;
+    const int smem_bytes = std::max(p.stages * stage_bytes + 16 * p.stages + 64, staging_bytes) + 1024;
+
+    int64_t adims[4] = {k, m, 1, 1}, astr[4] = {1, k, 4, 4};
+    int abox[4] = {kBlockK, kBlockM, 1, 1};
+    const CUtensorMap map_a = make_map(a, 4, adims, astr, abox);
+    int64_t bdims[3] = {k, n, 1}, bstr[3] = {1, k, 4};
+    int bbox[3] = {kBlockK, bn, 1};
+    const CUtensorMap map_b = make_map(b, 3, bdims, bstr, bbox);
+
+    SplitKReduceParams r;
+    memset(&r, 0, sizeof(r));
+    r.partial = dev.scratch;
+    r.splits = (int)splits;
+    r.batch = 1;
+    r.m = m;
+    r.n = n;
+    r.out = c;
+    r.so[0] = m * n;
+    r.so[1] = n;
+    r.so[2] = 1;
+
+    dim3 grid((unsigned)((m + kBlockM - 1) / kBlockM), (unsigned)((n + bn - 1) / bn), (unsigned)splits);
+    tc_contract_kernel<<<grid, kThreads, smem_bytes, stream>>>(map_a, map_b, p);
+    cudaError_t err = cudaGetLastError();
+    KN_CHECK(err == cudaSuccess, KN_ERR_CUDA, std::string("launch failed: ") + cudaGetErrorString(err));
+    const int64_t total = m * n;
+    const unsigned blocks = (unsigned)std::min<int64_t>((total + 255) / 256, 148 * 8);
+    splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(r);
+    err = cudaGetLastError();
+    KN_CHECK(err == cudaSuccess, KN_ERR_CUDA, std::string("launch failed: ") + cudaGetErrorString(err));
+}
+
+}  // namespace
+}  // namespace kn
+
+extern "C" KN_API int kn_matmul_tf32_static(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k,
+                                            void* stream) {
+    try {
+        kn::matmul_static(a, b, c, m, n, k, (cudaStream_t)stream);
+        return KN_OK;
+    } catch (const kn::Error& e) {
+        kn::set_last_error(e.what());
+        return e.code;
+    } catch (const std::exception& e) {
+        kn::set_last_error(e.what());
+        return KN_ERR_INTERNAL;
+    }
+}

@@ -11,6 +11,9 @@ void tc_prepare_step(Step& step, uint32_t* status_word);
 // Launches a step marked `tensor_core`; returns a cudaError_t as int.
 int tc_launch_step(const Step& step, cudaStream_t stream);
 
+// Stores the calling thread's error message (what kn_last_error returns).
+void set_last_error(const std::string& message);
+
 // Output tile of the convolution kernel: wb x hb x nb output positions (product 128).
 bool tc_conv_tile(int oh, int ow, int* wb, int* hb, int* nb);
 
