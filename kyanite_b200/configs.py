@@ -120,3 +120,279 @@ def resnet_tower_flops(batch: int, channels: int = 128, blocks: int = 16, board:
     f += 2.0 * px * policy_channels * channels + 2.0 * px * value_channels * channels
     f += 2.0 * batch * value_hidden * value_channels * board * board + 2.0 * batch * 3 * value_hidden
     return f
+
+
+# --------------------------------------------------------------------------------------
+# transformer-shaped workloads
+# --------------------------------------------------------------------------------------
+def _normal(seeds: _Seeds, shape_, std=0.02) -> np.ndarray:
+    return (_rng(seeds.take()).standard_normal(shape_) * std).astype(np.float32)
+
+
+def _dense(g: Graph, seeds: _Seeds, x: Value, n_in: int, n_out: int, bias: bool = True) -> Value:
+    """x [rows, n_in] -> [rows, n_out] with an [n_out, n_in] weight, N(0, 0.02)."""
+    y = g.linear(x, g.constant_tensor(_normal(seeds, (n_out, n_in))))
+    if bias:
+        y = g.add(y, g.constant_tensor(_normal(seeds, (1, n_out))))
+    return y
+
+
+def _gelu(g: Graph, x: Value) -> Value:
+    """x * 0.5 * (1 + erf(x / sqrt(2)))"""
+    from .graph import UnaryOp
+    inner = g.unary(UnaryOp.ERF, g.mul(x, g.scalar(1.0 / math.sqrt(2.0))))
+    return g.mul(g.mul(x, g.scalar(0.5)), g.add(inner, g.scalar(1.0)))
+
+
+def _layernorm_affine(g: Graph, x: Value, axis: int, eps: float, gamma: np.ndarray, beta: np.ndarray) -> Value:
+    y = g.layernorm(x, axis, eps)
+    return g.add(g.mul(y, g.constant_tensor(gamma)), g.constant_tensor(beta))
+
+
+def _attention(g: Graph, q: Value, k: Value, v: Value, rows_q, rows_kv, heads: int, head_dim: int, batch,
+               mask: Value = None) -> Value:
+    """q [B*Sq, h*d], k/v [B*Skv, h*d] -> [B*Sq, h*d]; scores are materialised (the IR has no attention op)."""
+    sq, skv = rows_q, rows_kv
+
+    def split(x, s):
+        x = g.view(x, shape(batch, s, heads, head_dim))
+        x = g.permute(x, [0, 2, 1, 3])
+        return g.view(x, shape(batch * heads, s, head_dim))
+
+    qh, kh, vh = split(q, sq), split(k, skv), split(v, skv)
+    scores = g.batched_mat_mul(qh, g.permute(kh, [0, 2, 1]))
+    scores = g.mul(scores, g.scalar(1.0 / math.sqrt(head_dim)))
+    if mask is not None:
+        scores = g.add(scores, mask)
+    probs = g.softmax(scores, 2)
+    ctx = g.batched_mat_mul(probs, vh)
+    ctx = g.view(ctx, shape(batch, heads, sq, head_dim))
+    ctx = g.permute(ctx, [0, 2, 1, 3])
+    return g.view(ctx, shape(batch * sq, heads * head_dim))
+
+
+def bert_encoder(layers: int = 12, hidden: int = 768, heads: int = 12, ffn: int = 3072, vocab: int = 30522,
+                 seq: int = 512, eps: float = 1e-12, seed: int = 10) -> Tuple[Graph, Inputs]:
+    """BERT-base-shaped encoder, f32, post-LayerNorm, learned positions, GELU via erf; weights N(0, 0.02),
+    gamma 1, beta 0.  Input: token ids [B, seq] (i32)."""
+    g = Graph()
+    seeds = _Seeds(seed)
+    head_dim = hidden // heads
+    ids = g.input(shape(BATCH, seq), DType.I32)
+    table = g.constant_tensor(_normal(seeds, (vocab, hidden)))
+    x = g.gather(table, 0, g.flatten(ids, 0))                         # [B*seq, hidden]
+    x = g.view(x, shape(BATCH, seq, hidden))
+    x = g.add(x, g.constant_tensor(_normal(seeds, (1, seq, hidden))))
+    ones, zeros = np.ones((1, 1, hidden), np.float32), np.zeros((1, 1, hidden), np.float32)
+    x = _layernorm_affine(g, x, 2, eps, ones, zeros)
+    rows = BATCH * seq
+    for _ in range(layers):
+        x2 = g.view(x, shape(rows, hidden))
+        q = _dense(g, seeds, x2, hidden, hidden)
+        k = _dense(g, seeds, x2, hidden, hidden)
+        v = _dense(g, seeds, x2, hidden, hidden)
+        ctx = _attention(g, q, k, v, seq, seq, heads, head_dim, BATCH)
+        att = _dense(g, seeds, ctx, hidden, hidden)
+        x = _layernorm_affine(g, g.add(g.view(att, shape(BATCH, seq, hidden)), x), 2, eps, ones, zeros)
+        x2 = g.view(x, shape(rows, hidden))
+        h = _gelu(g, _dense(g, seeds, x2, hidden, ffn))
+        y = _dense(g, seeds, h, ffn, hidden)
+        x = _layernorm_affine(g, g.add(g.view(y, shape(BATCH, seq, hidden)), x), 2, eps, ones, zeros)
+    g.output(x)
+
+    def make_inputs(batch_size: int, seed: int = 1):
+        return [_rng(seed).integers(0, vocab, (batch_size, seq)).astype(np.int32)]
+
+    return g, make_inputs
+
+
+def llama_decoder(layers: int = 32, d_model: int = 4096, heads: int = 32, ffn: int = 11008, vocab: int = 32000,
+                  seq: int = 2048, eps: float = 1e-6, rope_base: float = 10000.0, seed: int = 10) -> Tuple[Graph, Inputs]:
+    """LLaMA-shaped decoder prefill in f32 (half storage is not built): RMSNorm composed from
+    pow / mean / sqrt / div, rotary embedding from constant cos/sin tables with half-split slices,
+    additive causal mask, SwiGLU, tied-shape lm head.  Input: token ids [B, seq] (i32)."""
+    from .graph import BinaryOp, ReduceOp, SliceRange, UnaryOp
+    g = Graph()
+    seeds = _Seeds(seed)
+    hd = d_model // heads
+    ids = g.input(shape(BATCH, seq), DType.I32)
+    table = g.constant_tensor(_normal(seeds, (vocab, d_model)))
+    x = g.view(g.gather(table, 0, g.flatten(ids, 0)), shape(BATCH, seq, d_model))
+
+    inv_freq = rope_base ** (-np.arange(0, hd, 2, dtype=np.float64) / hd)
+    ang = np.arange(seq, dtype=np.float64)[:, None] * inv_freq[None, :]            # [seq, hd/2]
+    cos = g.constant_tensor(np.concatenate([np.cos(ang), np.cos(ang)], 1).astype(np.float32).reshape(1, seq, 1, hd))
+    sin = g.constant_tensor(np.concatenate([np.sin(ang), np.sin(ang)], 1).astype(np.float32).reshape(1, seq, 1, hd))
+    mask = g.constant_tensor(np.triu(np.full((seq, seq), -np.inf, np.float32), 1).reshape(1, seq, seq))
+
+    def rmsnorm(t):
+        ms = g.reduce(g.pow(t, g.scalar(2.0)), [2], ReduceOp.MEAN)
+        ms = g.view(ms, shape(BATCH, seq, 1))
+        rms = g.unary(UnaryOp.SQRT, g.add(ms, g.scalar(eps)))
+        w = g.constant_tensor(np.ones((1, 1, d_model), np.float32) + _normal(seeds, (1, 1, d_model)))
+        return g.mul(g.binary(BinaryOp.DIV, t, rms), w)
+
+    def rope(t):   # t [B*seq, d_model] -> rotated, same shape
+        t4 = g.view(t, shape(BATCH, seq, heads, hd))
+        lo = g.slice(t4, 3, SliceRange(0, hd // 2))
+        hi = g.slice(t4, 3, SliceRange(hd // 2, hd))
+        neg_hi = g.unary(UnaryOp.NEG, hi)
+        rot = g.concat([neg_hi, lo], 3)
+        out = g.add(g.mul(t4, cos), g.mul(rot, sin))
+        return g.view(out, shape(BATCH * seq, d_model))
+
+    rows = BATCH * seq
+    for _ in range(layers):
+        h = g.view(rmsnorm(x), shape(rows, d_model))
+        q = rope(_dense(g, seeds, h, d_model, d_model, bias=False))
+        k = rope(_dense(g, seeds, h, d_model, d_model, bias=False))
+        v = _dense(g, seeds, h, d_model, d_model, bias=False)
+        ctx = _attention(g, q, k, v, seq, seq, heads, hd, BATCH, mask=mask)
+        x = g.add(x, g.view(_dense(g, seeds, ctx, d_model, d_model, bias=False), shape(BATCH, seq, d_model)))
+        h = g.view(rmsnorm(x), shape(rows, d_model))
+        gate = _dense(g, seeds, h, d_model, ffn, bias=False)
+        up = _dense(g, seeds, h, d_model, ffn, bias=False)
+        act = g.mul(g.mul(gate, g.sigmoid(gate)), up)
+        x = g.add(x, g.view(_dense(g, seeds, act, ffn, d_model, bias=False), shape(BATCH, seq, d_model)))
+    logits = _dense(g, seeds, g.view(rmsnorm(x), shape(rows, d_model)), d_model, vocab, bias=False)
+    g.output(g.view(logits, shape(BATCH, seq, vocab)))
+
+    def make_inputs(batch_size: int, seed: int = 1):
+        return [_rng(seed).integers(0, vocab, (batch_size, seq)).astype(np.int32)]
+
+    return g, make_inputs
+
+
+# --------------------------------------------------------------------------------------
+# diffusion-UNet-shaped workload
+# --------------------------------------------------------------------------------------
+def unet_step(levels=(320, 640, 1280, 1280), res_blocks: int = 2, attention_levels=(0, 1, 2), heads: int = 8,
+              latent_channels: int = 4, size: int = 64, ctx_len: int = 77, ctx_dim: int = 768, groups: int = 32,
+              seed: int = 10) -> Tuple[Graph, Inputs]:
+    """One denoising step of a latent-diffusion-shaped UNet, f32.  The concrete layout (this file is
+    its definition): sinusoidal timestep embedding of dim levels[0] -> two linears with SiLU; conv-in;
+    per level `res_blocks` x [ResBlock (+ transformer block on attention levels)] then a stride-2
+    conv down (except the last level); middle ResBlock - transformer - ResBlock; up path mirrors it with
+    skip concatenation (res_blocks + 1 blocks per level) and nearest x2 upsampling + conv; GroupNorm
+    (as view + layernorm + affine), SiLU, conv-out.  Transformer block: self-attention, cross-attention
+    on the text context, GEGLU feed-forward, each with pre-LayerNorm and a residual.  Weights N(0, 0.02).
+    Inputs: latent [B, C, size, size], timestep [1], context [B, ctx_len, ctx_dim]."""
+    from .graph import SliceRange, UnaryOp
+    g = Graph()
+    seeds = _Seeds(seed)
+    ch0 = levels[0]
+    temb_dim = 4 * ch0
+
+    latent = g.input(shape(BATCH, latent_channels, size, size))
+    timestep = g.input(shape(1))
+    context = g.input(shape(BATCH, ctx_len, ctx_dim))
+
+    def silu(t):
+        return g.mul(t, g.sigmoid(t))
+
+    def conv(t, cin, cout, k, stride=1):
+        w = g.constant_tensor(_normal(seeds, (cout, cin, k, k)))
+        b = g.constant_tensor(_normal(seeds, (1, cout, 1, 1)))
+        return g.add(g.conv(t, w, stride, stride, k // 2, k // 2), b)
+
+    def group_norm(t, c, hw):
+        n = g.view(t, shape(BATCH, groups, (c // groups) * hw * hw))
+        n = g.view(g.layernorm(n, 2, 1e-5), shape(BATCH, c, hw, hw))
+        gamma = g.constant_tensor(np.ones((1, c, 1, 1), np.float32) + _normal(seeds, (1, c, 1, 1)))
+        beta = g.constant_tensor(_normal(seeds, (1, c, 1, 1)))
+        return g.add(g.mul(n, gamma), beta)
+
+    # timestep embedding
+    half = ch0 // 2
+    freqs = np.exp(-math.log(10000.0) * np.arange(half, dtype=np.float64) / half).astype(np.float32)
+    args = g.mul(g.view(timestep, shape(1, 1)), g.constant_tensor(freqs.reshape(1, half)))
+    emb = g.concat([g.unary(UnaryOp.COS, args), g.unary(UnaryOp.SIN, args)], 1)          # [1, ch0]
+    temb = _dense(g, seeds, silu(_dense(g, seeds, emb, ch0, temb_dim)), temb_dim, temb_dim)
+    temb_act = silu(temb)
+
+    def res_block(t, cin, cout, hw):
+        h = conv(silu(group_norm(t, cin, hw)), cin, cout, 3)
+        te = g.view(_dense(g, seeds, temb_act, temb_dim, cout), shape(1, cout, 1, 1))
+        h = g.add(h, te)
+        h = conv(silu(group_norm(h, cout, hw)), cout, cout, 3)
+        skip = t if cin == cout else conv(t, cin, cout, 1)
+        return g.add(h, skip)
+
+    ctx_rows = g.view(context, shape(BATCH * ctx_len, ctx_dim))
+
+    def layer_norm(t, c):
+        gamma = np.ones((1, 1, c), np.float32)
+        return _layernorm_affine(g, t, 2, 1e-5, gamma, np.zeros((1, 1, c), np.float32))
+
+    def transformer(t, c, hw):
+        tokens = hw * hw
+        hd = c // heads
+        h = conv(group_norm(t, c, hw), c, c, 1)
+        x = g.view(g.permute(h, [0, 2, 3, 1]), shape(BATCH, tokens, c))
+        # self-attention
+        n = g.view(layer_norm(x, c), shape(BATCH * tokens, c))
+        q = _dense(g, seeds, n, c, c, bias=False)
+        k = _dense(g, seeds, n, c, c, bias=False)
+        v = _dense(g, seeds, n, c, c, bias=False)
+        a = _dense(g, seeds, _attention(g, q, k, v, tokens, tokens, heads, hd, BATCH), c, c)
+        x = g.add(x, g.view(a, shape(BATCH, tokens, c)))
+        # cross-attention on the text context
+        n = g.view(layer_norm(x, c), shape(BATCH * tokens, c))
+        q = _dense(g, seeds, n, c, c, bias=False)
+        k = _dense(g, seeds, ctx_rows, ctx_dim, c, bias=False)
+        v = _dense(g, seeds, ctx_rows, ctx_dim, c, bias=False)
+        a = _dense(g, seeds, _attention(g, q, k, v, tokens, ctx_len, heads, hd, BATCH), c, c)
+        x = g.add(x, g.view(a, shape(BATCH, tokens, c)))
+        # GEGLU feed-forward
+        n = g.view(layer_norm(x, c), shape(BATCH * tokens, c))
+        proj = _dense(g, seeds, n, c, 8 * c)
+        val = g.slice(proj, 1, SliceRange(0, 4 * c))
+        gate = g.slice(proj, 1, SliceRange(4 * c, 8 * c))
+        ff = _dense(g, seeds, g.mul(val, _gelu(g, gate)), 4 * c, c)
+        x = g.add(x, g.view(ff, shape(BATCH, tokens, c)))
+        back = g.permute(g.view(x, shape(BATCH, hw, hw, c)), [0, 3, 1, 2])
+        return g.add(conv(back, c, c, 1), t)
+
+    # down path
+    cur = conv(latent, latent_channels, ch0, 3)
+    hw = size
+    skips = [(cur, ch0)]
+    c_prev = ch0
+    for li, c in enumerate(levels):
+        for _ in range(res_blocks):
+            cur = res_block(cur, c_prev, c, hw)
+            c_prev = c
+            if li in attention_levels:
+                cur = transformer(cur, c, hw)
+            skips.append((cur, c))
+        if li != len(levels) - 1:
+            cur = conv(cur, c, c, 3, stride=2)
+            hw //= 2
+            skips.append((cur, c))
+    # middle
+    cur = res_block(cur, c_prev, c_prev, hw)
+    cur = transformer(cur, c_prev, hw)
+    cur = res_block(cur, c_prev, c_prev, hw)
+    # up path
+    for li in reversed(range(len(levels))):
+        c = levels[li]
+        for _ in range(res_blocks + 1):
+            skip, cs = skips.pop()
+            cur = res_block(g.concat([cur, skip], 1), c_prev + cs, c, hw)
+            c_prev = c
+            if li in attention_levels:
+                cur = transformer(cur, c, hw)
+        if li != 0:
+            cur = g.repeat_interleave(g.repeat_interleave(cur, 2, 2), 3, 2)
+            hw *= 2
+            cur = conv(cur, c, c, 3)
+    out = conv(silu(group_norm(cur, c_prev, hw)), c_prev, latent_channels, 3)
+    g.output(out)
+
+    def make_inputs(batch_size: int, seed: int = 1):
+        r = _rng(seed)
+        return [r.standard_normal((batch_size, latent_channels, size, size)).astype(np.float32),
+                np.array([500.0], np.float32),
+                _rng(seed + 1).standard_normal((batch_size, ctx_len, ctx_dim)).astype(np.float32)]
+
+    return g, make_inputs
