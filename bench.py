@@ -35,6 +35,10 @@ sys.path.insert(0, ROOT)
 METRIC = "inferences_per_sec"
 UNIT = "inferences/s"
 BATCH = 256
+# DRAM bytes (read + written) per launch of the trunk convolution at batch 256, from one ncu capture of
+# this bench: 9.05 MB for conv+bias+relu and 17.44 MB with the residual operand (the output stays in L2,
+# 0 bytes written back); the two alternate in the trunk, so the mean is quoted.
+TRUNK_CONV_DRAM_BYTES = 13.24e6
 WORKLOAD = "resnet_tower_f32_b256 (21x8x8 planes, stem + 16 residual blocks @128ch, policy 73x8x8 softmax, value 3 softmax)"
 
 
@@ -48,67 +52,118 @@ def load_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons while the timed region runs: NVML polled every 5 ms from
+    a thread (read-only queries), or `nvidia-smi -lms` when NVML cannot be loaded.  Sampling starts before
+    the warm-up; only samples that arrive between `mark_start()` and `stop()` are summarised."""
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
-    def __init__(self, device_index: int):
+    def __init__(self, device_index: int, uuid: str = None):
         self.device_index = device_index
-        self.samples = []
+        self.uuid = uuid
+        self.samples = []          # (arrival time, sm MHz, set of reasons)
+        self.max_clock = None
         self.proc = None
         self.thread = None
+        self.running = False
+        self.t_start = None
+        self.source = None
 
     def start(self):
         try:
+            import pynvml
+            pynvml.nvmlInit()
+            handle = (pynvml.nvmlDeviceGetHandleByUUID(self.uuid.encode()) if self.uuid
+                      else pynvml.nvmlDeviceGetHandleByIndex(self.device_index))
+            self.max_clock = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+            masks = {"hw_slowdown": pynvml.nvmlClocksThrottleReasonHwSlowdown,
+                     "hw_thermal_slowdown": pynvml.nvmlClocksThrottleReasonHwThermalSlowdown,
+                     "sw_thermal_slowdown": pynvml.nvmlClocksThrottleReasonSwThermalSlowdown,
+                     "sw_power_cap": pynvml.nvmlClocksThrottleReasonSwPowerCap}
+            self.running = True
+            self.source = "nvml"
+
+            def poll():
+                while self.running:
+                    try:
+                        mhz = float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM))
+                        bits = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(handle)
+                        self.samples.append((time.perf_counter(), mhz, {n for n, m in masks.items() if bits & m}))
+                    except pynvml.NVMLError:
+                        pass
+                    time.sleep(0.005)
+
+            self.thread = threading.Thread(target=poll, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.running = False
+        try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
-                 "-i", str(self.device_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "20",
+                 "-i", self.uuid or str(self.device_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
             return
+        self.source = "nvidia-smi"
         self.thread = threading.Thread(target=self._read, daemon=True)
         self.thread.start()
 
     def _read(self):
         for line in self.proc.stdout:
             parts = [x.strip() for x in line.split(",")]
-            if len(parts) >= 6:
-                self.samples.append(parts)
-
-    def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        clocks, max_clock, reasons = [], None, set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for s in self.samples:
+            if len(parts) < 6:
+                continue
             try:
-                clocks.append(float(s[0]))
-                max_clock = float(s[1])
+                mhz = float(parts[0])
+                self.max_clock = float(parts[1])
             except ValueError:
                 continue
-            for name, val in zip(names, s[2:6]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": max_clock,
-                "reasons": sorted(reasons), "samples": len(clocks)}
+            reasons = {n for n, v in zip(self.NAMES, parts[2:6]) if v.lower().startswith("active")}
+            self.samples.append((time.perf_counter(), mhz, reasons))
+
+    def mark_start(self):
+        self.t_start = time.perf_counter()
+
+    def stop(self):
+        t_end = time.perf_counter()
+        if self.source is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no clock source available"], "samples": 0}
+        self.running = False
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        elif self.thread is not None:
+            self.thread.join(timeout=1)
+        t0 = self.t_start if self.t_start is not None else 0.0
+        window = [s for s in list(self.samples) if t0 <= s[0] <= t_end]
+        clocks = [s[1] for s in window]
+        reasons = set().union(*[s[2] for s in window]) if window else set()
+        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": self.max_clock,
+                "reasons": sorted(reasons), "samples": len(clocks), "source": self.source}
 
 
-def cpu_oracle_rate(sample_batch: int, repeats: int):
-    """inferences/s of the CPU oracle on `sample_batch` boards of the same tower."""
+def oracle_runner(sample_batch: int):
+    """Returns a function that pushes `sample_batch` boards of the same tower through the CPU oracle once."""
     from kyanite_b200.configs import resnet_tower
     from oracle.cpu_eval import cpu_eval_graph, parse_graph
     graph, make_inputs = resnet_tower()
     parsed = parse_graph(graph.to_bytes())
     inputs = make_inputs(sample_batch, 1)
-    cpu_eval_graph(parsed, sample_batch, inputs)   # warm the BLAS threads
+    return lambda: cpu_eval_graph(parsed, sample_batch, inputs)
+
+
+def cpu_oracle_rate(sample_batch: int, repeats: int):
+    """inferences/s of the CPU oracle on `sample_batch` boards of the same tower."""
+    run = oracle_runner(sample_batch)
+    run()   # warm the BLAS threads
     t0 = time.perf_counter()
     for _ in range(repeats):
-        cpu_eval_graph(parsed, sample_batch, inputs)
+        run()
     dt = time.perf_counter() - t0
     return sample_batch * repeats / dt, dt
 
@@ -117,14 +172,20 @@ def run_reference(args, rank, world):
     if rank != 0:
         return
     cores = os.cpu_count() or 1
-    sample = BATCH
-    rates = []
+    # bounded sample: boards per step chosen so that warm-up + steps take about 90 s on this host
+    probe_rate, _ = cpu_oracle_rate(32, 1)
+    budget_boards = probe_rate * 90.0
+    sample = int(max(8, min(BATCH, budget_boards // max(1, args.steps + args.warmup))))
+    sample -= sample % 8
+    run = oracle_runner(sample)
     for _ in range(args.warmup):
-        cpu_oracle_rate(sample, 1)
+        run()
+    rates = []
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        r, _ = cpu_oracle_rate(sample, 1)
-        rates.append(r)
+        t1 = time.perf_counter()
+        run()
+        rates.append(sample / (time.perf_counter() - t1))
     dt = time.perf_counter() - t0
     value = statistics.mean(rates)
     line = {
@@ -143,7 +204,7 @@ def run_reference(args, rank, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=400)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--math", default="tf32", choices=["tf32", "f32"])
@@ -186,17 +247,19 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(local_rank, "GPU-" + str(torch.cuda.get_device_properties(local_rank).uuid))
+    sampler.start()
+
     # ---- warm-up (also captures the CUDA graph)
     for _ in range(args.warmup):
         ex.evaluate_staged()
     ex.synchronize()
 
-    sampler = ClockSampler(local_rank)
     launches = 0
 
     # ---- device-resident: K timed iterations of run_async, L2 flushed in between
     barrier()
-    sampler.start()
+    sampler.mark_start()
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     with torch.cuda.stream(stream):
@@ -256,7 +319,7 @@ def main():
             achieved = flop / (us * 1e-6) / 1e12
             kind = conv_us[0][2]
             roofline = {"bound": "tensor", "kernel": "trunk conv3x3 128->128 (" + kind + ")", "achieved": achieved,
-                        "peak": tensor_peak, "unit": "TFLOP/s", "frac": achieved / tensor_peak, "traffic": None,
+                        "peak": tensor_peak, "unit": "TFLOP/s", "frac": achieved / tensor_peak, "traffic": TRUNK_CONV_DRAM_BYTES,
                         "peak_source": f"{peaks['source']} bf16 burst / 2 (tf32)", "us_per_launch": us}
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
