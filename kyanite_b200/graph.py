@@ -24,7 +24,7 @@ import enum
 import math
 import struct
 from dataclasses import dataclass
-from typing import Iterable, List, Optional, Sequence, Tuple, Union
+from typing import Dict, Iterable, List, Optional, Sequence, Tuple, Union
 
 import numpy as np
 
@@ -425,6 +425,64 @@ class Graph:
                 return None
             return _scalar_binary(info.binary_op, l, r)
         return None
+
+    def as_const(self, v: Value) -> Optional[np.ndarray]:
+        """The value as a numpy tensor if it depends on constants only (graph.rs:434-474), else None.
+        Covers the data-movement ops and elementwise arithmetic, which is what shape computations and
+        the model loaders need; contractions, normalisations and reductions of constants return None.
+        Shapes with a batch factor are not constant."""
+        memo: Dict[int, Optional[np.ndarray]] = {}
+        order = [v.index]
+        seen = {v.index}
+        i = 0
+        while i < len(order):       # operands of the cone, iteratively (no recursion limit)
+            for j in self.values[order[i]].inputs:
+                if j not in seen:
+                    seen.add(j)
+                    order.append(j)
+            i += 1
+        for idx in sorted(order):   # operands always precede their users
+            info = self.values[idx]
+            ops = [memo[j] for j in info.inputs]
+            memo[idx] = None
+            if any(o is None for o in ops) or not all(d.is_fixed for d in info.shape):
+                continue
+            out_shape = tuple(d.factor for d in info.shape)
+            k = info.kind
+            if k == OpKind.CONSTANT:
+                res = info.tensor
+            elif k == OpKind.VIEW:
+                res = ops[0].reshape(out_shape)
+            elif k == OpKind.BROADCAST:
+                res = np.broadcast_to(ops[0], out_shape)
+            elif k == OpKind.PERMUTE:
+                res = np.transpose(ops[0], info.permutation)
+            elif k == OpKind.SLICE:
+                r = info.range
+                index = [slice(None)] * ops[0].ndim
+                index[info.axis] = slice(r.start, r.end, r.step)
+                res = ops[0][tuple(index)]
+            elif k == OpKind.FLIP:
+                res = np.flip(ops[0], info.axis)
+            elif k == OpKind.GATHER:
+                indices = ops[1].astype(np.int64)
+                size = ops[0].shape[info.axis]
+                if indices.size and (indices.min() < 0 or indices.max() >= size):
+                    continue
+                res = np.take(ops[0], indices.reshape(-1), axis=info.axis)
+            elif k == OpKind.CONCAT:
+                res = np.concatenate(ops, axis=info.axis) if ops else np.zeros(out_shape, info.dtype.np)
+            elif k == OpKind.UNARY:
+                res = np.array([_scalar_unary(info.unary_op, info.cast_to, x) for x in ops[0].reshape(-1)],
+                               dtype=info.dtype.np)
+            elif k == OpKind.BINARY:
+                l, r = np.broadcast_arrays(ops[0], ops[1])
+                res = np.array([_scalar_binary(info.binary_op, a, b) for a, b in zip(l.reshape(-1), r.reshape(-1))],
+                               dtype=info.dtype.np)
+            else:
+                continue
+            memo[idx] = np.array(res, dtype=info.dtype.np, order="C", copy=True).reshape(out_shape)
+        return memo[v.index]
 
     def is_const_filled_with(self, v: Value, expected) -> bool:
         actual = self.as_single_const(v)
