@@ -59,8 +59,12 @@ typedef struct kn_options {
     uint32_t struct_size;   /* = sizeof(kn_options) */
     int32_t math_mode;      /* kn_math_mode */
     int32_t use_cuda_graph; /* 1: capture the step list once and replay it (default), 0: launch steps */
-    int32_t reserved;
+    int32_t flags;          /* bit set of KN_FLAG_*, 0 by default */
 } kn_options;
+
+/* keep every convolution its own step: do not merge runs of stride-1 3x3 convolutions into the
+   shared-memory-resident chain kernel (for A/B comparison and tests) */
+#define KN_FLAG_NO_CONV_CHAIN 1
 
 #define KN_MAX_RANK 8
 

@@ -17,10 +17,11 @@ STATUS_NAMES = {0: "KN_OK", 1: "KN_ERR_INVALID_ARG", 2: "KN_ERR_BAD_GRAPH", 3: "
                 5: "KN_ERR_SHAPE", 6: "KN_ERR_NO_DEVICE", 7: "KN_ERR_INTERNAL"}
 KN_MATH_TF32 = 0
 KN_MATH_F32 = 1
+KN_FLAG_NO_CONV_CHAIN = 1
 
 
 class KnOptions(Structure):
-    _fields_ = [("struct_size", c_uint32), ("math_mode", c_int32), ("use_cuda_graph", c_int32), ("reserved", c_int32)]
+    _fields_ = [("struct_size", c_uint32), ("math_mode", c_int32), ("use_cuda_graph", c_int32), ("flags", c_int32)]
 
 
 class KnTensorInfo(Structure):

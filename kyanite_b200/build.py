@@ -29,6 +29,7 @@ SOURCES = [
     "kernels/gather.cu",
     "kernels/contract_simt.cu",
     "kernels/contract_tc.cu",
+    "kernels/conv_chain.cu",
 ]
 
 NVCC_FLAGS = [

@@ -127,6 +127,12 @@ struct Executor {
                     s.conv.add1 = ptr.size() > 3 ? (const float*)ptr[3] : nullptr;
                     s.conv.add2 = ptr.size() > 4 ? (const float*)ptr[4] : nullptr;
                     break;
+                case StepKind::ConvChain:
+                    s.chain.in = (const float*)ptr[0];
+                    s.chain.out = (float*)ptr[1];
+                    s.chain.tiles = (const float*)ptr[2];
+                    s.chain.bias = (const float*)ptr[3];
+                    break;
                 default: fail(KN_ERR_INTERNAL, "unknown step kind");
             }
             if (s.tensor_core) tc_prepare_step(s, status_dev);
@@ -144,6 +150,7 @@ struct Executor {
             case StepKind::Gather: err = launch_gather(s.gather, stream); break;
             case StepKind::Gemm: err = s.tensor_core ? tc_launch_step(s, stream) : launch_gemm_simt(s.gemm, stream); break;
             case StepKind::Conv: err = s.tensor_core ? tc_launch_step(s, stream) : launch_conv_simt(s.conv, stream); break;
+            case StepKind::ConvChain: err = tc_launch_step(s, stream); break;
             default: fail(KN_ERR_INTERNAL, "unknown step kind");
         }
         if (err != 0)
@@ -355,7 +362,7 @@ int kn_options_default(kn_options* opts) {
     opts->struct_size = sizeof(kn_options);
     opts->math_mode = KN_MATH_TF32;
     opts->use_cuda_graph = 1;
-    opts->reserved = 0;
+    opts->flags = 0;
     return KN_OK;
 }
 
@@ -569,6 +576,11 @@ int kn_executor_time_step(kn_executor* exec, int step, int launches, float* micr
             float ms = 0;
             KN_CUDA(cudaEventElapsedTime(&ms, a, b));
             *microseconds = ms * 1000.f / (float)launches;
+            if (getenv("KN_CHAIN_TRACE")) {
+                uint32_t words[64];
+                cudaMemcpy(words, e.status_dev, 256, cudaMemcpyDeviceToHost);
+                for (int i = 16; i < 32; i++) fprintf(stderr, "%u%c", words[i] - words[16], (i % 4 == 3) ? '\n' : ' ');
+            }
         } catch (...) {
             cudaEventDestroy(a);
             cudaEventDestroy(b);

@@ -121,6 +121,26 @@ struct ConvParams {
     int32_t round_tf32;
 };
 
+// ---- a run of stride-1 3x3 same-padding convolutions executed by ONE kernel, activations resident
+// in shared memory: layer l computes  act_l(conv(x_l, filter_l) + bias_l [+ held])  where x_0 = `in`,
+// x_{l+1} = the layer's result and `held` is `in` or the last result flagged to be held (the skip
+// connection of a residual block).  Only the last layer's result reaches global memory.
+constexpr int kMaxChainLayers = 64;
+constexpr int kChainFlagRelu = 1, kChainFlagAddHeld = 2, kChainFlagHold = 4;
+struct ConvChainParams {
+    const float* in;      // [n, c_in, h, w], any strides
+    float* out;           // [n, k, h, w], any strides
+    const float* tiles;   // filter tiles [tile][128 output channels][32 input channels] in the 128-byte-swizzled
+                          // order of shared memory, TF32, layers back to back;
+                          // within a layer tile = tap * c_blocks + channel block, tap = r * 3 + s
+    const float* bias;    // [layer][128]
+    int32_t n, c_in, k, h, w;
+    int32_t n_layers;
+    int64_t s_in[4], s_out[4];
+    uint8_t flags[kMaxChainLayers];
+    uint8_t c_blocks[kMaxChainLayers];   // 32-channel blocks of the layer's input
+};
+
 // All launchers enqueue on `stream` and return the cudaError_t of the launch as int.
 int launch_scalar(const ScalarParams& p, cudaStream_t stream);
 int launch_reduce(const ReduceParams& p, cudaStream_t stream);

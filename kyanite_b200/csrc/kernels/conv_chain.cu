@@ -1,0 +1,505 @@
+// A run of 3x3 stride-1 same-padding convolutions (a residual tower) as ONE kernel for sm_100a.
+//
+// A 3x3 convolution of an image reads that image only, so a CTA that owns a few whole images can run
+// every layer of the run back to back without ever leaving its SM: the activations live in shared
+// memory (as the B operand of the next layer's MMAs), the skip connection of a residual block lives in
+// tensor memory next to the accumulator, and per layer only the filter streams in from L2 through a
+// ring of 16 KB tiles.  Compared with one launch per layer this removes, per layer, the launch, the
+// pipeline fill, the activation round trip through L2 and the output store.
+//
+// Accumulator orientation: D[output channel = TMEM lane][padded position = column].
+//   A operand  filter tile [128 output channels x 32 input channels], K-major, 128-byte swizzle, loaded
+//              by TMA from a tile array the planner lays out in consumption order
+//   B operand  the activation buffer: per 32-channel block, one 128-byte row per padded position, same
+//              swizzle.  The images are stored as one tall zero-padded image (ChainGeometry, tc.h), so
+//              filter tap (r, s) is the same operand started `(r-1) * wp + (s-1)` rows further on.  Such a
+//              start is 128-byte but not 1024-byte aligned.  The tensor core resolves the swizzle from the
+//              absolute shared-memory address (16-byte chunk index XOR address bits 7..9), and the buffer's
+//              pattern is anchored at a 1024-byte boundary, so the descriptor's base-offset field stays 0
+//              (measured: a non-zero base offset permutes the channels).
+//
+// Warp roles (320 threads): warp 0 lane 0 streams filter tiles; warp 1 lane 0 issues the MMAs of a layer
+// once its input is complete; warps 2..9 are the epilogue (two warps per TMEM lane quarter, each taking
+// alternate 32-column blocks): accumulator + bias (+ held skip tensor) -> ReLU -> written back as the
+// next layer's operand (rounded to TF32, zeros at padding positions) and, if a later layer adds it,
+// into the held-tensor columns of TMEM in full f32; the last layer's result goes to global memory.
+//
+// Every mbarrier wait is bounded; on expiry the executor's status word is raised, all roles leave, TMEM is
+// freed and the kernel returns.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdlib>
+#include <cstring>
+#include <memory>
+#include <mutex>
+
+#include "../tc.h"
+#include "tc_host.h"
+#include "tc_ptx.cuh"
+
+namespace kn {
+
+namespace {
+
+using namespace tcp;
+
+constexpr int kChainThreads = 320;
+constexpr int kEpilogueThreads = 256;
+constexpr int kTileBytes = 128 * 128;   // one filter tile: 128 rows of 128 bytes
+
+struct ChainKernelParams {
+    const float* in;
+    float* out;
+    const float* bias;
+    const float* tiles;
+    int64_t s_in[4], s_out[4];
+    int32_t n_img, c_in, k, h, w;
+    int32_t n_layers, per_cta, wp, q_first, n_mma, rows_alloc, slots, tmem_cols, c_blocks_max;
+    int32_t total_tiles;
+    int32_t dbg;
+    int32_t group;   // filter tiles per request and per ring slot
+    uint8_t flags[kMaxChainLayers];
+    uint8_t c_blocks[kMaxChainLayers];
+    uint32_t* status;
+};
+
+__device__ __forceinline__ void tmem_store_32(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+          "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]),
+          "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]),
+          "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_store_16(uint32_t taddr, const uint32_t (&v)[16]) {   // caller waits (tcgen05.wait::st)
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+          "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_load_16_nowait(uint32_t taddr, uint32_t (&v)[16]) {   // caller waits (tcgen05.wait::ld)
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr)
+        : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ uint32_t round_tf32_bits(float v) {
+    uint32_t u;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v));
+    return u;
+}
+
+__global__ void __launch_bounds__(kChainThreads, 1)
+conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_constant__ ChainKernelParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t block_bytes = (uint32_t)p.rows_alloc * 128u;                 // one 32-channel block of activations
+    const uint32_t act_bytes = (uint32_t)p.c_blocks_max * block_bytes;
+    const uint32_t ring_base = base + act_bytes;
+    const uint32_t slot_bytes = (uint32_t)p.group * kTileBytes;
+    const uint32_t bar_base = ring_base + (uint32_t)p.slots * slot_bytes;
+    const uint32_t full_bar = bar_base, empty_bar = bar_base + 8u * p.slots;
+    const uint32_t accum_bar = bar_base + 16u * p.slots, act_bar = accum_bar + 8u;
+    const uint32_t slot_addr = act_bar + 8u;
+    volatile uint32_t* tmem_slot = (volatile uint32_t*)(gen_base + (slot_addr - base));
+    volatile int* abandon = (volatile int*)(gen_base + (slot_addr + 4u - base));
+    uint32_t* colinfo = (uint32_t*)(gen_base + (slot_addr + 8u - base));         // 256 entries
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int blocks32 = (p.n_mma + 31) >> 5;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.slots; s++) {
+            mbar_init(full_bar + 8u * s, 1);
+            mbar_init(empty_bar + 8u * s, 1);
+        }
+        mbar_init(accum_bar, 1);
+        mbar_init(act_bar, kEpilogueThreads);
+        *abandon = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // the activation buffer starts as zeros: padding positions and guard rows are never written with
+    // anything else
+    {
+        uint4* z = (uint4*)gen_base;
+        const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+        for (uint32_t i = threadIdx.x; i < act_bytes / 16u; i += kChainThreads) z[i] = zero;
+    }
+    // column -> pixel table: bit 31 real pixel, bits 16..23 image within the CTA, 8..15 y, 0..7 x
+    if (threadIdx.x < 256) {
+        const int n = threadIdx.x;
+        uint32_t info = 0;
+        if (n < p.n_mma) {
+            const int q = n + p.q_first;
+            const int row = q / p.wp, col = q - row * p.wp;
+            const int img = row / (p.h + 1), ry = row - img * (p.h + 1);
+            if (col != 0 && ry != 0 && img < p.per_cta && (int64_t)blockIdx.x * p.per_cta + img < p.n_img)
+                info = 0x80000000u | ((uint32_t)img << 16) | ((uint32_t)(ry - 1) << 8) | (uint32_t)(col - 1);
+        }
+        colinfo[n] = info;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_addr), "r"((uint32_t)p.tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_acc = *tmem_slot;
+    const uint32_t tmem_held = tmem_acc + (uint32_t)(blocks32 * 32);
+
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- filter producer: tiles are consumed in the order they are stored; the filter
+        // is a constant of the plan, so nothing here waits for the previous kernel
+        // Within a layer the tiles may be consumed in any order (they all accumulate into the same
+        // tile), so every CTA starts at a different one: at any moment the SMs then pull different
+        // lines from L2 instead of all hammering the slice that holds the current tile.
+        // (ring position and indices are advanced by hand: integer division by a run-time value costs
+        // tens of cycles, and this loop runs once per request)
+        int layer_base = 0, slot = 0, round = 0;
+        bool ok = true;
+        for (int l = 0; l < p.n_layers && ok; l++) {
+            const int n = 9 * p.c_blocks[l];
+            const int g = n % p.group == 0 ? p.group : 1;      // tiles per request
+            const int groups = n / g;
+            int idx = (int)((blockIdx.x * 5u) % (uint32_t)groups);
+            for (int i = 0; i < groups; i++) {
+                if ((p.dbg & 16) && round > 0) continue;
+                if (round > 0) {
+                    if (!mbar_wait(empty_bar + 8u * slot, (uint32_t)((round & 1) ^ 1), abandon, p.status, 11)) { ok = false; break; }
+                }
+                const uint32_t bar = full_bar + 8u * slot;
+                mbar_expect_tx(bar, (uint32_t)g * kTileBytes);
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                             ::"r"(ring_base + (uint32_t)slot * slot_bytes), "l"(p.tiles + (size_t)(layer_base + idx * g) * (kTileBytes / 4)),
+                               "r"((uint32_t)g * kTileBytes), "r"(bar)
+                             : "memory");
+                if (++idx == groups) idx = 0;
+                if (++slot == p.slots) { slot = 0; round++; }
+            }
+            layer_base += n;
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---------------- MMA issuer
+        const int n_dbg = (p.dbg >> 8) ? (p.dbg >> 8) : p.n_mma;
+        const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n_dbg >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+        int slot = 0, round = 0;
+        bool ok = true;
+        for (int l = 0; l < p.n_layers && ok; l++) {
+            // the layer's input is complete in shared memory and the accumulator has been read out
+            ok = mbar_wait(act_bar, (uint32_t)(l & 1), abandon, p.status, 12);
+            if (!ok) break;
+            tc_fence_after();
+            if ((p.dbg & 128) && blockIdx.x == 0 && l >= 2 && l < 6) p.status[16 + (l - 2) * 4 + 0] = (uint32_t)clock64();
+            const int cbl = p.c_blocks[l];
+            uint32_t accumulate = 0;
+            const int n = 9 * cbl;
+            const int g = n % p.group == 0 ? p.group : 1;
+            const int groups = n / g;
+            // the producer's order: start at group (blockIdx.x * 5) % groups, wrap around
+            int tile = (int)((blockIdx.x * 5u) % (uint32_t)groups) * g;
+            int tap = tile / cbl, cb = tile - tap * cbl;
+            for (int i = 0; i < groups && ok; i++) {
+                if (!((p.dbg & 16) && round > 0)) ok = mbar_wait(full_bar + 8u * slot, (uint32_t)(round & 1), abandon, p.status, 13);
+                if (!ok) break;
+                tc_fence_after();
+                for (int u = 0; u < g; u++) {
+                    const int r = tap >= 6 ? 2 : (tap >= 3 ? 1 : 0), s = tap - 3 * r;
+                    const uint32_t row0 = (uint32_t)(p.q_first + (r - 1) * p.wp + (s - 1));
+                    const uint64_t da = smem_desc_sw128(ring_base + (uint32_t)slot * slot_bytes + (uint32_t)u * kTileBytes);
+                    const uint64_t db = smem_desc_sw128(base + (uint32_t)cb * block_bytes + row0 * 128u);
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        if (!(p.dbg & 1)) mma_tf32(tmem_acc, da + 2u * j, db + 2u * j, idesc, accumulate);
+                        accumulate = 1;
+                    }
+                    if (++cb == cbl) {
+                        cb = 0;
+                        if (++tap == 9) tap = 0;
+                    }
+                }
+                mma_commit(empty_bar + 8u * slot);
+                if (++slot == p.slots) { slot = 0; round++; }
+            }
+            if (ok) mma_commit(accum_bar);
+            if ((p.dbg & 128) && blockIdx.x == 0 && l >= 2 && l < 6) p.status[16 + (l - 2) * 4 + 1] = (uint32_t)clock64();
+        }
+    } else if (warp >= 2) {
+        // ---------------- epilogue: thread <-> accumulator lane <-> channel; the two warps of a lane
+        // quarter take alternate 16-column chunks
+        const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;
+        const int ch = quarter * 32 + lane;
+        const uint32_t lane_bits = (uint32_t)(quarter * 32) << 16;
+        const int64_t img0 = (int64_t)blockIdx.x * p.per_cta;
+        const bool has_block = (ch >> 5) < p.c_blocks_max;     // narrower layers: no operand rows for these channels
+        const uint32_t chunk = (uint32_t)(ch >> 2) & 7u;
+        // this channel's 4 bytes inside a 128-byte row of its 32-channel block, before the swizzle
+        uint8_t* const my_rows = gen_base + (uint32_t)(ch >> 5) * block_bytes + (uint32_t)(ch & 3) * 4u;
+        const int chunks16 = (p.n_mma + 15) >> 4;
+        constexpr int kMaxMine = 8;                             // 256 columns / 16 / 2 warps
+        // which of my columns are real pixels (everything else is written as zero padding)
+        uint32_t real[kMaxMine];
+#pragma unroll
+        for (int k = 0; k < kMaxMine; k++) {
+            const int c = half + 2 * k;
+            uint32_t m = 0;
+            if (c < chunks16)
+                for (int j = 0; j < 16; j++) m |= (colinfo[c * 16 + j] >> 31) << j;
+            real[k] = m;
+        }
+        auto store_operand = [&](uint32_t q, float v) {
+            *(uint32_t*)(my_rows + q * 128u + ((chunk ^ (q & 7u)) << 4)) = round_tf32_bits(v);
+        };
+
+        // layer 0's input: from global memory into the operand layout and the held-tensor columns
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        for (int c = half; c < chunks16; c += 2) {
+            uint32_t v[16];
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+                const uint32_t info = colinfo[c * 16 + j];
+                float x = 0.f;
+                if ((info >> 31) && ch < p.c_in)
+                    x = p.in[(img0 + ((info >> 16) & 0xFF)) * p.s_in[0] + (int64_t)ch * p.s_in[1] + (int64_t)((info >> 8) & 0xFF) * p.s_in[2] +
+                             (int64_t)(info & 0xFF) * p.s_in[3]];
+                v[j] = __float_as_uint(x);
+                if (has_block) store_operand((uint32_t)(c * 16 + j + p.q_first), x);
+            }
+            tmem_store_16(tmem_held + lane_bits + (uint32_t)(c * 16), v);
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> tensor-core reads
+        tc_fence_before();
+        mbar_arrive(act_bar);
+
+        for (int l = 0; l < p.n_layers; l++) {
+            const uint32_t flags = p.flags[l];
+            const bool last = l == p.n_layers - 1;
+            const bool add_held = (flags & kChainFlagAddHeld) != 0, relu = (flags & kChainFlagRelu) != 0;
+            const bool hold = (flags & kChainFlagHold) != 0 && !last;
+            const float bias = ch < p.k ? p.bias[l * 128 + ch] : 0.f;
+            // One lane per warp polls: 256 threads spinning on a shared-memory barrier for the whole
+            // mainloop would compete with the copy engine and the tensor core for shared memory.  The
+            // outcome is warp-uniform (the tensor-memory accesses below need the whole warp); every lane
+            // then observes the completed phase itself.
+            {
+                uint32_t ok = 1;
+                if (lane == 0) {
+                    const long long start = clock64();
+                    while (!mbar_try_wait(accum_bar, (uint32_t)(l & 1))) {
+                        if (*abandon) { ok = 0; break; }
+                        if (clock64() - start > kWaitCycles) {
+                            *abandon = 1;
+                            atomicMax(p.status, 14u);
+                            ok = 0;
+                            break;
+                        }
+                    }
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+                while (!mbar_try_wait(accum_bar, (uint32_t)(l & 1))) {}
+            }
+            tc_fence_after();
+            if ((p.dbg & 128) && blockIdx.x == 0 && threadIdx.x == 64 && l >= 2 && l < 6) p.status[16 + (l - 2) * 4 + 2] = (uint32_t)clock64();
+            if (!(p.dbg & 2)) {
+#pragma unroll
+                for (int k = 0; k < kMaxMine; k++) {
+                    const int c = half + 2 * k;
+                    if (c >= chunks16) break;
+                    uint32_t v[16], hv[16];
+                    tmem_load_16_nowait(tmem_acc + lane_bits + (uint32_t)(c * 16), v);
+                    if (add_held) tmem_load_16_nowait(tmem_held + lane_bits + (uint32_t)(c * 16), hv);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    const uint32_t q0 = (uint32_t)(c * 16 + p.q_first);
+                    const uint32_t mask = (ch < p.k) ? real[k] : 0u;
+#pragma unroll
+                    for (int j = 0; j < 16; j++) {
+                        float x = __uint_as_float(v[j]) + bias;
+                        if (add_held) x += __uint_as_float(hv[j]);
+                        if (relu) x = fmaxf(x, 0.f);
+                        if (!((mask >> j) & 1u)) x = 0.f;
+                        v[j] = __float_as_uint(x);
+                        if (!last && has_block) store_operand(q0 + (uint32_t)j, x);
+                    }
+                    if (hold) tmem_store_16(tmem_held + lane_bits + (uint32_t)(c * 16), v);
+                    if (last) {
+#pragma unroll
+                        for (int j = 0; j < 16; j++) {
+                            if ((mask >> j) & 1u) {
+                                const uint32_t info = colinfo[c * 16 + j];
+                                p.out[(img0 + ((info >> 16) & 0xFF)) * p.s_out[0] + (int64_t)ch * p.s_out[1] +
+                                      (int64_t)((info >> 8) & 0xFF) * p.s_out[2] + (int64_t)(info & 0xFF) * p.s_out[3]] = __uint_as_float(v[j]);
+                            }
+                        }
+                    }
+                }
+                if (hold) asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            }
+            if (!last) {
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                tc_fence_before();
+                mbar_arrive(act_bar);
+            }
+            if ((p.dbg & 128) && blockIdx.x == 0 && threadIdx.x == 64 && l >= 2 && l < 6) p.status[16 + (l - 2) * 4 + 3] = (uint32_t)clock64();
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)p.tmem_cols) : "memory");
+    }
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------- host side
+static int round_up_int(int x, int to) { return (x + to - 1) / to * to; }
+
+bool tc_chain_geometry(int h, int w, int64_t n_img, int c_blocks, ChainGeometry* out) {
+    if (h < 1 || w < 1 || h > 254 || w > 254 || n_img < 1 || c_blocks < 1 || c_blocks > 4) return false;
+    const int wp = w + 1;
+    ChainGeometry best{};
+    double best_cost = 1e300;
+    for (int per = 1; per <= 255; per++) {
+        ChainGeometry g{};
+        g.per_cta = per;
+        g.wp = wp;
+        g.q_first = wp + 1;
+        const int q_last = (per * (h + 1) - 1) * wp + w;
+        g.n_mma = round_up_int(q_last - g.q_first + 1, 16);
+        if (g.n_mma > 256) break;
+        const int cols = round_up_int(g.n_mma, 32);
+        g.rows_alloc = round_up_int(g.q_first + cols + wp + 2, 8);
+        const int act_bytes = c_blocks * g.rows_alloc * 128;
+        const int fixed = 1024 /* alignment */ + 16 * 8 + 32 + 1024 /* column table */;
+        g.slots = std::min(8, (227 * 1024 - fixed - act_bytes) / kTileBytes);
+        if (g.slots < 3) break;
+        g.smem_bytes = fixed + act_bytes + g.slots * kTileBytes;
+        // per layer: 36 tiles x 4 MMAs (an MMA costs ~70 cycles up to N = 128, then grows with N), plus
+        // the epilogue over the columns; CTAs run in waves of one per SM
+        const double mma = std::max(70.0, 0.53 * g.n_mma + 2.0);
+        const double per_layer = 144.0 * mma + 12.0 * cols;
+        const int64_t ctas = (n_img + per - 1) / per;
+        const double cost = (double)((ctas + 147) / 148) * per_layer;
+        if (cost < best_cost) {
+            best_cost = cost;
+            best = g;
+        }
+    }
+    if (best.per_cta == 0) return false;
+    if (out) *out = best;
+    return true;
+}
+
+struct ChainLaunch {
+    CUtensorMap map_tiles;
+    ChainKernelParams p;
+    dim3 grid;
+    int smem_bytes;
+};
+
+std::shared_ptr<void> chain_prepare(const ConvChainParams& c, uint32_t* status_word) {
+    auto l = std::make_shared<ChainLaunch>();
+    ChainKernelParams& p = l->p;
+    memset(&p, 0, sizeof(p));
+    int c_blocks_max = 1;
+    p.total_tiles = 0;
+    for (int i = 0; i < c.n_layers; i++) {
+        c_blocks_max = std::max<int>(c_blocks_max, c.c_blocks[i]);
+        p.total_tiles += 9 * c.c_blocks[i];
+        p.flags[i] = c.flags[i];
+        p.c_blocks[i] = c.c_blocks[i];
+    }
+    c_blocks_max = std::max(c_blocks_max, (c.k + 31) / 32);
+    ChainGeometry g;
+    KN_CHECK(tc_chain_geometry(c.h, c.w, c.n, c_blocks_max, &g), KN_ERR_INTERNAL, "convolution chain does not fit");
+    p.in = c.in;
+    p.out = c.out;
+    p.bias = c.bias;
+    p.tiles = c.tiles;
+    for (int i = 0; i < 4; i++) {
+        p.s_in[i] = c.s_in[i];
+        p.s_out[i] = c.s_out[i];
+    }
+    p.n_img = c.n;
+    p.c_in = c.c_in;
+    p.k = c.k;
+    p.h = c.h;
+    p.w = c.w;
+    p.n_layers = c.n_layers;
+    p.per_cta = g.per_cta;
+    p.wp = g.wp;
+    p.q_first = g.q_first;
+    p.n_mma = g.n_mma;
+    p.rows_alloc = g.rows_alloc;
+    p.slots = g.slots;
+    p.c_blocks_max = c_blocks_max;
+    int cols = 2 * round_up_int(g.n_mma, 32), tmem = 32;
+    while (tmem < cols) tmem <<= 1;
+    p.tmem_cols = tmem;
+    p.status = status_word;
+    p.dbg = getenv("KN_CHAIN_DBG") ? atoi(getenv("KN_CHAIN_DBG")) : 0;
+    p.group = getenv("KN_CHAIN_G") ? atoi(getenv("KN_CHAIN_G")) : c_blocks_max;
+    p.slots = g.slots / p.group;
+    int64_t dims[3] = {32, 128, p.total_tiles}, strides[3] = {1, 32, 128 * 32};
+    int box[3] = {32, 128, 1};
+    l->map_tiles = tc_make_map(c.tiles, 3, dims, strides, box, true);
+    l->grid = dim3((unsigned)((c.n + g.per_cta - 1) / g.per_cta), 1, 1);
+    l->smem_bytes = g.smem_bytes;
+    return l;
+}
+
+int chain_launch(const void* launch, cudaStream_t stream) {
+    const ChainLaunch& l = *(const ChainLaunch*)launch;
+    static std::mutex mu;
+    static bool done[64] = {false};
+    int device = 0;
+    cudaGetDevice(&device);
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (device >= 0 && device < 64 && !done[device]) {
+            cudaError_t e = cudaFuncSetAttribute(conv_chain_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            if (e != cudaSuccess) return (int)e;
+            done[device] = true;
+        }
+    }
+    if (l.grid.x == 0) return 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = l.grid;
+    cfg.blockDim = dim3(kChainThreads);
+    cfg.dynamicSmemBytes = (size_t)l.smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return (int)cudaLaunchKernelEx(&cfg, conv_chain_kernel, l.map_tiles, l.p);
+}
+
+}  // namespace kn

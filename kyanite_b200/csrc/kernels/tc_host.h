@@ -1,0 +1,22 @@
+// Host-side helpers shared by the tensor-core kernel files.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <memory>
+
+#include "../kernels.h"
+
+namespace kn {
+
+// Tiled tensor map over f32 data.  dims / strides innermost first, strides in elements (dims[0] has
+// stride 1).  `operand`: 128-byte swizzle and round-to-TF32 on load (an MMA operand tile); otherwise a
+// plain f32 tile without swizzle (an epilogue tile).
+CUtensorMap tc_make_map(const void* base, int rank, const int64_t* dims, const int64_t* strides, const int* box, bool operand);
+
+// Convolution chain (kernels/conv_chain.cu): launch data built once the device pointers are known.
+std::shared_ptr<void> chain_prepare(const ConvChainParams& c, uint32_t* status_word);
+int chain_launch(const void* launch, cudaStream_t stream);
+
+}  // namespace kn

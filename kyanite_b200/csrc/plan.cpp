@@ -9,12 +9,13 @@
 #include <sstream>
 
 #include "scalar_ops.h"
+#include "tc.h"
 
 namespace kn {
 
 const char* step_kind_name(StepKind k) {
-    static const char* names[] = {"Scalar", "Reduce", "Softmax", "Layernorm", "Gather", "Gemm", "Conv"};
-    return (int)k < 7 ? names[(int)k] : "?";
+    static const char* names[] = {"Scalar", "Reduce", "Softmax", "Layernorm", "Gather", "Gemm", "Conv", "ConvChain"};
+    return (int)k < 8 ? names[(int)k] : "?";
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -161,6 +162,8 @@ class Planner {
             plan_.output_shapes.push_back(t.ss.shape);
         }
         for (auto& t : plan_.inputs) plan_.input_shapes.push_back(t.ss.shape);
+        fuse_conv_chains();
+        drop_unused_constants();
         assign_memory();
     }
 
@@ -923,6 +926,219 @@ class Planner {
         s.desc = "reduce out=" + std::to_string(p.n_out) + " red=" + std::to_string(p.n_red);
         if (out.ss.size() != 0) push_step(std::move(s));
         return out;
+    }
+
+    // ---------------------------------------------------------------- convolution chains
+    // A run of consecutive tensor-core steps conv3x3(stride 1, same padding) -> [+bias] [+skip] [relu],
+    // each reading the previous one's result and none of whose intermediate results is needed
+    // elsewhere, becomes ONE ConvChain step: the activations of a group of whole images stay in the
+    // shared memory of one SM from the first layer to the last (a 3x3 convolution of an image depends on
+    // that image only), so per layer only the filter crosses from L2.  The skip operand of a residual
+    // block must be the tensor the kernel currently holds: the chain's input, or the latest result
+    // that a later layer of the chain adds.
+    struct ChainLayer {
+        size_t step;
+        int bias_operand = -1, res_operand = -1;
+    };
+
+    bool chain_candidate(const Step& s, ChainLayer& l) const {
+        if (s.kind != StepKind::Conv || !s.tensor_core) return false;
+        const ConvParams& c = s.conv;
+        if (c.r != 3 || c.s != 3 || c.pad_y != 1 || c.pad_x != 1 || c.stride_y != 1 || c.stride_x != 1) return false;
+        if (c.k > 128 || c.c > 128 || c.oh != c.h || c.ow != c.w) return false;
+        if (!tc_chain_geometry(c.h, c.w, c.n, 4, nullptr)) return false;
+        // the filter must be a planner-made tap-major constant [3][3][K][C_pad] whose bytes are still on the host
+        const PlanTensor& w = s.operands[1];
+        const BufferInfo& wb = plan_.buffers[w.buf];
+        const int64_t c_pad = (c.c + 3) / 4 * 4;
+        if (wb.kind != BufKind::Const || !wb.owned || w.offset != 0) return false;
+        if (w.ss.strides[0] != c_pad || (c.c > 1 && w.ss.strides[1] != 1) || w.ss.strides[2] != 3 * c.k * c_pad ||
+            w.ss.strides[3] != c.k * c_pad)
+            return false;
+        for (size_t o = 3; o < s.operands.size(); o++) {
+            const PlanTensor& a = s.operands[o];
+            const BufferInfo& ab = plan_.buffers[a.buf];
+            const auto& st = a.ss.strides;
+            if (st[0] == 0 && st[2] == 0 && st[3] == 0 && ab.kind == BufKind::Const && ab.host_data != nullptr && l.bias_operand < 0)
+                l.bias_operand = (int)o;
+            else if (l.res_operand < 0)
+                l.res_operand = (int)o;
+            else
+                return false;
+        }
+        return true;
+    }
+
+    bool buffer_used_outside(int buf, size_t first, size_t last) const {
+        if (plan_.buffers[buf].always_live) return true;
+        for (size_t i = 0; i < plan_.steps.size(); i++) {
+            if (i >= first && i <= last) continue;
+            for (auto& t : plan_.steps[i].operands)
+                if (t.buf == buf) return true;
+        }
+        return false;
+    }
+
+    void fuse_conv_chains() {
+        if (opts_.math_mode != KN_MATH_TF32 || (opts_.flags & KN_FLAG_NO_CONV_CHAIN)) return;
+        std::vector<Step>& steps = plan_.steps;
+        std::vector<Step> result;
+        size_t i = 0;
+        while (i < steps.size()) {
+            // longest run starting at i
+            std::vector<ChainLayer> layers;
+            for (size_t j = i; j < steps.size() && layers.size() < (size_t)kMaxChainLayers; j++) {
+                ChainLayer l;
+                l.step = j;
+                if (!chain_candidate(steps[j], l)) break;
+                if (!layers.empty()) {
+                    const Step& prev = steps[j - 1];
+                    if (!steps[j].operands[0].same_storage(prev.operands[2])) break;
+                    if (steps[j].conv.n != prev.conv.n || steps[j].conv.h != prev.conv.h || steps[j].conv.w != prev.conv.w) break;
+                }
+                layers.push_back(l);
+            }
+            // the held tensor: follow the skip connections, cut where one does not match
+            size_t len = 0;
+            std::vector<uint8_t> hold(layers.size(), 0);
+            if (!layers.empty()) {
+                PlanTensor held = steps[layers[0].step].operands[0];
+                for (size_t a = 0; a < layers.size(); a++) {
+                    const Step& s = steps[layers[a].step];
+                    if (layers[a].res_operand >= 0 && !s.operands[layers[a].res_operand].same_storage(held)) break;
+                    for (size_t b = a + 1; b < layers.size(); b++) {
+                        const Step& later = steps[layers[b].step];
+                        if (layers[b].res_operand >= 0 && later.operands[layers[b].res_operand].same_storage(s.operands[2])) hold[a] = 1;
+                    }
+                    if (hold[a]) held = s.operands[2];
+                    len = a + 1;
+                }
+                // an intermediate result that something else reads must reach global memory: end the chain there
+                // (a cut moves later layers outside, which may expose earlier results in turn: repeat)
+                for (bool changed = true; changed;) {
+                    changed = false;
+                    for (size_t a = 0; a + 1 < len; a++) {
+                        if (buffer_used_outside(steps[layers[a].step].operands[2].buf, layers[0].step, layers[len - 1].step)) {
+                            len = a + 1;
+                            changed = true;
+                            break;
+                        }
+                    }
+                }
+                // the tensor held at the end must not be required after a cut (it never is: cuts only shorten)
+            }
+            if (len < 2) {
+                result.push_back(std::move(steps[i]));
+                i++;
+                continue;
+            }
+            Step chain = make_chain_step(steps, layers, hold, len);
+            // The chain reads its input through element strides, so a copy that only exists to make the
+            // input channels-last for the per-layer kernel is skipped: read the copy's source instead.
+            if (!result.empty()) {
+                const Step& prev = result.back();
+                const size_t prev_index = layers[0].step - 1;
+                if (prev.kind == StepKind::Scalar && prev.desc == "copy" && prev.operands.size() == 2 && prev.writes[1] &&
+                    prev.operands[1].same_storage(chain.operands[0]) && prev.operands[0].dtype == DType::F32 &&
+                    prev.operands[0].ss.shape == chain.operands[0].ss.shape &&
+                    !buffer_used_outside(prev.operands[1].buf, prev_index, layers[len - 1].step)) {
+                    chain.operands[0] = prev.operands[0];
+                    for (int d = 0; d < 4; d++) chain.chain.s_in[d] = chain.operands[0].ss.strides[d];
+                    chain.alg_bytes = 0;
+                    for (auto& t : chain.operands) chain.alg_bytes += touched_bytes(t);
+                    result.pop_back();
+                }
+            }
+            result.push_back(std::move(chain));
+            i += len;
+        }
+        steps = std::move(result);
+    }
+
+    Step make_chain_step(const std::vector<Step>& steps, const std::vector<ChainLayer>& layers, const std::vector<uint8_t>& hold,
+                         size_t len) {
+        const Step& first = steps[layers[0].step];
+        const Step& last = steps[layers[len - 1].step];
+        Step s;
+        s.kind = StepKind::ConvChain;
+        s.tensor_core = true;
+        s.value = last.value;
+        ConvChainParams& p = s.chain;
+        p.n = first.conv.n;
+        p.c_in = first.conv.c;
+        p.k = first.conv.k;
+        p.h = first.conv.h;
+        p.w = first.conv.w;
+        p.n_layers = (int32_t)len;
+        int64_t n_tiles = 0;
+        for (size_t a = 0; a < len; a++) {
+            const ConvParams& c = steps[layers[a].step].conv;
+            KN_CHECK(c.k == p.k && (a == 0 || c.c == p.k), KN_ERR_INTERNAL, "convolution chain with changing width");
+            p.c_blocks[a] = (uint8_t)((c.c + 31) / 32);
+            n_tiles += 9 * p.c_blocks[a];
+            p.flags[a] = (uint8_t)((c.act == (int32_t)Activation::Relu ? kChainFlagRelu : 0) |
+                                   (layers[a].res_operand >= 0 ? kChainFlagAddHeld : 0) | (hold[a] ? kChainFlagHold : 0));
+            s.flops += steps[layers[a].step].flops;
+        }
+        // filter tiles: [tile][128][32] f32 (already TF32), zero beyond the real channels
+        auto tiles = std::make_shared<std::vector<uint8_t>>((size_t)n_tiles * 128 * 32 * 4, 0);
+        auto bias = std::make_shared<std::vector<uint8_t>>(len * 128 * 4, 0);
+        float* tp = (float*)tiles->data();
+        float* bp = (float*)bias->data();
+        int64_t tile = 0;
+        for (size_t a = 0; a < len; a++) {
+            const Step& st = steps[layers[a].step];
+            const ConvParams& c = st.conv;
+            const int64_t c_pad = (c.c + 3) / 4 * 4;
+            const float* src = (const float*)plan_.buffers[st.operands[1].buf].owned->data();   // [tap][K][c_pad]
+            for (int tap = 0; tap < 9; tap++)
+                for (int cb = 0; cb < p.c_blocks[a]; cb++, tile++)
+                    for (int k = 0; k < c.k; k++)
+                        for (int ch = cb * 32; ch < std::min<int>(c.c, cb * 32 + 32); ch++)
+                        {
+                            // stored exactly as the tile sits in shared memory (rows of 128 bytes whose 16-byte
+                            // chunks are XOR-swizzled with the row number), so a linear bulk copy delivers it
+                            const int col = ch - cb * 32;
+                            const int64_t pos = (int64_t)k * 32 + ((((col >> 2) ^ (k & 7)) << 2) | (col & 3));
+                            tp[tile * 128 * 32 + pos] = src[((int64_t)tap * c.k + k) * c_pad + ch];
+                        }
+            if (layers[a].bias_operand >= 0) {
+                const PlanTensor& b = st.operands[layers[a].bias_operand];
+                const float* bsrc = (const float*)plan_.buffers[b.buf].host_data;
+                for (int k = 0; k < c.k; k++) bp[a * 128 + k] = bsrc[b.offset + (int64_t)k * b.ss.strides[1]];
+            }
+        }
+        PlanTensor t_tiles = alloc_const({n_tiles, 128, 32}, DType::F32, s.value, nullptr, tiles);
+        PlanTensor t_bias = alloc_const({(int64_t)len, 128}, DType::F32, s.value, nullptr, bias);
+        s.operands = {first.operands[0], last.operands[2], t_tiles, t_bias};
+        s.writes = {0, 1, 0, 0};
+        for (int d = 0; d < 4; d++) {
+            p.s_in[d] = first.operands[0].ss.strides[d];
+            p.s_out[d] = last.operands[2].ss.strides[d];
+        }
+        s.desc = "convchain layers=" + std::to_string(len) + " n=" + std::to_string(p.n) + " c=" + std::to_string(p.c_in) + " hw=" +
+                 std::to_string(p.h) + "x" + std::to_string(p.w) + " k=" + std::to_string(p.k) + " rs=3x3 tf32";
+        s.alg_bytes = 0;
+        for (auto& t : s.operands) s.alg_bytes += touched_bytes(t);
+        return s;
+    }
+
+    // Constants no step reads any more (a raw filter whose tap-major copy is used instead, filters
+    // folded into a chain) are not uploaded.
+    void drop_unused_constants() {
+        std::vector<uint8_t> used(plan_.buffers.size(), 0);
+        for (auto& s : plan_.steps)
+            for (auto& t : s.operands) used[t.buf] = 1;
+        for (auto& t : plan_.outputs) used[t.buf] = 1;
+        for (auto& t : plan_.inputs) used[t.buf] = 1;
+        for (size_t b = 0; b < plan_.buffers.size(); b++) {
+            BufferInfo& bi = plan_.buffers[b];
+            if (bi.kind == BufKind::Const && !used[b]) {
+                bi.bytes = 0;
+                bi.host_data = nullptr;
+                bi.owned.reset();
+            }
+        }
     }
 
     // ---------------------------------------------------------------- memory

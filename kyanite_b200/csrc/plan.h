@@ -46,7 +46,7 @@ struct PlanTensor {
 
 struct TcLaunch;   // tensor maps and launch geometry of a tensor-core step (kernels/contract_tc.cu)
 
-enum class StepKind : uint8_t { Scalar = 0, Reduce, Softmax, Layernorm, Gather, Gemm, Conv, COUNT };
+enum class StepKind : uint8_t { Scalar = 0, Reduce, Softmax, Layernorm, Gather, Gemm, Conv, ConvChain, COUNT };
 const char* step_kind_name(StepKind k);
 
 struct Step {
@@ -67,6 +67,7 @@ struct Step {
     GatherParams gather{};
     GemmParams gemm{};
     ConvParams conv{};
+    ConvChainParams chain{};
 };
 
 struct Plan {

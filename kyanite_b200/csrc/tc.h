@@ -17,4 +17,23 @@ void set_last_error(const std::string& message);
 // Output tile of the convolution kernel: wb x hb x nb output positions (product 128).
 bool tc_conv_tile(int oh, int ow, int* wb, int* hb, int* nb);
 
+// Shared-memory layout of the convolution-chain kernel (kernels/conv_chain.cu).  The images of one CTA
+// are stored as one tall zero-padded image: rows of `wp = w + 1` positions (position 0 of a row is the
+// zero left of it and, being adjacent in memory, the zero right of the previous row), `h + 1` rows per
+// image (the first is the zero row shared with the image above), one more zero row at the end.  With
+// that, filter tap (r, s) of every output position is the position `(r - 1) * wp + (s - 1)` further on,
+// a constant shift of the operand's start address.
+struct ChainGeometry {
+    int per_cta;      // images per CTA
+    int wp;           // positions per padded row
+    int q_first;      // padded position of output column 0 (the first real pixel)
+    int n_mma;        // accumulator columns: padded positions q_first .. q_first + n_mma - 1
+    int rows_alloc;   // 128-byte rows per 32-channel block of the activation buffer
+    int slots;        // 16 KB filter tiles in flight
+    int smem_bytes;
+};
+// False if images of this size do not fit (then every layer stays its own step).  `c_blocks` = 32-channel
+// blocks of the widest layer.  Pure host arithmetic.
+bool tc_chain_geometry(int h, int w, int64_t n_img, int c_blocks, ChainGeometry* out);
+
 }  // namespace kn

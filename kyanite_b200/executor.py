@@ -24,19 +24,21 @@ from ._lib import KnError, KnMemUsage, KnOptions, KnTensorInfo, check
 from .graph import DType, Graph
 
 __all__ = ["CudaDevice", "CudaDeviceNotAvailable", "CudaExecutor", "Device", "PreparedGraph", "MemoryUsage",
-           "plan_describe", "KnError", "MATH_TF32", "MATH_F32"]
+           "plan_describe", "KnError", "MATH_TF32", "MATH_F32", "FLAG_NO_CONV_CHAIN"]
 
 MATH_TF32 = _lib.KN_MATH_TF32
 MATH_F32 = _lib.KN_MATH_F32
+FLAG_NO_CONV_CHAIN = _lib.KN_FLAG_NO_CONV_CHAIN
 
 
 class CudaDeviceNotAvailable(RuntimeError):
     pass
 
 
-def _options(math_mode: Optional[int], use_cuda_graph: Optional[bool]) -> KnOptions:
+def _options(math_mode: Optional[int], use_cuda_graph: Optional[bool], flags: int = 0) -> KnOptions:
     opts = KnOptions()
     check(_lib.load().kn_options_default(byref(opts)))
+    opts.flags = int(flags)
     if math_mode is not None:
         opts.math_mode = int(math_mode)
     if use_cuda_graph is not None:
@@ -63,12 +65,12 @@ class _GraphHandle:
             pass
 
 
-def plan_describe(graph, batch_size: int, math_mode: Optional[int] = None) -> str:
+def plan_describe(graph, batch_size: int, math_mode: Optional[int] = None, flags: int = 0) -> str:
     """Text dump of the planned step list; needs no GPU."""
     lib = _lib.load()
     h = _GraphHandle(graph)
     try:
-        opts = _options(math_mode, None)
+        opts = _options(math_mode, None, flags)
         needed = c_size_t()
         check(lib.kn_plan_describe(h.ptr, batch_size, byref(opts), None, 0, byref(needed)))
         buf = ctypes.create_string_buffer(needed.value + 1)
@@ -108,7 +110,7 @@ class MemoryUsage:
 
 class CudaExecutor:
     def __init__(self, device, graph, batch_size: int, math_mode: Optional[int] = None,
-                 use_cuda_graph: Optional[bool] = None):
+                 use_cuda_graph: Optional[bool] = None, flags: int = 0):
         self._lib = _lib.load()
         self._ptr = c_void_p()
         index = device.index if isinstance(device, CudaDevice) else int(device)
@@ -116,7 +118,7 @@ class CudaExecutor:
         self.batch_size = int(batch_size)
         h = _GraphHandle(graph)
         try:
-            opts = _options(math_mode, use_cuda_graph)
+            opts = _options(math_mode, use_cuda_graph, flags)
             status = self._lib.kn_executor_create(index, h.ptr, self.batch_size, byref(opts), byref(self._ptr))
             if status == 6:
                 raise CudaDeviceNotAvailable(self._lib.kn_last_error().decode())

@@ -1,0 +1,125 @@
+"""Runs of 3x3 convolutions merged into the shared-memory-resident chain kernel (kernels/conv_chain.cu):
+what the planner merges (CPU) and that the merged kernel computes what the per-layer kernels and the
+oracle compute (GPU)."""
+import re
+
+import numpy as np
+import pytest
+
+from kyanite_b200.configs import resnet_tower
+from kyanite_b200.executor import FLAG_NO_CONV_CHAIN, MATH_F32, MATH_TF32, plan_describe
+from kyanite_b200.graph import BATCH, Graph, UnaryOp, shape
+from oracle.cpu_eval import assert_tensors_match, cpu_eval_graph
+
+
+def rng(seed):
+    return np.random.Generator(np.random.PCG64(seed))
+
+
+def tower(channels, blocks, h, w, c_in, seed=0, residual=True, relu=True, tap_value=False):
+    """conv-bias-relu stem, then `blocks` x [conv-bias-relu, conv-bias-(+skip)-relu]."""
+    r = rng(seed)
+    g = Graph()
+    x = g.input(shape(BATCH, c_in, h, w))
+
+    def conv(t, cin, scale=1.0):
+        wgt = (r.standard_normal((channels, cin, 3, 3)) * scale * np.sqrt(2.0 / (9 * cin))).astype(np.float32)
+        b = (0.1 * r.standard_normal((1, channels, 1, 1))).astype(np.float32)
+        return g.add(g.conv(t, g.constant_tensor(wgt), 1, 1, 1, 1), g.constant_tensor(b))
+
+    cur = g.relu(conv(x, c_in))
+    extra = None
+    for i in range(blocks):
+        y = g.relu(conv(cur, channels))
+        if tap_value and i == 0:
+            extra = y
+        y = conv(y, channels, 0.5)
+        if residual:
+            y = g.add(y, cur)
+        cur = g.relu(y) if relu else y
+    g.output(cur)
+    if extra is not None:
+        g.output(g.unary(UnaryOp.TANH, extra))
+    return g
+
+
+def steps(description):
+    return [line for line in description.splitlines() if line.startswith("step")]
+
+
+def test_tower_becomes_one_chain():
+    g, _ = resnet_tower()
+    d = plan_describe(g, 256, MATH_TF32)
+    chains = [l for l in steps(d) if " ConvChain/tc " in l]
+    assert len(chains) == 1 and "layers=33" in chains[0]
+    assert not any(" Conv/tc " in l and "rs=3x3" in l for l in steps(d))
+    # the flag and exact-f32 mode keep one step per layer
+    for kwargs in ({"math_mode": MATH_TF32, "flags": FLAG_NO_CONV_CHAIN}, {"math_mode": MATH_F32}):
+        d = plan_describe(g, 256, **kwargs)
+        assert not any("ConvChain" in l for l in steps(d))
+        assert len([l for l in steps(d) if "rs=3x3" in l]) == 33
+
+
+def test_chain_is_cut_where_an_intermediate_escapes():
+    g = tower(32, 3, 8, 8, 32, tap_value=True)
+    d = plan_describe(g, 32, MATH_TF32)
+    chains = [l for l in steps(d) if " ConvChain/tc " in l]
+    # stem + first conv of block 1 (whose result is also an output); the second conv of block 1 adds the
+    # stem's result, which a chain starting there would not hold, so it stays a step of its own; then
+    # the remaining four
+    assert [int(re.search(r"layers=(\d+)", l).group(1)) for l in chains] == [2, 4]
+    assert len([l for l in steps(d) if " Conv/tc " in l]) == 1
+
+
+def test_images_too_large_for_a_chain_stay_per_layer():
+    g = tower(32, 1, 19, 19, 8)
+    d = plan_describe(g, 8, MATH_TF32)
+    assert not any("ConvChain" in l for l in steps(d))
+
+
+CASES = {
+    "tower_8x8_c128": dict(channels=128, blocks=2, h=8, w=8, c_in=21, batch=8),
+    "odd_batch": dict(channels=128, blocks=1, h=8, w=8, c_in=128, batch=5),
+    "two_images": dict(channels=128, blocks=1, h=8, w=8, c_in=16, batch=2),
+    "narrow_64": dict(channels=64, blocks=2, h=8, w=8, c_in=3, batch=6),
+    "narrow_32_5x7": dict(channels=32, blocks=2, h=5, w=7, c_in=32, batch=9),
+    "wide_board_9x9": dict(channels=96, blocks=1, h=9, w=9, c_in=2, batch=4),
+    "tall_12x4": dict(channels=128, blocks=1, h=12, w=4, c_in=40, batch=7),
+    "no_residual_no_relu": dict(channels=128, blocks=2, h=8, w=8, c_in=128, batch=4, residual=False, relu=False),
+    "escaping_intermediate": dict(channels=64, blocks=2, h=6, w=6, c_in=64, batch=4, tap_value=True),
+    "deep": dict(channels=128, blocks=10, h=8, w=8, c_in=21, batch=16),
+}
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_chain_matches_oracle_and_per_layer_kernels(name):
+    from kyanite_b200.executor import CudaExecutor
+    cfg = dict(CASES[name])
+    batch = cfg.pop("batch")
+    g = tower(seed=hash(name) % 1000, **cfg)
+    x = rng(5).standard_normal((batch, cfg["c_in"], cfg["h"], cfg["w"])).astype(np.float32)
+    assert any("ConvChain" in l for l in steps(plan_describe(g, batch, MATH_TF32)))
+    expected = cpu_eval_graph(g.to_bytes(), batch, [x])
+    with CudaExecutor(0, g, batch, math_mode=MATH_TF32) as ex:
+        fused = ex.evaluate([x])
+        assert_tensors_match(expected, fused, 4e-3, 4e-3, abs_scaled=True)
+        assert_tensors_match(fused, ex.evaluate([x]), 0.0, 0.0)      # replay is deterministic
+    with CudaExecutor(0, g, batch, math_mode=MATH_TF32, flags=FLAG_NO_CONV_CHAIN) as ex:
+        per_layer = ex.evaluate([x])
+    # same operands, same TF32 rounding points; only the summation order inside a layer differs
+    assert_tensors_match(per_layer, fused, 2e-4, 2e-4, abs_scaled=True)
+
+
+@pytest.mark.gpu
+def test_full_tower_batch_256():
+    from kyanite_b200.executor import CudaExecutor
+    g, make_inputs = resnet_tower()
+    inputs = make_inputs(256, 3)
+    with CudaExecutor(0, g, 256, math_mode=MATH_TF32) as ex:
+        fused = ex.evaluate(inputs)
+    with CudaExecutor(0, g, 256, math_mode=MATH_TF32, flags=FLAG_NO_CONV_CHAIN) as ex:
+        per_layer = ex.evaluate(inputs)
+    assert_tensors_match(per_layer, fused, 2e-4, 2e-4, abs_scaled=True)
+    expected = cpu_eval_graph(g.to_bytes(), 256, inputs)
+    assert_tensors_match(expected, fused, 4e-3, 4e-3, abs_scaled=True)

@@ -6,7 +6,7 @@ import pytest
 
 import ref_graphs
 from kyanite_b200.configs import mlp, resnet_tower
-from kyanite_b200.executor import MATH_F32, MATH_TF32, KnError, plan_describe
+from kyanite_b200.executor import FLAG_NO_CONV_CHAIN, MATH_F32, MATH_TF32, KnError, plan_describe
 from kyanite_b200.graph import BATCH, DType, Graph, shape
 
 CASES = ref_graphs.all_cases()
@@ -42,15 +42,18 @@ def test_mlp_is_three_gemms_and_a_softmax():
 def test_resnet_tower_step_list():
     g, _ = resnet_tower(channels=16, blocks=2)
     for mode in (MATH_F32, MATH_TF32):
-        kinds = [s.split()[2] for s in steps_of(plan_describe(g, 4, mode))]
+        # (one step per convolution: the merged chain step is covered by tests/test_conv_chain.py)
+        kinds = [s.split()[2] for s in steps_of(plan_describe(g, 4, mode, FLAG_NO_CONV_CHAIN))]
         assert sum(k.startswith("Conv") for k in kinds) == 1 + 2 * 2 + 2
         assert sum(k.startswith("Gemm") for k in kinds) == 2
         assert kinds.count("Softmax") == 2
         # f32: nothing but contractions and softmax; tf32: one channels-last copy of the network input,
         # after which activations stay channels-last from convolution to convolution
         assert kinds.count("Scalar") == (0 if mode == MATH_F32 else 1)
-    kinds = [s.split()[2] for s in steps_of(plan_describe(g, 4, MATH_TF32))]
+    kinds = [s.split()[2] for s in steps_of(plan_describe(g, 4, MATH_TF32, FLAG_NO_CONV_CHAIN))]
     assert kinds.count("Conv/tc") == 7
+    kinds = [s.split()[2] for s in steps_of(plan_describe(g, 4, MATH_TF32))]
+    assert kinds.count("ConvChain/tc") == 1 and kinds.count("Conv/tc") == 2
 
 
 def test_arena_reuses_buffers():
