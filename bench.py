@@ -9,7 +9,7 @@ Prints ONE JSON line (rank 0).  A "step" is one pass of the planned step list ov
              CUDA events on the executor's stream, L2 flushed between timed iterations
   e2e        the same metric through the public `evaluate` call with host buffers: pinned
              host -> device copy of the inputs, the steps, device -> host copy of the outputs
-  roofline   the dominant kernel (trunk 3x3 convolution): algorithmic FLOP per launch / measured
+  roofline   the dominant kernel (the convolution chain that runs the residual tower): algorithmic FLOP per launch / measured
              launch time, against the measured dense tensor peak
   cpu_baseline  the CPU oracle (numpy restatement of the reference's cpu_eval_graph) timed on this
              box's host cores on a bounded sample
@@ -39,6 +39,9 @@ BATCH = 256
 # this bench: 9.05 MB for conv+bias+relu and 17.44 MB with the residual operand (the output stays in L2,
 # 0 bytes written back); the two alternate in the trunk, so the mean is quoted.
 TRUNK_CONV_DRAM_BYTES = 13.24e6
+# DRAM bytes per launch of the convolution chain (all 33 tower layers) at batch 256, from one ncu capture
+# of this bench; None until such a capture is committed under profiles/.
+CHAIN_DRAM_BYTES = None
 WORKLOAD = "resnet_tower_f32_b256 (21x8x8 planes, stem + 16 residual blocks @128ch, policy 73x8x8 softmax, value 3 softmax)"
 
 
@@ -209,6 +212,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--math", default="tf32", choices=["tf32", "f32"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-chain", action="store_true", help="one launch per convolution instead of the merged chain kernel (A/B)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -224,7 +228,7 @@ def main():
     import torch.distributed as dist
 
     from kyanite_b200.configs import resnet_tower, resnet_tower_flops
-    from kyanite_b200.executor import MATH_F32, MATH_TF32, CudaExecutor
+    from kyanite_b200.executor import FLAG_NO_CONV_CHAIN, MATH_F32, MATH_TF32, CudaExecutor
 
     torch.cuda.set_device(local_rank)
     if world > 1:
@@ -233,7 +237,7 @@ def main():
 
     graph, make_inputs = resnet_tower()
     math_mode = MATH_TF32 if args.math == "tf32" else MATH_F32
-    ex = CudaExecutor(local_rank, graph, BATCH, math_mode=math_mode)
+    ex = CudaExecutor(local_rank, graph, BATCH, math_mode=math_mode, flags=FLAG_NO_CONV_CHAIN if args.no_chain else 0)
     inputs = make_inputs(BATCH, 1 + rank)
     for dst, src in zip(ex.host_inputs, inputs):
         dst[...] = src
@@ -288,18 +292,22 @@ def main():
     e2e_ms = e2e_start.elapsed_time(e2e_end)
     clocks = sampler.stop()
 
-    # ---- dominant kernel: every trunk convolution step, each launched back to back between one pair
-    # of CUDA events on the executor's stream (its operands, 8.4 MB activations and 0.6 MB filter, are
-    # L2-resident there exactly as they are inside the step list)
+    # ---- dominant kernel: the contraction step with the most FLOP (the convolution chain that runs the
+    # whole residual tower in one launch; with chains switched off, the trunk convolutions, which are
+    # timed one by one and averaged).  Each is launched 20x back to back between one pair of CUDA events
+    # on the executor's stream.
     ex.set_profile(True)
     ex.run_async()
-    trunk = []
+    contractions = []
     for line in ex.last_profile().splitlines():
         parts = line.split()
-        if len(parts) > 6 and parts[1].startswith("Conv") and "c=128" in line and "k=128" in line and "rs=3x3" in line:
-            trunk.append((int(parts[0]), float(parts[4]), parts[1]))
+        if len(parts) > 6 and parts[0].isdigit() and parts[1].split("/")[0] in ("Conv", "ConvChain", "Gemm"):
+            contractions.append((int(parts[0]), float(parts[4]), parts[1], " ".join(parts[5:])))
     ex.set_profile(False)
-    conv_us = [(ex.time_step(idx, 20), flop, kind) for idx, flop, kind in trunk]
+    dominant = []
+    if contractions:
+        top = max(c[1] for c in contractions)
+        dominant = [(ex.time_step(idx, 20), flop, kind, desc) for idx, flop, kind, desc in contractions if flop == top]
 
     t = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device="cuda")
     if world > 1:
@@ -313,14 +321,16 @@ def main():
         e2e_value = total / (e2e_ms / 1000.0)
         tensor_peak = peaks["bf16_tflops"] / 2.0   # TF32 dense = half the bf16 rate
         roofline = None
-        if conv_us:
-            us = statistics.mean(u for u, _, _ in conv_us)
-            flop = conv_us[0][1]
+        if dominant:
+            us = statistics.mean(u for u, _, _, _ in dominant)
+            flop, kind, desc = dominant[0][1], dominant[0][2], dominant[0][3]
             achieved = flop / (us * 1e-6) / 1e12
-            kind = conv_us[0][2]
-            roofline = {"bound": "tensor", "kernel": "trunk conv3x3 128->128 (" + kind + ")", "achieved": achieved,
-                        "peak": tensor_peak, "unit": "TFLOP/s", "frac": achieved / tensor_peak, "traffic": TRUNK_CONV_DRAM_BYTES,
-                        "peak_source": f"{peaks['source']} bf16 burst / 2 (tf32)", "us_per_launch": us}
+            chain = kind.startswith("ConvChain")
+            roofline = {"bound": "tensor", "kernel": ("conv_chain_kernel: " if chain else "tc_conv_cl_kernel: ") + desc,
+                        "achieved": achieved, "peak": tensor_peak, "unit": "TFLOP/s", "frac": achieved / tensor_peak,
+                        "traffic": CHAIN_DRAM_BYTES if chain else TRUNK_CONV_DRAM_BYTES,
+                        "peak_source": f"{peaks['source']} bf16 burst / 2 (tf32)", "us_per_launch": us,
+                        "gflop_per_launch": flop / 1e9, "launches_per_step": len(dominant)}
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,

@@ -576,11 +576,6 @@ int kn_executor_time_step(kn_executor* exec, int step, int launches, float* micr
             float ms = 0;
             KN_CUDA(cudaEventElapsedTime(&ms, a, b));
             *microseconds = ms * 1000.f / (float)launches;
-            if (getenv("KN_CHAIN_TRACE")) {
-                uint32_t words[64];
-                cudaMemcpy(words, e.status_dev, 256, cudaMemcpyDeviceToHost);
-                for (int i = 16; i < 32; i++) fprintf(stderr, "%u%c", words[i] - words[16], (i % 4 == 3) ? '\n' : ' ');
-            }
         } catch (...) {
             cudaEventDestroy(a);
             cudaEventDestroy(b);

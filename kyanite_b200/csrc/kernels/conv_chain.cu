@@ -4,12 +4,14 @@
 // every layer of the run back to back without ever leaving its SM: the activations live in shared
 // memory (as the B operand of the next layer's MMAs), the skip connection of a residual block lives in
 // tensor memory next to the accumulator, and per layer only the filter streams in from L2 through a
-// ring of 16 KB tiles.  Compared with one launch per layer this removes, per layer, the launch, the
-// pipeline fill, the activation round trip through L2 and the output store.
+// small ring (one request per filter tap: up to four 16 KB tiles, stored by the planner in the swizzled
+// byte order of shared memory so a linear bulk copy delivers them).  Compared with one launch per layer
+// this removes, per layer, the launch, the pipeline fill, the activation round trip through L2 and the
+// output store.
 //
 // Accumulator orientation: D[output channel = TMEM lane][padded position = column].
-//   A operand  filter tile [128 output channels x 32 input channels], K-major, 128-byte swizzle, loaded
-//              by TMA from a tile array the planner lays out in consumption order
+//   A operand  filter tile [128 output channels x 32 input channels], K-major, 128-byte swizzle, copied
+//              with `cp.async.bulk` from a tile array the planner lays out tap by tap
 //   B operand  the activation buffer: per 32-channel block, one 128-byte row per padded position, same
 //              swizzle.  The images are stored as one tall zero-padded image (ChainGeometry, tc.h), so
 //              filter tap (r, s) is the same operand started `(r-1) * wp + (s-1)` rows further on.  Such a
@@ -20,7 +22,7 @@
 //
 // Warp roles (320 threads): warp 0 lane 0 streams filter tiles; warp 1 lane 0 issues the MMAs of a layer
 // once its input is complete; warps 2..9 are the epilogue (two warps per TMEM lane quarter, each taking
-// alternate 32-column blocks): accumulator + bias (+ held skip tensor) -> ReLU -> written back as the
+// alternate 16-column chunks): accumulator + bias (+ held skip tensor) -> ReLU -> written back as the
 // next layer's operand (rounded to TF32, zeros at padding positions) and, if a later layer adds it,
 // into the held-tensor columns of TMEM in full f32; the last layer's result goes to global memory.
 //
@@ -30,7 +32,6 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
-#include <cstdlib>
 #include <cstring>
 #include <memory>
 #include <mutex>
@@ -56,27 +57,13 @@ struct ChainKernelParams {
     const float* tiles;
     int64_t s_in[4], s_out[4];
     int32_t n_img, c_in, k, h, w;
-    int32_t n_layers, per_cta, wp, q_first, n_mma, rows_alloc, slots, tmem_cols, c_blocks_max;
+    int32_t n_layers, per_cta, wp, q_first, r_first, n_mma, rows_alloc, slots, tmem_cols, c_blocks_max;
     int32_t total_tiles;
-    int32_t dbg;
     int32_t group;   // filter tiles per request and per ring slot
     uint8_t flags[kMaxChainLayers];
     uint8_t c_blocks[kMaxChainLayers];
     uint32_t* status;
 };
-
-__device__ __forceinline__ void tmem_store_32(uint32_t taddr, const uint32_t (&v)[32]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
-        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
-          "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]),
-          "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]),
-          "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
-        : "memory");
-    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-}
 
 __device__ __forceinline__ void tmem_store_16(uint32_t taddr, const uint32_t (&v)[16]) {   // caller waits (tcgen05.wait::st)
     asm volatile(
@@ -99,12 +86,6 @@ __device__ __forceinline__ void tmem_load_16_nowait(uint32_t taddr, uint32_t (&v
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-
-__device__ __forceinline__ uint32_t round_tf32_bits(float v) {
-    uint32_t u;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v));
-    return u;
 }
 
 __global__ void __launch_bounds__(kChainThreads, 1)
@@ -186,7 +167,6 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
             const int groups = n / g;
             int idx = (int)((blockIdx.x * 5u) % (uint32_t)groups);
             for (int i = 0; i < groups; i++) {
-                if ((p.dbg & 16) && round > 0) continue;
                 if (round > 0) {
                     if (!mbar_wait(empty_bar + 8u * slot, (uint32_t)((round & 1) ^ 1), abandon, p.status, 11)) { ok = false; break; }
                 }
@@ -203,8 +183,7 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
         }
     } else if (warp == 1 && lane == 0) {
         // ---------------- MMA issuer
-        const int n_dbg = (p.dbg >> 8) ? (p.dbg >> 8) : p.n_mma;
-        const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n_dbg >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+        const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(p.n_mma >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
         int slot = 0, round = 0;
         bool ok = true;
         for (int l = 0; l < p.n_layers && ok; l++) {
@@ -212,7 +191,6 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
             ok = mbar_wait(act_bar, (uint32_t)(l & 1), abandon, p.status, 12);
             if (!ok) break;
             tc_fence_after();
-            if ((p.dbg & 128) && blockIdx.x == 0 && l >= 2 && l < 6) p.status[16 + (l - 2) * 4 + 0] = (uint32_t)clock64();
             const int cbl = p.c_blocks[l];
             uint32_t accumulate = 0;
             const int n = 9 * cbl;
@@ -222,17 +200,17 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
             int tile = (int)((blockIdx.x * 5u) % (uint32_t)groups) * g;
             int tap = tile / cbl, cb = tile - tap * cbl;
             for (int i = 0; i < groups && ok; i++) {
-                if (!((p.dbg & 16) && round > 0)) ok = mbar_wait(full_bar + 8u * slot, (uint32_t)(round & 1), abandon, p.status, 13);
+                ok = mbar_wait(full_bar + 8u * slot, (uint32_t)(round & 1), abandon, p.status, 13);
                 if (!ok) break;
                 tc_fence_after();
                 for (int u = 0; u < g; u++) {
                     const int r = tap >= 6 ? 2 : (tap >= 3 ? 1 : 0), s = tap - 3 * r;
-                    const uint32_t row0 = (uint32_t)(p.q_first + (r - 1) * p.wp + (s - 1));
+                    const uint32_t row0 = (uint32_t)(p.r_first + (r - 1) * p.wp + (s - 1));
                     const uint64_t da = smem_desc_sw128(ring_base + (uint32_t)slot * slot_bytes + (uint32_t)u * kTileBytes);
                     const uint64_t db = smem_desc_sw128(base + (uint32_t)cb * block_bytes + row0 * 128u);
 #pragma unroll
                     for (int j = 0; j < 4; j++) {
-                        if (!(p.dbg & 1)) mma_tf32(tmem_acc, da + 2u * j, db + 2u * j, idesc, accumulate);
+                        mma_tf32(tmem_acc, da + 2u * j, db + 2u * j, idesc, accumulate);
                         accumulate = 1;
                     }
                     if (++cb == cbl) {
@@ -244,7 +222,6 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
                 if (++slot == p.slots) { slot = 0; round++; }
             }
             if (ok) mma_commit(accum_bar);
-            if ((p.dbg & 128) && blockIdx.x == 0 && l >= 2 && l < 6) p.status[16 + (l - 2) * 4 + 1] = (uint32_t)clock64();
         }
     } else if (warp >= 2) {
         // ---------------- epilogue: thread <-> accumulator lane <-> channel; the two warps of a lane
@@ -257,7 +234,6 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
         const bool has_block = (ch >> 5) < p.c_blocks_max;     // narrower layers: no operand rows for these channels
         const uint32_t chunk = (uint32_t)(ch >> 2) & 7u;
         // this channel's 4 bytes inside a 128-byte row of its 32-channel block, before the swizzle
-        uint8_t* const my_rows = gen_base + (uint32_t)(ch >> 5) * block_bytes + (uint32_t)(ch & 3) * 4u;
         const int chunks16 = (p.n_mma + 15) >> 4;
         constexpr int kMaxMine = 8;                             // 256 columns / 16 / 2 warps
         // which of my columns are real pixels (everything else is written as zero padding)
@@ -270,10 +246,20 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
                 for (int j = 0; j < 16; j++) m |= (colinfo[c * 16 + j] >> 31) << j;
             real[k] = m;
         }
-        auto store_operand = [&](uint32_t q, float v) {
-            *(uint32_t*)(my_rows + q * 128u + ((chunk ^ (q & 7u)) << 4)) = round_tf32_bits(v);
+        // Output column n is stored in row r_first + n of the channel's block; r_first is a multiple of 8, so
+        // the swizzle phase of a row (row & 7) is the column's n & 7, known at compile time inside the
+        // unrolled loops: the eight swizzled chunk offsets are computed once.
+        uint32_t sw[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) sw[i] = (chunk ^ (uint32_t)i) << 4;
+        const uint32_t my_rows = base + (uint32_t)(ch >> 5) * block_bytes + (uint32_t)(ch & 3) * 4u + (uint32_t)p.r_first * 128u;
+        // round to TF32 (nearest, ties away from zero) with integer arithmetic: the tensor core ignores
+        // the low 13 mantissa bits, so adding half an ulp of TF32 to the magnitude is all it takes
+        auto store_operand = [&](uint32_t chunk_rows, int j, float v) {
+            uint32_t u = __float_as_uint(v);
+            if ((u & 0x7F800000u) != 0x7F800000u) u += 0x1000u;
+            asm volatile("st.shared.b32 [%0], %1;" ::"r"(chunk_rows + sw[j & 7] + (uint32_t)j * 128u), "r"(u) : "memory");
         };
-
         // layer 0's input: from global memory into the operand layout and the held-tensor columns
         asm volatile("griddepcontrol.wait;" ::: "memory");
         for (int c = half; c < chunks16; c += 2) {
@@ -286,7 +272,7 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
                     x = p.in[(img0 + ((info >> 16) & 0xFF)) * p.s_in[0] + (int64_t)ch * p.s_in[1] + (int64_t)((info >> 8) & 0xFF) * p.s_in[2] +
                              (int64_t)(info & 0xFF) * p.s_in[3]];
                 v[j] = __float_as_uint(x);
-                if (has_block) store_operand((uint32_t)(c * 16 + j + p.q_first), x);
+                if (has_block) store_operand(my_rows + (uint32_t)c * 2048u, j, x);
             }
             tmem_store_16(tmem_held + lane_bits + (uint32_t)(c * 16), v);
         }
@@ -324,26 +310,26 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
                 while (!mbar_try_wait(accum_bar, (uint32_t)(l & 1))) {}
             }
             tc_fence_after();
-            if ((p.dbg & 128) && blockIdx.x == 0 && threadIdx.x == 64 && l >= 2 && l < 6) p.status[16 + (l - 2) * 4 + 2] = (uint32_t)clock64();
-            if (!(p.dbg & 2)) {
-#pragma unroll
-                for (int k = 0; k < kMaxMine; k++) {
-                    const int c = half + 2 * k;
-                    if (c >= chunks16) break;
-                    uint32_t v[16], hv[16];
+            {
+                // Software pipeline over my chunks: while chunk k is being finished, the tensor-memory loads
+                // of chunk k + 1 are in flight.  `tcgen05.wait::ld` waits for every outstanding load, so it
+                // comes right before the next chunk's loads are issued.
+                uint32_t va[16], ha[16], vb[16], hb[16];
+                auto issue = [&](int c, uint32_t (&v)[16], uint32_t (&h)[16]) {
                     tmem_load_16_nowait(tmem_acc + lane_bits + (uint32_t)(c * 16), v);
-                    if (add_held) tmem_load_16_nowait(tmem_held + lane_bits + (uint32_t)(c * 16), hv);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    const uint32_t q0 = (uint32_t)(c * 16 + p.q_first);
+                    if (add_held) tmem_load_16_nowait(tmem_held + lane_bits + (uint32_t)(c * 16), h);
+                };
+                auto finish = [&](int k, int c, uint32_t (&v)[16], uint32_t (&h)[16]) {
+                    const uint32_t chunk_rows = my_rows + (uint32_t)c * 2048u;
                     const uint32_t mask = (ch < p.k) ? real[k] : 0u;
 #pragma unroll
                     for (int j = 0; j < 16; j++) {
                         float x = __uint_as_float(v[j]) + bias;
-                        if (add_held) x += __uint_as_float(hv[j]);
+                        if (add_held) x += __uint_as_float(h[j]);
                         if (relu) x = fmaxf(x, 0.f);
                         if (!((mask >> j) & 1u)) x = 0.f;
                         v[j] = __float_as_uint(x);
-                        if (!last && has_block) store_operand(q0 + (uint32_t)j, x);
+                        if (!last && has_block) store_operand(chunk_rows, j, x);
                     }
                     if (hold) tmem_store_16(tmem_held + lane_bits + (uint32_t)(c * 16), v);
                     if (last) {
@@ -356,6 +342,19 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
                             }
                         }
                     }
+                };
+                if (half < chunks16) issue(half, va, ha);
+#pragma unroll
+                for (int k = 0; k < kMaxMine; k += 2) {
+                    const int c = half + 2 * k;
+                    if (c >= chunks16) break;
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (c + 2 < chunks16) issue(c + 2, vb, hb);
+                    finish(k, c, va, ha);
+                    if (c + 2 >= chunks16) break;
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (c + 4 < chunks16) issue(c + 4, va, ha);
+                    finish(k + 1, c + 2, vb, hb);
                 }
                 if (hold) asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             }
@@ -364,7 +363,6 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
                 tc_fence_before();
                 mbar_arrive(act_bar);
             }
-            if ((p.dbg & 128) && blockIdx.x == 0 && threadIdx.x == 64 && l >= 2 && l < 6) p.status[16 + (l - 2) * 4 + 3] = (uint32_t)clock64();
         }
     }
 
@@ -390,11 +388,12 @@ bool tc_chain_geometry(int h, int w, int64_t n_img, int c_blocks, ChainGeometry*
         g.per_cta = per;
         g.wp = wp;
         g.q_first = wp + 1;
+        g.r_first = round_up_int(g.q_first, 8);
         const int q_last = (per * (h + 1) - 1) * wp + w;
         g.n_mma = round_up_int(q_last - g.q_first + 1, 16);
         if (g.n_mma > 256) break;
         const int cols = round_up_int(g.n_mma, 32);
-        g.rows_alloc = round_up_int(g.q_first + cols + wp + 2, 8);
+        g.rows_alloc = round_up_int(g.r_first + cols + wp + 2, 8);
         const int act_bytes = c_blocks * g.rows_alloc * 128;
         const int fixed = 1024 /* alignment */ + 16 * 8 + 32 + 1024 /* column table */;
         g.slots = std::min(8, (227 * 1024 - fixed - act_bytes) / kTileBytes);
@@ -455,6 +454,7 @@ std::shared_ptr<void> chain_prepare(const ConvChainParams& c, uint32_t* status_w
     p.per_cta = g.per_cta;
     p.wp = g.wp;
     p.q_first = g.q_first;
+    p.r_first = g.r_first;
     p.n_mma = g.n_mma;
     p.rows_alloc = g.rows_alloc;
     p.slots = g.slots;
@@ -463,8 +463,9 @@ std::shared_ptr<void> chain_prepare(const ConvChainParams& c, uint32_t* status_w
     while (tmem < cols) tmem <<= 1;
     p.tmem_cols = tmem;
     p.status = status_word;
-    p.dbg = getenv("KN_CHAIN_DBG") ? atoi(getenv("KN_CHAIN_DBG")) : 0;
-    p.group = getenv("KN_CHAIN_G") ? atoi(getenv("KN_CHAIN_G")) : c_blocks_max;
+    // one request per filter tap (all channel blocks of the tap, up to 64 KB): large requests stream at
+    // about twice the rate of single 16 KB tiles
+    p.group = c_blocks_max;
     p.slots = g.slots / p.group;
     int64_t dims[3] = {32, 128, p.total_tiles}, strides[3] = {1, 32, 128 * 32};
     int box[3] = {32, 128, 1};

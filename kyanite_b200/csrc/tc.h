@@ -27,6 +27,8 @@ struct ChainGeometry {
     int per_cta;      // images per CTA
     int wp;           // positions per padded row
     int q_first;      // padded position of output column 0 (the first real pixel)
+    int r_first;      // shared-memory row that holds position q_first: q_first rounded up to a multiple of 8, so
+                      // that a column's swizzle phase (row & 7) does not depend on the geometry
     int n_mma;        // accumulator columns: padded positions q_first .. q_first + n_mma - 1
     int rows_alloc;   // 128-byte rows per 32-channel block of the activation buffer
     int slots;        // 16 KB filter tiles in flight

@@ -64,11 +64,12 @@ def test_chain_is_cut_where_an_intermediate_escapes():
     g = tower(32, 3, 8, 8, 32, tap_value=True)
     d = plan_describe(g, 32, MATH_TF32)
     chains = [l for l in steps(d) if " ConvChain/tc " in l]
-    # stem + first conv of block 1 (whose result is also an output); the second conv of block 1 adds the
-    # stem's result, which a chain starting there would not hold, so it stays a step of its own; then
-    # the remaining four
-    assert [int(re.search(r"layers=(\d+)", l).group(1)) for l in chains] == [2, 4]
-    assert len([l for l in steps(d) if " Conv/tc " in l]) == 1
+    # The first conv of block 1 produces a graph output, so a chain would have to end there; but then the
+    # stem's result, which the second conv of block 1 adds, would be needed outside that chain while only
+    # a chain's last result reaches global memory.  So stem, first and second conv of block 1 stay steps
+    # of their own, and the remaining four layers form a chain.
+    assert [int(re.search(r"layers=(\d+)", l).group(1)) for l in chains] == [4]
+    assert len([l for l in steps(d) if " Conv/tc " in l]) == 3
 
 
 def test_images_too_large_for_a_chain_stay_per_layer():
@@ -104,11 +105,14 @@ def test_chain_matches_oracle_and_per_layer_kernels(name):
     with CudaExecutor(0, g, batch, math_mode=MATH_TF32) as ex:
         fused = ex.evaluate([x])
         assert_tensors_match(expected, fused, 4e-3, 4e-3, abs_scaled=True)
-        assert_tensors_match(fused, ex.evaluate([x]), 0.0, 0.0)      # replay is deterministic
+        for a, b in zip(fused, ex.evaluate([x])):                    # replay is deterministic
+            np.testing.assert_array_equal(a, b)
     with CudaExecutor(0, g, batch, math_mode=MATH_TF32, flags=FLAG_NO_CONV_CHAIN) as ex:
         per_layer = ex.evaluate([x])
-    # same operands, same TF32 rounding points; only the summation order inside a layer differs
-    assert_tensors_match(per_layer, fused, 2e-4, 2e-4, abs_scaled=True)
+    # Same operands and the same TF32 rounding points; only the summation order inside a layer differs.
+    # That moves a result by an ulp of f32, which now and then flips the TF32 rounding of an activation
+    # (2^-11 relative); over tens of layers these flips add up to about 1e-3 of the output scale.
+    assert_tensors_match(per_layer, fused, 1e-3, 1e-3, abs_scaled=True)
 
 
 @pytest.mark.gpu
@@ -120,6 +124,6 @@ def test_full_tower_batch_256():
         fused = ex.evaluate(inputs)
     with CudaExecutor(0, g, 256, math_mode=MATH_TF32, flags=FLAG_NO_CONV_CHAIN) as ex:
         per_layer = ex.evaluate(inputs)
-    assert_tensors_match(per_layer, fused, 2e-4, 2e-4, abs_scaled=True)
+    assert_tensors_match(per_layer, fused, 1e-3, 1e-3, abs_scaled=True)
     expected = cpu_eval_graph(g.to_bytes(), 256, inputs)
     assert_tensors_match(expected, fused, 4e-3, 4e-3, abs_scaled=True)
