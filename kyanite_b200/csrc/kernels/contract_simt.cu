@@ -150,9 +150,52 @@ int launch(const Problem& prob, int64_t M, int64_t N, int64_t batch, cudaStream_
     return (int)cudaGetLastError();
 }
 
+// Matrix multiply with very few output columns (a classifier head, n <= 8): a 64 x 64 tile would leave
+// almost every thread idle and walk K serially, so one warp takes one output row instead, its lanes
+// stride through K (coalesced when K is the fast axis of both operands) and a shuffle tree sums them.
+constexpr int kSkinnyMaxN = 8;
+
+__global__ void __launch_bounds__(256) gemm_skinny_kernel(const __grid_constant__ GemmParams p) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row_id = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row_id >= p.batch * p.m) return;
+    const int64_t b = row_id / p.m, m = row_id - b * p.m;
+    const float* a = p.a + b * p.sa[0] + m * p.sa[1];
+    const float* w = p.b + b * p.sb[0];
+    float acc[kSkinnyMaxN];
+#pragma unroll
+    for (int n = 0; n < kSkinnyMaxN; n++) acc[n] = 0.f;
+    for (int64_t k = lane; k < p.k; k += 32) {
+        const float x = a[k * p.sa[2]];
+#pragma unroll
+        for (int n = 0; n < kSkinnyMaxN; n++)
+            if (n < p.n) acc[n] = fmaf(x, w[k * p.sb[1] + n * p.sb[2]], acc[n]);
+    }
+#pragma unroll
+    for (int n = 0; n < kSkinnyMaxN; n++)
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) acc[n] += __shfl_xor_sync(0xffffffffu, acc[n], off);
+#pragma unroll
+    for (int n = 0; n < kSkinnyMaxN; n++) {
+        if (n < p.n && lane == n) {
+            float v = acc[n];
+            if (p.add1) v += p.add1[b * p.s1[0] + m * p.s1[1] + n * p.s1[2]];
+            if (p.add2) v += p.add2[b * p.s2[0] + m * p.s2[1] + n * p.s2[2]];
+            p.c[b * p.sc[0] + m * p.sc[1] + n * p.sc[2]] = apply_epilogue(v, p.act, p.round_tf32);
+        }
+    }
+}
+
 }  // namespace
 
-int launch_gemm_simt(const GemmParams& p, cudaStream_t stream) { return launch(GemmProblem{p}, p.m, p.n, p.batch, stream); }
+int launch_gemm_simt(const GemmParams& p, cudaStream_t stream) {
+    if (p.n >= 1 && p.n <= kSkinnyMaxN && p.k >= 32 && p.batch * p.m > 0) {
+        const int64_t rows = p.batch * p.m;
+        gemm_skinny_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(p);
+        return (int)cudaGetLastError();
+    }
+    return launch(GemmProblem{p}, p.m, p.n, p.batch, stream);
+}
 
 int launch_conv_simt(const ConvParams& p, cudaStream_t stream) {
     return launch(ConvProblem{p}, (int64_t)p.n * p.oh * p.ow, p.k, 1, stream);

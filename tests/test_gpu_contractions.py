@@ -81,3 +81,21 @@ def test_full_tower(mode, tol):
     with CudaExecutor(0, g, 16, math_mode=mode) as ex:
         got = ex.evaluate(ins)
     assert_tensors_match(want, got, tol_abs=tol, tol_rel=tol)
+
+
+@pytest.mark.parametrize("mode", [MATH_F32, MATH_TF32], ids=["f32", "tf32"])
+@pytest.mark.parametrize("b,m,n,k", [(1, 256, 3, 256), (1, 7, 1, 33), (4, 50, 8, 1000), (2, 300, 5, 32), (1, 1, 2, 4096)])
+def test_matmul_with_few_columns(b, m, n, k, mode):
+    """n <= 8 takes the one-warp-per-row kernel: linear-layer operands (K fast in both), a bias and ReLU,
+    and a second graph with the operands transposed the other way (K slow)."""
+    g = Graph()
+    a = g.input(shape(b, m, k))
+    w = g.input(shape(b, n, k))
+    bias = g.input(shape(1, 1, n))
+    g.output(g.relu(g.add(g.batched_mat_mul(a, g.permute(w, [0, 2, 1])), bias)))
+    check(g, 0, [rng(1, b, m, k), rng(2, b, n, k), rng(3, 1, 1, n)], mode=mode)
+    g = Graph()
+    at = g.input(shape(b, k, m))
+    w2 = g.input(shape(b, k, n))
+    g.output(g.batched_mat_mul(g.permute(at, [0, 2, 1]), w2))
+    check(g, 0, [rng(4, b, k, m), rng(5, b, k, n)], mode=mode)
