@@ -56,7 +56,9 @@ struct Executor {
     std::vector<void*> pinned_in, pinned_out;
     std::vector<size_t> bytes_in, bytes_out;
     std::vector<DType> dtype_in, dtype_out;
-    cudaGraphExec_t graph_exec = nullptr;
+    cudaGraphExec_t graph_exec = nullptr;        // the step list
+    cudaGraphExec_t eval_graph_exec = nullptr;   // uploads + step list + downloads (see capture_evaluate)
+    cudaStream_t side_stream = nullptr;          // capture-time fork for early output copies
     bool profile = false;
     std::vector<float> step_us;
     int launches = 0;
@@ -65,6 +67,8 @@ struct Executor {
         cudaSetDevice(device);
         if (stream) cudaStreamSynchronize(stream);
         if (graph_exec) cudaGraphExecDestroy(graph_exec);
+        if (eval_graph_exec) cudaGraphExecDestroy(eval_graph_exec);
+        if (side_stream) cudaStreamDestroy(side_stream);
         for (void* p : pinned_in) if (p) cudaFreeHost(p);
         for (void* p : pinned_out) if (p) cudaFreeHost(p);
         if (arena) cudaFree(arena);
@@ -220,15 +224,83 @@ struct Executor {
         }
     }
 
+    // One graph for a whole `evaluate`: input copies, the steps, output copies.  An output that is complete
+    // before the last step (the large policy tensor of a two-headed network, say) starts its way back to
+    // the host on a forked branch right after the step that produces it, so the copy overlaps the rest
+    // of the step list instead of following it.
+    void capture_evaluate() {
+        const size_t n_steps = plan->steps.size();
+        // last step that writes each output's buffer (-1: none, e.g. an output that is an input or a constant)
+        std::vector<int> producer(plan->outputs.size(), -1);
+        for (size_t o = 0; o < plan->outputs.size(); o++)
+            for (size_t i = 0; i < n_steps; i++)
+                for (size_t k = 0; k < plan->steps[i].operands.size(); k++)
+                    if (plan->steps[i].writes[k] && plan->steps[i].operands[k].buf == plan->outputs[o].buf) producer[o] = (int)i;
+        if (!side_stream) KN_CUDA(cudaStreamCreateWithFlags(&side_stream, cudaStreamNonBlocking));
+        std::vector<cudaEvent_t> events;
+        auto new_event = [&]() {
+            cudaEvent_t e;
+            KN_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+            events.push_back(e);
+            return e;
+        };
+        auto copy_out = [&](size_t o, cudaStream_t st) {
+            if (bytes_out[o])
+                KN_CUDA(cudaMemcpyAsync(pinned_out[o], device_ptr(plan->outputs[o]), bytes_out[o], cudaMemcpyDeviceToHost, st));
+        };
+        cudaGraph_t graph = nullptr;
+        KN_CUDA(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
+        try {
+            upload_inputs();
+            bool forked = false;
+            for (size_t i = 0; i < n_steps; i++) {
+                launch_step(plan->steps[i]);
+                if (i + 1 == n_steps) break;
+                for (size_t o = 0; o < producer.size(); o++) {
+                    if (producer[o] != (int)i || bytes_out[o] == 0) continue;
+                    cudaEvent_t e = new_event();
+                    KN_CUDA(cudaEventRecord(e, stream));
+                    KN_CUDA(cudaStreamWaitEvent(side_stream, e, 0));
+                    copy_out(o, side_stream);
+                    forked = true;
+                }
+            }
+            for (size_t o = 0; o < producer.size(); o++)
+                if (n_steps == 0 || producer[o] < 0 || producer[o] == (int)n_steps - 1) copy_out(o, stream);
+            KN_CUDA(cudaMemcpyAsync(status_host, status_dev, 4, cudaMemcpyDeviceToHost, stream));
+            if (forked) {
+                cudaEvent_t e = new_event();
+                KN_CUDA(cudaEventRecord(e, side_stream));
+                KN_CUDA(cudaStreamWaitEvent(stream, e, 0));
+            }
+        } catch (...) {
+            cudaStreamEndCapture(stream, &graph);
+            if (graph) cudaGraphDestroy(graph);
+            for (cudaEvent_t e : events) cudaEventDestroy(e);
+            throw;
+        }
+        cudaError_t end = cudaStreamEndCapture(stream, &graph);
+        for (cudaEvent_t e : events) cudaEventDestroy(e);
+        KN_CUDA(end);
+        cudaError_t err = cudaGraphInstantiate(&eval_graph_exec, graph, 0);
+        cudaGraphDestroy(graph);
+        KN_CUDA(err);
+    }
+
     void evaluate(const void* const* inputs, void* const* outputs) {
         KN_CUDA(cudaStreamSynchronize(stream));
         for (size_t i = 0; i < pinned_in.size(); i++) {
             KN_CHECK(inputs != nullptr && (inputs[i] != nullptr || bytes_in[i] == 0), KN_ERR_INVALID_ARG, "null input buffer");
             if (bytes_in[i] && inputs[i] != pinned_in[i]) memcpy(pinned_in[i], inputs[i], bytes_in[i]);
         }
-        upload_inputs();
-        run_async();
-        download_outputs();
+        if (plan->opts.use_cuda_graph && !profile) {
+            if (!eval_graph_exec) capture_evaluate();
+            KN_CUDA(cudaGraphLaunch(eval_graph_exec, stream));
+        } else {
+            upload_inputs();
+            run_async();
+            download_outputs();
+        }
         KN_CUDA(cudaStreamSynchronize(stream));
         check_status();
         for (size_t i = 0; i < pinned_out.size(); i++) {
