@@ -57,7 +57,7 @@ struct ChainKernelParams {
     const float* tiles;
     int64_t s_in[4], s_out[4];
     int32_t n_img, c_in, k, h, w;
-    int32_t n_layers, per_cta, wp, q_first, r_first, n_mma, rows_alloc, slots, tmem_cols, c_blocks_max;
+    int32_t n_layers, per_cta, gx, gy, wp, q_first, r_first, n_mma, rows_alloc, slots, tmem_cols, c_blocks_max;
     int32_t total_tiles;
     int32_t group;   // filter tiles per request and per ring slot
     uint8_t flags[kMaxChainLayers];
@@ -106,7 +106,6 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
     uint32_t* colinfo = (uint32_t*)(gen_base + (slot_addr + 8u - base));         // 256 entries
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int blocks32 = (p.n_mma + 31) >> 5;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.slots; s++) {
@@ -132,9 +131,11 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
         if (n < p.n_mma) {
             const int q = n + p.q_first;
             const int row = q / p.wp, col = q - row * p.wp;
-            const int img = row / (p.h + 1), ry = row - img * (p.h + 1);
-            if (col != 0 && ry != 0 && img < p.per_cta && (int64_t)blockIdx.x * p.per_cta + img < p.n_img)
-                info = 0x80000000u | ((uint32_t)img << 16) | ((uint32_t)(ry - 1) << 8) | (uint32_t)(col - 1);
+            const int iy = row / (p.h + 1), ry = row - iy * (p.h + 1);
+            const int ix = col / (p.w + 1), cx = col - ix * (p.w + 1);
+            const int img = iy * p.gx + ix;
+            if (cx != 0 && ry != 0 && iy < p.gy && (int64_t)blockIdx.x * p.per_cta + img < p.n_img)
+                info = 0x80000000u | ((uint32_t)img << 16) | ((uint32_t)(ry - 1) << 8) | (uint32_t)(cx - 1);
         }
         colinfo[n] = info;
     }
@@ -147,7 +148,7 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_acc = *tmem_slot;
-    const uint32_t tmem_held = tmem_acc + (uint32_t)(blocks32 * 32);
+    const uint32_t tmem_held = tmem_acc + (uint32_t)p.n_mma;      // n_mma is a multiple of 16
 
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
@@ -380,34 +381,39 @@ static int round_up_int(int x, int to) { return (x + to - 1) / to * to; }
 
 bool tc_chain_geometry(int h, int w, int64_t n_img, int c_blocks, ChainGeometry* out) {
     if (h < 1 || w < 1 || h > 254 || w > 254 || n_img < 1 || c_blocks < 1 || c_blocks > 4) return false;
-    const int wp = w + 1;
     ChainGeometry best{};
     double best_cost = 1e300;
-    for (int per = 1; per <= 255; per++) {
-        ChainGeometry g{};
-        g.per_cta = per;
-        g.wp = wp;
-        g.q_first = wp + 1;
-        g.r_first = round_up_int(g.q_first, 8);
-        const int q_last = (per * (h + 1) - 1) * wp + w;
-        g.n_mma = round_up_int(q_last - g.q_first + 1, 16);
-        if (g.n_mma > 256) break;
-        const int cols = round_up_int(g.n_mma, 32);
-        g.rows_alloc = round_up_int(g.r_first + cols + wp + 2, 8);
-        const int act_bytes = c_blocks * g.rows_alloc * 128;
-        const int fixed = 1024 /* alignment */ + 16 * 8 + 32 + 1024 /* column table */;
-        g.slots = std::min(8, (227 * 1024 - fixed - act_bytes) / kTileBytes);
-        if (g.slots < 3) break;
-        g.smem_bytes = fixed + act_bytes + g.slots * kTileBytes;
-        // per layer: 36 tiles x 4 MMAs (an MMA costs ~70 cycles up to N = 128, then grows with N), plus
-        // the epilogue over the columns; CTAs run in waves of one per SM
-        const double mma = std::max(70.0, 0.53 * g.n_mma + 2.0);
-        const double per_layer = 144.0 * mma + 12.0 * cols;
-        const int64_t ctas = (n_img + per - 1) / per;
-        const double cost = (double)((ctas + 147) / 148) * per_layer;
-        if (cost < best_cost) {
-            best_cost = cost;
-            best = g;
+    // gx images side by side, gy such rows of images below one another
+    for (int gx = 1; gx <= 16; gx++) {
+        for (int gy = 1; gy <= 16; gy++) {
+            ChainGeometry g{};
+            g.gx = gx;
+            g.gy = gy;
+            g.per_cta = gx * gy;
+            g.wp = gx * (w + 1);
+            g.q_first = g.wp + 1;
+            g.r_first = round_up_int(g.q_first, 8);
+            const int q_last = ((gy - 1) * (h + 1) + h) * g.wp + (gx - 1) * (w + 1) + w;
+            g.n_mma = round_up_int(q_last - g.q_first + 1, 16);
+            if (g.n_mma > 256) break;
+            g.rows_alloc = round_up_int(g.r_first + g.n_mma + g.wp + 2, 8);
+            const int act_bytes = c_blocks * g.rows_alloc * 128;
+            const int fixed = 1024 /* alignment */ + 16 * 8 + 32 + 1024 /* column table */;
+            // the ring holds whole taps (c_blocks tiles each): two of them at least, four at most
+            const int taps = std::min(4, (227 * 1024 - fixed - act_bytes) / (kTileBytes * c_blocks));
+            if (taps < 2) break;
+            g.slots = taps * c_blocks;
+            g.smem_bytes = fixed + act_bytes + g.slots * kTileBytes;
+            // per layer: 36 tiles x 4 MMAs (an MMA costs ~70 cycles up to N = 128, then grows with N), plus
+            // the epilogue over the columns; CTAs run in waves of one per SM
+            const double mma = std::max(70.0, 0.47 * g.n_mma + 16.0);
+            const double per_layer = 144.0 * mma + 22.0 * g.n_mma + 900.0;
+            const int64_t ctas = (n_img + g.per_cta - 1) / g.per_cta;
+            const double cost = (double)((ctas + 147) / 148) * per_layer;
+            if (cost < best_cost) {
+                best_cost = cost;
+                best = g;
+            }
         }
     }
     if (best.per_cta == 0) return false;
@@ -452,6 +458,8 @@ std::shared_ptr<void> chain_prepare(const ConvChainParams& c, uint32_t* status_w
     p.w = c.w;
     p.n_layers = c.n_layers;
     p.per_cta = g.per_cta;
+    p.gx = g.gx;
+    p.gy = g.gy;
     p.wp = g.wp;
     p.q_first = g.q_first;
     p.r_first = g.r_first;
@@ -459,7 +467,7 @@ std::shared_ptr<void> chain_prepare(const ConvChainParams& c, uint32_t* status_w
     p.rows_alloc = g.rows_alloc;
     p.slots = g.slots;
     p.c_blocks_max = c_blocks_max;
-    int cols = 2 * round_up_int(g.n_mma, 32), tmem = 32;
+    int cols = 2 * g.n_mma, tmem = 32;
     while (tmem < cols) tmem <<= 1;
     p.tmem_cols = tmem;
     p.status = status_word;

@@ -18,13 +18,16 @@ void set_last_error(const std::string& message);
 bool tc_conv_tile(int oh, int ow, int* wb, int* hb, int* nb);
 
 // Shared-memory layout of the convolution-chain kernel (kernels/conv_chain.cu).  The images of one CTA
-// are stored as one tall zero-padded image: rows of `wp = w + 1` positions (position 0 of a row is the
-// zero left of it and, being adjacent in memory, the zero right of the previous row), `h + 1` rows per
-// image (the first is the zero row shared with the image above), one more zero row at the end.  With
-// that, filter tap (r, s) of every output position is the position `(r - 1) * wp + (s - 1)` further on,
-// a constant shift of the operand's start address.
+// are stored as one large zero-padded image, `gx` images side by side and `gy` such rows of images below
+// one another: a row has `wp = gx * (w + 1)` positions (the position in front of each image row is the
+// zero left of it and, being adjacent in memory, the zero right of the image row before it), there are
+// `h + 1` rows per row of images (the first is the zero row shared with the images above), and one more
+// zero row at the end.  With that, filter tap (r, s) of every output position is the position
+// `(r - 1) * wp + (s - 1)` further on, a constant shift of the operand's start address.  Two 8x8 boards
+// side by side need 144 accumulator columns (128 of them real pixels), stacked they would need 160.
 struct ChainGeometry {
-    int per_cta;      // images per CTA
+    int per_cta;      // images per CTA = gx * gy
+    int gx, gy;
     int wp;           // positions per padded row
     int q_first;      // padded position of output column 0 (the first real pixel)
     int r_first;      // shared-memory row that holds position q_first: q_first rounded up to a multiple of 8, so
