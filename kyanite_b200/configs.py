@@ -206,56 +206,110 @@ def bert_encoder(layers: int = 12, hidden: int = 768, heads: int = 12, ffn: int 
     return g, make_inputs
 
 
+def llama_weights(layers: int, d_model: int, heads: int, ffn: int, vocab: int, seed: int = 10) -> dict:
+    """The decoder's weights, N(0, 0.02) (norm gains 1 + N(0, 0.02)), drawn in a fixed order so that every
+    builder of the same model (whole, or one tensor-parallel rank's slice) sees the same numbers."""
+    seeds = _Seeds(seed)
+    w = {"table": _normal(seeds, (vocab, d_model)), "layers": []}
+    for _ in range(layers):
+        layer = {}
+        layer["norm1"] = np.ones((1, 1, d_model), np.float32) + _normal(seeds, (1, 1, d_model))
+        for name in ("wq", "wk", "wv", "wo"):
+            layer[name] = _normal(seeds, (d_model, d_model))
+        layer["norm2"] = np.ones((1, 1, d_model), np.float32) + _normal(seeds, (1, 1, d_model))
+        layer["gate"] = _normal(seeds, (ffn, d_model))
+        layer["up"] = _normal(seeds, (ffn, d_model))
+        layer["down"] = _normal(seeds, (d_model, ffn))
+        w["layers"].append(layer)
+    w["norm_f"] = np.ones((1, 1, d_model), np.float32) + _normal(seeds, (1, 1, d_model))
+    w["lm_head"] = _normal(seeds, (vocab, d_model))
+    return w
+
+
+def rope_tables(seq: int, head_dim: int, rope_base: float):
+    """cos / sin tables [1, seq, 1, head_dim] of the half-split rotary embedding."""
+    inv_freq = rope_base ** (-np.arange(0, head_dim, 2, dtype=np.float64) / head_dim)
+    ang = np.arange(seq, dtype=np.float64)[:, None] * inv_freq[None, :]            # [seq, hd/2]
+    cos = np.concatenate([np.cos(ang), np.cos(ang)], 1).astype(np.float32).reshape(1, seq, 1, head_dim)
+    sin = np.concatenate([np.sin(ang), np.sin(ang)], 1).astype(np.float32).reshape(1, seq, 1, head_dim)
+    return cos, sin
+
+
+class LlamaBlocks:
+    """The pieces of the LLaMA-shaped decoder as graph fragments, shared by `llama_decoder` and by the
+    tensor-parallel builder (kyanite_b200/tensor_parallel.py), which uses them on weight slices."""
+
+    def __init__(self, g: Graph, d_model: int, head_dim: int, seq: int, eps: float, rope_base: float):
+        self.g, self.d_model, self.hd, self.seq, self.eps = g, d_model, head_dim, seq, eps
+        cos, sin = rope_tables(seq, head_dim, rope_base)
+        self.cos, self.sin = g.constant_tensor(cos), g.constant_tensor(sin)
+        self.mask = g.constant_tensor(np.triu(np.full((seq, seq), -np.inf, np.float32), 1).reshape(1, seq, seq))
+        self.rows = BATCH * seq
+
+    def linear(self, x: Value, w: np.ndarray) -> Value:
+        return self.g.linear(x, self.g.constant_tensor(np.ascontiguousarray(w)))
+
+    def rmsnorm(self, t: Value, gain: np.ndarray) -> Value:
+        """t [B, seq, d_model]: composed from pow / mean / sqrt / div (the IR has no RMSNorm)."""
+        from .graph import BinaryOp, ReduceOp, UnaryOp
+        g = self.g
+        ms = g.view(g.reduce(g.pow(t, g.scalar(2.0)), [2], ReduceOp.MEAN), shape(BATCH, self.seq, 1))
+        rms = g.unary(UnaryOp.SQRT, g.add(ms, g.scalar(self.eps)))
+        return g.mul(g.binary(BinaryOp.DIV, t, rms), g.constant_tensor(gain))
+
+    def rope(self, t: Value, heads: int) -> Value:
+        """t [B*seq, heads*hd] -> rotated, same shape (half-split: pairs (i, i + hd/2))."""
+        from .graph import SliceRange, UnaryOp
+        g, hd = self.g, self.hd
+        t4 = g.view(t, shape(BATCH, self.seq, heads, hd))
+        lo = g.slice(t4, 3, SliceRange(0, hd // 2))
+        hi = g.slice(t4, 3, SliceRange(hd // 2, hd))
+        rot = g.concat([g.unary(UnaryOp.NEG, hi), lo], 3)
+        out = g.add(g.mul(t4, self.cos), g.mul(rot, self.sin))
+        return g.view(out, shape(self.rows, heads * hd))
+
+    def attention_partial(self, x: Value, layer: dict, head_slice: slice, heads: int) -> Value:
+        """Pre-norm causal self-attention over the heads in `head_slice`, projected by the matching
+        columns of W_o: [B, seq, d_model].  With all heads this is the whole attention output; with a
+        slice, the slices of all ranks sum to it (column-parallel Q/K/V, row-parallel O)."""
+        g, hd = self.g, self.hd
+        cols = slice(head_slice.start * hd, head_slice.stop * hd)
+        h = g.view(self.rmsnorm(x, layer["norm1"]), shape(self.rows, self.d_model))
+        q = self.rope(self.linear(h, layer["wq"][cols]), heads)
+        k = self.rope(self.linear(h, layer["wk"][cols]), heads)
+        v = self.linear(h, layer["wv"][cols])
+        ctx = _attention(g, q, k, v, self.seq, self.seq, heads, hd, BATCH, mask=self.mask)
+        return g.view(self.linear(ctx, layer["wo"][:, cols]), shape(BATCH, self.seq, self.d_model))
+
+    def ffn_partial(self, x: Value, layer: dict, ffn_slice: slice) -> Value:
+        """Pre-norm SwiGLU feed-forward over the hidden units in `ffn_slice`: [B, seq, d_model]
+        (column-parallel gate/up, row-parallel down)."""
+        g = self.g
+        h = g.view(self.rmsnorm(x, layer["norm2"]), shape(self.rows, self.d_model))
+        gate = self.linear(h, layer["gate"][ffn_slice])
+        up = self.linear(h, layer["up"][ffn_slice])
+        act = g.mul(g.mul(gate, g.sigmoid(gate)), up)
+        return g.view(self.linear(act, layer["down"][:, ffn_slice]), shape(BATCH, self.seq, self.d_model))
+
+    def logits(self, x: Value, gain: np.ndarray, lm_head: np.ndarray) -> Value:
+        h = self.g.view(self.rmsnorm(x, gain), shape(self.rows, self.d_model))
+        return self.g.view(self.linear(h, lm_head), shape(BATCH, self.seq, lm_head.shape[0]))
+
+
 def llama_decoder(layers: int = 32, d_model: int = 4096, heads: int = 32, ffn: int = 11008, vocab: int = 32000,
                   seq: int = 2048, eps: float = 1e-6, rope_base: float = 10000.0, seed: int = 10) -> Tuple[Graph, Inputs]:
     """LLaMA-shaped decoder prefill in f32 (half storage is not built): RMSNorm composed from
     pow / mean / sqrt / div, rotary embedding from constant cos/sin tables with half-split slices,
     additive causal mask, SwiGLU, tied-shape lm head.  Input: token ids [B, seq] (i32)."""
-    from .graph import BinaryOp, ReduceOp, SliceRange, UnaryOp
     g = Graph()
-    seeds = _Seeds(seed)
-    hd = d_model // heads
+    w = llama_weights(layers, d_model, heads, ffn, vocab, seed)
+    blocks = LlamaBlocks(g, d_model, d_model // heads, seq, eps, rope_base)
     ids = g.input(shape(BATCH, seq), DType.I32)
-    table = g.constant_tensor(_normal(seeds, (vocab, d_model)))
-    x = g.view(g.gather(table, 0, g.flatten(ids, 0)), shape(BATCH, seq, d_model))
-
-    inv_freq = rope_base ** (-np.arange(0, hd, 2, dtype=np.float64) / hd)
-    ang = np.arange(seq, dtype=np.float64)[:, None] * inv_freq[None, :]            # [seq, hd/2]
-    cos = g.constant_tensor(np.concatenate([np.cos(ang), np.cos(ang)], 1).astype(np.float32).reshape(1, seq, 1, hd))
-    sin = g.constant_tensor(np.concatenate([np.sin(ang), np.sin(ang)], 1).astype(np.float32).reshape(1, seq, 1, hd))
-    mask = g.constant_tensor(np.triu(np.full((seq, seq), -np.inf, np.float32), 1).reshape(1, seq, seq))
-
-    def rmsnorm(t):
-        ms = g.reduce(g.pow(t, g.scalar(2.0)), [2], ReduceOp.MEAN)
-        ms = g.view(ms, shape(BATCH, seq, 1))
-        rms = g.unary(UnaryOp.SQRT, g.add(ms, g.scalar(eps)))
-        w = g.constant_tensor(np.ones((1, 1, d_model), np.float32) + _normal(seeds, (1, 1, d_model)))
-        return g.mul(g.binary(BinaryOp.DIV, t, rms), w)
-
-    def rope(t):   # t [B*seq, d_model] -> rotated, same shape
-        t4 = g.view(t, shape(BATCH, seq, heads, hd))
-        lo = g.slice(t4, 3, SliceRange(0, hd // 2))
-        hi = g.slice(t4, 3, SliceRange(hd // 2, hd))
-        neg_hi = g.unary(UnaryOp.NEG, hi)
-        rot = g.concat([neg_hi, lo], 3)
-        out = g.add(g.mul(t4, cos), g.mul(rot, sin))
-        return g.view(out, shape(BATCH * seq, d_model))
-
-    rows = BATCH * seq
-    for _ in range(layers):
-        h = g.view(rmsnorm(x), shape(rows, d_model))
-        q = rope(_dense(g, seeds, h, d_model, d_model, bias=False))
-        k = rope(_dense(g, seeds, h, d_model, d_model, bias=False))
-        v = _dense(g, seeds, h, d_model, d_model, bias=False)
-        ctx = _attention(g, q, k, v, seq, seq, heads, hd, BATCH, mask=mask)
-        x = g.add(x, g.view(_dense(g, seeds, ctx, d_model, d_model, bias=False), shape(BATCH, seq, d_model)))
-        h = g.view(rmsnorm(x), shape(rows, d_model))
-        gate = _dense(g, seeds, h, d_model, ffn, bias=False)
-        up = _dense(g, seeds, h, d_model, ffn, bias=False)
-        act = g.mul(g.mul(gate, g.sigmoid(gate)), up)
-        x = g.add(x, g.view(_dense(g, seeds, act, ffn, d_model, bias=False), shape(BATCH, seq, d_model)))
-    logits = _dense(g, seeds, g.view(rmsnorm(x), shape(rows, d_model)), d_model, vocab, bias=False)
-    g.output(g.view(logits, shape(BATCH, seq, vocab)))
+    x = g.view(g.gather(g.constant_tensor(w["table"]), 0, g.flatten(ids, 0)), shape(BATCH, seq, d_model))
+    for layer in w["layers"]:
+        x = g.add(x, blocks.attention_partial(x, layer, slice(0, heads), heads))
+        x = g.add(x, blocks.ffn_partial(x, layer, slice(0, ffn)))
+    g.output(blocks.logits(x, w["norm_f"], w["lm_head"]))
 
     def make_inputs(batch_size: int, seed: int = 1):
         return [_rng(seed).integers(0, vocab, (batch_size, seq)).astype(np.int32)]

@@ -1,0 +1,171 @@
+"""Tensor-parallel execution of the LLaMA-shaped decoder: one process per GPU, NCCL all-reduce after the
+row-parallel projections.  This has no counterpart in the reference (which runs one graph on one device);
+it is built on top of the executor, not inside it: every rank runs ordinary graphs through `CudaExecutor`,
+and the only cross-rank operations are one all-reduce per attention block and per feed-forward block and
+one all-gather of the logits.
+
+Partitioning (world size W, rank r):
+* attention: heads `[r*H/W, (r+1)*H/W)`.  W_q, W_k, W_v are split by output rows (column-parallel), RoPE,
+  scores, softmax and the context product are local per head, W_o is split by input columns
+  (row-parallel), so each rank produces a partial `[B, seq, d_model]` sum;
+* feed-forward: hidden units `[r*F/W, (r+1)*F/W)`: gate and up column-parallel, down row-parallel, again a
+  partial sum;
+* RMSNorm, the residual stream, the embedding table and the final norm are replicated;
+* lm head: vocabulary rows `[r*V/W, (r+1)*V/W)`, logits all-gathered along the vocabulary axis.
+
+The decoder is cut into `2 * layers + 1` graph segments at the all-reduce points.  Segment k takes the
+residual stream `x` and the reduced sum `s` of the previous block, forms `x + s` (replicated arithmetic,
+bit-identical on every rank) and returns it together with this rank's partial sum of the next block:
+
+    ids      -> seg[0]   -> x0,   p0 (attention 0)        s0 = all_reduce(p0)
+    x0, s0   -> seg[1]   -> x1,   p1 (feed-forward 0)      s1 = all_reduce(p1)
+    ...
+    x, s     -> seg[2L]  -> logits[:, :, vocab slice]      logits = all_gather(...)
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, List, Optional, Sequence
+
+import numpy as np
+
+from .configs import LlamaBlocks, llama_weights
+from .graph import BATCH, DType, Graph, shape
+
+__all__ = ["LlamaShape", "llama_segments", "TorchComm", "LocalComm", "TensorParallelLlama"]
+
+
+@dataclass(frozen=True)
+class LlamaShape:
+    layers: int = 32
+    d_model: int = 4096
+    heads: int = 32
+    ffn: int = 11008
+    vocab: int = 32000
+    seq: int = 2048
+    eps: float = 1e-6
+    rope_base: float = 10000.0
+    seed: int = 10
+
+
+def _even_slice(total: int, rank: int, world: int, what: str) -> slice:
+    if total % world != 0:
+        raise ValueError(f"{what} ({total}) is not divisible by the tensor-parallel size {world}")
+    step = total // world
+    return slice(rank * step, (rank + 1) * step)
+
+
+def llama_segments(cfg: LlamaShape, rank: int, world: int) -> List[Graph]:
+    """The graphs rank `rank` of `world` runs, in order (see the module docstring)."""
+    if not (0 <= rank < world):
+        raise ValueError(f"rank {rank} outside world of size {world}")
+    w = llama_weights(cfg.layers, cfg.d_model, cfg.heads, cfg.ffn, cfg.vocab, cfg.seed)
+    head_slice = _even_slice(cfg.heads, rank, world, "head count")
+    ffn_slice = _even_slice(cfg.ffn, rank, world, "feed-forward width")
+    vocab_slice = _even_slice(cfg.vocab, rank, world, "vocabulary")
+    local_heads = head_slice.stop - head_slice.start
+    hd = cfg.d_model // cfg.heads
+    stream = shape(BATCH, cfg.seq, cfg.d_model)
+
+    def begin():
+        g = Graph()
+        return g, LlamaBlocks(g, cfg.d_model, hd, cfg.seq, cfg.eps, cfg.rope_base)
+
+    segments: List[Graph] = []
+    # segment 0: embedding, attention of layer 0
+    g, blocks = begin()
+    ids = g.input(shape(BATCH, cfg.seq), DType.I32)
+    x = g.view(g.gather(g.constant_tensor(w["table"]), 0, g.flatten(ids, 0)), stream)
+    g.output(x)
+    g.output(blocks.attention_partial(x, w["layers"][0], head_slice, local_heads))
+    segments.append(g)
+    for li, layer in enumerate(w["layers"]):
+        # feed-forward of layer li
+        g, blocks = begin()
+        x = g.add(g.input(stream), g.input(stream))
+        g.output(x)
+        g.output(blocks.ffn_partial(x, layer, ffn_slice))
+        segments.append(g)
+        if li + 1 < cfg.layers:
+            # attention of layer li + 1
+            g, blocks = begin()
+            x = g.add(g.input(stream), g.input(stream))
+            g.output(x)
+            g.output(blocks.attention_partial(x, w["layers"][li + 1], head_slice, local_heads))
+            segments.append(g)
+    # last segment: final norm and this rank's slice of the lm head
+    g, blocks = begin()
+    x = g.add(g.input(stream), g.input(stream))
+    g.output(blocks.logits(x, w["norm_f"], w["lm_head"][vocab_slice]))
+    segments.append(g)
+    return segments
+
+
+class LocalComm:
+    """World of size 1: the collectives are identities."""
+    rank, world = 0, 1
+
+    def all_reduce_sum(self, a: np.ndarray) -> np.ndarray:
+        return a
+
+    def all_gather_last_axis(self, a: np.ndarray) -> np.ndarray:
+        return a
+
+
+class TorchComm:
+    """Collectives through an initialised `torch.distributed` process group: NCCL when `device` is a CUDA
+    device (the arrays cross to that GPU, are reduced over NVLink and come back), gloo on CPU."""
+
+    def __init__(self, device: Optional[str] = None):
+        import torch
+        import torch.distributed as dist
+        if not dist.is_initialized():
+            raise RuntimeError("torch.distributed is not initialised")
+        self.torch, self.dist = torch, dist
+        self.rank, self.world = dist.get_rank(), dist.get_world_size()
+        self.device = torch.device(device) if device is not None else torch.device("cpu")
+
+    def all_reduce_sum(self, a: np.ndarray) -> np.ndarray:
+        t = self.torch.from_numpy(np.ascontiguousarray(a)).to(self.device)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM)
+        return t.cpu().numpy()
+
+    def all_gather_last_axis(self, a: np.ndarray) -> np.ndarray:
+        t = self.torch.from_numpy(np.ascontiguousarray(a)).to(self.device)
+        parts = [self.torch.empty_like(t) for _ in range(self.world)]
+        self.dist.all_gather(parts, t)
+        return self.torch.cat(parts, dim=-1).cpu().numpy()
+
+
+class TensorParallelLlama:
+    """One rank of the tensor-parallel decoder.
+
+    `prepare(graph, batch_size)` returns a callable `inputs -> outputs` for one segment: on a GPU
+    `lambda g, b: CudaExecutor(device, g, b).evaluate`; tests on CPU pass an evaluator of their own."""
+
+    def __init__(self, cfg: LlamaShape, batch_size: int, comm, prepare: Callable[[Graph, int], Callable]):
+        self.cfg, self.batch_size, self.comm = cfg, batch_size, comm
+        self.segments = [prepare(g, batch_size) for g in llama_segments(cfg, comm.rank, comm.world)]
+        self.all_reduces = 0
+
+    def forward(self, ids: np.ndarray) -> np.ndarray:
+        """Token ids [B, seq] (identical on every rank) -> logits [B, seq, vocab] (identical on every rank)."""
+        x, partial = self.segments[0]([np.ascontiguousarray(ids, dtype=np.int32)])
+        for seg in self.segments[1:-1]:
+            s = self.comm.all_reduce_sum(partial)
+            self.all_reduces += 1
+            x, partial = seg([x, s])
+        s = self.comm.all_reduce_sum(partial)
+        self.all_reduces += 1
+        (local_logits,) = self.segments[-1]([x, s])
+        return self.comm.all_gather_last_axis(local_logits)
+
+
+def cuda_prepare(device_index: int, **executor_kwargs) -> Callable[[Graph, int], Callable]:
+    """`prepare` for `TensorParallelLlama` on CUDA device `device_index`."""
+    from .executor import CudaExecutor
+
+    def prepare(graph: Graph, batch_size: int):
+        return CudaExecutor(device_index, graph, batch_size, **executor_kwargs).evaluate
+
+    return prepare
