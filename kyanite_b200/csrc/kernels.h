@@ -46,6 +46,10 @@ struct ScalarParams {
     uint8_t store_operand[SCALAR_MAX_OPERANDS];
     uint8_t store_slot[SCALAR_MAX_OPERANDS];
     ScalarInstr instr[SCALAR_MAX_INSTR];
+    // vec4 == 2: the same program as an accumulator program (built by the planner's allocate_registers, which
+    // documents the micro-op format); `n_regs` = number of spill slots it uses (0..8).
+    int32_t n_micro, n_regs;
+    ScalarInstr micro[SCALAR_MAX_INSTR + 2 * SCALAR_MAX_OPERANDS];
 };
 
 // ---- reduce: replaces autokernel/reduce.{rs,cu}

@@ -10,6 +10,8 @@
 //                          innermost axis: 128-bit loads and stores, four elements per iteration.
 #include <cuda_runtime.h>
 
+#include <mutex>
+
 #include "../kernels.h"
 #include "../scalar_ops.h"
 
@@ -118,11 +120,198 @@ int grid_for(int64_t work_items) {
     return (int)blocks;
 }
 
+// Accumulator-program variant of the 128-bit kernel.  The slot arrays above are indexed with run-time
+// indices and therefore live in local memory, which makes every instruction of the program a round trip
+// through L1, and selecting among registers with switches costs more instructions than the arithmetic.
+// Here every micro-op leaves its result in an accumulator that IS a register; only values that are needed
+// again later are also copied to a numbered spill slot in shared memory ([slot][position][thread] float4:
+// conflict-free 128-bit accesses, and the run-time slot number is just an address).  Every thread carries V
+// consecutive float4 positions through the program; all loads of the program are issued first.
+constexpr int kRegOperands = 4;
+
+template <int V>
+struct Vec {
+    float4 v[V];
+};
+
+template <int V, typename F>
+__device__ __forceinline__ void map1(Vec<V>& acc, const Vec<V>& a, F f) {
+#pragma unroll
+    for (int i = 0; i < V; i++) acc.v[i] = make_float4(f(a.v[i].x), f(a.v[i].y), f(a.v[i].z), f(a.v[i].w));
+}
+template <int V, typename F>
+__device__ __forceinline__ void map2(Vec<V>& acc, const Vec<V>& a, const Vec<V>& b, F f) {
+#pragma unroll
+    for (int i = 0; i < V; i++)
+        acc.v[i] = make_float4(f(a.v[i].x, b.v[i].x), f(a.v[i].y, b.v[i].y), f(a.v[i].z, b.v[i].z), f(a.v[i].w, b.v[i].w));
+}
+
+template <int V>
+__device__ __forceinline__ void unary_v(UnaryOp op, Vec<V>& acc, const Vec<V>& a) {
+    switch (op) {   // uniform: one branch per micro-op, the loops over positions and lanes are inside
+        case UnaryOp::Abs: map1(acc, a, [](float x) { return fabsf(x); }); break;
+        case UnaryOp::Neg: map1(acc, a, [](float x) { return -x; }); break;
+        case UnaryOp::Exp: map1(acc, a, [](float x) { return expf(x); }); break;
+        case UnaryOp::Sqrt: map1(acc, a, [](float x) { return sqrtf(x); }); break;
+        case UnaryOp::Sigmoid: map1(acc, a, [](float x) { return 1.0f / (1.0f + expf(-x)); }); break;
+        case UnaryOp::Tanh: map1(acc, a, [](float x) { return tanhf(x); }); break;
+        case UnaryOp::Erf: map1(acc, a, [](float x) { return erff(x); }); break;
+        default: map1(acc, a, [op](float x) { return f32_unary(op, x); }); break;
+    }
+}
+template <int V>
+__device__ __forceinline__ void binary_v(BinaryOp op, Vec<V>& acc, const Vec<V>& a, const Vec<V>& b) {
+    switch (op) {
+        case BinaryOp::Add: map2(acc, a, b, [](float x, float y) { return x + y; }); break;
+        case BinaryOp::Sub: map2(acc, a, b, [](float x, float y) { return x - y; }); break;
+        case BinaryOp::Mul: map2(acc, a, b, [](float x, float y) { return x * y; }); break;
+        case BinaryOp::Div: map2(acc, a, b, [](float x, float y) { return x / y; }); break;
+        case BinaryOp::Min: map2(acc, a, b, [](float x, float y) { return fminf(x, y); }); break;
+        case BinaryOp::Max: map2(acc, a, b, [](float x, float y) { return fmaxf(x, y); }); break;
+        default: map2(acc, a, b, [](float x, float y) { return powf(x, y); }); break;
+    }
+}
+
+template <int V, bool RANK1>
+__global__ void __launch_bounds__(kThreads) scalar_acc_kernel(const __grid_constant__ ScalarParams p) {
+    extern __shared__ float4 spill[];   // [slot][position][thread]
+    const int last = p.rank - 1;
+    const uint32_t inner_v = (uint32_t)(p.dims[last] / (4 * V));   // groups of V float4 along the innermost axis
+    const uint32_t total_v = (uint32_t)(p.total / (4 * V));
+    const uint32_t step = gridDim.x * blockDim.x;
+    uint32_t inner_bytes[kRegOperands];   // bytes between two consecutive float4 positions (0 = broadcast)
+#pragma unroll
+    for (int o = 0; o < kRegOperands; o++) inner_bytes[o] = o < p.n_operands && p.strides[o][last] != 0 ? 16u : 0u;
+    float4* const my_spill = spill + threadIdx.x;
+    auto slot_read = [&](int slot, Vec<V>& out) {
+#pragma unroll
+        for (int v = 0; v < V; v++) out.v[v] = my_spill[(slot * V + v) * kThreads];
+    };
+
+    for (uint32_t g = blockIdx.x * blockDim.x + threadIdx.x; g < total_v; g += step) {
+        uint32_t off[kRegOperands];   // element offset of the group's first position
+        if (RANK1) {
+#pragma unroll
+            for (int o = 0; o < kRegOperands; o++) off[o] = inner_bytes[o] ? g * (uint32_t)(4 * V) : 0u;
+        } else {
+            uint32_t rem = g / inner_v;
+            const uint32_t inner = (g - rem * inner_v) * (uint32_t)(4 * V);
+#pragma unroll
+            for (int o = 0; o < kRegOperands; o++) off[o] = inner_bytes[o] ? inner : 0u;
+            for (int d = last - 1; d >= 0; d--) {
+                const uint32_t dim = (uint32_t)p.dims[d];
+                const uint32_t q = rem / dim;
+                const uint32_t i = rem - q * dim;
+                rem = q;
+#pragma unroll
+                for (int o = 0; o < kRegOperands; o++)
+                    if (o < p.n_operands) off[o] += i * (uint32_t)p.strides[o][d];
+            }
+        }
+        const char* base[kRegOperands];
+#pragma unroll
+        for (int o = 0; o < kRegOperands; o++) base[o] = o < p.n_operands ? (const char*)p.ptr[o] + (size_t)off[o] * 4u : nullptr;
+        auto operand = [&](int o, uint32_t* stride_bytes) -> const char* {
+            switch (o) {
+                case 0: *stride_bytes = inner_bytes[0]; return base[0];
+                case 1: *stride_bytes = inner_bytes[1]; return base[1];
+                case 2: *stride_bytes = inner_bytes[2]; return base[2];
+                default: *stride_bytes = inner_bytes[3]; return base[3];
+            }
+        };
+
+        Vec<V> acc;
+#pragma unroll
+        for (int v = 0; v < V; v++) acc.v[v] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int k = 0; k < p.n_micro; k++) {
+            const ScalarInstr in = p.micro[k];
+            Vec<V> a = acc, b = acc;
+            if (in.kind != 0 && in.kind != 3 && in.a != 255) slot_read(in.a, a);
+            switch (in.kind) {
+                case 0:
+#pragma unroll
+                    for (int v = 0; v < V; v++) acc.v[v] = splat(bits_to_f32(in.imm));
+                    break;
+                case 1: unary_v<V>((UnaryOp)in.op, acc, a); break;
+                case 2:
+                    if (in.b != 255) slot_read(in.b, b);
+                    binary_v<V>((BinaryOp)in.op, acc, a, b);
+                    break;
+                case 3: {
+                    uint32_t sb;
+                    const char* src = operand(in.a, &sb);
+                    if (sb) {
+#pragma unroll
+                        for (int v = 0; v < V; v++) acc.v[v] = __ldg((const float4*)(src + v * 16));
+                    } else {
+                        const float4 x = splat(__ldg((const float*)src));
+#pragma unroll
+                        for (int v = 0; v < V; v++) acc.v[v] = x;
+                    }
+                    break;
+                }
+                case 4: {
+                    uint32_t sb;
+                    char* dst = const_cast<char*>(operand(in.b, &sb));
+#pragma unroll
+                    for (int v = 0; v < V; v++) *(float4*)(dst + v * 16) = a.v[v];
+                    break;
+                }
+                case 5:
+#pragma unroll
+                    for (int v = 0; v < V; v++) b.v[v] = splat(bits_to_f32(in.imm));
+                    binary_v<V>((BinaryOp)in.op, acc, a, b);
+                    break;
+                default:
+#pragma unroll
+                    for (int v = 0; v < V; v++) b.v[v] = splat(bits_to_f32(in.imm));
+                    binary_v<V>((BinaryOp)in.op, acc, b, a);
+                    break;
+            }
+            if (in.pad != 255) {
+#pragma unroll
+                for (int v = 0; v < V; v++) my_spill[((int)in.pad * V + v) * kThreads] = acc.v[v];
+            }
+        }
+    }
+}
+
+template <int V>
+int launch_acc(const ScalarParams& p, cudaStream_t stream) {
+    const int64_t groups = p.total / (4 * V);
+    const int grid = grid_for(groups);
+    const size_t smem = (size_t)p.n_regs * V * kThreads * sizeof(float4);
+    static std::mutex mu;
+    static bool done[64] = {false};
+    int device = 0;
+    cudaGetDevice(&device);
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (device >= 0 && device < 64 && !done[device]) {
+            cudaError_t e1 = cudaFuncSetAttribute(scalar_acc_kernel<V, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024);
+            cudaError_t e2 = cudaFuncSetAttribute(scalar_acc_kernel<V, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024);
+            if (e1 != cudaSuccess) return (int)e1;
+            if (e2 != cudaSuccess) return (int)e2;
+            done[device] = true;
+        }
+    }
+    if (p.rank == 1) scalar_acc_kernel<V, true><<<grid, kThreads, smem, stream>>>(p);
+    else scalar_acc_kernel<V, false><<<grid, kThreads, smem, stream>>>(p);
+    return (int)cudaGetLastError();
+}
+
 }  // namespace
 
 int launch_scalar(const ScalarParams& p, cudaStream_t stream) {
     if (p.total == 0) return 0;
-    if (p.vec4) {
+    if (p.vec4 == 2) {
+        // V consecutive float4 positions per thread: as many as the innermost extent and the spill slots
+        // (n_regs * V * 4 KB of shared memory per block) allow
+        const int64_t inner4 = p.dims[p.rank - 1] / 4;
+        if (inner4 % 4 == 0 && p.n_regs <= 4) return launch_acc<4>(p, stream);
+        if (inner4 % 2 == 0) return launch_acc<2>(p, stream);
+        return launch_acc<1>(p, stream);
+    } else if (p.vec4) {
         const int64_t total4 = p.total >> 2;
         if (total4 < (1ll << 31)) scalar_vec4_kernel<uint32_t><<<grid_for(total4), kThreads, 0, stream>>>(p);
         else scalar_vec4_kernel<uint64_t><<<grid_for(total4), kThreads, 0, stream>>>(p);

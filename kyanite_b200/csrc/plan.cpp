@@ -304,8 +304,148 @@ class Planner {
             }
         }
         p.vec4 = vec ? 1 : 0;
+        // the accumulator-program kernel computes element offsets in 32 bits and keeps four operand addresses
+        // in registers: non-negative strides, no operand may reach 2^31 elements from its start
+        bool small = vec && total < (1ll << 31) && p.n_operands <= 4;
+        for (int o = 0; o < p.n_operands && small; o++) {
+            int64_t reach = 0;
+            for (int d = 0; d < p.rank; d++) {
+                if (strides[o][d] < 0) small = false;
+                reach += (dims[d] - 1) * strides[o][d];
+            }
+            if (reach >= (1ll << 31) - 16) small = false;
+        }
+        if (small && allocate_registers(p)) p.vec4 = 2;
         push_step(std::move(s));
     }
+
+    // Turns the slot program into an accumulator program (ScalarParams::micro).  Every micro-op leaves its
+    // result in the accumulator; an operand is read from the accumulator when it was computed by the
+    // micro-op just before, from a constant folded into the operation, or else from a numbered spill slot
+    // that its defining micro-op copies the result to.  All loads come first (so they are in flight
+    // together), slots are recycled after a value's last use.  False if more than 8 slots would be live.
+    //   kind 0 acc = imm                      3 acc = load operand `a`
+    //   kind 1 acc = unary(A)                 4 store A -> operand `b`
+    //   kind 2 acc = binary(A, B)             5 acc = binary(A, imm)     6 acc = binary(imm, A)
+    // A / B: `a` / `b` = 255 means the accumulator, otherwise a slot; `pad` = slot to copy the result to, or 255.
+    static bool allocate_registers(ScalarParams& p) {
+        const int kAcc = 255;
+        const int n_values = p.n_loads + p.n_instr;
+        auto is_const = [&](int v) { return v >= p.n_loads && p.instr[v - p.n_loads].kind == 0; };
+        struct Op {
+            ScalarInstr m;
+            int result = -1, src_a = -1, src_b = -1;   // value ids
+        };
+        std::vector<Op> ops;
+        std::vector<int> const_op(n_values, -1);   // constant used as a value -> op that materialises it
+        auto materialise_const = [&](int v) {
+            if (const_op[v] >= 0) return;
+            Op o;
+            o.m.kind = 0;
+            o.m.imm = p.instr[v - p.n_loads].imm;
+            o.result = v;
+            const_op[v] = (int)ops.size();
+            ops.push_back(o);
+        };
+        // pass 1: order of the micro-ops
+        for (int l = 0; l < p.n_loads; l++) {
+            Op o;
+            o.m.kind = 3;
+            o.m.a = p.load_operand[l];
+            o.result = l;
+            ops.push_back(o);
+        }
+        for (int k = 0; k < p.n_instr; k++) {
+            const ScalarInstr& in = p.instr[k];
+            if (in.kind == 0) continue;
+            Op o;
+            o.m = in;
+            o.result = p.n_loads + k;
+            if (in.kind == 1) {
+                if (is_const(in.a)) materialise_const(in.a);
+                o.src_a = in.a;
+            } else if (is_const(in.b) && !is_const(in.a)) {
+                o.m.kind = 5;
+                o.m.imm = p.instr[in.b - p.n_loads].imm;
+                o.src_a = in.a;
+                // x ^ 2 is the square: exact, and far cheaper than the general power function
+                if (in.op == (uint8_t)BinaryOp::Pow && in.dtype == (uint8_t)DType::F32 && o.m.imm == 0x40000000ull) {
+                    o.m.kind = 2;
+                    o.m.op = (uint8_t)BinaryOp::Mul;
+                    o.src_b = in.a;
+                }
+            } else if (is_const(in.a) && !is_const(in.b)) {
+                o.m.kind = 6;
+                o.m.imm = p.instr[in.a - p.n_loads].imm;
+                o.src_a = in.b;
+            } else {
+                if (is_const(in.a)) materialise_const(in.a);
+                if (is_const(in.b)) materialise_const(in.b);
+                o.src_a = in.a;
+                o.src_b = in.b;
+            }
+            ops.push_back(o);
+        }
+        for (int st = 0; st < p.n_stores; st++) {
+            const int v = p.store_slot[st];
+            if (is_const(v)) materialise_const(v);
+            Op o;
+            o.m.kind = 4;
+            o.m.b = p.store_operand[st];
+            o.src_a = v;
+            ops.push_back(o);
+        }
+        if ((int)ops.size() > SCALAR_MAX_INSTR + 2 * SCALAR_MAX_OPERANDS) return false;
+        // pass 2: a value needs a slot unless its only uses are operands of the op right after its definition
+        std::vector<int> def(n_values, -1), last_use(n_values, -1);
+        std::vector<uint8_t> needs_slot(n_values, 0);
+        for (int i = 0; i < (int)ops.size(); i++)
+            if (ops[i].result >= 0) def[ops[i].result] = i;
+        for (int i = 0; i < (int)ops.size(); i++)
+            for (int v : {ops[i].src_a, ops[i].src_b}) {
+                if (v < 0) continue;
+                if (def[v] < 0) return false;   // (cannot happen: every used value has a defining op)
+                last_use[v] = std::max(last_use[v], i);
+                if (i != def[v] + 1) needs_slot[v] = 1;
+            }
+        std::vector<int> slot_of(n_values, -1);
+        std::vector<int> free_slots;
+        std::vector<std::vector<int>> expiring(ops.size() + 1);
+        int n_regs = 0;
+        for (int i = 0; i < (int)ops.size(); i++) {
+            // operands are read before the result is written: slots whose last reader is this op are free again
+            for (int v : expiring[i]) free_slots.push_back(slot_of[v]);
+            Op& o = ops[i];
+            o.m.pad = (uint16_t)kAcc;
+            auto where = [&](int v) -> int { return (i == def[v] + 1) ? kAcc : slot_of[v]; };
+            if (o.m.kind == 4) {
+                o.m.a = (uint8_t)where(o.src_a);
+            } else if (o.m.kind != 0 && o.m.kind != 3) {
+                if (o.src_a >= 0) o.m.a = (uint8_t)where(o.src_a);
+                if (o.src_b >= 0) o.m.b = (uint8_t)where(o.src_b);
+            }
+            const int v = o.result;
+            if (v >= 0 && needs_slot[v] && last_use[v] > i) {
+                int s;
+                if (!free_slots.empty()) {
+                    s = free_slots.back();
+                    free_slots.pop_back();
+                } else if (n_regs < 8) {
+                    s = n_regs++;
+                } else {
+                    return false;
+                }
+                slot_of[v] = s;
+                o.m.pad = (uint16_t)s;
+                expiring[last_use[v]].push_back(v);
+            }
+        }
+        p.n_micro = (int)ops.size();
+        for (int i = 0; i < p.n_micro; i++) p.micro[i] = ops[i].m;
+        p.n_regs = n_regs;
+        return true;
+    }
+
 
     void emit_copy(const PlanTensor& src, const PlanTensor& dst, int value) {
         ScalarBlock block;
