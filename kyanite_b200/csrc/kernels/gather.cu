@@ -37,10 +37,60 @@ __global__ void __launch_bounds__(256) gather_kernel(const __grid_constant__ Gat
     }
 }
 
+// Row gather (an embedding lookup): everything behind the gathered axis is one contiguous run of at
+// least 16 bytes in both tensors.  One warp per output row: the index is read once, the row moves as
+// 128-bit words.  `rows` = product of the extents up to and including the axis.
+__global__ void __launch_bounds__(256) gather_rows_kernel(const __grid_constant__ GatherParams p, int64_t rows, int row_vec4) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+    for (int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows; row += warps) {
+        int64_t rem = row, in_off = 0, out_off = 0;
+        bool valid = true;
+        for (int d = p.axis; d >= 0; d--) {
+            const int64_t dim = p.out_dims[d];
+            const int64_t q = rem / dim;
+            int64_t i = rem - q * dim;
+            rem = q;
+            out_off += i * p.out_strides[d];
+            if (d == p.axis) {
+                const uint64_t raw = load_bits(p.idx, (DType)p.idx_dtype, i * p.idx_stride);
+                valid = raw < (uint64_t)p.axis_in_size;
+                i = valid ? (int64_t)raw : 0;
+            }
+            in_off += i * p.in_strides[d];
+        }
+        const uint4* src = (const uint4*)((const char*)p.in + in_off * p.elem_size);
+        uint4* dst = (uint4*)((char*)p.out + out_off * p.elem_size);
+        const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+        for (int e = lane; e < row_vec4; e += 32) dst[e] = valid ? __ldg(src + e) : zero;
+    }
+}
+
 }  // namespace
 
 int launch_gather(const GatherParams& p, cudaStream_t stream) {
     if (p.total == 0) return 0;
+    {
+        // dense tail behind the axis?
+        int64_t inner = 1;
+        bool dense = true;
+        for (int d = p.rank - 1; d > p.axis; d--) {
+            dense = dense && p.in_strides[d] == inner && p.out_strides[d] == inner;
+            inner *= p.out_dims[d];
+        }
+        const int64_t row_bytes = inner * p.elem_size;
+        dense = dense && row_bytes >= 64 && row_bytes % 16 == 0 && row_bytes / 16 < (1 << 30) && ((uintptr_t)p.in & 15) == 0 &&
+                ((uintptr_t)p.out & 15) == 0;
+        for (int d = 0; d <= p.axis && dense; d++)
+            dense = (p.in_strides[d] * p.elem_size) % 16 == 0 && (p.out_strides[d] * p.elem_size) % 16 == 0;
+        if (dense) {
+            const int64_t rows = p.total / inner;
+            int64_t blocks = (rows + 7) / 8;
+            if (blocks > 148 * 16) blocks = 148 * 16;
+            gather_rows_kernel<<<(unsigned)blocks, 256, 0, stream>>>(p, rows, (int)(row_bytes / 16));
+            return (int)cudaGetLastError();
+        }
+    }
     int64_t blocks = (p.total + 255) / 256;
     if (blocks > 148 * 8) blocks = 148 * 8;
     const unsigned grid = (unsigned)blocks;

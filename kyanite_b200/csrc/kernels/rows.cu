@@ -181,6 +181,149 @@ __global__ void __launch_bounds__(256) layernorm_streaming_kernel(const __grid_c
     for (int64_t e = threadIdx.x; e < p.len; e += 256) out[e * p.out_axis_stride] = (ln_load(p, in0, in1, e) - mean) / denom;
 }
 
+// ------------------------------------------------------------------ 128-bit variants
+// Rows that are contiguous along the axis, a multiple of 4 long and 16-byte aligned (the planner's dense
+// tensors always are): every lane moves float4s, offsets are 32-bit, and the per-lane item count is exactly
+// what the row needs.  One warp (TPR = 32) or one block (TPR = 256) per row, the row stays in registers
+// between the statistics and the normalising pass: one read, one write.
+template <int TPR, int ITEMS4>
+__global__ void __launch_bounds__(256) softmax_vec4_kernel(const __grid_constant__ RowParams p) {
+    __shared__ float smem[8];
+    const int rows_per_block = blockDim.x / TPR;
+    const int64_t row = (int64_t)blockIdx.x * rows_per_block + threadIdx.x / TPR;
+    const int t = threadIdx.x % TPR;
+    const bool active = row < p.rows;
+    int64_t oi = 0, oo = 0;
+    if (active) decode_offsets(row, p.outer_rank, p.outer_dims, p.in_strides, p.out_strides, oi, oo);
+    const float4* in = (const float4*)(p.in0 + oi);
+    float4* out = (float4*)(p.out + oo);
+    const int len4 = (int)(p.len >> 2);
+
+    float4 v[ITEMS4];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < ITEMS4; i++) {
+        const int e = i * TPR + t;
+        if (active && e < len4) {
+            v[i] = __ldg(in + e);
+            v[i].x *= p.scale; v[i].y *= p.scale; v[i].z *= p.scale; v[i].w *= p.scale;
+        } else {
+            v[i] = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+        }
+        mx = fmaxf(mx, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
+    }
+    mx = row_reduce<TPR, true>(mx, smem);
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < ITEMS4; i++) {
+        v[i].x = expf(v[i].x - mx); v[i].y = expf(v[i].y - mx); v[i].z = expf(v[i].z - mx); v[i].w = expf(v[i].w - mx);
+        sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);     // padding lanes hold exp(-inf) = 0
+    }
+    sum = row_reduce<TPR, false>(sum, smem);
+    if (!active) return;
+#pragma unroll
+    for (int i = 0; i < ITEMS4; i++) {
+        const int e = i * TPR + t;
+        if (e < len4) out[e] = make_float4(v[i].x / sum, v[i].y / sum, v[i].z / sum, v[i].w / sum);
+    }
+}
+
+template <int TPR, int ITEMS4>
+__global__ void __launch_bounds__(256) layernorm_vec4_kernel(const __grid_constant__ RowParams p) {
+    __shared__ float smem[8];
+    const int rows_per_block = blockDim.x / TPR;
+    const int64_t row = (int64_t)blockIdx.x * rows_per_block + threadIdx.x / TPR;
+    const int t = threadIdx.x % TPR;
+    const bool active = row < p.rows;
+    int64_t oi = 0, oo = 0;
+    if (active) decode_offsets(row, p.outer_rank, p.outer_dims, p.in_strides, p.out_strides, oi, oo);
+    const float4* in0 = (const float4*)(p.in0 + oi);
+    const float4* in1 = p.in1 ? (const float4*)(p.in1 + oi) : nullptr;
+    float4* out = (float4*)(p.out + oo);
+    const int len4 = (int)(p.len >> 2);
+
+    float4 v[ITEMS4];
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < ITEMS4; i++) {
+        const int e = i * TPR + t;
+        v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (active && e < len4) {
+            const float4 a = __ldg(in0 + e);
+            v[i] = make_float4(p.alpha0 * a.x, p.alpha0 * a.y, p.alpha0 * a.z, p.alpha0 * a.w);
+            if (in1 != nullptr) {
+                const float4 b = __ldg(in1 + e);
+                v[i].x += p.alpha1 * b.x; v[i].y += p.alpha1 * b.y; v[i].z += p.alpha1 * b.z; v[i].w += p.alpha1 * b.w;
+            }
+        }
+        sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    }
+    const float n = (float)p.len;
+    const float mean = row_reduce<TPR, false>(sum, smem) / n;
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < ITEMS4; i++) {
+        const int e = i * TPR + t;
+        v[i].x -= mean; v[i].y -= mean; v[i].z -= mean; v[i].w -= mean;
+        if (e < len4) sq += (v[i].x * v[i].x + v[i].y * v[i].y) + (v[i].z * v[i].z + v[i].w * v[i].w);
+    }
+    const float var = row_reduce<TPR, false>(sq, smem) / n;
+    const float denom = sqrtf(var + p.eps);
+    if (!active) return;
+#pragma unroll
+    for (int i = 0; i < ITEMS4; i++) {
+        const int e = i * TPR + t;
+        if (e < len4) out[e] = make_float4(v[i].x / denom, v[i].y / denom, v[i].z / denom, v[i].w / denom);
+    }
+}
+
+// Sum / mean of f32 over a contiguous innermost axis: TPO threads per output, float4 loads.
+template <int TPO>
+__global__ void __launch_bounds__(256) reduce_f32_rows_kernel(const __grid_constant__ ReduceParams p) {
+    __shared__ float smem[8];
+    const int outs_per_block = 256 / TPO;
+    const int64_t o = (int64_t)blockIdx.x * outs_per_block + threadIdx.x / TPO;
+    const int t = threadIdx.x % TPO;
+    const bool active = o < p.n_out;
+    const ReduceOp rop = (ReduceOp)p.op;
+    int64_t oi = 0, oo = 0;
+    if (active) decode_offsets(o, p.kept_rank, p.kept_dims, p.kept_in_strides, p.kept_out_strides, oi, oo);
+    const float4* in = (const float4*)((const float*)p.in + oi);
+    const int len4 = (int)(p.n_red >> 2);
+    const bool is_max = rop == ReduceOp::Max, is_min = rop == ReduceOp::Min, is_prod = rop == ReduceOp::Prod;
+    float acc = is_max ? -INFINITY : is_min ? INFINITY : is_prod ? 1.f : 0.f;
+    if (active) {
+        // four independent accumulators keep several loads in flight per lane
+        float a0 = acc, a1 = acc, a2 = acc, a3 = acc;
+        for (int e = t; e < len4; e += TPO) {
+            const float4 x = __ldg(in + e);
+            if (is_max) { a0 = fmaxf(a0, x.x); a1 = fmaxf(a1, x.y); a2 = fmaxf(a2, x.z); a3 = fmaxf(a3, x.w); }
+            else if (is_min) { a0 = fminf(a0, x.x); a1 = fminf(a1, x.y); a2 = fminf(a2, x.z); a3 = fminf(a3, x.w); }
+            else if (is_prod) { a0 *= x.x; a1 *= x.y; a2 *= x.z; a3 *= x.w; }
+            else { a0 += x.x; a1 += x.y; a2 += x.z; a3 += x.w; }
+        }
+        if (is_max) acc = fmaxf(fmaxf(a0, a1), fmaxf(a2, a3));
+        else if (is_min) acc = fminf(fminf(a0, a1), fminf(a2, a3));
+        else if (is_prod) acc = (a0 * a1) * (a2 * a3);
+        else acc = (a0 + a1) + (a2 + a3);
+    }
+    auto combine = [&](float x, float y) { return is_max ? fmaxf(x, y) : is_min ? fminf(x, y) : is_prod ? x * y : x + y; };
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) acc = combine(acc, __shfl_xor_sync(kFull, acc, s));
+    if (TPO > 32) {
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        if (lane == 0) smem[warp] = acc;
+        __syncthreads();
+        acc = lane < (TPO >> 5) ? smem[lane] : (is_max ? -INFINITY : is_min ? INFINITY : is_prod ? 1.f : 0.f);
+#pragma unroll
+        for (int s = 16; s > 0; s >>= 1) acc = combine(acc, __shfl_xor_sync(kFull, acc, s));
+    }
+    if (active && t == 0) {
+        if (rop == ReduceOp::Mean) acc = acc / p.mean_scale;
+        ((float*)p.out)[oo] = acc;
+    }
+}
+
 // ------------------------------------------------------------------ reduce
 __device__ __forceinline__ uint64_t reduce_identity(ReduceOp op, DType d) {
     const bool is_float = d == DType::F32 || d == DType::F64 || d == DType::F16;
@@ -254,10 +397,41 @@ __global__ void __launch_bounds__(256) reduce_kernel(const __grid_constant__ Red
 
 }  // namespace
 
-#define KN_ROW_DISPATCH(KERNEL, STREAMING)                                                                     \
+static bool row_vec4_ok(const RowParams& p) {
+    if (p.len % 4 != 0 || p.in_axis_stride != 1 || p.out_axis_stride != 1 || p.len > 8192) return false;
+    if (((uintptr_t)p.in0 & 15) || ((uintptr_t)p.out & 15) || (p.in1 && ((uintptr_t)p.in1 & 15))) return false;
+    for (int d = 0; d < p.outer_rank; d++)
+        if (p.in_strides[d] % 4 != 0 || p.out_strides[d] % 4 != 0) return false;
+    return true;
+}
+
+#define KN_ROW_VEC4_CASE(KERNEL, TPR, N)                     \
+    case N: KERNEL<TPR, N><<<grid, 256, 0, stream>>>(p); break;
+
+#define KN_ROW_DISPATCH(KERNEL, VEC4, STREAMING)                                                               \
     if (p.rows == 0 || p.len == 0) return 0;                                                                   \
     if (p.rows > 0x7FFFFFFFll) return (int)cudaErrorInvalidValue;                                              \
     const int64_t len = p.len;                                                                                 \
+    if (row_vec4_ok(p)) {                                                                                      \
+        const int len4 = (int)(len / 4);                                                                       \
+        if (len4 <= 256) {                                                                                     \
+            const unsigned grid = (unsigned)((p.rows + 7) / 8);                                                \
+            switch ((len4 + 31) / 32) {                                                                        \
+                KN_ROW_VEC4_CASE(VEC4, 32, 1) KN_ROW_VEC4_CASE(VEC4, 32, 2) KN_ROW_VEC4_CASE(VEC4, 32, 3)      \
+                KN_ROW_VEC4_CASE(VEC4, 32, 4) KN_ROW_VEC4_CASE(VEC4, 32, 5) KN_ROW_VEC4_CASE(VEC4, 32, 6)      \
+                KN_ROW_VEC4_CASE(VEC4, 32, 7)                                                                  \
+                default: VEC4<32, 8><<<grid, 256, 0, stream>>>(p); break;                                      \
+            }                                                                                                  \
+        } else {                                                                                               \
+            const unsigned grid = (unsigned)p.rows;                                                            \
+            switch ((len4 + 255) / 256) {                                                                      \
+                KN_ROW_VEC4_CASE(VEC4, 256, 2) KN_ROW_VEC4_CASE(VEC4, 256, 3) KN_ROW_VEC4_CASE(VEC4, 256, 4)   \
+                KN_ROW_VEC4_CASE(VEC4, 256, 5) KN_ROW_VEC4_CASE(VEC4, 256, 6) KN_ROW_VEC4_CASE(VEC4, 256, 7)   \
+                default: VEC4<256, 8><<<grid, 256, 0, stream>>>(p); break;                                     \
+            }                                                                                                  \
+        }                                                                                                      \
+        return (int)cudaGetLastError();                                                                        \
+    }                                                                                                          \
     if (len <= 1024) {                                                                                         \
         const int rows_per_block = 8;                                                                          \
         const unsigned grid = (unsigned)((p.rows + rows_per_block - 1) / rows_per_block);                      \
@@ -277,14 +451,25 @@ __global__ void __launch_bounds__(256) reduce_kernel(const __grid_constant__ Red
     }                                                                                                          \
     return (int)cudaGetLastError();
 
-int launch_softmax(const RowParams& p, cudaStream_t stream) { KN_ROW_DISPATCH(softmax_cached_kernel, softmax_streaming_kernel) }
+int launch_softmax(const RowParams& p, cudaStream_t stream) {
+    KN_ROW_DISPATCH(softmax_cached_kernel, softmax_vec4_kernel, softmax_streaming_kernel)
+}
 
 int launch_layernorm(const RowParams& p, cudaStream_t stream) {
-    KN_ROW_DISPATCH(layernorm_cached_kernel, layernorm_streaming_kernel)
+    KN_ROW_DISPATCH(layernorm_cached_kernel, layernorm_vec4_kernel, layernorm_streaming_kernel)
 }
 
 int launch_reduce(const ReduceParams& p, cudaStream_t stream) {
     if (p.n_out == 0) return 0;
+    // f32 over one contiguous, 16-byte-aligned axis: the 128-bit kernel
+    bool rows = (DType)p.dtype == DType::F32 && p.red_rank == 1 && p.red_strides[0] == 1 && p.n_red % 4 == 0 && p.n_red >= 128 &&
+                p.n_red < (1ll << 31) && ((uintptr_t)p.in & 15) == 0 && p.n_out <= 0x7FFFFFFFll;
+    for (int d = 0; d < p.kept_rank && rows; d++) rows = p.kept_in_strides[d] % 4 == 0;
+    if (rows) {
+        if (p.n_red >= 8192) reduce_f32_rows_kernel<256><<<(unsigned)p.n_out, 256, 0, stream>>>(p);
+        else reduce_f32_rows_kernel<32><<<(unsigned)((p.n_out + 7) / 8), 256, 0, stream>>>(p);
+        return (int)cudaGetLastError();
+    }
     if (p.n_red >= 2048) {
         if (p.n_out > 0x7FFFFFFFll) return (int)cudaErrorInvalidValue;
         reduce_kernel<256><<<(unsigned)p.n_out, 256, 0, stream>>>(p);
