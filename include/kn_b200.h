@@ -65,6 +65,8 @@ typedef struct kn_options {
 /* keep every convolution its own step: do not merge runs of stride-1 3x3 convolutions into the
    shared-memory-resident chain kernel (for A/B comparison and tests) */
 #define KN_FLAG_NO_CONV_CHAIN 1
+/* matrix multiplies use the one-tile-per-CTA kernel instead of the persistent one (A/B comparison and tests) */
+#define KN_FLAG_NO_PERSISTENT_GEMM 2
 
 #define KN_MAX_RANK 8
 

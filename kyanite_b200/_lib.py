@@ -18,6 +18,7 @@ STATUS_NAMES = {0: "KN_OK", 1: "KN_ERR_INVALID_ARG", 2: "KN_ERR_BAD_GRAPH", 3: "
 KN_MATH_TF32 = 0
 KN_MATH_F32 = 1
 KN_FLAG_NO_CONV_CHAIN = 1
+KN_FLAG_NO_PERSISTENT_GEMM = 2
 
 
 class KnOptions(Structure):

@@ -30,6 +30,7 @@ SOURCES = [
     "kernels/contract_simt.cu",
     "kernels/contract_tc.cu",
     "kernels/conv_chain.cu",
+    "kernels/gemm_persistent.cu",
 ]
 
 NVCC_FLAGS = [

@@ -139,7 +139,7 @@ struct Executor {
                     break;
                 default: fail(KN_ERR_INTERNAL, "unknown step kind");
             }
-            if (s.tensor_core) tc_prepare_step(s, status_dev);
+            if (s.tensor_core) tc_prepare_step(s, status_dev, plan->opts.flags);
             launches += s.launches;
         }
     }

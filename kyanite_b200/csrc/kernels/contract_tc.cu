@@ -673,7 +673,31 @@ struct TcLaunch {
     dim3 grid;
     int smem_bytes;
     std::shared_ptr<void> chain;  // ConvChain step: launch data of kernels/conv_chain.cu
+    std::shared_ptr<void> gemm_p; // matmul taken by the persistent kernel (kernels/gemm_persistent.cu)
 };
+
+CUtensorMap tc_make_store_map(const void* base, int rank, const int64_t* dims, const int64_t* strides, const int* box) {
+    KN_CHECK(((uintptr_t)base & 15) == 0, KN_ERR_INTERNAL, "TMA base address is not 16-byte aligned");
+    cuuint64_t gdim[5], gstride[4];
+    cuuint32_t gbox[5], estride[5];
+    for (int i = 0; i < rank; i++) {
+        gdim[i] = (cuuint64_t)std::max<int64_t>(dims[i], 1);
+        gbox[i] = (cuuint32_t)box[i];
+        estride[i] = 1;
+        if (i > 0) {
+            int64_t bytes = strides[i] * 4;
+            if (dims[i] <= 1 && (bytes <= 0 || bytes % 16 != 0)) bytes = 16;
+            KN_CHECK(bytes > 0 && bytes % 16 == 0, KN_ERR_INTERNAL, "TMA stride is not a positive multiple of 16 bytes");
+            gstride[i - 1] = (cuuint64_t)bytes;
+        }
+    }
+    CUtensorMap map;
+    CUresult res = encode_tiled_fn()(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstride,
+                                     gbox, estride, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    KN_CHECK(res == CUDA_SUCCESS, KN_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)res));
+    return map;
+}
 
 CUtensorMap tc_make_map(const void* base, int rank, const int64_t* dims, const int64_t* strides, const int* box, bool operand) {
     return make_map(base, rank, dims, strides, box, operand);
@@ -811,7 +835,7 @@ bool tc_conv_tile(int oh, int ow, int* wb, int* hb, int* nb) {
     return true;
 }
 
-void tc_prepare_step(Step& step, uint32_t* status_word) {
+void tc_prepare_step(Step& step, uint32_t* status_word, int flags) {
     auto launch = std::make_shared<TcLaunch>();
     if (step.kind == StepKind::ConvChain) {
         launch->chain = chain_prepare(step.chain, status_word);
@@ -824,6 +848,13 @@ void tc_prepare_step(Step& step, uint32_t* status_word) {
     int64_t n_cols;
     if (step.kind == StepKind::Gemm) {
         const GemmParams& g = step.gemm;
+        if (g.splits <= 1 && !(flags & KN_FLAG_NO_PERSISTENT_GEMM)) {
+            launch->gemm_p = gemm_persistent_prepare(g, status_word);
+            if (launch->gemm_p) {
+                step.tc = launch;
+                return;
+            }
+        }
         p.mode = 0;
         n_cols = g.n;
         p.m = g.m;
@@ -962,6 +993,7 @@ void tc_prepare_step(Step& step, uint32_t* status_word) {
 int tc_launch_step(const Step& step, cudaStream_t stream) {
     const TcLaunch& l = *step.tc;
     if (l.chain) return chain_launch(l.chain.get(), stream);
+    if (l.gemm_p) return gemm_persistent_launch(l.gemm_p.get(), stream);
     // the opt-in to large dynamic shared memory is per device
     static std::mutex mu;
     static bool done[64] = {false};

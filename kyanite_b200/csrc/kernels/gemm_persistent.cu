@@ -1,0 +1,346 @@
+// Persistent TF32 matrix multiply for sm_100a: C[b] = act(A[b] . B[b]^T-layout + add1 + add2) with a dense
+// row-major C.
+//
+// Compared with the one-tile-per-CTA kernel in contract_tc.cu, a CTA here stays on its SM and walks over
+// output tiles, and tensor memory holds TWO accumulators: while the four epilogue warps drain tile i
+// (tcgen05.ld -> addends / activation -> swizzled staging tile in shared memory -> bulk tensor store),
+// the producer is already loading and the MMA thread already multiplying tile i + 1.  For the short-K
+// shapes of transformer layers (K = 768: 24 K-blocks per tile) fill and drain were most of a tile's time.
+//
+//   warp 0 lane 0   TMA producer: per K block the 128 x 32 A tile and the BN x 32 B tile (K-major, 128-byte
+//                   swizzle, rounded to TF32 by the copy engine), ring of stages with full / empty mbarriers
+//   warp 1 lane 0   MMA issuer: four tcgen05.mma.kind::tf32 (K = 8) per stage into accumulator `tile & 1`;
+//                   waits for that accumulator to be drained, signals it full with tcgen05.commit
+//   warps 2..5      epilogue: thread <-> accumulator lane <-> output row; 32 columns at a time
+//
+// Tiles are walked column-block-major (all row blocks of one column block before the next), so the CTAs
+// that run at the same time share a B tile in L2.  Row and column tails are the copy engine's zero fill
+// (loads) and clipping (stores).  Every mbarrier wait is bounded as in the other tensor-core kernels.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstring>
+#include <memory>
+#include <mutex>
+
+#include "../tc.h"
+#include "tc_host.h"
+#include "tc_ptx.cuh"
+
+namespace kn {
+
+namespace {
+
+using namespace tcp;
+
+constexpr int kGpThreads = 192;
+constexpr int kGpBlockM = 128;
+constexpr int kGpBlockK = 32;
+constexpr int kGpATileBytes = kGpBlockM * 128;
+constexpr int kGpStageTileBytes = 128 * 128;   // epilogue staging: 128 rows x 32 columns of f32
+
+struct GemmPersistentParams {
+    int32_t bn, stages, k_iters;
+    int32_t m_tiles, n_tiles, batch, total_tiles;
+    int64_t m, n;
+    const float* add1;
+    const float* add2;
+    int64_t s1[3], s2[3];            // (batch, row, col) strides of the addends
+    int32_t add1_mode, add2_mode;    // 0 absent, 1 one value per column, 2 a value per element (row-contiguous)
+    int32_t act;
+    uint32_t* status;
+};
+
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_local(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__global__ void __launch_bounds__(kGpThreads, 1)
+gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                       const __grid_constant__ CUtensorMap map_c, const __grid_constant__ GemmPersistentParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+    const int stages = p.stages;
+    const uint32_t b_tile_bytes = (uint32_t)p.bn * 128u;
+    const uint32_t stage_bytes = kGpATileBytes + b_tile_bytes;
+    const uint32_t staging_base = base + (uint32_t)stages * stage_bytes;          // two staging tiles
+    const uint32_t bar_base = staging_base + 2u * kGpStageTileBytes;
+    const uint32_t full_bar = bar_base, empty_bar = bar_base + 8u * stages;
+    const uint32_t acc_full = bar_base + 16u * stages, acc_empty = acc_full + 16u;
+    const uint32_t slot_addr = acc_empty + 16u;
+    volatile uint32_t* tmem_slot = (volatile uint32_t*)(gen_base + (slot_addr - base));
+    volatile int* abandon = (volatile int*)(gen_base + (slot_addr + 4u - base));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; s++) {
+            mbar_init(full_bar + 8u * s, 1);
+            mbar_init(empty_bar + 8u * s, 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(acc_full + 8u * b, 1);
+            mbar_init(acc_empty + 8u * b, 128);
+        }
+        *abandon = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const uint32_t tmem_cols = 2u * (uint32_t)p.bn <= 32u ? 32u : (2u * (uint32_t)p.bn <= 64u ? 64u : (2u * (uint32_t)p.bn <= 128u ? 128u : (2u * (uint32_t)p.bn <= 256u ? 256u : 512u)));
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_addr), "r"(tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    // tile t -> (row block, column block, batch): row blocks fastest
+    auto tile_coords = [&](int t, int& mt, int& nt, int& bt) {
+        mt = t % p.m_tiles;
+        const int r = t / p.m_tiles;
+        nt = r % p.n_tiles;
+        bt = r / p.n_tiles;
+    };
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- producer
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+        int s = 0, round = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+            int mt, nt, bt;
+            tile_coords(t, mt, nt, bt);
+            for (int k = 0; k < p.k_iters; k++) {
+                if (round > 0 && !mbar_wait(empty_bar + 8u * s, (uint32_t)((round & 1) ^ 1), abandon, p.status, 21)) { ok = false; break; }
+                const uint32_t bar = full_bar + 8u * s;
+                mbar_expect_tx(bar, stage_bytes);
+                const uint32_t dst = base + (uint32_t)s * stage_bytes;
+                tma_load_3d(dst, &map_a, bar, k * kGpBlockK, mt * kGpBlockM, bt);
+                tma_load_3d(dst + kGpATileBytes, &map_b, bar, k * kGpBlockK, nt * p.bn, bt);
+                if (++s == stages) { s = 0; round++; }
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---------------- MMA issuer
+        const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(p.bn >> 3) << 17) | ((uint32_t)(kGpBlockM >> 4) << 24);
+        int s = 0, round = 0, local = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, local++) {
+            const int buf = local & 1;
+            // the epilogue has drained this accumulator (its previous use was tile local - 2)
+            if (local >= 2 && !mbar_wait(acc_empty + 8u * buf, (uint32_t)(((local >> 1) - 1) & 1), abandon, p.status, 22)) break;
+            tc_fence_after();
+            const uint32_t acc = tmem_base + (uint32_t)(buf * p.bn);
+            for (int k = 0; k < p.k_iters; k++) {
+                if (!mbar_wait(full_bar + 8u * s, (uint32_t)(round & 1), abandon, p.status, 23)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t a_addr = base + (uint32_t)s * stage_bytes;
+                const uint64_t da = smem_desc_sw128(a_addr);
+                const uint64_t db = smem_desc_sw128(a_addr + kGpATileBytes);
+#pragma unroll
+                for (int j = 0; j < kGpBlockK / 8; j++) mma_tf32(acc, da + 2u * j, db + 2u * j, idesc, (k | j) != 0 ? 1u : 0u);
+                mma_commit(empty_bar + 8u * s);
+                if (++s == stages) { s = 0; round++; }
+            }
+            if (ok) mma_commit(acc_full + 8u * buf);
+        }
+    } else if (warp >= 2) {
+        // ---------------- epilogue
+        const int quarter = warp & 3;
+        const int row_in_tile = quarter * 32 + lane;
+        const uint32_t lane_bits = (uint32_t)(quarter * 32) << 16;
+        const bool issuer = threadIdx.x == 64;   // the thread that talks to the copy engine
+        // swizzled position of this row's 16-byte chunk c inside a staging tile: chunk ^ (row & 7)
+        const uint32_t row_base = (uint32_t)row_in_tile * 128u;
+        const uint32_t row_phase = (uint32_t)row_in_tile & 7u;
+        int local = 0, stage_buf = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, local++) {
+            int mt, nt, bt;
+            tile_coords(t, mt, nt, bt);
+            const int buf = local & 1;
+            {
+                uint32_t good = 1;
+                if (lane == 0) good = mbar_wait(acc_full + 8u * buf, (uint32_t)((local >> 1) & 1), abandon, p.status, 24) ? 1u : 0u;
+                good = __shfl_sync(0xffffffffu, good, 0);
+                // the loop below synchronises the four epilogue warps with each other, so they must agree on
+                // entering it: vote (every epilogue thread gets here, its wait being bounded)
+                uint32_t all_good;
+                asm volatile(
+                    "{\n\t.reg .pred p, q;\n\t"
+                    "setp.ne.u32 p, %1, 0;\n\t"
+                    "bar.red.and.pred q, 2, 128, p;\n\t"
+                    "selp.u32 %0, 1, 0, q;\n\t}"
+                    : "=r"(all_good)
+                    : "r"(good)
+                    : "memory");
+                if (!all_good) { ok = false; break; }
+                while (!mbar_try_wait(acc_full + 8u * buf, (uint32_t)((local >> 1) & 1))) {}
+            }
+            tc_fence_after();
+            const int64_t row = (int64_t)mt * kGpBlockM + row_in_tile;
+            const bool row_ok = row < p.m;
+            const int chunks = (p.bn + 31) >> 5;
+            for (int c = 0; c < chunks; c++) {
+                const int col0 = nt * p.bn + c * 32;
+                if (col0 >= p.n) break;                       // uniform: nothing of this chunk is inside the matrix
+                uint32_t v[32];
+                tmem_load_32(tmem_base + lane_bits + (uint32_t)(buf * p.bn + c * 32), v);
+                // addends: a per-column value is fetched once per chunk (lane j holds column col0 + j) and
+                // handed round with shuffles; a per-element addend is this thread's own row, 128 contiguous bytes
+#pragma unroll
+                for (int which = 0; which < 2; which++) {
+                    const int mode = which == 0 ? p.add1_mode : p.add2_mode;
+                    if (mode == 0) continue;
+                    const float* add = which == 0 ? p.add1 : p.add2;
+                    const int64_t* st = which == 0 ? p.s1 : p.s2;
+                    if (mode == 1) {
+                        const int64_t col = col0 + lane;
+                        const float mine = col < p.n ? __ldg(add + bt * st[0] + col * st[2]) : 0.f;
+#pragma unroll
+                        for (int j = 0; j < 32; j++) v[j] = __float_as_uint(__uint_as_float(v[j]) + __shfl_sync(0xffffffffu, mine, j));
+                    } else if (row_ok) {
+                        const float* src = add + bt * st[0] + row * st[1] + col0;
+                        if (col0 + 32 <= p.n && ((uintptr_t)src & 15) == 0) {
+#pragma unroll
+                            for (int q = 0; q < 8; q++) {
+                                const float4 a4 = __ldg((const float4*)src + q);
+                                v[4 * q] = __float_as_uint(__uint_as_float(v[4 * q]) + a4.x);
+                                v[4 * q + 1] = __float_as_uint(__uint_as_float(v[4 * q + 1]) + a4.y);
+                                v[4 * q + 2] = __float_as_uint(__uint_as_float(v[4 * q + 2]) + a4.z);
+                                v[4 * q + 3] = __float_as_uint(__uint_as_float(v[4 * q + 3]) + a4.w);
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j++)
+                                if (col0 + j < p.n) v[j] = __float_as_uint(__uint_as_float(v[j]) + __ldg(src + j));
+                        }
+                    }
+                }
+                if (p.act == (int)Activation::Relu) {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) v[j] = __float_as_uint(fmaxf(__uint_as_float(v[j]), 0.f));
+                }
+                // the staging tile about to be written was handed to the copy engine two chunks ago
+                if (issuer) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                const uint32_t stile = staging_base + (uint32_t)stage_buf * kGpStageTileBytes + row_base;
+#pragma unroll
+                for (int q = 0; q < 8; q++)
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stile + (((uint32_t)q ^ row_phase) << 4)),
+                                 "r"(v[4 * q]), "r"(v[4 * q + 1]), "r"(v[4 * q + 2]), "r"(v[4 * q + 3])
+                                 : "memory");
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (issuer) {
+                    tma_store_3d(&map_c, staging_base + (uint32_t)stage_buf * kGpStageTileBytes, col0, mt * kGpBlockM, bt);
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                }
+                stage_buf ^= 1;
+            }
+            // every tcgen05.ld of this accumulator has completed (tmem_load_32 waits): the MMA thread may reuse it
+            tc_fence_before();
+            mbar_arrive_local(acc_empty + 8u * buf);
+        }
+        if (issuer) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // shared memory must outlive the stores
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+    }
+}
+
+struct GemmPersistentLaunch {
+    CUtensorMap map_a, map_b, map_c;
+    GemmPersistentParams p;
+    dim3 grid;
+    int smem_bytes;
+};
+
+// 0 absent, 1 one value per column (row stride 0), 2 a value per element with contiguous rows, 3 anything else
+int classify_addend(const float* ptr, const int64_t* st) {
+    if (ptr == nullptr) return 0;
+    if (st[1] == 0) return 1;
+    if (st[2] == 1) return 2;
+    return 3;
+}
+
+}  // namespace
+
+std::shared_ptr<void> gemm_persistent_prepare(const GemmParams& g, uint32_t* status_word) {
+    if (g.splits > 1 || g.batch < 1 || g.m < 1 || g.n < 16 || g.k < 1) return nullptr;
+    // dense row-major C whose rows start on 16-byte boundaries
+    if (g.sc[2] != 1 || g.sc[1] % 4 != 0 || (g.batch > 1 && g.sc[0] % 4 != 0) || ((uintptr_t)g.c & 15) != 0) return nullptr;
+    const int m1 = classify_addend(g.add1, g.s1), m2 = classify_addend(g.add2, g.s2);
+    if (m1 == 3 || m2 == 3) return nullptr;
+    auto l = std::make_shared<GemmPersistentLaunch>();
+    GemmPersistentParams& p = l->p;
+    memset(&p, 0, sizeof(p));
+    p.bn = (int)std::min<int64_t>((std::min<int64_t>(g.n, 256) + 15) / 16 * 16, 256);
+    p.k_iters = (int)((g.k + kGpBlockK - 1) / kGpBlockK);
+    p.m_tiles = (int)((g.m + kGpBlockM - 1) / kGpBlockM);
+    p.n_tiles = (int)((g.n + p.bn - 1) / p.bn);
+    p.batch = (int)g.batch;
+    const int64_t total = (int64_t)p.m_tiles * p.n_tiles * g.batch;
+    if (total > (1 << 30)) return nullptr;
+    p.total_tiles = (int)total;
+    p.m = g.m;
+    p.n = g.n;
+    p.add1 = g.add1;
+    p.add2 = g.add2;
+    for (int i = 0; i < 3; i++) {
+        p.s1[i] = g.s1[i];
+        p.s2[i] = g.s2[i];
+    }
+    p.add1_mode = m1;
+    p.add2_mode = m2;
+    p.act = g.act;
+    p.status = status_word;
+    const int stage_bytes = kGpATileBytes + p.bn * 128;
+    const int fixed = 1024 + 2 * kGpStageTileBytes + 16 * 8 + 64 + 64;
+    p.stages = std::max(2, std::min(6, (227 * 1024 - fixed) / stage_bytes));
+    l->smem_bytes = fixed + p.stages * stage_bytes;
+    int64_t adims[3] = {g.k, g.m, g.batch}, astr[3] = {1, g.sa[1], g.sa[0]};
+    int abox[3] = {kGpBlockK, kGpBlockM, 1};
+    l->map_a = tc_make_map(g.a, 3, adims, astr, abox, true);
+    int64_t bdims[3] = {g.k, g.n, g.batch}, bstr[3] = {1, g.sb[2], g.sb[0]};
+    int bbox[3] = {kGpBlockK, p.bn, 1};
+    l->map_b = tc_make_map(g.b, 3, bdims, bstr, bbox, true);
+    int64_t cdims[3] = {g.n, g.m, g.batch}, cstr[3] = {1, g.sc[1], g.sc[0]};
+    int cbox[3] = {32, kGpBlockM, 1};
+    l->map_c = tc_make_store_map(g.c, 3, cdims, cstr, cbox);
+    l->grid = dim3((unsigned)std::min<int64_t>(total, 148), 1, 1);
+    return l;
+}
+
+int gemm_persistent_launch(const void* launch, cudaStream_t stream) {
+    const GemmPersistentLaunch& l = *(const GemmPersistentLaunch*)launch;
+    static std::mutex mu;
+    static bool done[64] = {false};
+    int device = 0;
+    cudaGetDevice(&device);
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (device >= 0 && device < 64 && !done[device]) {
+            cudaError_t e = cudaFuncSetAttribute(gemm_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            if (e != cudaSuccess) return (int)e;
+            done[device] = true;
+        }
+    }
+    gemm_persistent_kernel<<<l.grid, kGpThreads, l.smem_bytes, stream>>>(l.map_a, l.map_b, l.map_c, l.p);
+    return (int)cudaGetLastError();
+}
+
+}  // namespace kn

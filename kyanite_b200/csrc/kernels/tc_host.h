@@ -15,6 +15,14 @@ namespace kn {
 // plain f32 tile without swizzle (an epilogue tile).
 CUtensorMap tc_make_map(const void* base, int rank, const int64_t* dims, const int64_t* strides, const int* box, bool operand);
 
+// Tiled tensor map for bulk tensor STORES of plain f32 from a 128-byte-swizzled staging tile (inner box
+// extent 32 floats).
+CUtensorMap tc_make_store_map(const void* base, int rank, const int64_t* dims, const int64_t* strides, const int* box);
+
+// Persistent matrix multiply (kernels/gemm_persistent.cu): null if the step does not qualify.
+std::shared_ptr<void> gemm_persistent_prepare(const GemmParams& g, uint32_t* status_word);
+int gemm_persistent_launch(const void* launch, cudaStream_t stream);
+
 // Convolution chain (kernels/conv_chain.cu): launch data built once the device pointers are known.
 std::shared_ptr<void> chain_prepare(const ConvChainParams& c, uint32_t* status_word);
 int chain_launch(const void* launch, cudaStream_t stream);

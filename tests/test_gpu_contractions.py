@@ -99,3 +99,31 @@ def test_matmul_with_few_columns(b, m, n, k, mode):
     w2 = g.input(shape(b, k, n))
     g.output(g.batched_mat_mul(g.permute(at, [0, 2, 1]), w2))
     check(g, 0, [rng(4, b, k, m), rng(5, b, k, n)], mode=mode)
+
+
+@pytest.mark.parametrize("b,m,n,k", [(1, 5120, 1024, 128), (3, 300, 200, 100), (1, 130, 20, 40), (2, 256, 272, 64),
+                                     (1, 257, 18, 96), (1, 4096, 512, 1536)])
+def test_persistent_matmul_against_one_tile_kernel(b, m, n, k):
+    """Matmuls without split-K run on the persistent kernel (one CTA per SM walking the tile list, two
+    accumulators in tensor memory); `FLAG_NO_PERSISTENT_GEMM` selects the one-tile-per-CTA kernel instead.
+    Both must match the oracle, with a per-column bias, a full residual addend and ReLU in the epilogue, on
+    tile lists longer than the grid (160 tiles of 128 x 256), ragged edges, batches and a row length that
+    only the one-tile kernel accepts (n = 18)."""
+    from kyanite_b200.executor import FLAG_NO_PERSISTENT_GEMM
+    g = Graph()
+    a = g.input(shape(b, m, k))
+    w = g.input(shape(b, n, k))
+    bias = g.input(shape(1, 1, n))
+    res = g.input(shape(b, m, n))
+    g.output(g.relu(g.add(g.add(g.batched_mat_mul(a, g.permute(w, [0, 2, 1])), bias), res)))
+    ins = [rng(1, b, m, k), rng(2, b, n, k), rng(3, 1, 1, n), rng(4, b, m, n)]
+    blob = g.to_bytes()
+    want = cpu_eval_graph(blob, 0, ins)
+    got = {}
+    for flags in (0, FLAG_NO_PERSISTENT_GEMM):
+        with CudaExecutor(0, blob, 0, math_mode=MATH_TF32, flags=flags) as ex:
+            for _ in range(2):
+                got[flags] = ex.evaluate(ins)
+                assert_tensors_match(want, got[flags], tol_abs=4e-3, tol_rel=4e-3, abs_scaled=True)
+    # same operand rounding and the same order of the K blocks in both kernels
+    assert_tensors_match(got[0], got[FLAG_NO_PERSISTENT_GEMM], tol_abs=1e-5, tol_rel=1e-5, abs_scaled=True)
