@@ -136,6 +136,7 @@ struct Executor {
                     s.chain.out = (float*)ptr[1];
                     s.chain.tiles = (const float*)ptr[2];
                     s.chain.bias = (const float*)ptr[3];
+                    for (int h = 0; h < s.chain.n_heads; h++) s.chain.head_out[h] = (float*)ptr[4 + h];
                     break;
                 default: fail(KN_ERR_INTERNAL, "unknown step kind");
             }

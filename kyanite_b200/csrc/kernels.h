@@ -128,9 +128,14 @@ struct ConvParams {
 // ---- a run of stride-1 3x3 same-padding convolutions executed by ONE kernel, activations resident
 // in shared memory: layer l computes  act_l(conv(x_l, filter_l) + bias_l [+ held])  where x_0 = `in`,
 // x_{l+1} = the layer's result and `held` is `in` or the last result flagged to be held (the skip
-// connection of a residual block).  Only the last layer's result reaches global memory.
+// connection of a residual block).  Results reach global memory only where a layer is flagged to store,
+// and through the heads of the optional pointwise last layer.
 constexpr int kMaxChainLayers = 64;
 constexpr int kChainFlagRelu = 1, kChainFlagAddHeld = 2, kChainFlagHold = 4;
+constexpr int kChainFlagStore = 8;       // the layer's result is written to `out` (always set on the last 3x3 layer
+                                         // unless nothing outside the chain reads it)
+constexpr int kChainFlagPointwise = 16;  // a 1x1 layer: one tap, c_blocks tiles
+constexpr int kMaxChainHeads = 4;
 struct ConvChainParams {
     const float* in;      // [n, c_in, h, w], any strides
     float* out;           // [n, k, h, w], any strides
@@ -143,6 +148,14 @@ struct ConvChainParams {
     int64_t s_in[4], s_out[4];
     uint8_t flags[kMaxChainLayers];
     uint8_t c_blocks[kMaxChainLayers];   // 32-channel blocks of the layer's input
+    // Heads: when n_heads > 0 the last layer is a pointwise layer whose output channels are several 1x1
+    // convolutions of the last 3x3 result side by side (a policy and a value head, say); head i owns
+    // channels [head_begin[i], head_begin[i + 1]) and has its own output tensor [n, channels, h, w].
+    int32_t n_heads;
+    int32_t head_begin[kMaxChainHeads + 1];
+    float* head_out[kMaxChainHeads];
+    int64_t head_s_out[kMaxChainHeads][4];
+    uint8_t head_relu[kMaxChainHeads];
 };
 
 // All launchers enqueue on `stream` and return the cudaError_t of the launch as int.

@@ -849,7 +849,7 @@ void tc_prepare_step(Step& step, uint32_t* status_word, int flags) {
     if (step.kind == StepKind::Gemm) {
         const GemmParams& g = step.gemm;
         if (g.splits <= 1 && !(flags & KN_FLAG_NO_PERSISTENT_GEMM)) {
-            launch->gemm_p = gemm_persistent_prepare(g, status_word);
+            launch->gemm_p = gemm_persistent_prepare(g, status_word, 1, 0);
             if (launch->gemm_p) {
                 step.tc = launch;
                 return;
@@ -915,6 +915,9 @@ void tc_prepare_step(Step& step, uint32_t* status_word, int flags) {
             p.so[2] = 1;
             launch->grid.z = (unsigned)(g.batch * p.splits);
             launch->split_k = true;
+            // the partial tiles can come from the persistent kernel too (its epilogue hands whole 128 x 32
+            // blocks to the copy engine instead of storing row by row)
+            if (!(flags & KN_FLAG_NO_PERSISTENT_GEMM)) launch->gemm_p = gemm_persistent_prepare(g, status_word, p.splits, per_slice);
         }
     } else {
         const ConvParams& c = step.conv;
@@ -990,10 +993,21 @@ void tc_prepare_step(Step& step, uint32_t* status_word, int flags) {
     step.tc = launch;
 }
 
+static int launch_splitk_reduce(const SplitKReduceParams& r, cudaStream_t stream) {
+    const int64_t total = r.batch * r.m * r.n;
+    const unsigned blocks = (unsigned)std::min<int64_t>((total + 255) / 256, 148 * 8);
+    splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(r);
+    return (int)cudaGetLastError();
+}
+
 int tc_launch_step(const Step& step, cudaStream_t stream) {
     const TcLaunch& l = *step.tc;
     if (l.chain) return chain_launch(l.chain.get(), stream);
-    if (l.gemm_p) return gemm_persistent_launch(l.gemm_p.get(), stream);
+    if (l.gemm_p) {
+        const int err = gemm_persistent_launch(l.gemm_p.get(), stream);
+        if (err != 0 || !l.split_k) return err;
+        return launch_splitk_reduce(l.reduce, stream);
+    }
     // the opt-in to large dynamic shared memory is per device
     static std::mutex mu;
     static bool done[64] = {false};
@@ -1025,11 +1039,7 @@ int tc_launch_step(const Step& step, cudaStream_t stream) {
         return (int)cudaLaunchKernelEx(&cfg, tc_conv_cl_kernel, l.map_a, l.map_b, l.map_res, l.map_out, l.cl);
     }
     tc_contract_kernel<<<l.grid, kThreads, l.smem_bytes, stream>>>(l.map_a, l.map_b, l.p);
-    if (l.split_k) {
-        const int64_t total = l.reduce.batch * l.reduce.m * l.reduce.n;
-        const unsigned blocks = (unsigned)std::min<int64_t>((total + 255) / 256, 148 * 8);
-        splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(l.reduce);
-    }
+    if (l.split_k) return launch_splitk_reduce(l.reduce, stream);
     return (int)cudaGetLastError();
 }
 

@@ -24,7 +24,10 @@
 // once its input is complete; warps 2..9 are the epilogue (two warps per TMEM lane quarter, each taking
 // alternate 16-column chunks): accumulator + bias (+ held skip tensor) -> ReLU -> written back as the
 // next layer's operand (rounded to TF32, zeros at padding positions) and, if a later layer adds it,
-// into the held-tensor columns of TMEM in full f32; the last layer's result goes to global memory.
+// into the held-tensor columns of TMEM in full f32; a layer flagged to store writes its result to global
+// memory.  The last layer may be a pointwise (1x1) layer that computes several convolutions of the last
+// 3x3 result at once, their output channels side by side in the accumulator's lanes ("heads": each with
+// its own output tensor and activation), so the tower's result need not leave the SM at all.
 //
 // Every mbarrier wait is bounded; on expiry the executor's status word is raised, all roles leave, TMEM is
 // freed and the kernel returns.
@@ -63,6 +66,11 @@ struct ChainKernelParams {
     uint8_t flags[kMaxChainLayers];
     uint8_t c_blocks[kMaxChainLayers];
     uint32_t* status;
+    int32_t n_heads;
+    int32_t head_begin[kMaxChainHeads + 1];
+    float* head_out[kMaxChainHeads];
+    int64_t head_s_out[kMaxChainHeads][4];
+    uint8_t head_relu[kMaxChainHeads];
 };
 
 __device__ __forceinline__ void tmem_store_16(uint32_t taddr, const uint32_t (&v)[16]) {   // caller waits (tcgen05.wait::st)
@@ -163,7 +171,7 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
         int layer_base = 0, slot = 0, round = 0;
         bool ok = true;
         for (int l = 0; l < p.n_layers && ok; l++) {
-            const int n = 9 * p.c_blocks[l];
+            const int n = ((p.flags[l] & kChainFlagPointwise) ? 1 : 9) * p.c_blocks[l];
             const int g = n % p.group == 0 ? p.group : 1;      // tiles per request
             const int groups = n / g;
             int idx = (int)((blockIdx.x * 5u) % (uint32_t)groups);
@@ -194,12 +202,14 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
             tc_fence_after();
             const int cbl = p.c_blocks[l];
             uint32_t accumulate = 0;
-            const int n = 9 * cbl;
+            const bool pointwise = (p.flags[l] & kChainFlagPointwise) != 0;
+            const int n = (pointwise ? 1 : 9) * cbl;
             const int g = n % p.group == 0 ? p.group : 1;
             const int groups = n / g;
             // the producer's order: start at group (blockIdx.x * 5) % groups, wrap around
             int tile = (int)((blockIdx.x * 5u) % (uint32_t)groups) * g;
             int tap = tile / cbl, cb = tile - tap * cbl;
+            if (pointwise) tap = 4;     // the centre tap: the operand starts at the pixel itself
             for (int i = 0; i < groups && ok; i++) {
                 ok = mbar_wait(full_bar + 8u * slot, (uint32_t)(round & 1), abandon, p.status, 13);
                 if (!ok) break;
@@ -216,7 +226,7 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
                     }
                     if (++cb == cbl) {
                         cb = 0;
-                        if (++tap == 9) tap = 0;
+                        if (!pointwise && ++tap == 9) tap = 0;
                     }
                 }
                 mma_commit(empty_bar + 8u * slot);
@@ -261,6 +271,10 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
             if ((u & 0x7F800000u) != 0x7F800000u) u += 0x1000u;
             asm volatile("st.shared.b32 [%0], %1;" ::"r"(chunk_rows + sw[j & 7] + (uint32_t)j * 128u), "r"(u) : "memory");
         };
+        // the head this thread's channel belongs to in the pointwise last layer
+        int head = -1;
+        for (int i = 0; i < p.n_heads; i++)
+            if (ch >= p.head_begin[i] && ch < p.head_begin[i + 1]) head = i;
         // layer 0's input: from global memory into the operand layout and the held-tensor columns
         asm volatile("griddepcontrol.wait;" ::: "memory");
         for (int c = half; c < chunks16; c += 2) {
@@ -285,9 +299,22 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
         for (int l = 0; l < p.n_layers; l++) {
             const uint32_t flags = p.flags[l];
             const bool last = l == p.n_layers - 1;
-            const bool add_held = (flags & kChainFlagAddHeld) != 0, relu = (flags & kChainFlagRelu) != 0;
+            const bool heads = last && p.n_heads > 0;
+            const bool add_held = (flags & kChainFlagAddHeld) != 0;
             const bool hold = (flags & kChainFlagHold) != 0 && !last;
-            const float bias = ch < p.k ? p.bias[l * 128 + ch] : 0.f;
+            // where this thread's channel goes in global memory, if anywhere
+            bool relu = (flags & kChainFlagRelu) != 0, valid = ch < p.k, to_global = (flags & kChainFlagStore) != 0;
+            float* o_ptr = p.out + (int64_t)ch * p.s_out[1];
+            int64_t o_s0 = p.s_out[0], o_s2 = p.s_out[2], o_s3 = p.s_out[3];
+            if (heads) {
+                valid = to_global = head >= 0;
+                if (valid) {
+                    relu = p.head_relu[head] != 0;
+                    o_ptr = p.head_out[head] + (int64_t)(ch - p.head_begin[head]) * p.head_s_out[head][1];
+                    o_s0 = p.head_s_out[head][0], o_s2 = p.head_s_out[head][2], o_s3 = p.head_s_out[head][3];
+                }
+            }
+            const float bias = valid ? p.bias[l * 128 + ch] : 0.f;
             // One lane per warp polls: 256 threads spinning on a shared-memory barrier for the whole
             // mainloop would compete with the copy engine and the tensor core for shared memory.  The
             // outcome is warp-uniform (the tensor-memory accesses below need the whole warp); every lane
@@ -322,7 +349,7 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
                 };
                 auto finish = [&](int k, int c, uint32_t (&v)[16], uint32_t (&h)[16]) {
                     const uint32_t chunk_rows = my_rows + (uint32_t)c * 2048u;
-                    const uint32_t mask = (ch < p.k) ? real[k] : 0u;
+                    const uint32_t mask = valid ? real[k] : 0u;
 #pragma unroll
                     for (int j = 0; j < 16; j++) {
                         float x = __uint_as_float(v[j]) + bias;
@@ -333,13 +360,13 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
                         if (!last && has_block) store_operand(chunk_rows, j, x);
                     }
                     if (hold) tmem_store_16(tmem_held + lane_bits + (uint32_t)(c * 16), v);
-                    if (last) {
+                    if (to_global) {
 #pragma unroll
                         for (int j = 0; j < 16; j++) {
                             if ((mask >> j) & 1u) {
                                 const uint32_t info = colinfo[c * 16 + j];
-                                p.out[(img0 + ((info >> 16) & 0xFF)) * p.s_out[0] + (int64_t)ch * p.s_out[1] +
-                                      (int64_t)((info >> 8) & 0xFF) * p.s_out[2] + (int64_t)(info & 0xFF) * p.s_out[3]] = __uint_as_float(v[j]);
+                                o_ptr[(img0 + ((info >> 16) & 0xFF)) * o_s0 + (int64_t)((info >> 8) & 0xFF) * o_s2 +
+                                      (int64_t)(info & 0xFF) * o_s3] = __uint_as_float(v[j]);
                             }
                         }
                     }
@@ -436,7 +463,7 @@ std::shared_ptr<void> chain_prepare(const ConvChainParams& c, uint32_t* status_w
     p.total_tiles = 0;
     for (int i = 0; i < c.n_layers; i++) {
         c_blocks_max = std::max<int>(c_blocks_max, c.c_blocks[i]);
-        p.total_tiles += 9 * c.c_blocks[i];
+        p.total_tiles += ((c.flags[i] & kChainFlagPointwise) ? 1 : 9) * c.c_blocks[i];
         p.flags[i] = c.flags[i];
         p.c_blocks[i] = c.c_blocks[i];
     }
@@ -471,6 +498,15 @@ std::shared_ptr<void> chain_prepare(const ConvChainParams& c, uint32_t* status_w
     while (tmem < cols) tmem <<= 1;
     p.tmem_cols = tmem;
     p.status = status_word;
+    KN_CHECK(c.n_heads >= 0 && c.n_heads <= kMaxChainHeads, KN_ERR_INTERNAL, "convolution chain with too many heads");
+    p.n_heads = c.n_heads;
+    for (int i = 0; i < c.n_heads; i++) {
+        p.head_begin[i] = c.head_begin[i];
+        p.head_out[i] = c.head_out[i];
+        p.head_relu[i] = c.head_relu[i];
+        for (int d = 0; d < 4; d++) p.head_s_out[i][d] = c.head_s_out[i][d];
+    }
+    p.head_begin[c.n_heads] = c.head_begin[c.n_heads];
     // one request per filter tap (all channel blocks of the tap, up to 64 KB): large requests stream at
     // about twice the rate of single 16 KB tiles
     p.group = c_blocks_max;

@@ -42,6 +42,8 @@ constexpr int kGpStageTileBytes = 128 * 128;   // epilogue staging: 128 rows x 3
 
 struct GemmPersistentParams {
     int32_t bn, stages, k_iters;
+    int32_t splits, k_iters_slice;   // split K: slice sp of a tile covers K blocks [sp * k_iters_slice, ...) and is stored
+                                     // as matrix `batch * splits + sp` of the output map (the partial-sum buffer)
     int32_t m_tiles, n_tiles, batch, total_tiles;
     int64_t m, n;
     const float* add1;
@@ -104,12 +106,15 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     const uint32_t tmem_base = *tmem_slot;
 
     // tile t -> (row block, column block, batch): row blocks fastest
-    auto tile_coords = [&](int t, int& mt, int& nt, int& bt) {
+    auto tile_coords = [&](int t, int& mt, int& nt, int& bt, int& sp) {
         mt = t % p.m_tiles;
         const int r = t / p.m_tiles;
         nt = r % p.n_tiles;
-        bt = r / p.n_tiles;
+        const int r2 = r / p.n_tiles;
+        sp = r2 % p.splits;
+        bt = r2 / p.splits;
     };
+    auto slice_blocks = [&](int sp) { return min(p.k_iters_slice, p.k_iters - sp * p.k_iters_slice); };
 
     if (warp == 0 && lane == 0) {
         // ---------------- producer
@@ -118,9 +123,10 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         int s = 0, round = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
-            int mt, nt, bt;
-            tile_coords(t, mt, nt, bt);
-            for (int k = 0; k < p.k_iters; k++) {
+            int mt, nt, bt, sp;
+            tile_coords(t, mt, nt, bt, sp);
+            const int k_begin = sp * p.k_iters_slice, k_end = k_begin + slice_blocks(sp);
+            for (int k = k_begin; k < k_end; k++) {
                 if (round > 0 && !mbar_wait(empty_bar + 8u * s, (uint32_t)((round & 1) ^ 1), abandon, p.status, 21)) { ok = false; break; }
                 const uint32_t bar = full_bar + 8u * s;
                 mbar_expect_tx(bar, stage_bytes);
@@ -141,7 +147,10 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             if (local >= 2 && !mbar_wait(acc_empty + 8u * buf, (uint32_t)(((local >> 1) - 1) & 1), abandon, p.status, 22)) break;
             tc_fence_after();
             const uint32_t acc = tmem_base + (uint32_t)(buf * p.bn);
-            for (int k = 0; k < p.k_iters; k++) {
+            int mt, nt, bt, sp;
+            tile_coords(t, mt, nt, bt, sp);
+            const int k_count = slice_blocks(sp);
+            for (int k = 0; k < k_count; k++) {
                 if (!mbar_wait(full_bar + 8u * s, (uint32_t)(round & 1), abandon, p.status, 23)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t a_addr = base + (uint32_t)s * stage_bytes;
@@ -166,8 +175,8 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         int local = 0, stage_buf = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, local++) {
-            int mt, nt, bt;
-            tile_coords(t, mt, nt, bt);
+            int mt, nt, bt, sp;
+            tile_coords(t, mt, nt, bt, sp);
             const int buf = local & 1;
             {
                 uint32_t good = 1;
@@ -243,7 +252,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (issuer) {
-                    tma_store_3d(&map_c, staging_base + (uint32_t)stage_buf * kGpStageTileBytes, col0, mt * kGpBlockM, bt);
+                    tma_store_3d(&map_c, staging_base + (uint32_t)stage_buf * kGpStageTileBytes, col0, mt * kGpBlockM, bt * p.splits + sp);
                     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 }
                 stage_buf ^= 1;
@@ -279,11 +288,17 @@ int classify_addend(const float* ptr, const int64_t* st) {
 
 }  // namespace
 
-std::shared_ptr<void> gemm_persistent_prepare(const GemmParams& g, uint32_t* status_word) {
-    if (g.splits > 1 || g.batch < 1 || g.m < 1 || g.n < 16 || g.k < 1) return nullptr;
-    // dense row-major C whose rows start on 16-byte boundaries
-    if (g.sc[2] != 1 || g.sc[1] % 4 != 0 || (g.batch > 1 && g.sc[0] % 4 != 0) || ((uintptr_t)g.c & 15) != 0) return nullptr;
-    const int m1 = classify_addend(g.add1, g.s1), m2 = classify_addend(g.add2, g.s2);
+std::shared_ptr<void> gemm_persistent_prepare(const GemmParams& g, uint32_t* status_word, int splits, int k_iters_slice) {
+    if (g.batch < 1 || g.m < 1 || g.n < 16 || g.k < 1 || splits < 1) return nullptr;
+    const bool split = splits > 1;
+    // dense row-major C whose rows start on 16-byte boundaries (split K: the partial sums [batch][slice][m][n],
+    // which the reduction kernel turns into C; addends and activation are applied there)
+    if (split) {
+        if (g.n % 4 != 0 || ((uintptr_t)g.scratch & 15) != 0 || g.scratch == nullptr) return nullptr;
+    } else if (g.sc[2] != 1 || g.sc[1] % 4 != 0 || (g.batch > 1 && g.sc[0] % 4 != 0) || ((uintptr_t)g.c & 15) != 0) {
+        return nullptr;
+    }
+    const int m1 = split ? 0 : classify_addend(g.add1, g.s1), m2 = split ? 0 : classify_addend(g.add2, g.s2);
     if (m1 == 3 || m2 == 3) return nullptr;
     auto l = std::make_shared<GemmPersistentLaunch>();
     GemmPersistentParams& p = l->p;
@@ -293,7 +308,10 @@ std::shared_ptr<void> gemm_persistent_prepare(const GemmParams& g, uint32_t* sta
     p.m_tiles = (int)((g.m + kGpBlockM - 1) / kGpBlockM);
     p.n_tiles = (int)((g.n + p.bn - 1) / p.bn);
     p.batch = (int)g.batch;
-    const int64_t total = (int64_t)p.m_tiles * p.n_tiles * g.batch;
+    p.splits = splits;
+    p.k_iters_slice = split ? k_iters_slice : p.k_iters;
+    if ((int64_t)(splits - 1) * p.k_iters_slice >= p.k_iters) return nullptr;   // an empty slice
+    const int64_t total = (int64_t)p.m_tiles * p.n_tiles * g.batch * splits;
     if (total > (1 << 30)) return nullptr;
     p.total_tiles = (int)total;
     p.m = g.m;
@@ -306,7 +324,7 @@ std::shared_ptr<void> gemm_persistent_prepare(const GemmParams& g, uint32_t* sta
     }
     p.add1_mode = m1;
     p.add2_mode = m2;
-    p.act = g.act;
+    p.act = split ? 0 : g.act;
     p.status = status_word;
     const int stage_bytes = kGpATileBytes + p.bn * 128;
     const int fixed = 1024 + 2 * kGpStageTileBytes + 16 * 8 + 64 + 64;
@@ -318,9 +336,9 @@ std::shared_ptr<void> gemm_persistent_prepare(const GemmParams& g, uint32_t* sta
     int64_t bdims[3] = {g.k, g.n, g.batch}, bstr[3] = {1, g.sb[2], g.sb[0]};
     int bbox[3] = {kGpBlockK, p.bn, 1};
     l->map_b = tc_make_map(g.b, 3, bdims, bstr, bbox, true);
-    int64_t cdims[3] = {g.n, g.m, g.batch}, cstr[3] = {1, g.sc[1], g.sc[0]};
+    int64_t cdims[3] = {g.n, g.m, g.batch * splits}, cstr[3] = {1, split ? g.n : g.sc[1], split ? g.m * g.n : g.sc[0]};
     int cbox[3] = {32, kGpBlockM, 1};
-    l->map_c = tc_make_store_map(g.c, 3, cdims, cstr, cbox);
+    l->map_c = tc_make_store_map(split ? g.scratch : g.c, 3, cdims, cstr, cbox);
     l->grid = dim3((unsigned)std::min<int64_t>(total, 148), 1, 1);
     return l;
 }

@@ -20,7 +20,8 @@ CUtensorMap tc_make_map(const void* base, int rank, const int64_t* dims, const i
 CUtensorMap tc_make_store_map(const void* base, int rank, const int64_t* dims, const int64_t* strides, const int* box);
 
 // Persistent matrix multiply (kernels/gemm_persistent.cu): null if the step does not qualify.
-std::shared_ptr<void> gemm_persistent_prepare(const GemmParams& g, uint32_t* status_word);
+// `splits` > 1: K is cut into slices of `k_iters_slice` 32-wide blocks whose partial tiles go to g.scratch.
+std::shared_ptr<void> gemm_persistent_prepare(const GemmParams& g, uint32_t* status_word, int splits, int k_iters_slice);
 int gemm_persistent_launch(const void* launch, cudaStream_t stream);
 
 // Convolution chain (kernels/conv_chain.cu): launch data built once the device pointers are known.

@@ -1080,6 +1080,19 @@ class Planner {
         size_t step;
         int bias_operand = -1, res_operand = -1;
     };
+    struct ChainHead {
+        size_t step;
+        int bias_operand = -1;
+    };
+
+    // every operand once; the trunk's result only if the chain stores it
+    static void chain_alg_bytes(Step& s) {
+        bool stored = false;
+        for (int l = 0; l < s.chain.n_layers; l++) stored = stored || (s.chain.flags[l] & kChainFlagStore);
+        s.alg_bytes = 0;
+        for (size_t o = 0; o < s.operands.size(); o++)
+            if (o != 1 || stored) s.alg_bytes += touched_bytes(s.operands[o]);
+    }
 
     bool chain_candidate(const Step& s, ChainLayer& l) const {
         if (s.kind != StepKind::Conv || !s.tensor_core) return false;
@@ -1109,10 +1122,33 @@ class Planner {
         return true;
     }
 
-    bool buffer_used_outside(int buf, size_t first, size_t last) const {
+    // A later 1x1 convolution of the chain's last result, with constant filter and bias: it can run as
+    // part of the chain's pointwise last layer (ConvChainParams: heads).
+    bool head_candidate(const Step& s, const Step& last, int& bias_operand) const {
+        if (s.kind != StepKind::Conv || !s.tensor_core || s.operands.size() < 3 || s.operands.size() > 4) return false;
+        const ConvParams& c = s.conv;
+        if (c.r != 1 || c.s != 1 || c.pad_y != 0 || c.pad_x != 0 || c.stride_y != 1 || c.stride_x != 1) return false;
+        if (c.c != last.conv.k || c.n != last.conv.n || c.h != last.conv.h || c.w != last.conv.w || c.k > 128) return false;
+        if (!s.operands[0].same_storage(last.operands[2])) return false;
+        if (c.act != (int32_t)Activation::None && c.act != (int32_t)Activation::Relu) return false;
+        const BufferInfo& wb = plan_.buffers[s.operands[1].buf];
+        if (wb.kind != BufKind::Const || wb.host_data == nullptr) return false;
+        bias_operand = -1;
+        if (s.operands.size() == 4) {
+            const PlanTensor& a = s.operands[3];
+            const BufferInfo& ab = plan_.buffers[a.buf];
+            const auto& st = a.ss.strides;
+            if (!(st[0] == 0 && st[2] == 0 && st[3] == 0 && ab.kind == BufKind::Const && ab.host_data != nullptr)) return false;
+            bias_operand = 3;
+        }
+        return true;
+    }
+
+    bool buffer_used_outside(int buf, size_t first, size_t last, const std::vector<uint8_t>* skip = nullptr) const {
         if (plan_.buffers[buf].always_live) return true;
         for (size_t i = 0; i < plan_.steps.size(); i++) {
             if (i >= first && i <= last) continue;
+            if (skip && (*skip)[i]) continue;
             for (auto& t : plan_.steps[i].operands)
                 if (t.buf == buf) return true;
         }
@@ -1123,8 +1159,13 @@ class Planner {
         if (opts_.math_mode != KN_MATH_TF32 || (opts_.flags & KN_FLAG_NO_CONV_CHAIN)) return;
         std::vector<Step>& steps = plan_.steps;
         std::vector<Step> result;
+        std::vector<uint8_t> consumed(steps.size(), 0);   // 1x1 convolutions that became heads of an earlier chain
         size_t i = 0;
         while (i < steps.size()) {
+            if (consumed[i]) {
+                i++;
+                continue;
+            }
             // longest run starting at i
             std::vector<ChainLayer> layers;
             for (size_t j = i; j < steps.size() && layers.size() < (size_t)kMaxChainLayers; j++) {
@@ -1172,7 +1213,25 @@ class Planner {
                 i++;
                 continue;
             }
-            Step chain = make_chain_step(steps, layers, hold, len);
+            // 1x1 convolutions of the chain's result anywhere later in the plan become heads of a pointwise
+            // last layer (their inputs are the result and constants, so they can run this early)
+            std::vector<ChainHead> heads;
+            if (len < (size_t)kMaxChainLayers) {
+                const Step& last = steps[layers[len - 1].step];
+                int channels = 0;
+                for (size_t j = layers[len - 1].step + 1; j < steps.size() && heads.size() < (size_t)kMaxChainHeads; j++) {
+                    ChainHead h;
+                    h.step = j;
+                    if (consumed[j] || !head_candidate(steps[j], last, h.bias_operand)) continue;
+                    if (channels + steps[j].conv.k > 128) continue;
+                    channels += steps[j].conv.k;
+                    heads.push_back(h);
+                }
+            }
+            for (auto& h : heads) consumed[h.step] = 1;
+            const bool store_trunk = heads.empty() || buffer_used_outside(steps[layers[len - 1].step].operands[2].buf, layers[0].step,
+                                                                           layers[len - 1].step, &consumed);
+            Step chain = make_chain_step(steps, layers, hold, len, heads, store_trunk);
             // The chain reads its input through element strides, so a copy that only exists to make the
             // input channels-last for the per-layer kernel is skipped: read the copy's source instead.
             if (!result.empty()) {
@@ -1184,8 +1243,7 @@ class Planner {
                     !buffer_used_outside(prev.operands[1].buf, prev_index, layers[len - 1].step)) {
                     chain.operands[0] = prev.operands[0];
                     for (int d = 0; d < 4; d++) chain.chain.s_in[d] = chain.operands[0].ss.strides[d];
-                    chain.alg_bytes = 0;
-                    for (auto& t : chain.operands) chain.alg_bytes += touched_bytes(t);
+                    chain_alg_bytes(chain);
                     result.pop_back();
                 }
             }
@@ -1196,7 +1254,7 @@ class Planner {
     }
 
     Step make_chain_step(const std::vector<Step>& steps, const std::vector<ChainLayer>& layers, const std::vector<uint8_t>& hold,
-                         size_t len) {
+                         size_t len, const std::vector<ChainHead>& heads, bool store_trunk) {
         const Step& first = steps[layers[0].step];
         const Step& last = steps[layers[len - 1].step];
         Step s;
@@ -1209,7 +1267,8 @@ class Planner {
         p.k = first.conv.k;
         p.h = first.conv.h;
         p.w = first.conv.w;
-        p.n_layers = (int32_t)len;
+        const size_t n_layers = len + (heads.empty() ? 0 : 1);
+        p.n_layers = (int32_t)n_layers;
         int64_t n_tiles = 0;
         for (size_t a = 0; a < len; a++) {
             const ConvParams& c = steps[layers[a].step].conv;
@@ -1220,9 +1279,15 @@ class Planner {
                                    (layers[a].res_operand >= 0 ? kChainFlagAddHeld : 0) | (hold[a] ? kChainFlagHold : 0));
             s.flops += steps[layers[a].step].flops;
         }
+        if (store_trunk) p.flags[len - 1] |= kChainFlagStore;
+        if (!heads.empty()) {
+            p.c_blocks[len] = (uint8_t)((p.k + 31) / 32);
+            p.flags[len] = kChainFlagPointwise;
+            n_tiles += p.c_blocks[len];
+        }
         // filter tiles: [tile][128][32] f32 (already TF32), zero beyond the real channels
         auto tiles = std::make_shared<std::vector<uint8_t>>((size_t)n_tiles * 128 * 32 * 4, 0);
-        auto bias = std::make_shared<std::vector<uint8_t>>(len * 128 * 4, 0);
+        auto bias = std::make_shared<std::vector<uint8_t>>(n_layers * 128 * 4, 0);
         float* tp = (float*)tiles->data();
         float* bp = (float*)bias->data();
         int64_t tile = 0;
@@ -1248,18 +1313,61 @@ class Planner {
                 for (int k = 0; k < c.k; k++) bp[a * 128 + k] = bsrc[b.offset + (int64_t)k * b.ss.strides[1]];
             }
         }
+        // the pointwise last layer: the heads' filters below one another (rows = output channels)
+        p.n_heads = (int32_t)heads.size();
+        std::vector<PlanTensor> head_outputs;
+        int row0 = 0;
+        for (size_t hi = 0; hi < heads.size(); hi++) {
+            const Step& st = steps[heads[hi].step];
+            const ConvParams& c = st.conv;
+            const PlanTensor& w = st.operands[1];
+            const float* src = (const float*)plan_.buffers[w.buf].host_data;
+            for (int k = 0; k < c.k; k++)
+                for (int ch = 0; ch < c.c; ch++) {
+                    float v = src[w.offset + (int64_t)k * w.ss.strides[0] + (int64_t)ch * w.ss.strides[1]];
+                    uint32_t bits;
+                    memcpy(&bits, &v, 4);
+                    if ((bits & 0x7F800000u) != 0x7F800000u) bits = (bits + 0x1000u) & 0xFFFFE000u;
+                    memcpy(&v, &bits, 4);
+                    const int row = row0 + k, cb = ch / 32, col = ch % 32;
+                    const int64_t pos = (int64_t)row * 32 + ((((col >> 2) ^ (row & 7)) << 2) | (col & 3));
+                    tp[(tile + cb) * 128 * 32 + pos] = v;
+                }
+            if (heads[hi].bias_operand >= 0) {
+                const PlanTensor& b = st.operands[heads[hi].bias_operand];
+                const float* bsrc = (const float*)plan_.buffers[b.buf].host_data;
+                for (int k = 0; k < c.k; k++) bp[len * 128 + row0 + k] = bsrc[b.offset + (int64_t)k * b.ss.strides[1]];
+            }
+            p.head_begin[hi] = row0;
+            p.head_relu[hi] = c.act == (int32_t)Activation::Relu;
+            for (int d = 0; d < 4; d++) p.head_s_out[hi][d] = st.operands[2].ss.strides[d];
+            head_outputs.push_back(st.operands[2]);
+            row0 += c.k;
+            s.flops += st.flops;
+        }
+        p.head_begin[heads.size()] = row0;
         PlanTensor t_tiles = alloc_const({n_tiles, 128, 32}, DType::F32, s.value, nullptr, tiles);
-        PlanTensor t_bias = alloc_const({(int64_t)len, 128}, DType::F32, s.value, nullptr, bias);
-        s.operands = {first.operands[0], last.operands[2], t_tiles, t_bias};
+        PlanTensor t_bias = alloc_const({(int64_t)n_layers, 128}, DType::F32, s.value, nullptr, bias);
+        // operand 1 is the trunk's result; when nothing reads it, it is neither stored nor allocated (the slot
+        // then repeats the first head's output)
+        s.operands = {first.operands[0], store_trunk ? last.operands[2] : head_outputs[0], t_tiles, t_bias};
         s.writes = {0, 1, 0, 0};
+        for (auto& t : head_outputs) {
+            s.operands.push_back(t);
+            s.writes.push_back(1);
+        }
         for (int d = 0; d < 4; d++) {
             p.s_in[d] = first.operands[0].ss.strides[d];
             p.s_out[d] = last.operands[2].ss.strides[d];
         }
         s.desc = "convchain layers=" + std::to_string(len) + " n=" + std::to_string(p.n) + " c=" + std::to_string(p.c_in) + " hw=" +
                  std::to_string(p.h) + "x" + std::to_string(p.w) + " k=" + std::to_string(p.k) + " rs=3x3 tf32";
-        s.alg_bytes = 0;
-        for (auto& t : s.operands) s.alg_bytes += touched_bytes(t);
+        if (!heads.empty()) {
+            s.desc += " heads=";
+            for (size_t hi = 0; hi < heads.size(); hi++) s.desc += (hi ? "+" : "") + std::to_string(p.head_begin[hi + 1] - p.head_begin[hi]);
+            if (!store_trunk) s.desc += " (trunk result not stored)";
+        }
+        chain_alg_bytes(s);
         return s;
     }
 

@@ -127,3 +127,67 @@ def test_full_tower_batch_256():
     assert_tensors_match(per_layer, fused, 1e-3, 1e-3, abs_scaled=True)
     expected = cpu_eval_graph(g.to_bytes(), 256, inputs)
     assert_tensors_match(expected, fused, 4e-3, 4e-3, abs_scaled=True)
+
+
+def tower_with_heads(channels, h, w, c_in, head_channels, head_relu, trunk_output=False, seed=0, computed_filter=False):
+    """Stem + one residual block, then one 1x1 convolution (+ bias, optional ReLU) per entry of
+    `head_channels`, each flattened and run through a softmax so that other steps sit between them."""
+    r = rng(seed)
+    g = tower(channels, 1, h, w, c_in, seed=seed)
+    cur = g.outputs[0]
+    g.outputs.clear()
+    for k, relu in zip(head_channels, head_relu):
+        wgt = g.constant_tensor((r.standard_normal((k, channels, 1, 1)) * np.sqrt(2.0 / channels)).astype(np.float32))
+        if computed_filter:
+            wgt = g.mul(wgt, g.view(g.input(shape(1)), shape(1, 1, 1, 1)))
+        y = g.add(g.conv(cur, wgt, 1, 1, 0, 0), g.constant_tensor((0.1 * r.standard_normal((1, k, 1, 1))).astype(np.float32)))
+        if relu:
+            y = g.relu(y)
+        g.output(y)
+        g.output(g.softmax(g.flatten(y, 1), 1))
+    if trunk_output:
+        g.output(cur)
+    return g
+
+
+def test_pointwise_heads_join_the_chain():
+    g, _ = resnet_tower()
+    d = steps(plan_describe(g, 256, MATH_TF32))
+    assert "heads=73+32 (trunk result not stored)" in d[0] and not any(" Conv/tc " in l for l in d)
+    # a trunk that is also a graph output is stored as well
+    d = steps(plan_describe(tower_with_heads(64, 8, 8, 8, [5, 70], [True, False], trunk_output=True), 4, MATH_TF32))
+    assert "heads=5+70" in d[0] and "not stored" not in d[0] and not any(" Conv/tc " in l for l in d)
+    # 128 accumulator lanes: a head that does not fit stays a step of its own
+    d = steps(plan_describe(tower_with_heads(32, 8, 8, 8, [100, 40, 20], [False] * 3), 4, MATH_TF32))
+    assert "heads=100+20" in d[0] and len([l for l in d if " Conv/tc " in l and "k=40" in l]) == 1
+    # a filter computed at run time cannot be laid out by the planner
+    d = steps(plan_describe(tower_with_heads(32, 8, 8, 8, [10], [False], computed_filter=True), 4, MATH_TF32))
+    assert "heads=" not in d[0] and len([l for l in d if " Conv/tc " in l and "rs=1x1" in l]) == 1
+
+
+HEAD_CASES = {
+    "policy_value": dict(channels=128, h=8, w=8, c_in=21, head_channels=[73, 32], head_relu=[False, False], batch=8),
+    "relu_and_plain": dict(channels=128, h=8, w=8, c_in=16, head_channels=[3, 64, 61], head_relu=[True, False, True], batch=5),
+    "trunk_kept": dict(channels=64, h=8, w=8, c_in=8, head_channels=[5, 70], head_relu=[True, False], trunk_output=True, batch=6),
+    "narrow_trunk_wide_head": dict(channels=32, h=5, w=7, c_in=32, head_channels=[128], head_relu=[False], batch=9),
+    "one_left_out": dict(channels=32, h=8, w=8, c_in=8, head_channels=[100, 40, 20], head_relu=[False, True, False], batch=4),
+}
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", sorted(HEAD_CASES))
+def test_heads_match_oracle_and_separate_kernels(name):
+    from kyanite_b200.executor import CudaExecutor
+    cfg = dict(HEAD_CASES[name])
+    batch = cfg.pop("batch")
+    g = tower_with_heads(seed=hash(name) % 1000, **cfg)
+    x = rng(6).standard_normal((batch, cfg["c_in"], cfg["h"], cfg["w"])).astype(np.float32)
+    assert "heads=" in steps(plan_describe(g, batch, MATH_TF32))[0]
+    expected = cpu_eval_graph(g.to_bytes(), batch, [x])
+    with CudaExecutor(0, g, batch, math_mode=MATH_TF32) as ex:
+        fused = ex.evaluate([x])
+        assert_tensors_match(expected, fused, 4e-3, 4e-3, abs_scaled=True)
+        for a, b in zip(fused, ex.evaluate([x])):
+            np.testing.assert_array_equal(a, b)
+    with CudaExecutor(0, g, batch, math_mode=MATH_TF32, flags=FLAG_NO_CONV_CHAIN) as ex:
+        assert_tensors_match(ex.evaluate([x]), fused, 1e-3, 1e-3, abs_scaled=True)

@@ -102,13 +102,14 @@ def test_matmul_with_few_columns(b, m, n, k, mode):
 
 
 @pytest.mark.parametrize("b,m,n,k", [(1, 5120, 1024, 128), (3, 300, 200, 100), (1, 130, 20, 40), (2, 256, 272, 64),
-                                     (1, 257, 18, 96), (1, 4096, 512, 1536)])
+                                     (1, 257, 18, 96), (1, 4096, 512, 1536), (1, 256, 256, 2048), (2, 130, 40, 1000)])
 def test_persistent_matmul_against_one_tile_kernel(b, m, n, k):
     """Matmuls without split-K run on the persistent kernel (one CTA per SM walking the tile list, two
     accumulators in tensor memory); `FLAG_NO_PERSISTENT_GEMM` selects the one-tile-per-CTA kernel instead.
     Both must match the oracle, with a per-column bias, a full residual addend and ReLU in the epilogue, on
     tile lists longer than the grid (160 tiles of 128 x 256), ragged edges, batches and a row length that
-    only the one-tile kernel accepts (n = 18)."""
+    only the one-tile kernel accepts (n = 18), and split-K shapes (the last two), whose partial tiles either
+    kernel writes for the reduction kernel."""
     from kyanite_b200.executor import FLAG_NO_PERSISTENT_GEMM
     g = Graph()
     a = g.input(shape(b, m, k))
