@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 
 #include "../kernels.h"
+#include "launch.cuh"
 
 namespace kn {
 
@@ -81,6 +82,7 @@ struct ConvProblem {
 
 template <class Problem>
 __global__ void __launch_bounds__(256) contract_simt_kernel(const __grid_constant__ Problem prob) {
+    pdl_enter();
     __shared__ float As[BK][BM + 4];
     __shared__ float Bs[BK][BN + 4];
     const int64_t M = prob.M(), N = prob.N(), K = prob.K();
@@ -146,7 +148,7 @@ int launch(const Problem& prob, int64_t M, int64_t N, int64_t batch, cudaStream_
     const int64_t gx = (M + BM - 1) / BM, gy = (N + BN - 1) / BN;
     if (gy > 65535 || batch > 65535 || gx > 0x7FFFFFFFll) return (int)cudaErrorInvalidValue;
     dim3 grid((unsigned)gx, (unsigned)gy, (unsigned)batch);
-    contract_simt_kernel<Problem><<<grid, 256, 0, stream>>>(prob);
+    launch_pdl(contract_simt_kernel<Problem>, dim3(grid), dim3(256), (size_t)(0), stream, prob);
     return (int)cudaGetLastError();
 }
 
@@ -156,6 +158,7 @@ int launch(const Problem& prob, int64_t M, int64_t N, int64_t batch, cudaStream_
 constexpr int kSkinnyMaxN = 8;
 
 __global__ void __launch_bounds__(256) gemm_skinny_kernel(const __grid_constant__ GemmParams p) {
+    pdl_enter();
     const int lane = threadIdx.x & 31;
     const int64_t row_id = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row_id >= p.batch * p.m) return;
@@ -165,6 +168,7 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const __grid_constant_
     float acc[kSkinnyMaxN];
 #pragma unroll
     for (int n = 0; n < kSkinnyMaxN; n++) acc[n] = 0.f;
+#pragma unroll 4
     for (int64_t k = lane; k < p.k; k += 32) {
         const float x = a[k * p.sa[2]];
 #pragma unroll
@@ -191,7 +195,7 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const __grid_constant_
 int launch_gemm_simt(const GemmParams& p, cudaStream_t stream) {
     if (p.n >= 1 && p.n <= kSkinnyMaxN && p.k >= 32 && p.batch * p.m > 0) {
         const int64_t rows = p.batch * p.m;
-        gemm_skinny_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(p);
+        launch_pdl(gemm_skinny_kernel, dim3((unsigned)((rows + 7) / 8)), dim3(256), (size_t)(0), stream, p);
         return (int)cudaGetLastError();
     }
     return launch(GemmProblem{p}, p.m, p.n, p.batch, stream);

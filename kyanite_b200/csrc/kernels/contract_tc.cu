@@ -28,6 +28,7 @@
 #include "../tc.h"
 #include "tc_host.h"
 #include "tc_ptx.cuh"
+#include "launch.cuh"
 
 namespace kn {
 
@@ -108,6 +109,7 @@ tc_contract_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_enter();   // nothing above touches global memory
 
     // tile coordinates
     int m0 = 0, n0_img = 0, h0 = 0, w0 = 0;
@@ -313,6 +315,7 @@ struct SplitKReduceParams {
 };
 
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const __grid_constant__ SplitKReduceParams p) {
+    pdl_enter();
     const int64_t total = p.batch * p.m * p.n;
     const int64_t step = (int64_t)gridDim.x * blockDim.x;
     for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += step) {
@@ -996,7 +999,7 @@ void tc_prepare_step(Step& step, uint32_t* status_word, int flags) {
 static int launch_splitk_reduce(const SplitKReduceParams& r, cudaStream_t stream) {
     const int64_t total = r.batch * r.m * r.n;
     const unsigned blocks = (unsigned)std::min<int64_t>((total + 255) / 256, 148 * 8);
-    splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(r);
+    launch_pdl(splitk_reduce_kernel, dim3(blocks), dim3(256), (size_t)(0), stream, r);
     return (int)cudaGetLastError();
 }
 
@@ -1038,7 +1041,7 @@ int tc_launch_step(const Step& step, cudaStream_t stream) {
         cfg.numAttrs = 1;
         return (int)cudaLaunchKernelEx(&cfg, tc_conv_cl_kernel, l.map_a, l.map_b, l.map_res, l.map_out, l.cl);
     }
-    tc_contract_kernel<<<l.grid, kThreads, l.smem_bytes, stream>>>(l.map_a, l.map_b, l.p);
+    launch_pdl(tc_contract_kernel, dim3(l.grid), dim3(kThreads), (size_t)(l.smem_bytes), stream, l.map_a, l.map_b, l.p);
     if (l.split_k) return launch_splitk_reduce(l.reduce, stream);
     return (int)cudaGetLastError();
 }
@@ -1173,12 +1176,12 @@ void matmul_static(const float* a, const float* b, float* c, int64_t m, int64_t 
     r.so[2] = 1;
 
     dim3 grid((unsigned)((m + kBlockM - 1) / kBlockM), (unsigned)((n + bn - 1) / bn), (unsigned)splits);
-    tc_contract_kernel<<<grid, kThreads, smem_bytes, stream>>>(map_a, map_b, p);
+    launch_pdl(tc_contract_kernel, dim3(grid), dim3(kThreads), (size_t)(smem_bytes), stream, map_a, map_b, p);
     cudaError_t err = cudaGetLastError();
     KN_CHECK(err == cudaSuccess, KN_ERR_CUDA, std::string("launch failed: ") + cudaGetErrorString(err));
     const int64_t total = m * n;
     const unsigned blocks = (unsigned)std::min<int64_t>((total + 255) / 256, 148 * 8);
-    splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(r);
+    launch_pdl(splitk_reduce_kernel, dim3(blocks), dim3(256), (size_t)(0), stream, r);
     err = cudaGetLastError();
     KN_CHECK(err == cudaSuccess, KN_ERR_CUDA, std::string("launch failed: ") + cudaGetErrorString(err));
 }

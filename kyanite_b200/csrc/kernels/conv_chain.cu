@@ -158,8 +158,6 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
     const uint32_t tmem_acc = *tmem_slot;
     const uint32_t tmem_held = tmem_acc + (uint32_t)p.n_mma;      // n_mma is a multiple of 16
 
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-
     if (warp == 0 && lane == 0) {
         // ---------------- filter producer: tiles are consumed in the order they are stored; the filter
         // is a constant of the plan, so nothing here waits for the previous kernel
@@ -200,6 +198,10 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
             ok = mbar_wait(act_bar, (uint32_t)(l & 1), abandon, p.status, 12);
             if (!ok) break;
             tc_fence_after();
+            // The next kernel of the stream may be scheduled once every CTA is in its last layer: early enough
+            // to hide that kernel's launch and set-up, late enough that its CTAs do not sit on this SM (blocked
+            // in griddepcontrol.wait) for the whole run.
+            if (l == p.n_layers - 1) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
             const int cbl = p.c_blocks[l];
             uint32_t accumulate = 0;
             const bool pointwise = (p.flags[l] & kChainFlagPointwise) != 0;

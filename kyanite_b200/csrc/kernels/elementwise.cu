@@ -14,6 +14,7 @@
 
 #include "../kernels.h"
 #include "../scalar_ops.h"
+#include "launch.cuh"
 
 namespace kn {
 
@@ -24,6 +25,7 @@ constexpr int kSlots = SCALAR_MAX_OPERANDS + SCALAR_MAX_INSTR;
 
 template <typename I>
 __global__ void __launch_bounds__(kThreads) scalar_generic_kernel(const __grid_constant__ ScalarParams p) {
+    pdl_enter();
     const I total = (I)p.total;
     const I step = (I)gridDim.x * (I)blockDim.x;
     for (I idx = (I)blockIdx.x * (I)blockDim.x + (I)threadIdx.x; idx < total; idx += step) {
@@ -63,6 +65,7 @@ __device__ __forceinline__ float4 splat(float v) { return make_float4(v, v, v, v
 
 template <typename I>
 __global__ void __launch_bounds__(kThreads) scalar_vec4_kernel(const __grid_constant__ ScalarParams p) {
+    pdl_enter();
     const int last = p.rank - 1;
     const I inner4 = (I)(p.dims[last] >> 2);
     const I total4 = (I)(p.total >> 2);
@@ -174,6 +177,7 @@ __device__ __forceinline__ void binary_v(BinaryOp op, Vec<V>& acc, const Vec<V>&
 
 template <int V, bool RANK1>
 __global__ void __launch_bounds__(kThreads) scalar_acc_kernel(const __grid_constant__ ScalarParams p) {
+    pdl_enter();
     extern __shared__ float4 spill[];   // [slot][position][thread]
     const int last = p.rank - 1;
     const uint32_t inner_v = (uint32_t)(p.dims[last] / (4 * V));   // groups of V float4 along the innermost axis
@@ -295,8 +299,8 @@ int launch_acc(const ScalarParams& p, cudaStream_t stream) {
             done[device] = true;
         }
     }
-    if (p.rank == 1) scalar_acc_kernel<V, true><<<grid, kThreads, smem, stream>>>(p);
-    else scalar_acc_kernel<V, false><<<grid, kThreads, smem, stream>>>(p);
+    if (p.rank == 1) launch_pdl(scalar_acc_kernel<V, true>, dim3(grid), dim3(kThreads), (size_t)(smem), stream, p);
+    else launch_pdl(scalar_acc_kernel<V, false>, dim3(grid), dim3(kThreads), (size_t)(smem), stream, p);
     return (int)cudaGetLastError();
 }
 
@@ -313,11 +317,11 @@ int launch_scalar(const ScalarParams& p, cudaStream_t stream) {
         return launch_acc<1>(p, stream);
     } else if (p.vec4) {
         const int64_t total4 = p.total >> 2;
-        if (total4 < (1ll << 31)) scalar_vec4_kernel<uint32_t><<<grid_for(total4), kThreads, 0, stream>>>(p);
-        else scalar_vec4_kernel<uint64_t><<<grid_for(total4), kThreads, 0, stream>>>(p);
+        if (total4 < (1ll << 31)) launch_pdl(scalar_vec4_kernel<uint32_t>, dim3(grid_for(total4)), dim3(kThreads), (size_t)(0), stream, p);
+        else launch_pdl(scalar_vec4_kernel<uint64_t>, dim3(grid_for(total4)), dim3(kThreads), (size_t)(0), stream, p);
     } else {
-        if (p.total < (1ll << 31)) scalar_generic_kernel<uint32_t><<<grid_for(p.total), kThreads, 0, stream>>>(p);
-        else scalar_generic_kernel<uint64_t><<<grid_for(p.total), kThreads, 0, stream>>>(p);
+        if (p.total < (1ll << 31)) launch_pdl(scalar_generic_kernel<uint32_t>, dim3(grid_for(p.total)), dim3(kThreads), (size_t)(0), stream, p);
+        else launch_pdl(scalar_generic_kernel<uint64_t>, dim3(grid_for(p.total)), dim3(kThreads), (size_t)(0), stream, p);
     }
     return (int)cudaGetLastError();
 }

@@ -7,6 +7,7 @@
 
 #include "../kernels.h"
 #include "../scalar_ops.h"
+#include "launch.cuh"
 
 namespace kn {
 
@@ -14,6 +15,7 @@ namespace {
 
 template <typename W>
 __global__ void __launch_bounds__(256) gather_kernel(const __grid_constant__ GatherParams p) {
+    pdl_enter();
     const int64_t step = (int64_t)gridDim.x * blockDim.x;
     for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < p.total; idx += step) {
         int64_t rem = idx, in_off = 0, out_off = 0;
@@ -41,6 +43,7 @@ __global__ void __launch_bounds__(256) gather_kernel(const __grid_constant__ Gat
 // least 16 bytes in both tensors.  One warp per output row: the index is read once, the row moves as
 // 128-bit words.  `rows` = product of the extents up to and including the axis.
 __global__ void __launch_bounds__(256) gather_rows_kernel(const __grid_constant__ GatherParams p, int64_t rows, int row_vec4) {
+    pdl_enter();
     const int lane = threadIdx.x & 31;
     const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
     for (int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows; row += warps) {
@@ -87,7 +90,7 @@ int launch_gather(const GatherParams& p, cudaStream_t stream) {
             const int64_t rows = p.total / inner;
             int64_t blocks = (rows + 7) / 8;
             if (blocks > 148 * 16) blocks = 148 * 16;
-            gather_rows_kernel<<<(unsigned)blocks, 256, 0, stream>>>(p, rows, (int)(row_bytes / 16));
+            launch_pdl(gather_rows_kernel, dim3((unsigned)blocks), dim3(256), (size_t)(0), stream, p, rows, (int)(row_bytes / 16));
             return (int)cudaGetLastError();
         }
     }
@@ -95,10 +98,10 @@ int launch_gather(const GatherParams& p, cudaStream_t stream) {
     if (blocks > 148 * 8) blocks = 148 * 8;
     const unsigned grid = (unsigned)blocks;
     switch (p.elem_size) {
-        case 1: gather_kernel<uint8_t><<<grid, 256, 0, stream>>>(p); break;
-        case 2: gather_kernel<uint16_t><<<grid, 256, 0, stream>>>(p); break;
-        case 4: gather_kernel<uint32_t><<<grid, 256, 0, stream>>>(p); break;
-        case 8: gather_kernel<uint64_t><<<grid, 256, 0, stream>>>(p); break;
+        case 1: launch_pdl(gather_kernel<uint8_t>, dim3(grid), dim3(256), (size_t)(0), stream, p); break;
+        case 2: launch_pdl(gather_kernel<uint16_t>, dim3(grid), dim3(256), (size_t)(0), stream, p); break;
+        case 4: launch_pdl(gather_kernel<uint32_t>, dim3(grid), dim3(256), (size_t)(0), stream, p); break;
+        case 8: launch_pdl(gather_kernel<uint64_t>, dim3(grid), dim3(256), (size_t)(0), stream, p); break;
         default: return (int)cudaErrorInvalidValue;
     }
     return (int)cudaGetLastError();

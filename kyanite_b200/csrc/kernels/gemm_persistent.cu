@@ -27,6 +27,7 @@
 #include "../tc.h"
 #include "tc_host.h"
 #include "tc_ptx.cuh"
+#include "launch.cuh"
 
 namespace kn {
 
@@ -104,6 +105,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // nothing above touches global memory
 
     // tile t -> (row block, column block, batch): row blocks fastest
     auto tile_coords = [&](int t, int& mt, int& nt, int& bt, int& sp) {
@@ -150,6 +152,8 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             int mt, nt, bt, sp;
             tile_coords(t, mt, nt, bt, sp);
             const int k_count = slice_blocks(sp);
+            // last tile of this CTA: the next kernel of the stream may be scheduled (once every CTA says so)
+            if (t + (int)gridDim.x >= p.total_tiles) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
             for (int k = 0; k < k_count; k++) {
                 if (!mbar_wait(full_bar + 8u * s, (uint32_t)(round & 1), abandon, p.status, 23)) { ok = false; break; }
                 tc_fence_after();
@@ -357,7 +361,7 @@ int gemm_persistent_launch(const void* launch, cudaStream_t stream) {
             done[device] = true;
         }
     }
-    gemm_persistent_kernel<<<l.grid, kGpThreads, l.smem_bytes, stream>>>(l.map_a, l.map_b, l.map_c, l.p);
+    launch_pdl(gemm_persistent_kernel, dim3(l.grid), dim3(kGpThreads), (size_t)(l.smem_bytes), stream, l.map_a, l.map_b, l.map_c, l.p);
     return (int)cudaGetLastError();
 }
 

@@ -10,6 +10,7 @@
 
 #include "../kernels.h"
 #include "../scalar_ops.h"
+#include "launch.cuh"
 
 namespace kn {
 
@@ -59,6 +60,7 @@ __device__ __forceinline__ float row_reduce(float v, float* smem) {
 // ------------------------------------------------------------------ softmax
 template <int TPR, int ITEMS>
 __global__ void __launch_bounds__(256) softmax_cached_kernel(const __grid_constant__ RowParams p) {
+    pdl_enter();
     __shared__ float smem[8];
     const int rows_per_block = blockDim.x / TPR;
     const int64_t row = (int64_t)blockIdx.x * rows_per_block + threadIdx.x / TPR;
@@ -96,6 +98,7 @@ __global__ void __launch_bounds__(256) softmax_cached_kernel(const __grid_consta
 
 // rows longer than a block can keep in registers: three sweeps over global memory
 __global__ void __launch_bounds__(256) softmax_streaming_kernel(const __grid_constant__ RowParams p) {
+    pdl_enter();
     __shared__ float smem[8];
     const int64_t row = blockIdx.x;
     int64_t oi, oo;
@@ -121,6 +124,7 @@ __device__ __forceinline__ float ln_load(const RowParams& p, const float* in0, c
 
 template <int TPR, int ITEMS>
 __global__ void __launch_bounds__(256) layernorm_cached_kernel(const __grid_constant__ RowParams p) {
+    pdl_enter();
     __shared__ float smem[8];
     const int rows_per_block = blockDim.x / TPR;
     const int64_t row = (int64_t)blockIdx.x * rows_per_block + threadIdx.x / TPR;
@@ -160,6 +164,7 @@ __global__ void __launch_bounds__(256) layernorm_cached_kernel(const __grid_cons
 }
 
 __global__ void __launch_bounds__(256) layernorm_streaming_kernel(const __grid_constant__ RowParams p) {
+    pdl_enter();
     __shared__ float smem[8];
     const int64_t row = blockIdx.x;
     int64_t oi, oo;
@@ -188,6 +193,7 @@ __global__ void __launch_bounds__(256) layernorm_streaming_kernel(const __grid_c
 // between the statistics and the normalising pass: one read, one write.
 template <int TPR, int ITEMS4>
 __global__ void __launch_bounds__(256) softmax_vec4_kernel(const __grid_constant__ RowParams p) {
+    pdl_enter();
     __shared__ float smem[8];
     const int rows_per_block = blockDim.x / TPR;
     const int64_t row = (int64_t)blockIdx.x * rows_per_block + threadIdx.x / TPR;
@@ -230,6 +236,7 @@ __global__ void __launch_bounds__(256) softmax_vec4_kernel(const __grid_constant
 
 template <int TPR, int ITEMS4>
 __global__ void __launch_bounds__(256) layernorm_vec4_kernel(const __grid_constant__ RowParams p) {
+    pdl_enter();
     __shared__ float smem[8];
     const int rows_per_block = blockDim.x / TPR;
     const int64_t row = (int64_t)blockIdx.x * rows_per_block + threadIdx.x / TPR;
@@ -280,6 +287,7 @@ __global__ void __launch_bounds__(256) layernorm_vec4_kernel(const __grid_consta
 // Sum / mean of f32 over a contiguous innermost axis: TPO threads per output, float4 loads.
 template <int TPO>
 __global__ void __launch_bounds__(256) reduce_f32_rows_kernel(const __grid_constant__ ReduceParams p) {
+    pdl_enter();
     __shared__ float smem[8];
     const int outs_per_block = 256 / TPO;
     const int64_t o = (int64_t)blockIdx.x * outs_per_block + threadIdx.x / TPO;
@@ -359,6 +367,7 @@ __device__ __forceinline__ BinaryOp reduce_binary(ReduceOp op) {
 // TPO threads cooperate on one output element.
 template <int TPO>
 __global__ void __launch_bounds__(256) reduce_kernel(const __grid_constant__ ReduceParams p) {
+    pdl_enter();
     __shared__ uint64_t smem[8];
     const int outs_per_block = 256 / TPO;
     const int64_t o = (int64_t)blockIdx.x * outs_per_block + threadIdx.x / TPO;
@@ -406,7 +415,7 @@ static bool row_vec4_ok(const RowParams& p) {
 }
 
 #define KN_ROW_VEC4_CASE(KERNEL, TPR, N)                     \
-    case N: KERNEL<TPR, N><<<grid, 256, 0, stream>>>(p); break;
+    case N: launch_pdl(KERNEL<TPR, N>, dim3(grid), dim3(256), (size_t)(0), stream, p); break;
 
 #define KN_ROW_DISPATCH(KERNEL, VEC4, STREAMING)                                                               \
     if (p.rows == 0 || p.len == 0) return 0;                                                                   \
@@ -420,14 +429,14 @@ static bool row_vec4_ok(const RowParams& p) {
                 KN_ROW_VEC4_CASE(VEC4, 32, 1) KN_ROW_VEC4_CASE(VEC4, 32, 2) KN_ROW_VEC4_CASE(VEC4, 32, 3)      \
                 KN_ROW_VEC4_CASE(VEC4, 32, 4) KN_ROW_VEC4_CASE(VEC4, 32, 5) KN_ROW_VEC4_CASE(VEC4, 32, 6)      \
                 KN_ROW_VEC4_CASE(VEC4, 32, 7)                                                                  \
-                default: VEC4<32, 8><<<grid, 256, 0, stream>>>(p); break;                                      \
+                default: launch_pdl(VEC4<32, 8>, dim3(grid), dim3(256), (size_t)(0), stream, p); break;                                      \
             }                                                                                                  \
         } else {                                                                                               \
             const unsigned grid = (unsigned)p.rows;                                                            \
             switch ((len4 + 255) / 256) {                                                                      \
                 KN_ROW_VEC4_CASE(VEC4, 256, 2) KN_ROW_VEC4_CASE(VEC4, 256, 3) KN_ROW_VEC4_CASE(VEC4, 256, 4)   \
                 KN_ROW_VEC4_CASE(VEC4, 256, 5) KN_ROW_VEC4_CASE(VEC4, 256, 6) KN_ROW_VEC4_CASE(VEC4, 256, 7)   \
-                default: VEC4<256, 8><<<grid, 256, 0, stream>>>(p); break;                                     \
+                default: launch_pdl(VEC4<256, 8>, dim3(grid), dim3(256), (size_t)(0), stream, p); break;                                     \
             }                                                                                                  \
         }                                                                                                      \
         return (int)cudaGetLastError();                                                                        \
@@ -435,19 +444,19 @@ static bool row_vec4_ok(const RowParams& p) {
     if (len <= 1024) {                                                                                         \
         const int rows_per_block = 8;                                                                          \
         const unsigned grid = (unsigned)((p.rows + rows_per_block - 1) / rows_per_block);                      \
-        if (len <= 32) KERNEL<32, 1><<<grid, 256, 0, stream>>>(p);                                             \
-        else if (len <= 64) KERNEL<32, 2><<<grid, 256, 0, stream>>>(p);                                        \
-        else if (len <= 128) KERNEL<32, 4><<<grid, 256, 0, stream>>>(p);                                       \
-        else if (len <= 256) KERNEL<32, 8><<<grid, 256, 0, stream>>>(p);                                       \
-        else if (len <= 512) KERNEL<32, 16><<<grid, 256, 0, stream>>>(p);                                      \
-        else KERNEL<32, 32><<<grid, 256, 0, stream>>>(p);                                                      \
+        if (len <= 32) launch_pdl(KERNEL<32, 1>, dim3(grid), dim3(256), (size_t)(0), stream, p);                                             \
+        else if (len <= 64) launch_pdl(KERNEL<32, 2>, dim3(grid), dim3(256), (size_t)(0), stream, p);                                        \
+        else if (len <= 128) launch_pdl(KERNEL<32, 4>, dim3(grid), dim3(256), (size_t)(0), stream, p);                                       \
+        else if (len <= 256) launch_pdl(KERNEL<32, 8>, dim3(grid), dim3(256), (size_t)(0), stream, p);                                       \
+        else if (len <= 512) launch_pdl(KERNEL<32, 16>, dim3(grid), dim3(256), (size_t)(0), stream, p);                                      \
+        else launch_pdl(KERNEL<32, 32>, dim3(grid), dim3(256), (size_t)(0), stream, p);                                                      \
     } else if (len <= 8192) {                                                                                  \
         const unsigned grid = (unsigned)p.rows;                                                                \
-        if (len <= 2048) KERNEL<256, 8><<<grid, 256, 0, stream>>>(p);                                          \
-        else if (len <= 4096) KERNEL<256, 16><<<grid, 256, 0, stream>>>(p);                                    \
-        else KERNEL<256, 32><<<grid, 256, 0, stream>>>(p);                                                     \
+        if (len <= 2048) launch_pdl(KERNEL<256, 8>, dim3(grid), dim3(256), (size_t)(0), stream, p);                                          \
+        else if (len <= 4096) launch_pdl(KERNEL<256, 16>, dim3(grid), dim3(256), (size_t)(0), stream, p);                                    \
+        else launch_pdl(KERNEL<256, 32>, dim3(grid), dim3(256), (size_t)(0), stream, p);                                                     \
     } else {                                                                                                   \
-        STREAMING<<<(unsigned)p.rows, 256, 0, stream>>>(p);                                                    \
+        launch_pdl(STREAMING, dim3((unsigned)p.rows), dim3(256), (size_t)(0), stream, p);                                                    \
     }                                                                                                          \
     return (int)cudaGetLastError();
 
@@ -466,17 +475,17 @@ int launch_reduce(const ReduceParams& p, cudaStream_t stream) {
                 p.n_red < (1ll << 31) && ((uintptr_t)p.in & 15) == 0 && p.n_out <= 0x7FFFFFFFll;
     for (int d = 0; d < p.kept_rank && rows; d++) rows = p.kept_in_strides[d] % 4 == 0;
     if (rows) {
-        if (p.n_red >= 8192) reduce_f32_rows_kernel<256><<<(unsigned)p.n_out, 256, 0, stream>>>(p);
-        else reduce_f32_rows_kernel<32><<<(unsigned)((p.n_out + 7) / 8), 256, 0, stream>>>(p);
+        if (p.n_red >= 8192) launch_pdl(reduce_f32_rows_kernel<256>, dim3((unsigned)p.n_out), dim3(256), (size_t)(0), stream, p);
+        else launch_pdl(reduce_f32_rows_kernel<32>, dim3((unsigned)((p.n_out + 7) / 8)), dim3(256), (size_t)(0), stream, p);
         return (int)cudaGetLastError();
     }
     if (p.n_red >= 2048) {
         if (p.n_out > 0x7FFFFFFFll) return (int)cudaErrorInvalidValue;
-        reduce_kernel<256><<<(unsigned)p.n_out, 256, 0, stream>>>(p);
+        launch_pdl(reduce_kernel<256>, dim3((unsigned)p.n_out), dim3(256), (size_t)(0), stream, p);
     } else {
         const int64_t grid = (p.n_out + 7) / 8;
         if (grid > 0x7FFFFFFFll) return (int)cudaErrorInvalidValue;
-        reduce_kernel<32><<<(unsigned)grid, 256, 0, stream>>>(p);
+        launch_pdl(reduce_kernel<32>, dim3((unsigned)grid), dim3(256), (size_t)(0), stream, p);
     }
     return (int)cudaGetLastError();
 }
