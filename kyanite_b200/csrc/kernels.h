@@ -19,7 +19,8 @@ constexpr int DEV_MAX_RANK = 8;
 constexpr int SCALAR_MAX_OPERANDS = 10;
 constexpr int SCALAR_MAX_INSTR = 40;
 
-enum class Activation : int32_t { None = 0, Relu = 1 };
+// Gelu is the exact form  x * 0.5 * (1 + erf(x / sqrt(2)))
+enum class Activation : int32_t { None = 0, Relu = 1, Gelu = 2 };
 
 // ---- fused elementwise ("scalar") kernel: replaces kn-cuda-eval/src/autokernel/scalar.{rs,cu}.
 // The body is a small register program instead of generated C source: slot i < n_loads holds the

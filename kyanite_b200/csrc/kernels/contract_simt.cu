@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 
 #include "../kernels.h"
+#include "epilogue.cuh"
 #include "launch.cuh"
 
 namespace kn {
@@ -16,7 +17,7 @@ namespace {
 constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
 
 __device__ __forceinline__ float apply_epilogue(float v, int act, int round_tf32) {
-    if (act == (int)Activation::Relu) v = fmaxf(v, 0.0f);
+    v = apply_activation(v, act);
     if (round_tf32) {
         uint32_t u;
         asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v));

@@ -28,6 +28,7 @@
 #include "../tc.h"
 #include "tc_host.h"
 #include "tc_ptx.cuh"
+#include "epilogue.cuh"
 #include "launch.cuh"
 
 namespace kn {
@@ -62,7 +63,7 @@ struct TcParams {
 using namespace tcp;   // PTX wrappers (kernels/tc_ptx.cuh)
 
 __device__ __forceinline__ float finish(float v, int act, int round_tf32) {
-    if (act == (int)Activation::Relu) v = fmaxf(v, 0.0f);
+    v = apply_activation(v, act);
     if (round_tf32) {
         uint32_t u;
         asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v));

@@ -646,7 +646,61 @@ class Planner {
         std::vector<int> addends;
     };
 
-    // Matches  relu?( add*( view?( conv | matmul ) ) )  rooted at `root`
+    // `root` = y * 0.5 * (1 + erf(y * sqrt(1/2))) as a product tree in any association, every node of it
+    // hidden and used by this expression only (y itself twice: as a factor and inside erf): returns y, else -1.
+    int match_gelu(int root) {
+        const ValueInfo& ri = g_.values[root];
+        if (ri.dtype != DType::F32 || ri.op != OpKind::Binary || ri.binary_op != BinaryOp::Mul) return -1;
+        // flatten the product
+        std::vector<int> factors, stack = {ri.inputs[1], ri.inputs[0]};
+        while (!stack.empty()) {
+            const int v = stack.back();
+            stack.pop_back();
+            const ValueInfo& vi = g_.values[v];
+            if (vi.op == OpKind::Binary && vi.binary_op == BinaryOp::Mul && fusable(v) && !g_.as_single_const(v)) {
+                stack.push_back(vi.inputs[1]);
+                stack.push_back(vi.inputs[0]);
+            } else {
+                factors.push_back(v);
+            }
+            if (factors.size() > 3) return -1;
+        }
+        if (factors.size() != 3) return -1;
+        int half = -1, y = -1, gate = -1;
+        for (int v : factors) {
+            auto c = g_.as_single_const(v);
+            const ValueInfo& vi = g_.values[v];
+            if (c && half < 0 && c->as_f32() == 0.5f) half = v;
+            else if (vi.op == OpKind::Binary && vi.binary_op == BinaryOp::Add && fusable(v) && gate < 0 && !c) gate = v;
+            else if (y < 0) y = v;
+            else return -1;
+        }
+        if (half < 0 || y < 0 || gate < 0) return -1;
+        // gate = 1 + erf(y * c)
+        const ValueInfo& gi = g_.values[gate];
+        int erf = -1;
+        for (int side = 0; side < 2; side++) {
+            auto one = g_.as_single_const(gi.inputs[side]);
+            if (one && one->as_f32() == 1.0f) erf = gi.inputs[1 - side];
+        }
+        if (erf < 0) return -1;
+        const ValueInfo& ei = g_.values[erf];
+        if (ei.op != OpKind::Unary || ei.unary_op != UnaryOp::Erf || !fusable(erf)) return -1;
+        const int arg = ei.inputs[0];
+        const ValueInfo& ai = g_.values[arg];
+        if (ai.op != OpKind::Binary || ai.binary_op != BinaryOp::Mul || !fusable(arg)) return -1;
+        bool scaled = false;
+        for (int side = 0; side < 2; side++) {
+            auto c = g_.as_single_const(ai.inputs[side]);
+            if (c && std::fabs(c->as_f32() - 0.70710678f) < 1e-6f && ai.inputs[1 - side] == y) scaled = true;
+        }
+        if (!scaled) return -1;
+        // y feeds exactly the product and the erf argument, has the product's shape, and is a hidden value
+        if (!g_.is_hidden_with_uses(y, 2) || g_.values[y].dtype != DType::F32 || shape_of(y) != shape_of(root)) return -1;
+        return y;
+    }
+
+    // Matches  (relu | gelu)?( add*( view?( conv | matmul ) ) )  rooted at `root`
     // (generalises try_visit_fused_conv, kn-cuda-eval/src/planner.rs:669-833, to MatMul and to
     // addends of any broadcast shape).
     std::optional<Epilogue> match_epilogue(int root) {
@@ -654,7 +708,11 @@ class Planner {
         if (ri.dtype != DType::F32) return std::nullopt;
         Epilogue e;
         int curr = root;
-        if (ri.op == OpKind::Binary && ri.binary_op == BinaryOp::Max) {
+        if (int y = match_gelu(root); y >= 0) {
+            if (chain_end(y) < 0) return std::nullopt;
+            curr = y;
+            e.act = Activation::Gelu;
+        } else if (ri.op == OpKind::Binary && ri.binary_op == BinaryOp::Max) {
             int l = ri.inputs[0], r = ri.inputs[1];
             if (g_.is_const_zero(r) && fusable(l) && chain_end(l) >= 0) { curr = l; e.act = Activation::Relu; }
             else if (g_.is_const_zero(l) && fusable(r) && chain_end(r) >= 0) { curr = r; e.act = Activation::Relu; }
@@ -799,7 +857,8 @@ class Planner {
             s.desc = "conv n=" + std::to_string(p.n) + " c=" + std::to_string(p.c) + " hw=" + std::to_string(p.h) + "x" +
                      std::to_string(p.w) + " k=" + std::to_string(p.k) + " rs=" + std::to_string(p.r) + "x" + std::to_string(p.s);
         }
-        s.desc += std::string(" +") + std::to_string(addends.size()) + (m->act == Activation::Relu ? " relu" : "");
+        s.desc += std::string(" +") + std::to_string(addends.size()) +
+                  (m->act == Activation::Relu ? " relu" : (m->act == Activation::Gelu ? " gelu" : ""));
         if (tensor_core) s.desc += " tf32";
         if (s.kind == StepKind::Gemm && s.gemm.splits > 1) s.desc += " splitk=" + std::to_string(s.gemm.splits);
         int64_t total = 1;
@@ -1099,6 +1158,7 @@ class Planner {
         const ConvParams& c = s.conv;
         if (c.r != 3 || c.s != 3 || c.pad_y != 1 || c.pad_x != 1 || c.stride_y != 1 || c.stride_x != 1) return false;
         if (c.k > 128 || c.c > 128 || c.oh != c.h || c.ow != c.w) return false;
+        if (c.act != (int32_t)Activation::None && c.act != (int32_t)Activation::Relu) return false;
         if (!tc_chain_geometry(c.h, c.w, c.n, 4, nullptr)) return false;
         // the filter must be a planner-made tap-major constant [3][3][K][C_pad] whose bytes are still on the host
         const PlanTensor& w = s.operands[1];

@@ -97,7 +97,7 @@ def case_permute_copy(rng):
     return g, 0, [rng.standard_normal((256, 512, 12, 64)).astype(np.float32)]
 
 
-def _linear_case(m, n, k, bias=True, relu=False):
+def _linear_case(m, n, k, bias=True, relu=False, gelu=False):
     def build(rng):
         g = Graph()
         x = g.input(shape(m, k))
@@ -106,9 +106,13 @@ def _linear_case(m, n, k, bias=True, relu=False):
             y = g.add(y, _const(g, rng, 1, n))
         if relu:
             y = g.relu(y)
+        if gelu:
+            gate = g.add(g.unary(UnaryOp.ERF, g.mul(y, g.scalar(1.0 / math.sqrt(2.0)))), g.scalar(1.0))
+            y = g.mul(g.mul(y, g.scalar(0.5)), gate)
         g.output(y)
         return g, 0, [rng.standard_normal((m, k)).astype(np.float32)]
-    build.__doc__ = f"Linear layer [{m}, {k}] x [{k}, {n}]" + (" + bias" if bias else "") + (" + relu" if relu else "")
+    build.__doc__ = (f"Linear layer [{m}, {k}] x [{k}, {n}]" + (" + bias" if bias else "") + (" + relu" if relu else "") +
+                     (" + GELU(erf) in the epilogue" if gelu else ""))
     return build
 
 
@@ -149,6 +153,7 @@ CASES = {
     "permute_copy": case_permute_copy,
     "linear_bert_qkv": _linear_case(16384, 768, 768),
     "linear_bert_ffn": _linear_case(16384, 3072, 768),
+    "linear_bert_ffn_gelu": _linear_case(16384, 3072, 768, gelu=True),
     "linear_llama_proj": _linear_case(2048, 4096, 4096, bias=False),
     "linear_llama_ffn": _linear_case(2048, 11008, 4096, bias=False),
     "attention_scores": case_attention_scores,

@@ -128,3 +128,39 @@ def test_persistent_matmul_against_one_tile_kernel(b, m, n, k):
                 assert_tensors_match(want, got[flags], tol_abs=4e-3, tol_rel=4e-3, abs_scaled=True)
     # same operand rounding and the same order of the K blocks in both kernels
     assert_tensors_match(got[0], got[FLAG_NO_PERSISTENT_GEMM], tol_abs=1e-5, tol_rel=1e-5, abs_scaled=True)
+
+
+@pytest.mark.parametrize("mode", [MATH_F32, MATH_TF32], ids=["f32", "tf32"])
+@pytest.mark.parametrize("m,n,k", [(300, 200, 100), (256, 256, 2048), (64, 5, 96), (33, 18, 40)])
+def test_matmul_with_gelu_epilogue(m, n, k, mode):
+    """bias + exact GELU as the matmul's activation: persistent kernel, split-K reduction, few-column kernel,
+    one-tile kernel (n = 18), and the exact-f32 kernels."""
+    import math
+    from kyanite_b200.executor import FLAG_NO_PERSISTENT_GEMM
+    from kyanite_b200.graph import UnaryOp
+    g = Graph()
+    a = g.input(shape(m, k))
+    y = g.add(g.linear(a, g.constant_tensor(rng(2, n, k) * 0.2)), g.constant_tensor(rng(3, 1, n)))
+    gate = g.add(g.unary(UnaryOp.ERF, g.mul(y, g.scalar(1.0 / math.sqrt(2.0)))), g.scalar(1.0))
+    g.output(g.mul(g.mul(y, g.scalar(0.5)), gate))
+    assert " gelu" in plan_describe(g.to_bytes(), 0, math_mode=mode)
+    check(g, 0, [rng(1, m, k)], mode=mode)
+    blob = g.to_bytes()
+    want = cpu_eval_graph(blob, 0, [rng(1, m, k)])
+    with CudaExecutor(0, blob, 0, math_mode=mode, flags=FLAG_NO_PERSISTENT_GEMM) as ex:
+        assert_tensors_match(want, ex.evaluate([rng(1, m, k)]), tol_abs=4e-3, tol_rel=4e-3, abs_scaled=True)
+
+
+def test_conv_with_gelu_epilogue():
+    import math
+    from kyanite_b200.graph import UnaryOp
+    g = Graph()
+    x = g.input(shape(BATCH, 24, 8, 8))
+    y = g.add(g.conv(x, g.constant_tensor(rng(1, 40, 24, 3, 3) * 0.1), 1, 1, 1, 1), g.constant_tensor(rng(2, 1, 40, 1, 1)))
+    gate = g.add(g.unary(UnaryOp.ERF, g.mul(y, g.scalar(1.0 / math.sqrt(2.0)))), g.scalar(1.0))
+    z = g.mul(g.mul(y, g.scalar(0.5)), gate)
+    # a second convolution after it: the first one must not become part of a chain that only knows ReLU
+    g.output(g.relu(g.conv(z, g.constant_tensor(rng(3, 40, 40, 3, 3) * 0.1), 1, 1, 1, 1)))
+    d = plan_describe(g.to_bytes(), 3, math_mode=MATH_TF32)
+    assert " gelu" in d and "ConvChain" not in d
+    check(g, 3, [rng(4, 3, 24, 8, 8)])

@@ -92,3 +92,39 @@ def test_deep_chain_plans():
         cur = g.softmax(g.add(cur, g.scalar(float(i % 3) + 0.5)), 1)
     g.output(cur)
     assert len(steps_of(plan_describe(g, 2))) == 6000
+
+
+def test_gelu_folds_into_the_contraction():
+    """x * 0.5 * (1 + erf(x / sqrt(2))) after a linear layer or a convolution is the step's activation, in
+    either association of the product; a tanh-free variant with another constant is not."""
+    import math
+    import numpy as np
+    from kyanite_b200.graph import Graph, UnaryOp, shape
+    rng = np.random.Generator(np.random.PCG64(0))
+
+    def build(form, scale=1.0 / math.sqrt(2.0)):
+        g = Graph()
+        x = g.input(shape(64, 32))
+        y = g.add(g.linear(x, g.constant_tensor(rng.standard_normal((48, 32)).astype(np.float32))),
+                  g.constant_tensor(rng.standard_normal((1, 48)).astype(np.float32)))
+        gate = g.add(g.unary(UnaryOp.ERF, g.mul(y, g.scalar(scale))), g.scalar(1.0))
+        if form == 0:
+            out = g.mul(g.mul(y, g.scalar(0.5)), gate)
+        elif form == 1:
+            out = g.mul(g.scalar(0.5), g.mul(gate, y))
+        else:
+            out = g.mul(g.mul(y, gate), g.scalar(0.5))
+        g.output(out)
+        return g
+
+    for form in range(3):
+        for mode in (MATH_F32, MATH_TF32):
+            s = steps_of(plan_describe(build(form), 0, mode))
+            assert len(s) == 1 and " gelu" in s[0], s
+    s = steps_of(plan_describe(build(0, scale=0.5), 0, MATH_TF32))
+    assert len(s) == 2 and " gelu" not in s[0]
+    # the BERT-shaped encoder: no elementwise step is left for the feed-forward activation
+    from kyanite_b200.configs import bert_encoder
+    g, _ = bert_encoder(layers=1, hidden=64, heads=4, ffn=128, vocab=100, seq=16)
+    text = plan_describe(g, 2, MATH_TF32)
+    assert sum(" gelu" in l for l in steps_of(text)) == 1
