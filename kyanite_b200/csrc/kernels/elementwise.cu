@@ -304,10 +304,100 @@ int launch_acc(const ScalarParams& p, cudaStream_t stream) {
     return (int)cudaGetLastError();
 }
 
+// ---------------------------------------------------------------- transposing copy
+// A plain copy of 4-byte elements whose source is contiguous along one axis (s) and whose destination is
+// contiguous along another (t): a [batch, k, n] matmul operand rewritten K-contiguous, a head split.
+// Read by the generic kernel, one side of it touches a 32-byte sector per element.  Here a block moves a
+// 32 x 32 tile through shared memory: rows of 128 bytes on both sides.
+struct TransposeParams {
+    const uint32_t* src;
+    uint32_t* dst;
+    int64_t ns, nt;                 // extents of the two axes
+    int64_t src_t_stride, dst_s_stride;
+    int64_t tiles_s, tiles_t;
+    int32_t n_outer;
+    int64_t outer_dims[DEV_MAX_RANK], outer_src[DEV_MAX_RANK], outer_dst[DEV_MAX_RANK];
+};
+
+__global__ void __launch_bounds__(256) transpose_copy_kernel(const __grid_constant__ TransposeParams q) {
+    pdl_enter();
+    __shared__ uint32_t tile[32][33];
+    int64_t rem = blockIdx.x;
+    const int64_t ts = rem % q.tiles_s;
+    rem /= q.tiles_s;
+    const int64_t tt = rem % q.tiles_t;
+    rem /= q.tiles_t;
+    int64_t src_off = 0, dst_off = 0;
+    for (int d = q.n_outer - 1; d >= 0; d--) {
+        const int64_t i = rem % q.outer_dims[d];
+        rem /= q.outer_dims[d];
+        src_off += i * q.outer_src[d];
+        dst_off += i * q.outer_dst[d];
+    }
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int64_t s0 = ts * 32, t0 = tt * 32;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const int64_t t = t0 + ty + 8 * j, s2 = s0 + tx;
+        if (t < q.nt && s2 < q.ns) tile[ty + 8 * j][tx] = q.src[src_off + s2 + t * q.src_t_stride];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const int64_t s2 = s0 + ty + 8 * j, t = t0 + tx;
+        if (t < q.nt && s2 < q.ns) q.dst[dst_off + t + s2 * q.dst_s_stride] = tile[tx][ty + 8 * j];
+    }
+}
+
+// Fills `q` and returns true if `p` is such a copy.
+bool as_transpose(const ScalarParams& p, TransposeParams& q) {
+    if (p.n_operands != 2 || p.n_loads != 1 || p.n_instr != 0 || p.n_stores != 1 || p.rank < 2) return false;
+    const int src = p.load_operand[0], dst = p.store_operand[0];
+    if (src == dst || p.store_slot[0] != 0 || p.dtype[src] != p.dtype[dst]) return false;
+    const DType dt = (DType)p.dtype[src];
+    if (dt != DType::F32 && dt != DType::I32 && dt != DType::U32) return false;
+    int s_axis = -1, t_axis = -1;
+    for (int d = 0; d < p.rank; d++) {
+        if (p.dims[d] <= 1) continue;
+        if (p.strides[src][d] == 1 && s_axis < 0) s_axis = d;
+        if (p.strides[dst][d] == 1 && t_axis < 0) t_axis = d;
+    }
+    if (s_axis < 0 || t_axis < 0 || s_axis == t_axis) return false;
+    if (p.dims[s_axis] < 16 || p.dims[t_axis] < 16) return false;
+    q.src = (const uint32_t*)p.ptr[src];
+    q.dst = (uint32_t*)p.ptr[dst];
+    q.ns = p.dims[s_axis];
+    q.nt = p.dims[t_axis];
+    q.src_t_stride = p.strides[src][t_axis];
+    q.dst_s_stride = p.strides[dst][s_axis];
+    q.tiles_s = (q.ns + 31) / 32;
+    q.tiles_t = (q.nt + 31) / 32;
+    q.n_outer = 0;
+    int64_t blocks = q.tiles_s * q.tiles_t;
+    for (int d = 0; d < p.rank; d++) {
+        if (d == s_axis || d == t_axis || p.dims[d] <= 1) continue;
+        q.outer_dims[q.n_outer] = p.dims[d];
+        q.outer_src[q.n_outer] = p.strides[src][d];
+        q.outer_dst[q.n_outer] = p.strides[dst][d];
+        q.n_outer++;
+        blocks *= p.dims[d];
+    }
+    return blocks < (1ll << 31);
+}
+
 }  // namespace
 
 int launch_scalar(const ScalarParams& p, cudaStream_t stream) {
     if (p.total == 0) return 0;
+    if (p.vec4 != 2) {
+        TransposeParams q;
+        if (as_transpose(p, q)) {
+            int64_t blocks = q.tiles_s * q.tiles_t;
+            for (int d = 0; d < q.n_outer; d++) blocks *= q.outer_dims[d];
+            launch_pdl(transpose_copy_kernel, dim3((unsigned)blocks), dim3(256), (size_t)0, stream, q);
+            return (int)cudaGetLastError();
+        }
+    }
     if (p.vec4 == 2) {
         // V consecutive float4 positions per thread: as many as the innermost extent and the spill slots
         // (n_regs * V * 4 KB of shared memory per block) allow

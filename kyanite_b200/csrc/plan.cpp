@@ -760,7 +760,19 @@ class Planner {
         PlanTensor out;
         bool tensor_core = false;
         if (opts_.math_mode == KN_MATH_TF32) {
-            if (ci.op == OpKind::MatMul) tensor_core = gemm_fits_tensor_core(x, w);
+            if (ci.op == OpKind::MatMul) {
+                // An operand that is not contiguous along K (the value matrix of an attention head arrives as
+                // [batch, k, n] with n contiguous) gets a transposing copy: the exact-f32 kernel this would
+                // otherwise fall back to is some twenty times slower than copy + tensor cores.
+                if (!gemm_fits_tensor_core(x, w) && gemm_worth_a_copy(x, w)) {
+                    PlanTensor x2 = k_major_a(x, ci.inputs[0]), w2 = k_major_b(w, ci.inputs[1]);
+                    if (gemm_fits_tensor_core(x2, w2)) {
+                        x = x2;
+                        w = w2;
+                    }
+                }
+                tensor_core = gemm_fits_tensor_core(x, w);
+            }
             else tensor_core = conv_fits_tensor_core(ci, x, w, native);
         }
         if (tensor_core && ci.op == OpKind::Conv) {
@@ -884,6 +896,38 @@ class Planner {
         if (a.offset % 4 != 0 || b.offset % 4 != 0) return false;
         if (m > (1ll << 30) || n > (1ll << 30) || k > (1ll << 30)) return false;
         return true;
+    }
+
+    // shapes the tensor-core kernels take, large enough that an extra pass over an operand pays off
+    bool gemm_worth_a_copy(const PlanTensor& a, const PlanTensor& b) const {
+        if (a.ss.rank() != 3 || b.ss.rank() != 3) return false;
+        const int64_t batch = a.ss.shape[0], m = a.ss.shape[1], k = a.ss.shape[2], n = b.ss.shape[2];
+        if (batch < 1 || batch > 65535 || m < 64 || n < 32 || k < 32) return false;
+        return 2.0 * (double)batch * (double)m * (double)n * (double)k >= 2e8;
+    }
+    bool k_major_ok(const PlanTensor& t, int k_axis, int other_axis) const {
+        const auto& sh = t.ss.shape;
+        const auto& st = t.ss.strides;
+        return (sh[k_axis] <= 1 || st[k_axis] == 1) && tma_stride_ok(sh[other_axis], st[other_axis]) && tma_stride_ok(sh[0], st[0]) &&
+               t.offset % 4 == 0;
+    }
+    // A [b, m, k] with k contiguous: `a` itself, or a copy of it
+    PlanTensor k_major_a(const PlanTensor& a, int value) {
+        if (k_major_ok(a, 2, 1)) return a;
+        const int64_t k_pad = (a.ss.shape[2] + 3) / 4 * 4;
+        PlanTensor dense = alloc_shared({a.ss.shape[0], a.ss.shape[1], k_pad}, DType::F32, value);
+        PlanTensor dst = dense.slice(2, 0, a.ss.shape[2], 1);
+        emit_copy(a, dst, value);
+        return dst;
+    }
+    // B [b, k, n] with k contiguous (stored as [b, n, k_pad]): `b` itself, or a transposed copy of it
+    PlanTensor k_major_b(const PlanTensor& b, int value) {
+        if (k_major_ok(b, 1, 2)) return b;
+        const int64_t k_pad = (b.ss.shape[1] + 3) / 4 * 4;
+        PlanTensor dense = alloc_shared({b.ss.shape[0], b.ss.shape[2], k_pad}, DType::F32, value);
+        PlanTensor dst = dense.with(dense.ss.permute({0, 2, 1})).slice(1, 0, b.ss.shape[1], 1);
+        emit_copy(b, dst, value);
+        return dst;
     }
 
     bool conv_fits_tensor_core(const ValueInfo& ci, const PlanTensor& x, const PlanTensor& w, const std::vector<int64_t>& out) const {

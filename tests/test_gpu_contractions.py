@@ -164,3 +164,21 @@ def test_conv_with_gelu_epilogue():
     d = plan_describe(g.to_bytes(), 3, math_mode=MATH_TF32)
     assert " gelu" in d and "ConvChain" not in d
     check(g, 3, [rng(4, 3, 24, 8, 8)])
+
+
+def test_matmul_operands_not_contiguous_along_k():
+    """probabilities . values of an attention head: B arrives as [batch, k, n] with n contiguous, and here A
+    as [batch, k, m] transposed as well.  The planner copies such operands into K-contiguous buffers and
+    keeps the tensor-core kernel (the step list shows the copies and a Gemm/tc step)."""
+    b, m, n, k = 8, 512, 128, 260
+    g = Graph()
+    at = g.input(shape(b, k, m))
+    v = g.input(shape(b, k, n))
+    g.output(g.batched_mat_mul(g.permute(at, [0, 2, 1]), v))
+    d = plan_describe(g.to_bytes(), 0, math_mode=MATH_TF32)
+    assert d.count(" copy ") == 2 and "Gemm/tc" in d
+    check(g, 0, [rng(1, b, k, m), rng(2, b, k, n)])
+    # small problems are not worth the extra pass
+    g = Graph()
+    g.output(g.batched_mat_mul(g.input(shape(2, 64, 32)), g.input(shape(2, 32, 32))))
+    assert " copy " not in plan_describe(g.to_bytes(), 0, math_mode=MATH_TF32)
