@@ -99,7 +99,7 @@ struct Executor {
                     break;
                 case StepKind::Softmax:
                     s.row.in0 = (const float*)ptr[0];
-                    s.row.in1 = nullptr;
+                    s.row.in1 = ptr.size() > 2 ? (const float*)ptr[2] : nullptr;   // additive term
                     s.row.out = (float*)ptr[1];
                     break;
                 case StepKind::Layernorm:

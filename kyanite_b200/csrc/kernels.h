@@ -68,13 +68,15 @@ struct ReduceParams {
 // ---- softmax / layernorm over one axis: replace autokernel/{softmax,layernorm}.{rs,cu}
 struct RowParams {
     const float* in0;
-    const float* in1;        // layernorm only, may be null; same strides as in0
+    const float* in1;        // may be null.  layernorm: second input, same strides as in0.
+                             // softmax: additive term (an attention mask) with strides of its own
     float* out;
     int32_t outer_rank;
     int64_t rows, len;
     int64_t outer_dims[DEV_MAX_RANK], in_strides[DEV_MAX_RANK], out_strides[DEV_MAX_RANK];
     int64_t in_axis_stride, out_axis_stride;
-    float scale;             // softmax: input scale folded in
+    int64_t in1_strides[DEV_MAX_RANK], in1_axis_stride;   // softmax only
+    float scale;             // softmax: x = scale * in0 + in1
     float alpha0, alpha1;    // layernorm: x = alpha0 * in0 + alpha1 * in1
     float eps;
 };

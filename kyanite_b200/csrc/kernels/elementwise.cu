@@ -308,7 +308,8 @@ int launch_acc(const ScalarParams& p, cudaStream_t stream) {
 // A plain copy of 4-byte elements whose source is contiguous along one axis (s) and whose destination is
 // contiguous along another (t): a [batch, k, n] matmul operand rewritten K-contiguous, a head split.
 // Read by the generic kernel, one side of it touches a 32-byte sector per element.  Here a block moves a
-// 32 x 32 tile through shared memory: rows of 128 bytes on both sides.
+// 32 x 64 tile through shared memory: rows of 128 bytes on both sides, eight loads per thread in flight.
+constexpr int kTransposeT = 64;   // tile extent along t (32 along s)
 struct TransposeParams {
     const uint32_t* src;
     uint32_t* dst;
@@ -321,7 +322,7 @@ struct TransposeParams {
 
 __global__ void __launch_bounds__(256) transpose_copy_kernel(const __grid_constant__ TransposeParams q) {
     pdl_enter();
-    __shared__ uint32_t tile[32][33];
+    __shared__ uint32_t tile[kTransposeT][33];
     int64_t rem = blockIdx.x;
     const int64_t ts = rem % q.tiles_s;
     rem /= q.tiles_s;
@@ -335,17 +336,23 @@ __global__ void __launch_bounds__(256) transpose_copy_kernel(const __grid_consta
         dst_off += i * q.outer_dst[d];
     }
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-    const int64_t s0 = ts * 32, t0 = tt * 32;
+    const int64_t s0 = ts * 32, t0 = tt * kTransposeT;
+    uint32_t r[kTransposeT / 8];
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
+    for (int j = 0; j < kTransposeT / 8; j++) {
         const int64_t t = t0 + ty + 8 * j, s2 = s0 + tx;
-        if (t < q.nt && s2 < q.ns) tile[ty + 8 * j][tx] = q.src[src_off + s2 + t * q.src_t_stride];
+        r[j] = (t < q.nt && s2 < q.ns) ? __ldg(q.src + src_off + s2 + t * q.src_t_stride) : 0u;
     }
+#pragma unroll
+    for (int j = 0; j < kTransposeT / 8; j++) tile[ty + 8 * j][tx] = r[j];
     __syncthreads();
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
-        const int64_t s2 = s0 + ty + 8 * j, t = t0 + tx;
-        if (t < q.nt && s2 < q.ns) q.dst[dst_off + t + s2 * q.dst_s_stride] = tile[tx][ty + 8 * j];
+    for (int h = 0; h < kTransposeT / 32; h++) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int64_t s2 = s0 + ty + 8 * j, t = t0 + 32 * h + tx;
+            if (t < q.nt && s2 < q.ns) q.dst[dst_off + t + s2 * q.dst_s_stride] = tile[32 * h + tx][ty + 8 * j];
+        }
     }
 }
 
@@ -371,7 +378,7 @@ bool as_transpose(const ScalarParams& p, TransposeParams& q) {
     q.src_t_stride = p.strides[src][t_axis];
     q.dst_s_stride = p.strides[dst][s_axis];
     q.tiles_s = (q.ns + 31) / 32;
-    q.tiles_t = (q.nt + 31) / 32;
+    q.tiles_t = (q.nt + kTransposeT - 1) / kTransposeT;
     q.n_outer = 0;
     int64_t blocks = q.tiles_s * q.tiles_t;
     for (int d = 0; d < p.rank; d++) {

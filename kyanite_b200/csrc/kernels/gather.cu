@@ -46,9 +46,13 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const __grid_constant_
     pdl_enter();
     const int lane = threadIdx.x & 31;
     const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
-    for (int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows; row += warps) {
-        int64_t rem = row, in_off = 0, out_off = 0;
-        bool valid = true;
+    // where a row comes from and goes to (the index load and the divisions are a dependent chain of their
+    // own, so the next row's are resolved while the current row moves)
+    auto locate = [&](int64_t row, int64_t& in_off, int64_t& out_off, bool& valid) {
+        int64_t rem = row;
+        in_off = 0;
+        out_off = 0;
+        valid = true;
         for (int d = p.axis; d >= 0; d--) {
             const int64_t dim = p.out_dims[d];
             const int64_t q = rem / dim;
@@ -62,10 +66,39 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const __grid_constant_
             }
             in_off += i * p.in_strides[d];
         }
+    };
+    int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    int64_t in_off, out_off;
+    bool valid;
+    locate(row, in_off, out_off, valid);
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    while (true) {
+        const int64_t next = row + warps;
+        int64_t n_in = 0, n_out = 0;
+        bool n_valid = false;
+        if (next < rows) locate(next, n_in, n_out, n_valid);
         const uint4* src = (const uint4*)((const char*)p.in + in_off * p.elem_size);
         uint4* dst = (uint4*)((char*)p.out + out_off * p.elem_size);
-        const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-        for (int e = lane; e < row_vec4; e += 32) dst[e] = valid ? __ldg(src + e) : zero;
+        // four 128-bit loads per lane in flight before the first store
+        for (int e0 = lane; e0 < row_vec4; e0 += 128) {
+            uint4 r[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int e = e0 + 32 * j;
+                r[j] = (valid && e < row_vec4) ? __ldg(src + e) : zero;
+            }
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int e = e0 + 32 * j;
+                if (e < row_vec4) dst[e] = r[j];
+            }
+        }
+        if (next >= rows) break;
+        row = next;
+        in_off = n_in;
+        out_off = n_out;
+        valid = n_valid;
     }
 }
 

@@ -70,13 +70,19 @@ __global__ void __launch_bounds__(256) softmax_cached_kernel(const __grid_consta
     if (active) decode_offsets(row, p.outer_rank, p.outer_dims, p.in_strides, p.out_strides, oi, oo);
     const float* in = p.in0 + oi;
     float* out = p.out + oo;
+    const float* add = nullptr;
+    if (p.in1 != nullptr && active) {
+        int64_t o1, unused;
+        decode_offsets(row, p.outer_rank, p.outer_dims, p.in1_strides, p.out_strides, o1, unused);
+        add = p.in1 + o1;
+    }
 
     float v[ITEMS];
     float mx = -INFINITY;
 #pragma unroll
     for (int i = 0; i < ITEMS; i++) {
         const int64_t e = (int64_t)i * TPR + t;
-        v[i] = (active && e < p.len) ? in[e * p.in_axis_stride] * p.scale : -INFINITY;
+        v[i] = (active && e < p.len) ? in[e * p.in_axis_stride] * p.scale + (add ? add[e * p.in1_axis_stride] : 0.f) : -INFINITY;
         mx = fmaxf(mx, v[i]);
     }
     mx = row_reduce<TPR, true>(mx, smem);
@@ -105,14 +111,20 @@ __global__ void __launch_bounds__(256) softmax_streaming_kernel(const __grid_con
     decode_offsets(row, p.outer_rank, p.outer_dims, p.in_strides, p.out_strides, oi, oo);
     const float* in = p.in0 + oi;
     float* out = p.out + oo;
+    const float* add = nullptr;
+    if (p.in1 != nullptr) {
+        int64_t o1, unused;
+        decode_offsets(row, p.outer_rank, p.outer_dims, p.in1_strides, p.out_strides, o1, unused);
+        add = p.in1 + o1;
+    }
+    auto load = [&](int64_t e) { return in[e * p.in_axis_stride] * p.scale + (add ? add[e * p.in1_axis_stride] : 0.f); };
     float mx = -INFINITY;
-    for (int64_t e = threadIdx.x; e < p.len; e += 256) mx = fmaxf(mx, in[e * p.in_axis_stride] * p.scale);
+    for (int64_t e = threadIdx.x; e < p.len; e += 256) mx = fmaxf(mx, load(e));
     mx = row_reduce<256, true>(mx, smem);
     float sum = 0.f;
-    for (int64_t e = threadIdx.x; e < p.len; e += 256) sum += expf(in[e * p.in_axis_stride] * p.scale - mx);
+    for (int64_t e = threadIdx.x; e < p.len; e += 256) sum += expf(load(e) - mx);
     sum = row_reduce<256, false>(sum, smem);
-    for (int64_t e = threadIdx.x; e < p.len; e += 256)
-        out[e * p.out_axis_stride] = expf(in[e * p.in_axis_stride] * p.scale - mx) / sum;
+    for (int64_t e = threadIdx.x; e < p.len; e += 256) out[e * p.out_axis_stride] = expf(load(e) - mx) / sum;
 }
 
 // ------------------------------------------------------------------ layernorm
@@ -204,6 +216,12 @@ __global__ void __launch_bounds__(256) softmax_vec4_kernel(const __grid_constant
     const float4* in = (const float4*)(p.in0 + oi);
     float4* out = (float4*)(p.out + oo);
     const int len4 = (int)(p.len >> 2);
+    const float4* add = nullptr;
+    if (p.in1 != nullptr && active) {
+        int64_t o1, unused;
+        decode_offsets(row, p.outer_rank, p.outer_dims, p.in1_strides, p.out_strides, o1, unused);
+        add = (const float4*)(p.in1 + o1);
+    }
 
     float4 v[ITEMS4];
     float mx = -INFINITY;
@@ -216,8 +234,21 @@ __global__ void __launch_bounds__(256) softmax_vec4_kernel(const __grid_constant
         } else {
             v[i] = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
         }
-        mx = fmaxf(mx, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
     }
+    // the additive term in a loop of its own: a branch inside the loop above would keep the compiler from
+    // issuing all the row's loads back to back
+    if (add != nullptr) {
+#pragma unroll
+        for (int i = 0; i < ITEMS4; i++) {
+            const int e = i * TPR + t;
+            if (e < len4) {
+                const float4 a = __ldg(add + e);
+                v[i].x += a.x; v[i].y += a.y; v[i].z += a.z; v[i].w += a.w;
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < ITEMS4; i++) mx = fmaxf(mx, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
     mx = row_reduce<TPR, true>(mx, smem);
     float sum = 0.f;
 #pragma unroll
@@ -414,21 +445,34 @@ static bool row_vec4_ok(const RowParams& p) {
     return true;
 }
 
+// softmax's additive term is read 128 bits at a time like the input
+static bool softmax_vec4_ok(const RowParams& p) {
+    if (!row_vec4_ok(p)) return false;
+    if (p.in1 == nullptr) return true;
+    if (p.in1_axis_stride != 1) return false;
+    for (int d = 0; d < p.outer_rank; d++)
+        if (p.in1_strides[d] % 4 != 0) return false;
+    return true;
+}
+
 #define KN_ROW_VEC4_CASE(KERNEL, TPR, N)                     \
     case N: launch_pdl(KERNEL<TPR, N>, dim3(grid), dim3(256), (size_t)(0), stream, p); break;
 
-#define KN_ROW_DISPATCH(KERNEL, VEC4, STREAMING)                                                               \
+#define KN_ROW_DISPATCH(KERNEL, VEC4, STREAMING, OK)                                                            \
     if (p.rows == 0 || p.len == 0) return 0;                                                                   \
     if (p.rows > 0x7FFFFFFFll) return (int)cudaErrorInvalidValue;                                              \
     const int64_t len = p.len;                                                                                 \
-    if (row_vec4_ok(p)) {                                                                                      \
+    if (OK(p)) {                                                                                               \
         const int len4 = (int)(len / 4);                                                                       \
-        if (len4 <= 256) {                                                                                     \
+        if (len4 <= 512) {                                                                                     \
+            /* one warp per row, the row in registers (up to 16 float4 per lane) */                            \
             const unsigned grid = (unsigned)((p.rows + 7) / 8);                                                \
-            switch ((len4 + 31) / 32) {                                                                        \
+            const int items = (len4 + 31) / 32;                                                                \
+            switch (items <= 8 ? items : (items + 1) / 2 * 2) {                                                \
                 KN_ROW_VEC4_CASE(VEC4, 32, 1) KN_ROW_VEC4_CASE(VEC4, 32, 2) KN_ROW_VEC4_CASE(VEC4, 32, 3)      \
                 KN_ROW_VEC4_CASE(VEC4, 32, 4) KN_ROW_VEC4_CASE(VEC4, 32, 5) KN_ROW_VEC4_CASE(VEC4, 32, 6)      \
-                KN_ROW_VEC4_CASE(VEC4, 32, 7)                                                                  \
+                KN_ROW_VEC4_CASE(VEC4, 32, 7) KN_ROW_VEC4_CASE(VEC4, 32, 10) KN_ROW_VEC4_CASE(VEC4, 32, 12)    \
+                KN_ROW_VEC4_CASE(VEC4, 32, 14) KN_ROW_VEC4_CASE(VEC4, 32, 16)                                  \
                 default: launch_pdl(VEC4<32, 8>, dim3(grid), dim3(256), (size_t)(0), stream, p); break;                                      \
             }                                                                                                  \
         } else {                                                                                               \
@@ -461,11 +505,11 @@ static bool row_vec4_ok(const RowParams& p) {
     return (int)cudaGetLastError();
 
 int launch_softmax(const RowParams& p, cudaStream_t stream) {
-    KN_ROW_DISPATCH(softmax_cached_kernel, softmax_vec4_kernel, softmax_streaming_kernel)
+    KN_ROW_DISPATCH(softmax_cached_kernel, softmax_vec4_kernel, softmax_streaming_kernel, softmax_vec4_ok)
 }
 
 int launch_layernorm(const RowParams& p, cudaStream_t stream) {
-    KN_ROW_DISPATCH(layernorm_cached_kernel, layernorm_vec4_kernel, layernorm_streaming_kernel)
+    KN_ROW_DISPATCH(layernorm_cached_kernel, layernorm_vec4_kernel, layernorm_streaming_kernel, row_vec4_ok)
 }
 
 int launch_reduce(const ReduceParams& p, cudaStream_t stream) {

@@ -1059,7 +1059,21 @@ class Planner {
     PlanTensor visit_softmax(int v) {
         const ValueInfo& info = g_.values[v];
         KN_CHECK(info.dtype == DType::F32, KN_ERR_UNSUPPORTED, "softmax needs f32");
-        auto [scale, in] = visit_scalable(info.inputs[0]);
+        // softmax(c * x + mask): the scale and the additive term (an attention mask, usually a broadcast view)
+        // are applied as the row is loaded instead of by an elementwise step of their own
+        float scale = 1.f;
+        PlanTensor in;
+        std::optional<PlanTensor> term;
+        const int input = info.inputs[0];
+        const ValueInfo& ii = g_.values[input];
+        if (ii.op == OpKind::Binary && ii.binary_op == BinaryOp::Add && ii.dtype == DType::F32 && fusable(input) && !map_[input] &&
+            !match_epilogue(input)) {
+            auto [s0, t0] = visit_scalable(ii.inputs[0]);
+            auto [s1, t1] = visit_scalable(ii.inputs[1]);
+            if (s1 == 1.f && t0.ss.shape == t1.ss.shape) { scale = s0; in = t0; term = t1; }
+            else if (s0 == 1.f && t0.ss.shape == t1.ss.shape) { scale = s1; in = t1; term = t0; }
+        }
+        if (!term) std::tie(scale, in) = visit_scalable(input);
         PlanTensor out = alloc_shared(shape_of(v), DType::F32, v);
         Step s;
         s.kind = StepKind::Softmax;
@@ -1067,8 +1081,18 @@ class Planner {
         s.operands = {in, out};
         s.writes = {0, 1};
         fill_rows(s.row, in, out, info.axis);
+        if (term) {
+            s.operands.push_back(*term);
+            s.writes.push_back(0);
+            int r = 0;
+            for (int d = 0; d < in.ss.rank(); d++) {
+                if (d == info.axis || in.ss.shape[d] == 1) continue;
+                s.row.in1_strides[r++] = term->ss.strides[d];
+            }
+            s.row.in1_axis_stride = term->ss.strides[info.axis];
+        }
         s.row.scale = scale;
-        s.desc = "softmax rows=" + std::to_string(s.row.rows) + " len=" + std::to_string(s.row.len);
+        s.desc = "softmax rows=" + std::to_string(s.row.rows) + " len=" + std::to_string(s.row.len) + (term ? " +term" : "");
         if (out.ss.size() != 0) push_step(std::move(s));
         return out;
     }

@@ -122,3 +122,28 @@ def test_transposing_copies_are_bit_exact(dims, perm):
         with CudaExecutor(0, g, 0) as ex:
             (got,) = ex.evaluate([data])
         np.testing.assert_array_equal(got, np.transpose(data, perm).reshape(-1))
+
+
+@pytest.mark.parametrize("rows,length,mask_kind", [(64, 512, "rows"), (10, 37, "rows"), (3, 9000, "rows"), (8, 256, "full"),
+                                                    (8, 64, "per_row_constant"), (4, 2048, "rows")])
+def test_softmax_with_scale_and_additive_term(rows, length, mask_kind):
+    """softmax(0.125 * x + mask) is one step: the 128-bit kernel (row length a multiple of 4), the scalar
+    kernel (37), the streaming kernel (9000); the term broadcast over the batch axis, of full shape, or
+    constant along the row."""
+    from kyanite_b200.graph import Graph, shape
+    r = np.random.Generator(np.random.PCG64(11))
+    b = 3
+    g = Graph()
+    x = g.input(shape(b, rows, length))
+    mask_shape = {"rows": (1, rows, length), "full": (b, rows, length), "per_row_constant": (b, rows, 1)}[mask_kind]
+    mask = g.input(shape(*mask_shape))
+    full = g.broadcast(mask, shape(b, rows, length)) if mask_shape != (b, rows, length) else mask
+    g.output(g.softmax(g.add(g.mul(x, g.scalar(0.125)), full), 2))
+    text = plan_describe(g, 0)
+    assert len([l for l in text.splitlines() if l.startswith("step")]) == 1 and "+term" in text
+    m = np.where(r.random(mask_shape) < 0.3, -1e9, 0.0).astype(np.float32)
+    m[..., 0] = 0.0   # never a fully masked row
+    ins = [(r.standard_normal((b, rows, length)) * 8).astype(np.float32), m]
+    expected = cpu_eval_graph(g.to_bytes(), 0, ins)
+    with CudaExecutor(0, g, 0) as ex:
+        assert_tensors_match(expected, ex.evaluate(ins))
