@@ -112,6 +112,7 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
     volatile uint32_t* tmem_slot = (volatile uint32_t*)(gen_base + (slot_addr - base));
     volatile int* abandon = (volatile int*)(gen_base + (slot_addr + 4u - base));
     uint32_t* colinfo = (uint32_t*)(gen_base + (slot_addr + 8u - base));         // 256 entries
+    uint32_t* realmask = colinfo + 256;                                          // 16 entries: per 16-column chunk, which columns are real pixels
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -148,6 +149,12 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
         colinfo[n] = info;
     }
     __syncthreads();
+    if (threadIdx.x >= 64 && threadIdx.x < 80) {
+        const int c = threadIdx.x - 64;
+        uint32_t m = 0;
+        for (int j = 0; j < 16; j++) m |= (colinfo[c * 16 + j] >> 31) << j;
+        realmask[c] = m;
+    }
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_addr), "r"((uint32_t)p.tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -248,17 +255,6 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
         const uint32_t chunk = (uint32_t)(ch >> 2) & 7u;
         // this channel's 4 bytes inside a 128-byte row of its 32-channel block, before the swizzle
         const int chunks16 = (p.n_mma + 15) >> 4;
-        constexpr int kMaxMine = 8;                             // 256 columns / 16 / 2 warps
-        // which of my columns are real pixels (everything else is written as zero padding)
-        uint32_t real[kMaxMine];
-#pragma unroll
-        for (int k = 0; k < kMaxMine; k++) {
-            const int c = half + 2 * k;
-            uint32_t m = 0;
-            if (c < chunks16)
-                for (int j = 0; j < 16; j++) m |= (colinfo[c * 16 + j] >> 31) << j;
-            real[k] = m;
-        }
         // Output column n is stored in row r_first + n of the channel's block; r_first is a multiple of 8, so
         // the swizzle phase of a row (row & 7) is the column's n & 7, known at compile time inside the
         // unrolled loops: the eight swizzled chunk offsets are computed once.
@@ -349,9 +345,9 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
                     tmem_load_16_nowait(tmem_acc + lane_bits + (uint32_t)(c * 16), v);
                     if (add_held) tmem_load_16_nowait(tmem_held + lane_bits + (uint32_t)(c * 16), h);
                 };
-                auto finish = [&](int k, int c, uint32_t (&v)[16], uint32_t (&h)[16]) {
+                auto finish = [&](int c, uint32_t (&v)[16], uint32_t (&h)[16]) {
                     const uint32_t chunk_rows = my_rows + (uint32_t)c * 2048u;
-                    const uint32_t mask = valid ? real[k] : 0u;
+                    const uint32_t mask = valid ? realmask[c] : 0u;   // columns that are real pixels; the rest is zero padding
 #pragma unroll
                     for (int j = 0; j < 16; j++) {
                         float x = __uint_as_float(v[j]) + bias;
@@ -373,18 +369,18 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
                         }
                     }
                 };
+                // (not unrolled over the chunks: eight copies of the body made the epilogue's code so large that
+                // the kernel's speed depended on where unrelated code happened to be placed, measured)
                 if (half < chunks16) issue(half, va, ha);
-#pragma unroll
-                for (int k = 0; k < kMaxMine; k += 2) {
-                    const int c = half + 2 * k;
-                    if (c >= chunks16) break;
+#pragma unroll 1
+                for (int c = half; c < chunks16; c += 4) {
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                     if (c + 2 < chunks16) issue(c + 2, vb, hb);
-                    finish(k, c, va, ha);
+                    finish(c, va, ha);
                     if (c + 2 >= chunks16) break;
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                     if (c + 4 < chunks16) issue(c + 4, va, ha);
-                    finish(k + 1, c + 2, vb, hb);
+                    finish(c + 2, vb, hb);
                 }
                 if (hold) asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             }
@@ -427,7 +423,7 @@ bool tc_chain_geometry(int h, int w, int64_t n_img, int c_blocks, ChainGeometry*
             if (g.n_mma > 256) break;
             g.rows_alloc = round_up_int(g.r_first + g.n_mma + g.wp + 2, 8);
             const int act_bytes = c_blocks * g.rows_alloc * 128;
-            const int fixed = 1024 /* alignment */ + 16 * 8 + 32 + 1024 /* column table */;
+            const int fixed = 1024 /* alignment */ + 16 * 8 + 32 + 1024 /* column table */ + 64 /* chunk masks */;
             // the ring holds whole taps (c_blocks tiles each): two of them at least, four at most
             const int taps = std::min(4, (227 * 1024 - fixed - act_bytes) / (kTileBytes * c_blocks));
             if (taps < 2) break;
