@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 
 #include "../kernels.h"
+#include <utility>
+
 #include "epilogue.cuh"
 #include "launch.cuh"
 
@@ -197,6 +199,26 @@ int launch_gemm_simt(const GemmParams& p, cudaStream_t stream) {
     if (p.n >= 1 && p.n <= kSkinnyMaxN && p.k >= 32 && p.batch * p.m > 0) {
         const int64_t rows = p.batch * p.m;
         launch_pdl(gemm_skinny_kernel, dim3((unsigned)((rows + 7) / 8)), dim3(256), (size_t)(0), stream, p);
+        return (int)cudaGetLastError();
+    }
+    if (p.m >= 1 && p.m <= kSkinnyMaxN && p.k >= 32 && p.batch * p.n > 0) {
+        // few output ROWS (a single token through a linear layer): the same kernel on the transposed problem,
+        // C^T = B^T . A^T, one warp per output column
+        GemmParams t = p;
+        t.a = p.b;
+        t.b = p.a;
+        t.m = p.n;
+        t.n = p.m;
+        const int64_t sa[3] = {p.sb[0], p.sb[2], p.sb[1]}, sb[3] = {p.sa[0], p.sa[2], p.sa[1]};
+        for (int i = 0; i < 3; i++) {
+            t.sa[i] = sa[i];
+            t.sb[i] = sb[i];
+        }
+        std::swap(t.sc[1], t.sc[2]);
+        std::swap(t.s1[1], t.s1[2]);
+        std::swap(t.s2[1], t.s2[2]);
+        const int64_t rows = t.batch * t.m;
+        launch_pdl(gemm_skinny_kernel, dim3((unsigned)((rows + 7) / 8)), dim3(256), (size_t)(0), stream, t);
         return (int)cudaGetLastError();
     }
     return launch(GemmProblem{p}, p.m, p.n, p.batch, stream);

@@ -44,6 +44,7 @@ struct TcParams {
     int32_t mode;   // 0 = matmul, 1 = conv
     int32_t bn, tmem_cols, k_iters, stages;
     int32_t splits, k_iters_total;   // matmul split K: slices per batch entry, K blocks overall (k_iters = per slice)
+    int32_t b_batch;                 // matmul: 1, or 0 when every batch entry multiplies the same B (batch stride 0)
     // conv tiling
     int32_t cblocks, kernel_w, pad_y, pad_x, wb, hb, nb, tiles_w, tiles_h;
     int32_t wb_shift, hb_shift;   // log2 of wb, hb
@@ -140,7 +141,7 @@ tc_contract_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             mbar_expect_tx(full_bar + 8u * s, kATileBytes + b_tile_bytes);
             if (p.mode == 0) {
                 tma_load_4d(a_base + s * kATileBytes, &map_a, full_bar + 8u * s, (k_first + it) * kBlockK, m0, batch, 0);
-                tma_load_3d(b_base + s * b_tile_bytes, &map_b, full_bar + 8u * s, (k_first + it) * kBlockK, ncol0, batch);
+                tma_load_3d(b_base + s * b_tile_bytes, &map_b, full_bar + 8u * s, (k_first + it) * kBlockK, ncol0, batch * p.b_batch);
             } else {
                 const int tap = it / p.cblocks, cb = it - tap * p.cblocks;
                 const int r = tap / p.kernel_w, sx = tap - r * p.kernel_w;
@@ -880,7 +881,8 @@ void tc_prepare_step(Step& step, uint32_t* status_word, int flags) {
         launch->map_a = make_map(g.a, 4, adims, astr, abox);
         p.bn = (int)std::min<int64_t>(round_up((int)std::min<int64_t>(n_cols, 256), 16), 256);
         if (n_cols > 256) p.bn = 128;
-        int64_t bdims[3] = {g.k, g.n, g.batch}, bstr[3] = {1, g.sb[2], g.sb[0]};
+        p.b_batch = (g.batch > 1 && g.sb[0] == 0) ? 0 : 1;
+        int64_t bdims[3] = {g.k, g.n, p.b_batch ? g.batch : 1}, bstr[3] = {1, g.sb[2], p.b_batch ? g.sb[0] : 4};
         int bbox[3] = {kBlockK, p.bn, 1};
         launch->map_b = make_map(g.b, 3, bdims, bstr, bbox);
         launch->grid = dim3((unsigned)((g.m + kBlockM - 1) / kBlockM), (unsigned)((n_cols + p.bn - 1) / p.bn), (unsigned)g.batch);
@@ -1144,6 +1146,7 @@ void matmul_static(const float* a, const float* b, float* c, int64_t m, int64_t 
     p.so[1] = n;
     p.so[2] = 1;
     p.status = dev.status;
+    p.b_batch = 1;
     const int stage_bytes = kATileBytes + bn * 128;
     p.stages = std::max(2, std::min(6, (200 * 1024) / stage_bytes));
     p.stages = std::min(p.stages, std::max(2, p.k_iters));

@@ -44,6 +44,7 @@ constexpr int kGpStageTileBytes = 128 * 128;   // epilogue staging: 128 rows x 3
 
 struct GemmPersistentParams {
     int32_t bn, stages, k_iters;
+    int32_t b_batch;                 // 1, or 0 when every batch entry multiplies the same B (batch stride 0)
     int32_t splits, k_iters_slice;   // split K: slice sp of a tile covers K blocks [sp * k_iters_slice, ...) and is stored
                                      // as matrix `batch * splits + sp` of the output map (the partial-sum buffer)
     int32_t m_tiles, n_tiles, batch, total_tiles;
@@ -135,7 +136,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 mbar_expect_tx(bar, stage_bytes);
                 const uint32_t dst = base + (uint32_t)s * stage_bytes;
                 tma_load_3d(dst, &map_a, bar, k * kGpBlockK, mt * kGpBlockM, bt);
-                tma_load_3d(dst + kGpATileBytes, &map_b, bar, k * kGpBlockK, nt * p.bn, bt);
+                tma_load_3d(dst + kGpATileBytes, &map_b, bar, k * kGpBlockK, nt * p.bn, bt * p.b_batch);
                 if (++s == stages) { s = 0; round++; }
             }
         }
@@ -341,7 +342,8 @@ std::shared_ptr<void> gemm_persistent_prepare(const GemmParams& g, uint32_t* sta
     int64_t adims[3] = {g.k, g.m, g.batch}, astr[3] = {1, g.sa[1], g.sa[0]};
     int abox[3] = {kGpBlockK, kGpBlockM, 1};
     l->map_a = tc_make_map(g.a, 3, adims, astr, abox, true);
-    int64_t bdims[3] = {g.k, g.n, g.batch}, bstr[3] = {1, g.sb[2], g.sb[0]};
+    p.b_batch = (g.batch > 1 && g.sb[0] == 0) ? 0 : 1;
+    int64_t bdims[3] = {g.k, g.n, p.b_batch ? g.batch : 1}, bstr[3] = {1, g.sb[2], p.b_batch ? g.sb[0] : 4};
     int bbox[3] = {kGpBlockK, p.bn, 1};
     l->map_b = tc_make_map(g.b, 3, bdims, bstr, bbox, true);
     int64_t cdims[3] = {g.n, g.m, g.batch * splits}, cstr[3] = {1, split ? g.n : g.sc[1], split ? g.m * g.n : g.sc[0]};

@@ -758,7 +758,8 @@ class Planner {
             addends.push_back(t.with(*s));
         }
         PlanTensor out;
-        bool tensor_core = false;
+        bool tensor_core = false, as_gemm = false;
+        PlanTensor conv_view;   // as_gemm: the matmul's output seen as [N, K, OH, OW]
         if (opts_.math_mode == KN_MATH_TF32) {
             if (ci.op == OpKind::MatMul) {
                 // An operand that is not contiguous along K (the value matrix of an attention head arrives as
@@ -773,9 +774,19 @@ class Planner {
                 }
                 tensor_core = gemm_fits_tensor_core(x, w);
             }
+            else if (auto g = conv_as_gemm(ci, x, w, native, addends, root)) {
+                // im2col + batched matmul (see conv_as_gemm); from here on this is a matmul step
+                x = g->a;
+                w = g->b;
+                out = g->c;
+                addends = g->addends;
+                conv_view = g->result;
+                as_gemm = true;
+                tensor_core = true;
+            }
             else tensor_core = conv_fits_tensor_core(ci, x, w, native);
         }
-        if (tensor_core && ci.op == OpKind::Conv) {
+        if (tensor_core && ci.op == OpKind::Conv && !as_gemm) {
             x = channels_last(x, ci.inputs[0]);
             w = tap_major_filter(w, ci.inputs[1]);
             // keep the activation channels-last while it flows from convolution to convolution
@@ -795,7 +806,7 @@ class Planner {
             s.operands.push_back(a);
             s.writes.push_back(0);
         }
-        if (ci.op == OpKind::MatMul) {
+        if (ci.op == OpKind::MatMul || as_gemm) {
             KN_CHECK(x.ss.rank() == 3 && w.ss.rank() == 3, KN_ERR_SHAPE, "matmul operands must have rank 3");
             s.kind = StepKind::Gemm;
             GemmParams& p = s.gemm;
@@ -875,8 +886,10 @@ class Planner {
         if (s.kind == StepKind::Gemm && s.gemm.splits > 1) s.desc += " splitk=" + std::to_string(s.gemm.splits);
         int64_t total = 1;
         for (int64_t d : native) total *= d;
+        if (as_gemm) s.desc += " (conv via im2col, stride " + std::to_string(ci.stride_y) + "x" + std::to_string(ci.stride_x) + ")";
         if (total != 0) push_step(std::move(s));
 
+        if (as_gemm) out = conv_view;
         auto rs = out.ss.view(root_shape);
         KN_CHECK(rs.has_value(), KN_ERR_INTERNAL, "view of a dense contraction output failed");
         return out.with(*rs);
@@ -892,7 +905,8 @@ class Planner {
         if (batch < 1 || batch > 65535 || m < 64 || n < 8 || k < 8) return false;
         if (k > 1 && (a.ss.strides[2] != 1 || b.ss.strides[1] != 1)) return false;
         if (!tma_stride_ok(m, a.ss.strides[1]) || !tma_stride_ok(batch, a.ss.strides[0])) return false;
-        if (!tma_stride_ok(n, b.ss.strides[2]) || !tma_stride_ok(batch, b.ss.strides[0])) return false;
+        // (a B shared by every batch entry, batch stride 0, is loaded with batch coordinate 0)
+        if (!tma_stride_ok(n, b.ss.strides[2]) || !(tma_stride_ok(batch, b.ss.strides[0]) || b.ss.strides[0] == 0)) return false;
         if (a.offset % 4 != 0 || b.offset % 4 != 0) return false;
         if (m > (1ll << 30) || n > (1ll << 30) || k > (1ll << 30)) return false;
         return true;
@@ -928,6 +942,102 @@ class Planner {
         PlanTensor dst = dense.with(dense.ss.permute({0, 2, 1})).slice(1, 0, b.ss.shape[1], 1);
         emit_copy(b, dst, value);
         return dst;
+    }
+
+    // A convolution the tensor-core convolution kernels do not take (stride > 1) or take badly (a handful
+    // of output positions under a long reduction: one M tile, so a handful of CTAs walk K = C*R*S serially)
+    // as im2col + batched matmul: the input is gathered tap by tap into [N, OH*OW, R*S*C_pad] (one strided
+    // copy per tap; padding taps stay zero from a fill step), the constant filter is laid out as
+    // [K, R*S*C_pad] on the host, and the matmul (persistent kernel, split-K when there are few tiles)
+    // writes [N, OH*OW, K], which the rest of the plan sees as a channels-last [N, K, OH, OW] tensor.
+    struct ConvGemm {
+        PlanTensor a, b, c, result;
+        std::vector<PlanTensor> addends;
+    };
+    std::optional<ConvGemm> conv_as_gemm(const ValueInfo& ci, const PlanTensor& x, const PlanTensor& w, const std::vector<int64_t>& native,
+                                         const std::vector<PlanTensor>& addends, int root) {
+        if (x.ss.rank() != 4 || w.ss.rank() != 4 || native.size() != 4) return std::nullopt;
+        const int64_t N = x.ss.shape[0], C = x.ss.shape[1], H = x.ss.shape[2], W = x.ss.shape[3];
+        const int64_t K = w.ss.shape[0], R = w.ss.shape[2], S = w.ss.shape[3], OH = native[2], OW = native[3];
+        const int64_t sy = ci.stride_y, sx = ci.stride_x, py = ci.pad_y, px = ci.pad_x;
+        const bool strided = sy != 1 || sx != 1;
+        const bool few_positions = N * OH * OW <= 512 && C * R * S >= 1024;
+        if (!strided && !few_positions) return std::nullopt;
+        if (N < 1 || N > 65535 || OH * OW < 64 || K < 16 || K % 4 != 0 || C < 1 || R * S > 64) return std::nullopt;
+        if (2.0 * (double)N * OH * OW * K * C * R * S < 2e8) return std::nullopt;
+        const ValueInfo& wi = g_.values[ci.inputs[1]];
+        if (wi.op != OpKind::Constant || !w.ss.has_simple_strides() || w.offset != 0) return std::nullopt;
+        // the result is channels-last in memory; the value the graph asks for (a view of it, possibly) must
+        // be expressible on that layout
+        if (!StridedShape({N, K, OH, OW}, {OH * OW * K, 1, OW * K, K}).view(shape_of(root)).has_value()) return std::nullopt;
+        // addends as [N, OH*OW, K]
+        ConvGemm g;
+        for (const PlanTensor& t : addends) {
+            const auto& st = t.ss.strides;
+            int64_t row;
+            if (OH * OW == 1 || (st[2] == 0 && st[3] == 0)) row = 0;
+            else if (OH == 1) row = st[3];
+            else if (OW == 1) row = st[2];
+            else if (st[2] == OW * st[3]) row = st[3];
+            else return std::nullopt;
+            g.addends.push_back(t.with(StridedShape({N, OH * OW, K}, {st[0], row, st[1]})));
+        }
+        const int64_t taps = R * S, c_pad = (C + 3) / 4 * 4, kk = taps * c_pad;
+        // the filter as [K, taps * c_pad], rounded to TF32 like the other tensor-core filters
+        auto data = std::make_shared<std::vector<uint8_t>>((size_t)(K * kk) * 4, 0);
+        {
+            const uint8_t* src = wi.const_data;
+            uint32_t* dst = (uint32_t*)data->data();
+            for (int64_t k = 0; k < K; k++)
+                for (int64_t c = 0; c < C; c++)
+                    for (int64_t t = 0; t < taps; t++) {
+                        uint32_t bits;
+                        memcpy(&bits, src + 4 * ((k * C + c) * taps + t), 4);
+                        if ((bits & 0x7F800000u) != 0x7F800000u) bits = (bits + 0x1000u) & 0xFFFFE000u;
+                        dst[k * kk + t * c_pad + c] = bits;
+                    }
+        }
+        PlanTensor wmat = alloc_const({K, kk}, DType::F32, ci.inputs[1], nullptr, data);
+        g.b = wmat.with(StridedShape({N, kk, K}, {0, 1, kk}));
+        // im2col
+        PlanTensor col = alloc_shared({N, OH * OW, kk}, DType::F32, root);
+        bool needs_zero = c_pad != C;
+        struct Tap { int64_t oy0, oy1, ox0, ox1; };
+        std::vector<Tap> ranges;
+        for (int64_t r = 0; r < R; r++)
+            for (int64_t q = 0; q < S; q++) {
+                // output rows whose input row  oy * sy + r - py  lies inside the image
+                Tap t;
+                t.oy0 = std::max<int64_t>(0, (py - r + sy - 1) / sy);
+                t.oy1 = std::min<int64_t>(OH, (H - 1 + py - r) / sy + 1);
+                t.ox0 = std::max<int64_t>(0, (px - q + sx - 1) / sx);
+                t.ox1 = std::min<int64_t>(OW, (W - 1 + px - q) / sx + 1);
+                if (H - 1 + py - r < 0) t.oy1 = 0;
+                if (W - 1 + px - q < 0) t.ox1 = 0;
+                needs_zero = needs_zero || t.oy0 > 0 || t.ox0 > 0 || t.oy1 < OH || t.ox1 < OW;
+                ranges.push_back(t);
+            }
+        if (needs_zero) {
+            ScalarBlock block;
+            Ref zero = block.constant(Scalar::f32(0.0f));
+            emit_scalar(block, {{col, zero}}, root, "zero");
+        }
+        for (int64_t r = 0; r < R; r++)
+            for (int64_t q = 0; q < S; q++) {
+                const Tap& t = ranges[(size_t)(r * S + q)];
+                if (t.oy1 <= t.oy0 || t.ox1 <= t.ox0) continue;
+                const int64_t ny = t.oy1 - t.oy0, nx = t.ox1 - t.ox0;
+                const int64_t iy0 = t.oy0 * sy + r - py, ix0 = t.ox0 * sx + q - px;
+                PlanTensor src = x.slice(2, iy0, iy0 + ny * sy, sy).slice(3, ix0, ix0 + nx * sx, sx);   // (end - start) / step elements
+                PlanTensor dst = col.with(StridedShape({N, C, ny, nx}, {OH * OW * kk, 1, OW * kk, kk}),
+                                          (t.oy0 * OW + t.ox0) * kk + (r * S + q) * c_pad);
+                emit_copy(src, dst, root);
+            }
+        g.a = col;
+        g.c = alloc_shared({N, OH * OW, K}, DType::F32, root);
+        g.result = g.c.with(StridedShape({N, K, OH, OW}, {OH * OW * K, 1, OW * K, K}));
+        if (!gemm_fits_tensor_core(g.a, g.b)) return std::nullopt;
+        return g;
     }
 
     bool conv_fits_tensor_core(const ValueInfo& ci, const PlanTensor& x, const PlanTensor& w, const std::vector<int64_t>& out) const {

@@ -182,3 +182,37 @@ def test_matmul_operands_not_contiguous_along_k():
     g = Graph()
     g.output(g.batched_mat_mul(g.input(shape(2, 64, 32)), g.input(shape(2, 32, 32))))
     assert " copy " not in plan_describe(g.to_bytes(), 0, math_mode=MATH_TF32)
+
+
+@pytest.mark.parametrize("n,c,h,w,k,r,stride,pad", [(16, 64, 32, 32, 64, 3, 2, 1), (32, 36, 33, 31, 48, 3, 2, 1), (32, 256, 16, 16, 256, 1, 2, 0),
+                                                     (24, 32, 40, 40, 32, 5, 3, 2), (2, 640, 8, 8, 320, 3, 1, 1), (8, 130, 10, 10, 256, 3, 1, 0)])
+def test_conv_as_im2col_matmul(n, c, h, w, k, r, stride, pad):
+    """Strided convolutions, and convolutions with few output positions under a long reduction, are planned as
+    im2col copies + one batched tensor-core matmul whose B operand (the filter) is shared by the batch.
+    Epilogue: bias, a per-(image, channel) addend broadcast over the positions, ReLU."""
+    g = Graph()
+    x = g.input(shape(n, c, h, w))
+    t = g.input(shape(n, k, 1, 1))
+    y = g.conv(x, g.constant_tensor(rng(1, k, c, r, r) * 0.05), stride, stride, pad, pad)
+    oh, ow = (h + 2 * pad - r) // stride + 1, (w + 2 * pad - r) // stride + 1
+    y = g.add(g.add(y, g.constant_tensor(rng(2, 1, k, 1, 1))), g.broadcast(t, shape(n, k, oh, ow)))
+    g.output(g.relu(y))
+    d = plan_describe(g.to_bytes(), 0, math_mode=MATH_TF32)
+    assert "via im2col" in d and "Gemm/tc" in d, d
+    check(g, 0, [rng(3, n, c, h, w), rng(4, n, k, 1, 1)])
+    # exact-f32 mode keeps the convolution kernel
+    assert "via im2col" not in plan_describe(g.to_bytes(), 0, math_mode=MATH_F32)
+    check(g, 0, [rng(3, n, c, h, w), rng(4, n, k, 1, 1)], mode=MATH_F32)
+
+
+@pytest.mark.parametrize("mode", [MATH_F32, MATH_TF32], ids=["f32", "tf32"])
+@pytest.mark.parametrize("b,m,n,k", [(1, 1, 1280, 1280), (3, 2, 70, 33), (1, 8, 300, 64), (2, 5, 9, 1000)])
+def test_matmul_with_few_rows(b, m, n, k, mode):
+    """m <= 8 (one token through a linear layer): the one-warp-per-row kernel on the transposed problem."""
+    g = Graph()
+    a = g.input(shape(b, m, k))
+    w = g.input(shape(b, n, k))
+    bias = g.input(shape(1, 1, n))
+    res = g.input(shape(b, m, n))
+    g.output(g.relu(g.add(g.add(g.batched_mat_mul(a, g.permute(w, [0, 2, 1])), bias), res)))
+    check(g, 0, [rng(1, b, m, k), rng(2, b, n, k), rng(3, 1, 1, n), rng(4, b, m, n)], mode=mode)
