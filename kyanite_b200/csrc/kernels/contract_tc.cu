@@ -44,7 +44,7 @@ struct TcParams {
     int32_t mode;   // 0 = matmul, 1 = conv
     int32_t bn, tmem_cols, k_iters, stages;
     int32_t splits, k_iters_total;   // matmul split K: slices per batch entry, K blocks overall (k_iters = per slice)
-    int32_t b_batch;                 // matmul: 1, or 0 when every batch entry multiplies the same B (batch stride 0)
+    int32_t a_batch, b_batch;        // matmul: 1, or 0 when every batch entry uses the same A / B (batch stride 0)
     // conv tiling
     int32_t cblocks, kernel_w, pad_y, pad_x, wb, hb, nb, tiles_w, tiles_h;
     int32_t wb_shift, hb_shift;   // log2 of wb, hb
@@ -140,7 +140,7 @@ tc_contract_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             if (!mbar_wait(empty_bar + 8u * s, parity, abandon, p.status, 1)) break;
             mbar_expect_tx(full_bar + 8u * s, kATileBytes + b_tile_bytes);
             if (p.mode == 0) {
-                tma_load_4d(a_base + s * kATileBytes, &map_a, full_bar + 8u * s, (k_first + it) * kBlockK, m0, batch, 0);
+                tma_load_4d(a_base + s * kATileBytes, &map_a, full_bar + 8u * s, (k_first + it) * kBlockK, m0, batch * p.a_batch, 0);
                 tma_load_3d(b_base + s * b_tile_bytes, &map_b, full_bar + 8u * s, (k_first + it) * kBlockK, ncol0, batch * p.b_batch);
             } else {
                 const int tap = it / p.cblocks, cb = it - tap * p.cblocks;
@@ -876,7 +876,8 @@ void tc_prepare_step(Step& step, uint32_t* status_word, int flags) {
         p.act = g.act;
         p.round_tf32 = g.round_tf32;
         // A: [batch, m, k] with k contiguous; B: [batch, k, n] with k contiguous
-        int64_t adims[4] = {g.k, g.m, g.batch, 1}, astr[4] = {1, g.sa[1], g.sa[0], 4};
+        p.a_batch = (g.batch > 1 && g.sa[0] == 0) ? 0 : 1;
+        int64_t adims[4] = {g.k, g.m, p.a_batch ? g.batch : 1, 1}, astr[4] = {1, g.sa[1], p.a_batch ? g.sa[0] : 4, 4};
         int abox[4] = {kBlockK, kBlockM, 1, 1};
         launch->map_a = make_map(g.a, 4, adims, astr, abox);
         p.bn = (int)std::min<int64_t>(round_up((int)std::min<int64_t>(n_cols, 256), 16), 256);
@@ -1146,6 +1147,7 @@ void matmul_static(const float* a, const float* b, float* c, int64_t m, int64_t 
     p.so[1] = n;
     p.so[2] = 1;
     p.status = dev.status;
+    p.a_batch = 1;
     p.b_batch = 1;
     const int stage_bytes = kATileBytes + bn * 128;
     p.stages = std::max(2, std::min(6, (200 * 1024) / stage_bytes));

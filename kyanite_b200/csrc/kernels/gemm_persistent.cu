@@ -44,7 +44,7 @@ constexpr int kGpStageTileBytes = 128 * 128;   // epilogue staging: 128 rows x 3
 
 struct GemmPersistentParams {
     int32_t bn, stages, k_iters;
-    int32_t b_batch;                 // 1, or 0 when every batch entry multiplies the same B (batch stride 0)
+    int32_t a_batch, b_batch;        // 1, or 0 when every batch entry uses the same A / B (batch stride 0)
     int32_t splits, k_iters_slice;   // split K: slice sp of a tile covers K blocks [sp * k_iters_slice, ...) and is stored
                                      // as matrix `batch * splits + sp` of the output map (the partial-sum buffer)
     int32_t m_tiles, n_tiles, batch, total_tiles;
@@ -52,7 +52,7 @@ struct GemmPersistentParams {
     const float* add1;
     const float* add2;
     int64_t s1[3], s2[3];            // (batch, row, col) strides of the addends
-    int32_t add1_mode, add2_mode;    // 0 absent, 1 one value per column, 2 a value per element (row-contiguous)
+    int32_t add1_mode, add2_mode;    // 0 absent, 1 one value per column, 2 a value per element (row-contiguous), 4 one value per row
     int32_t act;
     uint32_t* status;
 };
@@ -135,7 +135,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 const uint32_t bar = full_bar + 8u * s;
                 mbar_expect_tx(bar, stage_bytes);
                 const uint32_t dst = base + (uint32_t)s * stage_bytes;
-                tma_load_3d(dst, &map_a, bar, k * kGpBlockK, mt * kGpBlockM, bt);
+                tma_load_3d(dst, &map_a, bar, k * kGpBlockK, mt * kGpBlockM, bt * p.a_batch);
                 tma_load_3d(dst + kGpATileBytes, &map_b, bar, k * kGpBlockK, nt * p.bn, bt * p.b_batch);
                 if (++s == stages) { s = 0; round++; }
             }
@@ -224,6 +224,10 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                         const float mine = col < p.n ? __ldg(add + bt * st[0] + col * st[2]) : 0.f;
 #pragma unroll
                         for (int j = 0; j < 32; j++) v[j] = __float_as_uint(__uint_as_float(v[j]) + __shfl_sync(0xffffffffu, mine, j));
+                    } else if (mode == 4) {
+                        const float mine = row_ok ? __ldg(add + bt * st[0] + row * st[1]) : 0.f;
+#pragma unroll
+                        for (int j = 0; j < 32; j++) v[j] = __float_as_uint(__uint_as_float(v[j]) + mine);
                     } else if (row_ok) {
                         const float* src = add + bt * st[0] + row * st[1] + col0;
                         if (col0 + 32 <= p.n && ((uintptr_t)src & 15) == 0) {
@@ -287,11 +291,13 @@ struct GemmPersistentLaunch {
     int smem_bytes;
 };
 
-// 0 absent, 1 one value per column (row stride 0), 2 a value per element with contiguous rows, 3 anything else
+// 0 absent, 1 one value per column (row stride 0), 2 a value per element with contiguous rows, 4 one value per
+// row (column stride 0), 3 anything else
 int classify_addend(const float* ptr, const int64_t* st) {
     if (ptr == nullptr) return 0;
     if (st[1] == 0) return 1;
     if (st[2] == 1) return 2;
+    if (st[2] == 0) return 4;
     return 3;
 }
 
@@ -339,7 +345,8 @@ std::shared_ptr<void> gemm_persistent_prepare(const GemmParams& g, uint32_t* sta
     const int fixed = 1024 + 2 * kGpStageTileBytes + 16 * 8 + 64 + 64;
     p.stages = std::max(2, std::min(6, (227 * 1024 - fixed) / stage_bytes));
     l->smem_bytes = fixed + p.stages * stage_bytes;
-    int64_t adims[3] = {g.k, g.m, g.batch}, astr[3] = {1, g.sa[1], g.sa[0]};
+    p.a_batch = (g.batch > 1 && g.sa[0] == 0) ? 0 : 1;
+    int64_t adims[3] = {g.k, g.m, p.a_batch ? g.batch : 1}, astr[3] = {1, g.sa[1], p.a_batch ? g.sa[0] : 4};
     int abox[3] = {kGpBlockK, kGpBlockM, 1};
     l->map_a = tc_make_map(g.a, 3, adims, astr, abox, true);
     p.b_batch = (g.batch > 1 && g.sb[0] == 0) ? 0 : 1;

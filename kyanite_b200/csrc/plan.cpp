@@ -904,7 +904,7 @@ class Planner {
         const int64_t batch = a.ss.shape[0], m = a.ss.shape[1], k = a.ss.shape[2], n = b.ss.shape[2];
         if (batch < 1 || batch > 65535 || m < 64 || n < 8 || k < 8) return false;
         if (k > 1 && (a.ss.strides[2] != 1 || b.ss.strides[1] != 1)) return false;
-        if (!tma_stride_ok(m, a.ss.strides[1]) || !tma_stride_ok(batch, a.ss.strides[0])) return false;
+        if (!tma_stride_ok(m, a.ss.strides[1]) || !(tma_stride_ok(batch, a.ss.strides[0]) || a.ss.strides[0] == 0)) return false;
         // (a B shared by every batch entry, batch stride 0, is loaded with batch coordinate 0)
         if (!tma_stride_ok(n, b.ss.strides[2]) || !(tma_stride_ok(batch, b.ss.strides[0]) || b.ss.strides[0] == 0)) return false;
         if (a.offset % 4 != 0 || b.offset % 4 != 0) return false;
@@ -967,10 +967,13 @@ class Planner {
         if (2.0 * (double)N * OH * OW * K * C * R * S < 2e8) return std::nullopt;
         const ValueInfo& wi = g_.values[ci.inputs[1]];
         if (wi.op != OpKind::Constant || !w.ss.has_simple_strides() || w.offset != 0) return std::nullopt;
-        // the result is channels-last in memory; the value the graph asks for (a view of it, possibly) must
-        // be expressible on that layout
-        if (!StridedShape({N, K, OH, OW}, {OH * OW * K, 1, OW * K, K}).view(shape_of(root)).has_value()) return std::nullopt;
-        // addends as [N, OH*OW, K]
+        // Two orientations.  positions x channels: the result is channels-last in memory, which the next
+        // tensor-core convolution wants.  If the value the graph asks for (a view of the result, say the
+        // [N, groups, ...] view a group norm takes) cannot be expressed on that layout, channels x positions:
+        // the filter is the A operand (shared by the batch), the result is plain NCHW.
+        const bool nchw = !StridedShape({N, K, OH, OW}, {OH * OW * K, 1, OW * K, K}).view(shape_of(root)).has_value();
+        if (nchw && (K < 64 || OH * OW < 16 || (OH * OW) % 4 != 0)) return std::nullopt;
+        // addends as [N, OH*OW, K] or [N, K, OH*OW]
         ConvGemm g;
         for (const PlanTensor& t : addends) {
             const auto& st = t.ss.strides;
@@ -980,7 +983,8 @@ class Planner {
             else if (OW == 1) row = st[2];
             else if (st[2] == OW * st[3]) row = st[3];
             else return std::nullopt;
-            g.addends.push_back(t.with(StridedShape({N, OH * OW, K}, {st[0], row, st[1]})));
+            if (nchw) g.addends.push_back(t.with(StridedShape({N, K, OH * OW}, {st[0], st[1], row})));
+            else g.addends.push_back(t.with(StridedShape({N, OH * OW, K}, {st[0], row, st[1]})));
         }
         const int64_t taps = R * S, c_pad = (C + 3) / 4 * 4, kk = taps * c_pad;
         // the filter as [K, taps * c_pad], rounded to TF32 like the other tensor-core filters
@@ -998,7 +1002,8 @@ class Planner {
                     }
         }
         PlanTensor wmat = alloc_const({K, kk}, DType::F32, ci.inputs[1], nullptr, data);
-        g.b = wmat.with(StridedShape({N, kk, K}, {0, 1, kk}));
+        if (nchw) g.a = wmat.with(StridedShape({N, K, kk}, {0, kk, 1}));
+        else g.b = wmat.with(StridedShape({N, kk, K}, {0, 1, kk}));
         // im2col
         PlanTensor col = alloc_shared({N, OH * OW, kk}, DType::F32, root);
         bool needs_zero = c_pad != C;
@@ -1033,9 +1038,15 @@ class Planner {
                                           (t.oy0 * OW + t.ox0) * kk + (r * S + q) * c_pad);
                 emit_copy(src, dst, root);
             }
-        g.a = col;
-        g.c = alloc_shared({N, OH * OW, K}, DType::F32, root);
-        g.result = g.c.with(StridedShape({N, K, OH, OW}, {OH * OW * K, 1, OW * K, K}));
+        if (nchw) {
+            g.b = col.with(StridedShape({N, kk, OH * OW}, {OH * OW * kk, 1, kk}));
+            g.c = alloc_shared({N, K, OH * OW}, DType::F32, root);
+            g.result = g.c.with(StridedShape({N, K, OH, OW}, {K * OH * OW, OH * OW, OW, 1}));
+        } else {
+            g.a = col;
+            g.c = alloc_shared({N, OH * OW, K}, DType::F32, root);
+            g.result = g.c.with(StridedShape({N, K, OH, OW}, {OH * OW * K, 1, OW * K, K}));
+        }
         if (!gemm_fits_tensor_core(g.a, g.b)) return std::nullopt;
         return g;
     }

@@ -216,3 +216,21 @@ def test_matmul_with_few_rows(b, m, n, k, mode):
     res = g.input(shape(b, m, n))
     g.output(g.relu(g.add(g.add(g.batched_mat_mul(a, g.permute(w, [0, 2, 1])), bias), res)))
     check(g, 0, [rng(1, b, m, k), rng(2, b, n, k), rng(3, 1, 1, n), rng(4, b, m, n)], mode=mode)
+
+
+@pytest.mark.parametrize("n,c,h,w,k,r,stride,pad", [(2, 640, 8, 8, 320, 3, 1, 1), (16, 64, 32, 32, 64, 3, 2, 1), (2, 256, 16, 16, 128, 3, 1, 1),
+                                                     (32, 32, 32, 32, 128, 3, 2, 1)])
+def test_conv_as_im2col_matmul_with_nchw_result(n, c, h, w, k, r, stride, pad):
+    """The graph takes the convolution's result through a flat [N, K*OH*OW] view before a per-element term is
+    added, which only a plain NCHW result can serve: the matmul then runs channels x positions with the
+    filter as the A operand shared by the batch, and the step may be split along K."""
+    oh, ow = (h + 2 * pad - r) // stride + 1, (w + 2 * pad - r) // stride + 1
+    g = Graph()
+    x = g.input(shape(n, c, h, w))
+    y = g.conv(x, g.constant_tensor(rng(1, k, c, r, r) * 0.05), stride, stride, pad, pad)
+    v = g.view(y, shape(n, k * oh * ow))
+    term = g.constant_tensor(rng(2, 1, k * oh * ow))
+    g.output(g.relu(g.add(v, g.broadcast(term, shape(n, k * oh * ow)))))
+    d = plan_describe(g.to_bytes(), 0, math_mode=MATH_TF32)
+    assert "via im2col" in d and f"m={k} n={oh * ow}" in d, d
+    check(g, 0, [rng(3, n, c, h, w)])
