@@ -131,6 +131,10 @@ struct Executor {
                     s.conv.add1 = ptr.size() > 3 ? (const float*)ptr[3] : nullptr;
                     s.conv.add2 = ptr.size() > 4 ? (const float*)ptr[4] : nullptr;
                     break;
+                case StepKind::Im2col:
+                    s.im2col.in = (const float*)ptr[0];
+                    s.im2col.col = (float*)ptr[1];
+                    break;
                 case StepKind::ConvChain:
                     s.chain.in = (const float*)ptr[0];
                     s.chain.out = (float*)ptr[1];
@@ -156,6 +160,7 @@ struct Executor {
             case StepKind::Gemm: err = s.tensor_core ? tc_launch_step(s, stream) : launch_gemm_simt(s.gemm, stream); break;
             case StepKind::Conv: err = s.tensor_core ? tc_launch_step(s, stream) : launch_conv_simt(s.conv, stream); break;
             case StepKind::ConvChain: err = tc_launch_step(s, stream); break;
+            case StepKind::Im2col: err = launch_im2col(s.im2col, stream); break;
             default: fail(KN_ERR_INTERNAL, "unknown step kind");
         }
         if (err != 0)

@@ -161,12 +161,22 @@ struct ConvChainParams {
     uint8_t head_relu[kMaxChainHeads];
 };
 
+// ---- im2col for a convolution that runs as a matmul: col[n][oy*OW + ox][tap][c] = in[n][c][oy*sy + r - py][ox*sx + s - px]
+// (tap = r * S + s), zero outside the image and for the padding channels c >= C up to c_pad.
+struct Im2colParams {
+    const float* in;     // [N, C, H, W], any strides
+    float* col;          // [N, OH*OW, R*S, c_pad], dense
+    int32_t n, c, h, w, r, s, oh, ow, stride_y, stride_x, pad_y, pad_x, c_pad;
+    int64_t s_in[4];
+};
+
 // All launchers enqueue on `stream` and return the cudaError_t of the launch as int.
 int launch_scalar(const ScalarParams& p, cudaStream_t stream);
 int launch_reduce(const ReduceParams& p, cudaStream_t stream);
 int launch_softmax(const RowParams& p, cudaStream_t stream);
 int launch_layernorm(const RowParams& p, cudaStream_t stream);
 int launch_gather(const GatherParams& p, cudaStream_t stream);
+int launch_im2col(const Im2colParams& p, cudaStream_t stream);
 int launch_gemm_simt(const GemmParams& p, cudaStream_t stream);
 int launch_conv_simt(const ConvParams& p, cudaStream_t stream);
 

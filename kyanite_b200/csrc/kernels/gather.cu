@@ -140,4 +140,70 @@ int launch_gather(const GatherParams& p, cudaStream_t stream) {
     return (int)cudaGetLastError();
 }
 
+// ------------------------------------------------------------------ im2col
+namespace {
+
+// One block: one filter tap, 32 output positions of one image, 32 channels.  A source that is contiguous
+// along W is read with the lanes along the positions and turned through shared memory so that the lanes
+// run along the channels for the store (rows of 128 bytes); a channels-last source is read that way already.
+__global__ void __launch_bounds__(256) im2col_kernel(const __grid_constant__ Im2colParams p, int p_tiles, int c_tiles, int channels_last) {
+    pdl_enter();
+    __shared__ float tile[32][33];
+    int rem = blockIdx.x;
+    const int ct = rem % c_tiles;
+    rem /= c_tiles;
+    const int pt = rem % p_tiles;
+    rem /= p_tiles;
+    const int tap = rem % (p.r * p.s);
+    const int n = rem / (p.r * p.s);
+    const int r = tap / p.s, q = tap - r * p.s;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int positions = p.oh * p.ow;
+    const float* in = p.in + (int64_t)n * p.s_in[0];
+    float* col = p.col + ((int64_t)n * positions * (p.r * p.s) + tap) * p.c_pad;
+    const int p0 = pt * 32, c0 = ct * 32;
+    if (!channels_last) {
+        // this thread's position for the read: p0 + tx
+        const int pos = p0 + tx;
+        const int oy = pos / p.ow, ox = pos - oy * p.ow;
+        const int iy = oy * p.stride_y + r - p.pad_y, ix = ox * p.stride_x + q - p.pad_x;
+        const bool inside = pos < positions && iy >= 0 && iy < p.h && ix >= 0 && ix < p.w;
+        const float* src = in + (int64_t)iy * p.s_in[2] + (int64_t)ix * p.s_in[3];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int c = c0 + ty + 8 * j;
+            tile[ty + 8 * j][tx] = (inside && c < p.c) ? __ldg(src + (int64_t)c * p.s_in[1]) : 0.f;
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const int pos = p0 + ty + 8 * j, c = c0 + tx;
+        if (pos >= positions || c >= p.c_pad) continue;
+        float v;
+        if (channels_last) {
+            const int oy = pos / p.ow, ox = pos - oy * p.ow;
+            const int iy = oy * p.stride_y + r - p.pad_y, ix = ox * p.stride_x + q - p.pad_x;
+            const bool inside = iy >= 0 && iy < p.h && ix >= 0 && ix < p.w && c < p.c;
+            v = inside ? __ldg(in + (int64_t)c * p.s_in[1] + (int64_t)iy * p.s_in[2] + (int64_t)ix * p.s_in[3]) : 0.f;
+        } else {
+            v = tile[tx][ty + 8 * j];
+        }
+        col[(int64_t)pos * (p.r * p.s) * p.c_pad + c] = v;
+    }
+}
+
+}  // namespace
+
+int launch_im2col(const Im2colParams& p, cudaStream_t stream) {
+    const int64_t positions = (int64_t)p.oh * p.ow;
+    if (p.n == 0 || positions == 0 || p.c_pad == 0) return 0;
+    const int64_t p_tiles = (positions + 31) / 32, c_tiles = (p.c_pad + 31) / 32;
+    const int64_t blocks = p_tiles * c_tiles * p.r * p.s * p.n;
+    if (blocks >= (1ll << 31)) return (int)cudaErrorInvalidValue;
+    const int channels_last = (p.c <= 1 || p.s_in[1] == 1) ? 1 : 0;
+    launch_pdl(im2col_kernel, dim3((unsigned)blocks), dim3(256), (size_t)0, stream, p, (int)p_tiles, (int)c_tiles, channels_last);
+    return (int)cudaGetLastError();
+}
+
 }  // namespace kn

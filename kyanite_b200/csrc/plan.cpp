@@ -14,7 +14,7 @@
 namespace kn {
 
 const char* step_kind_name(StepKind k) {
-    static const char* names[] = {"Scalar", "Reduce", "Softmax", "Layernorm", "Gather", "Gemm", "Conv", "ConvChain"};
+    static const char* names[] = {"Scalar", "Reduce", "Softmax", "Layernorm", "Gather", "Gemm", "Conv", "ConvChain", "Im2col"};
     return (int)k < 8 ? names[(int)k] : "?";
 }
 
@@ -946,8 +946,8 @@ class Planner {
 
     // A convolution the tensor-core convolution kernels do not take (stride > 1) or take badly (a handful
     // of output positions under a long reduction: one M tile, so a handful of CTAs walk K = C*R*S serially)
-    // as im2col + batched matmul: the input is gathered tap by tap into [N, OH*OW, R*S*C_pad] (one strided
-    // copy per tap; padding taps stay zero from a fill step), the constant filter is laid out as
+    // as im2col + batched matmul: the input is gathered into [N, OH*OW, R*S*C_pad] by one Im2col step (zeros
+    // for taps outside the image and for padding channels), the constant filter is laid out as
     // [K, R*S*C_pad] on the host, and the matmul (persistent kernel, split-K when there are few tiles)
     // writes [N, OH*OW, K], which the rest of the plan sees as a channels-last [N, K, OH, OW] tensor.
     struct ConvGemm {
@@ -1006,38 +1006,22 @@ class Planner {
         else g.b = wmat.with(StridedShape({N, kk, K}, {0, 1, kk}));
         // im2col
         PlanTensor col = alloc_shared({N, OH * OW, kk}, DType::F32, root);
-        bool needs_zero = c_pad != C;
-        struct Tap { int64_t oy0, oy1, ox0, ox1; };
-        std::vector<Tap> ranges;
-        for (int64_t r = 0; r < R; r++)
-            for (int64_t q = 0; q < S; q++) {
-                // output rows whose input row  oy * sy + r - py  lies inside the image
-                Tap t;
-                t.oy0 = std::max<int64_t>(0, (py - r + sy - 1) / sy);
-                t.oy1 = std::min<int64_t>(OH, (H - 1 + py - r) / sy + 1);
-                t.ox0 = std::max<int64_t>(0, (px - q + sx - 1) / sx);
-                t.ox1 = std::min<int64_t>(OW, (W - 1 + px - q) / sx + 1);
-                if (H - 1 + py - r < 0) t.oy1 = 0;
-                if (W - 1 + px - q < 0) t.ox1 = 0;
-                needs_zero = needs_zero || t.oy0 > 0 || t.ox0 > 0 || t.oy1 < OH || t.ox1 < OW;
-                ranges.push_back(t);
-            }
-        if (needs_zero) {
-            ScalarBlock block;
-            Ref zero = block.constant(Scalar::f32(0.0f));
-            emit_scalar(block, {{col, zero}}, root, "zero");
+        {
+            Step st;
+            st.kind = StepKind::Im2col;
+            st.value = root;
+            st.operands = {x, col};
+            st.writes = {0, 1};
+            Im2colParams& ip = st.im2col;
+            ip.n = (int32_t)N; ip.c = (int32_t)C; ip.h = (int32_t)H; ip.w = (int32_t)W;
+            ip.r = (int32_t)R; ip.s = (int32_t)S; ip.oh = (int32_t)OH; ip.ow = (int32_t)OW;
+            ip.stride_y = (int32_t)sy; ip.stride_x = (int32_t)sx; ip.pad_y = (int32_t)py; ip.pad_x = (int32_t)px;
+            ip.c_pad = (int32_t)c_pad;
+            for (int d = 0; d < 4; d++) ip.s_in[d] = x.ss.strides[d];
+            st.desc = "im2col n=" + std::to_string(N) + " c=" + std::to_string(C) + " hw=" + std::to_string(H) + "x" + std::to_string(W) +
+                      " rs=" + std::to_string(R) + "x" + std::to_string(S) + " -> " + std::to_string(OH) + "x" + std::to_string(OW);
+            push_step(std::move(st));
         }
-        for (int64_t r = 0; r < R; r++)
-            for (int64_t q = 0; q < S; q++) {
-                const Tap& t = ranges[(size_t)(r * S + q)];
-                if (t.oy1 <= t.oy0 || t.ox1 <= t.ox0) continue;
-                const int64_t ny = t.oy1 - t.oy0, nx = t.ox1 - t.ox0;
-                const int64_t iy0 = t.oy0 * sy + r - py, ix0 = t.ox0 * sx + q - px;
-                PlanTensor src = x.slice(2, iy0, iy0 + ny * sy, sy).slice(3, ix0, ix0 + nx * sx, sx);   // (end - start) / step elements
-                PlanTensor dst = col.with(StridedShape({N, C, ny, nx}, {OH * OW * kk, 1, OW * kk, kk}),
-                                          (t.oy0 * OW + t.ox0) * kk + (r * S + q) * c_pad);
-                emit_copy(src, dst, root);
-            }
         if (nchw) {
             g.b = col.with(StridedShape({N, kk, OH * OW}, {OH * OW * kk, 1, kk}));
             g.c = alloc_shared({N, K, OH * OW}, DType::F32, root);

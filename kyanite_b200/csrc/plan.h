@@ -46,7 +46,7 @@ struct PlanTensor {
 
 struct TcLaunch;   // tensor maps and launch geometry of a tensor-core step (kernels/contract_tc.cu)
 
-enum class StepKind : uint8_t { Scalar = 0, Reduce, Softmax, Layernorm, Gather, Gemm, Conv, ConvChain, COUNT };
+enum class StepKind : uint8_t { Scalar = 0, Reduce, Softmax, Layernorm, Gather, Gemm, Conv, ConvChain, Im2col, COUNT };
 const char* step_kind_name(StepKind k);
 
 struct Step {
@@ -68,6 +68,7 @@ struct Step {
     GemmParams gemm{};
     ConvParams conv{};
     ConvChainParams chain{};
+    Im2colParams im2col{};
 };
 
 struct Plan {
