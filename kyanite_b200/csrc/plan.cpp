@@ -15,7 +15,7 @@ namespace kn {
 
 const char* step_kind_name(StepKind k) {
     static const char* names[] = {"Scalar", "Reduce", "Softmax", "Layernorm", "Gather", "Gemm", "Conv", "ConvChain", "Im2col"};
-    return (int)k < 8 ? names[(int)k] : "?";
+    return (int)k < (int)StepKind::COUNT ? names[(int)k] : "?";
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -962,7 +962,10 @@ class Planner {
         const int64_t sy = ci.stride_y, sx = ci.stride_x, py = ci.pad_y, px = ci.pad_x;
         const bool strided = sy != 1 || sx != 1;
         const bool few_positions = N * OH * OW <= 512 && C * R * S >= 1024;
-        if (!strided && !few_positions) return std::nullopt;
+        // a 1x1 convolution IS a matmul over the channels; the generic convolution kernel stores its result
+        // one row per thread, which the matmul kernels' staged epilogues do not
+        const bool pointwise = R == 1 && S == 1;
+        if (!strided && !few_positions && !pointwise) return std::nullopt;
         if (N < 1 || N > 65535 || OH * OW < 64 || K < 16 || K % 4 != 0 || C < 1 || R * S > 64) return std::nullopt;
         if (2.0 * (double)N * OH * OW * K * C * R * S < 2e8) return std::nullopt;
         const ValueInfo& wi = g_.values[ci.inputs[1]];
@@ -1004,9 +1007,16 @@ class Planner {
         PlanTensor wmat = alloc_const({K, kk}, DType::F32, ci.inputs[1], nullptr, data);
         if (nchw) g.a = wmat.with(StridedShape({N, K, kk}, {0, kk, 1}));
         else g.b = wmat.with(StridedShape({N, kk, K}, {0, 1, kk}));
-        // im2col
-        PlanTensor col = alloc_shared({N, OH * OW, kk}, DType::F32, root);
-        {
+        // im2col (not needed for a 1x1 stride-1 convolution of a channels-last tensor: that is the matrix already)
+        PlanTensor col;
+        const auto& xs = x.ss.strides;
+        if (pointwise && !strided && py == 0 && px == 0 && c_pad == C && (C <= 1 || xs[1] == 1) && xs[2] == W * xs[3] && xs[3] % 4 == 0 &&
+            xs[3] >= C && (N <= 1 || xs[0] % 4 == 0) && x.offset % 4 == 0) {
+            col = x.with(StridedShape({N, OH * OW, kk}, {xs[0], xs[3], 1}));
+        } else {
+            col = alloc_shared({N, OH * OW, kk}, DType::F32, root);
+        }
+        if (col.buf != x.buf || col.offset != x.offset) {
             Step st;
             st.kind = StepKind::Im2col;
             st.value = root;
@@ -1023,7 +1033,7 @@ class Planner {
             push_step(std::move(st));
         }
         if (nchw) {
-            g.b = col.with(StridedShape({N, kk, OH * OW}, {OH * OW * kk, 1, kk}));
+            g.b = col.with(StridedShape({N, kk, OH * OW}, {col.ss.strides[0], 1, col.ss.strides[1]}));
             g.c = alloc_shared({N, K, OH * OW}, DType::F32, root);
             g.result = g.c.with(StridedShape({N, K, OH, OW}, {K * OH * OW, OH * OW, OW, 1}));
         } else {

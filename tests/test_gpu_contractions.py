@@ -234,3 +234,20 @@ def test_conv_as_im2col_matmul_with_nchw_result(n, c, h, w, k, r, stride, pad):
     d = plan_describe(g.to_bytes(), 0, math_mode=MATH_TF32)
     assert "via im2col" in d and f"m={k} n={oh * ow}" in d, d
     check(g, 0, [rng(3, n, c, h, w)])
+
+
+@pytest.mark.parametrize("n,c,h,w,k,chained", [(2, 320, 64, 64, 320, False), (12, 96, 40, 24, 136, False), (4, 256, 32, 32, 256, True)])
+def test_pointwise_conv_as_matmul(n, c, h, w, k, chained):
+    """1x1 stride-1 convolutions are matmuls over the channels: from an NCHW input through one Im2col step (a
+    transpose), from the channels-last result of a previous convolution-as-matmul directly."""
+    g = Graph()
+    x = g.input(shape(n, c, h, w))
+    cur, cin = x, c
+    if chained:
+        cur = g.relu(g.add(g.conv(x, g.constant_tensor(rng(5, c, c, 1, 1) * 0.1), 1, 1, 0, 0), g.constant_tensor(rng(6, 1, c, 1, 1))))
+    y = g.add(g.conv(cur, g.constant_tensor(rng(1, k, cin, 1, 1) * 0.1), 1, 1, 0, 0), g.constant_tensor(rng(2, 1, k, 1, 1)))
+    g.output(y)
+    d = plan_describe(g.to_bytes(), 0, math_mode=MATH_TF32)
+    steps = [l.split()[2] for l in d.splitlines() if l.startswith("step")]
+    assert steps.count("Gemm/tc") == (2 if chained else 1) and steps.count("Im2col") == 1 and "Conv" not in " ".join(steps), d
+    check(g, 0, [rng(3, n, c, h, w)])
