@@ -143,12 +143,14 @@ int launch_gather(const GatherParams& p, cudaStream_t stream) {
 // ------------------------------------------------------------------ im2col
 namespace {
 
-// One block: one filter tap, 32 output positions of one image, 32 channels.  A source that is contiguous
+constexpr int kIm2colC = 128;   // channels per block
+
+// One block: one filter tap, 32 output positions of one image, 128 channels (16 elements per thread in flight).  A source that is contiguous
 // along W is read with the lanes along the positions and turned through shared memory so that the lanes
 // run along the channels for the store (rows of 128 bytes); a channels-last source is read that way already.
 __global__ void __launch_bounds__(256) im2col_kernel(const __grid_constant__ Im2colParams p, int p_tiles, int c_tiles, int channels_last) {
     pdl_enter();
-    __shared__ float tile[32][33];
+    __shared__ float tile[kIm2colC][33];
     int rem = blockIdx.x;
     const int ct = rem % c_tiles;
     rem /= c_tiles;
@@ -161,7 +163,7 @@ __global__ void __launch_bounds__(256) im2col_kernel(const __grid_constant__ Im2
     const int positions = p.oh * p.ow;
     const float* in = p.in + (int64_t)n * p.s_in[0];
     float* col = p.col + ((int64_t)n * positions * (p.r * p.s) + tap) * p.c_pad;
-    const int p0 = pt * 32, c0 = ct * 32;
+    const int p0 = pt * 32, c0 = ct * kIm2colC;
     if (!channels_last) {
         // this thread's position for the read: p0 + tx
         const int pos = p0 + tx;
@@ -169,16 +171,21 @@ __global__ void __launch_bounds__(256) im2col_kernel(const __grid_constant__ Im2
         const int iy = oy * p.stride_y + r - p.pad_y, ix = ox * p.stride_x + q - p.pad_x;
         const bool inside = pos < positions && iy >= 0 && iy < p.h && ix >= 0 && ix < p.w;
         const float* src = in + (int64_t)iy * p.s_in[2] + (int64_t)ix * p.s_in[3];
+        float v[kIm2colC / 8];
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
+        for (int j = 0; j < kIm2colC / 8; j++) {
             const int c = c0 + ty + 8 * j;
-            tile[ty + 8 * j][tx] = (inside && c < p.c) ? __ldg(src + (int64_t)c * p.s_in[1]) : 0.f;
+            v[j] = (inside && c < p.c) ? __ldg(src + (int64_t)c * p.s_in[1]) : 0.f;
         }
+#pragma unroll
+        for (int j = 0; j < kIm2colC / 8; j++) tile[ty + 8 * j][tx] = v[j];
         __syncthreads();
     }
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
-        const int pos = p0 + ty + 8 * j, c = c0 + tx;
+    for (int j = 0; j < kIm2colC / 8; j++) {
+        // store: lanes along the channels; (j & 3) picks the 32-channel group, ty + 8 * (j >> 2) the position
+        const int cl = 32 * (j & 3) + tx, pl = ty + 8 * (j >> 2);
+        const int pos = p0 + pl, c = c0 + cl;
         if (pos >= positions || c >= p.c_pad) continue;
         float v;
         if (channels_last) {
@@ -187,7 +194,7 @@ __global__ void __launch_bounds__(256) im2col_kernel(const __grid_constant__ Im2
             const bool inside = iy >= 0 && iy < p.h && ix >= 0 && ix < p.w && c < p.c;
             v = inside ? __ldg(in + (int64_t)c * p.s_in[1] + (int64_t)iy * p.s_in[2] + (int64_t)ix * p.s_in[3]) : 0.f;
         } else {
-            v = tile[tx][ty + 8 * j];
+            v = tile[cl][pl];
         }
         col[(int64_t)pos * (p.r * p.s) * p.c_pad + c] = v;
     }
@@ -198,7 +205,7 @@ __global__ void __launch_bounds__(256) im2col_kernel(const __grid_constant__ Im2
 int launch_im2col(const Im2colParams& p, cudaStream_t stream) {
     const int64_t positions = (int64_t)p.oh * p.ow;
     if (p.n == 0 || positions == 0 || p.c_pad == 0) return 0;
-    const int64_t p_tiles = (positions + 31) / 32, c_tiles = (p.c_pad + 31) / 32;
+    const int64_t p_tiles = (positions + 31) / 32, c_tiles = (p.c_pad + kIm2colC - 1) / kIm2colC;
     const int64_t blocks = p_tiles * c_tiles * p.r * p.s * p.n;
     if (blocks >= (1ll << 31)) return (int)cudaErrorInvalidValue;
     const int channels_last = (p.c <= 1 || p.s_in[1] == 1) ? 1 : 0;

@@ -318,7 +318,14 @@ std::shared_ptr<void> gemm_persistent_prepare(const GemmParams& g, uint32_t* sta
     auto l = std::make_shared<GemmPersistentLaunch>();
     GemmPersistentParams& p = l->p;
     memset(&p, 0, sizeof(p));
-    p.bn = (int)std::min<int64_t>((std::min<int64_t>(g.n, 256) + 15) / 16 * 16, 256);
+    // column blocks of equal width: n = 320 is two blocks of 160, not 256 + 64 with three quarters of the second empty
+    {
+        const int64_t blocks = (g.n + 255) / 256;
+        // (several blocks: a multiple of 32, the width of an epilogue chunk, so that no chunk reaches into the
+        // next block's columns; a single block is clipped by the store's tensor bounds)
+        const int64_t unit = blocks > 1 ? 32 : 16;
+        p.bn = (int)std::min<int64_t>(((g.n + blocks - 1) / blocks + unit - 1) / unit * unit, 256);
+    }
     p.k_iters = (int)((g.k + kGpBlockK - 1) / kGpBlockK);
     p.m_tiles = (int)((g.m + kGpBlockM - 1) / kGpBlockM);
     p.n_tiles = (int)((g.n + p.bn - 1) / p.bn);

@@ -828,11 +828,13 @@ class Planner {
                 // A contraction with few output tiles but a long K would leave most SMs idle: cut K into
                 // slices computed by separate CTAs.  Their partial tiles go to a scratch buffer of the
                 // arena (live only during this step) and a second small kernel sums them.
-                const int64_t bn = p.n > 256 ? 128 : std::min<int64_t>((std::min<int64_t>(p.n, 256) + 15) / 16 * 16, 256);
+                const int64_t n_blocks = (p.n + 255) / 256;   // the persistent kernel's column blocks
+                const int64_t bn = std::min<int64_t>(((p.n + n_blocks - 1) / n_blocks + 31) / 32 * 32, 256);
                 const int64_t tiles = ((p.m + 127) / 128) * ((p.n + bn - 1) / bn) * p.batch;
                 const int64_t k_blocks = (p.k + 31) / 32;
-                if (tiles < 48 && k_blocks >= 16) {
-                    int64_t splits = std::min<int64_t>(std::min<int64_t>(k_blocks / 4, (96 + tiles - 1) / tiles), 32);
+                if (tiles < 74 && k_blocks >= 16) {
+                    // aim at one CTA per SM
+                    int64_t splits = std::min<int64_t>(std::min<int64_t>(k_blocks / 4, (148 + tiles - 1) / tiles), 32);
                     if (splits > 1) {
                         const int64_t per = (k_blocks + splits - 1) / splits;
                         splits = (k_blocks + per - 1) / per;

@@ -142,6 +142,25 @@ def case_conv_unet(rng):
     return g, 8, [rng.standard_normal((8, 320, 64, 64)).astype(np.float32)]
 
 
+def _conv_case(n, c, h, w, k, r, stride, pad, doc):
+    def build(rng):
+        g = Graph()
+        x = g.input(shape(BATCH, c, h, w))
+        y = g.conv(x, _const(g, rng, k, c, r, r), stride, stride, pad, pad)
+        g.output(g.add(y, _const(g, rng, 1, k, 1, 1)))
+        return g, n, [rng.standard_normal((n, c, h, w)).astype(np.float32)]
+    build.__doc__ = doc
+    return build
+
+
+def case_transpose(rng):
+    """Value matrices of 384 attention heads made K-contiguous: [384, 512, 64] -> [384, 64, 512] (a transposing copy)."""
+    g = Graph()
+    x = g.input(shape(384, 512, 64))
+    g.output(g.view(g.permute(x, [0, 2, 1]), shape(384 * 64 * 512)))
+    return g, 0, [rng.standard_normal((384, 512, 64)).astype(np.float32)]
+
+
 CASES = {
     "gelu": case_gelu,
     "residual_add": case_residual_add,
@@ -159,6 +178,10 @@ CASES = {
     "attention_scores": case_attention_scores,
     "conv_trunk": case_conv_trunk,
     "conv_unet": case_conv_unet,
+    "conv_unet_down": _conv_case(8, 320, 64, 64, 320, 3, 2, 1, "UNet downsampling convolution: 3x3 stride 2, 320 -> 320, batch 8, 64x64 (Im2col + matmul)"),
+    "conv_unet_mid": _conv_case(2, 1280, 8, 8, 1280, 3, 1, 1, "UNet middle-block convolution: 3x3, 1280 -> 1280, batch 2, 8x8 (Im2col + split-K matmul)"),
+    "conv_unet_pointwise": _conv_case(8, 320, 64, 64, 320, 1, 1, 0, "UNet 1x1 projection: 320 -> 320, batch 8, 64x64 (Im2col as transpose + matmul)"),
+    "transpose": case_transpose,
 }
 
 
