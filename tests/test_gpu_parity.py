@@ -147,3 +147,19 @@ def test_softmax_with_scale_and_additive_term(rows, length, mask_kind):
     expected = cpu_eval_graph(g.to_bytes(), 0, ins)
     with CudaExecutor(0, g, 0) as ex:
         assert_tensors_match(expected, ex.evaluate(ins))
+
+
+@pytest.mark.parametrize("rows,length", [(5, 8196), (64, 20480), (3, 40960), (2, 49152), (2, 49156), (2, 81920)])
+def test_layernorm_over_long_rows(rows, length):
+    """Group-norm sized rows: 8193..49152 elements run on the one-block-per-row kernel with the row in
+    registers (with a second input scaled into the first), longer ones on the streaming kernel."""
+    from kyanite_b200.graph import Graph, shape
+    r = np.random.Generator(np.random.PCG64(21))
+    g = Graph()
+    a = g.input(shape(rows, length))
+    b = g.input(shape(rows, length))
+    g.output(g.layernorm(g.add(a, g.mul(b, g.scalar(0.5))), 1, 1e-5))
+    ins = [(r.standard_normal((rows, length)) * 3 + 1).astype(np.float32), r.standard_normal((rows, length)).astype(np.float32)]
+    expected = cpu_eval_graph(g.to_bytes(), 0, ins)
+    with CudaExecutor(0, g, 0) as ex:
+        assert_tensors_match(expected, ex.evaluate(ins))
