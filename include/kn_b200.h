@@ -136,6 +136,13 @@ KN_API int kn_executor_io_info(const kn_executor* exec, int is_output, int index
  * the executor's own staging pointer (kn_executor_host_buffer) for an entry skips the extra host
  * copy for it.  Bool outputs are validated to be 0/1 (executor.rs:181-189). */
 KN_API int kn_executor_evaluate(kn_executor* exec, const void* const* inputs, void* const* outputs);
+/* `evaluate` in two halves, for hosts that keep several executors of one device busy at once (the
+ * reference's self-play and server loops run several executor threads per GPU; here one thread can do it):
+ * `begin` stages the inputs and enqueues upload, steps and download on the executor's stream without waiting,
+ * `end` waits, checks the status word and hands out the outputs.  While executor A computes, executor B's
+ * upload and A's previous download use the copy engines.  One evaluation per executor may be in flight. */
+KN_API int kn_executor_evaluate_begin(kn_executor* exec, const void* const* inputs);
+KN_API int kn_executor_evaluate_end(kn_executor* exec, void* const* outputs);
 
 /* `CudaExecutor::run_async` (kn-cuda-eval/src/executor.rs:199-258): enqueues the steps on the
  * executor's stream without touching host memory; inputs are whatever the device input buffers hold. */

@@ -49,6 +49,8 @@ SIGNATURES = {
     "kn_executor_io_count": (c_int, [c_void_p, POINTER(c_int), POINTER(c_int)]),
     "kn_executor_io_info": (c_int, [c_void_p, c_int, c_int, POINTER(KnTensorInfo)]),
     "kn_executor_evaluate": (c_int, [c_void_p, POINTER(c_void_p), POINTER(c_void_p)]),
+    "kn_executor_evaluate_begin": (c_int, [c_void_p, POINTER(c_void_p)]),
+    "kn_executor_evaluate_end": (c_int, [c_void_p, POINTER(c_void_p)]),
     "kn_executor_run_async": (c_int, [c_void_p]),
     "kn_executor_synchronize": (c_int, [c_void_p]),
     "kn_executor_stream": (c_int, [c_void_p, POINTER(c_void_p)]),

@@ -294,6 +294,14 @@ struct Executor {
     }
 
     void evaluate(const void* const* inputs, void* const* outputs) {
+        evaluate_begin(inputs);
+        evaluate_end(outputs);
+    }
+
+    bool in_flight = false;   // evaluate_begin without its evaluate_end
+
+    void evaluate_begin(const void* const* inputs) {
+        KN_CHECK(!in_flight, KN_ERR_INVALID_ARG, "evaluate_begin while an evaluation is in flight");
         KN_CUDA(cudaStreamSynchronize(stream));
         for (size_t i = 0; i < pinned_in.size(); i++) {
             KN_CHECK(inputs != nullptr && (inputs[i] != nullptr || bytes_in[i] == 0), KN_ERR_INVALID_ARG, "null input buffer");
@@ -307,6 +315,12 @@ struct Executor {
             run_async();
             download_outputs();
         }
+        in_flight = true;
+    }
+
+    void evaluate_end(void* const* outputs) {
+        KN_CHECK(in_flight, KN_ERR_INVALID_ARG, "evaluate_end without evaluate_begin");
+        in_flight = false;
         KN_CUDA(cudaStreamSynchronize(stream));
         check_status();
         for (size_t i = 0; i < pinned_out.size(); i++) {
@@ -531,6 +545,22 @@ int kn_executor_evaluate(kn_executor* exec, const void* const* inputs, void* con
         KN_CHECK(exec != nullptr, KN_ERR_INVALID_ARG, "null executor");
         kn::DeviceGuard guard(exec->e->device);
         exec->e->evaluate(inputs, outputs);
+    });
+}
+
+int kn_executor_evaluate_begin(kn_executor* exec, const void* const* inputs) {
+    return guarded([&] {
+        KN_CHECK(exec != nullptr, KN_ERR_INVALID_ARG, "null executor");
+        kn::DeviceGuard guard(exec->e->device);
+        exec->e->evaluate_begin(inputs);
+    });
+}
+
+int kn_executor_evaluate_end(kn_executor* exec, void* const* outputs) {
+    return guarded([&] {
+        KN_CHECK(exec != nullptr, KN_ERR_INVALID_ARG, "null executor");
+        kn::DeviceGuard guard(exec->e->device);
+        exec->e->evaluate_end(outputs);
     });
 }
 

@@ -210,6 +210,20 @@ class CudaExecutor:
         check(self._lib.kn_executor_evaluate(self._ptr, in_ptrs, out_ptrs))
         return self.host_outputs
 
+    def evaluate_staged_begin(self):
+        """First half of `evaluate_staged`: enqueue upload, steps and download, do not wait.  With two
+        executors on one device, `b.evaluate_staged_begin(); a.evaluate_staged_end()` keeps the GPU and both
+        copy engines busy (kn_executor_evaluate_begin / _end)."""
+        in_ptrs = (c_void_p * max(1, len(self.host_inputs)))(
+            *[a.ctypes.data if a.size else None for a in self.host_inputs])
+        check(self._lib.kn_executor_evaluate_begin(self._ptr, in_ptrs))
+
+    def evaluate_staged_end(self) -> List[np.ndarray]:
+        out_ptrs = (c_void_p * max(1, len(self.host_outputs)))(
+            *[a.ctypes.data if a.size else None for a in self.host_outputs])
+        check(self._lib.kn_executor_evaluate_end(self._ptr, out_ptrs))
+        return self.host_outputs
+
     def upload_inputs(self):
         check(self._lib.kn_executor_upload_inputs(self._ptr))
 

@@ -163,3 +163,30 @@ def test_layernorm_over_long_rows(rows, length):
     expected = cpu_eval_graph(g.to_bytes(), 0, ins)
     with CudaExecutor(0, g, 0) as ex:
         assert_tensors_match(expected, ex.evaluate(ins))
+
+
+def test_evaluate_in_two_halves_with_two_executors():
+    """kn_executor_evaluate_begin / _end: two executors of one graph on one device, the next batch submitted
+    before the current one is waited for; results equal those of plain `evaluate`, and the call order is
+    checked (begin twice, end without begin)."""
+    from kyanite_b200._lib import KnError
+    case = next(c for c in CASES if c.name == "fuse_res")
+    expected = cpu_eval_graph(case.graph.to_bytes(), case.batch_size, case.inputs)
+    with CudaExecutor(0, case.graph, case.batch_size, math_mode=MATH_F32) as a, \
+            CudaExecutor(0, case.graph, case.batch_size, math_mode=MATH_F32) as b:
+        pair = [a, b]
+        for ex in pair:
+            for dst, src in zip(ex.host_inputs, case.inputs):
+                dst[...] = src
+        pair[0].evaluate_staged_begin()
+        for i in range(6):
+            if i + 1 < 6:
+                pair[(i + 1) % 2].evaluate_staged_begin()
+            outs = [o.copy() for o in pair[i % 2].evaluate_staged_end()]
+            assert_tensors_match(expected, outs)
+        with pytest.raises(KnError, match="without evaluate_begin"):
+            a.evaluate_staged_end()
+        a.evaluate_staged_begin()
+        with pytest.raises(KnError, match="in flight"):
+            a.evaluate_staged_begin()
+        assert_tensors_match(expected, [o.copy() for o in a.evaluate_staged_end()])
