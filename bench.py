@@ -213,6 +213,8 @@ def main():
     ap.add_argument("--math", default="tf32", choices=["tf32", "f32"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-chain", action="store_true", help="one launch per convolution instead of the merged chain kernel (A/B)")
+    ap.add_argument("--e2e-executors", type=int, default=2, help="executors per GPU in the end-to-end measurement")
+    ap.add_argument("--e2e-dense", type=int, default=0, help="1: the end-to-end executors use KN_FLAG_DENSE_CONV_CHAIN")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -228,7 +230,7 @@ def main():
     import torch.distributed as dist
 
     from kyanite_b200.configs import resnet_tower, resnet_tower_flops
-    from kyanite_b200.executor import FLAG_NO_CONV_CHAIN, MATH_F32, MATH_TF32, CudaExecutor
+    from kyanite_b200.executor import FLAG_DENSE_CONV_CHAIN, FLAG_NO_CONV_CHAIN, MATH_F32, MATH_TF32, CudaExecutor
 
     torch.cuda.set_device(local_rank)
     if world > 1:
@@ -296,28 +298,36 @@ def main():
     # upload and the previous download run on the copy engines while the GPU computes.  Every batch is
     # still uploaded from and downloaded to pinned host memory inside the timed region, and every result
     # is complete in host memory when its evaluate_staged_end returns.
-    ex2 = CudaExecutor(local_rank, graph, BATCH, math_mode=math_mode, flags=FLAG_NO_CONV_CHAIN if args.no_chain else 0)
-    for dst, src in zip(ex2.host_inputs, make_inputs(BATCH, 1001 + rank)):
-        dst[...] = src
-    pair = [ex, ex2]
-    streams = [stream, torch.cuda.ExternalStream(ex2.stream(), device=torch.device("cuda", local_rank))]
-    for _ in range(max(2, args.warmup)):
-        ex2.evaluate_staged()
+    e2e_flags = FLAG_NO_CONV_CHAIN if args.no_chain else (FLAG_DENSE_CONV_CHAIN if args.e2e_dense else 0)
+    pair = []
+    for k in range(args.e2e_executors):
+        e = CudaExecutor(local_rank, graph, BATCH, math_mode=math_mode, flags=e2e_flags)
+        for dst, src in zip(e.host_inputs, make_inputs(BATCH, 1001 + 17 * k + rank)):
+            dst[...] = src
+        pair.append(e)
+    streams = [torch.cuda.ExternalStream(e.stream(), device=torch.device("cuda", local_rank)) for e in pair]
+    for e in pair:
+        for _ in range(max(2, args.warmup)):
+            e.evaluate_staged()
     barrier()
     e2e_start = torch.cuda.Event(enable_timing=True)
     e2e_end = torch.cuda.Event(enable_timing=True)
+    n_ex = len(pair)
+    e2e_launches = pair[0].step_count()[1]
     e2e_start.record(streams[0])
-    pair[0].evaluate_staged_begin()
+    for k in range(min(n_ex - 1, args.steps)):
+        pair[k].evaluate_staged_begin()
     for i in range(args.steps):
-        if i + 1 < args.steps:
-            pair[(i + 1) % 2].evaluate_staged_begin()
-        pair[i % 2].evaluate_staged_end()
-        launches += launches_per_run
-    e2e_end.record(streams[(args.steps - 1) % 2])
+        if i + n_ex - 1 < args.steps:
+            pair[(i + n_ex - 1) % n_ex].evaluate_staged_begin()
+        pair[i % n_ex].evaluate_staged_end()
+        launches += e2e_launches
+    e2e_end.record(streams[(args.steps - 1) % n_ex])
     barrier()
     e2e_ms = e2e_start.elapsed_time(e2e_end)
     clocks = sampler.stop()
-    ex2.close()
+    for e in pair:
+        e.close()
 
     # ---- dominant kernel: the contraction step with the most FLOP (the convolution chain that runs the
     # whole residual tower in one launch; with chains switched off, the trunk convolutions, which are
@@ -368,7 +378,8 @@ def main():
                        "gflop_per_step": resnet_tower_flops(BATCH) / 1e9, "steps_per_run": steps_per_run},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms / args.steps,
-                    "mode": "two executors per GPU, the next batch submitted before the current one is waited for "
+                    "executors_per_gpu": args.e2e_executors, "dense_conv_chain": bool(args.e2e_dense),
+                    "mode": "several executors per GPU, the next batches submitted before the current one is waited for "
                             "(kn_executor_evaluate_begin / _end); every batch is uploaded from and downloaded to "
                             "pinned host memory inside the timed region",
                     "one_executor_serial": {"value": total / (serial_ms / 1000.0), "ms_per_step": serial_ms / args.steps}},

@@ -67,6 +67,11 @@ typedef struct kn_options {
 #define KN_FLAG_NO_CONV_CHAIN 1
 /* matrix multiplies use the one-tile-per-CTA kernel instead of the persistent one (A/B comparison and tests) */
 #define KN_FLAG_NO_PERSISTENT_GEMM 2
+/* convolution chains pack as many images per CTA as shared and tensor memory allow: less SM time per image
+   (the filter stream is shared by more pixels), fewer CTAs and a longer single launch.  For hosts that keep
+   several executors in flight on one device (kn_executor_evaluate_begin / _end); the default arrangement
+   minimises the duration of one launch. */
+#define KN_FLAG_DENSE_CONV_CHAIN 4
 
 #define KN_MAX_RANK 8
 

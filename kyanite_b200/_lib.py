@@ -19,6 +19,7 @@ KN_MATH_TF32 = 0
 KN_MATH_F32 = 1
 KN_FLAG_NO_CONV_CHAIN = 1
 KN_FLAG_NO_PERSISTENT_GEMM = 2
+KN_FLAG_DENSE_CONV_CHAIN = 4
 
 
 class KnOptions(Structure):

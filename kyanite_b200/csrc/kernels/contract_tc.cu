@@ -843,7 +843,7 @@ bool tc_conv_tile(int oh, int ow, int* wb, int* hb, int* nb) {
 void tc_prepare_step(Step& step, uint32_t* status_word, int flags) {
     auto launch = std::make_shared<TcLaunch>();
     if (step.kind == StepKind::ConvChain) {
-        launch->chain = chain_prepare(step.chain, status_word);
+        launch->chain = chain_prepare(step.chain, status_word, (flags & KN_FLAG_DENSE_CONV_CHAIN) != 0);
         step.tc = launch;
         return;
     }

@@ -24,12 +24,14 @@ from ._lib import KnError, KnMemUsage, KnOptions, KnTensorInfo, check
 from .graph import DType, Graph
 
 __all__ = ["CudaDevice", "CudaDeviceNotAvailable", "CudaExecutor", "Device", "PreparedGraph", "MemoryUsage",
-           "plan_describe", "KnError", "MATH_TF32", "MATH_F32", "FLAG_NO_CONV_CHAIN", "FLAG_NO_PERSISTENT_GEMM"]
+           "plan_describe", "KnError", "MATH_TF32", "MATH_F32", "FLAG_NO_CONV_CHAIN", "FLAG_NO_PERSISTENT_GEMM",
+           "FLAG_DENSE_CONV_CHAIN"]
 
 MATH_TF32 = _lib.KN_MATH_TF32
 MATH_F32 = _lib.KN_MATH_F32
 FLAG_NO_CONV_CHAIN = _lib.KN_FLAG_NO_CONV_CHAIN
 FLAG_NO_PERSISTENT_GEMM = _lib.KN_FLAG_NO_PERSISTENT_GEMM
+FLAG_DENSE_CONV_CHAIN = _lib.KN_FLAG_DENSE_CONV_CHAIN
 
 
 class CudaDeviceNotAvailable(RuntimeError):
