@@ -181,22 +181,30 @@ __global__ void __launch_bounds__(256) im2col_kernel(const __grid_constant__ Im2
         for (int j = 0; j < kIm2colC / 8; j++) tile[ty + 8 * j][tx] = v[j];
         __syncthreads();
     }
+    // store: lanes along the channels; jp picks the position (ty + 8 * jp), jc the 32-channel group
 #pragma unroll
-    for (int j = 0; j < kIm2colC / 8; j++) {
-        // store: lanes along the channels; (j & 3) picks the 32-channel group, ty + 8 * (j >> 2) the position
-        const int cl = 32 * (j & 3) + tx, pl = ty + 8 * (j >> 2);
-        const int pos = p0 + pl, c = c0 + cl;
-        if (pos >= positions || c >= p.c_pad) continue;
-        float v;
+    for (int jp = 0; jp < 4; jp++) {
+        const int pl = ty + 8 * jp, pos = p0 + pl;
+        if (pos >= positions) continue;
+        const float* src = nullptr;   // channels-last source: this position's pixel, or null outside the image
         if (channels_last) {
             const int oy = pos / p.ow, ox = pos - oy * p.ow;
             const int iy = oy * p.stride_y + r - p.pad_y, ix = ox * p.stride_x + q - p.pad_x;
-            const bool inside = iy >= 0 && iy < p.h && ix >= 0 && ix < p.w && c < p.c;
-            v = inside ? __ldg(in + (int64_t)c * p.s_in[1] + (int64_t)iy * p.s_in[2] + (int64_t)ix * p.s_in[3]) : 0.f;
-        } else {
-            v = tile[cl][pl];
+            if (iy >= 0 && iy < p.h && ix >= 0 && ix < p.w) src = in + (int64_t)iy * p.s_in[2] + (int64_t)ix * p.s_in[3];
         }
-        col[(int64_t)pos * (p.r * p.s) * p.c_pad + c] = v;
+        float* dst = col + (int64_t)pos * (p.r * p.s) * p.c_pad;
+        float v[kIm2colC / 32];
+#pragma unroll
+        for (int jc = 0; jc < kIm2colC / 32; jc++) {
+            const int cl = 32 * jc + tx, c = c0 + cl;
+            if (channels_last) v[jc] = (src != nullptr && c < p.c) ? __ldg(src + (int64_t)c * p.s_in[1]) : 0.f;
+            else v[jc] = tile[cl][pl];
+        }
+#pragma unroll
+        for (int jc = 0; jc < kIm2colC / 32; jc++) {
+            const int c = c0 + 32 * jc + tx;
+            if (c < p.c_pad) dst[c] = v[jc];
+        }
     }
 }
 

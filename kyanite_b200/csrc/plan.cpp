@@ -967,7 +967,11 @@ class Planner {
         // a 1x1 convolution IS a matmul over the channels; the generic convolution kernel stores its result
         // one row per thread, which the matmul kernels' staged epilogues do not
         const bool pointwise = R == 1 && S == 1;
-        if (!strided && !few_positions && !pointwise) return std::nullopt;
+        // a long reduction over many channels: the convolution kernels' 128-channel tiles and row-per-thread
+        // epilogue reach about 0.2 of the tensor peak there, im2col + the persistent matmul about 0.5, which
+        // pays for writing the R*S times larger matrix as long as that stays a few hundred MB
+        const bool long_k = C * R * S >= 2048 && N * OH * OW * R * S * C * 4 <= (256ll << 20);
+        if (!strided && !few_positions && !pointwise && !long_k) return std::nullopt;
         if (N < 1 || N > 65535 || OH * OW < 64 || K < 16 || K % 4 != 0 || C < 1 || R * S > 64) return std::nullopt;
         if (2.0 * (double)N * OH * OW * K * C * R * S < 2e8) return std::nullopt;
         const ValueInfo& wi = g_.values[ci.inputs[1]];
