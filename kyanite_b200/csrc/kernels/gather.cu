@@ -91,7 +91,7 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const __grid_constant_
 #pragma unroll
             for (int j = 0; j < 4; j++) {
                 const int e = e0 + 32 * j;
-                if (e < row_vec4) dst[e] = r[j];
+                if (e < row_vec4) __stcs(dst + e, r[j]);   // streaming store: the table, not the output, should stay in L2
             }
         }
         if (next >= rows) break;

@@ -465,8 +465,13 @@ static bool softmax_vec4_ok(const RowParams& p) {
     const int64_t len = p.len;                                                                                 \
     if (OK(p)) {                                                                                               \
         const int len4 = (int)(len / 4);                                                                       \
-        if (len4 <= 512) {                                                                                     \
-            /* one warp per row, the row in registers (up to 16 float4 per lane) */                            \
+        if (len4 > 256 && len4 <= 512) {                                                                       \
+            /* four warps per row (a block of 128 threads), three or four float4 per thread */                  \
+            const unsigned grid = (unsigned)p.rows;                                                            \
+            if (len4 <= 384) launch_pdl(VEC4<128, 3>, dim3(grid), dim3(128), (size_t)(0), stream, p);           \
+            else launch_pdl(VEC4<128, 4>, dim3(grid), dim3(128), (size_t)(0), stream, p);                       \
+        } else if (len4 <= 512) {                                                                              \
+            /* one warp per row, the row in registers (up to 8 float4 per lane) */                             \
             const unsigned grid = (unsigned)((p.rows + 7) / 8);                                                \
             const int items = (len4 + 31) / 32;                                                                \
             switch (items <= 8 ? items : (items + 1) / 2 * 2) {                                                \
