@@ -171,12 +171,29 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const __grid_constant_
     float acc[kSkinnyMaxN];
 #pragma unroll
     for (int n = 0; n < kSkinnyMaxN; n++) acc[n] = 0.f;
-#pragma unroll 4
-    for (int64_t k = lane; k < p.k; k += 32) {
-        const float x = a[k * p.sa[2]];
+    const bool wide = p.sa[2] == 1 && p.sb[1] == 1 && (p.k & 3) == 0 && (((uintptr_t)a | (uintptr_t)w) & 15) == 0 && (p.sb[2] & 3) == 0;
+    if (wide) {
+        // both operands contiguous along K: 128-bit loads, two per lane in flight for each operand row
+        const int64_t k4 = p.k >> 2;
+        const float4* a4 = (const float4*)a;
+#pragma unroll 2
+        for (int64_t k = lane; k < k4; k += 32) {
+            const float4 x = __ldg(a4 + k);
 #pragma unroll
-        for (int n = 0; n < kSkinnyMaxN; n++)
-            if (n < p.n) acc[n] = fmaf(x, w[k * p.sb[1] + n * p.sb[2]], acc[n]);
+            for (int n = 0; n < kSkinnyMaxN; n++)
+                if (n < p.n) {
+                    const float4 y = __ldg((const float4*)(w + n * p.sb[2]) + k);
+                    acc[n] = fmaf(x.x, y.x, fmaf(x.y, y.y, fmaf(x.z, y.z, fmaf(x.w, y.w, acc[n]))));
+                }
+        }
+    } else {
+#pragma unroll 4
+        for (int64_t k = lane; k < p.k; k += 32) {
+            const float x = a[k * p.sa[2]];
+#pragma unroll
+            for (int n = 0; n < kSkinnyMaxN; n++)
+                if (n < p.n) acc[n] = fmaf(x, w[k * p.sb[1] + n * p.sb[2]], acc[n]);
+        }
     }
 #pragma unroll
     for (int n = 0; n < kSkinnyMaxN; n++)
