@@ -942,6 +942,22 @@ class Planner {
         const int64_t k_pad = (b.ss.shape[1] + 3) / 4 * 4;
         PlanTensor dense = alloc_shared({b.ss.shape[0], b.ss.shape[2], k_pad}, DType::F32, value);
         PlanTensor dst = dense.with(dense.ss.permute({0, 2, 1})).slice(1, 0, b.ss.shape[1], 1);
+        // `b` itself is often the product of a copy (the head split [B, s, h, d] -> [B*h, s, d] cannot be a view)
+        // that nothing else reads: copy from that copy's source straight into the K-contiguous buffer
+        if (!plan_.steps.empty() && g_.is_hidden_with_uses(value, 1)) {
+            const Step& last = plan_.steps.back();
+            if (last.kind == StepKind::Scalar && last.desc.rfind("copy", 0) == 0 && last.value == value && last.operands.size() == 2 &&
+                last.writes[1] && !last.writes[0] && last.operands[1].buf == b.buf && last.operands[1].offset == 0 && b.offset == 0 &&
+                last.operands[1].ss.has_simple_strides() && b.ss.has_simple_strides() && last.operands[1].ss.size() == b.ss.size() &&
+                last.operands[0].dtype == DType::F32) {
+                if (auto v = dst.ss.view(last.operands[1].ss.shape)) {
+                    const PlanTensor src = last.operands[0];
+                    plan_.steps.pop_back();
+                    emit_copy(src, dst.with(*v), value);
+                    return dst;
+                }
+            }
+        }
         emit_copy(b, dst, value);
         return dst;
     }

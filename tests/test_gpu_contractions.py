@@ -251,3 +251,19 @@ def test_pointwise_conv_as_matmul(n, c, h, w, k, chained):
     steps = [l.split()[2] for l in d.splitlines() if l.startswith("step")]
     assert steps.count("Gemm/tc") == (2 if chained else 1) and steps.count("Im2col") == 1 and "Conv" not in " ".join(steps), d
     check(g, 0, [rng(3, n, c, h, w)])
+
+
+def test_head_split_and_k_major_copy_are_one_step():
+    """values [B, s, h*d] -> heads [B*h, s, d] needs a copy (the head axis moves in front of the sequence axis),
+    and as the B operand of probabilities x values a K-contiguous layout: the planner writes that layout
+    straight from the projection's output, one transposing copy instead of two passes."""
+    B, s, h, d = 4, 256, 6, 64
+    g = Graph()
+    probs = g.input(shape(B * h, s, s))
+    x = g.input(shape(B, s, h * d))
+    v = g.view(g.permute(g.view(x, shape(B, s, h, d)), [0, 2, 1, 3]), shape(B * h, s, d))
+    g.output(g.batched_mat_mul(probs, v))
+    text = plan_describe(g.to_bytes(), 0, math_mode=MATH_TF32)
+    kinds = [l.split()[2] for l in text.splitlines() if l.startswith("step")]
+    assert kinds == ["Scalar", "Gemm/tc"], text
+    check(g, 0, [rng(1, B * h, s, s) * 0.1, rng(2, B, s, h * d)])
