@@ -207,6 +207,117 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def tower_parity(ex, make_inputs, math):
+    """Max abs / rel difference between the executor and the CPU oracle on the bench workload itself (all 256
+    boards of one batch), per output, with the tolerance the tests assert."""
+    from kyanite_b200.configs import resnet_tower
+    from oracle.cpu_eval import assert_tensors_match, cpu_eval_graph
+    graph, _ = resnet_tower()
+    inputs = make_inputs(BATCH, 4242)
+    got = [np.array(a) for a in ex.evaluate(inputs)]
+    expected = cpu_eval_graph(graph.to_bytes(), BATCH, inputs)
+    tol = 4e-3 if math == "tf32" else 1e-3
+    out = {"config": "resnet_tower_f32_b256, all 256 boards of one batch against the CPU oracle",
+           "rule": f"a value mismatches iff abs >= {tol} * max|expected| of its tensor AND rel >= {tol}", "tol": tol}
+    names = ["policy", "value"]
+    worst_abs = worst_rel = 0.0
+    for name, e, g in zip(names, expected, got):
+        max_abs, max_rel = assert_tensors_match([e], [g], tol, tol, abs_scaled=True)
+        out[name] = {"max_abs": max_abs, "max_rel": max_rel, "scale": float(np.abs(e).max())}
+        worst_abs, worst_rel = max(worst_abs, max_abs), max(worst_rel, max_rel)
+    out["max_abs"], out["max_rel"] = worst_abs, worst_rel
+    return out
+
+
+def library_proxy(make_inputs, seconds=1.0):
+    """The same tower through the vendor libraries, as information only: cuDNN's fused convolution + bias
+    (+ residual) + ReLU in TF32, channels-last, the whole forward pass captured in a CUDA graph and replayed
+    at batch 256.  That is what the reference's cudnnConvolutionBiasActivationForward
+    (kn-cuda-sys/src/wrapper/operation.rs:219-239) and cublasSgemm calls would do on this GPU; torch stands
+    in for the Rust bindings.  Random weights of the same shapes; inputs rotate through a pool larger
+    than L2."""
+    import torch
+    import torch.nn.functional as F
+    torch.backends.cudnn.allow_tf32 = True
+    torch.backends.cuda.matmul.allow_tf32 = False     # the reference's cublasSgemm is exact f32
+    dev = torch.device("cuda")
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(7)
+    cl = torch.channels_last
+
+    def w(co, ci, k):
+        return (torch.randn((co, ci, k, k), device=dev, generator=gen) * (2.0 / (ci * k * k)) ** 0.5).contiguous(memory_format=cl)
+
+    def b(c):
+        return 0.1 * torch.randn((c,), device=dev, generator=gen)
+
+    stem = (w(128, 21, 3), b(128))
+    blocks = [((w(128, 128, 3), b(128)), (w(128, 128, 3) * (1 / 32 ** 0.5), b(128))) for _ in range(16)]
+    pol, val = (w(73, 128, 1), b(73)), (w(32, 128, 1), b(32))
+    w1, b1 = torch.randn((256, 2048), device=dev, generator=gen) * (2 / 2048) ** 0.5, b(256)
+    w2, b2 = torch.randn((3, 256), device=dev, generator=gen) * (2 / 256) ** 0.5, b(3)
+    fused = hasattr(torch, "cudnn_convolution_relu") and hasattr(torch, "cudnn_convolution_add_relu")
+
+    def conv_relu(x, wb, pad):
+        if fused:
+            return torch.cudnn_convolution_relu(x, wb[0], wb[1], (1, 1), (pad, pad), (1, 1), 1)
+        return F.relu(F.conv2d(x, wb[0], wb[1], padding=pad))
+
+    def conv_add_relu(x, wb, z):
+        if fused:
+            return torch.cudnn_convolution_add_relu(x, wb[0], z, 1.0, wb[1], (1, 1), (1, 1), (1, 1), 1)
+        return F.relu(F.conv2d(x, wb[0], wb[1], padding=1) + z)
+
+    def trunk(x):
+        cur = conv_relu(x, stem, 1)
+        for c1, c2 in blocks:
+            cur = conv_add_relu(conv_relu(cur, c1, 1), c2, cur)
+        return cur
+
+    def forward(x):
+        cur = trunk(x)
+        p = torch.softmax(F.conv2d(cur, pol[0], pol[1]).flatten(1), 1)
+        v = F.conv2d(cur, val[0], val[1]).flatten(1)
+        v = torch.softmax(F.linear(F.relu(F.linear(v, w1, b1)), w2, b2), 1)
+        return p, v
+
+    pool_sets = 128
+    pool = (torch.rand((pool_sets, BATCH, 21, 8, 8), device=dev, generator=gen) < 0.1).float()
+    x = pool[0].clone().contiguous(memory_format=cl)
+    result = {"what": "torch " + torch.__version__ + ": cuDNN " + str(torch.backends.cudnn.version()) +
+                      (" fused conv+bias(+residual)+relu" if fused else " conv2d + relu") +
+                      ", TF32, channels-last, CUDA graph, batch 256, f32 linears"}
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side), torch.no_grad():
+        for _ in range(3):
+            forward(x)
+        side.synchronize()
+        g_full, g_trunk = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g_full, stream=side):
+            forward(x)
+        with torch.cuda.graph(g_trunk, stream=side):
+            trunk(x)
+        for name, graph in (("whole_step", g_full), ("trunk_33_convs", g_trunk)):
+            for i in range(5):
+                x.copy_(pool[i % pool_sets])
+                graph.replay()
+            side.synchronize()
+            t0 = time.perf_counter()
+            n, ms_total = 0, 0.0
+            while time.perf_counter() - t0 < seconds:
+                a, c = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(side)
+                for i in range(50):
+                    x.copy_(pool[(n + i) % pool_sets])
+                    graph.replay()
+                c.record(side)
+                c.synchronize()
+                ms_total += a.elapsed_time(c)
+                n += 50
+            result[name] = {"ms_per_step": ms_total / n, "inferences_per_s": BATCH * n / (ms_total / 1000.0)}
+    return result
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -215,9 +326,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--math", default="tf32", choices=["tf32", "f32"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-library-proxy", action="store_true")
     ap.add_argument("--no-chain", action="store_true", help="one launch per convolution instead of the merged chain kernel (A/B)")
-    ap.add_argument("--e2e-executors", type=int, default=2, help="executors per GPU in the end-to-end measurement")
-    ap.add_argument("--e2e-dense", type=int, default=0, help="1: the end-to-end executors use KN_FLAG_DENSE_CONV_CHAIN")
+    ap.add_argument("--e2e-executors", type=int, default=2, help="executors per GPU in the pipelined measurements")
+    ap.add_argument("--min-seconds", type=float, default=1.5,
+                    help="each pipelined leg repeats its window of --steps steps until this much time is covered")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -233,7 +346,7 @@ def main():
     import torch.distributed as dist
 
     from kyanite_b200.configs import resnet_tower, resnet_tower_flops
-    from kyanite_b200.executor import FLAG_DENSE_CONV_CHAIN, FLAG_NO_CONV_CHAIN, MATH_F32, MATH_TF32, CudaExecutor
+    from kyanite_b200.executor import FLAG_NO_CONV_CHAIN, MATH_F32, MATH_TF32, CudaExecutor
 
     torch.cuda.set_device(local_rank)
     if world > 1:
@@ -242,11 +355,13 @@ def main():
 
     graph, make_inputs = resnet_tower()
     math_mode = MATH_TF32 if args.math == "tf32" else MATH_F32
-    ex = CudaExecutor(local_rank, graph, BATCH, math_mode=math_mode, flags=FLAG_NO_CONV_CHAIN if args.no_chain else 0)
+    flags = FLAG_NO_CONV_CHAIN if args.no_chain else 0
+    ex = CudaExecutor(local_rank, graph, BATCH, math_mode=math_mode, flags=flags)
     inputs = make_inputs(BATCH, 1 + rank)
     for dst, src in zip(ex.host_inputs, inputs):
         dst[...] = src
     steps_per_run, launches_per_run = ex.step_count()
+    K = args.steps
 
     stream = torch.cuda.ExternalStream(ex.stream(), device=torch.device("cuda", local_rank))
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")   # 2x the 126 MB L2
@@ -256,23 +371,27 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    sampler = ClockSampler(local_rank, "GPU-" + str(torch.cuda.get_device_properties(local_rank).uuid))
-    sampler.start()
+    # clocks: one sampler (rank 0's GPU), every 50 ms, so that N ranks do not add N polling threads to the host
+    sampler = None
+    if rank == 0:
+        sampler = ClockSampler(local_rank, "GPU-" + str(torch.cuda.get_device_properties(local_rank).uuid))
+        sampler.start()
 
     # ---- warm-up (also captures the CUDA graph)
     for _ in range(args.warmup):
         ex.evaluate_staged()
     ex.synchronize()
 
-    launches = 0
+    launches = args.warmup * launches_per_run
 
-    # ---- device-resident: K timed iterations of run_async, L2 flushed in between
+    # ---- one executor, one step after the other, L2 flushed before every timed step (`config.one_executor_flushed`)
     barrier()
-    sampler.mark_start()
-    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-    ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    if sampler:
+        sampler.mark_start()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(K)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(K)]
     with torch.cuda.stream(stream):
-        for i in range(args.steps):
+        for i in range(K):
             flush.zero_()
             starts[i].record(stream)
             ex.run_async()
@@ -281,59 +400,99 @@ def main():
     barrier()
     dev_ms = sum(s.elapsed_time(e) for s, e in zip(starts, ends))
 
-    # ---- end to end through evaluate(): pinned H2D + steps + D2H, host buffers
+    # ---- `e2e.one_executor_serial`: plain evaluate() calls in series with caller-owned input arrays
     h2d = sum(a.nbytes for a in ex.host_inputs)
     d2h = sum(a.nbytes for a in ex.host_outputs)
-    # (a) one executor, one call after the other: upload, steps and download of a batch in series
+    host_sets = 16            # caller-owned (pageable) input arrays the calls rotate through
+    host_pool = [[np.ascontiguousarray(a) for a in make_inputs(BATCH, 5000 + 31 * j + rank)] for j in range(host_sets)]
     barrier()
     e2e_start = torch.cuda.Event(enable_timing=True)
     e2e_end = torch.cuda.Event(enable_timing=True)
-    with torch.cuda.stream(stream):
-        e2e_start.record(stream)
-        for i in range(args.steps):
-            ex.evaluate_staged()
-            launches += launches_per_run
-        e2e_end.record(stream)
+    e2e_start.record(stream)
+    for i in range(K):
+        ex.evaluate_begin(host_pool[i % host_sets])
+        ex.evaluate_end()
+        launches += launches_per_run
+    e2e_end.record(stream)
     barrier()
     serial_ms = e2e_start.elapsed_time(e2e_end)
-    # (b) two executors of the same graph on this GPU, the way the reference's hosts keep a GPU busy (several
-    # executor threads per device): the next batch is submitted before the current one is waited for, so its
-    # upload and the previous download run on the copy engines while the GPU computes.  Every batch is
-    # still uploaded from and downloaded to pinned host memory inside the timed region, and every result
-    # is complete in host memory when its evaluate_staged_end returns.
-    e2e_flags = FLAG_NO_CONV_CHAIN if args.no_chain else (FLAG_DENSE_CONV_CHAIN if args.e2e_dense else 0)
+
+    # ---- the pipelined legs: several executors of the same graph on this GPU, the way the reference's hosts keep
+    # a GPU busy (several executor threads per device).  Each leg first fills the pipeline with untimed steps,
+    # then times windows of K steps back to back WITHOUT draining in between (a CUDA event behind the last step
+    # of every window, on the stream that step runs on), until --min-seconds are covered; the median window is
+    # reported, with the spread.
     pair = []
     for k in range(args.e2e_executors):
-        e = CudaExecutor(local_rank, graph, BATCH, math_mode=math_mode, flags=e2e_flags)
+        e = CudaExecutor(local_rank, graph, BATCH, math_mode=math_mode, flags=flags)
         for dst, src in zip(e.host_inputs, make_inputs(BATCH, 1001 + 17 * k + rank)):
             dst[...] = src
         pair.append(e)
     streams = [torch.cuda.ExternalStream(e.stream(), device=torch.device("cuda", local_rank)) for e in pair]
+    n_ex = len(pair)
     for e in pair:
         for _ in range(max(2, args.warmup)):
             e.evaluate_staged()
-    barrier()
-    e2e_start = torch.cuda.Event(enable_timing=True)
-    e2e_end = torch.cuda.Event(enable_timing=True)
-    n_ex = len(pair)
-    e2e_launches = pair[0].step_count()[1]
-    e2e_start.record(streams[0])
-    for k in range(min(n_ex - 1, args.steps)):
-        pair[k].evaluate_staged_begin()
-    for i in range(args.steps):
-        if i + n_ex - 1 < args.steps:
-            pair[(i + n_ex - 1) % n_ex].evaluate_staged_begin()
-        pair[i % n_ex].evaluate_staged_end()
-        launches += e2e_launches
-    e2e_end.record(streams[(args.steps - 1) % n_ex])
-    barrier()
-    e2e_ms = e2e_start.elapsed_time(e2e_end)
+            launches += launches_per_run
 
-    # ---- device-resident throughput (`value`): the same executors, batches already in HBM.  No flush here:
-    # a pool of input sets larger than the 126 MB L2 rotates through the executors' input buffers (one
-    # device-to-device copy per step, inside the timed region), so no step finds its input in L2, while the
-    # 20 MB of weights stay there as they do in steady-state serving.  With two executors alternating, CTAs of
-    # the next batch fill the SMs the current one leaves idle (128 CTAs for 148 SMs).
+    def run_windows(submit, finish, est_ms_per_step):
+        """`submit(i)` enqueues step i on executor i % n_ex, `finish(i)` waits for it (or None).  Returns the list
+        of window durations in ms and the host time spent inside submit per step (us)."""
+        nonlocal launches
+        windows = max(3, int(np.ceil(args.min_seconds * 1000.0 / max(1e-3, est_ms_per_step * K))))
+        total = windows * K
+        lead = n_ex - 1 if finish else 0
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(windows + 1)]
+        fill = 2 * n_ex + lead                      # untimed steps that fill the pipeline
+        host_s = 0.0
+        for i in range(fill):
+            submit(i)
+        if finish:
+            for i in range(fill - lead):
+                finish(i)
+        marks[0].record(streams[(fill - 1) % n_ex])   # behind the newest submitted step
+        for j in range(total):
+            i = fill + j
+            t0 = time.perf_counter()
+            submit(i)
+            host_s += time.perf_counter() - t0
+            if (j + 1) % K == 0:
+                marks[(j + 1) // K].record(streams[i % n_ex])
+            if finish:
+                finish(i - lead)
+        if finish:
+            for i in range(fill + total - lead, fill + total):
+                finish(i)
+        launches += (fill + total) * launches_per_run
+        barrier()
+        return [a.elapsed_time(b) for a, b in zip(marks[:-1], marks[1:])], 1e6 * host_s / total
+
+    # (a) `e2e`: every batch copied from a caller-owned array to pinned staging, uploaded, computed and downloaded
+    # inside the timed region; the next batch is submitted before the current one is waited for.
+    barrier()
+    e2e_windows, e2e_host_us = run_windows(lambda i: pair[i % n_ex].evaluate_begin(host_pool[i % host_sets]),
+                                           lambda i: pair[i % n_ex].evaluate_end(), serial_ms / K / 1.5)
+
+    # (b) the copy-only ceiling of (a): the same host -> pinned, pinned -> device and device -> pinned bytes per
+    # step on the same streams, no kernels
+    def copy_submit(i):
+        e = pair[i % n_ex]
+        e.synchronize()
+        for dst, src in zip(e.host_inputs, host_pool[i % host_sets]):
+            np.copyto(dst, src)
+        e.upload_inputs()
+        e.download_outputs()
+
+    barrier()
+    saved = launches
+    copy_windows, _ = run_windows(copy_submit, None, statistics.median(e2e_windows) / K / 2)
+    launches = saved                                  # no kernel launches in that leg
+
+    # (c) `value`: batches already in HBM.  No flush here: a pool of input sets larger than the 126 MB L2
+    # rotates through the executors' input buffers (one device-to-device copy per step, inside the timed
+    # region), so no step finds its input in L2, while the 20 MB of weights stay there as they do in
+    # steady-state serving.  With two executors alternating, CTAs of the next batch fill the SMs the current
+    # one leaves idle (128 CTAs for 148 SMs).
     class _DevArray:
         def __init__(self, ptr, shape):
             self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": "<f4", "data": (ptr, False), "version": 3}
@@ -349,24 +508,17 @@ def main():
             ptr, _ = e.device_buffer(False, idx)
             dev_in[k].append(torch.as_tensor(_DevArray(ptr, arr.shape), device="cuda"))
     pool_bytes = sum(p.numel() * 4 for p in pools)
-    barrier()
-    pipe_start = torch.cuda.Event(enable_timing=True)
-    pipe_ends = [torch.cuda.Event(enable_timing=True) for _ in pair]
-    pipe_start.record(streams[0])
-    for st in streams[1:]:
-        st.wait_event(pipe_start)
-    for i in range(args.steps):
+
+    def value_submit(i):
         k = i % n_ex
         with torch.cuda.stream(streams[k]):
             for pool, dst in zip(pools, dev_in[k]):
                 dst.copy_(pool[i % pool_sets], non_blocking=True)
         pair[k].run_async()
-        launches += e2e_launches
-    for ev, st in zip(pipe_ends, streams):
-        ev.record(st)
+
     barrier()
-    pipe_ms = max(pipe_start.elapsed_time(ev) for ev in pipe_ends)
-    clocks = sampler.stop()
+    pipe_windows, pipe_host_us = run_windows(value_submit, None, statistics.median(e2e_windows) / K)
+    clocks = sampler.stop() if sampler else None
     for e in pair:
         e.close()
 
@@ -376,6 +528,7 @@ def main():
     # on the executor's stream.
     ex.set_profile(True)
     ex.run_async()
+    launches += launches_per_run
     contractions = []
     for line in ex.last_profile().splitlines():
         parts = line.split()
@@ -386,15 +539,22 @@ def main():
     if contractions:
         top = max(c[1] for c in contractions)
         dominant = [(ex.time_step(idx, 20), flop, kind, desc) for idx, flop, kind, desc in contractions if flop == top]
+        launches += 21 * len(dominant)
 
-    t = torch.tensor([dev_ms, e2e_ms, serial_ms, pipe_ms], dtype=torch.float64, device="cuda")
+    pipe_ms, e2e_ms, copy_ms = (statistics.median(w) for w in (pipe_windows, e2e_windows, copy_windows))
+    mine = torch.tensor([dev_ms, e2e_ms, serial_ms, pipe_ms, copy_ms, pipe_host_us, e2e_host_us], dtype=torch.float64,
+                        device="cuda")
     if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    dev_ms, e2e_ms, serial_ms, pipe_ms = t.tolist()
+        gathered = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(gathered, mine)
+        per_rank = torch.stack(gathered).cpu().numpy()
+    else:
+        per_rank = mine.cpu().numpy()[None]
+    dev_ms, e2e_ms, serial_ms, pipe_ms, copy_ms = (float(per_rank[:, c].max()) for c in range(5))   # MAX over ranks
 
     if rank == 0:
         peaks = load_peaks()
-        total = BATCH * world * args.steps
+        total = BATCH * world * K
         value = total / (pipe_ms / 1000.0)
         e2e_value = total / (e2e_ms / 1000.0)
         tensor_peak = peaks["bf16_tflops"] / 2.0   # TF32 dense = half the bf16 rate
@@ -409,35 +569,71 @@ def main():
                         "traffic": CHAIN_DRAM_BYTES if chain else TRUNK_CONV_DRAM_BYTES,
                         "peak_source": f"{peaks['source']} bf16 burst / 2 (tf32)", "us_per_launch": us,
                         "gflop_per_launch": flop / 1e9, "launches_per_step": len(dominant)}
+
+        def spread(windows):
+            return {"windows": len(windows), "min_ms_per_step": min(windows) / K, "median_ms_per_step": statistics.median(windows) / K,
+                    "max_ms_per_step": max(windows) / K}
+
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": pipe_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": args.warmup,
+            "ms_per_step": pipe_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "tf32 operands, f32 storage and accumulate" if args.math == "tf32" else "f32",
             "data": "synthetic",
             "config": {"workload": WORKLOAD, "batch_per_gpu": BATCH, "parallelism": f"batch-sharded x{world}, no collective",
                        "executors_per_gpu": args.e2e_executors,
+                       "timing": f"steady state: the pipeline is filled with untimed steps, then windows of {K} steps are "
+                                 "timed back to back with CUDA events (no drain in between) for at least "
+                                 f"{args.min_seconds} s; value and e2e are the MEDIAN window, max over ranks; "
+                                 "ms_per_step x steps = one window",
+                       "value_windows_rank0": spread(pipe_windows), "host_enqueue_us_per_step": float(per_rank[:, 5].max()),
+                       "per_rank_ms_per_step": [float(x) / K for x in per_rank[:, 3]],
                        "l2": f"no flush: {pool_sets} input sets ({pool_bytes / 1e6:.0f} MB, larger than the 126 MB L2) rotate "
                              "through the executors' input buffers, one device-to-device copy per step inside the timed "
                              "region; weights (20 MB) stay in L2",
-                       "one_executor_flushed": {"value": total / (dev_ms / 1000.0), "ms_per_step": dev_ms / args.steps,
+                       "one_executor_flushed": {"value": total / (dev_ms / 1000.0), "ms_per_step": dev_ms / K,
                                                 "l2": "one executor, steps one after the other, 256 MiB L2 flush "
                                                       "between timed iterations"},
                        "gflop_per_step": resnet_tower_flops(BATCH) / 1e9, "steps_per_run": steps_per_run},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": e2e_ms / args.steps,
-                    "executors_per_gpu": args.e2e_executors, "dense_conv_chain": bool(args.e2e_dense),
-                    "mode": "several executors per GPU, the next batches submitted before the current one is waited for "
-                            "(kn_executor_evaluate_begin / _end); every batch is uploaded from and downloaded to "
-                            "pinned host memory inside the timed region",
-                    "one_executor_serial": {"value": total / (serial_ms / 1000.0), "ms_per_step": serial_ms / args.steps}},
+                    "ms_per_step": e2e_ms / K, "executors_per_gpu": args.e2e_executors,
+                    "windows_rank0": spread(e2e_windows), "host_enqueue_us_per_step": float(per_rank[:, 6].max()),
+                    "per_rank_ms_per_step": [float(x) / K for x in per_rank[:, 1]],
+                    "mode": "kn_executor_evaluate_begin(inputs) / _end on several executors per GPU, the next batch "
+                            "submitted before the current one is waited for; inputs are caller-owned pageable arrays "
+                            f"({host_sets} sets in rotation): the library copies them to pinned staging, uploads, runs "
+                            "the steps and downloads every output to pinned host memory, all inside the timed region",
+                    "copy_only": {"value": total / (copy_ms / 1000.0), "ms_per_step": copy_ms / K,
+                                  "per_rank_ms_per_step": [float(x) / K for x in per_rank[:, 4]],
+                                  "what": "the same host->pinned, pinned->device and device->pinned bytes per step on "
+                                          "the same streams with no kernels: the ceiling the copies alone set at this "
+                                          "number of GPUs"},
+                    "one_executor_serial": {"value": total / (serial_ms / 1000.0), "ms_per_step": serial_ms / K}},
             "gpu_launches": launches,
             "clocks": clocks,
             "roofline": roofline,
         }
         if world == 1 and not args.no_cpu_baseline:
+            line["parity"] = tower_parity(ex, make_inputs, args.math)
+            launches += launches_per_run
+            line["gpu_launches"] = launches
             rate, dt = cpu_oracle_rate(BATCH, 4)
             line["cpu_baseline"] = {"value": rate, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port",
                                     "sample": f"4 x {BATCH} boards through the numpy oracle in {dt:.1f} s"}
+            try:
+                from threadpoolctl import threadpool_limits
+                with threadpool_limits(limits=1):
+                    rate1, dt1 = cpu_oracle_rate(32, 1)
+                line["cpu_baseline"]["one_thread"] = {"value": rate1, "cores": 1,
+                                                      "sample": f"32 boards with the BLAS pool limited to one thread in {dt1:.1f} s "
+                                                                "(the reference's CPU executor is single-threaded)"}
+            except ImportError:
+                pass
+        if world == 1 and not args.no_library_proxy:
+            ex.close()
+            try:
+                line["config"]["library_proxy"] = library_proxy(make_inputs)
+            except Exception as e:   # information only: never fails the bench
+                line["config"]["library_proxy"] = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
         print(json.dumps(line), flush=True)
 
     ex.close()

@@ -67,11 +67,6 @@ typedef struct kn_options {
 #define KN_FLAG_NO_CONV_CHAIN 1
 /* matrix multiplies use the one-tile-per-CTA kernel instead of the persistent one (A/B comparison and tests) */
 #define KN_FLAG_NO_PERSISTENT_GEMM 2
-/* convolution chains pack as many images per CTA as shared and tensor memory allow: less SM time per image
-   (the filter stream is shared by more pixels), fewer CTAs and a longer single launch.  For hosts that keep
-   several executors in flight on one device (kn_executor_evaluate_begin / _end); the default arrangement
-   minimises the duration of one launch. */
-#define KN_FLAG_DENSE_CONV_CHAIN 4
 
 #define KN_MAX_RANK 8
 
@@ -190,16 +185,22 @@ KN_API int kn_executor_time_step(kn_executor* exec, int step, int launches, floa
  *
  * For callers that cannot allocate device memory: a serving loop with a fixed memory footprint, a
  * plugin callback inside a runtime that owns every byte of the device, a context whose pool is
- * already handed out.  It runs the executor's split-K tensor-core matmul (TF32 operands rounded to
- * nearest, f32 accumulation) with the per-slice partial sums kept in a fixed array inside the
- * library's device module instead of an allocated buffer; it calls no cudaMalloc / cudaFree and no
- * allocating library routine.  The kernels are enqueued on `stream` (a cudaStream_t, may be NULL for
- * the default stream) of the CURRENT device and the call returns without waiting.
+ * already handed out.  It runs a split-K tensor-core matmul (the executor's one-tile kernel and its
+ * reduction kernel; TF32 operands rounded to nearest, f32 accumulation) with the per-slice partial
+ * sums kept in a fixed array inside the library's device module instead of an allocated buffer; it
+ * calls no cudaMalloc / cudaFree and no allocating library routine.  The kernels are enqueued on
+ * `stream` (a cudaStream_t, may be NULL for the default stream) of the CURRENT device and the call
+ * returns without waiting.
  *
- *  - Limit: slices * m * n * 4 bytes <= KN_STATIC_SCRATCH_BYTES, where slices (1..32) grows with k
- *    and shrinks with the number of 128-row output tiles; larger problems are rejected with
+ *  - Limit: slices * m * n * 4 bytes <= KN_STATIC_SCRATCH_BYTES; larger problems are rejected with
  *    KN_ERR_UNSUPPORTED and a message that states the need.  k must be a multiple of 4; A and B
- *    16-byte aligned.
+ *    16-byte aligned.  `slices` follows from the shape alone, by this rule (integer arithmetic):
+ *        bn       = n > 256 ? 128 : min(256, n rounded up to a multiple of 16)
+ *        tiles    = ceil(m / 128) * ceil(n / bn)
+ *        k_blocks = ceil(k / 32)
+ *        s        = clamp(min(k_blocks / 4, ceil(96 / tiles)), 1, 32)
+ *        slices   = ceil(k_blocks / ceil(k_blocks / s))          (no empty slice)
+ *    (The executor's planner slices its own matmuls by a different rule; only this one applies here.)
  *  - The array costs KN_STATIC_SCRATCH_BYTES of device memory on every GPU that loads the library, for
  *    the life of the process.
  *  - The first call on a device looks up the array's device address and opts the kernel in to large
@@ -210,6 +211,14 @@ KN_API int kn_executor_time_step(kn_executor* exec, int step, int launches, floa
 #define KN_STATIC_SCRATCH_BYTES (8u << 20)
 KN_API int kn_matmul_tf32_static(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k,
                                  void* stream);
+/* Companion of kn_matmul_tf32_static (no counterpart in the reference either).  Every barrier wait in
+ * the kernels is bounded; a CTA whose wait runs out gives up its part of the result and raises a status
+ * word that lives next to the scratch array.  kn_matmul_tf32_static itself returns before the kernels
+ * run, so it cannot report that: after synchronising the stream, call this to learn whether any call
+ * since the last query gave up.  `*code` receives 0 (every result is complete) or the code of the wait
+ * that expired (the affected C is then incomplete: run the call again); the word is cleared.  Reads
+ * the CURRENT device's word with a 4-byte copy; allocates nothing. */
+KN_API int kn_matmul_tf32_static_status(int* code);
 
 /* Host-only element semantics, exported so the scalar rules can be tested without a device:
  * applies one unary / binary operation to 64-bit canonical element patterns. */

@@ -19,7 +19,6 @@ KN_MATH_TF32 = 0
 KN_MATH_F32 = 1
 KN_FLAG_NO_CONV_CHAIN = 1
 KN_FLAG_NO_PERSISTENT_GEMM = 2
-KN_FLAG_DENSE_CONV_CHAIN = 4
 
 
 class KnOptions(Structure):
@@ -65,6 +64,7 @@ SIGNATURES = {
     "kn_executor_last_profile": (c_int, [c_void_p, c_void_p, c_size_t, POINTER(c_size_t)]),
     "kn_executor_time_step": (c_int, [c_void_p, c_int, c_int, POINTER(ctypes.c_float)]),
     "kn_matmul_tf32_static": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p]),
+    "kn_matmul_tf32_static_status": (c_int, [POINTER(c_int)]),
     "kn_scalar_unary": (c_int, [c_int, c_int, c_int, c_uint64, POINTER(c_uint64)]),
     "kn_scalar_binary": (c_int, [c_int, c_int, c_uint64, c_uint64, POINTER(c_uint64)]),
 }

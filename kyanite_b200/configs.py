@@ -126,7 +126,10 @@ def resnet_tower_flops(batch: int, channels: int = 128, blocks: int = 16, board:
 # transformer-shaped workloads
 # --------------------------------------------------------------------------------------
 def _normal(seeds: _Seeds, shape_, std=0.02) -> np.ndarray:
-    return (_rng(seeds.take()).standard_normal(shape_) * std).astype(np.float32)
+    # drawn directly in f32: the diffusion-shaped graph has 860 M weights
+    out = _rng(seeds.take()).standard_normal(shape_, dtype=np.float32)
+    out *= np.float32(std)
+    return out
 
 
 def _dense(g: Graph, seeds: _Seeds, x: Value, n_in: int, n_out: int, bias: bool = True) -> Value:
@@ -172,9 +175,10 @@ def _attention(g: Graph, q: Value, k: Value, v: Value, rows_q, rows_kv, heads: i
 
 
 def bert_encoder(layers: int = 12, hidden: int = 768, heads: int = 12, ffn: int = 3072, vocab: int = 30522,
-                 seq: int = 512, eps: float = 1e-12, seed: int = 10) -> Tuple[Graph, Inputs]:
+                 seq: int = 512, eps: float = 1e-12, seed: int = 10, taps: list = None) -> Tuple[Graph, Inputs]:
     """BERT-base-shaped encoder, f32, post-LayerNorm, learned positions, GELU via erf; weights N(0, 0.02),
-    gamma 1, beta 0.  Input: token ids [B, seq] (i32)."""
+    gamma 1, beta 0.  Input: token ids [B, seq] (i32).  `taps`, if given, receives (name, value) for the
+    embedding output and every layer's output, for layer-wise checks."""
     g = Graph()
     seeds = _Seeds(seed)
     head_dim = hidden // heads
@@ -185,8 +189,10 @@ def bert_encoder(layers: int = 12, hidden: int = 768, heads: int = 12, ffn: int 
     x = g.add(x, g.constant_tensor(_normal(seeds, (1, seq, hidden))))
     ones, zeros = np.ones((1, 1, hidden), np.float32), np.zeros((1, 1, hidden), np.float32)
     x = _layernorm_affine(g, x, 2, eps, ones, zeros)
+    if taps is not None:
+        taps.append(("embedding", x))
     rows = BATCH * seq
-    for _ in range(layers):
+    for li in range(layers):
         x2 = g.view(x, shape(rows, hidden))
         q = _dense(g, seeds, x2, hidden, hidden)
         k = _dense(g, seeds, x2, hidden, hidden)
@@ -198,6 +204,8 @@ def bert_encoder(layers: int = 12, hidden: int = 768, heads: int = 12, ffn: int 
         h = _gelu(g, _dense(g, seeds, x2, hidden, ffn))
         y = _dense(g, seeds, h, ffn, hidden)
         x = _layernorm_affine(g, g.add(g.view(y, shape(BATCH, seq, hidden)), x), 2, eps, ones, zeros)
+        if taps is not None:
+            taps.append((f"layer{li}", x))
     g.output(x)
 
     def make_inputs(batch_size: int, seed: int = 1):
@@ -322,7 +330,7 @@ def llama_decoder(layers: int = 32, d_model: int = 4096, heads: int = 32, ffn: i
 # --------------------------------------------------------------------------------------
 def unet_step(levels=(320, 640, 1280, 1280), res_blocks: int = 2, attention_levels=(0, 1, 2), heads: int = 8,
               latent_channels: int = 4, size: int = 64, ctx_len: int = 77, ctx_dim: int = 768, groups: int = 32,
-              seed: int = 10) -> Tuple[Graph, Inputs]:
+              seed: int = 10, taps: list = None) -> Tuple[Graph, Inputs]:
     """One denoising step of a latent-diffusion-shaped UNet, f32.  The concrete layout (this file is
     its definition): sinusoidal timestep embedding of dim levels[0] -> two linears with SiLU; conv-in;
     per level `res_blocks` x [ResBlock (+ transformer block on attention levels)] then a stride-2
@@ -330,7 +338,9 @@ def unet_step(levels=(320, 640, 1280, 1280), res_blocks: int = 2, attention_leve
     skip concatenation (res_blocks + 1 blocks per level) and nearest x2 upsampling + conv; GroupNorm
     (as view + layernorm + affine), SiLU, conv-out.  Transformer block: self-attention, cross-attention
     on the text context, GEGLU feed-forward, each with pre-LayerNorm and a residual.  Weights N(0, 0.02).
-    Inputs: latent [B, C, size, size], timestep [1], context [B, ctx_len, ctx_dim]."""
+    Inputs: latent [B, C, size, size], timestep [1], context [B, ctx_len, ctx_dim].  `taps`, if given, receives
+    (name, value) for the output of every block (ResBlock, transformer, down- and up-sampling convolution),
+    for layer-wise checks."""
     from .graph import SliceRange, UnaryOp
     g = Graph()
     seeds = _Seeds(seed)
@@ -407,39 +417,44 @@ def unet_step(levels=(320, 640, 1280, 1280), res_blocks: int = 2, attention_leve
         back = g.permute(g.view(x, shape(BATCH, hw, hw, c)), [0, 3, 1, 2])
         return g.add(conv(back, c, c, 1), t)
 
+    def tap(name, v):
+        if taps is not None:
+            taps.append((name, v))
+        return v
+
     # down path
-    cur = conv(latent, latent_channels, ch0, 3)
+    cur = tap("conv_in", conv(latent, latent_channels, ch0, 3))
     hw = size
     skips = [(cur, ch0)]
     c_prev = ch0
     for li, c in enumerate(levels):
-        for _ in range(res_blocks):
-            cur = res_block(cur, c_prev, c, hw)
+        for bi in range(res_blocks):
+            cur = tap(f"down{li}.res{bi}", res_block(cur, c_prev, c, hw))
             c_prev = c
             if li in attention_levels:
-                cur = transformer(cur, c, hw)
+                cur = tap(f"down{li}.attn{bi}", transformer(cur, c, hw))
             skips.append((cur, c))
         if li != len(levels) - 1:
-            cur = conv(cur, c, c, 3, stride=2)
+            cur = tap(f"down{li}.downsample", conv(cur, c, c, 3, stride=2))
             hw //= 2
             skips.append((cur, c))
     # middle
-    cur = res_block(cur, c_prev, c_prev, hw)
-    cur = transformer(cur, c_prev, hw)
-    cur = res_block(cur, c_prev, c_prev, hw)
+    cur = tap("mid.res0", res_block(cur, c_prev, c_prev, hw))
+    cur = tap("mid.attn", transformer(cur, c_prev, hw))
+    cur = tap("mid.res1", res_block(cur, c_prev, c_prev, hw))
     # up path
     for li in reversed(range(len(levels))):
         c = levels[li]
-        for _ in range(res_blocks + 1):
+        for bi in range(res_blocks + 1):
             skip, cs = skips.pop()
-            cur = res_block(g.concat([cur, skip], 1), c_prev + cs, c, hw)
+            cur = tap(f"up{li}.res{bi}", res_block(g.concat([cur, skip], 1), c_prev + cs, c, hw))
             c_prev = c
             if li in attention_levels:
-                cur = transformer(cur, c, hw)
+                cur = tap(f"up{li}.attn{bi}", transformer(cur, c, hw))
         if li != 0:
             cur = g.repeat_interleave(g.repeat_interleave(cur, 2, 2), 3, 2)
             hw *= 2
-            cur = conv(cur, c, c, 3)
+            cur = tap(f"up{li}.upsample", conv(cur, c, c, 3))
     out = conv(silu(group_norm(cur, c_prev, hw)), c_prev, latent_channels, 3)
     g.output(out)
 

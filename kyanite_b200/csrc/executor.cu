@@ -64,6 +64,9 @@ struct Executor {
     int launches = 0;
 
     ~Executor() {
+        // the caller's current device is left as it was (a host may share the thread with other CUDA users)
+        int prev = -1;
+        cudaGetDevice(&prev);
         cudaSetDevice(device);
         if (stream) cudaStreamSynchronize(stream);
         if (graph_exec) cudaGraphExecDestroy(graph_exec);
@@ -76,6 +79,7 @@ struct Executor {
         if (status_dev) cudaFree(status_dev);
         if (status_host) cudaFreeHost(status_host);
         if (stream) cudaStreamDestroy(stream);
+        if (prev >= 0) cudaSetDevice(prev);
     }
 
     uint8_t* device_ptr(const PlanTensor& t) const {
@@ -171,19 +175,24 @@ struct Executor {
     void run_async() {
         if (plan->steps.empty()) return;
         if (profile) {
-            std::vector<cudaEvent_t> ev(plan->steps.size() + 1);
-            for (auto& e : ev) KN_CUDA(cudaEventCreate(&e));
-            KN_CUDA(cudaEventRecord(ev[0], stream));
-            for (size_t i = 0; i < plan->steps.size(); i++) {
-                launch_step(plan->steps[i]);
-                KN_CUDA(cudaEventRecord(ev[i + 1], stream));
-            }
-            KN_CUDA(cudaStreamSynchronize(stream));
-            step_us.assign(plan->steps.size(), 0.f);
-            for (size_t i = 0; i < plan->steps.size(); i++) {
-                float ms = 0;
-                KN_CUDA(cudaEventElapsedTime(&ms, ev[i], ev[i + 1]));
-                step_us[i] = ms * 1000.f;
+            std::vector<cudaEvent_t> ev(plan->steps.size() + 1, nullptr);
+            try {
+                for (auto& e : ev) KN_CUDA(cudaEventCreate(&e));
+                KN_CUDA(cudaEventRecord(ev[0], stream));
+                for (size_t i = 0; i < plan->steps.size(); i++) {
+                    launch_step(plan->steps[i]);
+                    KN_CUDA(cudaEventRecord(ev[i + 1], stream));
+                }
+                KN_CUDA(cudaStreamSynchronize(stream));
+                step_us.assign(plan->steps.size(), 0.f);
+                for (size_t i = 0; i < plan->steps.size(); i++) {
+                    float ms = 0;
+                    KN_CUDA(cudaEventElapsedTime(&ms, ev[i], ev[i + 1]));
+                    step_us[i] = ms * 1000.f;
+                }
+            } catch (...) {
+                for (auto& e : ev) if (e) cudaEventDestroy(e);
+                throw;
             }
             for (auto& e : ev) cudaEventDestroy(e);
             return;

@@ -108,13 +108,18 @@ std::unique_ptr<Graph> Graph::parse(const void* bytes, size_t len) {
                 break;
             case OpKind::Constant: {
                 uint64_t n = r.take<uint64_t>();
-                KN_CHECK(r.pos + n <= len, KN_ERR_BAD_GRAPH, "graph blob: constant payload truncated");
+                // (n and the shape factors come from the blob: compare without letting a sum or product wrap)
+                KN_CHECK(n <= (uint64_t)(len - r.pos), KN_ERR_BAD_GRAPH, "graph blob: constant payload truncated");
+                const uint64_t elem_size = (uint64_t)dtype_size(info.dtype);
                 uint64_t elems = 1;
                 for (auto& s : info.shape) {
                     KN_CHECK(s.exp == 0, KN_ERR_BAD_GRAPH, "graph blob: constant with batch-dependent shape");
+                    KN_CHECK(s.factor == 0 || elems <= (uint64_t)len / s.factor, KN_ERR_BAD_GRAPH,
+                             "graph blob: constant shape larger than the blob");
                     elems *= s.factor;
                 }
-                KN_CHECK(elems * dtype_size(info.dtype) == n, KN_ERR_BAD_GRAPH, "graph blob: constant size mismatch");
+                KN_CHECK(elems <= (uint64_t)len / elem_size && elems * elem_size == n, KN_ERR_BAD_GRAPH,
+                         "graph blob: constant size mismatch");
                 info.const_data = r.p + r.pos;
                 info.const_bytes = n;
                 r.pos += n;

@@ -83,7 +83,13 @@ tc_contract_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     const uint32_t b_tile_bytes = (uint32_t)p.bn * 128u;
     const uint32_t a_base = base;
     const uint32_t b_base = base + (uint32_t)stages * kATileBytes;
-    const uint32_t bar_base = b_base + (uint32_t)stages * b_tile_bytes;   // 8-byte aligned
+    // The barriers and control words sit behind whichever is larger, the operand stages or the tile the
+    // staged epilogue transposes through (128 rows of bn + 4 floats, which reuses the stages' memory): with
+    // few stages and a wide tile the staging tile is the larger one and must not reach the barriers, which
+    // other epilogue warps may still be polling.
+    const uint32_t operand_end = b_base + (uint32_t)stages * b_tile_bytes;
+    const uint32_t staging_end = base + (p.staged ? (uint32_t)kBlockM * (uint32_t)(p.bn + 4) * 4u : 0u);
+    const uint32_t bar_base = operand_end > staging_end ? operand_end : staging_end;   // 8-byte aligned
     const uint32_t full_bar = bar_base, empty_bar = bar_base + 8u * stages, accum_bar = bar_base + 16u * stages;
     const uint32_t slot_addr = accum_bar + 8u;
     // generic pointers to the same words
@@ -660,6 +666,13 @@ CUtensorMap make_map(const void* base, int rank, const int64_t* dims, const int6
 }
 
 int round_up(int x, int to) { return (x + to - 1) / to * to; }
+// dynamic shared memory of tc_contract_kernel: operand stages or the staged epilogue's tile (whichever
+// is larger), then barriers and control words, plus slack for the 1024-byte alignment of the base
+int contract_smem_bytes(int stages, int bn, bool staged) {
+    const int operands = stages * (kATileBytes + bn * 128);
+    const int staging = staged ? kBlockM * (bn + 4) * 4 : 0;
+    return std::max(operands, staging) + 16 * stages + 64 + 1024;
+}
 int pow2_ceil(int x) {
     int p = 1;
     while (p < x) p <<= 1;
@@ -843,7 +856,7 @@ bool tc_conv_tile(int oh, int ow, int* wb, int* hb, int* nb) {
 void tc_prepare_step(Step& step, uint32_t* status_word, int flags) {
     auto launch = std::make_shared<TcLaunch>();
     if (step.kind == StepKind::ConvChain) {
-        launch->chain = chain_prepare(step.chain, status_word, (flags & KN_FLAG_DENSE_CONV_CHAIN) != 0);
+        launch->chain = chain_prepare(step.chain, status_word);
         step.tc = launch;
         return;
     }
@@ -995,8 +1008,7 @@ void tc_prepare_step(Step& step, uint32_t* status_word, int flags) {
         const int out_mode = classify(p.out, p.so);
         p.vec4 = p.staged && p.n % 4 == 0 && out_mode == 2 && p.add1_mode != 3 && p.add2_mode != 3;
     }
-    const int staging_bytes = p.staged ? kBlockM * (p.bn + 4) * 4 : 0;
-    launch->smem_bytes = std::max(p.stages * stage_bytes + 16 * p.stages + 64, staging_bytes) + 1024;
+    launch->smem_bytes = contract_smem_bytes(p.stages, p.bn, p.staged != 0);
     step.tc = launch;
 }
 
@@ -1116,7 +1128,9 @@ void matmul_static(const float* a, const float* b, float* c, int64_t m, int64_t 
     KN_CHECK(((uintptr_t)a & 15) == 0 && ((uintptr_t)b & 15) == 0 && ((uintptr_t)c & 3) == 0, KN_ERR_INVALID_ARG,
              "A and B must be 16-byte aligned, C 4-byte aligned");
 
-    // same slicing rule as the planner: aim at ~96 CTAs, at least 4 K blocks per slice, at most 32 slices
+    // The slicing rule of this entry point (stated in kn_b200.h; the executor's planner uses a rule of its own):
+    // column tiles of bn = 128 when n > 256, else n rounded up to 16; K in 32-element blocks; enough slices to
+    // reach about 96 CTAs, at least 4 K blocks per slice, at most 32 slices, no empty slice.
     const int bn = n > 256 ? 128 : (int)std::min<int64_t>(round_up((int)std::min<int64_t>(n, 256), 16), 256);
     const int64_t tiles = ((m + kBlockM - 1) / kBlockM) * ((n + bn - 1) / bn);
     const int64_t k_blocks = (k + kBlockK - 1) / kBlockK;
@@ -1159,8 +1173,7 @@ void matmul_static(const float* a, const float* b, float* c, int64_t m, int64_t 
         p.add1_mode = 0;
         p.add2_mode = 0;
     }
-    const int staging_bytes = kBlockM * (bn + 4) * 4;
-    const int smem_bytes = std::max(p.stages * stage_bytes + 16 * p.stages + 64, staging_bytes) + 1024;
+    const int smem_bytes = contract_smem_bytes(p.stages, bn, true);
 
     int64_t adims[4] = {k, m, 1, 1}, astr[4] = {1, k, 4, 4};
     int abox[4] = {kBlockK, kBlockM, 1, 1};
@@ -1192,8 +1205,47 @@ void matmul_static(const float* a, const float* b, float* c, int64_t m, int64_t 
     KN_CHECK(err == cudaSuccess, KN_ERR_CUDA, std::string("launch failed: ") + cudaGetErrorString(err));
 }
 
+// Reads the status word of the current device and clears it.  The word is raised by a kernel of
+// kn_matmul_tf32_static whose bounded barrier wait ran out (that CTA then skipped its part of the result).
+// Two 4-byte copies between the module's array and the host: nothing is allocated.
+int matmul_static_status() {
+    int device = -1;
+    cudaError_t err = cudaGetDevice(&device);
+    KN_CHECK(err == cudaSuccess, KN_ERR_CUDA, std::string("cudaGetDevice failed: ") + cudaGetErrorString(err));
+    KN_CHECK(device >= 0 && device < 64, KN_ERR_UNSUPPORTED, "device index above 63");
+    uint32_t* word = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_static_mu);
+        if (!g_static_dev[device].ready) return 0;   // no call has run on this device yet
+        word = g_static_dev[device].status;
+    }
+    uint32_t code = 0;
+    err = cudaMemcpy(&code, word, sizeof(code), cudaMemcpyDeviceToHost);
+    KN_CHECK(err == cudaSuccess, KN_ERR_CUDA, std::string("reading the status word failed: ") + cudaGetErrorString(err));
+    if (code != 0) {
+        const uint32_t zero = 0;
+        err = cudaMemcpy(word, &zero, sizeof(zero), cudaMemcpyHostToDevice);
+        KN_CHECK(err == cudaSuccess, KN_ERR_CUDA, std::string("clearing the status word failed: ") + cudaGetErrorString(err));
+    }
+    return (int)code;
+}
+
 }  // namespace
 }  // namespace kn
+
+extern "C" KN_API int kn_matmul_tf32_static_status(int* code) {
+    try {
+        KN_CHECK(code != nullptr, KN_ERR_INVALID_ARG, "null code pointer");
+        *code = kn::matmul_static_status();
+        return KN_OK;
+    } catch (const kn::Error& e) {
+        kn::set_last_error(e.what());
+        return e.code;
+    } catch (const std::exception& e) {
+        kn::set_last_error(e.what());
+        return KN_ERR_INTERNAL;
+    }
+}
 
 extern "C" KN_API int kn_matmul_tf32_static(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k,
                                             void* stream) {

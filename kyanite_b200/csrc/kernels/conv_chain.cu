@@ -404,7 +404,7 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
 // ---------------------------------------------------------------- host side
 static int round_up_int(int x, int to) { return (x + to - 1) / to * to; }
 
-bool tc_chain_geometry(int h, int w, int64_t n_img, int c_blocks, ChainGeometry* out, bool dense) {
+bool tc_chain_geometry(int h, int w, int64_t n_img, int c_blocks, ChainGeometry* out) {
     if (h < 1 || w < 1 || h > 254 || w > 254 || n_img < 1 || c_blocks < 1 || c_blocks > 4) return false;
     ChainGeometry best{};
     double best_cost = 1e300;
@@ -424,14 +424,9 @@ bool tc_chain_geometry(int h, int w, int64_t n_img, int c_blocks, ChainGeometry*
             g.rows_alloc = round_up_int(g.r_first + g.n_mma + g.wp + 2, 8);
             const int act_bytes = c_blocks * g.rows_alloc * 128;
             const int fixed = 1024 /* alignment */ + 16 * 8 + 32 + 1024 /* column table */ + 64 /* chunk masks */;
-            // the ring holds whole taps (c_blocks tiles each): two of them at least, four at most; a dense
-            // arrangement may settle for half taps when the activations leave room for nothing else
+            // the ring holds whole taps (c_blocks tiles each): two of them at least, four at most
             g.group = c_blocks;
-            int requests = std::min(4, (227 * 1024 - fixed - act_bytes) / (kTileBytes * g.group));
-            if (requests < 2 && dense && c_blocks % 2 == 0) {
-                g.group = c_blocks / 2;
-                requests = std::min(4, (227 * 1024 - fixed - act_bytes) / (kTileBytes * g.group));
-            }
+            const int requests = std::min(4, (227 * 1024 - fixed - act_bytes) / (kTileBytes * g.group));
             if (requests < 2) break;
             g.slots = requests * g.group;
             g.smem_bytes = fixed + act_bytes + g.slots * kTileBytes;
@@ -440,7 +435,7 @@ bool tc_chain_geometry(int h, int w, int64_t n_img, int c_blocks, ChainGeometry*
             const double mma = std::max(70.0, 0.47 * g.n_mma + 16.0);
             const double per_layer = 144.0 * mma + 22.0 * g.n_mma + 900.0;
             const int64_t ctas = (n_img + g.per_cta - 1) / g.per_cta;
-            const double cost = dense ? per_layer / g.per_cta : (double)((ctas + 147) / 148) * per_layer;
+            const double cost = (double)((ctas + 147) / 148) * per_layer;
             if (cost < best_cost) {
                 best_cost = cost;
                 best = g;
@@ -459,7 +454,7 @@ struct ChainLaunch {
     int smem_bytes;
 };
 
-std::shared_ptr<void> chain_prepare(const ConvChainParams& c, uint32_t* status_word, bool dense) {
+std::shared_ptr<void> chain_prepare(const ConvChainParams& c, uint32_t* status_word) {
     auto l = std::make_shared<ChainLaunch>();
     ChainKernelParams& p = l->p;
     memset(&p, 0, sizeof(p));
@@ -473,7 +468,7 @@ std::shared_ptr<void> chain_prepare(const ConvChainParams& c, uint32_t* status_w
     }
     c_blocks_max = std::max(c_blocks_max, (c.k + 31) / 32);
     ChainGeometry g;
-    KN_CHECK(tc_chain_geometry(c.h, c.w, c.n, c_blocks_max, &g, dense), KN_ERR_INTERNAL, "convolution chain does not fit");
+    KN_CHECK(tc_chain_geometry(c.h, c.w, c.n, c_blocks_max, &g), KN_ERR_INTERNAL, "convolution chain does not fit");
     p.in = c.in;
     p.out = c.out;
     p.bias = c.bias;

@@ -25,7 +25,7 @@ std::shared_ptr<void> gemm_persistent_prepare(const GemmParams& g, uint32_t* sta
 int gemm_persistent_launch(const void* launch, cudaStream_t stream);
 
 // Convolution chain (kernels/conv_chain.cu): launch data built once the device pointers are known.
-std::shared_ptr<void> chain_prepare(const ConvChainParams& c, uint32_t* status_word, bool dense);
+std::shared_ptr<void> chain_prepare(const ConvChainParams& c, uint32_t* status_word);
 int chain_launch(const void* launch, cudaStream_t stream);
 
 }  // namespace kn

@@ -36,13 +36,11 @@ struct ChainGeometry {
     int n_mma;        // accumulator columns: padded positions q_first .. q_first + n_mma - 1
     int rows_alloc;   // 128-byte rows per 32-channel block of the activation buffer
     int slots;        // 16 KB filter tiles in flight
-    int group;        // filter tiles per request (a whole tap = the layer's channel blocks, or half a tap)
+    int group;        // filter tiles per request (a whole tap = the layer's channel blocks)
     int smem_bytes;
 };
 // False if images of this size do not fit (then every layer stays its own step).  `c_blocks` = 32-channel
 // blocks of the widest layer.  Pure host arithmetic.
-// `dense`: choose the arrangement with the least SM time per image instead of the shortest launch (more images
-// per CTA, fewer CTAs: for hosts that keep several executors in flight on one device).
-bool tc_chain_geometry(int h, int w, int64_t n_img, int c_blocks, ChainGeometry* out, bool dense = false);
+bool tc_chain_geometry(int h, int w, int64_t n_img, int c_blocks, ChainGeometry* out);
 
 }  // namespace kn

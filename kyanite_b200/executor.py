@@ -24,14 +24,12 @@ from ._lib import KnError, KnMemUsage, KnOptions, KnTensorInfo, check
 from .graph import DType, Graph
 
 __all__ = ["CudaDevice", "CudaDeviceNotAvailable", "CudaExecutor", "Device", "PreparedGraph", "MemoryUsage",
-           "plan_describe", "KnError", "MATH_TF32", "MATH_F32", "FLAG_NO_CONV_CHAIN", "FLAG_NO_PERSISTENT_GEMM",
-           "FLAG_DENSE_CONV_CHAIN"]
+           "plan_describe", "KnError", "MATH_TF32", "MATH_F32", "FLAG_NO_CONV_CHAIN", "FLAG_NO_PERSISTENT_GEMM"]
 
 MATH_TF32 = _lib.KN_MATH_TF32
 MATH_F32 = _lib.KN_MATH_F32
 FLAG_NO_CONV_CHAIN = _lib.KN_FLAG_NO_CONV_CHAIN
 FLAG_NO_PERSISTENT_GEMM = _lib.KN_FLAG_NO_PERSISTENT_GEMM
-FLAG_DENSE_CONV_CHAIN = _lib.KN_FLAG_DENSE_CONV_CHAIN
 
 
 class CudaDeviceNotAvailable(RuntimeError):
@@ -53,7 +51,10 @@ class _GraphHandle:
     def __init__(self, graph):
         blob = graph if isinstance(graph, (bytes, bytearray)) else graph.to_bytes()
         self.ptr = c_void_p()
-        buf = (ctypes.c_char * len(blob)).from_buffer_copy(blob)
+        if isinstance(blob, bytes):
+            buf = ctypes.c_char_p(blob)          # the library copies the blob: no second copy here
+        else:
+            buf = (ctypes.c_char * len(blob)).from_buffer(blob)
         check(_lib.load().kn_graph_from_blob(ctypes.cast(buf, c_void_p), len(blob), byref(self.ptr)))
 
     def close(self):
@@ -201,6 +202,24 @@ class CudaExecutor:
         out_ptrs = (c_void_p * max(1, len(outs)))(*[o.ctypes.data for o in outs])
         check(self._lib.kn_executor_evaluate(self._ptr, in_ptrs, out_ptrs))
         return outs
+
+    def evaluate_begin(self, inputs: Sequence[np.ndarray]):
+        """First half of `evaluate` with caller-owned input arrays (C-contiguous, right shape and dtype; checked):
+        the library copies them to its pinned staging, then enqueues upload, steps and download without
+        waiting (kn_executor_evaluate_begin).  The arrays may be reused as soon as this returns."""
+        if len(inputs) != len(self._in_info):
+            raise ValueError(f"Wrong input count, expected {len(self._in_info)} but got {len(inputs)}")
+        for i, (x, (shape, dtype, _)) in enumerate(zip(inputs, self._in_info)):
+            if tuple(x.shape) != shape or x.dtype != dtype.np or not x.flags.c_contiguous:
+                raise ValueError(f"input {i}: expected a C-contiguous {dtype.np} array of shape {shape}")
+        in_ptrs = (c_void_p * max(1, len(inputs)))(*[a.ctypes.data if a.size else None for a in inputs])
+        check(self._lib.kn_executor_evaluate_begin(self._ptr, in_ptrs))
+
+    def evaluate_end(self) -> List[np.ndarray]:
+        """Second half: waits for the evaluation started by `evaluate_begin` and returns the outputs as views
+        of the executor's pinned staging, valid until the next evaluation (the reference's `evaluate`
+        returns borrowed tensors too, kn-cuda-eval/src/executor.rs:194)."""
+        return self.evaluate_staged_end()
 
     def evaluate_staged(self) -> List[np.ndarray]:
         """`evaluate` on the pinned staging buffers: the caller has filled `host_inputs` and reads

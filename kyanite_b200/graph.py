@@ -936,6 +936,7 @@ class Graph:
           LAYERNORM  u32 input, u32 axis, f32 eps
           REDUCE     u32 input, u8 op, u32 count, count x u32 axes
         """
+        parts = []          # large constants are appended as they are (one copy, in the final join)
         out = bytearray()
         out += b"KNG1"
         out += struct.pack("<III", len(self.values), len(self.inputs), len(self.outputs))
@@ -951,9 +952,14 @@ class Graph:
             if k == OpKind.INPUT:
                 out += struct.pack("<I", info.input_index)
             elif k == OpKind.CONSTANT:
-                raw = info.tensor.tobytes()
-                out += struct.pack("<Q", len(raw))
-                out += raw
+                raw = np.ascontiguousarray(info.tensor)
+                out += struct.pack("<Q", raw.nbytes)
+                if raw.nbytes >= 1 << 16:
+                    parts.append(bytes(out))
+                    parts.append(raw.reshape(-1).view(np.uint8).data)
+                    out = bytearray()
+                else:
+                    out += raw.tobytes()
             elif k in (OpKind.VIEW, OpKind.BROADCAST):
                 out += struct.pack("<I", info.inputs[0])
             elif k == OpKind.PERMUTE:
@@ -991,7 +997,8 @@ class Graph:
                     out += struct.pack("<I", a)
             else:
                 raise AssertionError(k)
-        return bytes(out)
+        parts.append(bytes(out))
+        return b"".join(parts)
 
     def __repr__(self):
         return f"Graph(inputs={self.input_shapes()}, outputs={self.output_shapes()}, values={len(self.values)})"

@@ -396,26 +396,50 @@ def gather(x: np.ndarray, axis: int, indices: np.ndarray) -> np.ndarray:
 # --------------------------------------------------------------------------------------
 # graph evaluation
 # --------------------------------------------------------------------------------------
-def cpu_eval_graph(blob, batch_size: int, inputs: Sequence[np.ndarray], keep_all: bool = False):
+def cpu_eval_graph(blob, batch_size: int, inputs: Sequence[np.ndarray], keep_all: bool = False,
+                   overrides: Optional[dict] = None, wanted: Optional[Sequence[int]] = None):
     """Evaluate the graph on the CPU (cpu.rs:20-98).  Returns the list of outputs, each a
-    C-contiguous array (cpu.rs:526-535); with `keep_all` also returns every intermediate."""
+    C-contiguous array (cpu.rs:526-535); with `keep_all` also returns every intermediate.
+
+    For layer-wise checks of graphs too large to evaluate whole (the reference tests big graphs
+    differentially too, kn-cuda-eval/tests/root/runner.rs:29-55): `overrides` maps value indices to arrays
+    that stand in for those values (another executor's result for the layer's input, say) and `wanted`
+    lists the value indices to return instead of the graph's outputs.  Only values that `wanted` depends
+    on, up to the overridden ones, are computed; graph inputs nothing needs may be passed as None."""
     g = blob if isinstance(blob, ParsedGraph) else parse_graph(blob)
     if len(inputs) != len(g.inputs):
         raise ValueError(f"expected {len(g.inputs)} inputs, got {len(inputs)}")
+    overrides = overrides or {}
+    targets = list(g.outputs) if wanted is None else list(wanted)
+
+    needed = [False] * len(g.nodes)
+    stack = list(targets)
+    while stack:
+        i = stack.pop()
+        if needed[i]:
+            continue
+        needed[i] = True
+        if i not in overrides:
+            stack.extend(g.nodes[i].inputs)
 
     last_use = {}
     for i, node in enumerate(g.nodes):
-        for j in node.inputs:
-            last_use[j] = i
-    keep = set(g.outputs)
+        if needed[i] and i not in overrides:
+            for j in node.inputs:
+                last_use[j] = i
+    keep = set(targets)
 
     vals: List[Optional[np.ndarray]] = [None] * len(g.nodes)
     for i, node in enumerate(g.nodes):
+        if not needed[i]:
+            continue
         out_shape = tuple(f * batch_size ** e for f, e in node.shape)
         np_dtype = np.dtype(NP_DTYPES[node.dtype])
-        a = [vals[j] for j in node.inputs]
+        a = [vals[j] for j in node.inputs] if i not in overrides else []
         op = node.op
-        if op == OP_INPUT:
+        if i in overrides:
+            res = np.asarray(overrides[i])
+        elif op == OP_INPUT:
             x = np.asarray(inputs[node.attr["index"]])
             if x.dtype != np_dtype:
                 raise ValueError(f"input {node.attr['index']}: expected dtype {np_dtype}, got {x.dtype}")
@@ -467,13 +491,13 @@ def cpu_eval_graph(blob, batch_size: int, inputs: Sequence[np.ndarray], keep_all
             raise AssertionError(f"value {i}: wrong dtype {res.dtype}, expected {np_dtype}")
         vals[i] = res
 
-        if not keep_all:
+        if not keep_all and i not in overrides:
             for j in set(node.inputs):
                 if last_use.get(j) == i and j not in keep:
                     vals[j] = None
 
     # (np.ascontiguousarray would promote rank 0 to rank 1)
-    outs = [np.array(vals[o], order="C", copy=True) for o in g.outputs]
+    outs = [np.array(vals[o], order="C", copy=True) for o in targets]
     if keep_all:
         return outs, vals
     return outs
@@ -484,8 +508,10 @@ def assert_tensors_match(expected: Sequence[np.ndarray], actual: Sequence[np.nda
     """The reference's comparison rule (kn-cuda-eval/src/tester.rs:28-29,216-302): floats mismatch
     iff abs_diff >= tol_abs AND rel_diff >= tol_rel, NaN positions must agree, non-floats must be
     exactly equal.  With `abs_scaled` the absolute threshold of each tensor is
-    tol_abs * max(1, largest finite |expected|), for reduced-precision operands whose rounding error
-    is relative to the summed magnitudes rather than to the (possibly cancelled) result.
+    tol_abs * (largest finite |expected| of that tensor), for reduced-precision operands whose rounding
+    error is relative to the summed magnitudes rather than to the (possibly cancelled) result.  There is
+    no floor at 1: a tensor of small numbers (a softmax over thousands of entries) is held to its own
+    scale.  A tensor that is all zeros keeps the plain tol_abs.
     Returns the (max abs, max rel) float error seen."""
     assert len(expected) == len(actual), f"wrong number of tensors: {len(expected)} vs {len(actual)}"
     max_abs = 0.0
@@ -511,13 +537,14 @@ def assert_tensors_match(expected: Sequence[np.ndarray], actual: Sequence[np.nda
         tensor_abs = tol_abs
         if abs_scaled:
             finite = np.abs(e64[np.isfinite(e64)])
-            tensor_abs = tol_abs * max(1.0, float(finite.max()) if finite.size else 1.0)
+            scale = float(finite.max()) if finite.size else 0.0
+            tensor_abs = tol_abs * scale if scale > 0.0 else tol_abs
         bad = (d >= tensor_abs) & (rel >= tol_rel)
         if bad.any():
             idx = np.argwhere(bad)[:5]
             msg = ", ".join(f"{tuple(j)}: expected {e[tuple(j)]}, got {a[tuple(j)]}" for j in idx)
-            raise AssertionError(f"tensor {i}: {int(bad.sum())}/{bad.size} mismatches (abs>={tol_abs} and "
-                                 f"rel>={tol_rel}); {msg}")
+            raise AssertionError(f"tensor {i}: {int(bad.sum())}/{bad.size} mismatches (abs>={tensor_abs:.3g} and "
+                                 f"rel>={tol_rel}; worst abs {float(d[bad].max()):.3g}); {msg}")
         fin = np.isfinite(d)
         if fin.any():
             max_abs = max(max_abs, float(d[fin].max()))

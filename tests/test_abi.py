@@ -48,6 +48,36 @@ def test_bad_blob_is_an_error_not_a_crash():
         plan_describe(blob + b"x", 1)
 
 
+def test_constant_sizes_that_wrap_are_refused():
+    """A constant's byte count and shape factors come from the blob; values chosen so that a 64-bit sum or
+    product wraps must not pass the size checks."""
+    import struct
+    lib = _lib.load()
+    out = ctypes.c_void_p()
+
+    def blob_with_constant(factors, byte_count, payload):
+        b = bytearray(b"KNG1") + struct.pack("<III", 1, 0, 1) + struct.pack("<I", 0)
+        b += struct.pack("<BBH", 1, 0, len(factors))        # CONSTANT, f32
+        for f in factors:
+            b += struct.pack("<QI", f, 0)
+        b += struct.pack("<Q", byte_count) + payload
+        return bytes(b)
+
+    good = blob_with_constant([2], 8, b"\0" * 8)
+    assert lib.kn_graph_from_blob(good, len(good), ctypes.byref(out)) == 0
+    lib.kn_graph_destroy(out)
+    cases = [
+        blob_with_constant([2], 2**64 - 4, b"\0" * 8),            # position + count wraps
+        blob_with_constant([2**62, 2**2 + 0, 2], 8, b"\0" * 8),   # product of factors wraps to 0 elements x 4... then 8
+        blob_with_constant([2**63, 2, 2], 8, b"\0" * 8),          # 2^65 elements wraps to 0
+        blob_with_constant([2**62 + 2], 8, b"\0" * 8),            # elements x 4 bytes wraps to 8
+    ]
+    for bad in cases:
+        out = ctypes.c_void_p()
+        assert lib.kn_graph_from_blob(bad, len(bad), ctypes.byref(out)) == 2
+        assert not out.value
+
+
 def test_null_arguments():
     lib = _lib.load()
     assert lib.kn_graph_from_blob(None, 0, None) == 1

@@ -74,3 +74,38 @@ def test_config_matches_oracle(name, mode):
         else:
             # TF32 operands (10-bit mantissa), f32 accumulation; scaled by the output magnitude
             assert_tensors_match(expected, actual, 4e-3, 4e-3, abs_scaled=True)
+
+
+@pytest.mark.parametrize("name", ["bert", "unet"])
+def test_oracle_block_by_block_equals_whole(name):
+    """The plumbing of the full-size GPU tests (tests/test_full_size.py) on small graphs, with the oracle's own
+    full-batch result standing in for the executor's: evaluating a subset of batch rows alone, and evaluating
+    one block from overridden values of all other block boundaries, reproduce the whole-graph result."""
+    from oracle.cpu_eval import parse_graph
+    taps = []
+    if name == "bert":
+        graph, make_inputs = configs.bert_encoder(layers=2, hidden=64, heads=4, ffn=128, vocab=100, seq=16, taps=taps)
+    else:
+        graph, make_inputs = configs.unet_step(levels=(32, 64), res_blocks=1, attention_levels=(0,), heads=2, size=16,
+                                               ctx_len=5, ctx_dim=24, groups=8, taps=taps)
+    assert len(taps) >= 3
+    for _, v in taps:
+        if v.index not in [o.index for o in graph.outputs]:
+            graph.output(v)
+    out_pos = {o.index: i for i, o in enumerate(graph.outputs)}
+    parsed = parse_graph(graph.to_bytes())
+    batch, rows = 3, [2]
+    inputs = make_inputs(batch, 5)
+    whole = cpu_eval_graph(parsed, batch, inputs)
+    sub_inputs = [x[rows] if x.shape[:1] == (batch,) else x for x in inputs]
+    alone = cpu_eval_graph(parsed, len(rows), sub_inputs)
+    assert_tensors_match([w[rows] for w in whole], alone, 1e-5, 1e-5)
+    for tap_name, v in taps:
+        overrides = {w.index: whole[out_pos[w.index]][rows] for n, w in taps if n != tap_name}
+        block = cpu_eval_graph(parsed, len(rows), sub_inputs, overrides=overrides, wanted=[v.index])
+        assert_tensors_match([whole[out_pos[v.index]][rows]], block, 1e-5, 1e-5)
+    # values nothing needs are not computed: with every tap overridden and one of them wanted, no input is read
+    last = taps[-1][1]
+    only = cpu_eval_graph(parsed, len(rows), [None] * len(inputs),
+                          overrides={w.index: whole[out_pos[w.index]][rows] for _, w in taps}, wanted=[last.index])
+    np.testing.assert_array_equal(only[0], whole[out_pos[last.index]][rows])

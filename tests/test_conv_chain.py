@@ -191,33 +191,3 @@ def test_heads_match_oracle_and_separate_kernels(name):
             np.testing.assert_array_equal(a, b)
     with CudaExecutor(0, g, batch, math_mode=MATH_TF32, flags=FLAG_NO_CONV_CHAIN) as ex:
         assert_tensors_match(ex.evaluate([x]), fused, 1e-3, 1e-3, abs_scaled=True)
-
-
-@pytest.mark.gpu
-@pytest.mark.parametrize("name", ["tower_8x8_c128", "odd_batch", "narrow_64", "deep", "tall_12x4"])
-def test_dense_arrangement_matches(name):
-    """KN_FLAG_DENSE_CONV_CHAIN packs more images into a CTA (three 8x8 boards, 224 accumulator columns, filter
-    requests of half a tap); results must equal the default arrangement's up to the summation order."""
-    from kyanite_b200.executor import FLAG_DENSE_CONV_CHAIN, CudaExecutor
-    cfg = dict(CASES[name])
-    batch = cfg.pop("batch")
-    g = tower(seed=hash(name) % 1000, **cfg)
-    x = rng(5).standard_normal((batch, cfg["c_in"], cfg["h"], cfg["w"])).astype(np.float32)
-    expected = cpu_eval_graph(g.to_bytes(), batch, [x])
-    with CudaExecutor(0, g, batch, math_mode=MATH_TF32, flags=FLAG_DENSE_CONV_CHAIN) as ex:
-        dense = ex.evaluate([x])
-        assert_tensors_match(expected, dense, 4e-3, 4e-3, abs_scaled=True)
-        for a, b in zip(dense, ex.evaluate([x])):
-            np.testing.assert_array_equal(a, b)
-    with CudaExecutor(0, g, batch, math_mode=MATH_TF32) as ex:
-        assert_tensors_match(ex.evaluate([x]), dense, 1e-3, 1e-3, abs_scaled=True)
-
-
-@pytest.mark.gpu
-def test_dense_full_tower_batch_256():
-    from kyanite_b200.executor import FLAG_DENSE_CONV_CHAIN, CudaExecutor
-    g, make_inputs = resnet_tower()
-    inputs = make_inputs(256, 3)
-    expected = cpu_eval_graph(g.to_bytes(), 256, inputs)
-    with CudaExecutor(0, g, 256, math_mode=MATH_TF32, flags=FLAG_DENSE_CONV_CHAIN) as ex:
-        assert_tensors_match(expected, ex.evaluate(inputs), 4e-3, 4e-3, abs_scaled=True)

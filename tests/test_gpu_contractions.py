@@ -1,7 +1,7 @@
 """Tensor-core contraction kernels against the CPU oracle on shapes the reference suite does not
 reach: tiles with ragged edges, channel tails, boards that are not a power of two, 5x5 filters, split-K
 matmuls (partial tiles through the step's scratch buffer), channels-last chains with a residual.
-Tolerance for TF32 operands: abs >= 4e-3 * max(1, largest |expected|) AND rel >= 4e-3 is a mismatch."""
+Tolerance for TF32 operands: abs >= 4e-3 * (largest |expected| of the tensor) AND rel >= 4e-3 is a mismatch."""
 import numpy as np
 import pytest
 
