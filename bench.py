@@ -447,9 +447,8 @@ def main():
         host_s = 0.0
         for i in range(fill):
             submit(i)
-        if finish:
-            for i in range(fill - lead):
-                finish(i)
+            if finish and i >= lead:
+                finish(i - lead)
         marks[0].record(streams[(fill - 1) % n_ex])   # behind the newest submitted step
         for j in range(total):
             i = fill + j

@@ -179,6 +179,16 @@ KN_API int kn_executor_last_profile(kn_executor* exec, char* buf, size_t cap, si
  * the event and launch gaps of a one-by-one run; this one does not.)  No reference counterpart. */
 KN_API int kn_executor_time_step(kn_executor* exec, int step, int launches, float* microseconds);
 
+/* Self-test of the bounded waits, with no counterpart in the reference.  Every barrier wait inside the
+ * tensor-core kernels gives up after a cycle limit, raises the executor's status word and lets the
+ * kernel return, and the next synchronising call reports KN_ERR_INTERNAL.  In normal operation no wait
+ * expires, so this entry point makes one expire on purpose, harmlessly: a one-thread kernel waits
+ * through the same routine, with a limit of `limit_us` microseconds (1 .. 100000), on a barrier in its own
+ * shared memory that nothing arrives on.  It holds no tensor memory and has no copies in flight.
+ * Returns KN_ERR_INTERNAL (the status path works, message "a kernel gave up waiting ... (code 99)") or
+ * KN_OK (the expiry went unreported: a defect).  The status word is cleared and the executor stays usable. */
+KN_API int kn_executor_selftest_wait_expiry(kn_executor* exec, uint32_t limit_us);
+
 /* Matrix multiply that allocates nothing.  No counterpart in the reference.
  *
  *     C[m][n] = sum_k A[m][k] * B[n][k]        (A, B, C dense row-major f32 in DEVICE memory)

@@ -63,6 +63,7 @@ SIGNATURES = {
     "kn_executor_set_profile": (c_int, [c_void_p, c_int]),
     "kn_executor_last_profile": (c_int, [c_void_p, c_void_p, c_size_t, POINTER(c_size_t)]),
     "kn_executor_time_step": (c_int, [c_void_p, c_int, c_int, POINTER(ctypes.c_float)]),
+    "kn_executor_selftest_wait_expiry": (c_int, [c_void_p, c_uint32]),
     "kn_matmul_tf32_static": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p]),
     "kn_matmul_tf32_static_status": (c_int, [POINTER(c_int)]),
     "kn_scalar_unary": (c_int, [c_int, c_int, c_int, c_uint64, POINTER(c_uint64)]),

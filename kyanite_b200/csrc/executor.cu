@@ -16,8 +16,24 @@
 #include "plan.h"
 #include "scalar_ops.h"
 #include "tc.h"
+#include "kernels/tc_ptx.cuh"
 
 namespace kn {
+
+// One thread waits, through the same bounded wait every tensor-core kernel uses, on a barrier that nobody
+// arrives on: the wait runs out after `limit_cycles`, raises the status word and the kernel returns.  No tensor
+// memory, no copies in flight: nothing is left behind.  (kn_executor_selftest_wait_expiry)
+__global__ void wait_expiry_kernel(uint32_t* status, long long limit_cycles, uint32_t code) {
+    __shared__ __align__(8) unsigned long long bar;
+    __shared__ int abandon;
+    if (threadIdx.x == 0) {
+        tcp::mbar_init(tcp::smem_u32(&bar), 1);
+        abandon = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) tcp::mbar_wait(tcp::smem_u32(&bar), 0, &abandon, status, code, limit_cycles);
+}
 
 namespace {
 
@@ -700,6 +716,24 @@ int kn_executor_time_step(kn_executor* exec, int step, int launches, float* micr
         }
         cudaEventDestroy(a);
         cudaEventDestroy(b);
+    });
+}
+
+int kn_executor_selftest_wait_expiry(kn_executor* exec, uint32_t limit_us) {
+    return guarded([&] {
+        KN_CHECK(exec != nullptr, KN_ERR_INVALID_ARG, "null executor");
+        KN_CHECK(limit_us >= 1 && limit_us <= 100000, KN_ERR_INVALID_ARG, "limit must be 1 .. 100000 microseconds");
+        kn::Executor& e = *exec->e;
+        KN_CHECK(!e.in_flight, KN_ERR_INVALID_ARG, "an evaluation is in flight");
+        kn::DeviceGuard guard(e.device);
+        int khz = 0;
+        KN_CUDA(cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, e.device));
+        const long long cycles = (long long)limit_us * (long long)(khz > 0 ? khz : 2000000) / 1000ll;
+        kn::wait_expiry_kernel<<<1, 32, 0, e.stream>>>(e.status_dev, cycles, 99u);
+        KN_CUDA(cudaGetLastError());
+        KN_CUDA(cudaMemcpyAsync(e.status_host, e.status_dev, 4, cudaMemcpyDeviceToHost, e.stream));
+        KN_CUDA(cudaStreamSynchronize(e.stream));
+        e.check_status();   // throws KN_ERR_INTERNAL: the expected outcome
     });
 }
 

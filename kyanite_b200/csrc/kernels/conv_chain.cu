@@ -20,9 +20,10 @@
 //              pattern is anchored at a 1024-byte boundary, so the descriptor's base-offset field stays 0
 //              (measured: a non-zero base offset permutes the channels).
 //
-// Warp roles (320 threads): warp 0 lane 0 streams filter tiles; warp 1 lane 0 issues the MMAs of a layer
-// once its input is complete; warps 2..9 are the epilogue (two warps per TMEM lane quarter, each taking
-// alternate 16-column chunks): accumulator + bias (+ held skip tensor) -> ReLU -> written back as the
+// Warp roles (64 + 128 E threads): warp 0 lane 0 streams filter tiles; warp 1 lane 0 issues the MMAs of a layer
+// once its input is complete; the other 4 E warps are the epilogue (E warps per TMEM lane quarter, taking the
+// 16-column chunks of the accumulator in turn; E = 3 when the chunk count divides by three, as the 9 chunks of
+// two 8x8 boards do, else 2): accumulator + bias (+ held skip tensor) -> ReLU -> written back as the
 // next layer's operand (rounded to TF32, zeros at padding positions) and, if a later layer adds it,
 // into the held-tensor columns of TMEM in full f32; a layer flagged to store writes its result to global
 // memory.  The last layer may be a pointwise (1x1) layer that computes several convolutions of the last
@@ -49,8 +50,7 @@ namespace {
 
 using namespace tcp;
 
-constexpr int kChainThreads = 320;
-constexpr int kEpilogueThreads = 256;
+constexpr int kChainThreadsMin = 320;    // every variant has at least this many threads (set-up loops rely on >= 256)
 constexpr int kTileBytes = 128 * 128;   // one filter tile: 128 rows of 128 bytes
 
 struct ChainKernelParams {
@@ -96,8 +96,12 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-__global__ void __launch_bounds__(kChainThreads, 1)
+template <int E>   // epilogue warps per TMEM lane quarter
+__global__ void __launch_bounds__(64 + 128 * E, 1)
 conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_constant__ ChainKernelParams p) {
+    constexpr int kChainThreads = 64 + 128 * E;
+    constexpr int kEpilogueThreads = 128 * E;
+    static_assert(kChainThreads >= kChainThreadsMin, "set-up loops assume at least 320 threads");
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
@@ -247,7 +251,7 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
         // ---------------- epilogue: thread <-> accumulator lane <-> channel; the two warps of a lane
         // quarter take alternate 16-column chunks
         const int quarter = warp & 3;
-        const int half = (warp - 2) >> 2;
+        const int half = (warp - 2) >> 2;      // which of the quarter's E warps this is: it takes chunks half, half + E, ...
         const int ch = quarter * 32 + lane;
         const uint32_t lane_bits = (uint32_t)(quarter * 32) << 16;
         const int64_t img0 = (int64_t)blockIdx.x * p.per_cta;
@@ -275,7 +279,7 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
             if (ch >= p.head_begin[i] && ch < p.head_begin[i + 1]) head = i;
         // layer 0's input: from global memory into the operand layout and the held-tensor columns
         asm volatile("griddepcontrol.wait;" ::: "memory");
-        for (int c = half; c < chunks16; c += 2) {
+        for (int c = half; c < chunks16; c += E) {
             uint32_t v[16];
 #pragma unroll
             for (int j = 0; j < 16; j++) {
@@ -373,14 +377,14 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
                 // the kernel's speed depended on where unrelated code happened to be placed, measured)
                 if (half < chunks16) issue(half, va, ha);
 #pragma unroll 1
-                for (int c = half; c < chunks16; c += 4) {
+                for (int c = half; c < chunks16; c += 2 * E) {
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (c + 2 < chunks16) issue(c + 2, vb, hb);
+                    if (c + E < chunks16) issue(c + E, vb, hb);
                     finish(c, va, ha);
-                    if (c + 2 >= chunks16) break;
+                    if (c + E >= chunks16) break;
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (c + 4 < chunks16) issue(c + 4, va, ha);
-                    finish(c + 2, vb, hb);
+                    if (c + 2 * E < chunks16) issue(c + 2 * E, va, ha);
+                    finish(c + E, vb, hb);
                 }
                 if (hold) asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             }
@@ -452,6 +456,7 @@ struct ChainLaunch {
     ChainKernelParams p;
     dim3 grid;
     int smem_bytes;
+    int epilogue_warps;   // per lane quarter: the kernel variant
 };
 
 std::shared_ptr<void> chain_prepare(const ConvChainParams& c, uint32_t* status_word) {
@@ -515,6 +520,9 @@ std::shared_ptr<void> chain_prepare(const ConvChainParams& c, uint32_t* status_w
     l->map_tiles = tc_make_map(c.tiles, 3, dims, strides, box, true);
     l->grid = dim3((unsigned)((c.n + g.per_cta - 1) / g.per_cta), 1, 1);
     l->smem_bytes = g.smem_bytes;
+    // three epilogue warps per quarter share the chunks evenly when their number divides by three (two 8x8
+    // boards: 9 chunks, three each instead of five and four); otherwise two
+    l->epilogue_warps = ((g.n_mma / 16) % 3 == 0) ? 3 : 2;
     return l;
 }
 
@@ -527,7 +535,9 @@ int chain_launch(const void* launch, cudaStream_t stream) {
     {
         std::lock_guard<std::mutex> lock(mu);
         if (device >= 0 && device < 64 && !done[device]) {
-            cudaError_t e = cudaFuncSetAttribute(conv_chain_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            cudaError_t e = cudaFuncSetAttribute(conv_chain_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            if (e != cudaSuccess) return (int)e;
+            e = cudaFuncSetAttribute(conv_chain_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
             if (e != cudaSuccess) return (int)e;
             done[device] = true;
         }
@@ -535,7 +545,7 @@ int chain_launch(const void* launch, cudaStream_t stream) {
     if (l.grid.x == 0) return 0;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = l.grid;
-    cfg.blockDim = dim3(kChainThreads);
+    cfg.blockDim = dim3(64 + 128 * l.epilogue_warps);
     cfg.dynamicSmemBytes = (size_t)l.smem_bytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -543,7 +553,8 @@ int chain_launch(const void* launch, cudaStream_t stream) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return (int)cudaLaunchKernelEx(&cfg, conv_chain_kernel, l.map_tiles, l.p);
+    if (l.epilogue_warps == 3) return (int)cudaLaunchKernelEx(&cfg, conv_chain_kernel<3>, l.map_tiles, l.p);
+    return (int)cudaLaunchKernelEx(&cfg, conv_chain_kernel<2>, l.map_tiles, l.p);
 }
 
 }  // namespace kn

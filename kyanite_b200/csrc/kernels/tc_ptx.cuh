@@ -29,15 +29,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait.  Returns false if the kernel is being abandoned.
+// Bounded wait.  Returns false if the kernel is being abandoned: another role gave up, or this wait ran for
+// `limit` clock cycles, in which case it raises `*status` to `code` and sets the CTA's abandon flag.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abandon, uint32_t* status,
-                                          uint32_t code) {
+                                          uint32_t code, long long limit = kWaitCycles) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long start = clock64();
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
         if (*abandon) return false;
-        if (clock64() - start > kWaitCycles) {
+        if (clock64() - start > limit) {
             *abandon = 1;
             atomicMax(status, code);
             return false;

@@ -190,4 +190,7 @@ def test_heads_match_oracle_and_separate_kernels(name):
         for a, b in zip(fused, ex.evaluate([x])):
             np.testing.assert_array_equal(a, b)
     with CudaExecutor(0, g, batch, math_mode=MATH_TF32, flags=FLAG_NO_CONV_CHAIN) as ex:
-        assert_tensors_match(ex.evaluate([x]), fused, 1e-3, 1e-3, abs_scaled=True)
+        # Same operands and rounding points, another summation order: the logits differ by about 1e-3 of their
+        # scale (see test_chain_matches_oracle_and_per_layer_kernels), and a softmax turns an absolute logit
+        # difference into the same RELATIVE difference of its outputs, so those are held to 2.5e-3.
+        assert_tensors_match(ex.evaluate([x]), fused, 2.5e-3, 2.5e-3, abs_scaled=True)

@@ -72,10 +72,11 @@ def test_bert_base_full_size(mode):
     e2e_abs, _ = assert_tensors_match(expected, [g[rows] for g in got], tol, tol, abs_scaled=True)
     report = []
     worst_frac, _ = _layerwise(parsed, taps, position, got, rows, sub_inputs, tol, report)
-    # measured bounds, asserted so that a drift shows: one layer's error stays below 1e-3 of the tensor's scale
-    # in TF32 mode (2e-5 in exact f32), the compounded end-to-end error below 2e-2 absolute (1e-3 in f32)
-    assert worst_frac <= (1e-3 if mode == MATH_TF32 else 2e-5), report
-    assert e2e_abs <= (2e-2 if mode == MATH_TF32 else 1e-3), e2e_abs
+    # measured bounds, asserted so that a drift shows: one layer's error stays below 5e-4 of the tensor's scale
+    # in TF32 mode (1e-5 in exact f32), the compounded end-to-end error below 1e-2 absolute (1e-4 in f32)
+    # (measured on a B200: TF32 1.7e-4 per block and 2.6e-3 end to end; exact f32 1.1e-6 and 7.6e-6)
+    assert worst_frac <= (5e-4 if mode == MATH_TF32 else 1e-5), report
+    assert e2e_abs <= (1e-2 if mode == MATH_TF32 else 1e-4), e2e_abs
     print(f"bert full size mode={mode}: end-to-end max abs {e2e_abs:.3e}; worst block error / scale {worst_frac:.3e}")
 
 
@@ -95,9 +96,13 @@ def test_unet_full_size():
     # end to end on one of the 8 latents (one full oracle pass)
     expected = cpu_eval_graph(parsed, len(rows), sub_inputs)
     e2e_abs, _ = assert_tensors_match(expected, [g[rows] for g in got], tol, tol, abs_scaled=True)
+    final_abs, _ = assert_tensors_match(expected[:1], [got[0][rows]], tol, tol, abs_scaled=True)
+    final_scale = float(np.abs(expected[0]).max())
     report = []
     worst_frac, _ = _layerwise(parsed, taps, position, got, rows, sub_inputs, tol, report)
-    # measured bound for one block (up to 8 contractions with K up to 23 040 in it): error below 2e-3 of the
-    # block output's scale
-    assert worst_frac <= 2e-3, report
-    print(f"unet full size: end-to-end max abs {e2e_abs:.3e}; worst block error / scale {worst_frac:.3e}")
+    # measured bound for one block (up to 8 contractions with K up to 23 040 in it): error below 1.5e-3 of the
+    # block output's scale (measured on a B200: 4.4e-4); the denoised latent end to end within 2e-3 of its scale
+    assert worst_frac <= 1.5e-3, report
+    assert final_abs <= 2e-3 * final_scale, (final_abs, final_scale)
+    print(f"unet full size: end-to-end max abs {e2e_abs:.3e} over all block outputs; final output max abs {final_abs:.3e} "
+          f"on a scale of {final_scale:.3e}; worst block error / scale {worst_frac:.3e}")

@@ -190,3 +190,27 @@ def test_evaluate_in_two_halves_with_two_executors():
         with pytest.raises(KnError, match="in flight"):
             a.evaluate_staged_begin()
         assert_tensors_match(expected, [o.copy() for o in a.evaluate_staged_end()])
+
+
+def test_expired_wait_is_reported_and_the_executor_stays_usable():
+    """Every barrier wait in the tensor-core kernels is bounded.  Here one runs out on purpose, harmlessly
+    (kn_executor_selftest_wait_expiry: one thread, a barrier nobody arrives on, 1 ms limit, no tensor memory,
+    no copies in flight): the kernel returns, the status word reaches the host as KN_ERR_INTERNAL, the word is
+    cleared, and the executor computes the same results before and after, through the captured graph too."""
+    import time
+    from kyanite_b200 import _lib
+    case = next(c for c in CASES if c.name == "fuse_res")
+    expected = cpu_eval_graph(case.graph.to_bytes(), case.batch_size, case.inputs)
+    lib = _lib.load()
+    with CudaExecutor(0, case.graph, case.batch_size) as ex:
+        assert_tensors_match(expected, ex.evaluate(case.inputs), 4e-3, 4e-3, abs_scaled=True)
+        t0 = time.perf_counter()
+        status = lib.kn_executor_selftest_wait_expiry(ex._ptr, 1000)
+        elapsed = time.perf_counter() - t0
+        assert status == 7, lib.kn_last_error()            # KN_ERR_INTERNAL
+        assert b"gave up waiting" in lib.kn_last_error() and b"99" in lib.kn_last_error()
+        assert elapsed < 1.0                                # a 1 ms limit, not the 2 s default
+        ex.synchronize()                                    # the word was cleared: no stale error
+        for _ in range(2):
+            assert_tensors_match(expected, ex.evaluate(case.inputs), 4e-3, 4e-3, abs_scaled=True)
+        assert lib.kn_executor_selftest_wait_expiry(ex._ptr, 0) == 1      # limit out of range
