@@ -179,6 +179,35 @@ KN_API int kn_executor_last_profile(kn_executor* exec, char* buf, size_t cap, si
  * the event and launch gaps of a one-by-one run; this one does not.)  No reference counterpart. */
 KN_API int kn_executor_time_step(kn_executor* exec, int step, int launches, float* microseconds);
 
+/* Tensor-parallel graphs.  No counterpart in the reference, which runs one graph on one device.
+ *
+ * A graph may contain all-reduce values (operation tag 16 of the blob: one operand, same shape and dtype,
+ * f32 or f16): the element-wise sum of the operand over the ranks of a communicator, one rank = one
+ * process with its own executor on its own GPU, every rank running a graph with the same sequence of
+ * all-reduce values of the same sizes.  The planner turns each into a step of the step list and the
+ * executor hands the arena buffers to ncclAllReduce on its own stream, between the kernels before and
+ * after it; nothing crosses host memory.  Without a communicator (or with one rank) the step is a
+ * device-to-device copy.  With a communicator of several ranks the step list is launched step by step
+ * instead of being replayed from a captured CUDA graph.
+ *
+ * NCCL is bound at run time: the library opens `libnccl.so.2` itself (the copy already loaded into the
+ * process if there is one, else `path` of kn_nccl_load, else the dynamic loader's search path).
+ * kn_nccl_load is optional and idempotent.
+ *
+ * Setting up: rank 0 calls kn_comm_unique_id and sends the KN_COMM_ID_BYTES to every rank by any means
+ * (a file, a socket, MPI ...); every rank then calls kn_comm_create (collective: it returns once all
+ * `world` ranks have called it) and kn_executor_set_comm.  A communicator must outlive the executors
+ * that use it; several executors of one device may share one, as long as their evaluations do not
+ * overlap. */
+#define KN_COMM_ID_BYTES 128
+typedef struct kn_comm kn_comm;
+KN_API int kn_nccl_load(const char* path);
+KN_API int kn_comm_unique_id(void* id, size_t id_bytes);
+KN_API int kn_comm_create(int device, int rank, int world, const void* id, size_t id_bytes, kn_comm** out);
+KN_API void kn_comm_destroy(kn_comm* comm);
+/* Attaches `comm` (may be NULL: back to a world of one) to the executor.  Not while an evaluation is in flight. */
+KN_API int kn_executor_set_comm(kn_executor* exec, kn_comm* comm);
+
 /* Self-test of the bounded waits, with no counterpart in the reference.  Every barrier wait inside the
  * tensor-core kernels gives up after a cycle limit, raises the executor's status word and lets the
  * kernel return, and the next synchronising call reports KN_ERR_INTERNAL.  In normal operation no wait

@@ -63,6 +63,11 @@ SIGNATURES = {
     "kn_executor_set_profile": (c_int, [c_void_p, c_int]),
     "kn_executor_last_profile": (c_int, [c_void_p, c_void_p, c_size_t, POINTER(c_size_t)]),
     "kn_executor_time_step": (c_int, [c_void_p, c_int, c_int, POINTER(ctypes.c_float)]),
+    "kn_nccl_load": (c_int, [c_char_p]),
+    "kn_comm_unique_id": (c_int, [c_void_p, c_size_t]),
+    "kn_comm_create": (c_int, [c_int, c_int, c_int, c_void_p, c_size_t, POINTER(c_void_p)]),
+    "kn_comm_destroy": (None, [c_void_p]),
+    "kn_executor_set_comm": (c_int, [c_void_p, c_void_p]),
     "kn_executor_selftest_wait_expiry": (c_int, [c_void_p, c_uint32]),
     "kn_matmul_tf32_static": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p]),
     "kn_matmul_tf32_static_status": (c_int, [POINTER(c_int)]),

@@ -23,6 +23,7 @@ SOURCES = [
     "ir.cpp",
     "strided.cpp",
     "plan.cpp",
+    "comm.cpp",
     "executor.cu",
     "kernels/elementwise.cu",
     "kernels/rows.cu",

@@ -214,23 +214,47 @@ def bert_encoder(layers: int = 12, hidden: int = 768, heads: int = 12, ffn: int 
     return g, make_inputs
 
 
-def llama_weights(layers: int, d_model: int, heads: int, ffn: int, vocab: int, seed: int = 10) -> dict:
+def llama_weights(layers: int, d_model: int, heads: int, ffn: int, vocab: int, seed: int = 10,
+                  head_slice: slice = None, ffn_slice: slice = None, vocab_slice: slice = None,
+                  draw_slices_only: bool = False) -> dict:
     """The decoder's weights, N(0, 0.02) (norm gains 1 + N(0, 0.02)), drawn in a fixed order so that every
-    builder of the same model (whole, or one tensor-parallel rank's slice) sees the same numbers."""
+    builder of the same model (whole, or one tensor-parallel rank's slice) sees the same numbers.
+
+    With slices given (a tensor-parallel rank), the split matrices are returned already cut: W_q/W_k/W_v rows
+    and W_o columns of the heads in `head_slice`, gate/up rows and down columns of `ffn_slice`, lm-head rows of
+    `vocab_slice`.  Each matrix is still drawn whole and then cut, so the numbers equal the unpartitioned
+    model's, but only the slice is kept in memory.  `draw_slices_only` draws just the slice's worth of numbers
+    instead (8x less work for 8 ranks; the numbers then differ from the whole model's: for timing runs)."""
     seeds = _Seeds(seed)
-    w = {"table": _normal(seeds, (vocab, d_model)), "layers": []}
+    hd = d_model // heads
+    cols = slice(head_slice.start * hd, head_slice.stop * hd) if head_slice is not None else None
+
+    def matrix(rows_n, cols_n, row_slice=None, col_slice=None):
+        if draw_slices_only:
+            r = rows_n if row_slice is None else row_slice.stop - row_slice.start
+            c = cols_n if col_slice is None else col_slice.stop - col_slice.start
+            return _normal(seeds, (r, c))
+        m = _normal(seeds, (rows_n, cols_n))
+        if row_slice is not None:
+            m = np.ascontiguousarray(m[row_slice])
+        if col_slice is not None:
+            m = np.ascontiguousarray(m[:, col_slice])
+        return m
+
+    w = {"table": _normal(seeds, (vocab, d_model)), "layers": [], "sliced": head_slice is not None or ffn_slice is not None}
     for _ in range(layers):
         layer = {}
         layer["norm1"] = np.ones((1, 1, d_model), np.float32) + _normal(seeds, (1, 1, d_model))
-        for name in ("wq", "wk", "wv", "wo"):
-            layer[name] = _normal(seeds, (d_model, d_model))
+        for name in ("wq", "wk", "wv"):
+            layer[name] = matrix(d_model, d_model, row_slice=cols)
+        layer["wo"] = matrix(d_model, d_model, col_slice=cols)
         layer["norm2"] = np.ones((1, 1, d_model), np.float32) + _normal(seeds, (1, 1, d_model))
-        layer["gate"] = _normal(seeds, (ffn, d_model))
-        layer["up"] = _normal(seeds, (ffn, d_model))
-        layer["down"] = _normal(seeds, (d_model, ffn))
+        layer["gate"] = matrix(ffn, d_model, row_slice=ffn_slice)
+        layer["up"] = matrix(ffn, d_model, row_slice=ffn_slice)
+        layer["down"] = matrix(d_model, ffn, col_slice=ffn_slice)
         w["layers"].append(layer)
     w["norm_f"] = np.ones((1, 1, d_model), np.float32) + _normal(seeds, (1, 1, d_model))
-    w["lm_head"] = _normal(seeds, (vocab, d_model))
+    w["lm_head"] = matrix(vocab, d_model, row_slice=vocab_slice)
     return w
 
 
@@ -282,6 +306,8 @@ class LlamaBlocks:
         slice, the slices of all ranks sum to it (column-parallel Q/K/V, row-parallel O)."""
         g, hd = self.g, self.hd
         cols = slice(head_slice.start * hd, head_slice.stop * hd)
+        if layer["wq"].shape[0] == heads * hd:      # weights that `llama_weights` already cut for this rank
+            cols = slice(None)
         h = g.view(self.rmsnorm(x, layer["norm1"]), shape(self.rows, self.d_model))
         q = self.rope(self.linear(h, layer["wq"][cols]), heads)
         k = self.rope(self.linear(h, layer["wk"][cols]), heads)
@@ -293,6 +319,8 @@ class LlamaBlocks:
         """Pre-norm SwiGLU feed-forward over the hidden units in `ffn_slice`: [B, seq, d_model]
         (column-parallel gate/up, row-parallel down)."""
         g = self.g
+        if layer["gate"].shape[0] == ffn_slice.stop - ffn_slice.start:   # already cut for this rank
+            ffn_slice = slice(None)
         h = g.view(self.rmsnorm(x, layer["norm2"]), shape(self.rows, self.d_model))
         gate = self.linear(h, layer["gate"][ffn_slice])
         up = self.linear(h, layer["up"][ffn_slice])

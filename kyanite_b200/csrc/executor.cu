@@ -10,6 +10,7 @@
 #include <string>
 #include <vector>
 
+#include "comm.h"
 #include "ir.h"
 #include "kernels.h"
 #include "kn_b200.h"
@@ -78,6 +79,7 @@ struct Executor {
     bool profile = false;
     std::vector<float> step_us;
     int launches = 0;
+    Comm* comm = nullptr;              // not owned; AllReduce steps sum over its ranks (null: a world of one)
 
     ~Executor() {
         // the caller's current device is left as it was (a host may share the thread with other CUDA users)
@@ -155,6 +157,10 @@ struct Executor {
                     s.im2col.in = (const float*)ptr[0];
                     s.im2col.col = (float*)ptr[1];
                     break;
+                case StepKind::AllReduce:
+                    s.all_reduce.in = ptr[0];
+                    s.all_reduce.out = ptr[1];
+                    break;
                 case StepKind::ConvChain:
                     s.chain.in = (const float*)ptr[0];
                     s.chain.out = (float*)ptr[1];
@@ -181,6 +187,14 @@ struct Executor {
             case StepKind::Conv: err = s.tensor_core ? tc_launch_step(s, stream) : launch_conv_simt(s.conv, stream); break;
             case StepKind::ConvChain: err = tc_launch_step(s, stream); break;
             case StepKind::Im2col: err = launch_im2col(s.im2col, stream); break;
+            case StepKind::AllReduce: {
+                const AllReduceParams& a = s.all_reduce;
+                if (comm != nullptr && comm->world > 1)
+                    comm_all_reduce_sum(comm, a.in, a.out, (size_t)a.count, (DType)a.dtype, stream);
+                else   // one rank: the sum is the value
+                    err = (int)cudaMemcpyAsync(a.out, a.in, (size_t)a.count * dtype_size((DType)a.dtype), cudaMemcpyDeviceToDevice, stream);
+                break;
+            }
             default: fail(KN_ERR_INTERNAL, "unknown step kind");
         }
         if (err != 0)
@@ -213,7 +227,7 @@ struct Executor {
             for (auto& e : ev) cudaEventDestroy(e);
             return;
         }
-        if (plan->opts.use_cuda_graph) {
+        if (use_graph()) {
             if (!graph_exec) {
                 cudaGraph_t graph = nullptr;
                 KN_CUDA(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
@@ -234,6 +248,11 @@ struct Executor {
             for (const Step& s : plan->steps) launch_step(s);
         }
     }
+
+    // The step list is captured into a CUDA graph and replayed, except when it contains collectives that go
+    // through NCCL: those are enqueued call by call, so that a rank that fails between steps cannot leave a
+    // captured collective half-issued on the others.
+    bool use_graph() const { return plan->opts.use_cuda_graph && !(plan->collectives > 0 && comm != nullptr && comm->world > 1); }
 
     void upload_inputs() {
         for (size_t i = 0; i < pinned_in.size(); i++)
@@ -332,7 +351,7 @@ struct Executor {
             KN_CHECK(inputs != nullptr && (inputs[i] != nullptr || bytes_in[i] == 0), KN_ERR_INVALID_ARG, "null input buffer");
             if (bytes_in[i] && inputs[i] != pinned_in[i]) memcpy(pinned_in[i], inputs[i], bytes_in[i]);
         }
-        if (plan->opts.use_cuda_graph && !profile) {
+        if (use_graph() && !profile) {
             if (!eval_graph_exec) capture_evaluate();
             KN_CUDA(cudaGraphLaunch(eval_graph_exec, stream));
         } else {
@@ -424,6 +443,9 @@ struct kn_graph {
 };
 struct kn_executor {
     std::unique_ptr<kn::Executor> e;
+};
+struct kn_comm {
+    kn::Comm* c = nullptr;
 };
 
 namespace {
@@ -716,6 +738,48 @@ int kn_executor_time_step(kn_executor* exec, int step, int launches, float* micr
         }
         cudaEventDestroy(a);
         cudaEventDestroy(b);
+    });
+}
+
+int kn_nccl_load(const char* path) {
+    return guarded([&] { kn::nccl_load(path); });
+}
+
+int kn_comm_unique_id(void* id, size_t id_bytes) {
+    return guarded([&] {
+        KN_CHECK(id != nullptr && id_bytes == KN_COMM_ID_BYTES, KN_ERR_INVALID_ARG, "the id buffer must be KN_COMM_ID_BYTES long");
+        kn::comm_unique_id(id);
+    });
+}
+
+int kn_comm_create(int device, int rank, int world, const void* id, size_t id_bytes, kn_comm** out) {
+    return guarded([&] {
+        KN_CHECK(out != nullptr, KN_ERR_INVALID_ARG, "null out pointer");
+        *out = nullptr;
+        KN_CHECK(id != nullptr && id_bytes == KN_COMM_ID_BYTES, KN_ERR_INVALID_ARG, "the id buffer must be KN_COMM_ID_BYTES long");
+        kn::Comm* c = kn::comm_create(device, rank, world, id);
+        *out = new kn_comm{c};
+    });
+}
+
+void kn_comm_destroy(kn_comm* comm) {
+    if (!comm) return;
+    kn::comm_destroy(comm->c);
+    delete comm;
+}
+
+int kn_executor_set_comm(kn_executor* exec, kn_comm* comm) {
+    return guarded([&] {
+        KN_CHECK(exec != nullptr, KN_ERR_INVALID_ARG, "null executor");
+        kn::Executor& e = *exec->e;
+        KN_CHECK(!e.in_flight, KN_ERR_INVALID_ARG, "an evaluation is in flight");
+        KN_CHECK(comm == nullptr || comm->c->device == e.device, KN_ERR_INVALID_ARG, "communicator and executor are on different devices");
+        kn::DeviceGuard guard(e.device);
+        KN_CUDA(cudaStreamSynchronize(e.stream));
+        // graphs captured under the previous setting would replay the wrong kind of step
+        if (e.graph_exec) { cudaGraphExecDestroy(e.graph_exec); e.graph_exec = nullptr; }
+        if (e.eval_graph_exec) { cudaGraphExecDestroy(e.eval_graph_exec); e.eval_graph_exec = nullptr; }
+        e.comm = comm ? comm->c : nullptr;
     });
 }
 

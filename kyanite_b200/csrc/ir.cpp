@@ -16,8 +16,8 @@ const char* dtype_name(DType d) {
 
 const char* op_name(OpKind k) {
     static const char* names[] = {"Input", "Constant", "View", "Broadcast", "Permute", "Slice", "Flip", "Gather",
-                                  "Concat", "Conv", "MatMul", "Unary", "Binary", "Softmax", "Layernorm", "Reduce"};
-    return (int)k < 16 ? names[(int)k] : "?";
+                                  "Concat", "Conv", "MatMul", "Unary", "Binary", "Softmax", "Layernorm", "Reduce", "AllReduce"};
+    return (int)k < (int)OpKind::COUNT ? names[(int)k] : "?";
 }
 
 int64_t Size::eval(int64_t batch) const {
@@ -127,6 +127,11 @@ std::unique_ptr<Graph> Graph::parse(const void* bytes, size_t len) {
             }
             case OpKind::View: case OpKind::Broadcast:
                 info.inputs = {checked_operand(r, i)};
+                break;
+            case OpKind::AllReduce:
+                info.inputs = {checked_operand(r, i)};
+                KN_CHECK(g->values[info.inputs[0]].dtype == info.dtype && (info.dtype == DType::F32 || info.dtype == DType::F16),
+                         KN_ERR_BAD_GRAPH, "graph blob: all-reduce takes f32 or f16 and keeps the dtype");
                 break;
             case OpKind::Permute:
                 info.inputs = {checked_operand(r, i)};

@@ -8,9 +8,12 @@
 
 namespace kn {
 
+// 0..15 are the reference's `Operation` variants (kn-graph/src/graph.rs:106-162); AllReduce is an extension
+// for tensor-parallel graphs (the reference runs one graph on one device): the element-wise sum of the value
+// over the ranks of the communicator attached to the executor, the value itself when there is none.
 enum class OpKind : uint8_t {
     Input = 0, Constant, View, Broadcast, Permute, Slice, Flip, Gather, Concat, Conv, MatMul, Unary, Binary,
-    Softmax, Layernorm, Reduce, COUNT
+    Softmax, Layernorm, Reduce, AllReduce, COUNT
 };
 const char* op_name(OpKind k);
 

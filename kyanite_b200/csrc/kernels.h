@@ -170,6 +170,15 @@ struct Im2colParams {
     int64_t s_in[4];
 };
 
+// ---- sum of a dense tensor over the ranks of the executor's communicator (tensor-parallel graphs); no kernel of
+// this library: the executor hands the buffers to ncclAllReduce on its stream, or copies in -> out without one
+struct AllReduceParams {
+    const void* in;
+    void* out;
+    int64_t count;     // elements
+    uint8_t dtype;     // DType: F32 or F16
+};
+
 // All launchers enqueue on `stream` and return the cudaError_t of the launch as int.
 int launch_scalar(const ScalarParams& p, cudaStream_t stream);
 int launch_reduce(const ReduceParams& p, cudaStream_t stream);

@@ -14,7 +14,7 @@
 namespace kn {
 
 const char* step_kind_name(StepKind k) {
-    static const char* names[] = {"Scalar", "Reduce", "Softmax", "Layernorm", "Gather", "Gemm", "Conv", "ConvChain", "Im2col"};
+    static const char* names[] = {"Scalar", "Reduce", "Softmax", "Layernorm", "Gather", "Gemm", "Conv", "ConvChain", "Im2col", "AllReduce"};
     return (int)k < (int)StepKind::COUNT ? names[(int)k] : "?";
 }
 
@@ -528,6 +528,25 @@ class Planner {
             case OpKind::Softmax: return visit_softmax(v);
             case OpKind::Layernorm: return visit_layernorm(v);
             case OpKind::Reduce: return visit_reduce(v);
+            case OpKind::AllReduce: {
+                // the collective library wants dense buffers; the result is a buffer of its own, so the step is the
+                // same whether or not other steps still read the partial sum
+                PlanTensor in = ensure_simple(visit(info.inputs[0]), v);
+                PlanTensor out = alloc_shared(shape, info.dtype, v);
+                Step s;
+                s.kind = StepKind::AllReduce;
+                s.value = v;
+                s.operands = {in, out};
+                s.writes = {0, 1};
+                s.all_reduce.count = out.ss.size();
+                s.all_reduce.dtype = (uint8_t)info.dtype;
+                s.desc = "allreduce sum count=" + std::to_string(out.ss.size()) + " " + dtype_name(info.dtype);
+                if (out.ss.size() != 0) {
+                    push_step(std::move(s));
+                    plan_.collectives++;
+                }
+                return out;
+            }
             default: fail(KN_ERR_INTERNAL, "unknown operation");
         }
     }

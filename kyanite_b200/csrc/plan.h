@@ -46,7 +46,7 @@ struct PlanTensor {
 
 struct TcLaunch;   // tensor maps and launch geometry of a tensor-core step (kernels/contract_tc.cu)
 
-enum class StepKind : uint8_t { Scalar = 0, Reduce, Softmax, Layernorm, Gather, Gemm, Conv, ConvChain, Im2col, COUNT };
+enum class StepKind : uint8_t { Scalar = 0, Reduce, Softmax, Layernorm, Gather, Gemm, Conv, ConvChain, Im2col, AllReduce, COUNT };
 const char* step_kind_name(StepKind k);
 
 struct Step {
@@ -69,6 +69,7 @@ struct Step {
     ConvParams conv{};
     ConvChainParams chain{};
     Im2colParams im2col{};
+    AllReduceParams all_reduce{};
 };
 
 struct Plan {
@@ -80,6 +81,7 @@ struct Plan {
     std::vector<PlanTensor> outputs;   // dense, one per graph output
     std::vector<std::vector<int64_t>> input_shapes, output_shapes;
     size_t arena_bytes = 0, const_bytes = 0, zero_bytes = 0;
+    int collectives = 0;               // AllReduce steps
     kn_mem_usage mem{};
 
     std::string describe() const;

@@ -23,7 +23,7 @@ from . import _lib
 from ._lib import KnError, KnMemUsage, KnOptions, KnTensorInfo, check
 from .graph import DType, Graph
 
-__all__ = ["CudaDevice", "CudaDeviceNotAvailable", "CudaExecutor", "Device", "PreparedGraph", "MemoryUsage",
+__all__ = ["Communicator", "CudaDevice", "CudaDeviceNotAvailable", "CudaExecutor", "Device", "PreparedGraph", "MemoryUsage",
            "plan_describe", "KnError", "MATH_TF32", "MATH_F32", "FLAG_NO_CONV_CHAIN", "FLAG_NO_PERSISTENT_GEMM"]
 
 MATH_TF32 = _lib.KN_MATH_TF32
@@ -110,6 +110,58 @@ class MemoryUsage:
     zero_bytes: int
     hypo_peak_bytes: int
     hypo_total_bytes: int
+
+
+def bundled_nccl_path() -> Optional[str]:
+    """Path of the NCCL library that ships with the Python environment (the `nvidia-nccl` wheel), if any."""
+    import importlib.util
+    import os
+    spec = importlib.util.find_spec("nvidia")
+    for root in (spec.submodule_search_locations if spec and spec.submodule_search_locations else []):
+        path = os.path.join(root, "nccl", "lib", "libnccl.so.2")
+        if os.path.exists(path):
+            return path
+    return None
+
+
+class Communicator:
+    """One rank of an NCCL communicator for the all-reduce steps of tensor-parallel graphs
+    (kn_comm_unique_id / kn_comm_create).  Rank 0 makes the id with `Communicator.unique_id()` and the host
+    program sends the 128 bytes to the other ranks; every rank then constructs its `Communicator`, which
+    returns once all ranks have."""
+
+    def __init__(self, device: int, rank: int, world: int, unique_id: bytes):
+        self._lib = _lib.load()
+        self._ptr = c_void_p()
+        self.device, self.rank, self.world = int(device), int(rank), int(world)
+        Communicator.load_library()
+        buf = ctypes.create_string_buffer(bytes(unique_id), len(unique_id))
+        check(self._lib.kn_comm_create(self.device, self.rank, self.world, ctypes.cast(buf, c_void_p), len(unique_id),
+                                       byref(self._ptr)))
+
+    @staticmethod
+    def load_library(path: Optional[str] = None):
+        lib = _lib.load()
+        path = path or bundled_nccl_path()
+        check(lib.kn_nccl_load(path.encode() if path else None))
+
+    @staticmethod
+    def unique_id() -> bytes:
+        Communicator.load_library()
+        buf = ctypes.create_string_buffer(128)
+        check(_lib.load().kn_comm_unique_id(ctypes.cast(buf, c_void_p), 128))
+        return buf.raw
+
+    def close(self):
+        if getattr(self, "_ptr", None):
+            self._lib.kn_comm_destroy(self._ptr)
+            self._ptr = c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 class CudaExecutor:
@@ -244,6 +296,11 @@ class CudaExecutor:
             *[a.ctypes.data if a.size else None for a in self.host_outputs])
         check(self._lib.kn_executor_evaluate_end(self._ptr, out_ptrs))
         return self.host_outputs
+
+    def set_comm(self, comm: Optional["Communicator"]):
+        """Attaches the communicator the graph's all-reduce values sum over (None: a world of one rank)."""
+        check(self._lib.kn_executor_set_comm(self._ptr, comm._ptr if comm is not None else None))
+        self._comm = comm   # keep it alive as long as the executor uses it
 
     def upload_inputs(self):
         check(self._lib.kn_executor_upload_inputs(self._ptr))

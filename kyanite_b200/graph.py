@@ -291,6 +291,7 @@ class OpKind(enum.IntEnum):
     SOFTMAX = 13
     LAYERNORM = 14
     REDUCE = 15
+    ALL_REDUCE = 16    # extension (no counterpart in the reference): sum over the ranks of a communicator
 
 
 @dataclass(frozen=True)
@@ -813,6 +814,15 @@ class Graph:
         new_shape = tuple(dim for i, dim in enumerate(s) if i not in axes)
         return self._push(ValueInfo(new_shape, d, OpKind.REDUCE, inputs=(input.index,), axes=axes, reduce_op=op))
 
+    def all_reduce(self, input: Value) -> Value:
+        """Extension for tensor-parallel graphs (the reference runs one graph on one device): the element-wise
+        sum of `input` over the ranks of the communicator attached to the executor; the value itself when
+        there is none.  f32 or f16."""
+        s, d = self.shape_dtype(input)
+        if d not in (DType.F32, DType.F16):
+            raise ValueError(f"all_reduce takes f32 or f16, got {d}")
+        return self._push(ValueInfo(s, d, OpKind.ALL_REDUCE, inputs=(input.index,)))
+
     # ---------------------------------------------------------------- elementwise
     def sigmoid(self, input: Value) -> Value:
         return self.unary(UnaryOp.SIGMOID, input)
@@ -922,7 +932,7 @@ class Graph:
         value : u8 op, u8 dtype, u16 rank, rank x (u64 factor, u32 batch_exp), then per op:
           INPUT      u32 index
           CONSTANT   u64 byte_count, raw data
-          VIEW/BROADCAST  u32 input
+          VIEW/BROADCAST/ALL_REDUCE  u32 input
           PERMUTE    u32 input, rank x u32
           SLICE      u32 input, u32 axis, u64 start, u64 end, u64 step
           FLIP       u32 input, u32 axis
@@ -960,7 +970,7 @@ class Graph:
                     out = bytearray()
                 else:
                     out += raw.tobytes()
-            elif k in (OpKind.VIEW, OpKind.BROADCAST):
+            elif k in (OpKind.VIEW, OpKind.BROADCAST, OpKind.ALL_REDUCE):
                 out += struct.pack("<I", info.inputs[0])
             elif k == OpKind.PERMUTE:
                 out += struct.pack("<I", info.inputs[0])

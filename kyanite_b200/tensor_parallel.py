@@ -1,8 +1,10 @@
 """Tensor-parallel execution of the LLaMA-shaped decoder: one process per GPU, NCCL all-reduce after the
-row-parallel projections.  This has no counterpart in the reference (which runs one graph on one device);
-it is built on top of the executor, not inside it: every rank runs ordinary graphs through `CudaExecutor`,
-and the only cross-rank operations are one all-reduce per attention block and per feed-forward block and
-one all-gather of the logits.
+row-parallel projections.  This has no counterpart in the reference (which runs one graph on one device).
+Every rank runs ONE graph (`llama_rank_graph`) through one `CudaExecutor`; the all-reduce after each
+attention block and each feed-forward block is a value of that graph (`Graph.all_reduce`), which the executor
+runs as a step of its step list: the arena buffer goes to ncclAllReduce on the executor's stream, between the
+kernels before and after it, with nothing crossing host memory.  Only the final all-gather of the logits
+(once per prefill, each rank holds a vocabulary slice) is done by the host.
 
 Partitioning (world size W, rank r):
 * attention: heads `[r*H/W, (r+1)*H/W)`.  W_q, W_k, W_v are split by output rows (column-parallel), RoPE,
@@ -13,7 +15,9 @@ Partitioning (world size W, rank r):
 * RMSNorm, the residual stream, the embedding table and the final norm are replicated;
 * lm head: vocabulary rows `[r*V/W, (r+1)*V/W)`, logits all-gathered along the vocabulary axis.
 
-The decoder is cut into `2 * layers + 1` graph segments at the all-reduce points.  Segment k takes the
+`llama_segments` is the same partition cut into `2 * layers + 1` separate graphs at the all-reduce points, so
+that the slices of several ranks can be checked on ONE device (the tests play the collective on the host
+between segments); it is not the execution path.  Segment k takes the
 residual stream `x` and the reduced sum `s` of the previous block, forms `x + s` (replicated arithmetic,
 bit-identical on every rank) and returns it together with this rank's partial sum of the next block:
 
@@ -32,7 +36,8 @@ import numpy as np
 from .configs import LlamaBlocks, llama_weights
 from .graph import BATCH, DType, Graph, shape
 
-__all__ = ["LlamaShape", "llama_segments", "TorchComm", "LocalComm", "TensorParallelLlama"]
+__all__ = ["LlamaShape", "llama_rank_graph", "llama_segments", "TorchComm", "LocalComm", "TensorParallelLlama",
+           "cuda_prepare"]
 
 
 @dataclass(frozen=True)
@@ -53,6 +58,29 @@ def _even_slice(total: int, rank: int, world: int, what: str) -> slice:
         raise ValueError(f"{what} ({total}) is not divisible by the tensor-parallel size {world}")
     step = total // world
     return slice(rank * step, (rank + 1) * step)
+
+
+def llama_rank_graph(cfg: LlamaShape, rank: int, world: int, draw_slices_only: bool = False) -> Graph:
+    """The one graph rank `rank` of `world` runs: token ids [B, seq] -> this rank's vocabulary slice of the
+    logits [B, seq, vocab / world], with an all-reduce value after every row-parallel projection
+    (2 * layers of them, each [B, seq, d_model]).  `draw_slices_only`: see `llama_weights` (timing runs)."""
+    if not (0 <= rank < world):
+        raise ValueError(f"rank {rank} outside world of size {world}")
+    head_slice = _even_slice(cfg.heads, rank, world, "head count")
+    ffn_slice = _even_slice(cfg.ffn, rank, world, "feed-forward width")
+    vocab_slice = _even_slice(cfg.vocab, rank, world, "vocabulary")
+    w = llama_weights(cfg.layers, cfg.d_model, cfg.heads, cfg.ffn, cfg.vocab, cfg.seed, head_slice=head_slice,
+                      ffn_slice=ffn_slice, vocab_slice=vocab_slice, draw_slices_only=draw_slices_only)
+    local_heads = head_slice.stop - head_slice.start
+    g = Graph()
+    blocks = LlamaBlocks(g, cfg.d_model, cfg.d_model // cfg.heads, cfg.seq, cfg.eps, cfg.rope_base)
+    ids = g.input(shape(BATCH, cfg.seq), DType.I32)
+    x = g.view(g.gather(g.constant_tensor(w["table"]), 0, g.flatten(ids, 0)), shape(BATCH, cfg.seq, cfg.d_model))
+    for layer in w["layers"]:
+        x = g.add(x, g.all_reduce(blocks.attention_partial(x, layer, head_slice, local_heads)))
+        x = g.add(x, g.all_reduce(blocks.ffn_partial(x, layer, ffn_slice)))
+    g.output(blocks.logits(x, w["norm_f"], w["lm_head"]))
+    return g
 
 
 def llama_segments(cfg: LlamaShape, rank: int, world: int) -> List[Graph]:
@@ -104,6 +132,7 @@ def llama_segments(cfg: LlamaShape, rank: int, world: int) -> List[Graph]:
 class LocalComm:
     """World of size 1: the collectives are identities."""
     rank, world = 0, 1
+    device_comm = None
 
     def all_reduce_sum(self, a: np.ndarray) -> np.ndarray:
         return a
@@ -113,8 +142,11 @@ class LocalComm:
 
 
 class TorchComm:
-    """Collectives through an initialised `torch.distributed` process group: NCCL when `device` is a CUDA
-    device (the arrays cross to that GPU, are reduced over NVLink and come back), gloo on CPU."""
+    """The host side of a rank, over an initialised `torch.distributed` process group (gloo on CPU, NCCL on
+    GPUs): carries the communicator id to the ranks, gathers the logits once per prefill, and, for the CPU
+    tests, plays the all-reduce for the oracle.  With a CUDA `device`, `device_comm` is the executor's own NCCL
+    communicator (kyanite_b200.executor.Communicator), created from an id that rank 0 makes and this process
+    group broadcasts."""
 
     def __init__(self, device: Optional[str] = None):
         import torch
@@ -124,6 +156,13 @@ class TorchComm:
         self.torch, self.dist = torch, dist
         self.rank, self.world = dist.get_rank(), dist.get_world_size()
         self.device = torch.device(device) if device is not None else torch.device("cpu")
+        self.device_comm = None
+        if self.device.type == "cuda":
+            from .executor import Communicator
+            box = [Communicator.unique_id() if self.rank == 0 else None]
+            dist.broadcast_object_list(box, src=0)
+            index = self.device.index if self.device.index is not None else torch.cuda.current_device()
+            self.device_comm = Communicator(index, self.rank, self.world, box[0])
 
     def all_reduce_sum(self, a: np.ndarray) -> np.ndarray:
         t = self.torch.from_numpy(np.ascontiguousarray(a)).to(self.device)
@@ -136,36 +175,49 @@ class TorchComm:
         self.dist.all_gather(parts, t)
         return self.torch.cat(parts, dim=-1).cpu().numpy()
 
+    def close(self):
+        if self.device_comm is not None:
+            self.device_comm.close()
+            self.device_comm = None
+
 
 class TensorParallelLlama:
     """One rank of the tensor-parallel decoder.
 
-    `prepare(graph, batch_size)` returns a callable `inputs -> outputs` for one segment: on a GPU
-    `lambda g, b: CudaExecutor(device, g, b).evaluate`; tests on CPU pass an evaluator of their own."""
+    `prepare(graph, batch_size, comm)` returns a callable `inputs -> outputs` for the rank's graph: on a GPU
+    `cuda_prepare(device)`, which builds a `CudaExecutor` and attaches `comm.device_comm`; tests on CPU pass an
+    evaluator that runs the oracle with `comm.all_reduce_sum` as the collective."""
 
-    def __init__(self, cfg: LlamaShape, batch_size: int, comm, prepare: Callable[[Graph, int], Callable]):
+    def __init__(self, cfg: LlamaShape, batch_size: int, comm, prepare: Callable):
         self.cfg, self.batch_size, self.comm = cfg, batch_size, comm
-        self.segments = [prepare(g, batch_size) for g in llama_segments(cfg, comm.rank, comm.world)]
-        self.all_reduces = 0
+        self.graph = llama_rank_graph(cfg, comm.rank, comm.world)
+        self.run = prepare(self.graph, batch_size, comm)
+        self.all_reduces = 2 * cfg.layers
+
+    def forward_local(self, ids: np.ndarray) -> np.ndarray:
+        """Token ids [B, seq] (identical on every rank) -> this rank's slice of the logits."""
+        (local_logits,) = self.run([np.ascontiguousarray(ids, dtype=np.int32)])
+        return local_logits
 
     def forward(self, ids: np.ndarray) -> np.ndarray:
         """Token ids [B, seq] (identical on every rank) -> logits [B, seq, vocab] (identical on every rank)."""
-        x, partial = self.segments[0]([np.ascontiguousarray(ids, dtype=np.int32)])
-        for seg in self.segments[1:-1]:
-            s = self.comm.all_reduce_sum(partial)
-            self.all_reduces += 1
-            x, partial = seg([x, s])
-        s = self.comm.all_reduce_sum(partial)
-        self.all_reduces += 1
-        (local_logits,) = self.segments[-1]([x, s])
-        return self.comm.all_gather_last_axis(local_logits)
+        return self.comm.all_gather_last_axis(self.forward_local(ids))
 
 
-def cuda_prepare(device_index: int, **executor_kwargs) -> Callable[[Graph, int], Callable]:
-    """`prepare` for `TensorParallelLlama` on CUDA device `device_index`."""
+def cuda_prepare(device_index: int, **executor_kwargs) -> Callable:
+    """`prepare` for `TensorParallelLlama` (and for single segments: `comm` may be omitted) on CUDA device
+    `device_index`.  The executor is reachable as `.executor` of the returned callable."""
     from .executor import CudaExecutor
 
-    def prepare(graph: Graph, batch_size: int):
-        return CudaExecutor(device_index, graph, batch_size, **executor_kwargs).evaluate
+    def prepare(graph: Graph, batch_size: int, comm=None):
+        ex = CudaExecutor(device_index, graph, batch_size, **executor_kwargs)
+        if comm is not None and getattr(comm, "device_comm", None) is not None:
+            ex.set_comm(comm.device_comm)
+
+        def run(inputs):
+            return ex.evaluate(inputs)
+
+        run.executor = ex
+        return run
 
     return prepare

@@ -30,6 +30,7 @@ import numpy as np
 # tags of the wire format
 (OP_INPUT, OP_CONSTANT, OP_VIEW, OP_BROADCAST, OP_PERMUTE, OP_SLICE, OP_FLIP, OP_GATHER, OP_CONCAT, OP_CONV,
  OP_MATMUL, OP_UNARY, OP_BINARY, OP_SOFTMAX, OP_LAYERNORM, OP_REDUCE) = range(16)
+OP_ALL_REDUCE = 16   # extension of this repository's IR for tensor-parallel graphs (not in the reference)
 
 NP_DTYPES = [np.float32, np.float64, np.int8, np.int16, np.int32, np.int64, np.uint8, np.uint16, np.uint32,
              np.uint64, np.bool_, np.float16]
@@ -94,7 +95,7 @@ def parse_graph(blob: bytes) -> ParsedGraph:
             n = r.take("<Q")[0]
             dims = [f for f, _ in shape]
             node.attr["tensor"] = np.frombuffer(r.raw(n), dtype=NP_DTYPES[dtype]).reshape(dims)
-        elif op in (OP_VIEW, OP_BROADCAST):
+        elif op in (OP_VIEW, OP_BROADCAST, OP_ALL_REDUCE):
             node.inputs = [r.take("<I")[0]]
         elif op == OP_PERMUTE:
             node.inputs = [r.take("<I")[0]]
@@ -397,7 +398,7 @@ def gather(x: np.ndarray, axis: int, indices: np.ndarray) -> np.ndarray:
 # graph evaluation
 # --------------------------------------------------------------------------------------
 def cpu_eval_graph(blob, batch_size: int, inputs: Sequence[np.ndarray], keep_all: bool = False,
-                   overrides: Optional[dict] = None, wanted: Optional[Sequence[int]] = None):
+                   overrides: Optional[dict] = None, wanted: Optional[Sequence[int]] = None, all_reduce=None):
     """Evaluate the graph on the CPU (cpu.rs:20-98).  Returns the list of outputs, each a
     C-contiguous array (cpu.rs:526-535); with `keep_all` also returns every intermediate.
 
@@ -405,7 +406,10 @@ def cpu_eval_graph(blob, batch_size: int, inputs: Sequence[np.ndarray], keep_all
     differentially too, kn-cuda-eval/tests/root/runner.rs:29-55): `overrides` maps value indices to arrays
     that stand in for those values (another executor's result for the layer's input, say) and `wanted`
     lists the value indices to return instead of the graph's outputs.  Only values that `wanted` depends
-    on, up to the overridden ones, are computed; graph inputs nothing needs may be passed as None."""
+    on, up to the overridden ones, are computed; graph inputs nothing needs may be passed as None.
+
+    `all_reduce(array) -> array` plays the all-reduce values of a tensor-parallel graph (an extension of this
+    repository's IR): the sum over the ranks.  Without it the graph is evaluated as a world of one rank."""
     g = blob if isinstance(blob, ParsedGraph) else parse_graph(blob)
     if len(inputs) != len(g.inputs):
         raise ValueError(f"expected {len(g.inputs)} inputs, got {len(inputs)}")
@@ -477,6 +481,8 @@ def cpu_eval_graph(blob, batch_size: int, inputs: Sequence[np.ndarray], keep_all
             res = softmax(a[0], node.attr["axis"])
         elif op == OP_LAYERNORM:
             res = layernorm(a[0], node.attr["axis"], node.attr["eps"])
+        elif op == OP_ALL_REDUCE:
+            res = np.ascontiguousarray(a[0]) if all_reduce is None else np.asarray(all_reduce(np.ascontiguousarray(a[0])))
         elif op == OP_REDUCE:
             cur = a[0]
             for axis in node.attr["axes"]:
