@@ -68,6 +68,10 @@ typedef struct kn_options {
 /* matrix multiplies use the one-tile-per-CTA kernel instead of the persistent one (A/B comparison and tests) */
 #define KN_FLAG_NO_PERSISTENT_GEMM 2
 
+/* post-mortem aid: the persistent matmul kernel records how far its roles got in pinned host memory, and a CUDA
+   failure reported by kn_executor_evaluate / _end carries those markers in its message */
+#define KN_FLAG_TRACE_GEMM 4
+
 #define KN_MAX_RANK 8
 
 typedef struct kn_tensor_info {
@@ -258,6 +262,18 @@ KN_API int kn_matmul_tf32_static(const float* a, const float* b, float* c, int64
  * that expired (the affected C is then incomplete: run the call again); the word is cleared.  Reads
  * the CURRENT device's word with a 4-byte copy; allocates nothing. */
 KN_API int kn_matmul_tf32_static_status(int* code);
+
+/* Host-only: the shape / stride algebra every view-like operation of the planner goes through (the reference's
+ * `StridedShape`, kn-cuda-eval/src/shape.rs:11-344), exported so that its rules can be tested as numbers.
+ * Strides are in elements and may be zero (broadcast) or negative (flip).
+ *   op 0  nothing (flags of the input)          op 3  flip(axis)             args = {axis}
+ *   op 1  view(new shape)  args = new shape     op 4  permute(permutation)   args = permutation
+ *   op 2  slice(axis, start, end, step)         op 5  broadcast(new shape)   args = new shape
+ * The result (at most 16 axes) goes to out_rank / out_shape / out_strides, `*simple` and `*dense` receive
+ * the result's has_simple_strides / has_dense_strides flags (shape.rs:34-72).  A view that needs a copy returns
+ * KN_ERR_SHAPE (the reference's `ViewError`). */
+KN_API int kn_strided_shape(int op, int rank, const int64_t* shape, const int64_t* strides, int n_args, const int64_t* args,
+                            int* out_rank, int64_t* out_shape, int64_t* out_strides, int* simple, int* dense);
 
 /* Host-only element semantics, exported so the scalar rules can be tested without a device:
  * applies one unary / binary operation to 64-bit canonical element patterns. */

@@ -19,6 +19,7 @@ KN_MATH_TF32 = 0
 KN_MATH_F32 = 1
 KN_FLAG_NO_CONV_CHAIN = 1
 KN_FLAG_NO_PERSISTENT_GEMM = 2
+KN_FLAG_TRACE_GEMM = 4
 
 
 class KnOptions(Structure):
@@ -71,6 +72,8 @@ SIGNATURES = {
     "kn_executor_selftest_wait_expiry": (c_int, [c_void_p, c_uint32]),
     "kn_matmul_tf32_static": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p]),
     "kn_matmul_tf32_static_status": (c_int, [POINTER(c_int)]),
+    "kn_strided_shape": (c_int, [c_int, c_int, POINTER(c_int64), POINTER(c_int64), c_int, POINTER(c_int64), POINTER(c_int),
+                                 POINTER(c_int64), POINTER(c_int64), POINTER(c_int), POINTER(c_int)]),
     "kn_scalar_unary": (c_int, [c_int, c_int, c_int, c_uint64, POINTER(c_uint64)]),
     "kn_scalar_binary": (c_int, [c_int, c_int, c_uint64, c_uint64, POINTER(c_uint64)]),
 }

@@ -27,6 +27,7 @@ SOURCES = [
     "executor.cu",
     "kernels/elementwise.cu",
     "kernels/rows.cu",
+    "kernels/rows_f16.cu",
     "kernels/gather.cu",
     "kernels/contract_simt.cu",
     "kernels/contract_tc.cu",

@@ -153,7 +153,7 @@ def _layernorm_affine(g: Graph, x: Value, axis: int, eps: float, gamma: np.ndarr
 
 
 def _attention(g: Graph, q: Value, k: Value, v: Value, rows_q, rows_kv, heads: int, head_dim: int, batch,
-               mask: Value = None) -> Value:
+               mask: Value = None, dtype: DType = DType.F32) -> Value:
     """q [B*Sq, h*d], k/v [B*Skv, h*d] -> [B*Sq, h*d]; scores are materialised (the IR has no attention op)."""
     sq, skv = rows_q, rows_kv
 
@@ -164,7 +164,7 @@ def _attention(g: Graph, q: Value, k: Value, v: Value, rows_q, rows_kv, heads: i
 
     qh, kh, vh = split(q, sq), split(k, skv), split(v, skv)
     scores = g.batched_mat_mul(qh, g.permute(kh, [0, 2, 1]))
-    scores = g.mul(scores, g.scalar(1.0 / math.sqrt(head_dim)))
+    scores = g.mul(scores, g.scalar(1.0 / math.sqrt(head_dim), dtype))
     if mask is not None:
         scores = g.add(scores, mask)
     probs = g.softmax(scores, 2)
@@ -271,23 +271,30 @@ class LlamaBlocks:
     """The pieces of the LLaMA-shaped decoder as graph fragments, shared by `llama_decoder` and by the
     tensor-parallel builder (kyanite_b200/tensor_parallel.py), which uses them on weight slices."""
 
-    def __init__(self, g: Graph, d_model: int, head_dim: int, seq: int, eps: float, rope_base: float):
-        self.g, self.d_model, self.hd, self.seq, self.eps = g, d_model, head_dim, seq, eps
+    def __init__(self, g: Graph, d_model: int, head_dim: int, seq: int, eps: float, rope_base: float,
+                 dtype: DType = DType.F32):
+        """`dtype`: the storage type of activations and weights, F32 or F16.  With F16 every value of the graph is
+        f16 except inside RMSNorm, whose statistics are computed on f32 casts (as half-precision decoders do) and
+        whose result is cast back."""
+        self.g, self.d_model, self.hd, self.seq, self.eps, self.dtype = g, d_model, head_dim, seq, eps, dtype
         cos, sin = rope_tables(seq, head_dim, rope_base)
-        self.cos, self.sin = g.constant_tensor(cos), g.constant_tensor(sin)
-        self.mask = g.constant_tensor(np.triu(np.full((seq, seq), -np.inf, np.float32), 1).reshape(1, seq, seq))
+        self.cos, self.sin = g.constant_tensor(cos.astype(dtype.np)), g.constant_tensor(sin.astype(dtype.np))
+        self.mask = g.constant_tensor(np.triu(np.full((seq, seq), -np.inf, dtype.np), 1).reshape(1, seq, seq))
         self.rows = BATCH * seq
 
     def linear(self, x: Value, w: np.ndarray) -> Value:
-        return self.g.linear(x, self.g.constant_tensor(np.ascontiguousarray(w)))
+        return self.g.linear(x, self.g.constant_tensor(np.ascontiguousarray(w, dtype=self.dtype.np)))
 
     def rmsnorm(self, t: Value, gain: np.ndarray) -> Value:
         """t [B, seq, d_model]: composed from pow / mean / sqrt / div (the IR has no RMSNorm)."""
         from .graph import BinaryOp, ReduceOp, UnaryOp
         g = self.g
+        if self.dtype != DType.F32:
+            t = g.value_cast(t, DType.F32)
         ms = g.view(g.reduce(g.pow(t, g.scalar(2.0)), [2], ReduceOp.MEAN), shape(BATCH, self.seq, 1))
         rms = g.unary(UnaryOp.SQRT, g.add(ms, g.scalar(self.eps)))
-        return g.mul(g.binary(BinaryOp.DIV, t, rms), g.constant_tensor(gain))
+        out = g.mul(g.binary(BinaryOp.DIV, t, rms), g.constant_tensor(gain))
+        return out if self.dtype == DType.F32 else g.value_cast(out, self.dtype)
 
     def rope(self, t: Value, heads: int) -> Value:
         """t [B*seq, heads*hd] -> rotated, same shape (half-split: pairs (i, i + hd/2))."""
@@ -312,7 +319,7 @@ class LlamaBlocks:
         q = self.rope(self.linear(h, layer["wq"][cols]), heads)
         k = self.rope(self.linear(h, layer["wk"][cols]), heads)
         v = self.linear(h, layer["wv"][cols])
-        ctx = _attention(g, q, k, v, self.seq, self.seq, heads, hd, BATCH, mask=self.mask)
+        ctx = _attention(g, q, k, v, self.seq, self.seq, heads, hd, BATCH, mask=self.mask, dtype=self.dtype)
         return g.view(self.linear(ctx, layer["wo"][:, cols]), shape(BATCH, self.seq, self.d_model))
 
     def ffn_partial(self, x: Value, layer: dict, ffn_slice: slice) -> Value:
@@ -333,18 +340,27 @@ class LlamaBlocks:
 
 
 def llama_decoder(layers: int = 32, d_model: int = 4096, heads: int = 32, ffn: int = 11008, vocab: int = 32000,
-                  seq: int = 2048, eps: float = 1e-6, rope_base: float = 10000.0, seed: int = 10) -> Tuple[Graph, Inputs]:
-    """LLaMA-shaped decoder prefill in f32 (half storage is not built): RMSNorm composed from
-    pow / mean / sqrt / div, rotary embedding from constant cos/sin tables with half-split slices,
-    additive causal mask, SwiGLU, tied-shape lm head.  Input: token ids [B, seq] (i32)."""
+                  seq: int = 2048, eps: float = 1e-6, rope_base: float = 10000.0, seed: int = 10,
+                  dtype: DType = DType.F32, taps: list = None) -> Tuple[Graph, Inputs]:
+    """LLaMA-shaped decoder prefill: RMSNorm composed from pow / mean / sqrt / div, rotary embedding from
+    constant cos/sin tables with half-split slices, additive causal mask, SwiGLU, tied-shape lm head.
+    Input: token ids [B, seq] (i32).  `dtype` F32, or F16 for half storage with f32 accumulation (weights,
+    activations and logits f16; see `LlamaBlocks`).  `taps` receives (name, value) for the embedding and every
+    block's output."""
     g = Graph()
     w = llama_weights(layers, d_model, heads, ffn, vocab, seed)
-    blocks = LlamaBlocks(g, d_model, d_model // heads, seq, eps, rope_base)
+    blocks = LlamaBlocks(g, d_model, d_model // heads, seq, eps, rope_base, dtype)
     ids = g.input(shape(BATCH, seq), DType.I32)
-    x = g.view(g.gather(g.constant_tensor(w["table"]), 0, g.flatten(ids, 0)), shape(BATCH, seq, d_model))
-    for layer in w["layers"]:
+    x = g.view(g.gather(g.constant_tensor(w["table"].astype(dtype.np)), 0, g.flatten(ids, 0)), shape(BATCH, seq, d_model))
+    if taps is not None:
+        taps.append(("embedding", x))
+    for li, layer in enumerate(w["layers"]):
         x = g.add(x, blocks.attention_partial(x, layer, slice(0, heads), heads))
+        if taps is not None:
+            taps.append((f"layer{li}.attention", x))
         x = g.add(x, blocks.ffn_partial(x, layer, slice(0, ffn)))
+        if taps is not None:
+            taps.append((f"layer{li}.ffn", x))
     g.output(blocks.logits(x, w["norm_f"], w["lm_head"]))
 
     def make_inputs(batch_size: int, seed: int = 1):

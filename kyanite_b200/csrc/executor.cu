@@ -170,7 +170,8 @@ struct Executor {
                     break;
                 default: fail(KN_ERR_INTERNAL, "unknown step kind");
             }
-            if (s.tensor_core) tc_prepare_step(s, status_dev, plan->opts.flags);
+            if (s.tensor_core)
+                tc_prepare_step(s, status_dev, plan->opts.flags, (plan->opts.flags & KN_FLAG_TRACE_GEMM) ? status_host + 4 : nullptr);
             launches += s.launches;
         }
     }
@@ -365,7 +366,15 @@ struct Executor {
     void evaluate_end(void* const* outputs) {
         KN_CHECK(in_flight, KN_ERR_INVALID_ARG, "evaluate_end without evaluate_begin");
         in_flight = false;
-        KN_CUDA(cudaStreamSynchronize(stream));
+        {
+            cudaError_t done = cudaStreamSynchronize(stream);
+            if (done != cudaSuccess && (plan->opts.flags & KN_FLAG_TRACE_GEMM)) {
+                std::string m = std::string("cudaStreamSynchronize failed: ") + cudaGetErrorString(done) + "; matmul progress markers:";
+                for (int i = 0; i < 8; i++) m += " " + std::to_string(status_host[4 + i]);
+                fail(KN_ERR_CUDA, m);
+            }
+            KN_CUDA(done);
+        }
         check_status();
         for (size_t i = 0; i < pinned_out.size(); i++) {
             KN_CHECK(outputs != nullptr && (outputs[i] != nullptr || bytes_out[i] == 0), KN_ERR_INVALID_ARG, "null output buffer");
@@ -396,8 +405,8 @@ static std::unique_ptr<Executor> create_executor(int device, const Graph& graph,
     KN_CUDA(cudaMalloc((void**)&ex->consts, std::max<size_t>(plan.const_bytes, 256)));
     KN_CUDA(cudaMalloc((void**)&ex->status_dev, 256));
     KN_CUDA(cudaMemset(ex->status_dev, 0, 256));
-    KN_CUDA(cudaHostAlloc((void**)&ex->status_host, 16, cudaHostAllocDefault));
-    *ex->status_host = 0;
+    KN_CUDA(cudaHostAlloc((void**)&ex->status_host, 64, cudaHostAllocDefault));
+    memset(ex->status_host, 0, 64);   // word 0: status mirror; words 4..11: matmul progress markers (KN_FLAG_TRACE_GEMM)
     if (plan.const_bytes) {
         // constants cross to the device once, here (kn-cuda-eval/src/planner.rs:331-344)
         std::vector<uint8_t> staging(plan.const_bytes, 0);
@@ -798,6 +807,66 @@ int kn_executor_selftest_wait_expiry(kn_executor* exec, uint32_t limit_us) {
         KN_CUDA(cudaMemcpyAsync(e.status_host, e.status_dev, 4, cudaMemcpyDeviceToHost, e.stream));
         KN_CUDA(cudaStreamSynchronize(e.stream));
         e.check_status();   // throws KN_ERR_INTERNAL: the expected outcome
+    });
+}
+
+int kn_strided_shape(int op, int rank, const int64_t* shape, const int64_t* strides, int n_args, const int64_t* args, int* out_rank,
+                     int64_t* out_shape, int64_t* out_strides, int* simple, int* dense) {
+    return guarded([&] {
+        KN_CHECK(rank >= 0 && rank <= 16 && n_args >= 0 && n_args <= 16, KN_ERR_INVALID_ARG, "rank or argument count above 16");
+        KN_CHECK((rank == 0 || (shape != nullptr && strides != nullptr)) && (n_args == 0 || args != nullptr), KN_ERR_INVALID_ARG, "null array");
+        std::vector<int64_t> sh(shape, shape + rank), st(strides, strides + rank), a(args, args + n_args);
+        for (int64_t d : sh) KN_CHECK(d >= 0, KN_ERR_INVALID_ARG, "negative extent");
+        kn::StridedShape s(sh, st), r;
+        auto axis = [&](int i) {
+            KN_CHECK(n_args > i && a[i] >= 0 && a[i] < rank, KN_ERR_INVALID_ARG, "axis out of range");
+            return (int)a[i];
+        };
+        switch (op) {
+            case 0: r = s; break;
+            case 1: {
+                for (int64_t d : a) KN_CHECK(d >= 0, KN_ERR_INVALID_ARG, "negative extent");
+                int64_t n = 1;
+                for (int64_t d : a) n *= d;
+                KN_CHECK(n == s.size(), KN_ERR_INVALID_ARG, "a view keeps the element count");
+                auto v = s.view(a);
+                KN_CHECK(v.has_value(), KN_ERR_SHAPE, "cannot view " + s.str() + " as the requested shape without a copy");
+                r = *v;
+                break;
+            }
+            case 2:
+                KN_CHECK(n_args == 4 && a[3] >= 1 && a[1] >= 0 && a[2] >= a[1], KN_ERR_INVALID_ARG, "slice takes axis, start, end >= start, step >= 1");
+                r = s.slice(axis(0), a[1], a[2], a[3]);
+                break;
+            case 3: r = s.flip(axis(0)); break;
+            case 4: {
+                KN_CHECK(n_args == rank, KN_ERR_INVALID_ARG, "permutation length differs from the rank");
+                std::vector<int> perm;
+                std::vector<bool> seen(rank, false);
+                for (int i = 0; i < rank; i++) {
+                    const int p = axis(i);
+                    KN_CHECK(!seen[p], KN_ERR_INVALID_ARG, "not a permutation");
+                    seen[p] = true;
+                    perm.push_back(p);
+                }
+                r = s.permute(perm);
+                break;
+            }
+            case 5:
+                KN_CHECK(n_args == rank, KN_ERR_INVALID_ARG, "broadcast keeps the rank");
+                for (int i = 0; i < rank; i++)
+                    KN_CHECK(a[i] == sh[i] || sh[i] == 1, KN_ERR_INVALID_ARG, "only axes of size 1 can be broadcast");
+                r = s.broadcast(a);
+                break;
+            default: kn::fail(KN_ERR_INVALID_ARG, "unknown operation");
+        }
+        if (out_rank) *out_rank = r.rank();
+        for (int i = 0; i < r.rank(); i++) {
+            if (out_shape) out_shape[i] = r.shape[i];
+            if (out_strides) out_strides[i] = r.strides[i];
+        }
+        if (simple) *simple = r.has_simple_strides() ? 1 : 0;
+        if (dense) *dense = r.has_dense_strides() ? 1 : 0;
     });
 }
 

@@ -79,6 +79,8 @@ struct RowParams {
     float scale;             // softmax: x = scale * in0 + in1
     float alpha0, alpha1;    // layernorm: x = alpha0 * in0 + alpha1 * in1
     float eps;
+    int32_t half;            // 1: in0, in1 and out hold f16 elements (the pointers are reinterpreted); the
+                             // statistics and the arithmetic stay f32, the result is rounded to f16 once
 };
 
 // ---- gather along one axis with rank-1 indices: replaces autokernel/gather.{rs,cu}
@@ -111,6 +113,8 @@ struct GemmParams {
     // ([batch][slice][m][n] f32) and are summed by a second kernel; 1 = no split
     int32_t splits;
     float* scratch;
+    int32_t half;            // 1: A, B, C and the addends hold f16 elements (the pointers are reinterpreted); products
+                             // accumulate in f32 and the result is rounded to f16 once.  `scratch` stays f32.
 };
 
 // ---- 2D convolution (cross-correlation, zero padding) with fused epilogue
@@ -182,8 +186,10 @@ struct AllReduceParams {
 // All launchers enqueue on `stream` and return the cudaError_t of the launch as int.
 int launch_scalar(const ScalarParams& p, cudaStream_t stream);
 int launch_reduce(const ReduceParams& p, cudaStream_t stream);
-int launch_softmax(const RowParams& p, cudaStream_t stream);
+int launch_softmax(const RowParams& p, cudaStream_t stream);      // dispatches on p.half
 int launch_layernorm(const RowParams& p, cudaStream_t stream);
+int launch_softmax_f16(const RowParams& p, cudaStream_t stream);  // kernels/rows_f16.cu
+int launch_layernorm_f16(const RowParams& p, cudaStream_t stream);
 int launch_gather(const GatherParams& p, cudaStream_t stream);
 int launch_im2col(const Im2colParams& p, cudaStream_t stream);
 int launch_gemm_simt(const GemmParams& p, cudaStream_t stream);

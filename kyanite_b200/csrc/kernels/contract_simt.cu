@@ -4,6 +4,7 @@
 // These serve KN_MATH_F32 and every contraction shape the tensor-core kernels do not take
 // (arbitrary operand strides, stride/padding combinations, tiny extents).  Operands are addressed
 // through their element strides, so transposed, sliced, flipped or broadcast inputs need no copy.
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include "../kernels.h"
@@ -41,6 +42,28 @@ struct GemmProblem {
         if (p.add1) acc += p.add1[b * p.s1[0] + m * p.s1[1] + n * p.s1[2]];
         if (p.add2) acc += p.add2[b * p.s2[0] + m * p.s2[1] + n * p.s2[2]];
         p.c[b * p.sc[0] + m * p.sc[1] + n * p.sc[2]] = apply_epilogue(acc, p.act, p.round_tf32);
+    }
+};
+
+// The same problem with f16 storage: operands and addends are converted on load, products accumulate in f32,
+// the result is rounded to f16 once.
+struct GemmProblemHalf {
+    GemmParams p;
+    __device__ int64_t M() const { return p.m; }
+    __device__ int64_t N() const { return p.n; }
+    __device__ int64_t K() const { return p.k; }
+    __device__ bool a_k_fast() const { return p.sa[2] == 1; }
+    __device__ bool b_k_fast() const { return p.sb[1] == 1; }
+    __device__ float load_a(int64_t b, int64_t m, int64_t k) const {
+        return __half2float(((const __half*)p.a)[b * p.sa[0] + m * p.sa[1] + k * p.sa[2]]);
+    }
+    __device__ float load_b(int64_t b, int64_t k, int64_t n) const {
+        return __half2float(((const __half*)p.b)[b * p.sb[0] + k * p.sb[1] + n * p.sb[2]]);
+    }
+    __device__ void store(int64_t b, int64_t m, int64_t n, float acc) const {
+        if (p.add1) acc += __half2float(((const __half*)p.add1)[b * p.s1[0] + m * p.s1[1] + n * p.s1[2]]);
+        if (p.add2) acc += __half2float(((const __half*)p.add2)[b * p.s2[0] + m * p.s2[1] + n * p.s2[2]]);
+        ((__half*)p.c)[b * p.sc[0] + m * p.sc[1] + n * p.sc[2]] = __float2half_rn(apply_activation(acc, p.act));
     }
 };
 
@@ -213,6 +236,7 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const __grid_constant_
 }  // namespace
 
 int launch_gemm_simt(const GemmParams& p, cudaStream_t stream) {
+    if (p.half) return launch(GemmProblemHalf{p}, p.m, p.n, p.batch, stream);
     if (p.n >= 1 && p.n <= kSkinnyMaxN && p.k >= 32 && p.batch * p.m > 0) {
         const int64_t rows = p.batch * p.m;
         launch_pdl(gemm_skinny_kernel, dim3((unsigned)((rows + 7) / 8)), dim3(256), (size_t)(0), stream, p);

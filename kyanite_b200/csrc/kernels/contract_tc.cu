@@ -19,6 +19,7 @@
 // Every mbarrier wait is bounded: on expiry the kernel records a code in the executor's status word,
 // all roles leave their loops, TMEM is released and the kernel returns.
 #include <cuda.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include <cstdlib>
@@ -320,6 +321,7 @@ struct SplitKReduceParams {
     const float* add2;
     int64_t so[3], s1[3], s2[3];
     int32_t act, round_tf32;
+    int32_t half;   // out and the addends hold f16 elements (the partial sums are always f32)
 };
 
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const __grid_constant__ SplitKReduceParams p) {
@@ -333,6 +335,12 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const __grid_constan
         const float* src = p.partial + (b * p.splits * p.m + m) * p.n + n;
         float acc = 0.f;
         for (int s = 0; s < p.splits; s++) acc += src[(int64_t)s * p.m * p.n];
+        if (p.half) {
+            if (p.add1) acc += __half2float(((const __half*)p.add1)[b * p.s1[0] + m * p.s1[1] + n * p.s1[2]]);
+            if (p.add2) acc += __half2float(((const __half*)p.add2)[b * p.s2[0] + m * p.s2[1] + n * p.s2[2]]);
+            ((__half*)p.out)[b * p.so[0] + m * p.so[1] + n * p.so[2]] = __float2half_rn(apply_activation(acc, p.act));
+            continue;
+        }
         if (p.add1) acc += p.add1[b * p.s1[0] + m * p.s1[1] + n * p.s1[2]];
         if (p.add2) acc += p.add2[b * p.s2[0] + m * p.s2[1] + n * p.s2[2]];
         p.out[b * p.so[0] + m * p.so[1] + n * p.so[2]] = finish(acc, p.act, p.round_tf32);
@@ -721,6 +729,30 @@ CUtensorMap tc_make_map(const void* base, int rank, const int64_t* dims, const i
     return make_map(base, rank, dims, strides, box, operand);
 }
 
+CUtensorMap tc_make_map_f16(const void* base, int rank, const int64_t* dims, const int64_t* strides, const int* box, bool operand) {
+    KN_CHECK(((uintptr_t)base & 15) == 0, KN_ERR_INTERNAL, "TMA base address is not 16-byte aligned");
+    cuuint64_t gdim[5], gstride[4];
+    cuuint32_t gbox[5], estride[5];
+    for (int i = 0; i < rank; i++) {
+        gdim[i] = (cuuint64_t)std::max<int64_t>(dims[i], 1);
+        gbox[i] = (cuuint32_t)box[i];
+        estride[i] = 1;
+        if (i > 0) {
+            int64_t bytes = strides[i] * 2;
+            if (dims[i] <= 1 && (bytes <= 0 || bytes % 16 != 0)) bytes = 16;   // never stepped: any legal value
+            KN_CHECK(bytes > 0 && bytes % 16 == 0, KN_ERR_INTERNAL, "TMA stride is not a positive multiple of 16 bytes");
+            gstride[i - 1] = (cuuint64_t)bytes;
+        }
+    }
+    CUtensorMap map;
+    CUresult res = encode_tiled_fn()(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstride,
+                                     gbox, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                     operand ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    KN_CHECK(res == CUDA_SUCCESS, KN_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)res));
+    return map;
+}
+
 static bool tma_stride_ok_host(int64_t dim, int64_t stride) { return dim <= 1 || (stride > 0 && stride % 4 == 0); }
 
 // Fills the channels-last convolution launch if the step qualifies: channels-last output, at least
@@ -853,7 +885,7 @@ bool tc_conv_tile(int oh, int ow, int* wb, int* hb, int* nb) {
     return true;
 }
 
-void tc_prepare_step(Step& step, uint32_t* status_word, int flags) {
+void tc_prepare_step(Step& step, uint32_t* status_word, int flags, uint32_t* trace_words) {
     auto launch = std::make_shared<TcLaunch>();
     if (step.kind == StepKind::ConvChain) {
         launch->chain = chain_prepare(step.chain, status_word);
@@ -866,8 +898,42 @@ void tc_prepare_step(Step& step, uint32_t* status_word, int flags) {
     int64_t n_cols;
     if (step.kind == StepKind::Gemm) {
         const GemmParams& g = step.gemm;
+        if (g.half) {
+            // f16 storage: the persistent kernel is the only tensor-core kernel with f16 operands; the planner marks
+            // a step tensor-core only when that kernel takes it
+            int per_slice = 0, splits = 1;
+            if (g.splits > 1) {
+                const int k_total = (int)((g.k + 63) / 64);
+                per_slice = (k_total + g.splits - 1) / g.splits;
+                splits = (k_total + per_slice - 1) / per_slice;
+            }
+            launch->gemm_p = gemm_persistent_prepare(g, status_word, splits, per_slice, trace_words);
+            KN_CHECK(launch->gemm_p != nullptr, KN_ERR_INTERNAL, "f16 matmul planned for the tensor cores does not qualify");
+            if (splits > 1) {
+                SplitKReduceParams& r = launch->reduce;
+                memset(&r, 0, sizeof(r));
+                r.partial = g.scratch;
+                r.splits = splits;
+                r.batch = g.batch;
+                r.m = g.m;
+                r.n = g.n;
+                r.out = g.c;
+                r.add1 = g.add1;
+                r.add2 = g.add2;
+                for (int i = 0; i < 3; i++) {
+                    r.so[i] = g.sc[i];
+                    r.s1[i] = g.s1[i];
+                    r.s2[i] = g.s2[i];
+                }
+                r.act = g.act;
+                r.half = 1;
+                launch->split_k = true;
+            }
+            step.tc = launch;
+            return;
+        }
         if (g.splits <= 1 && !(flags & KN_FLAG_NO_PERSISTENT_GEMM)) {
-            launch->gemm_p = gemm_persistent_prepare(g, status_word, 1, 0);
+            launch->gemm_p = gemm_persistent_prepare(g, status_word, 1, 0, trace_words);
             if (launch->gemm_p) {
                 step.tc = launch;
                 return;
@@ -937,7 +1003,7 @@ void tc_prepare_step(Step& step, uint32_t* status_word, int flags) {
             launch->split_k = true;
             // the partial tiles can come from the persistent kernel too (its epilogue hands whole 128 x 32
             // blocks to the copy engine instead of storing row by row)
-            if (!(flags & KN_FLAG_NO_PERSISTENT_GEMM)) launch->gemm_p = gemm_persistent_prepare(g, status_word, p.splits, per_slice);
+            if (!(flags & KN_FLAG_NO_PERSISTENT_GEMM)) launch->gemm_p = gemm_persistent_prepare(g, status_word, p.splits, per_slice, trace_words);
         }
     } else {
         const ConvParams& c = step.conv;

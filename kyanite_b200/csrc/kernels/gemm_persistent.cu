@@ -1,5 +1,8 @@
-// Persistent TF32 matrix multiply for sm_100a: C[b] = act(A[b] . B[b]^T-layout + add1 + add2) with a dense
-// row-major C.
+// Persistent matrix multiply for sm_100a: C[b] = act(A[b] . B[b]^T-layout + add1 + add2) with a dense
+// row-major C.  Two operand types, one kernel template: f32 storage with TF32 operands (kind::tf32, 32-element
+// K blocks) and f16 storage (kind::f16, 64-element K blocks, f32 accumulation, the result rounded to f16 once in
+// the epilogue; an extension, the reference's IR has no half type).  A K block is 128 bytes of either, so
+// the pipeline, the shared-memory layout and the operand descriptors are the same.
 //
 // Compared with the one-tile-per-CTA kernel in contract_tc.cu, a CTA here stays on its SM and walks over
 // output tiles, and tensor memory holds TWO accumulators: while the four epilogue warps drain tile i
@@ -17,6 +20,7 @@
 // that run at the same time share a B tile in L2.  Row and column tails are the copy engine's zero fill
 // (loads) and clipping (stores).  Every mbarrier wait is bounded as in the other tensor-core kernels.
 #include <cuda.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include <algorithm>
@@ -54,8 +58,21 @@ struct GemmPersistentParams {
     int64_t s1[3], s2[3];            // (batch, row, col) strides of the addends
     int32_t add1_mode, add2_mode;    // 0 absent, 1 one value per column, 2 a value per element (row-contiguous), 4 one value per row
     int32_t act;
+    int32_t out_half;                // f16 storage and no split: the output tile is f16 (else f32: plain C or partial sums)
     uint32_t* status;
+    volatile uint32_t* dbg;          // null, or 8 progress words in pinned host memory (KN_FLAG_TRACE_GEMM)
 };
+
+// Post-mortem aid: with KN_FLAG_TRACE_GEMM the first CTA records how far each role got (words: 0 kernel entered,
+// 1 K blocks requested, 2 K blocks landed, 3 K blocks multiplied, 4 accumulator seen by the epilogue, 5 chunks
+// stored, 6 epilogue done) in pinned host memory, which the host can still read after a fault has taken the
+// context.  Off (null pointer) in normal operation.
+__device__ __forceinline__ void dbg_mark(const GemmPersistentParams& p, uint32_t slot, uint32_t value) {
+    if (p.dbg != nullptr && blockIdx.x == 0) {
+        p.dbg[slot] = value;
+        __threadfence_system();
+    }
+}
 
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2) {
     asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
@@ -67,10 +84,12 @@ __device__ __forceinline__ void mbar_arrive_local(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
+template <bool HALF>   // operand storage: f16 (kind::f16) or f32 (kind::tf32)
 __global__ void __launch_bounds__(kGpThreads, 1)
 gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                        const __grid_constant__ CUtensorMap map_c, const __grid_constant__ GemmPersistentParams p) {
     extern __shared__ uint8_t smem_raw[];
+    constexpr int kBlockKElems = HALF ? 64 : 32;   // elements per 128-byte K block
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
     const int stages = p.stages;
@@ -120,6 +139,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     };
     auto slice_blocks = [&](int sp) { return min(p.k_iters_slice, p.k_iters - sp * p.k_iters_slice); };
 
+    if (threadIdx.x == 0) dbg_mark(p, 0, 1);
     if (warp == 0 && lane == 0) {
         // ---------------- producer
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
@@ -135,14 +155,18 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 const uint32_t bar = full_bar + 8u * s;
                 mbar_expect_tx(bar, stage_bytes);
                 const uint32_t dst = base + (uint32_t)s * stage_bytes;
-                tma_load_3d(dst, &map_a, bar, k * kGpBlockK, mt * kGpBlockM, bt * p.a_batch);
-                tma_load_3d(dst + kGpATileBytes, &map_b, bar, k * kGpBlockK, nt * p.bn, bt * p.b_batch);
+                tma_load_3d(dst, &map_a, bar, k * kBlockKElems, mt * kGpBlockM, bt * p.a_batch);
+                tma_load_3d(dst + kGpATileBytes, &map_b, bar, k * kBlockKElems, nt * p.bn, bt * p.b_batch);
+                dbg_mark(p, 1, (uint32_t)(k + 1));
                 if (++s == stages) { s = 0; round++; }
             }
         }
     } else if (warp == 1 && lane == 0) {
         // ---------------- MMA issuer
-        const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(p.bn >> 3) << 17) | ((uint32_t)(kGpBlockM >> 4) << 24);
+        // instruction descriptor: f32 accumulate; A and B formats 2 = TF32 (kind::tf32) or 0 = F16 (kind::f16); both
+        // K-major; N, M
+        const uint32_t fmt = HALF ? 0u : 2u;
+        const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(p.bn >> 3) << 17) | ((uint32_t)(kGpBlockM >> 4) << 24);
         int s = 0, round = 0, local = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, local++) {
@@ -158,13 +182,19 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             if (t + (int)gridDim.x >= p.total_tiles) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
             for (int k = 0; k < k_count; k++) {
                 if (!mbar_wait(full_bar + 8u * s, (uint32_t)(round & 1), abandon, p.status, 23)) { ok = false; break; }
+                dbg_mark(p, 2, (uint32_t)(k + 1));
                 tc_fence_after();
                 const uint32_t a_addr = base + (uint32_t)s * stage_bytes;
                 const uint64_t da = smem_desc_sw128(a_addr);
                 const uint64_t db = smem_desc_sw128(a_addr + kGpATileBytes);
+                // four instructions of 32 bytes of K each: the start address advances by 2 (16-byte units)
 #pragma unroll
-                for (int j = 0; j < kGpBlockK / 8; j++) mma_tf32(acc, da + 2u * j, db + 2u * j, idesc, (k | j) != 0 ? 1u : 0u);
+                for (int j = 0; j < 4; j++) {
+                    if (HALF) mma_f16(acc, da + 2u * j, db + 2u * j, idesc, (k | j) != 0 ? 1u : 0u);
+                    else mma_tf32(acc, da + 2u * j, db + 2u * j, idesc, (k | j) != 0 ? 1u : 0u);
+                }
                 mma_commit(empty_bar + 8u * s);
+                dbg_mark(p, 3, (uint32_t)(k + 1));
                 if (++s == stages) { s = 0; round++; }
             }
             if (ok) mma_commit(acc_full + 8u * buf);
@@ -203,6 +233,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 while (!mbar_try_wait(acc_full + 8u * buf, (uint32_t)((local >> 1) & 1))) {}
             }
             tc_fence_after();
+            if (issuer) dbg_mark(p, 4, 1);
             const int64_t row = (int64_t)mt * kGpBlockM + row_in_tile;
             const bool row_ok = row < p.m;
             const int chunks = (p.bn + 31) >> 5;
@@ -219,6 +250,40 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                     if (mode == 0) continue;
                     const float* add = which == 0 ? p.add1 : p.add2;
                     const int64_t* st = which == 0 ? p.s1 : p.s2;
+                    if (HALF) {
+                        // f16 addends: converted on load
+                        const __half* addh = (const __half*)add;
+                        if (mode == 1) {
+                            const int64_t col = col0 + lane;
+                            const float mine = col < p.n ? __half2float(__ldg(addh + bt * st[0] + col * st[2])) : 0.f;
+#pragma unroll
+                            for (int j = 0; j < 32; j++) v[j] = __float_as_uint(__uint_as_float(v[j]) + __shfl_sync(0xffffffffu, mine, j));
+                        } else if (mode == 4) {
+                            const float mine = row_ok ? __half2float(__ldg(addh + bt * st[0] + row * st[1])) : 0.f;
+#pragma unroll
+                            for (int j = 0; j < 32; j++) v[j] = __float_as_uint(__uint_as_float(v[j]) + mine);
+                        } else if (row_ok) {
+                            const __half* src = addh + bt * st[0] + row * st[1] + col0;
+                            if (col0 + 32 <= p.n && ((uintptr_t)src & 15) == 0) {
+#pragma unroll
+                                for (int q = 0; q < 4; q++) {
+                                    const uint4 a8 = __ldg((const uint4*)src + q);
+                                    const __half2* h2 = (const __half2*)&a8;
+#pragma unroll
+                                    for (int u = 0; u < 4; u++) {
+                                        const float2 f = __half22float2(h2[u]);
+                                        v[8 * q + 2 * u] = __float_as_uint(__uint_as_float(v[8 * q + 2 * u]) + f.x);
+                                        v[8 * q + 2 * u + 1] = __float_as_uint(__uint_as_float(v[8 * q + 2 * u + 1]) + f.y);
+                                    }
+                                }
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 32; j++)
+                                    if (col0 + j < p.n) v[j] = __float_as_uint(__uint_as_float(v[j]) + __half2float(__ldg(src + j)));
+                            }
+                        }
+                        continue;
+                    }
                     if (mode == 1) {
                         const int64_t col = col0 + lane;
                         const float mine = col < p.n ? __ldg(add + bt * st[0] + col * st[2]) : 0.f;
@@ -256,17 +321,35 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 // the staging tile about to be written was handed to the copy engine two chunks ago
                 if (issuer) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
                 asm volatile("bar.sync 1, 128;" ::: "memory");
-                const uint32_t stile = staging_base + (uint32_t)stage_buf * kGpStageTileBytes + row_base;
+                if (HALF && p.out_half) {
+                    // f16 output: rows of 32 halves = 64 bytes, plain row-major (the store map has no swizzle)
+                    const uint32_t stile = staging_base + (uint32_t)stage_buf * kGpStageTileBytes + (uint32_t)row_in_tile * 64u;
 #pragma unroll
-                for (int q = 0; q < 8; q++)
-                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stile + (((uint32_t)q ^ row_phase) << 4)),
-                                 "r"(v[4 * q]), "r"(v[4 * q + 1]), "r"(v[4 * q + 2]), "r"(v[4 * q + 3])
-                                 : "memory");
+                    for (int q = 0; q < 4; q++) {
+                        uint32_t h[4];
+#pragma unroll
+                        for (int u = 0; u < 4; u++) {
+                            const __half2 pair = __floats2half2_rn(__uint_as_float(v[8 * q + 2 * u]), __uint_as_float(v[8 * q + 2 * u + 1]));
+                            h[u] = *(const uint32_t*)&pair;
+                        }
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stile + (uint32_t)q * 16u), "r"(h[0]), "r"(h[1]),
+                                     "r"(h[2]), "r"(h[3])
+                                     : "memory");
+                    }
+                } else {
+                    const uint32_t stile = staging_base + (uint32_t)stage_buf * kGpStageTileBytes + row_base;
+#pragma unroll
+                    for (int q = 0; q < 8; q++)
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stile + (((uint32_t)q ^ row_phase) << 4)),
+                                     "r"(v[4 * q]), "r"(v[4 * q + 1]), "r"(v[4 * q + 2]), "r"(v[4 * q + 3])
+                                     : "memory");
+                }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (issuer) {
                     tma_store_3d(&map_c, staging_base + (uint32_t)stage_buf * kGpStageTileBytes, col0, mt * kGpBlockM, bt * p.splits + sp);
                     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    dbg_mark(p, 5, (uint32_t)(c + 1));
                 }
                 stage_buf ^= 1;
             }
@@ -275,6 +358,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             mbar_arrive_local(acc_empty + 8u * buf);
         }
         if (issuer) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // shared memory must outlive the stores
+        if (issuer) dbg_mark(p, 6, 1);
     }
 
     tc_fence_before();
@@ -289,6 +373,7 @@ struct GemmPersistentLaunch {
     GemmPersistentParams p;
     dim3 grid;
     int smem_bytes;
+    bool half;
 };
 
 // 0 absent, 1 one value per column (row stride 0), 2 a value per element with contiguous rows, 4 one value per
@@ -303,14 +388,18 @@ int classify_addend(const float* ptr, const int64_t* st) {
 
 }  // namespace
 
-std::shared_ptr<void> gemm_persistent_prepare(const GemmParams& g, uint32_t* status_word, int splits, int k_iters_slice) {
+std::shared_ptr<void> gemm_persistent_prepare(const GemmParams& g, uint32_t* status_word, int splits, int k_iters_slice,
+                                              uint32_t* trace_words) {
     if (g.batch < 1 || g.m < 1 || g.n < 16 || g.k < 1 || splits < 1) return nullptr;
     const bool split = splits > 1;
+    const bool half = g.half != 0;
+    const int64_t align = half ? 8 : 4;            // elements per 16 bytes
+    const int block_k = half ? 64 : 32;
     // dense row-major C whose rows start on 16-byte boundaries (split K: the partial sums [batch][slice][m][n],
     // which the reduction kernel turns into C; addends and activation are applied there)
     if (split) {
         if (g.n % 4 != 0 || ((uintptr_t)g.scratch & 15) != 0 || g.scratch == nullptr) return nullptr;
-    } else if (g.sc[2] != 1 || g.sc[1] % 4 != 0 || (g.batch > 1 && g.sc[0] % 4 != 0) || ((uintptr_t)g.c & 15) != 0) {
+    } else if (g.sc[2] != 1 || g.sc[1] % align != 0 || (g.batch > 1 && g.sc[0] % align != 0) || ((uintptr_t)g.c & 15) != 0) {
         return nullptr;
     }
     const int m1 = split ? 0 : classify_addend(g.add1, g.s1), m2 = split ? 0 : classify_addend(g.add2, g.s2);
@@ -326,7 +415,9 @@ std::shared_ptr<void> gemm_persistent_prepare(const GemmParams& g, uint32_t* sta
         const int64_t unit = blocks > 1 ? 32 : 16;
         p.bn = (int)std::min<int64_t>(((g.n + blocks - 1) / blocks + unit - 1) / unit * unit, 256);
     }
-    p.k_iters = (int)((g.k + kGpBlockK - 1) / kGpBlockK);
+    p.k_iters = (int)((g.k + block_k - 1) / block_k);
+    p.out_half = half && !split ? 1 : 0;
+    l->half = half;
     p.m_tiles = (int)((g.m + kGpBlockM - 1) / kGpBlockM);
     p.n_tiles = (int)((g.n + p.bn - 1) / p.bn);
     p.batch = (int)g.batch;
@@ -348,21 +439,28 @@ std::shared_ptr<void> gemm_persistent_prepare(const GemmParams& g, uint32_t* sta
     p.add2_mode = m2;
     p.act = split ? 0 : g.act;
     p.status = status_word;
+    p.dbg = (volatile uint32_t*)trace_words;
     const int stage_bytes = kGpATileBytes + p.bn * 128;
     const int fixed = 1024 + 2 * kGpStageTileBytes + 16 * 8 + 64 + 64;
     p.stages = std::max(2, std::min(6, (227 * 1024 - fixed) / stage_bytes));
     l->smem_bytes = fixed + p.stages * stage_bytes;
     p.a_batch = (g.batch > 1 && g.sa[0] == 0) ? 0 : 1;
-    int64_t adims[3] = {g.k, g.m, p.a_batch ? g.batch : 1}, astr[3] = {1, g.sa[1], p.a_batch ? g.sa[0] : 4};
-    int abox[3] = {kGpBlockK, kGpBlockM, 1};
-    l->map_a = tc_make_map(g.a, 3, adims, astr, abox, true);
+    int64_t adims[3] = {g.k, g.m, p.a_batch ? g.batch : 1}, astr[3] = {1, g.sa[1], p.a_batch ? g.sa[0] : align};
+    int abox[3] = {block_k, kGpBlockM, 1};
     p.b_batch = (g.batch > 1 && g.sb[0] == 0) ? 0 : 1;
-    int64_t bdims[3] = {g.k, g.n, p.b_batch ? g.batch : 1}, bstr[3] = {1, g.sb[2], p.b_batch ? g.sb[0] : 4};
-    int bbox[3] = {kGpBlockK, p.bn, 1};
-    l->map_b = tc_make_map(g.b, 3, bdims, bstr, bbox, true);
+    int64_t bdims[3] = {g.k, g.n, p.b_batch ? g.batch : 1}, bstr[3] = {1, g.sb[2], p.b_batch ? g.sb[0] : align};
+    int bbox[3] = {block_k, p.bn, 1};
+    if (half) {
+        l->map_a = tc_make_map_f16(g.a, 3, adims, astr, abox, true);
+        l->map_b = tc_make_map_f16(g.b, 3, bdims, bstr, bbox, true);
+    } else {
+        l->map_a = tc_make_map(g.a, 3, adims, astr, abox, true);
+        l->map_b = tc_make_map(g.b, 3, bdims, bstr, bbox, true);
+    }
     int64_t cdims[3] = {g.n, g.m, g.batch * splits}, cstr[3] = {1, split ? g.n : g.sc[1], split ? g.m * g.n : g.sc[0]};
     int cbox[3] = {32, kGpBlockM, 1};
-    l->map_c = tc_make_store_map(split ? g.scratch : g.c, 3, cdims, cstr, cbox);
+    if (p.out_half) l->map_c = tc_make_map_f16(g.c, 3, cdims, cstr, cbox, false);
+    else l->map_c = tc_make_store_map(split ? g.scratch : g.c, 3, cdims, cstr, cbox);
     l->grid = dim3((unsigned)std::min<int64_t>(total, 148), 1, 1);
     return l;
 }
@@ -376,12 +474,15 @@ int gemm_persistent_launch(const void* launch, cudaStream_t stream) {
     {
         std::lock_guard<std::mutex> lock(mu);
         if (device >= 0 && device < 64 && !done[device]) {
-            cudaError_t e = cudaFuncSetAttribute(gemm_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            cudaError_t e = cudaFuncSetAttribute(gemm_persistent_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            if (e != cudaSuccess) return (int)e;
+            e = cudaFuncSetAttribute(gemm_persistent_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
             if (e != cudaSuccess) return (int)e;
             done[device] = true;
         }
     }
-    launch_pdl(gemm_persistent_kernel, dim3(l.grid), dim3(kGpThreads), (size_t)(l.smem_bytes), stream, l.map_a, l.map_b, l.map_c, l.p);
+    if (l.half) launch_pdl(gemm_persistent_kernel<true>, dim3(l.grid), dim3(kGpThreads), (size_t)(l.smem_bytes), stream, l.map_a, l.map_b, l.map_c, l.p);
+    else launch_pdl(gemm_persistent_kernel<false>, dim3(l.grid), dim3(kGpThreads), (size_t)(l.smem_bytes), stream, l.map_a, l.map_b, l.map_c, l.p);
     return (int)cudaGetLastError();
 }
 

@@ -511,10 +511,12 @@ static bool softmax_vec4_ok(const RowParams& p) {
     return (int)cudaGetLastError();
 
 int launch_softmax(const RowParams& p, cudaStream_t stream) {
+    if (p.half) return launch_softmax_f16(p, stream);
     KN_ROW_DISPATCH(softmax_cached_kernel, softmax_vec4_kernel, softmax_streaming_kernel, softmax_vec4_ok)
 }
 
 int launch_layernorm(const RowParams& p, cudaStream_t stream) {
+    if (p.half) return launch_layernorm_f16(p, stream);
     // Rows of 8193..49152 elements (a group norm over [channels / groups, H, W]): one block of 512 threads per
     // row with the row in registers, one read and one write, instead of three sweeps by the streaming kernel.
     if (p.rows > 0 && p.rows <= 0x7FFFFFFFll && p.len > 8192 && p.len <= 49152 && row_vec4_ok_len(p, 49152)) {

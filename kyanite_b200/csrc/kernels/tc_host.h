@@ -19,9 +19,15 @@ CUtensorMap tc_make_map(const void* base, int rank, const int64_t* dims, const i
 // extent 32 floats).
 CUtensorMap tc_make_store_map(const void* base, int rank, const int64_t* dims, const int64_t* strides, const int* box);
 
+// Tiled tensor maps over f16 data (strides in ELEMENTS): an MMA operand tile (128-byte swizzle: inner box extent 64
+// halves) when `operand`, else a plain row-major tile without swizzle (an epilogue tile).
+CUtensorMap tc_make_map_f16(const void* base, int rank, const int64_t* dims, const int64_t* strides, const int* box, bool operand);
+
 // Persistent matrix multiply (kernels/gemm_persistent.cu): null if the step does not qualify.
 // `splits` > 1: K is cut into slices of `k_iters_slice` 32-wide blocks whose partial tiles go to g.scratch.
-std::shared_ptr<void> gemm_persistent_prepare(const GemmParams& g, uint32_t* status_word, int splits, int k_iters_slice);
+// `trace_words`: null, or 8 words of pinned host memory for the kernel's progress markers (KN_FLAG_TRACE_GEMM).
+std::shared_ptr<void> gemm_persistent_prepare(const GemmParams& g, uint32_t* status_word, int splits, int k_iters_slice,
+                                              uint32_t* trace_words = nullptr);
 int gemm_persistent_launch(const void* launch, cudaStream_t stream);
 
 // Convolution chain (kernels/conv_chain.cu): launch data built once the device pointers are known.

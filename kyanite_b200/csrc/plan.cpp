@@ -522,8 +522,11 @@ class Planner {
                 KN_CHECK(start == shape[info.axis], KN_ERR_SHAPE, "concat sizes do not add up");
                 return out;
             }
-            case OpKind::Conv: case OpKind::MatMul:
-                fail(KN_ERR_UNSUPPORTED, std::string(op_name(info.op)) + " is only supported for f32 operands");
+            case OpKind::MatMul:
+                if (info.dtype == DType::F16) return visit_matmul_f16(v);
+                fail(KN_ERR_UNSUPPORTED, "MatMul is only supported for f32 and f16 operands");
+            case OpKind::Conv:
+                fail(KN_ERR_UNSUPPORTED, "Conv is only supported for f32 operands");
             case OpKind::Unary: case OpKind::Binary: return visit_scalar(v);
             case OpKind::Softmax: return visit_softmax(v);
             case OpKind::Layernorm: return visit_layernorm(v);
@@ -916,6 +919,104 @@ class Planner {
         return out.with(*rs);
     }
 
+    // ---------------------------------------------------------------- f16 storage (an extension: the reference has no half type)
+    // A [b, m, k] and B [b, k, n] of f16, both contiguous along k, every other stride a multiple of 16 bytes (8 elements),
+    // and an output the persistent kernel can store through the copy engine (n a multiple of 8, at least 16)
+    bool gemm_f16_fits_tensor_core(const PlanTensor& a, const PlanTensor& b) const {
+        if (a.ss.rank() != 3 || b.ss.rank() != 3) return false;
+        const int64_t batch = a.ss.shape[0], m = a.ss.shape[1], k = a.ss.shape[2], n = b.ss.shape[2];
+        auto ok = [](int64_t dim, int64_t stride) { return dim <= 1 || (stride > 0 && stride % 8 == 0); };
+        if (batch < 1 || batch > 65535 || m < 64 || n < 16 || n % 8 != 0 || k < 16) return false;
+        if (k > 1 && (a.ss.strides[2] != 1 || b.ss.strides[1] != 1)) return false;
+        if (!ok(m, a.ss.strides[1]) || !(ok(batch, a.ss.strides[0]) || a.ss.strides[0] == 0)) return false;
+        if (!ok(n, b.ss.strides[2]) || !(ok(batch, b.ss.strides[0]) || b.ss.strides[0] == 0)) return false;
+        if (a.offset % 8 != 0 || b.offset % 8 != 0) return false;
+        if (m > (1ll << 30) || n > (1ll << 30) || k > (1ll << 30)) return false;
+        return true;
+    }
+    // `t` [b, rows, k] as it is when K-contiguous and aligned, else copied into a K-contiguous buffer
+    // (`transposed`: t is [b, k, rows], the copy is stored [b, rows, k_pad] and viewed back as [b, k, rows])
+    PlanTensor k_major_f16(const PlanTensor& t, bool transposed, int value) {
+        const int k_axis = transposed ? 1 : 2, other = transposed ? 2 : 1;
+        auto ok = [](int64_t dim, int64_t stride) { return dim <= 1 || (stride > 0 && stride % 8 == 0); };
+        if ((t.ss.shape[k_axis] <= 1 || t.ss.strides[k_axis] == 1) && ok(t.ss.shape[other], t.ss.strides[other]) &&
+            (ok(t.ss.shape[0], t.ss.strides[0]) || t.ss.strides[0] == 0) && t.offset % 8 == 0)
+            return t;
+        const int64_t k = t.ss.shape[k_axis], k_pad = (k + 7) / 8 * 8;
+        PlanTensor dense = alloc_shared({t.ss.shape[0], t.ss.shape[other], k_pad}, DType::F16, value);
+        PlanTensor dst = transposed ? dense.with(dense.ss.permute({0, 2, 1})).slice(1, 0, k, 1) : dense.slice(2, 0, k, 1);
+        emit_copy(t, dst, value);
+        return dst;
+    }
+
+    // MatMul on f16 values: f16 operands, f32 accumulation, the result rounded to f16 once.  No epilogue fusion (the
+    // graphs that use f16 have bias-free projections).  Tensor cores (kind::f16) when the persistent kernel takes the
+    // shape, else the SIMT kernel with conversion on load.
+    PlanTensor visit_matmul_f16(int v) {
+        const ValueInfo& info = g_.values[v];
+        PlanTensor x = visit(info.inputs[0]);
+        PlanTensor w = visit(info.inputs[1]);
+        KN_CHECK(x.dtype == DType::F16 && w.dtype == DType::F16, KN_ERR_UNSUPPORTED, "f16 matmul needs f16 operands");
+        KN_CHECK(x.ss.rank() == 3 && w.ss.rank() == 3, KN_ERR_SHAPE, "matmul operands must have rank 3");
+        std::vector<int64_t> native = shape_of(v);
+        bool tensor_core = false;
+        if (opts_.math_mode == KN_MATH_TF32) {
+            if (!gemm_f16_fits_tensor_core(x, w) && gemm_worth_a_copy(x, w)) {
+                PlanTensor x2 = k_major_f16(x, false, info.inputs[0]), w2 = k_major_f16(w, true, info.inputs[1]);
+                if (gemm_f16_fits_tensor_core(x2, w2)) {
+                    x = x2;
+                    w = w2;
+                }
+            }
+            tensor_core = gemm_f16_fits_tensor_core(x, w);
+        }
+        PlanTensor out = alloc_shared(native, DType::F16, v);
+        Step s;
+        s.value = v;
+        s.kind = StepKind::Gemm;
+        s.tensor_core = tensor_core;
+        s.operands = {x, w, out};
+        s.writes = {0, 0, 1};
+        GemmParams& p = s.gemm;
+        p.half = 1;
+        p.batch = x.ss.shape[0];
+        p.m = x.ss.shape[1];
+        p.k = x.ss.shape[2];
+        p.n = w.ss.shape[2];
+        KN_CHECK(w.ss.shape[0] == p.batch && w.ss.shape[1] == p.k, KN_ERR_SHAPE, "matmul operand shapes differ");
+        for (int i = 0; i < 3; i++) {
+            p.sa[i] = x.ss.strides[i];
+            p.sb[i] = w.ss.strides[i];
+            p.sc[i] = out.ss.strides[i];
+        }
+        p.act = 0;
+        p.splits = 1;
+        if (tensor_core) {
+            // few output tiles under a long K: slices of K on separate CTAs, f32 partial sums in a scratch buffer
+            const int64_t n_blocks = (p.n + 255) / 256;
+            const int64_t bn = std::min<int64_t>(((p.n + n_blocks - 1) / n_blocks + 31) / 32 * 32, 256);
+            const int64_t tiles = ((p.m + 127) / 128) * ((p.n + bn - 1) / bn) * p.batch;
+            const int64_t k_blocks = (p.k + 63) / 64;
+            if (tiles < 74 && k_blocks >= 16 && p.n % 4 == 0) {
+                int64_t splits = std::min<int64_t>(std::min<int64_t>(k_blocks / 4, (148 + tiles - 1) / tiles), 32);
+                if (splits > 1) {
+                    const int64_t per = (k_blocks + splits - 1) / splits;
+                    splits = (k_blocks + per - 1) / per;
+                    p.splits = (int32_t)splits;
+                    PlanTensor scratch = alloc_shared({p.batch, splits, p.m, p.n}, DType::F32, v);
+                    s.operands.push_back(scratch);
+                    s.writes.push_back(1);
+                    s.launches = 2;
+                }
+            }
+        }
+        s.flops = 2.0 * (double)p.batch * (double)p.m * (double)p.n * (double)p.k;
+        s.desc = "matmul b=" + std::to_string(p.batch) + " m=" + std::to_string(p.m) + " n=" + std::to_string(p.n) + " k=" +
+                 std::to_string(p.k) + " +0 f16" + (p.splits > 1 ? " splitk=" + std::to_string(p.splits) : "");
+        if (out.ss.size() != 0) push_step(std::move(s));
+        return out;
+    }
+
     // ---------------------------------------------------------------- tensor-core eligibility
     static bool tma_stride_ok(int64_t dim, int64_t stride) { return dim <= 1 || (stride > 0 && stride % 4 == 0); }
 
@@ -1187,9 +1288,10 @@ class Planner {
     // `const * x` -> (const, x)   (kn-cuda-eval/src/planner.rs:584-604)
     std::pair<float, PlanTensor> visit_scalable(int v) {
         const ValueInfo& info = g_.values[v];
-        if (info.op == OpKind::Binary && info.binary_op == BinaryOp::Mul && info.dtype == DType::F32 && !map_[v]) {
-            if (auto c = g_.as_single_const(info.inputs[0])) return {c->as_f32(), visit(info.inputs[1])};
-            if (auto c = g_.as_single_const(info.inputs[1])) return {c->as_f32(), visit(info.inputs[0])};
+        if (info.op == OpKind::Binary && info.binary_op == BinaryOp::Mul && (info.dtype == DType::F32 || info.dtype == DType::F16) &&
+            !map_[v]) {
+            if (auto c = g_.as_single_const(info.inputs[0])) return {(float)c->as_f64_value(), visit(info.inputs[1])};
+            if (auto c = g_.as_single_const(info.inputs[1])) return {(float)c->as_f64_value(), visit(info.inputs[0])};
         }
         return {1.0f, visit(v)};
     }
@@ -1214,7 +1316,7 @@ class Planner {
 
     PlanTensor visit_softmax(int v) {
         const ValueInfo& info = g_.values[v];
-        KN_CHECK(info.dtype == DType::F32, KN_ERR_UNSUPPORTED, "softmax needs f32");
+        KN_CHECK(info.dtype == DType::F32 || info.dtype == DType::F16, KN_ERR_UNSUPPORTED, "softmax needs f32 or f16");
         // softmax(c * x + mask): the scale and the additive term (an attention mask, usually a broadcast view)
         // are applied as the row is loaded instead of by an elementwise step of their own
         float scale = 1.f;
@@ -1222,7 +1324,7 @@ class Planner {
         std::optional<PlanTensor> term;
         const int input = info.inputs[0];
         const ValueInfo& ii = g_.values[input];
-        if (ii.op == OpKind::Binary && ii.binary_op == BinaryOp::Add && ii.dtype == DType::F32 && fusable(input) && !map_[input] &&
+        if (ii.op == OpKind::Binary && ii.binary_op == BinaryOp::Add && ii.dtype == info.dtype && fusable(input) && !map_[input] &&
             !match_epilogue(input)) {
             auto [s0, t0] = visit_scalable(ii.inputs[0]);
             auto [s1, t1] = visit_scalable(ii.inputs[1]);
@@ -1230,7 +1332,7 @@ class Planner {
             else if (s0 == 1.f && t0.ss.shape == t1.ss.shape) { scale = s1; in = t1; term = t0; }
         }
         if (!term) std::tie(scale, in) = visit_scalable(input);
-        PlanTensor out = alloc_shared(shape_of(v), DType::F32, v);
+        PlanTensor out = alloc_shared(shape_of(v), info.dtype, v);
         Step s;
         s.kind = StepKind::Softmax;
         s.value = v;
@@ -1248,6 +1350,7 @@ class Planner {
             s.row.in1_axis_stride = term->ss.strides[info.axis];
         }
         s.row.scale = scale;
+        s.row.half = info.dtype == DType::F16 ? 1 : 0;
         s.desc = "softmax rows=" + std::to_string(s.row.rows) + " len=" + std::to_string(s.row.len) + (term ? " +term" : "");
         if (out.ss.size() != 0) push_step(std::move(s));
         return out;
@@ -1256,7 +1359,7 @@ class Planner {
     // `a*x + b*y` -> the layernorm kernel's two inputs (kn-cuda-eval/src/planner.rs:522-552)
     PlanTensor visit_layernorm(int v) {
         const ValueInfo& info = g_.values[v];
-        KN_CHECK(info.dtype == DType::F32, KN_ERR_UNSUPPORTED, "layernorm needs f32");
+        KN_CHECK(info.dtype == DType::F32 || info.dtype == DType::F16, KN_ERR_UNSUPPORTED, "layernorm needs f32 or f16");
         int input = info.inputs[0];
         const ValueInfo& ii = g_.values[input];
         float a0 = 1.f, a1 = 0.f;
@@ -1275,7 +1378,7 @@ class Planner {
             a0 = s0;
             x0 = t0;
         }
-        PlanTensor out = alloc_shared(shape_of(v), DType::F32, v);
+        PlanTensor out = alloc_shared(shape_of(v), info.dtype, v);
         Step s;
         s.kind = StepKind::Layernorm;
         s.value = v;
@@ -1289,6 +1392,7 @@ class Planner {
         s.row.alpha0 = a0;
         s.row.alpha1 = a1;
         s.row.eps = info.eps;
+        s.row.half = info.dtype == DType::F16 ? 1 : 0;
         s.desc = "layernorm rows=" + std::to_string(s.row.rows) + " len=" + std::to_string(s.row.len) + (x1 ? " +res" : "");
         if (out.ss.size() != 0) push_step(std::move(s));
         return out;

@@ -7,8 +7,9 @@ namespace kn {
 
 // Builds the TMA tensor maps of a step marked `tensor_core` (needs the patched device pointers).
 // `status_word` is a device word the kernel raises when one of its bounded waits expires.
-// `flags`: the plan's kn_options.flags (KN_FLAG_*).
-void tc_prepare_step(Step& step, uint32_t* status_word, int flags);
+// `flags`: the plan's kn_options.flags (KN_FLAG_*).  `trace_words`: null, or 8 words of pinned host memory the
+// persistent matmul kernel writes progress markers to (KN_FLAG_TRACE_GEMM).
+void tc_prepare_step(Step& step, uint32_t* status_word, int flags, uint32_t* trace_words = nullptr);
 // Launches a step marked `tensor_core`; returns a cudaError_t as int.
 int tc_launch_step(const Step& step, cudaStream_t stream);
 

@@ -787,14 +787,14 @@ class Graph:
     # ---------------------------------------------------------------- row ops
     def softmax(self, input: Value, axis: int) -> Value:
         s, d = self.shape_dtype(input)
-        if d != DType.F32:
+        if d not in (DType.F32, DType.F16):     # (f16: this repository's storage extension)
             raise ValueError("Softmax input must be f32")
         _assert_axis(s, axis)
         return self._push(ValueInfo(s, d, OpKind.SOFTMAX, inputs=(input.index,), axis=axis))
 
     def layernorm(self, input: Value, axis: int, eps: float) -> Value:
         s, d = self.shape_dtype(input)
-        if d != DType.F32:
+        if d not in (DType.F32, DType.F16):
             raise ValueError("Layernorm input must be f32")
         _assert_axis(s, axis)
         eps = float(np.float32(eps))

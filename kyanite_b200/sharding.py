@@ -25,6 +25,43 @@ def batch_axis(shape) -> Optional[int]:
     return axes[0]
 
 
+def check_shardable(graph: Graph) -> None:
+    """Raises ValueError if some operation of `graph` combines different batch entries, so that evaluating
+    shards of the batch separately would give other numbers than evaluating the whole batch: a reduction,
+    softmax or layernorm along an axis whose size depends on the batch size, a matrix product that contracts
+    over one, a convolution with the batch size in its channels or image, a gather, slice, flip or concat
+    along one, or an all-reduce (that graph belongs to a tensor-parallel run, not a batch-sharded one)."""
+    from .graph import OpKind
+
+    def batchy(shape, axis) -> bool:
+        return shape[axis].exp > 0
+
+    for index, info in enumerate(graph.values):
+        k = info.kind
+        ins = [graph.values[i] for i in info.inputs]
+        reason = None
+        if k == OpKind.REDUCE and any(batchy(ins[0].shape, a) for a in info.axes):
+            reason = "reduces over a batch-sized axis"
+        elif k in (OpKind.SOFTMAX, OpKind.LAYERNORM) and batchy(ins[0].shape, info.axis):
+            reason = "normalises along a batch-sized axis"
+        elif k == OpKind.MATMUL and (batchy(ins[0].shape, 2) or batchy(ins[1].shape, 1)):
+            reason = "contracts over a batch-sized axis"
+        elif k == OpKind.CONV and (any(batchy(ins[0].shape, a) for a in (1, 2, 3)) or any(d.exp > 0 for d in ins[1].shape)):
+            reason = "convolves over a batch-sized axis"
+        elif k == OpKind.GATHER and batchy(ins[0].shape, info.axis):
+            reason = "gathers along a batch-sized axis"
+        elif k in (OpKind.SLICE, OpKind.FLIP) and batchy(ins[0].shape, info.axis):
+            reason = "slices or flips a batch-sized axis"
+        elif k == OpKind.CONCAT and batchy(info.shape, info.axis):
+            reason = "concatenates along a batch-sized axis"
+        elif k == OpKind.ALL_REDUCE:
+            reason = "is an all-reduce"
+        if reason:
+            raise ValueError(f"graph cannot be sharded by batch: value {index} ({k.name}) {reason}")
+    for v in list(graph.inputs) + list(graph.outputs):
+        batch_axis(graph[v].shape)
+
+
 def shard_sizes(global_batch: int, world: int) -> List[int]:
     """Per-rank batch sizes: as even as possible, earlier ranks take the remainder."""
     base, rem = divmod(global_batch, world)
@@ -32,6 +69,7 @@ def shard_sizes(global_batch: int, world: int) -> List[int]:
 
 
 def split_inputs(graph: Graph, inputs: Sequence[np.ndarray], global_batch: int, rank: int, world: int) -> List[np.ndarray]:
+    check_shardable(graph)
     sizes = shard_sizes(global_batch, world)
     start = sum(sizes[:rank])
     out = []

@@ -60,10 +60,12 @@ def _even_slice(total: int, rank: int, world: int, what: str) -> slice:
     return slice(rank * step, (rank + 1) * step)
 
 
-def llama_rank_graph(cfg: LlamaShape, rank: int, world: int, draw_slices_only: bool = False) -> Graph:
+def llama_rank_graph(cfg: LlamaShape, rank: int, world: int, draw_slices_only: bool = False, dtype="f32") -> Graph:
     """The one graph rank `rank` of `world` runs: token ids [B, seq] -> this rank's vocabulary slice of the
     logits [B, seq, vocab / world], with an all-reduce value after every row-parallel projection
-    (2 * layers of them, each [B, seq, d_model]).  `draw_slices_only`: see `llama_weights` (timing runs)."""
+    (2 * layers of them, each [B, seq, d_model]).  `draw_slices_only`: see `llama_weights` (timing runs).
+    `dtype`: "f32", or "f16" for half storage (weights, activations, all-reduce buffers and logits f16)."""
+    dt = DType.F16 if str(dtype).lower() in ("f16", "dtype.f16") or dtype == DType.F16 else DType.F32
     if not (0 <= rank < world):
         raise ValueError(f"rank {rank} outside world of size {world}")
     head_slice = _even_slice(cfg.heads, rank, world, "head count")
@@ -73,9 +75,9 @@ def llama_rank_graph(cfg: LlamaShape, rank: int, world: int, draw_slices_only: b
                       ffn_slice=ffn_slice, vocab_slice=vocab_slice, draw_slices_only=draw_slices_only)
     local_heads = head_slice.stop - head_slice.start
     g = Graph()
-    blocks = LlamaBlocks(g, cfg.d_model, cfg.d_model // cfg.heads, cfg.seq, cfg.eps, cfg.rope_base)
+    blocks = LlamaBlocks(g, cfg.d_model, cfg.d_model // cfg.heads, cfg.seq, cfg.eps, cfg.rope_base, dt)
     ids = g.input(shape(BATCH, cfg.seq), DType.I32)
-    x = g.view(g.gather(g.constant_tensor(w["table"]), 0, g.flatten(ids, 0)), shape(BATCH, cfg.seq, cfg.d_model))
+    x = g.view(g.gather(g.constant_tensor(w["table"].astype(dt.np)), 0, g.flatten(ids, 0)), shape(BATCH, cfg.seq, cfg.d_model))
     for layer in w["layers"]:
         x = g.add(x, g.all_reduce(blocks.attention_partial(x, layer, head_slice, local_heads)))
         x = g.add(x, g.all_reduce(blocks.ffn_partial(x, layer, ffn_slice)))

@@ -16,8 +16,13 @@ summation order is not reproducible; numpy's `matmul` stands in for it and resul
 with the reference's own tolerance rule (kn-cuda-eval/src/tester.rs:28-29).
 
 Pinning: every hand-computed expected output that the reference's tests hold for this path is
-replayed against this oracle in `tests/test_oracle_pins.py`.  F16 storage (an extension the
-reference does not have) is parity-unpinned.
+replayed against this oracle in `tests/test_oracle_pins.py`.
+
+F16 storage is an extension the reference does not have (kn-graph/src/dtype.rs:25-37 has no half type), so
+for it there is nothing to restate and nothing to pin against: PARITY UNPINNED.  The semantics chosen here:
+every value of dtype f16 is stored rounded to f16 (round to nearest even); each graph operation on f16
+values converts its operands to f32, computes as the f32 operation does (matmul: f32 products and sums;
+softmax / layernorm: f32 statistics) and rounds its result to f16 once.
 """
 from __future__ import annotations
 
@@ -211,6 +216,8 @@ def value_cast(x: np.ndarray, to) -> np.ndarray:
 
 
 def unary(op: int, cast: int, x: np.ndarray) -> np.ndarray:
+    if x.dtype == np.float16 and op not in (U_VALUE_CAST, U_BIT_CAST):
+        return unary(op, cast, x.astype(np.float32)).astype(np.float16)    # f16 storage: f32 arithmetic, one rounding
     t = x.dtype.type
     with np.errstate(all="ignore"):
         if op == U_ABS:
@@ -245,6 +252,9 @@ def unary(op: int, cast: int, x: np.ndarray) -> np.ndarray:
 
 
 def binary(op: int, l: np.ndarray, r: np.ndarray) -> np.ndarray:
+    if l.dtype == np.float16:
+        with np.errstate(all="ignore"):
+            return binary(op, l.astype(np.float32), r.astype(np.float32)).astype(np.float16)
     with np.errstate(all="ignore"):
         if l.dtype == np.bool_:
             # dtype.rs:726-757 and the derived Ord on DBool
@@ -324,6 +334,9 @@ def reduce_axis(op: int, x: np.ndarray, axis: int) -> np.ndarray:
 
 def softmax(x: np.ndarray, axis: int) -> np.ndarray:
     """cpu.rs:443-458"""
+    if x.dtype == np.float16:
+        with np.errstate(all="ignore"):
+            return softmax(x.astype(np.float32), axis).astype(np.float16)
     with np.errstate(all="ignore"):
         mx = np.fmax.reduce(x, axis=axis, keepdims=True, initial=np.float32(-np.inf))
         r = np.exp(x - mx)
@@ -333,6 +346,9 @@ def softmax(x: np.ndarray, axis: int) -> np.ndarray:
 
 def layernorm(x: np.ndarray, axis: int, eps) -> np.ndarray:
     """cpu.rs:461-479: biased variance of the centred values, eps inside the sqrt."""
+    if x.dtype == np.float16:
+        with np.errstate(all="ignore"):
+            return layernorm(x.astype(np.float32), axis, eps).astype(np.float16)
     with np.errstate(all="ignore"):
         n = np.float32(x.shape[axis])
         mean = np.add.reduce(x, axis=axis, keepdims=True, dtype=np.float32) / n
@@ -380,6 +396,8 @@ def batched_mat_mul(l: np.ndarray, r: np.ndarray) -> np.ndarray:
     """cpu.rs:421-439"""
     assert l.ndim == 3 and r.ndim == 3 and l.shape[0] == r.shape[0] and l.shape[2] == r.shape[1]
     with np.errstate(all="ignore"):
+        if l.dtype == np.float16:   # f16 storage: f32 products and sums, one rounding
+            return np.matmul(l.astype(np.float32), r.astype(np.float32)).astype(np.float16)
         return np.matmul(l, r)
 
 

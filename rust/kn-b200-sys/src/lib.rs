@@ -20,6 +20,7 @@ pub const KN_MATH_F32: i32 = 1;
 
 pub const KN_FLAG_NO_CONV_CHAIN: i32 = 1;
 pub const KN_FLAG_NO_PERSISTENT_GEMM: i32 = 2;
+pub const KN_FLAG_TRACE_GEMM: i32 = 4;
 
 pub const KN_MAX_RANK: usize = 8;
 pub const KN_COMM_ID_BYTES: usize = 128;
@@ -113,6 +114,9 @@ extern "C" {
 
     pub fn kn_matmul_tf32_static(a: *const f32, b: *const f32, c: *mut f32, m: i64, n: i64, k: i64, stream: *mut c_void) -> c_int;
     pub fn kn_matmul_tf32_static_status(code: *mut c_int) -> c_int;
+
+    pub fn kn_strided_shape(op: c_int, rank: c_int, shape: *const i64, strides: *const i64, n_args: c_int, args: *const i64,
+                            out_rank: *mut c_int, out_shape: *mut i64, out_strides: *mut i64, simple: *mut c_int, dense: *mut c_int) -> c_int;
 
     pub fn kn_scalar_unary(unary_op: c_int, from_dtype: c_int, to_dtype: c_int, x: u64, out: *mut u64) -> c_int;
     pub fn kn_scalar_binary(binary_op: c_int, dtype: c_int, a: u64, b: u64, out: *mut u64) -> c_int;

@@ -58,4 +58,4 @@ def main(reference_root: str):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    main(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("KN_REFERENCE_DIR", os.path.join(os.sep, "root", "reference")))

@@ -106,3 +106,31 @@ def test_unet_full_size():
     assert final_abs <= 2e-3 * final_scale, (final_abs, final_scale)
     print(f"unet full size: end-to-end max abs {e2e_abs:.3e} over all block outputs; final output max abs {final_abs:.3e} "
           f"on a scale of {final_scale:.3e}; worst block error / scale {worst_frac:.3e}")
+
+
+@pytest.mark.parametrize("dtype", ["f16", "f32"])
+def test_llama_layer_full_width(dtype):
+    """One decoder layer of the LLaMA-7B-shaped configuration at full width (d_model 4096, 32 heads of 128, SwiGLU
+    11008, 2048 tokens, causal mask, RoPE) plus final norm and a 1000-row slice of the lm head, against the oracle,
+    end to end and block by block.  f16: storage f16, accumulation f32 (an extension without reference vectors:
+    parity unpinned); f32: TF32 tensor cores."""
+    from kyanite_b200.graph import DType
+    dt = DType.F16 if dtype == "f16" else DType.F32
+    taps = []
+    graph, make_inputs = configs.llama_decoder(layers=1, vocab=1000, dtype=dt, taps=taps)
+    position = _with_tap_outputs(graph, taps)
+    inputs = make_inputs(1, 7)
+    blob = graph.to_bytes()
+    del graph
+    with CudaExecutor(0, blob, 1, math_mode=MATH_TF32) as ex:
+        got = ex.evaluate(inputs)
+    parsed = parse_graph(blob)
+    # f16: about 20 roundings to 11 bits on the path of an output; tf32: operands rounded to 11 bits, f32 sums
+    tol = 1e-2 if dtype == "f16" else 4e-3
+    expected = cpu_eval_graph(parsed, 1, inputs)
+    e2e_abs, _ = assert_tensors_match(expected, got, tol, tol, abs_scaled=True)
+    report = []
+    worst_frac, _ = _layerwise(parsed, taps, position, got, [0], inputs, tol, report)
+    # measured bound, asserted: one block's error stays below 4e-3 of its output's scale
+    assert worst_frac <= 4e-3, report
+    print(f"llama layer full width {dtype}: end-to-end max abs {e2e_abs:.3e}; worst block error / scale {worst_frac:.3e}")

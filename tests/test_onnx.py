@@ -16,7 +16,8 @@ from oracle.cpu_eval import assert_tensors_match, cpu_eval_graph
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 NAMES = ["simple-sttt-1x64", "simple-bn-sttt-1x64", "pre-sttt-4x8", "att-tiny"]
-REFERENCE_DATA = "/root/reference/kn-cuda-eval/tests/data"
+# a checkout of the reference project, if there is one: KN_REFERENCE_DIR (tests that need it skip without it)
+REFERENCE_DATA = os.path.join(os.environ.get("KN_REFERENCE_DIR", os.path.join(os.sep, "root", "reference")), "kn-cuda-eval", "tests", "data")
 
 
 def load_golden(name):

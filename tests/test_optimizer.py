@@ -207,7 +207,8 @@ def test_shared_affine_value_is_not_folded_twice():
 @pytest.mark.parametrize("name", ["simple-bn-sttt-1x64", "pre-sttt-4x8", "att-tiny"])
 def test_optimized_golden_model(name):
     from kyanite_b200.onnx import load_graph_from_onnx_path
-    path = os.path.join("/root/reference/kn-cuda-eval/tests/data", name + ".onnx")
+    reference = os.environ.get("KN_REFERENCE_DIR", os.path.join(os.sep, "root", "reference"))
+    path = os.path.join(reference, "kn-cuda-eval", "tests", "data", name + ".onnx")
     if not os.path.exists(path):
         pytest.skip("needs the reference checkout")
     z = np.load(os.path.join(GOLDEN, name + ".npz"))

@@ -10,7 +10,8 @@ import torch.multiprocessing as mp
 
 from kyanite_b200.configs import resnet_tower
 from kyanite_b200.graph import BATCH, DType, Graph, shape
-from kyanite_b200.sharding import aggregate_throughput, batch_axis, merge_outputs, shard_sizes, split_inputs
+from kyanite_b200.sharding import (aggregate_throughput, batch_axis, check_shardable, merge_outputs, shard_sizes,
+                                   split_inputs)
 from oracle.cpu_eval import cpu_eval_graph
 
 
@@ -70,3 +71,35 @@ def test_shard_helpers():
     assert np.array_equal(s0[0], x[:2]) and np.array_equal(s1[0], x[2:]) and s0[1] is tt
     with pytest.raises(ValueError):
         batch_axis((BATCH * BATCH,))
+
+
+def test_graphs_that_mix_batch_entries_are_refused():
+    from kyanite_b200 import configs
+    from kyanite_b200.graph import ReduceOp
+    # every workload graph is per-sample
+    for build in (configs.mlp, lambda: configs.resnet_tower(channels=8, blocks=1),
+                  lambda: configs.bert_encoder(layers=1, hidden=32, heads=2, ffn=64, vocab=50, seq=8),
+                  lambda: configs.unet_step(levels=(32,), res_blocks=1, attention_levels=(0,), heads=2, size=8, ctx_len=3,
+                                            ctx_dim=8, groups=8)):
+        check_shardable(build()[0])
+
+    def graph_with(f):
+        g = Graph()
+        g.output(f(g, g.input(shape(BATCH, 6))))
+        return g
+
+    bad = {
+        "reduces over": lambda g, x: g.reduce(x, [0], ReduceOp.SUM),
+        "normalises along": lambda g, x: g.softmax(x, 0),
+        "contracts over": lambda g, x: g.mat_mul(g.permute(x, [1, 0]), x),
+        "slices or flips": lambda g, x: g.flip(x, 0),
+        "is an all-reduce": lambda g, x: g.all_reduce(x),
+    }
+    for reason, f in bad.items():
+        g = graph_with(f)
+        with pytest.raises(ValueError, match=reason):
+            check_shardable(g)
+        with pytest.raises(ValueError, match="cannot be sharded"):
+            split_inputs(g, [np.zeros((4, 6), np.float32)], 4, 0, 2)
+    # the same operations along a per-sample axis are fine
+    check_shardable(graph_with(lambda g, x: g.softmax(g.flip(x, 1), 1)))
