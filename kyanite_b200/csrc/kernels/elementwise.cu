@@ -8,6 +8,7 @@
 //   scalar_generic_kernel  any dtype mix, one element per thread iteration, 64-bit value slots.
 //   scalar_vec4_kernel     all-f32 programs whose operands are contiguous (or broadcast) along the
 //                          innermost axis: 128-bit loads and stores, four elements per iteration.
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include <mutex>
@@ -115,6 +116,123 @@ __global__ void __launch_bounds__(kThreads) scalar_vec4_kernel(const __grid_cons
     }
 }
 
+// Programs over f16 and f32 values (the half-storage graphs: RoPE, SwiGLU, residual adds, the casts around a norm):
+// operands contiguous (or broadcast) along the innermost axis, eight elements per thread and iteration, so an
+// f16 operand moves as one 128-bit access and an f32 operand as two.  Values are carried as f32; an instruction
+// whose result type is f16 rounds its result to f16 (the storage semantics: every f16 value is rounded once per
+// operation), so the numbers equal the one-element-at-a-time kernel's.
+struct F8 {
+    float v[8];
+};
+
+__device__ __forceinline__ F8 load8(const void* base, DType dt, int64_t off, bool broadcast) {
+    F8 r;
+    if (dt == DType::F16) {
+        const __half* src = (const __half*)base + off;
+        if (broadcast) {
+            const float x = __half2float(__ldg(src));
+#pragma unroll
+            for (int i = 0; i < 8; i++) r.v[i] = x;
+        } else {
+            const uint4 u = __ldg((const uint4*)src);
+            const __half2* h = (const __half2*)&u;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float2 t = __half22float2(h[i]);
+                r.v[2 * i] = t.x;
+                r.v[2 * i + 1] = t.y;
+            }
+        }
+    } else {
+        const float* src = (const float*)base + off;
+        if (broadcast) {
+            const float x = __ldg(src);
+#pragma unroll
+            for (int i = 0; i < 8; i++) r.v[i] = x;
+        } else {
+            const float4 a = __ldg((const float4*)src), b = __ldg((const float4*)src + 1);
+            r.v[0] = a.x; r.v[1] = a.y; r.v[2] = a.z; r.v[3] = a.w;
+            r.v[4] = b.x; r.v[5] = b.y; r.v[6] = b.z; r.v[7] = b.w;
+        }
+    }
+    return r;
+}
+
+__device__ __forceinline__ void store8(void* base, DType dt, int64_t off, const F8& x) {
+    if (dt == DType::F16) {
+        uint4 u;
+        __half2* h = (__half2*)&u;
+#pragma unroll
+        for (int i = 0; i < 4; i++) h[i] = __floats2half2_rn(x.v[2 * i], x.v[2 * i + 1]);
+        *(uint4*)((__half*)base + off) = u;
+    } else {
+        float4* dst = (float4*)((float*)base + off);
+        dst[0] = make_float4(x.v[0], x.v[1], x.v[2], x.v[3]);
+        dst[1] = make_float4(x.v[4], x.v[5], x.v[6], x.v[7]);
+    }
+}
+
+template <typename I>
+__global__ void __launch_bounds__(kThreads) scalar_vec8_kernel(const __grid_constant__ ScalarParams p) {
+    pdl_enter();
+    const int last = p.rank - 1;
+    const I inner8 = (I)(p.dims[last] >> 3);
+    const I total8 = (I)(p.total >> 3);
+    const I step = (I)gridDim.x * (I)blockDim.x;
+    for (I idx = (I)blockIdx.x * (I)blockDim.x + (I)threadIdx.x; idx < total8; idx += step) {
+        int64_t off[SCALAR_MAX_OPERANDS];
+        I rem = idx / inner8;
+        const int64_t inner = (int64_t)(idx - rem * inner8) * 8;
+#pragma unroll
+        for (int o = 0; o < SCALAR_MAX_OPERANDS; o++) off[o] = 0;
+        for (int o = 0; o < p.n_operands; o++) off[o] = inner * p.strides[o][last];
+        for (int d = last - 1; d >= 0; d--) {
+            const I dim = (I)p.dims[d];
+            const I q = rem / dim;
+            const int64_t i = (int64_t)(rem - q * dim);
+            rem = q;
+            for (int o = 0; o < p.n_operands; o++) off[o] += i * p.strides[o][d];
+        }
+
+        F8 slot[kSlots];
+        for (int l = 0; l < p.n_loads; l++) {
+            const int o = p.load_operand[l];
+            slot[l] = load8(p.ptr[o], (DType)p.dtype[o], off[o], p.strides[o][last] == 0);
+        }
+        for (int k = 0; k < p.n_instr; k++) {
+            const ScalarInstr in = p.instr[k];
+            F8 r;
+            if (in.kind == 0) {
+                const float c = (DType)in.dtype == DType::F16 ? f16_bits_to_f32((uint16_t)in.imm) : bits_to_f32(in.imm);
+#pragma unroll
+                for (int i = 0; i < 8; i++) r.v[i] = c;
+            } else if (in.kind == 1) {
+                const F8 a = slot[in.a];
+                const UnaryOp op = (UnaryOp)in.op;
+                if (op == UnaryOp::ValueCast) r = a;   // f16 <-> f32: the value; rounding to f16 happens below
+                else {
+#pragma unroll
+                    for (int i = 0; i < 8; i++) r.v[i] = f32_unary(op, a.v[i]);
+                }
+            } else {
+                const F8 a = slot[in.a], b = slot[in.b];
+                const BinaryOp op = (BinaryOp)in.op;
+#pragma unroll
+                for (int i = 0; i < 8; i++) r.v[i] = f32_binary(op, a.v[i], b.v[i]);
+            }
+            if ((DType)in.dtype == DType::F16 && in.kind != 0) {
+#pragma unroll
+                for (int i = 0; i < 8; i++) r.v[i] = __half2float(__float2half_rn(r.v[i]));
+            }
+            slot[p.n_loads + k] = r;
+        }
+        for (int s = 0; s < p.n_stores; s++) {
+            const int o = p.store_operand[s];
+            store8(p.ptr[o], (DType)p.dtype[o], off[o], slot[p.store_slot[s]]);
+        }
+    }
+}
+
 int grid_for(int64_t work_items) {
     int64_t blocks = (work_items + kThreads - 1) / kThreads;
     const int64_t cap = 148 * 8;   // 8 resident blocks of 256 threads per SM
@@ -175,7 +293,13 @@ __device__ __forceinline__ void binary_v(BinaryOp op, Vec<V>& acc, const Vec<V>&
     }
 }
 
-template <int V, bool RANK1>
+// round to f16 and back: the value an f16-typed result is stored as
+__device__ __forceinline__ float round_f16(float x) { return __half2float(__float2half_rn(x)); }
+
+// MIXED: operands and values may be f16 as well as f32 (V is even then).  Values travel as f32; an f16 operand is
+// converted on load and store (four elements = 8 bytes per position), and a micro-op whose result type is f16
+// rounds its result to f16, which is what storing every intermediate as f16 would give.
+template <int V, bool RANK1, bool MIXED>
 __global__ void __launch_bounds__(kThreads) scalar_acc_kernel(const __grid_constant__ ScalarParams p) {
     pdl_enter();
     extern __shared__ float4 spill[];   // [slot][position][thread]
@@ -184,8 +308,12 @@ __global__ void __launch_bounds__(kThreads) scalar_acc_kernel(const __grid_const
     const uint32_t total_v = (uint32_t)(p.total / (4 * V));
     const uint32_t step = gridDim.x * blockDim.x;
     uint32_t inner_bytes[kRegOperands];   // bytes between two consecutive float4 positions (0 = broadcast)
+    bool is_half[kRegOperands];
 #pragma unroll
-    for (int o = 0; o < kRegOperands; o++) inner_bytes[o] = o < p.n_operands && p.strides[o][last] != 0 ? 16u : 0u;
+    for (int o = 0; o < kRegOperands; o++) {
+        is_half[o] = MIXED && o < p.n_operands && (DType)p.dtype[o] == DType::F16;
+        inner_bytes[o] = o < p.n_operands && p.strides[o][last] != 0 ? (is_half[o] ? 8u : 16u) : 0u;
+    }
     float4* const my_spill = spill + threadIdx.x;
     auto slot_read = [&](int slot, Vec<V>& out) {
 #pragma unroll
@@ -214,14 +342,18 @@ __global__ void __launch_bounds__(kThreads) scalar_acc_kernel(const __grid_const
         }
         const char* base[kRegOperands];
 #pragma unroll
-        for (int o = 0; o < kRegOperands; o++) base[o] = o < p.n_operands ? (const char*)p.ptr[o] + (size_t)off[o] * 4u : nullptr;
-        auto operand = [&](int o, uint32_t* stride_bytes) -> const char* {
+        for (int o = 0; o < kRegOperands; o++)
+            base[o] = o < p.n_operands ? (const char*)p.ptr[o] + (size_t)off[o] * (is_half[o] ? 2u : 4u) : nullptr;
+        auto operand = [&](int o, uint32_t* stride_bytes, bool* half) -> const char* {
             switch (o) {
-                case 0: *stride_bytes = inner_bytes[0]; return base[0];
-                case 1: *stride_bytes = inner_bytes[1]; return base[1];
-                case 2: *stride_bytes = inner_bytes[2]; return base[2];
-                default: *stride_bytes = inner_bytes[3]; return base[3];
+                case 0: *stride_bytes = inner_bytes[0]; *half = is_half[0]; return base[0];
+                case 1: *stride_bytes = inner_bytes[1]; *half = is_half[1]; return base[1];
+                case 2: *stride_bytes = inner_bytes[2]; *half = is_half[2]; return base[2];
+                default: *stride_bytes = inner_bytes[3]; *half = is_half[3]; return base[3];
             }
+        };
+        auto imm_value = [&](const ScalarInstr& in) {
+            return MIXED && (DType)in.dtype == DType::F16 ? f16_bits_to_f32((uint16_t)in.imm) : bits_to_f32(in.imm);
         };
 
         Vec<V> acc;
@@ -234,7 +366,7 @@ __global__ void __launch_bounds__(kThreads) scalar_acc_kernel(const __grid_const
             switch (in.kind) {
                 case 0:
 #pragma unroll
-                    for (int v = 0; v < V; v++) acc.v[v] = splat(bits_to_f32(in.imm));
+                    for (int v = 0; v < V; v++) acc.v[v] = splat(imm_value(in));
                     break;
                 case 1: unary_v<V>((UnaryOp)in.op, acc, a); break;
                 case 2:
@@ -243,8 +375,26 @@ __global__ void __launch_bounds__(kThreads) scalar_acc_kernel(const __grid_const
                     break;
                 case 3: {
                     uint32_t sb;
-                    const char* src = operand(in.a, &sb);
-                    if (sb) {
+                    bool half;
+                    const char* src = operand(in.a, &sb, &half);
+                    if (MIXED && half) {
+                        if (sb) {
+                            // 8 halves (two positions) per 128-bit load
+#pragma unroll
+                            for (int v = 0; v < V; v += 2) {
+                                const uint4 u = __ldg((const uint4*)(src + v * 8));
+                                const __half2* h = (const __half2*)&u;
+                                const float2 f0 = __half22float2(h[0]), f1 = __half22float2(h[1]), f2 = __half22float2(h[2]),
+                                             f3 = __half22float2(h[3]);
+                                acc.v[v] = make_float4(f0.x, f0.y, f1.x, f1.y);
+                                acc.v[v + 1] = make_float4(f2.x, f2.y, f3.x, f3.y);
+                            }
+                        } else {
+                            const float4 x = splat(__half2float(__ldg((const __half*)src)));
+#pragma unroll
+                            for (int v = 0; v < V; v++) acc.v[v] = x;
+                        }
+                    } else if (sb) {
 #pragma unroll
                         for (int v = 0; v < V; v++) acc.v[v] = __ldg((const float4*)(src + v * 16));
                     } else {
@@ -256,21 +406,40 @@ __global__ void __launch_bounds__(kThreads) scalar_acc_kernel(const __grid_const
                 }
                 case 4: {
                     uint32_t sb;
-                    char* dst = const_cast<char*>(operand(in.b, &sb));
+                    bool half;
+                    char* dst = const_cast<char*>(operand(in.b, &sb, &half));
+                    if (MIXED && half) {
 #pragma unroll
-                    for (int v = 0; v < V; v++) *(float4*)(dst + v * 16) = a.v[v];
+                        for (int v = 0; v < V; v += 2) {
+                            uint4 u;
+                            __half2* h = (__half2*)&u;
+                            h[0] = __floats2half2_rn(a.v[v].x, a.v[v].y);
+                            h[1] = __floats2half2_rn(a.v[v].z, a.v[v].w);
+                            h[2] = __floats2half2_rn(a.v[v + 1].x, a.v[v + 1].y);
+                            h[3] = __floats2half2_rn(a.v[v + 1].z, a.v[v + 1].w);
+                            *(uint4*)(dst + v * 8) = u;
+                        }
+                    } else {
+#pragma unroll
+                        for (int v = 0; v < V; v++) *(float4*)(dst + v * 16) = a.v[v];
+                    }
                     break;
                 }
                 case 5:
 #pragma unroll
-                    for (int v = 0; v < V; v++) b.v[v] = splat(bits_to_f32(in.imm));
+                    for (int v = 0; v < V; v++) b.v[v] = splat(imm_value(in));
                     binary_v<V>((BinaryOp)in.op, acc, a, b);
                     break;
                 default:
 #pragma unroll
-                    for (int v = 0; v < V; v++) b.v[v] = splat(bits_to_f32(in.imm));
+                    for (int v = 0; v < V; v++) b.v[v] = splat(imm_value(in));
                     binary_v<V>((BinaryOp)in.op, acc, b, a);
                     break;
+            }
+            if (MIXED && (DType)in.dtype == DType::F16 && (in.kind == 1 || in.kind == 2 || in.kind >= 5)) {
+#pragma unroll
+                for (int v = 0; v < V; v++)
+                    acc.v[v] = make_float4(round_f16(acc.v[v].x), round_f16(acc.v[v].y), round_f16(acc.v[v].z), round_f16(acc.v[v].w));
             }
             if (in.pad != 255) {
 #pragma unroll
@@ -280,27 +449,27 @@ __global__ void __launch_bounds__(kThreads) scalar_acc_kernel(const __grid_const
     }
 }
 
-template <int V>
+template <int V, bool MIXED>
 int launch_acc(const ScalarParams& p, cudaStream_t stream) {
     const int64_t groups = p.total / (4 * V);
     const int grid = grid_for(groups);
     const size_t smem = (size_t)p.n_regs * V * kThreads * sizeof(float4);
     static std::mutex mu;
-    static bool done[64] = {false};
+    static bool done[64] = {false};   // (one set per instantiation of this template)
     int device = 0;
     cudaGetDevice(&device);
     {
         std::lock_guard<std::mutex> lock(mu);
         if (device >= 0 && device < 64 && !done[device]) {
-            cudaError_t e1 = cudaFuncSetAttribute(scalar_acc_kernel<V, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024);
-            cudaError_t e2 = cudaFuncSetAttribute(scalar_acc_kernel<V, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024);
+            cudaError_t e1 = cudaFuncSetAttribute(scalar_acc_kernel<V, true, MIXED>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024);
+            cudaError_t e2 = cudaFuncSetAttribute(scalar_acc_kernel<V, false, MIXED>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024);
             if (e1 != cudaSuccess) return (int)e1;
             if (e2 != cudaSuccess) return (int)e2;
             done[device] = true;
         }
     }
-    if (p.rank == 1) launch_pdl(scalar_acc_kernel<V, true>, dim3(grid), dim3(kThreads), (size_t)(smem), stream, p);
-    else launch_pdl(scalar_acc_kernel<V, false>, dim3(grid), dim3(kThreads), (size_t)(smem), stream, p);
+    if (p.rank == 1) launch_pdl(scalar_acc_kernel<V, true, MIXED>, dim3(grid), dim3(kThreads), (size_t)(smem), stream, p);
+    else launch_pdl(scalar_acc_kernel<V, false, MIXED>, dim3(grid), dim3(kThreads), (size_t)(smem), stream, p);
     return (int)cudaGetLastError();
 }
 
@@ -396,7 +565,7 @@ bool as_transpose(const ScalarParams& p, TransposeParams& q) {
 
 int launch_scalar(const ScalarParams& p, cudaStream_t stream) {
     if (p.total == 0) return 0;
-    if (p.vec4 != 2) {
+    if (p.vec4 != 2 && p.vec4 != 4) {
         TransposeParams q;
         if (as_transpose(p, q)) {
             int64_t blocks = q.tiles_s * q.tiles_t;
@@ -409,9 +578,18 @@ int launch_scalar(const ScalarParams& p, cudaStream_t stream) {
         // V consecutive float4 positions per thread: as many as the innermost extent and the spill slots
         // (n_regs * V * 4 KB of shared memory per block) allow
         const int64_t inner4 = p.dims[p.rank - 1] / 4;
-        if (inner4 % 4 == 0 && p.n_regs <= 4) return launch_acc<4>(p, stream);
-        if (inner4 % 2 == 0) return launch_acc<2>(p, stream);
-        return launch_acc<1>(p, stream);
+        if (inner4 % 4 == 0 && p.n_regs <= 4) return launch_acc<4, false>(p, stream);
+        if (inner4 % 2 == 0) return launch_acc<2, false>(p, stream);
+        return launch_acc<1, false>(p, stream);
+    } else if (p.vec4 == 4) {
+        // f16 / f32 mix as an accumulator program: the innermost extent is a multiple of 8 (the planner's condition)
+        const int64_t inner4 = p.dims[p.rank - 1] / 4;
+        if (inner4 % 4 == 0 && p.n_regs <= 4) return launch_acc<4, true>(p, stream);
+        return launch_acc<2, true>(p, stream);
+    } else if (p.vec4 == 3) {
+        const int64_t total8 = p.total >> 3;
+        if (total8 < (1ll << 31)) launch_pdl(scalar_vec8_kernel<uint32_t>, dim3(grid_for(total8)), dim3(kThreads), (size_t)(0), stream, p);
+        else launch_pdl(scalar_vec8_kernel<uint64_t>, dim3(grid_for(total8)), dim3(kThreads), (size_t)(0), stream, p);
     } else if (p.vec4) {
         const int64_t total4 = p.total >> 2;
         if (total4 < (1ll << 31)) launch_pdl(scalar_vec4_kernel<uint32_t>, dim3(grid_for(total4)), dim3(kThreads), (size_t)(0), stream, p);

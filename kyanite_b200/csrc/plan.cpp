@@ -304,9 +304,36 @@ class Planner {
             }
         }
         p.vec4 = vec ? 1 : 0;
+        if (!vec && dims.back() % 8 == 0) {
+            // f16 / f32 mix (half-storage graphs): the eight-elements-per-access kernel
+            bool vec8 = true, any_half = false;
+            for (int k = 0; k < p.n_instr && vec8; k++) {
+                const DType d = (DType)p.instr[k].dtype, f = (DType)p.instr[k].from;
+                vec8 = (d == DType::F32 || d == DType::F16) && (f == DType::F32 || f == DType::F16) &&
+                       !(p.instr[k].kind == 1 && (UnaryOp)p.instr[k].op == UnaryOp::BitCast);
+            }
+            for (int o = 0; o < p.n_operands && vec8; o++) {
+                const PlanTensor& t = s.operands[o];
+                const int64_t inner = strides[o].back();
+                const bool is_store = o >= p.n_loads;
+                if (t.dtype != DType::F32 && t.dtype != DType::F16) { vec8 = false; break; }
+                any_half = any_half || t.dtype == DType::F16;
+                if (!(inner == 1 || (inner == 0 && !is_store))) { vec8 = false; break; }
+                const int64_t align = t.dtype == DType::F16 ? 8 : 4;
+                if (inner == 1) {
+                    if (t.offset % align != 0) vec8 = false;
+                    for (int d = 0; d + 1 < p.rank; d++)
+                        if (strides[o][d] % align != 0) vec8 = false;
+                } else if (t.offset % 1 != 0) {
+                    vec8 = false;
+                }
+            }
+            if (vec8 && any_half) p.vec4 = 3;
+        }
         // the accumulator-program kernel computes element offsets in 32 bits and keeps four operand addresses
         // in registers: non-negative strides, no operand may reach 2^31 elements from its start
-        bool small = vec && total < (1ll << 31) && p.n_operands <= 4;
+        const bool mixed = p.vec4 == 3;
+        bool small = (vec || mixed) && total < (1ll << 31) && p.n_operands <= 4;
         for (int o = 0; o < p.n_operands && small; o++) {
             int64_t reach = 0;
             for (int d = 0; d < p.rank; d++) {
@@ -315,7 +342,7 @@ class Planner {
             }
             if (reach >= (1ll << 31) - 16) small = false;
         }
-        if (small && allocate_registers(p)) p.vec4 = 2;
+        if (small && allocate_registers(p)) p.vec4 = mixed ? 4 : 2;
         push_step(std::move(s));
     }
 
@@ -343,6 +370,7 @@ class Planner {
             Op o;
             o.m.kind = 0;
             o.m.imm = p.instr[v - p.n_loads].imm;
+            o.m.dtype = p.instr[v - p.n_loads].dtype;   // how to read `imm`
             o.result = v;
             const_op[v] = (int)ops.size();
             ops.push_back(o);
@@ -1930,7 +1958,7 @@ std::string Plan::describe() const {
         os << "step " << i << " " << step_kind_name(s.kind) << (s.tensor_core ? "/tc" : "") << " value=" << s.value << " " << s.desc;
         if (s.kind == StepKind::Scalar)
             os << " loads=" << s.scalar.n_loads << " instr=" << s.scalar.n_instr << " rank=" << s.scalar.rank
-               << (s.scalar.vec4 ? " vec4" : "");
+               << (s.scalar.vec4 >= 3 ? " vec8" : (s.scalar.vec4 ? " vec4" : ""));
         os << " bytes=" << (uint64_t)s.alg_bytes << " flops=" << (uint64_t)s.flops << " [";
         for (size_t o = 0; o < s.operands.size(); o++) os << (o ? " " : "") << (s.writes[o] ? "w:" : "r:") << s.operands[o].str();
         os << "]\n";
