@@ -157,6 +157,11 @@ struct Executor {
                     s.im2col.in = (const float*)ptr[0];
                     s.im2col.col = (float*)ptr[1];
                     break;
+                case StepKind::RmsNorm:
+                    s.rms.in = ptr[0];
+                    s.rms.out = ptr[1];
+                    s.rms.gain = ptr.size() > 2 ? (const float*)ptr[2] : nullptr;
+                    break;
                 case StepKind::AllReduce:
                     s.all_reduce.in = ptr[0];
                     s.all_reduce.out = ptr[1];
@@ -188,6 +193,7 @@ struct Executor {
             case StepKind::Conv: err = s.tensor_core ? tc_launch_step(s, stream) : launch_conv_simt(s.conv, stream); break;
             case StepKind::ConvChain: err = tc_launch_step(s, stream); break;
             case StepKind::Im2col: err = launch_im2col(s.im2col, stream); break;
+            case StepKind::RmsNorm: err = launch_rmsnorm(s.rms, stream); break;
             case StepKind::AllReduce: {
                 const AllReduceParams& a = s.all_reduce;
                 if (comm != nullptr && comm->world > 1)

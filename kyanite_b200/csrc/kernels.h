@@ -85,6 +85,18 @@ struct RowParams {
                              // statistics and the arithmetic stay f32, the result is rounded to f16 once
 };
 
+// ---- root-mean-square norm over the innermost axis:  out = x / sqrt(mean(x^2) + eps) * gain.  The IR has no such
+// operation; the planner recognises the pow / mean / sqrt / div / mul subgraph (with the value casts around it in
+// half-storage graphs) and this one kernel takes the place of five elementwise and reduce steps.
+struct RmsNormParams {
+    const void* in;          // [rows, len], rows `in_row_stride` elements apart, f32 or f16
+    void* out;               // [rows, len] dense, f32 or f16
+    const float* gain;       // [len] f32 with element stride `gain_stride`, or null
+    int64_t rows, len, in_row_stride, out_row_stride, gain_stride;
+    float eps;
+    int32_t in_half, out_half;
+};
+
 // ---- gather along one axis with rank-1 indices: replaces autokernel/gather.{rs,cu}
 struct GatherParams {
     const void* in;
@@ -190,6 +202,7 @@ int launch_scalar(const ScalarParams& p, cudaStream_t stream);
 int launch_reduce(const ReduceParams& p, cudaStream_t stream);
 int launch_softmax(const RowParams& p, cudaStream_t stream);      // dispatches on p.half
 int launch_layernorm(const RowParams& p, cudaStream_t stream);
+int launch_rmsnorm(const RmsNormParams& p, cudaStream_t stream);  // kernels/rows_f16.cu
 int launch_softmax_f16(const RowParams& p, cudaStream_t stream);  // kernels/rows_f16.cu
 int launch_layernorm_f16(const RowParams& p, cudaStream_t stream);
 int launch_gather(const GatherParams& p, cudaStream_t stream);

@@ -248,7 +248,7 @@ int grid_for(int64_t work_items) {
 // again later are also copied to a numbered spill slot in shared memory ([slot][position][thread] float4:
 // conflict-free 128-bit accesses, and the run-time slot number is just an address).  Every thread carries V
 // consecutive float4 positions through the program; all loads of the program are issued first.
-constexpr int kRegOperands = 4;
+constexpr int kRegOperandsF32 = 4, kRegOperandsMixed = 6;   // operand addresses kept in registers
 
 template <int V>
 struct Vec {
@@ -277,6 +277,7 @@ __device__ __forceinline__ void unary_v(UnaryOp op, Vec<V>& acc, const Vec<V>& a
         case UnaryOp::Sigmoid: map1(acc, a, [](float x) { return 1.0f / (1.0f + expf(-x)); }); break;
         case UnaryOp::Tanh: map1(acc, a, [](float x) { return tanhf(x); }); break;
         case UnaryOp::Erf: map1(acc, a, [](float x) { return erff(x); }); break;
+        case UnaryOp::ValueCast: acc = a; break;   // between f16 and f32 values, which travel as f32 (mixed programs only)
         default: map1(acc, a, [op](float x) { return f32_unary(op, x); }); break;
     }
 }
@@ -301,6 +302,7 @@ __device__ __forceinline__ float round_f16(float x) { return __half2float(__floa
 // rounds its result to f16, which is what storing every intermediate as f16 would give.
 template <int V, bool RANK1, bool MIXED>
 __global__ void __launch_bounds__(kThreads) scalar_acc_kernel(const __grid_constant__ ScalarParams p) {
+    constexpr int kRegOperands = MIXED ? kRegOperandsMixed : kRegOperandsF32;
     pdl_enter();
     extern __shared__ float4 spill[];   // [slot][position][thread]
     const int last = p.rank - 1;
@@ -349,7 +351,9 @@ __global__ void __launch_bounds__(kThreads) scalar_acc_kernel(const __grid_const
                 case 0: *stride_bytes = inner_bytes[0]; *half = is_half[0]; return base[0];
                 case 1: *stride_bytes = inner_bytes[1]; *half = is_half[1]; return base[1];
                 case 2: *stride_bytes = inner_bytes[2]; *half = is_half[2]; return base[2];
-                default: *stride_bytes = inner_bytes[3]; *half = is_half[3]; return base[3];
+                case 3: *stride_bytes = inner_bytes[3]; *half = is_half[3]; return base[3];
+                case 4: *stride_bytes = inner_bytes[kRegOperands - 2]; *half = is_half[kRegOperands - 2]; return base[kRegOperands - 2];
+                default: *stride_bytes = inner_bytes[kRegOperands - 1]; *half = is_half[kRegOperands - 1]; return base[kRegOperands - 1];
             }
         };
         auto imm_value = [&](const ScalarInstr& in) {
@@ -368,7 +372,14 @@ __global__ void __launch_bounds__(kThreads) scalar_acc_kernel(const __grid_const
 #pragma unroll
                     for (int v = 0; v < V; v++) acc.v[v] = splat(imm_value(in));
                     break;
-                case 1: unary_v<V>((UnaryOp)in.op, acc, a); break;
+                case 1:
+                    if (MIXED && (DType)in.dtype == DType::F16 && (UnaryOp)in.op == UnaryOp::Sigmoid)
+                        // the result is rounded to f16 below: the hardware exponential and reciprocal (errors near
+                        // 2^-21) are exact enough, and the exact ones would bound a kernel that moves 2-byte elements
+                        map1(acc, a, [](float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); });
+                    else
+                        unary_v<V>((UnaryOp)in.op, acc, a);
+                    break;
                 case 2:
                     if (in.b != 255) slot_read(in.b, b);
                     binary_v<V>((BinaryOp)in.op, acc, a, b);
@@ -480,8 +491,8 @@ int launch_acc(const ScalarParams& p, cudaStream_t stream) {
 // 32 x 64 tile through shared memory: rows of 128 bytes on both sides, eight loads per thread in flight.
 constexpr int kTransposeT = 64;   // tile extent along t (32 along s)
 struct TransposeParams {
-    const uint32_t* src;
-    uint32_t* dst;
+    const void* src;                // elements of 4 bytes (transpose_copy_kernel<uint32_t>) or 2 bytes (<uint16_t>: f16 storage)
+    void* dst;
     int64_t ns, nt;                 // extents of the two axes
     int64_t src_t_stride, dst_s_stride;
     int64_t tiles_s, tiles_t;
@@ -489,9 +500,10 @@ struct TransposeParams {
     int64_t outer_dims[DEV_MAX_RANK], outer_src[DEV_MAX_RANK], outer_dst[DEV_MAX_RANK];
 };
 
+template <typename T>
 __global__ void __launch_bounds__(256) transpose_copy_kernel(const __grid_constant__ TransposeParams q) {
     pdl_enter();
-    __shared__ uint32_t tile[kTransposeT][33];
+    __shared__ T tile[kTransposeT][33 + (sizeof(T) == 2 ? 1 : 0)];   // (odd number of 4-byte words per row either way)
     int64_t rem = blockIdx.x;
     const int64_t ts = rem % q.tiles_s;
     rem /= q.tiles_s;
@@ -506,11 +518,11 @@ __global__ void __launch_bounds__(256) transpose_copy_kernel(const __grid_consta
     }
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
     const int64_t s0 = ts * 32, t0 = tt * kTransposeT;
-    uint32_t r[kTransposeT / 8];
+    T r[kTransposeT / 8];
 #pragma unroll
     for (int j = 0; j < kTransposeT / 8; j++) {
         const int64_t t = t0 + ty + 8 * j, s2 = s0 + tx;
-        r[j] = (t < q.nt && s2 < q.ns) ? __ldg(q.src + src_off + s2 + t * q.src_t_stride) : 0u;
+        r[j] = (t < q.nt && s2 < q.ns) ? __ldg((const T*)q.src + src_off + s2 + t * q.src_t_stride) : (T)0;
     }
 #pragma unroll
     for (int j = 0; j < kTransposeT / 8; j++) tile[ty + 8 * j][tx] = r[j];
@@ -520,7 +532,7 @@ __global__ void __launch_bounds__(256) transpose_copy_kernel(const __grid_consta
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             const int64_t s2 = s0 + ty + 8 * j, t = t0 + 32 * h + tx;
-            if (t < q.nt && s2 < q.ns) q.dst[dst_off + t + s2 * q.dst_s_stride] = tile[32 * h + tx][ty + 8 * j];
+            if (t < q.nt && s2 < q.ns) ((T*)q.dst)[dst_off + t + s2 * q.dst_s_stride] = tile[32 * h + tx][ty + 8 * j];
         }
     }
 }
@@ -531,7 +543,7 @@ bool as_transpose(const ScalarParams& p, TransposeParams& q) {
     const int src = p.load_operand[0], dst = p.store_operand[0];
     if (src == dst || p.store_slot[0] != 0 || p.dtype[src] != p.dtype[dst]) return false;
     const DType dt = (DType)p.dtype[src];
-    if (dt != DType::F32 && dt != DType::I32 && dt != DType::U32) return false;
+    if (dtype_size(dt) != 4 && dtype_size(dt) != 2) return false;
     int s_axis = -1, t_axis = -1;
     for (int d = 0; d < p.rank; d++) {
         if (p.dims[d] <= 1) continue;
@@ -540,8 +552,8 @@ bool as_transpose(const ScalarParams& p, TransposeParams& q) {
     }
     if (s_axis < 0 || t_axis < 0 || s_axis == t_axis) return false;
     if (p.dims[s_axis] < 16 || p.dims[t_axis] < 16) return false;
-    q.src = (const uint32_t*)p.ptr[src];
-    q.dst = (uint32_t*)p.ptr[dst];
+    q.src = p.ptr[src];
+    q.dst = p.ptr[dst];
     q.ns = p.dims[s_axis];
     q.nt = p.dims[t_axis];
     q.src_t_stride = p.strides[src][t_axis];
@@ -570,7 +582,10 @@ int launch_scalar(const ScalarParams& p, cudaStream_t stream) {
         if (as_transpose(p, q)) {
             int64_t blocks = q.tiles_s * q.tiles_t;
             for (int d = 0; d < q.n_outer; d++) blocks *= q.outer_dims[d];
-            launch_pdl(transpose_copy_kernel, dim3((unsigned)blocks), dim3(256), (size_t)0, stream, q);
+            if (dtype_size((DType)p.dtype[p.load_operand[0]]) == 2)
+                launch_pdl(transpose_copy_kernel<uint16_t>, dim3((unsigned)blocks), dim3(256), (size_t)0, stream, q);
+            else
+                launch_pdl(transpose_copy_kernel<uint32_t>, dim3((unsigned)blocks), dim3(256), (size_t)0, stream, q);
             return (int)cudaGetLastError();
         }
     }

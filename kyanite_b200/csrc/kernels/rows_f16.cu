@@ -128,17 +128,20 @@ __global__ void __launch_bounds__(256) rows_f16_vec_kernel(const __grid_constant
         for (int i = 0; i < ITEMS; i++)
 #pragma unroll
             for (int j = 0; j < 8; j++) {
-                v[i][j] = expf(v[i][j] - mx);   // padding: exp(-inf) = 0
+                // (the hardware exponential: its error, about 2^-21 relative, is far below the f16 step the result
+                // is rounded to; with half the bytes per element of an f32 row the exact expf would bound the kernel)
+                v[i][j] = __expf(v[i][j] - mx);   // padding: exp(-inf) = 0
                 sum += v[i][j];
             }
         sum = reduce_row<TPR, false>(sum, smem);
         if (!active) return;
+        const float inv = 1.0f / sum;
 #pragma unroll
         for (int i = 0; i < ITEMS; i++) {
             const int e = i * TPR + t;
             if (e < len8) {
 #pragma unroll
-                for (int j = 0; j < 8; j++) v[i][j] = v[i][j] / sum;
+                for (int j = 0; j < 8; j++) v[i][j] = v[i][j] * inv;
                 out[e] = pack8(v[i]);
             }
         }
@@ -161,14 +164,14 @@ __global__ void __launch_bounds__(256) rows_f16_vec_kernel(const __grid_constant
             }
         }
         const float var = reduce_row<TPR, false>(sq, smem) / n;
-        const float denom = sqrtf(var + p.eps);
+        const float inv = 1.0f / sqrtf(var + p.eps);
         if (!active) return;
 #pragma unroll
         for (int i = 0; i < ITEMS; i++) {
             const int e = i * TPR + t;
             if (e < len8) {
 #pragma unroll
-                for (int j = 0; j < 8; j++) v[i][j] = v[i][j] / denom;
+                for (int j = 0; j < 8; j++) v[i][j] = v[i][j] * inv;
                 out[e] = pack8(v[i]);
             }
         }
@@ -215,6 +218,67 @@ __global__ void __launch_bounds__(256) rows_f16_streaming_kernel(const __grid_co
     }
 }
 
+// One block of 256 threads per row, the row (up to 16384 elements, a multiple of 8) in registers as f32: one read,
+// one write.
+template <bool IN_HALF, bool OUT_HALF, int ITEMS>
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const __grid_constant__ RmsNormParams p) {
+    pdl_enter();
+    __shared__ float smem[8];
+    const int64_t row = blockIdx.x;
+    const int t = threadIdx.x;
+    const int len8 = (int)(p.len >> 3);
+    float v[ITEMS][8];
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < ITEMS; i++) {
+        const int e = i * 256 + t;
+        if (e < len8) {
+            if (IN_HALF) {
+                unpack8(__ldg((const uint4*)((const __half*)p.in + row * p.in_row_stride) + e), v[i]);
+            } else {
+                const float4* src = (const float4*)((const float*)p.in + row * p.in_row_stride) + 2 * e;
+                const float4 a = __ldg(src), b = __ldg(src + 1);
+                v[i][0] = a.x; v[i][1] = a.y; v[i][2] = a.z; v[i][3] = a.w;
+                v[i][4] = b.x; v[i][5] = b.y; v[i][6] = b.z; v[i][7] = b.w;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; j++) sq += v[i][j] * v[i][j];
+        }
+    }
+    const float ms = reduce_row<256, false>(sq, smem) / (float)p.len;
+    const float inv = 1.0f / sqrtf(ms + p.eps);
+#pragma unroll
+    for (int i = 0; i < ITEMS; i++) {
+        const int e = i * 256 + t;
+        if (e < len8) {
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                float y = v[i][j] * inv;
+                if (p.gain != nullptr) y *= __ldg(p.gain + (int64_t)(e * 8 + j) * p.gain_stride);
+                v[i][j] = y;
+            }
+            if (OUT_HALF) {
+                *((uint4*)((__half*)p.out + row * p.out_row_stride) + e) = pack8(v[i]);
+            } else {
+                float4* dst = (float4*)((float*)p.out + row * p.out_row_stride) + 2 * e;
+                dst[0] = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
+                dst[1] = make_float4(v[i][4], v[i][5], v[i][6], v[i][7]);
+            }
+        }
+    }
+}
+
+template <bool IN_HALF, bool OUT_HALF>
+int launch_rmsnorm_t(const RmsNormParams& p, cudaStream_t stream) {
+    const int items = (int)((p.len / 8 + 255) / 256);
+    const dim3 grid((unsigned)p.rows), block(256);
+    if (items <= 1) launch_pdl(rmsnorm_kernel<IN_HALF, OUT_HALF, 1>, grid, block, (size_t)0, stream, p);
+    else if (items <= 2) launch_pdl(rmsnorm_kernel<IN_HALF, OUT_HALF, 2>, grid, block, (size_t)0, stream, p);
+    else if (items <= 4) launch_pdl(rmsnorm_kernel<IN_HALF, OUT_HALF, 4>, grid, block, (size_t)0, stream, p);
+    else launch_pdl(rmsnorm_kernel<IN_HALF, OUT_HALF, 8>, grid, block, (size_t)0, stream, p);
+    return (int)cudaGetLastError();
+}
+
 bool vec_ok(const RowParams& p, bool softmax) {
     if (p.len % 8 != 0 || p.len > 16384 || p.in_axis_stride != 1 || p.out_axis_stride != 1) return false;
     if (((uintptr_t)p.in0 & 15) || ((uintptr_t)p.out & 15) || (p.in1 && ((uintptr_t)p.in1 & 15))) return false;
@@ -253,6 +317,14 @@ int launch_rows(const RowParams& p, cudaStream_t stream) {
 }
 
 }  // namespace
+
+// The planner emits this step only for rows it has checked: len a multiple of 8 and at most 16384, rows 16-byte aligned.
+int launch_rmsnorm(const RmsNormParams& p, cudaStream_t stream) {
+    if (p.rows == 0 || p.len == 0) return 0;
+    if (p.rows > 0x7FFFFFFFll || p.len % 8 != 0 || p.len > 16384) return (int)cudaErrorInvalidValue;
+    if (p.in_half) return p.out_half ? launch_rmsnorm_t<true, true>(p, stream) : launch_rmsnorm_t<true, false>(p, stream);
+    return p.out_half ? launch_rmsnorm_t<false, true>(p, stream) : launch_rmsnorm_t<false, false>(p, stream);
+}
 
 int launch_softmax_f16(const RowParams& p, cudaStream_t stream) { return launch_rows<true>(p, stream); }
 int launch_layernorm_f16(const RowParams& p, cudaStream_t stream) { return launch_rows<false>(p, stream); }

@@ -14,7 +14,7 @@
 namespace kn {
 
 const char* step_kind_name(StepKind k) {
-    static const char* names[] = {"Scalar", "Reduce", "Softmax", "Layernorm", "Gather", "Gemm", "Conv", "ConvChain", "Im2col", "AllReduce"};
+    static const char* names[] = {"Scalar", "Reduce", "Softmax", "Layernorm", "Gather", "Gemm", "Conv", "ConvChain", "Im2col", "AllReduce", "RmsNorm"};
     return (int)k < (int)StepKind::COUNT ? names[(int)k] : "?";
 }
 
@@ -333,7 +333,7 @@ class Planner {
         // the accumulator-program kernel computes element offsets in 32 bits and keeps four operand addresses
         // in registers: non-negative strides, no operand may reach 2^31 elements from its start
         const bool mixed = p.vec4 == 3;
-        bool small = (vec || mixed) && total < (1ll << 31) && p.n_operands <= 4;
+        bool small = (vec || mixed) && total < (1ll << 31) && p.n_operands <= (mixed ? 6 : 4);   // (the kernel's register operands)
         for (int o = 0; o < p.n_operands && small; o++) {
             int64_t reach = 0;
             for (int d = 0; d < p.rank; d++) {
@@ -500,6 +500,7 @@ class Planner {
 
     PlanTensor visit_new(int v) {
         if (auto fused = try_fused_contraction(v)) return *fused;
+        if (auto fused = try_fused_rmsnorm(v)) return *fused;
         const ValueInfo& info = g_.values[v];
         std::vector<int64_t> shape = shape_of(v);
         switch (info.op) {
@@ -945,6 +946,136 @@ class Planner {
         auto rs = out.ss.view(root_shape);
         KN_CHECK(rs.has_value(), KN_ERR_INTERNAL, "view of a dense contraction output failed");
         return out.with(*rs);
+    }
+
+    // ---------------------------------------------------------------- root-mean-square norm
+    // The IR has no RMS norm; decoder graphs compose it as
+    //     t = x (f32), or value_cast(x, f32) for f16 storage
+    //     y = t / broadcast(sqrt(view(mean(pow(t, 2), last axis)) + eps)) [* broadcast(gain)]   [value_cast(y, f16)]
+    // which planned node by node is five steps that move the activations five times.  Matched here from its last node
+    // (every node in between hidden and used by this expression only, `t` by the power and the division only) and
+    // emitted as ONE RmsNorm step: one read, one write.  The kernel multiplies by 1/sqrt(..) where the graph divides
+    // by sqrt(..): a difference of an f32 rounding step.
+    std::optional<PlanTensor> try_fused_rmsnorm(int root) {
+        auto is_binary = [&](int v, BinaryOp op) { return g_.values[v].op == OpKind::Binary && g_.values[v].binary_op == op; };
+        auto is_cast_to = [&](int v, DType to) {
+            const ValueInfo& i = g_.values[v];
+            return i.op == OpKind::Unary && i.unary_op == UnaryOp::ValueCast && i.dtype == to;
+        };
+        const ValueInfo& ri = g_.values[root];
+        int cur = root;
+        DType out_dtype = DType::F32;
+        if (is_cast_to(root, DType::F16)) {
+            out_dtype = DType::F16;
+            cur = ri.inputs[0];
+            if (!fusable(cur) || map_[cur]) return std::nullopt;
+        }
+        if (g_.values[cur].dtype != DType::F32) return std::nullopt;
+        // optional gain
+        int gain = -1, div = cur;
+        if (is_binary(cur, BinaryOp::Mul)) {
+            const ValueInfo& mi = g_.values[cur];
+            for (int side = 0; side < 2 && gain < 0; side++) {
+                const int d = mi.inputs[side], b = mi.inputs[1 - side];
+                if (is_binary(d, BinaryOp::Div) && fusable(d) && !map_[d] && g_.values[b].op == OpKind::Broadcast) {
+                    div = d;
+                    gain = g_.values[b].inputs[0];
+                }
+            }
+            if (gain < 0) return std::nullopt;
+        }
+        if (!is_binary(div, BinaryOp::Div)) return std::nullopt;
+        const ValueInfo& di = g_.values[div];
+        const int t = di.inputs[0], br = di.inputs[1];
+        if (g_.values[br].op != OpKind::Broadcast || !fusable(br) || map_[br]) return std::nullopt;
+        const int sq = g_.values[br].inputs[0];
+        const ValueInfo& si = g_.values[sq];
+        if (si.op != OpKind::Unary || si.unary_op != UnaryOp::Sqrt || !fusable(sq) || map_[sq]) return std::nullopt;
+        const int add = si.inputs[0];
+        if (!is_binary(add, BinaryOp::Add) || !fusable(add) || map_[add]) return std::nullopt;
+        int view = -1;
+        float eps = 0.f;
+        for (int side = 0; side < 2 && view < 0; side++) {
+            auto c = g_.as_single_const(g_.values[add].inputs[1 - side]);
+            if (c && c->dtype == DType::F32 && g_.values[g_.values[add].inputs[side]].op == OpKind::View) {
+                view = g_.values[add].inputs[side];
+                eps = c->as_f32();
+            }
+        }
+        if (view < 0 || !fusable(view) || map_[view]) return std::nullopt;
+        const int red = g_.values[view].inputs[0];
+        const ValueInfo& rdi = g_.values[red];
+        const int rank = (int)g_.values[t].shape.size();
+        if (rdi.op != OpKind::Reduce || rdi.reduce_op != ReduceOp::Mean || rdi.axes.size() != 1 || rdi.axes[0] != rank - 1 || rank < 1 ||
+            !fusable(red) || map_[red])
+            return std::nullopt;
+        const int pw = rdi.inputs[0];
+        if (!is_binary(pw, BinaryOp::Pow) || !fusable(pw) || map_[pw] || g_.values[pw].inputs[0] != t) return std::nullopt;
+        auto two = g_.as_single_const(g_.values[pw].inputs[1]);
+        if (!two || two->dtype != DType::F32 || two->as_f32() != 2.0f) return std::nullopt;
+        if (g_.values[t].dtype != DType::F32) return std::nullopt;
+        if (shape_of(view) != [&] { auto s = shape_of(t); s.back() = 1; return s; }()) return std::nullopt;
+        if (shape_of(root) != shape_of(t)) return std::nullopt;
+        // `t` itself is read, unless it is a cast from f16 that only this expression uses: then the f16 value is read
+        int source = t;
+        if (is_cast_to(t, DType::F32) && g_.values[g_.values[t].inputs[0]].dtype == DType::F16 && g_.is_hidden_with_uses(t, 2) && !map_[t])
+            source = g_.values[t].inputs[0];
+        if (gain >= 0) {
+            // one f32 value per position of the last axis, the same for every row
+            const std::vector<int64_t> gs = shape_of(gain);
+            bool per_column = g_.values[gain].dtype == DType::F32 && gs.size() == shape_of(t).size() && gs.back() == shape_of(t).back();
+            for (size_t d = 0; per_column && d + 1 < gs.size(); d++) per_column = gs[d] == 1;
+            if (!per_column) return std::nullopt;
+        }
+        const std::vector<int64_t> sh = shape_of(t);
+        const int64_t len = sh.back();
+        int64_t rows = 1;
+        for (size_t d = 0; d + 1 < sh.size(); d++) rows *= sh[d];
+        if (len % 8 != 0 || len > 16384 || rows > 0x7FFFFFFFll) return std::nullopt;
+
+        // from here on steps are emitted: nothing may fail any more
+        PlanTensor in = source == t ? visit(t) : visit(source);
+        const int64_t in_align = in.dtype == DType::F16 ? 8 : 4;
+        auto flat = in.ss.view({rows, len});
+        if (!flat || flat->strides[1] != 1 || (rows > 1 && flat->strides[0] % in_align != 0) || in.offset % in_align != 0) {
+            in = ensure_simple_copy(in, source);
+            flat = in.ss.view({rows, len});
+            KN_CHECK(flat.has_value(), KN_ERR_INTERNAL, "view of a dense tensor failed");
+        }
+        std::optional<PlanTensor> g_t;
+        int64_t gain_stride = 0;
+        if (gain >= 0) {
+            PlanTensor gt = visit(gain);
+            gain_stride = gt.ss.strides.back();
+            g_t = gt;
+        }
+        PlanTensor out = alloc_shared(sh, out_dtype, root);
+        Step s;
+        s.kind = StepKind::RmsNorm;
+        s.value = root;
+        s.operands = {in, out};
+        s.writes = {0, 1};
+        if (g_t) {
+            s.operands.push_back(*g_t);
+            s.writes.push_back(0);
+        }
+        s.rms.rows = rows;
+        s.rms.len = len;
+        s.rms.in_row_stride = rows > 1 ? flat->strides[0] : len;
+        s.rms.out_row_stride = len;
+        s.rms.gain_stride = gain_stride;
+        s.rms.eps = eps;
+        s.rms.in_half = in.dtype == DType::F16 ? 1 : 0;
+        s.rms.out_half = out_dtype == DType::F16 ? 1 : 0;
+        s.desc = "rmsnorm rows=" + std::to_string(rows) + " len=" + std::to_string(len) + (g_t ? " *gain" : "") + " " +
+                 dtype_name(in.dtype) + "->" + dtype_name(out_dtype);
+        if (out.ss.size() != 0) push_step(std::move(s));
+        return out;
+    }
+    PlanTensor ensure_simple_copy(const PlanTensor& t, int value) {
+        PlanTensor dense = alloc_shared(t.ss.shape, t.dtype, value);
+        emit_copy(t, dense, value);
+        return dense;
     }
 
     // ---------------------------------------------------------------- f16 storage (an extension: the reference has no half type)

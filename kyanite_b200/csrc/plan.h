@@ -46,7 +46,7 @@ struct PlanTensor {
 
 struct TcLaunch;   // tensor maps and launch geometry of a tensor-core step (kernels/contract_tc.cu)
 
-enum class StepKind : uint8_t { Scalar = 0, Reduce, Softmax, Layernorm, Gather, Gemm, Conv, ConvChain, Im2col, AllReduce, COUNT };
+enum class StepKind : uint8_t { Scalar = 0, Reduce, Softmax, Layernorm, Gather, Gemm, Conv, ConvChain, Im2col, AllReduce, RmsNorm, COUNT };
 const char* step_kind_name(StepKind k);
 
 struct Step {
@@ -70,6 +70,7 @@ struct Step {
     ConvChainParams chain{};
     Im2colParams im2col{};
     AllReduceParams all_reduce{};
+    RmsNormParams rms{};
 };
 
 struct Plan {

@@ -87,6 +87,37 @@ def test_llama_f16_lowers_and_oracle_is_close_to_f32():
     assert np.max(np.abs(h.astype(np.float32) - f)) <= 4e-3 * np.max(np.abs(f))
     for mode in (MATH_TF32, MATH_F32):
         assert sum(kinds(plan_describe(g16, 2, mode)).values()) > 0
+    # every RMS norm (two per layer and the final one) is ONE step, in the f16 graph (casts around it) and the f32 one:
+    # no reduce step and no elementwise step of the pow / mean / sqrt / div / mul subgraph is left
+    for g in (g16, g32):
+        k = kinds(plan_describe(g, 2, MATH_TF32))
+        assert k["RmsNorm"] == 2 * kw["layers"] + 1 and k["Reduce"] == 0, k
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [DType.F16, DType.F32], ids=["f16", "f32"])
+@pytest.mark.parametrize("rows,length,with_gain", [(64, 4096, True), (5, 64, False), (3, 16384, True), (7, 100, True)])
+def test_rmsnorm_subgraph_matches_oracle(rows, length, with_gain, dtype):
+    """The pow / mean / sqrt / div (/ mul) subgraph decoder graphs spell an RMS norm with: fused into one step when
+    the row length is a multiple of 8 (at most 16384), planned node by node otherwise; both must agree with the oracle."""
+    from kyanite_b200.executor import CudaExecutor
+    from kyanite_b200.graph import BinaryOp, ReduceOp, UnaryOp
+    r = rng(rows * length)
+    g = Graph()
+    x = g.input(shape(rows, length), dtype)
+    t = g.value_cast(x, DType.F32) if dtype == DType.F16 else x
+    ms = g.view(g.reduce(g.pow(t, g.scalar(2.0)), [1], ReduceOp.MEAN), shape(rows, 1))
+    y = g.binary(BinaryOp.DIV, t, g.unary(UnaryOp.SQRT, g.add(ms, g.scalar(1e-6))))
+    if with_gain:
+        y = g.mul(y, g.constant_tensor((1 + 0.1 * r.standard_normal((1, length))).astype(np.float32)))
+    g.output(g.value_cast(y, DType.F16) if dtype == DType.F16 else y)
+    ins = [(r.standard_normal((rows, length)) * 2).astype(dtype.np)]
+    expected = cpu_eval_graph(g.to_bytes(), 0, ins)
+    k = kinds(plan_describe(g, 0))
+    assert (k["RmsNorm"] == 1 and len(k) == 1) if length % 8 == 0 else k["RmsNorm"] == 0
+    tol = 2e-3 if dtype == DType.F16 else 1e-4
+    with CudaExecutor(0, g, 0) as ex:
+        assert_tensors_match(expected, ex.evaluate(ins), tol, tol, abs_scaled=True)
 
 
 # ------------------------------------------------------------------------------------------------ GPU
