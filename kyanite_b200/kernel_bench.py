@@ -8,7 +8,7 @@ over its algorithmic bytes (memory-bound steps) or TFLOP/s over its FLOP (contra
 
 Working sets are several times the 126 MB L2, so back-to-back launches still stream from HBM.  Peaks come
 from MEASURED_PEAKS.json at the repository root when present (copy bandwidth, bf16 GEMM burst; TF32 is
-taken as half the bf16 figure), else the fallback 6650 GB/s / 1590 TFLOP/s.
+taken as half the bf16 figure, f16 operands as the bf16 figure itself), else the fallback 6650 GB/s / 1590 TFLOP/s.
 """
 from __future__ import annotations
 
@@ -161,6 +161,56 @@ def case_transpose(rng):
     return g, 0, [rng.standard_normal((384, 512, 64)).astype(np.float32)]
 
 
+def _linear_f16_case(m, n, k):
+    def build(rng):
+        g = Graph()
+        x = g.input(shape(m, k), DType.F16)
+        w = g.constant_tensor((rng.standard_normal((n, k)) * 0.02).astype(np.float16))
+        g.output(g.linear(x, w))
+        return g, 0, [rng.standard_normal((m, k)).astype(np.float16)]
+    build.__doc__ = f"Linear layer [{m}, {k}] x [{k}, {n}] in f16 storage, f32 accumulation (kind::f16 tensor cores)"
+    return build
+
+
+def case_softmax_f16_masked(rng):
+    """LLaMA prefill attention probabilities in f16: softmax(scores / sqrt(128) + causal mask) over [32 x 2048, 2048]."""
+    g = Graph()
+    x = g.input(shape(32, 2048, 2048), DType.F16)
+    mask = g.constant_tensor(np.triu(np.full((2048, 2048), -np.inf, np.float16), 1).reshape(1, 2048, 2048))
+    g.output(g.softmax(g.add(g.mul(x, g.scalar(1.0 / math.sqrt(128.0), DType.F16)), mask), 2))
+    return g, 0, [rng.standard_normal((32, 2048, 2048)).astype(np.float16)]
+
+
+def case_rmsnorm_f16(rng):
+    """LLaMA RMS norm in f16 storage, the pow / mean / sqrt / div / mul subgraph as one step: [16384, 4096]."""
+    g = Graph()
+    x = g.input(shape(16384, 4096), DType.F16)
+    t = g.value_cast(x, DType.F32)
+    ms = g.view(g.reduce(g.pow(t, g.scalar(2.0)), [1], ReduceOp.MEAN), shape(16384, 1))
+    y = g.mul(g.binary(BinaryOp.DIV, t, g.unary(UnaryOp.SQRT, g.add(ms, g.scalar(1e-6)))),
+              g.constant_tensor((1 + 0.02 * rng.standard_normal((1, 4096))).astype(np.float32)))
+    g.output(g.value_cast(y, DType.F16))
+    return g, 0, [rng.standard_normal((16384, 4096)).astype(np.float16)]
+
+
+def case_swiglu_f16(rng):
+    """LLaMA feed-forward gate in f16: gate * sigmoid(gate) * up over [8192, 11008]."""
+    g = Graph()
+    a = g.input(shape(8192, 11008), DType.F16)
+    b = g.input(shape(8192, 11008), DType.F16)
+    g.output(g.mul(g.mul(a, g.sigmoid(a)), b))
+    return g, 0, [rng.standard_normal((8192, 11008)).astype(np.float16) for _ in range(2)]
+
+
+def case_residual_add_f16(rng):
+    """Residual add of two f16 [16384, 4096] tensors."""
+    g = Graph()
+    a = g.input(shape(16384, 4096), DType.F16)
+    b = g.input(shape(16384, 4096), DType.F16)
+    g.output(g.add(a, b))
+    return g, 0, [rng.standard_normal((16384, 4096)).astype(np.float16) for _ in range(2)]
+
+
 CASES = {
     "gelu": case_gelu,
     "residual_add": case_residual_add,
@@ -182,7 +232,18 @@ CASES = {
     "conv_unet_mid": _conv_case(2, 1280, 8, 8, 1280, 3, 1, 1, "UNet middle-block convolution: 3x3, 1280 -> 1280, batch 2, 8x8 (Im2col + split-K matmul)"),
     "conv_unet_pointwise": _conv_case(8, 320, 64, 64, 320, 1, 1, 0, "UNet 1x1 projection: 320 -> 320, batch 8, 64x64 (Im2col as transpose + matmul)"),
     "transpose": case_transpose,
+    "linear_llama_proj_f16": _linear_f16_case(2048, 4096, 4096),
+    "linear_llama_ffn_f16": _linear_f16_case(2048, 11008, 4096),
+    "linear_llama_down_f16": _linear_f16_case(2048, 4096, 11008),
+    "softmax_f16_masked": case_softmax_f16_masked,
+    "rmsnorm_f16": case_rmsnorm_f16,
+    "swiglu_f16": case_swiglu_f16,
+    "residual_add_f16": case_residual_add_f16,
 }
+
+
+def _is_f16(name: str) -> bool:
+    return "f16" in name
 
 
 def load_peaks():
@@ -212,8 +273,10 @@ def run_case(name: str, launches: int, device: int):
             us = ex.time_step(idx, launches)
             rec = {"case": name, "step": idx, "kind": kind, "desc": desc, "us": round(us, 2)}
             if flops > 0:
-                rec.update(bound="tensor", achieved=round(flops / us / 1e6, 1), unit="TFLOP/s", peak=tf32,
-                           frac=round(flops / us / 1e6 / tf32, 3))
+                # f16 operands: the dense f16 / bf16 rate (the measured bf16 GEMM figure); f32 storage: TF32, half of it
+                peak = 2.0 * tf32 if _is_f16(name) else tf32
+                rec.update(bound="tensor", achieved=round(flops / us / 1e6, 1), unit="TFLOP/s", peak=peak,
+                           frac=round(flops / us / 1e6 / peak, 3))
             else:
                 rec.update(bound="hbm", achieved=round(alg_bytes / us / 1e3, 1), unit="GB/s", peak=hbm,
                            frac=round(alg_bytes / us / 1e3 / hbm, 3), bytes=int(alg_bytes))
