@@ -63,6 +63,7 @@ struct ChainKernelParams {
     int32_t n_layers, per_cta, gx, gy, wp, q_first, r_first, n_mma, rows_alloc, slots, tmem_cols, c_blocks_max;
     int32_t total_tiles;
     int32_t group;   // filter tiles per request and per ring slot
+    long long* trace; // KN_CHAIN_TRACE only: per layer 8 clock64 stamps of CTA 0, in pinned host memory
     uint8_t flags[kMaxChainLayers];
     uint8_t c_blocks[kMaxChainLayers];
     uint32_t* status;
@@ -92,11 +93,35 @@ __device__ __forceinline__ void tmem_load_16_nowait(uint32_t taddr, uint32_t (&v
         : "memory");
 }
 
+__device__ __forceinline__ void tmem_store_8(uint32_t taddr, const uint32_t (&v)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_load_8_nowait(uint32_t taddr, uint32_t (&v)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "r"(taddr)
+                 : "memory");
+}
+template <int CW> __device__ __forceinline__ void tmem_store_chunk(uint32_t taddr, const uint32_t (&v)[CW]) {
+    if constexpr (CW == 16) tmem_store_16(taddr, v); else tmem_store_8(taddr, v);
+}
+template <int CW> __device__ __forceinline__ void tmem_load_chunk_nowait(uint32_t taddr, uint32_t (&v)[CW]) {
+    if constexpr (CW == 16) tmem_load_16_nowait(taddr, v); else tmem_load_8_nowait(taddr, v);
+}
+
+// Suspend-time hint of the kernel's mbarrier waits: a waiting thread is woken when the phase completes, so the hint
+// only bounds how long it sleeps between two looks at the abandon flag.
+constexpr uint32_t kSleepNs = 20000u;
+
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-template <int E>   // epilogue warps per TMEM lane quarter
+// E: epilogue warps per TMEM lane quarter; CW: accumulator columns per epilogue chunk (16 or 8); TRACE: whether the
+// first CTA stamps its phases
+template <int E, int CW, bool TRACE>
 __global__ void __launch_bounds__(64 + 128 * E, 1)
 conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_constant__ ChainKernelParams p) {
     constexpr int kChainThreads = 64 + 128 * E;
@@ -116,7 +141,9 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
     volatile uint32_t* tmem_slot = (volatile uint32_t*)(gen_base + (slot_addr - base));
     volatile int* abandon = (volatile int*)(gen_base + (slot_addr + 4u - base));
     uint32_t* colinfo = (uint32_t*)(gen_base + (slot_addr + 8u - base));         // 256 entries
-    uint32_t* realmask = colinfo + 256;                                          // 16 entries: per 16-column chunk, which columns are real pixels
+    uint32_t* realmask = colinfo + 256;                                          // 32 entries: per CW-column chunk, which columns are real pixels
+    const uint32_t dummy_rows = slot_addr + 8u + 1024u + 128u + 24u;             // (16-byte aligned) 128 bytes nobody reads: where the stores of padding positions go
+    volatile int* epilogue_go = (volatile int*)(realmask + 32);                  // 2 entries: the accumulator poller's verdict, per layer parity
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -126,7 +153,7 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
             mbar_init(empty_bar + 8u * s, 1);
         }
         mbar_init(accum_bar, 1);
-        mbar_init(act_bar, kEpilogueThreads);
+        mbar_init(act_bar, kEpilogueThreads / 32);   // one arrival per epilogue warp
         *abandon = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -153,10 +180,10 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
         colinfo[n] = info;
     }
     __syncthreads();
-    if (threadIdx.x >= 64 && threadIdx.x < 80) {
+    if (threadIdx.x >= 64 && threadIdx.x < 64 + 256 / CW) {
         const int c = threadIdx.x - 64;
         uint32_t m = 0;
-        for (int j = 0; j < 16; j++) m |= (colinfo[c * 16 + j] >> 31) << j;
+        for (int j = 0; j < CW; j++) m |= (colinfo[c * CW + j] >> 31) << j;
         realmask[c] = m;
     }
     if (warp == 0) {
@@ -186,7 +213,7 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
             int idx = (int)((blockIdx.x * 5u) % (uint32_t)groups);
             for (int i = 0; i < groups; i++) {
                 if (round > 0) {
-                    if (!mbar_wait(empty_bar + 8u * slot, (uint32_t)((round & 1) ^ 1), abandon, p.status, 11)) { ok = false; break; }
+                    if (!mbar_wait(empty_bar + 8u * slot, (uint32_t)((round & 1) ^ 1), abandon, p.status, 11, kWaitCycles, kSleepNs)) { ok = false; break; }
                 }
                 const uint32_t bar = full_bar + 8u * slot;
                 mbar_expect_tx(bar, (uint32_t)g * kTileBytes);
@@ -204,10 +231,14 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
         const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(p.n_mma >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
         int slot = 0, round = 0;
         bool ok = true;
+        const bool trace = TRACE && blockIdx.x == 0;
         for (int l = 0; l < p.n_layers && ok; l++) {
+            long long t0 = 0, full_wait = 0;
+            if (trace) t0 = clock64();
             // the layer's input is complete in shared memory and the accumulator has been read out
-            ok = mbar_wait(act_bar, (uint32_t)(l & 1), abandon, p.status, 12);
+            ok = mbar_wait(act_bar, (uint32_t)(l & 1), abandon, p.status, 12, kWaitCycles, kSleepNs);
             if (!ok) break;
+            if (trace) p.trace[l * 8 + 0] = t0, p.trace[l * 8 + 1] = clock64();
             tc_fence_after();
             // The next kernel of the stream may be scheduled once every CTA is in its last layer: early enough
             // to hide that kernel's launch and set-up, late enough that its CTAs do not sit on this SM (blocked
@@ -224,8 +255,11 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
             int tap = tile / cbl, cb = tile - tap * cbl;
             if (pointwise) tap = 4;     // the centre tap: the operand starts at the pixel itself
             for (int i = 0; i < groups && ok; i++) {
-                ok = mbar_wait(full_bar + 8u * slot, (uint32_t)(round & 1), abandon, p.status, 13);
+                long long tw = 0;
+                if (trace) tw = clock64();
+                ok = mbar_wait(full_bar + 8u * slot, (uint32_t)(round & 1), abandon, p.status, 13, kWaitCycles, kSleepNs);
                 if (!ok) break;
+                if (trace) full_wait += clock64() - tw;
                 tc_fence_after();
                 for (int u = 0; u < g; u++) {
                     const int r = tap >= 6 ? 2 : (tap >= 3 ? 1 : 0), s = tap - 3 * r;
@@ -246,6 +280,7 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
                 if (++slot == p.slots) { slot = 0; round++; }
             }
             if (ok) mma_commit(accum_bar);
+            if (trace) p.trace[l * 8 + 2] = clock64(), p.trace[l * 8 + 3] = full_wait;
         }
     } else if (warp >= 2) {
         // ---------------- epilogue: thread <-> accumulator lane <-> channel; the two warps of a lane
@@ -258,13 +293,14 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
         const bool has_block = (ch >> 5) < p.c_blocks_max;     // narrower layers: no operand rows for these channels
         const uint32_t chunk = (uint32_t)(ch >> 2) & 7u;
         // this channel's 4 bytes inside a 128-byte row of its 32-channel block, before the swizzle
-        const int chunks16 = (p.n_mma + 15) >> 4;
+        const int chunks = p.n_mma / CW;      // n_mma is a multiple of 16
         // Output column n is stored in row r_first + n of the channel's block; r_first is a multiple of 8, so
         // the swizzle phase of a row (row & 7) is the column's n & 7, known at compile time inside the
         // unrolled loops: the eight swizzled chunk offsets are computed once.
         uint32_t sw[8];
 #pragma unroll
         for (int i = 0; i < 8; i++) sw[i] = (chunk ^ (uint32_t)i) << 4;
+        const uint32_t block_rows = base + (uint32_t)(ch >> 5) * block_bytes + (uint32_t)p.r_first * 128u;   // this quarter's channel block, row of column 0
         const uint32_t my_rows = base + (uint32_t)(ch >> 5) * block_bytes + (uint32_t)(ch & 3) * 4u + (uint32_t)p.r_first * 128u;
         // round to TF32 (nearest, ties away from zero) with integer arithmetic: the tensor core ignores
         // the low 13 mantissa bits, so adding half an ulp of TF32 to the magnitude is all it takes
@@ -279,24 +315,25 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
             if (ch >= p.head_begin[i] && ch < p.head_begin[i + 1]) head = i;
         // layer 0's input: from global memory into the operand layout and the held-tensor columns
         asm volatile("griddepcontrol.wait;" ::: "memory");
-        for (int c = half; c < chunks16; c += E) {
-            uint32_t v[16];
+        for (int c = half; c < chunks; c += E) {
+            uint32_t v[CW];
 #pragma unroll
-            for (int j = 0; j < 16; j++) {
-                const uint32_t info = colinfo[c * 16 + j];
+            for (int j = 0; j < CW; j++) {
+                const uint32_t info = colinfo[c * CW + j];
                 float x = 0.f;
                 if ((info >> 31) && ch < p.c_in)
                     x = p.in[(img0 + ((info >> 16) & 0xFF)) * p.s_in[0] + (int64_t)ch * p.s_in[1] + (int64_t)((info >> 8) & 0xFF) * p.s_in[2] +
                              (int64_t)(info & 0xFF) * p.s_in[3]];
                 v[j] = __float_as_uint(x);
-                if (has_block) store_operand(my_rows + (uint32_t)c * 2048u, j, x);
+                if (has_block) store_operand(my_rows + (uint32_t)c * (CW * 128u), j, x);
             }
-            tmem_store_16(tmem_held + lane_bits + (uint32_t)(c * 16), v);
+            tmem_store_chunk<CW>(tmem_held + lane_bits + (uint32_t)(c * CW), v);
         }
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> tensor-core reads
         tc_fence_before();
-        mbar_arrive(act_bar);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(act_bar);
 
         for (int l = 0; l < p.n_layers; l++) {
             const uint32_t flags = p.flags[l];
@@ -317,56 +354,85 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
                 }
             }
             const float bias = valid ? p.bias[l * 128 + ch] : 0.f;
-            // One lane per warp polls: 256 threads spinning on a shared-memory barrier for the whole
-            // mainloop would compete with the copy engine and the tensor core for shared memory.  The
-            // outcome is warp-uniform (the tensor-memory accesses below need the whole warp); every lane
-            // then observes the completed phase itself.
+            // ONE thread of the CTA polls, with a long suspend hint; the other epilogue threads sleep in a hardware
+            // barrier.  During the mainloop the shared-memory data pipe is the busiest unit of the SM (the tensor core
+            // reads both operands through it and the copy engine writes the filters through it), and every poll of
+            // an mbarrier is a shared-memory access: a dozen polling warps took a measurable share of it.  The
+            // poller publishes its verdict (go on / abandon) in a word per layer parity, so that all threads take
+            // the same branch and none is left waiting in the barrier.
+            const bool trace = TRACE && blockIdx.x == 0 && warp == 2 && lane == 0;
+            if (trace) p.trace[l * 8 + 4] = clock64();
             {
-                uint32_t ok = 1;
-                if (lane == 0) {
+                if (warp == 2 && lane == 0) {
+                    int go = 1;
                     const long long start = clock64();
-                    while (!mbar_try_wait(accum_bar, (uint32_t)(l & 1))) {
-                        if (*abandon) { ok = 0; break; }
+                    while (!mbar_try_wait_hint(accum_bar, (uint32_t)(l & 1), kSleepNs)) {
+                        if (*abandon) { go = 0; break; }
                         if (clock64() - start > kWaitCycles) {
                             *abandon = 1;
                             atomicMax(p.status, 14u);
-                            ok = 0;
+                            go = 0;
                             break;
                         }
                     }
+                    epilogue_go[l & 1] = go;
                 }
-                ok = __shfl_sync(0xffffffffu, ok, 0);
-                if (!ok) break;
-                while (!mbar_try_wait(accum_bar, (uint32_t)(l & 1))) {}
+                asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");
+                if (!epilogue_go[l & 1]) break;
             }
             tc_fence_after();
+            if (trace) p.trace[l * 8 + 5] = clock64();
             {
                 // Software pipeline over my chunks: while chunk k is being finished, the tensor-memory loads
                 // of chunk k + 1 are in flight.  `tcgen05.wait::ld` waits for every outstanding load, so it
                 // comes right before the next chunk's loads are issued.
-                uint32_t va[16], ha[16], vb[16], hb[16];
-                auto issue = [&](int c, uint32_t (&v)[16], uint32_t (&h)[16]) {
-                    tmem_load_16_nowait(tmem_acc + lane_bits + (uint32_t)(c * 16), v);
-                    if (add_held) tmem_load_16_nowait(tmem_held + lane_bits + (uint32_t)(c * 16), h);
+                uint32_t va[CW], ha[CW], vb[CW], hb[CW];
+                auto issue = [&](int c, uint32_t (&v)[CW], uint32_t (&h)[CW]) {
+                    tmem_load_chunk_nowait<CW>(tmem_acc + lane_bits + (uint32_t)(c * CW), v);
+                    if (add_held) tmem_load_chunk_nowait<CW>(tmem_held + lane_bits + (uint32_t)(c * CW), h);
                 };
-                auto finish = [&](int c, uint32_t (&v)[16], uint32_t (&h)[16]) {
-                    const uint32_t chunk_rows = my_rows + (uint32_t)c * 2048u;
+                auto finish = [&](int c, uint32_t (&v)[CW], uint32_t (&h)[CW]) {
                     const uint32_t mask = valid ? realmask[c] : 0u;   // columns that are real pixels; the rest is zero padding
+                    // (`h` is zero in a layer that adds nothing.  Padding columns are computed like the others but never
+                    // stored: their rows of the operand buffer stay zero from the start, and what the held columns
+                    // carry there only ever flows back into padding columns.)
 #pragma unroll
-                    for (int j = 0; j < 16; j++) {
-                        float x = __uint_as_float(v[j]) + bias;
-                        if (add_held) x += __uint_as_float(h[j]);
+                    for (int j = 0; j < CW; j++) {
+                        float x = __uint_as_float(v[j]) + bias + __uint_as_float(h[j]);
                         if (relu) x = fmaxf(x, 0.f);
-                        if (!((mask >> j) & 1u)) x = 0.f;
                         v[j] = __float_as_uint(x);
-                        if (!last && has_block) store_operand(chunk_rows, j, x);
                     }
-                    if (hold) tmem_store_16(tmem_held + lane_bits + (uint32_t)(c * 16), v);
+                    if (!last && has_block) {
+                        // Four positions per store instruction: `stmatrix` writes four 8 x 16-byte matrices, and a
+                        // 16-byte matrix row is exactly what four neighbouring lanes (channels) hold of one position,
+                        // one 16-byte chunk of its 128-byte operand row.  Lane 8 k + r supplies the address of row r
+                        // (channels 4 r .. 4 r + 3) of matrix k (position 4 m + k of the chunk), swizzled like the rest.
+                        // One 32-bit store per position took four times the instructions and was the larger half of
+                        // the epilogue's time.
+                        uint32_t rounded[CW];
+#pragma unroll
+                        for (int j = 0; j < CW; j++) {
+                            uint32_t u = v[j];
+                            if ((u & 0x7F800000u) != 0x7F800000u) u += 0x1000u;
+                            rounded[j] = u;
+                        }
+                        const uint32_t all = realmask[c];
+#pragma unroll
+                        for (int m = 0; m < CW / 4; m++) {
+                            const uint32_t col = (uint32_t)(4 * m) + ((uint32_t)lane >> 3);
+                            uint32_t addr = block_rows + ((uint32_t)c * CW + col) * 128u + ((((uint32_t)lane & 7u) ^ (col & 7u)) << 4);
+                            if (!((all >> col) & 1u)) addr = dummy_rows + (((uint32_t)lane & 7u) << 4);
+                            asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1, %2, %3, %4};"
+                                         ::"r"(addr), "r"(rounded[4 * m]), "r"(rounded[4 * m + 1]), "r"(rounded[4 * m + 2]), "r"(rounded[4 * m + 3])
+                                         : "memory");
+                        }
+                    }
+                    if (hold) tmem_store_chunk<CW>(tmem_held + lane_bits + (uint32_t)(c * CW), v);
                     if (to_global) {
 #pragma unroll
-                        for (int j = 0; j < 16; j++) {
+                        for (int j = 0; j < CW; j++) {
                             if ((mask >> j) & 1u) {
-                                const uint32_t info = colinfo[c * 16 + j];
+                                const uint32_t info = colinfo[c * CW + j];
                                 o_ptr[(img0 + ((info >> 16) & 0xFF)) * o_s0 + (int64_t)((info >> 8) & 0xFF) * o_s2 +
                                       (int64_t)(info & 0xFF) * o_s3] = __uint_as_float(v[j]);
                             }
@@ -375,23 +441,29 @@ conv_chain_kernel(const __grid_constant__ CUtensorMap map_tiles, const __grid_co
                 };
                 // (not unrolled over the chunks: eight copies of the body made the epilogue's code so large that
                 // the kernel's speed depended on where unrelated code happened to be placed, measured)
-                if (half < chunks16) issue(half, va, ha);
+                if (!add_held) {
+#pragma unroll
+                    for (int j = 0; j < CW; j++) ha[j] = hb[j] = 0u;
+                }
+                if (half < chunks) issue(half, va, ha);
 #pragma unroll 1
-                for (int c = half; c < chunks16; c += 2 * E) {
+                for (int c = half; c < chunks; c += 2 * E) {
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (c + E < chunks16) issue(c + E, vb, hb);
+                    if (c + E < chunks) issue(c + E, vb, hb);
                     finish(c, va, ha);
-                    if (c + E >= chunks16) break;
+                    if (c + E >= chunks) break;
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (c + 2 * E < chunks16) issue(c + 2 * E, va, ha);
+                    if (c + 2 * E < chunks) issue(c + 2 * E, va, ha);
                     finish(c + E, vb, hb);
                 }
                 if (hold) asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             }
+            if (trace) p.trace[l * 8 + 6] = clock64();
             if (!last) {
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 tc_fence_before();
-                mbar_arrive(act_bar);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(act_bar);
             }
         }
     }
@@ -427,7 +499,7 @@ bool tc_chain_geometry(int h, int w, int64_t n_img, int c_blocks, ChainGeometry*
             if (g.n_mma > 256) break;
             g.rows_alloc = round_up_int(g.r_first + g.n_mma + g.wp + 2, 8);
             const int act_bytes = c_blocks * g.rows_alloc * 128;
-            const int fixed = 1024 /* alignment */ + 16 * 8 + 32 + 1024 /* column table */ + 64 /* chunk masks */;
+            const int fixed = 1024 /* alignment */ + 16 * 8 + 32 + 1024 /* column table */ + 128 /* chunk masks */ + 24 /* poller's verdict */ + 128 /* dummy rows */;
             // the ring holds whole taps (c_blocks tiles each): two of them at least, four at most
             g.group = c_blocks;
             const int requests = std::min(4, (227 * 1024 - fixed - act_bytes) / (kTileBytes * g.group));
@@ -515,14 +587,42 @@ std::shared_ptr<void> chain_prepare(const ConvChainParams& c, uint32_t* status_w
     // about twice the rate of single 16 KB tiles
     p.group = g.group;
     p.slots = g.slots / p.group;
+    // KN_CHAIN_TRACE=1 in the environment: the traced variant of the kernel stamps clock64 per layer in its first CTA
+    // (MMA issuer: wait for the layer's input, all MMAs issued; first epilogue warp: accumulator ready, chunks
+    // finished) and the table is printed when the process exits.  A measuring aid: the stamps cost a few percent.
+    if (getenv("KN_CHAIN_TRACE") && p.n_layers <= kMaxChainLayers) {
+        static long long* table = nullptr;
+        static int layers = 0;
+        if (!table && cudaHostAlloc((void**)&table, (size_t)kMaxChainLayers * 64, cudaHostAllocMapped) == cudaSuccess) {
+            atexit([] {
+                const long long* d = table;
+                fprintf(stderr, "conv_chain_kernel, CTA 0, SM clock cycles per layer\n"
+                                "layer  wait_input  issue_mmas  (of which filter waits)  accumulator_wait  epilogue_chunks  layer_period\n");
+                for (int i = 0; i < layers; i++)
+                    fprintf(stderr, "%5d  %10lld  %10lld  %23lld  %16lld  %15lld  %12lld\n", i, d[i * 8 + 1] - d[i * 8 + 0],
+                            d[i * 8 + 2] - d[i * 8 + 1], d[i * 8 + 3], d[i * 8 + 5] - d[i * 8 + 4], d[i * 8 + 6] - d[i * 8 + 5],
+                            i ? d[i * 8 + 1] - d[(i - 1) * 8 + 1] : 0);
+            });
+        }
+        if (table) {
+            memset(table, 0, (size_t)kMaxChainLayers * 64);
+            layers = p.n_layers;
+            p.trace = table;
+        }
+    }
     int64_t dims[3] = {32, 128, p.total_tiles}, strides[3] = {1, 32, 128 * 32};
     int box[3] = {32, 128, 1};
     l->map_tiles = tc_make_map(c.tiles, 3, dims, strides, box, true);
     l->grid = dim3((unsigned)((c.n + g.per_cta - 1) / g.per_cta), 1, 1);
     l->smem_bytes = g.smem_bytes;
-    // three epilogue warps per quarter share the chunks evenly when their number divides by three (two 8x8
-    // boards: 9 chunks, three each instead of five and four); otherwise two
-    l->epilogue_warps = ((g.n_mma / 16) % 3 == 0) ? 3 : 2;
+    // Epilogue variants: the accumulator's columns are shared out in chunks among E warps per lane quarter.  Six
+    // warps taking 8-column chunks when the chunk count divides by six (two 8x8 boards: 18 chunks, three each); else
+    // three or two warps taking 16-column chunks.  KN_CHAIN_EPILOGUE=<E> in the environment picks one (measuring).
+    l->epilogue_warps = ((g.n_mma / 8) % 6 == 0) ? 6 : ((g.n_mma / 16) % 3 == 0) ? 3 : 2;
+    if (const char* e = getenv("KN_CHAIN_EPILOGUE")) {
+        const int v = atoi(e);
+        if (v == 2 || v == 3 || v == 4 || v == 6) l->epilogue_warps = v;
+    }
     return l;
 }
 
@@ -535,10 +635,16 @@ int chain_launch(const void* launch, cudaStream_t stream) {
     {
         std::lock_guard<std::mutex> lock(mu);
         if (device >= 0 && device < 64 && !done[device]) {
-            cudaError_t e = cudaFuncSetAttribute(conv_chain_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-            if (e != cudaSuccess) return (int)e;
-            e = cudaFuncSetAttribute(conv_chain_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-            if (e != cudaSuccess) return (int)e;
+            const void* variants[] = {
+                (const void*)conv_chain_kernel<2, 16, false>, (const void*)conv_chain_kernel<3, 16, false>,
+                (const void*)conv_chain_kernel<4, 8, false>,  (const void*)conv_chain_kernel<6, 8, false>,
+                (const void*)conv_chain_kernel<2, 16, true>,  (const void*)conv_chain_kernel<3, 16, true>,
+                (const void*)conv_chain_kernel<4, 8, true>,   (const void*)conv_chain_kernel<6, 8, true>,
+            };
+            for (const void* v : variants) {
+                cudaError_t e = cudaFuncSetAttribute(v, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+                if (e != cudaSuccess) return (int)e;
+            }
             done[device] = true;
         }
     }
@@ -553,8 +659,16 @@ int chain_launch(const void* launch, cudaStream_t stream) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (l.epilogue_warps == 3) return (int)cudaLaunchKernelEx(&cfg, conv_chain_kernel<3>, l.map_tiles, l.p);
-    return (int)cudaLaunchKernelEx(&cfg, conv_chain_kernel<2>, l.map_tiles, l.p);
+    void* args[] = {(void*)&l.map_tiles, (void*)&l.p};
+    const void* kernel = nullptr;
+    const bool t = l.p.trace != nullptr;
+    switch (l.epilogue_warps) {
+        case 6: kernel = t ? (const void*)conv_chain_kernel<6, 8, true> : (const void*)conv_chain_kernel<6, 8, false>; break;
+        case 4: kernel = t ? (const void*)conv_chain_kernel<4, 8, true> : (const void*)conv_chain_kernel<4, 8, false>; break;
+        case 3: kernel = t ? (const void*)conv_chain_kernel<3, 16, true> : (const void*)conv_chain_kernel<3, 16, false>; break;
+        default: kernel = t ? (const void*)conv_chain_kernel<2, 16, true> : (const void*)conv_chain_kernel<2, 16, false>; break;
+    }
+    return (int)cudaLaunchKernelExC(&cfg, kernel, args);
 }
 
 }  // namespace kn

@@ -356,6 +356,22 @@ __global__ void __launch_bounds__(kThreads) scalar_acc_kernel(const __grid_const
                 default: *stride_bytes = inner_bytes[kRegOperands - 1]; *half = is_half[kRegOperands - 1]; return base[kRegOperands - 1];
             }
         };
+        if (MIXED) {
+            // The micro-ops run in program order, and each load is converted (and parked in its slot) before the
+            // next one is issued, so a thread has one operand's 32 bytes in flight at a time: too few to cover
+            // DRAM latency with 2-byte elements.  The later operands' lines are therefore requested into L2 now
+            // (the loads come first in the program), and with a one-dimensional index space so are all the
+            // operands of this thread's next iteration.
+            const bool ahead = RANK1 && g + step < total_v;
+            for (int k = 0; k < p.n_micro && p.micro[k].kind == 3; k++) {
+                uint32_t sb;
+                bool half;
+                const char* src = operand(p.micro[k].a, &sb, &half);
+                if (!sb) continue;
+                if (k > 0) asm volatile("prefetch.global.L2 [%0];" ::"l"(src));
+                if (ahead) asm volatile("prefetch.global.L2 [%0];" ::"l"(src + (size_t)step * (4 * V) * (half ? 2u : 4u)));
+            }
+        }
         auto imm_value = [&](const ScalarInstr& in) {
             return MIXED && (DType)in.dtype == DType::F16 ? f16_bits_to_f32((uint16_t)in.imm) : bits_to_f32(in.imm);
         };
@@ -447,14 +463,18 @@ __global__ void __launch_bounds__(kThreads) scalar_acc_kernel(const __grid_const
                     binary_v<V>((BinaryOp)in.op, acc, b, a);
                     break;
             }
-            if (MIXED && (DType)in.dtype == DType::F16 && (in.kind == 1 || in.kind == 2 || in.kind >= 5)) {
+            // (bit 8 of `pad`: only f16 stores read this result, and their rounding is the same rounding)
+            if (MIXED && (DType)in.dtype == DType::F16 && !(in.pad & 0x100) && (in.kind == 1 || in.kind == 2 || in.kind >= 5)) {
 #pragma unroll
-                for (int v = 0; v < V; v++)
-                    acc.v[v] = make_float4(round_f16(acc.v[v].x), round_f16(acc.v[v].y), round_f16(acc.v[v].z), round_f16(acc.v[v].w));
+                for (int v = 0; v < V; v++) {
+                    const float2 lo = __half22float2(__floats2half2_rn(acc.v[v].x, acc.v[v].y));
+                    const float2 hi = __half22float2(__floats2half2_rn(acc.v[v].z, acc.v[v].w));
+                    acc.v[v] = make_float4(lo.x, lo.y, hi.x, hi.y);
+                }
             }
-            if (in.pad != 255) {
+            if ((in.pad & 0xFF) != 255) {
 #pragma unroll
-                for (int v = 0; v < V; v++) my_spill[((int)in.pad * V + v) * kThreads] = acc.v[v];
+                for (int v = 0; v < V; v++) my_spill[((int)(in.pad & 0xFF) * V + v) * kThreads] = acc.v[v];
             }
         }
     }

@@ -9,6 +9,8 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
+
 #include "../kernels.h"
 #include "launch.cuh"
 
@@ -78,15 +80,36 @@ __global__ void __launch_bounds__(256) rows_f16_vec_kernel(const __grid_constant
     pdl_enter();
     __shared__ float smem[8];
     const int rows_per_block = blockDim.x / TPR;
-    const int64_t row = (int64_t)blockIdx.x * rows_per_block + threadIdx.x / TPR;
     const int t = threadIdx.x % TPR;
+    const int len8 = (int)(p.len >> 3);
+    // Persistent blocks.  While a row is being reduced nothing of it is in flight any more, and the converted row
+    // leaves no registers to hold the next one, so the next row's lines are requested into L2 instead: its loads
+    // then take a fraction of a DRAM round trip.
+    for (int64_t first = (int64_t)blockIdx.x * rows_per_block; first < p.rows; first += (int64_t)gridDim.x * rows_per_block) {
+    const int64_t row = first + threadIdx.x / TPR;
     const bool active = row < p.rows;
     int64_t oi = 0, oo = 0, o1 = 0;
     if (active) offsets(row, p.outer_rank, p.outer_dims, p.in_strides, p.out_strides, SOFTMAX ? p.in1_strides : p.in_strides, oi, oo, o1);
     const uint4* in0 = (const uint4*)((const __half*)p.in0 + oi);
     const uint4* in1 = p.in1 ? (const uint4*)((const __half*)p.in1 + o1) : nullptr;
     uint4* out = (uint4*)((__half*)p.out + oo);
-    const int len8 = (int)(p.len >> 3);
+    {
+        const int64_t next = row + (int64_t)gridDim.x * rows_per_block;
+        if (next < p.rows && (t & 7) == 0) {   // one request per 128-byte line
+            int64_t ni, no, n1;
+            offsets(next, p.outer_rank, p.outer_dims, p.in_strides, p.out_strides, p.in_strides, ni, no, n1);
+            const uint4* nin = (const uint4*)((const __half*)p.in0 + ni);
+#pragma unroll
+            for (int i = 0; i < ITEMS; i++)
+                if (i * TPR + t < len8) asm volatile("prefetch.global.L2 [%0];" ::"l"(nin + i * TPR + t));
+            if (!SOFTMAX && p.in1) {
+                const uint4* nin1 = (const uint4*)((const __half*)p.in1 + ni);
+#pragma unroll
+                for (int i = 0; i < ITEMS; i++)
+                    if (i * TPR + t < len8) asm volatile("prefetch.global.L2 [%0];" ::"l"(nin1 + i * TPR + t));
+            }
+        }
+    }
 
     float v[ITEMS][8];
     const float pad = SOFTMAX ? -INFINITY : 0.f;
@@ -134,12 +157,11 @@ __global__ void __launch_bounds__(256) rows_f16_vec_kernel(const __grid_constant
                 sum += v[i][j];
             }
         sum = reduce_row<TPR, false>(sum, smem);
-        if (!active) return;
         const float inv = 1.0f / sum;
 #pragma unroll
         for (int i = 0; i < ITEMS; i++) {
             const int e = i * TPR + t;
-            if (e < len8) {
+            if (active && e < len8) {
 #pragma unroll
                 for (int j = 0; j < 8; j++) v[i][j] = v[i][j] * inv;
                 out[e] = pack8(v[i]);
@@ -165,17 +187,17 @@ __global__ void __launch_bounds__(256) rows_f16_vec_kernel(const __grid_constant
         }
         const float var = reduce_row<TPR, false>(sq, smem) / n;
         const float inv = 1.0f / sqrtf(var + p.eps);
-        if (!active) return;
 #pragma unroll
         for (int i = 0; i < ITEMS; i++) {
             const int e = i * TPR + t;
-            if (e < len8) {
+            if (active && e < len8) {
 #pragma unroll
                 for (int j = 0; j < 8; j++) v[i][j] = v[i][j] * inv;
                 out[e] = pack8(v[i]);
             }
         }
     }
+    }   // rows of this block
 }
 
 template <bool SOFTMAX>
@@ -218,64 +240,105 @@ __global__ void __launch_bounds__(256) rows_f16_streaming_kernel(const __grid_co
     }
 }
 
-// One block of 256 threads per row, the row (up to 16384 elements, a multiple of 8) in registers as f32: one read,
-// one write.
+// One block of 256 threads per row at a time, the row (up to 16384 elements, a multiple of 8) in registers as f32: one
+// read, one write.  The blocks are persistent and software-pipelined: the next row's loads are issued (as raw 128-bit
+// registers) before this row's reduction, so a block always has a row in flight; with one short-lived block per row the
+// load -> barrier -> barrier -> store chain left the memory system idle half of the time.
 template <bool IN_HALF, bool OUT_HALF, int ITEMS>
 __global__ void __launch_bounds__(256) rmsnorm_kernel(const __grid_constant__ RmsNormParams p) {
     pdl_enter();
     __shared__ float smem[8];
-    const int64_t row = blockIdx.x;
+    constexpr int R = IN_HALF ? ITEMS : 2 * ITEMS;   // 128-bit loads per thread and row
     const int t = threadIdx.x;
     const int len8 = (int)(p.len >> 3);
-    float v[ITEMS][8];
-    float sq = 0.f;
+    auto load_row = [&](int64_t row, uint4 (&raw)[R]) {
 #pragma unroll
-    for (int i = 0; i < ITEMS; i++) {
-        const int e = i * 256 + t;
-        if (e < len8) {
-            if (IN_HALF) {
-                unpack8(__ldg((const uint4*)((const __half*)p.in + row * p.in_row_stride) + e), v[i]);
-            } else {
-                const float4* src = (const float4*)((const float*)p.in + row * p.in_row_stride) + 2 * e;
-                const float4 a = __ldg(src), b = __ldg(src + 1);
-                v[i][0] = a.x; v[i][1] = a.y; v[i][2] = a.z; v[i][3] = a.w;
-                v[i][4] = b.x; v[i][5] = b.y; v[i][6] = b.z; v[i][7] = b.w;
-            }
-#pragma unroll
-            for (int j = 0; j < 8; j++) sq += v[i][j] * v[i][j];
-        }
-    }
-    const float ms = reduce_row<256, false>(sq, smem) / (float)p.len;
-    const float inv = 1.0f / sqrtf(ms + p.eps);
-#pragma unroll
-    for (int i = 0; i < ITEMS; i++) {
-        const int e = i * 256 + t;
-        if (e < len8) {
-#pragma unroll
-            for (int j = 0; j < 8; j++) {
-                float y = v[i][j] * inv;
-                if (p.gain != nullptr) y *= __ldg(p.gain + (int64_t)(e * 8 + j) * p.gain_stride);
-                v[i][j] = y;
-            }
-            if (OUT_HALF) {
-                *((uint4*)((__half*)p.out + row * p.out_row_stride) + e) = pack8(v[i]);
-            } else {
-                float4* dst = (float4*)((float*)p.out + row * p.out_row_stride) + 2 * e;
-                dst[0] = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
-                dst[1] = make_float4(v[i][4], v[i][5], v[i][6], v[i][7]);
+        for (int i = 0; i < ITEMS; i++) {
+            const int e = i * 256 + t;
+            if (e < len8) {
+                if (IN_HALF) {
+                    raw[i] = __ldg((const uint4*)((const __half*)p.in + row * p.in_row_stride) + e);
+                } else {
+                    const uint4* src = (const uint4*)((const float*)p.in + row * p.in_row_stride) + 2 * e;
+                    raw[2 * i] = __ldg(src);
+                    raw[2 * i + 1] = __ldg(src + 1);
+                }
             }
         }
+    };
+    uint4 raw[R], next_raw[R];
+    int64_t row = blockIdx.x;
+    if (row < p.rows) load_row(row, raw);
+    for (; row < p.rows; row += gridDim.x) {
+        const int64_t next = row + gridDim.x;
+        if (next < p.rows) load_row(next, next_raw);
+        float v[ITEMS][8];
+        float sq = 0.f;
+#pragma unroll
+        for (int i = 0; i < ITEMS; i++) {
+            const int e = i * 256 + t;
+            if (e < len8) {
+                if (IN_HALF) {
+                    unpack8(raw[i], v[i]);
+                } else {
+                    const float4 a = *(const float4*)&raw[2 * i], b = *(const float4*)&raw[2 * i + 1];
+                    v[i][0] = a.x; v[i][1] = a.y; v[i][2] = a.z; v[i][3] = a.w;
+                    v[i][4] = b.x; v[i][5] = b.y; v[i][6] = b.z; v[i][7] = b.w;
+                }
+#pragma unroll
+                for (int j = 0; j < 8; j++) sq += v[i][j] * v[i][j];
+            }
+        }
+        const float ms = reduce_row<256, false>(sq, smem) / (float)p.len;
+        const float inv = 1.0f / sqrtf(ms + p.eps);
+#pragma unroll
+        for (int i = 0; i < ITEMS; i++) {
+            const int e = i * 256 + t;
+            if (e < len8) {
+                if (p.gain != nullptr && p.gain_stride == 1) {
+                    const float4 g0 = __ldg((const float4*)p.gain + 2 * e), g1 = __ldg((const float4*)p.gain + 2 * e + 1);
+                    const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+                    for (int j = 0; j < 8; j++) v[i][j] = v[i][j] * inv * g[j];
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        float y = v[i][j] * inv;
+                        if (p.gain != nullptr) y *= __ldg(p.gain + (int64_t)(e * 8 + j) * p.gain_stride);
+                        v[i][j] = y;
+                    }
+                }
+                if (OUT_HALF) {
+                    *((uint4*)((__half*)p.out + row * p.out_row_stride) + e) = pack8(v[i]);
+                } else {
+                    float4* dst = (float4*)((float*)p.out + row * p.out_row_stride) + 2 * e;
+                    dst[0] = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
+                    dst[1] = make_float4(v[i][4], v[i][5], v[i][6], v[i][7]);
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < R; i++) raw[i] = next_raw[i];
     }
+}
+
+template <bool IN_HALF, bool OUT_HALF, int ITEMS>
+void launch_rmsnorm_items(const RmsNormParams& p, cudaStream_t stream) {
+    // persistent blocks: as many as are resident at once on the 148 SMs
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, rmsnorm_kernel<IN_HALF, OUT_HALF, ITEMS>, 256, 0) != cudaSuccess || per_sm < 1)
+        per_sm = 1;
+    const dim3 grid((unsigned)std::min<int64_t>(p.rows, (int64_t)148 * per_sm)), block(256);
+    launch_pdl(rmsnorm_kernel<IN_HALF, OUT_HALF, ITEMS>, grid, block, (size_t)0, stream, p);
 }
 
 template <bool IN_HALF, bool OUT_HALF>
 int launch_rmsnorm_t(const RmsNormParams& p, cudaStream_t stream) {
     const int items = (int)((p.len / 8 + 255) / 256);
-    const dim3 grid((unsigned)p.rows), block(256);
-    if (items <= 1) launch_pdl(rmsnorm_kernel<IN_HALF, OUT_HALF, 1>, grid, block, (size_t)0, stream, p);
-    else if (items <= 2) launch_pdl(rmsnorm_kernel<IN_HALF, OUT_HALF, 2>, grid, block, (size_t)0, stream, p);
-    else if (items <= 4) launch_pdl(rmsnorm_kernel<IN_HALF, OUT_HALF, 4>, grid, block, (size_t)0, stream, p);
-    else launch_pdl(rmsnorm_kernel<IN_HALF, OUT_HALF, 8>, grid, block, (size_t)0, stream, p);
+    if (items <= 1) launch_rmsnorm_items<IN_HALF, OUT_HALF, 1>(p, stream);
+    else if (items <= 2) launch_rmsnorm_items<IN_HALF, OUT_HALF, 2>(p, stream);
+    else if (items <= 4) launch_rmsnorm_items<IN_HALF, OUT_HALF, 4>(p, stream);
+    else launch_rmsnorm_items<IN_HALF, OUT_HALF, 8>(p, stream);
     return (int)cudaGetLastError();
 }
 
@@ -290,6 +353,17 @@ bool vec_ok(const RowParams& p, bool softmax) {
     return true;
 }
 
+template <bool SOFTMAX, int TPR, int ITEMS>
+void launch_vec(const RowParams& p, cudaStream_t stream) {
+    const int64_t blocks = (p.rows + (256 / TPR) - 1) / (256 / TPR);
+    // persistent blocks: as many as are resident at once on the 148 SMs
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, rows_f16_vec_kernel<SOFTMAX, TPR, ITEMS>, 256, 0) != cudaSuccess || per_sm < 1)
+        per_sm = 1;
+    launch_pdl(rows_f16_vec_kernel<SOFTMAX, TPR, ITEMS>, dim3((unsigned)std::min<int64_t>(blocks, (int64_t)148 * per_sm)), dim3(256),
+               (size_t)0, stream, p);
+}
+
 template <bool SOFTMAX>
 int launch_rows(const RowParams& p, cudaStream_t stream) {
     if (p.rows == 0 || p.len == 0) return 0;
@@ -297,18 +371,16 @@ int launch_rows(const RowParams& p, cudaStream_t stream) {
     if (vec_ok(p, SOFTMAX)) {
         const int len8 = (int)(p.len / 8);
         if (len8 <= 256) {   // one warp per row, eight rows per block
-            const unsigned grid = (unsigned)((p.rows + 7) / 8);
             const int items = (len8 + 31) / 32;
-            if (items <= 1) launch_pdl(rows_f16_vec_kernel<SOFTMAX, 32, 1>, dim3(grid), dim3(256), (size_t)0, stream, p);
-            else if (items <= 2) launch_pdl(rows_f16_vec_kernel<SOFTMAX, 32, 2>, dim3(grid), dim3(256), (size_t)0, stream, p);
-            else if (items <= 4) launch_pdl(rows_f16_vec_kernel<SOFTMAX, 32, 4>, dim3(grid), dim3(256), (size_t)0, stream, p);
-            else launch_pdl(rows_f16_vec_kernel<SOFTMAX, 32, 8>, dim3(grid), dim3(256), (size_t)0, stream, p);
+            if (items <= 1) launch_vec<SOFTMAX, 32, 1>(p, stream);
+            else if (items <= 2) launch_vec<SOFTMAX, 32, 2>(p, stream);
+            else if (items <= 4) launch_vec<SOFTMAX, 32, 4>(p, stream);
+            else launch_vec<SOFTMAX, 32, 8>(p, stream);
         } else {             // one block per row
-            const unsigned grid = (unsigned)p.rows;
             const int items = (len8 + 255) / 256;
-            if (items <= 2) launch_pdl(rows_f16_vec_kernel<SOFTMAX, 256, 2>, dim3(grid), dim3(256), (size_t)0, stream, p);
-            else if (items <= 4) launch_pdl(rows_f16_vec_kernel<SOFTMAX, 256, 4>, dim3(grid), dim3(256), (size_t)0, stream, p);
-            else launch_pdl(rows_f16_vec_kernel<SOFTMAX, 256, 8>, dim3(grid), dim3(256), (size_t)0, stream, p);
+            if (items <= 2) launch_vec<SOFTMAX, 256, 2>(p, stream);
+            else if (items <= 4) launch_vec<SOFTMAX, 256, 4>(p, stream);
+            else launch_vec<SOFTMAX, 256, 8>(p, stream);
         }
         return (int)cudaGetLastError();
     }

@@ -29,14 +29,27 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// The same test with a suspend-time hint: the thread may sleep for up to `hint_ns` while the phase is incomplete (it
+// is woken when the phase completes), so a long wait costs a handful of shared-memory accesses instead of thousands.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait.  Returns false if the kernel is being abandoned: another role gave up, or this wait ran for
 // `limit` clock cycles, in which case it raises `*status` to `code` and sets the CTA's abandon flag.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abandon, uint32_t* status,
-                                          uint32_t code, long long limit = kWaitCycles) {
+                                          uint32_t code, long long limit = kWaitCycles, uint32_t hint_ns = 0) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long start = clock64();
     while (true) {
-        if (mbar_try_wait(bar, parity)) return true;
+        if (hint_ns ? mbar_try_wait_hint(bar, parity, hint_ns) : mbar_try_wait(bar, parity)) return true;
         if (*abandon) return false;
         if (clock64() - start > limit) {
             *abandon = 1;

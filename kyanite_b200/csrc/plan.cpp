@@ -354,7 +354,9 @@ class Planner {
     //   kind 0 acc = imm                      3 acc = load operand `a`
     //   kind 1 acc = unary(A)                 4 store A -> operand `b`
     //   kind 2 acc = binary(A, B)             5 acc = binary(A, imm)     6 acc = binary(imm, A)
-    // A / B: `a` / `b` = 255 means the accumulator, otherwise a slot; `pad` = slot to copy the result to, or 255.
+    // A / B: `a` / `b` = 255 means the accumulator, otherwise a slot; `pad` low byte = slot to copy the result to, or
+    // 255; `pad` bit 8 = the result goes to f16 stores only, so the store's rounding is the op's rounding and the
+    // kernel need not round the f16-typed result itself.
     static bool allocate_registers(ScalarParams& p) {
         const int kAcc = 255;
         const int n_values = p.n_loads + p.n_instr;
@@ -468,6 +470,19 @@ class Planner {
                 expiring[last_use[v]].push_back(v);
             }
         }
+        // results that only f16 stores read
+        std::vector<uint8_t> read_by_other(n_values, 0), read_by_store(n_values, 0);
+        for (const Op& o : ops) {
+            if (o.m.kind == 4) {
+                if (o.src_a >= 0) ((DType)p.dtype[o.m.b] == DType::F16 ? read_by_store : read_by_other)[o.src_a] = 1;
+            } else {
+                for (int v : {o.src_a, o.src_b})
+                    if (v >= 0) read_by_other[v] = 1;
+            }
+        }
+        for (Op& o : ops)
+            if (o.result >= 0 && o.m.kind != 0 && o.m.kind != 3 && o.m.kind != 4 && read_by_store[o.result] && !read_by_other[o.result])
+                o.m.pad |= 0x100;
         p.n_micro = (int)ops.size();
         for (int i = 0; i < p.n_micro; i++) p.micro[i] = ops[i].m;
         p.n_regs = n_regs;

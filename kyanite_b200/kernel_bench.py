@@ -134,6 +134,14 @@ def case_conv_trunk(rng):
     return g, 256, [rng.standard_normal((256, 128, 8, 8)).astype(np.float32)]
 
 
+def case_tower(rng):
+    """The whole ResNet tower of the headline benchmark at batch 256: its trunk runs as one `ConvChain` step.
+    With KN_CHAIN_TRACE=1 in the environment the kernel's per-layer phase clocks are printed at exit."""
+    from .configs import resnet_tower
+    g, make_inputs = resnet_tower()
+    return g, 256, make_inputs(256, 3)
+
+
 def case_conv_unet(rng):
     """UNet-sized convolution: 3x3, 320 -> 320, batch 8, 64x64, + bias."""
     g = Graph()
@@ -226,6 +234,7 @@ CASES = {
     "linear_llama_proj": _linear_case(2048, 4096, 4096, bias=False),
     "linear_llama_ffn": _linear_case(2048, 11008, 4096, bias=False),
     "attention_scores": case_attention_scores,
+    "tower": case_tower,
     "conv_trunk": case_conv_trunk,
     "conv_unet": case_conv_unet,
     "conv_unet_down": _conv_case(8, 320, 64, 64, 320, 3, 2, 1, "UNet downsampling convolution: 3x3 stride 2, 320 -> 320, batch 8, 64x64 (Im2col + matmul)"),
