@@ -129,6 +129,14 @@ struct GemmParams {
     float* scratch;
     int32_t half;            // 1: A, B, C and the addends hold f16 elements (the pointers are reinterpreted); products
                              // accumulate in f32 and the result is rounded to f16 once.  `scratch` stays f32.
+    // Implicit convolution operand (persistent tensor-core kernel only, f32 storage).  0: none.  1 / 2: the A / B
+    // operand is not a matrix in memory: `a` / `b` points to a channels-last image tensor [batch][h][w][c] and row
+    // `oy * conv_ow + ox` of batch entry `n` is the window of output position (oy, ox) of image n, K index
+    // (tap_y * conv_s + tap_x) * conv_c + channel, zeros outside the image (stride-1 convolution as a matmul
+    // without materialising the windows).  `sa` / `sb` are not used for that operand.
+    int32_t conv_operand;
+    int32_t conv_c, conv_h, conv_w, conv_ow, conv_r, conv_s, conv_pad_y, conv_pad_x;
+    int64_t conv_strides[3];   // element strides of the image tensor: image, row, pixel (channels are contiguous)
 };
 
 // ---- 2D convolution (cross-correlation, zero padding) with fused epilogue

@@ -898,17 +898,19 @@ void tc_prepare_step(Step& step, uint32_t* status_word, int flags, uint32_t* tra
     int64_t n_cols;
     if (step.kind == StepKind::Gemm) {
         const GemmParams& g = step.gemm;
-        if (g.half) {
-            // f16 storage: the persistent kernel is the only tensor-core kernel with f16 operands; the planner marks
-            // a step tensor-core only when that kernel takes it
+        if (g.half || g.conv_operand != 0) {
+            // f16 storage, or an implicit convolution operand: the persistent kernel is the only tensor-core kernel
+            // that takes these; the planner marks such a step tensor-core only when that kernel takes it
             int per_slice = 0, splits = 1;
             if (g.splits > 1) {
-                const int k_total = (int)((g.k + 63) / 64);
+                const int block_k = g.half ? 64 : 32;
+                const int k_total = (int)((g.k + block_k - 1) / block_k);
                 per_slice = (k_total + g.splits - 1) / g.splits;
                 splits = (k_total + per_slice - 1) / per_slice;
             }
             launch->gemm_p = gemm_persistent_prepare(g, status_word, splits, per_slice, trace_words);
-            KN_CHECK(launch->gemm_p != nullptr, KN_ERR_INTERNAL, "f16 matmul planned for the tensor cores does not qualify");
+            KN_CHECK(launch->gemm_p != nullptr, KN_ERR_INTERNAL,
+                     g.half ? "f16 matmul planned for the tensor cores does not qualify" : "implicit convolution matmul does not qualify");
             if (splits > 1) {
                 SplitKReduceParams& r = launch->reduce;
                 memset(&r, 0, sizeof(r));
@@ -926,7 +928,8 @@ void tc_prepare_step(Step& step, uint32_t* status_word, int flags, uint32_t* tra
                     r.s2[i] = g.s2[i];
                 }
                 r.act = g.act;
-                r.half = 1;
+                r.half = g.half;
+                r.round_tf32 = g.round_tf32;
                 launch->split_k = true;
             }
             step.tc = launch;

@@ -360,16 +360,19 @@ __global__ void __launch_bounds__(kThreads) scalar_acc_kernel(const __grid_const
             // The micro-ops run in program order, and each load is converted (and parked in its slot) before the
             // next one is issued, so a thread has one operand's 32 bytes in flight at a time: too few to cover
             // DRAM latency with 2-byte elements.  The later operands' lines are therefore requested into L2 now
-            // (the loads come first in the program), and with a one-dimensional index space so are all the
-            // operands of this thread's next iteration.
-            const bool ahead = RANK1 && g + step < total_v;
-            for (int k = 0; k < p.n_micro && p.micro[k].kind == 3; k++) {
+            // (the loads come first in the program), and with a one-dimensional index space so is the next
+            // iteration's first operand.  (Requesting every operand of the next iteration as well measured slower.)
+            for (int k = 1; k < p.n_micro && p.micro[k].kind == 3; k++) {
                 uint32_t sb;
                 bool half;
                 const char* src = operand(p.micro[k].a, &sb, &half);
-                if (!sb) continue;
-                if (k > 0) asm volatile("prefetch.global.L2 [%0];" ::"l"(src));
-                if (ahead) asm volatile("prefetch.global.L2 [%0];" ::"l"(src + (size_t)step * (4 * V) * (half ? 2u : 4u)));
+                if (sb) asm volatile("prefetch.global.L2 [%0];" ::"l"(src));
+            }
+            if (RANK1 && g + step < total_v && p.micro[0].kind == 3) {
+                uint32_t sb;
+                bool half;
+                const char* src = operand(p.micro[0].a, &sb, &half);
+                if (sb) asm volatile("prefetch.global.L2 [%0];" ::"l"(src + (size_t)step * (4 * V) * (half ? 2u : 4u)));
             }
         }
         auto imm_value = [&](const ScalarInstr& in) {

@@ -58,6 +58,9 @@ struct GemmPersistentParams {
     int64_t s1[3], s2[3];            // (batch, row, col) strides of the addends
     int32_t add1_mode, add2_mode;    // 0 absent, 1 one value per column, 2 a value per element (row-contiguous), 4 one value per row
     int32_t act;
+    // implicit convolution operand (GemmParams::conv_operand): which operand, 32-channel blocks per filter tap,
+    // filter width, padding, output width
+    int32_t conv_operand, conv_cblocks, conv_s, conv_pad_y, conv_pad_x, conv_ow;
     int32_t out_half;                // f16 storage and no split: the output tile is f16 (else f32: plain C or partial sums)
     uint32_t* status;
     volatile uint32_t* dbg;          // null, or 8 progress words in pinned host memory (KN_FLAG_TRACE_GEMM)
@@ -155,8 +158,24 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 const uint32_t bar = full_bar + 8u * s;
                 mbar_expect_tx(bar, stage_bytes);
                 const uint32_t dst = base + (uint32_t)s * stage_bytes;
-                tma_load_3d(dst, &map_a, bar, k * kBlockKElems, mt * kGpBlockM, bt * p.a_batch);
-                tma_load_3d(dst + kGpATileBytes, &map_b, bar, k * kBlockKElems, nt * p.bn, bt * p.b_batch);
+                if (p.conv_operand != 0) {
+                    // K block k = (filter tap, 32-channel block); the tile's rows are whole output rows of image `bt`,
+                    // so the operand tile is one box of the image tensor (channel, x, y, image) moved by the tap:
+                    // positions outside the image are the copy engine's zero fill
+                    const int tap = k / p.conv_cblocks, cb = k - tap * p.conv_cblocks;
+                    const int ty = tap / p.conv_s, tx = tap - ty * p.conv_s;
+                    const int row0 = (p.conv_operand == 1 ? mt * kGpBlockM : nt * p.bn) / p.conv_ow;
+                    if (p.conv_operand == 1) {
+                        tma_load_4d(dst, &map_a, bar, cb * 32, tx - p.conv_pad_x, row0 + ty - p.conv_pad_y, bt);
+                        tma_load_3d(dst + kGpATileBytes, &map_b, bar, k * kBlockKElems, nt * p.bn, bt * p.b_batch);
+                    } else {
+                        tma_load_3d(dst, &map_a, bar, k * kBlockKElems, mt * kGpBlockM, bt * p.a_batch);
+                        tma_load_4d(dst + kGpATileBytes, &map_b, bar, cb * 32, tx - p.conv_pad_x, row0 + ty - p.conv_pad_y, bt);
+                    }
+                } else {
+                    tma_load_3d(dst, &map_a, bar, k * kBlockKElems, mt * kGpBlockM, bt * p.a_batch);
+                    tma_load_3d(dst + kGpATileBytes, &map_b, bar, k * kBlockKElems, nt * p.bn, bt * p.b_batch);
+                }
                 dbg_mark(p, 1, (uint32_t)(k + 1));
                 if (++s == stages) { s = 0; round++; }
             }
@@ -388,6 +407,15 @@ int classify_addend(const float* ptr, const int64_t* st) {
 
 }  // namespace
 
+// Column blocks of equal width: n = 320 is two blocks of 160, not 256 + 64 with three quarters of the second empty.
+int gemm_persistent_bn(int64_t n) {
+    const int64_t blocks = (n + 255) / 256;
+    // (several blocks: a multiple of 32, the width of an epilogue chunk, so that no chunk reaches into the
+    // next block's columns; a single block is clipped by the store's tensor bounds)
+    const int64_t unit = blocks > 1 ? 32 : 16;
+    return (int)std::min<int64_t>(((n + blocks - 1) / blocks + unit - 1) / unit * unit, 256);
+}
+
 std::shared_ptr<void> gemm_persistent_prepare(const GemmParams& g, uint32_t* status_word, int splits, int k_iters_slice,
                                               uint32_t* trace_words) {
     if (g.batch < 1 || g.m < 1 || g.n < 16 || g.k < 1 || splits < 1) return nullptr;
@@ -407,14 +435,7 @@ std::shared_ptr<void> gemm_persistent_prepare(const GemmParams& g, uint32_t* sta
     auto l = std::make_shared<GemmPersistentLaunch>();
     GemmPersistentParams& p = l->p;
     memset(&p, 0, sizeof(p));
-    // column blocks of equal width: n = 320 is two blocks of 160, not 256 + 64 with three quarters of the second empty
-    {
-        const int64_t blocks = (g.n + 255) / 256;
-        // (several blocks: a multiple of 32, the width of an epilogue chunk, so that no chunk reaches into the
-        // next block's columns; a single block is clipped by the store's tensor bounds)
-        const int64_t unit = blocks > 1 ? 32 : 16;
-        p.bn = (int)std::min<int64_t>(((g.n + blocks - 1) / blocks + unit - 1) / unit * unit, 256);
-    }
+    p.bn = gemm_persistent_bn(g.n);
     p.k_iters = (int)((g.k + block_k - 1) / block_k);
     p.out_half = half && !split ? 1 : 0;
     l->half = half;
@@ -450,12 +471,30 @@ std::shared_ptr<void> gemm_persistent_prepare(const GemmParams& g, uint32_t* sta
     p.b_batch = (g.batch > 1 && g.sb[0] == 0) ? 0 : 1;
     int64_t bdims[3] = {g.k, g.n, p.b_batch ? g.batch : 1}, bstr[3] = {1, g.sb[2], p.b_batch ? g.sb[0] : align};
     int bbox[3] = {block_k, p.bn, 1};
+    // the implicit convolution operand: a 4-D map of the image tensor (channel, x, y, image) whose box is one K
+    // block of channels by whole output rows
+    int64_t idims[4] = {g.conv_c, g.conv_w, g.conv_h, g.batch}, istr[4] = {1, g.conv_strides[2], g.conv_strides[1], g.conv_strides[0]};
+    int ibox[4] = {32, 1, 1, 1};
+    if (g.conv_operand != 0) {
+        const int rows = g.conv_operand == 1 ? kGpBlockM : p.bn;
+        if (half || g.conv_c % 32 != 0 || g.conv_ow < 1 || g.conv_ow > 256 || rows % g.conv_ow != 0 || g.conv_r < 1 || g.conv_s < 1 ||
+            g.k != (int64_t)g.conv_r * g.conv_s * g.conv_c)
+            return nullptr;
+        ibox[1] = g.conv_ow;
+        ibox[2] = rows / g.conv_ow;
+        p.conv_operand = g.conv_operand;
+        p.conv_cblocks = g.conv_c / 32;
+        p.conv_s = g.conv_s;
+        p.conv_pad_y = g.conv_pad_y;
+        p.conv_pad_x = g.conv_pad_x;
+        p.conv_ow = g.conv_ow;
+    }
     if (half) {
         l->map_a = tc_make_map_f16(g.a, 3, adims, astr, abox, true);
         l->map_b = tc_make_map_f16(g.b, 3, bdims, bstr, bbox, true);
     } else {
-        l->map_a = tc_make_map(g.a, 3, adims, astr, abox, true);
-        l->map_b = tc_make_map(g.b, 3, bdims, bstr, bbox, true);
+        l->map_a = g.conv_operand == 1 ? tc_make_map(g.a, 4, idims, istr, ibox, true) : tc_make_map(g.a, 3, adims, astr, abox, true);
+        l->map_b = g.conv_operand == 2 ? tc_make_map(g.b, 4, idims, istr, ibox, true) : tc_make_map(g.b, 3, bdims, bstr, bbox, true);
     }
     int64_t cdims[3] = {g.n, g.m, g.batch * splits}, cstr[3] = {1, split ? g.n : g.sc[1], split ? g.m * g.n : g.sc[0]};
     int cbox[3] = {32, kGpBlockM, 1};

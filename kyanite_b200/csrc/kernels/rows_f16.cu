@@ -80,36 +80,15 @@ __global__ void __launch_bounds__(256) rows_f16_vec_kernel(const __grid_constant
     pdl_enter();
     __shared__ float smem[8];
     const int rows_per_block = blockDim.x / TPR;
+    const int64_t row = (int64_t)blockIdx.x * rows_per_block + threadIdx.x / TPR;
     const int t = threadIdx.x % TPR;
-    const int len8 = (int)(p.len >> 3);
-    // Persistent blocks.  While a row is being reduced nothing of it is in flight any more, and the converted row
-    // leaves no registers to hold the next one, so the next row's lines are requested into L2 instead: its loads
-    // then take a fraction of a DRAM round trip.
-    for (int64_t first = (int64_t)blockIdx.x * rows_per_block; first < p.rows; first += (int64_t)gridDim.x * rows_per_block) {
-    const int64_t row = first + threadIdx.x / TPR;
     const bool active = row < p.rows;
     int64_t oi = 0, oo = 0, o1 = 0;
     if (active) offsets(row, p.outer_rank, p.outer_dims, p.in_strides, p.out_strides, SOFTMAX ? p.in1_strides : p.in_strides, oi, oo, o1);
     const uint4* in0 = (const uint4*)((const __half*)p.in0 + oi);
     const uint4* in1 = p.in1 ? (const uint4*)((const __half*)p.in1 + o1) : nullptr;
     uint4* out = (uint4*)((__half*)p.out + oo);
-    {
-        const int64_t next = row + (int64_t)gridDim.x * rows_per_block;
-        if (next < p.rows && (t & 7) == 0) {   // one request per 128-byte line
-            int64_t ni, no, n1;
-            offsets(next, p.outer_rank, p.outer_dims, p.in_strides, p.out_strides, p.in_strides, ni, no, n1);
-            const uint4* nin = (const uint4*)((const __half*)p.in0 + ni);
-#pragma unroll
-            for (int i = 0; i < ITEMS; i++)
-                if (i * TPR + t < len8) asm volatile("prefetch.global.L2 [%0];" ::"l"(nin + i * TPR + t));
-            if (!SOFTMAX && p.in1) {
-                const uint4* nin1 = (const uint4*)((const __half*)p.in1 + ni);
-#pragma unroll
-                for (int i = 0; i < ITEMS; i++)
-                    if (i * TPR + t < len8) asm volatile("prefetch.global.L2 [%0];" ::"l"(nin1 + i * TPR + t));
-            }
-        }
-    }
+    const int len8 = (int)(p.len >> 3);
 
     float v[ITEMS][8];
     const float pad = SOFTMAX ? -INFINITY : 0.f;
@@ -157,11 +136,12 @@ __global__ void __launch_bounds__(256) rows_f16_vec_kernel(const __grid_constant
                 sum += v[i][j];
             }
         sum = reduce_row<TPR, false>(sum, smem);
+        if (!active) return;
         const float inv = 1.0f / sum;
 #pragma unroll
         for (int i = 0; i < ITEMS; i++) {
             const int e = i * TPR + t;
-            if (active && e < len8) {
+            if (e < len8) {
 #pragma unroll
                 for (int j = 0; j < 8; j++) v[i][j] = v[i][j] * inv;
                 out[e] = pack8(v[i]);
@@ -187,17 +167,17 @@ __global__ void __launch_bounds__(256) rows_f16_vec_kernel(const __grid_constant
         }
         const float var = reduce_row<TPR, false>(sq, smem) / n;
         const float inv = 1.0f / sqrtf(var + p.eps);
+        if (!active) return;
 #pragma unroll
         for (int i = 0; i < ITEMS; i++) {
             const int e = i * TPR + t;
-            if (active && e < len8) {
+            if (e < len8) {
 #pragma unroll
                 for (int j = 0; j < 8; j++) v[i][j] = v[i][j] * inv;
                 out[e] = pack8(v[i]);
             }
         }
     }
-    }   // rows of this block
 }
 
 template <bool SOFTMAX>
@@ -353,17 +333,6 @@ bool vec_ok(const RowParams& p, bool softmax) {
     return true;
 }
 
-template <bool SOFTMAX, int TPR, int ITEMS>
-void launch_vec(const RowParams& p, cudaStream_t stream) {
-    const int64_t blocks = (p.rows + (256 / TPR) - 1) / (256 / TPR);
-    // persistent blocks: as many as are resident at once on the 148 SMs
-    int per_sm = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, rows_f16_vec_kernel<SOFTMAX, TPR, ITEMS>, 256, 0) != cudaSuccess || per_sm < 1)
-        per_sm = 1;
-    launch_pdl(rows_f16_vec_kernel<SOFTMAX, TPR, ITEMS>, dim3((unsigned)std::min<int64_t>(blocks, (int64_t)148 * per_sm)), dim3(256),
-               (size_t)0, stream, p);
-}
-
 template <bool SOFTMAX>
 int launch_rows(const RowParams& p, cudaStream_t stream) {
     if (p.rows == 0 || p.len == 0) return 0;
@@ -371,16 +340,18 @@ int launch_rows(const RowParams& p, cudaStream_t stream) {
     if (vec_ok(p, SOFTMAX)) {
         const int len8 = (int)(p.len / 8);
         if (len8 <= 256) {   // one warp per row, eight rows per block
+            const unsigned grid = (unsigned)((p.rows + 7) / 8);
             const int items = (len8 + 31) / 32;
-            if (items <= 1) launch_vec<SOFTMAX, 32, 1>(p, stream);
-            else if (items <= 2) launch_vec<SOFTMAX, 32, 2>(p, stream);
-            else if (items <= 4) launch_vec<SOFTMAX, 32, 4>(p, stream);
-            else launch_vec<SOFTMAX, 32, 8>(p, stream);
+            if (items <= 1) launch_pdl(rows_f16_vec_kernel<SOFTMAX, 32, 1>, dim3(grid), dim3(256), (size_t)0, stream, p);
+            else if (items <= 2) launch_pdl(rows_f16_vec_kernel<SOFTMAX, 32, 2>, dim3(grid), dim3(256), (size_t)0, stream, p);
+            else if (items <= 4) launch_pdl(rows_f16_vec_kernel<SOFTMAX, 32, 4>, dim3(grid), dim3(256), (size_t)0, stream, p);
+            else launch_pdl(rows_f16_vec_kernel<SOFTMAX, 32, 8>, dim3(grid), dim3(256), (size_t)0, stream, p);
         } else {             // one block per row
+            const unsigned grid = (unsigned)p.rows;
             const int items = (len8 + 255) / 256;
-            if (items <= 2) launch_vec<SOFTMAX, 256, 2>(p, stream);
-            else if (items <= 4) launch_vec<SOFTMAX, 256, 4>(p, stream);
-            else launch_vec<SOFTMAX, 256, 8>(p, stream);
+            if (items <= 2) launch_pdl(rows_f16_vec_kernel<SOFTMAX, 256, 2>, dim3(grid), dim3(256), (size_t)0, stream, p);
+            else if (items <= 4) launch_pdl(rows_f16_vec_kernel<SOFTMAX, 256, 4>, dim3(grid), dim3(256), (size_t)0, stream, p);
+            else launch_pdl(rows_f16_vec_kernel<SOFTMAX, 256, 8>, dim3(grid), dim3(256), (size_t)0, stream, p);
         }
         return (int)cudaGetLastError();
     }

@@ -826,6 +826,7 @@ class Planner {
         PlanTensor out;
         bool tensor_core = false, as_gemm = false;
         PlanTensor conv_view;   // as_gemm: the matmul's output seen as [N, K, OH, OW]
+        ConvGemm implicit;      // as_gemm with an implicit operand (implicit.implicit != 0)
         if (opts_.math_mode == KN_MATH_TF32) {
             if (ci.op == OpKind::MatMul) {
                 // An operand that is not contiguous along K (the value matrix of an attention head arrives as
@@ -849,6 +850,7 @@ class Planner {
                 conv_view = g->result;
                 as_gemm = true;
                 tensor_core = true;
+                implicit = *g;
             }
             else tensor_core = conv_fits_tensor_core(ci, x, w, native);
         }
@@ -873,17 +875,39 @@ class Planner {
             s.writes.push_back(0);
         }
         if (ci.op == OpKind::MatMul || as_gemm) {
-            KN_CHECK(x.ss.rank() == 3 && w.ss.rank() == 3, KN_ERR_SHAPE, "matmul operands must have rank 3");
             s.kind = StepKind::Gemm;
             GemmParams& p = s.gemm;
-            p.batch = x.ss.shape[0];
-            p.m = x.ss.shape[1];
-            p.k = x.ss.shape[2];
-            p.n = w.ss.shape[2];
-            KN_CHECK(w.ss.shape[0] == p.batch && w.ss.shape[1] == p.k, KN_ERR_SHAPE, "matmul operand shapes differ");
+            if (implicit.implicit != 0) {
+                // the image tensor stands for operand a or b: its strides go to the convolution fields
+                const PlanTensor& img = implicit.implicit == 1 ? x : w;
+                p.batch = implicit.batch;
+                p.m = implicit.m;
+                p.n = implicit.n;
+                p.k = implicit.k;
+                p.conv_operand = implicit.implicit;
+                p.conv_c = (int32_t)img.ss.shape[1];
+                p.conv_h = (int32_t)img.ss.shape[2];
+                p.conv_w = (int32_t)img.ss.shape[3];
+                p.conv_ow = (int32_t)native[3];
+                const std::vector<int64_t> filter_shape = shape_of(ci.inputs[1]);
+                p.conv_r = (int32_t)filter_shape[2];
+                p.conv_s = (int32_t)filter_shape[3];
+                p.conv_pad_y = ci.pad_y;
+                p.conv_pad_x = ci.pad_x;
+                p.conv_strides[0] = img.ss.strides[0];
+                p.conv_strides[1] = img.ss.strides[2];
+                p.conv_strides[2] = img.ss.strides[3];
+            } else {
+                KN_CHECK(x.ss.rank() == 3 && w.ss.rank() == 3, KN_ERR_SHAPE, "matmul operands must have rank 3");
+                p.batch = x.ss.shape[0];
+                p.m = x.ss.shape[1];
+                p.k = x.ss.shape[2];
+                p.n = w.ss.shape[2];
+                KN_CHECK(w.ss.shape[0] == p.batch && w.ss.shape[1] == p.k, KN_ERR_SHAPE, "matmul operand shapes differ");
+            }
             for (int i = 0; i < 3; i++) {
-                p.sa[i] = x.ss.strides[i];
-                p.sb[i] = w.ss.strides[i];
+                if (implicit.implicit != 1) p.sa[i] = x.ss.strides[i];
+                if (implicit.implicit != 2) p.sb[i] = w.ss.strides[i];
                 p.sc[i] = out.ss.strides[i];
                 if (addends.size() > 0) p.s1[i] = addends[0].ss.strides[i];
                 if (addends.size() > 1) p.s2[i] = addends[1].ss.strides[i];
@@ -954,7 +978,9 @@ class Planner {
         if (s.kind == StepKind::Gemm && s.gemm.splits > 1) s.desc += " splitk=" + std::to_string(s.gemm.splits);
         int64_t total = 1;
         for (int64_t d : native) total *= d;
-        if (as_gemm) s.desc += " (conv via im2col, stride " + std::to_string(ci.stride_y) + "x" + std::to_string(ci.stride_x) + ")";
+        if (as_gemm && implicit.implicit != 0)
+            s.desc += std::string(" (conv, windows read from the image as operand ") + (implicit.implicit == 1 ? "a" : "b") + ")";
+        else if (as_gemm) s.desc += " (conv via im2col, stride " + std::to_string(ci.stride_y) + "x" + std::to_string(ci.stride_x) + ")";
         if (total != 0) push_step(std::move(s));
 
         if (as_gemm) out = conv_view;
@@ -1265,6 +1291,10 @@ class Planner {
     struct ConvGemm {
         PlanTensor a, b, c, result;
         std::vector<PlanTensor> addends;
+        // implicit route: operand `implicit` (1 = a, 2 = b) is the channels-last image tensor itself, the matmul reads
+        // the windows straight from it (GemmParams::conv_operand); dims of the matmul it stands for
+        int implicit = 0;
+        int64_t batch = 0, m = 0, n = 0, k = 0;
     };
     std::optional<ConvGemm> conv_as_gemm(const ValueInfo& ci, const PlanTensor& x, const PlanTensor& w, const std::vector<int64_t>& native,
                                          const std::vector<PlanTensor>& addends, int root) {
@@ -1280,7 +1310,11 @@ class Planner {
         // a long reduction over many channels: the convolution kernels' 128-channel tiles and row-per-thread
         // epilogue reach about 0.2 of the tensor peak there, im2col + the persistent matmul about 0.5, which
         // pays for writing the R*S times larger matrix as long as that stays a few hundred MB
-        const bool long_k = C * R * S >= 2048 && N * OH * OW * R * S * C * 4 <= (256ll << 20);
+        // (the limit is on the materialised matrix; the implicit route below has none, its operand tile rows being whole
+        // output rows is checked there)
+        const bool may_be_implicit = !strided && C % 32 == 0 && OW <= 256 && 128 % OW == 0 && OH * OW >= 64 &&
+                                     !(opts_.flags & KN_FLAG_NO_PERSISTENT_GEMM);
+        const bool long_k = C * R * S >= 2048 && (may_be_implicit || N * OH * OW * R * S * C * 4 <= (256ll << 20));
         if (!strided && !few_positions && !pointwise && !long_k) return std::nullopt;
         if (N < 1 || N > 65535 || OH * OW < 64 || K < 16 || K % 4 != 0 || C < 1 || R * S > 64) return std::nullopt;
         if (2.0 * (double)N * OH * OW * K * C * R * S < 2e8) return std::nullopt;
@@ -1323,6 +1357,51 @@ class Planner {
         PlanTensor wmat = alloc_const({K, kk}, DType::F32, ci.inputs[1], nullptr, data);
         if (nchw) g.a = wmat.with(StridedShape({N, K, kk}, {0, kk, 1}));
         else g.b = wmat.with(StridedShape({N, kk, K}, {0, 1, kk}));
+        // Implicit route: a stride-1 convolution over whole 32-channel blocks whose output rows tile the matmul
+        // kernel's operand tiles reads its windows straight from the channels-last image (one pass over the input to
+        // make it channels-last, if it is not) instead of from a materialised [positions, R*S*C] matrix, which is
+        // R*S times the input, written once and read once.
+        {
+            const int64_t rows = nchw ? gemm_persistent_bn(OH * OW) : 128;
+            const bool fits = !strided && !pointwise && c_pad == C && C % 32 == 0 && OW <= 256 && rows % OW == 0 && OH * OW >= 64 &&
+                              !(opts_.flags & KN_FLAG_NO_PERSISTENT_GEMM) && H <= 32768 && W <= 32768;
+            if (fits) {
+                PlanTensor xcl = channels_last(x, ci.inputs[0]);
+                const auto& cs = xcl.ss.strides;
+                if ((C <= 1 || cs[1] == 1) && cs[3] % 4 == 0 && cs[2] % 4 == 0 && (N <= 1 || cs[0] % 4 == 0) && cs[3] > 0 && cs[2] > 0) {
+                    g.implicit = nchw ? 2 : 1;
+                    g.batch = N;
+                    g.k = kk;
+                    // The persistent kernel is the only one that reads an implicit operand, and its epilogue takes an
+                    // addend per row, per column, or per element with contiguous rows.  Anything else (a skip
+                    // tensor that is channels-last where the result is not, or the other way round) is copied
+                    // into the result's layout first: one pass over a tensor the size of the result.
+                    for (PlanTensor& t : g.addends) {
+                        const auto& st = t.ss.strides;
+                        if (st[1] == 0 || st[2] == 1 || st[2] == 0) continue;
+                        PlanTensor dense = alloc_shared(t.ss.shape, DType::F32, root);
+                        emit_copy(t, dense, root);
+                        t = dense;
+                    }
+                    if (nchw) {
+                        g.b = xcl;
+                        g.m = K;
+                        g.n = OH * OW;
+                        g.c = alloc_shared({N, K, OH * OW}, DType::F32, root);
+                        g.result = g.c.with(StridedShape({N, K, OH, OW}, {K * OH * OW, OH * OW, OW, 1}));
+                    } else {
+                        g.a = xcl;
+                        g.m = OH * OW;
+                        g.n = K;
+                        g.c = alloc_shared({N, OH * OW, K}, DType::F32, root);
+                        g.result = g.c.with(StridedShape({N, K, OH, OW}, {OH * OW * K, 1, OW * K, K}));
+                    }
+                    return g;
+                }
+            }
+        }
+        // (a long-reduction convolution that did not take the implicit route after all: the size limit applies)
+        if (!strided && !few_positions && !pointwise && N * OH * OW * R * S * C * 4 > (256ll << 20)) return std::nullopt;
         // im2col (not needed for a 1x1 stride-1 convolution of a channels-last tensor: that is the matrix already)
         PlanTensor col;
         const auto& xs = x.ss.strides;

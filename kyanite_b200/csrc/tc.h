@@ -16,6 +16,9 @@ int tc_launch_step(const Step& step, cudaStream_t stream);
 // Stores the calling thread's error message (what kn_last_error returns).
 void set_last_error(const std::string& message);
 
+// Column-block width the persistent matmul kernel picks for a matrix with n columns (kernels/gemm_persistent.cu).
+int gemm_persistent_bn(int64_t n);
+
 // Output tile of the convolution kernel: wb x hb x nb output positions (product 128).
 bool tc_conv_tile(int oh, int ow, int* wb, int* hb, int* nb);
 
