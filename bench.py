@@ -53,7 +53,8 @@ def load_peaks():
     if os.path.exists(path):
         with open(path) as f:
             p = json.load(f)
-        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"], "source": "measured"}
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"], "bf16_tflops_sustained": p.get("bf16_tflops_sustained"),
+                "source": "measured"}
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
@@ -371,6 +372,25 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    def time_dominant():
+        """[(us per launch, flop, kind, description)] of the contraction step(s) with the most FLOP: 20 launches back
+        to back between one pair of CUDA events on the executor's stream."""
+        nonlocal launches
+        ex.set_profile(True)
+        ex.run_async()
+        launches += launches_per_run
+        contractions = []
+        for line in ex.last_profile().splitlines():
+            parts = line.split()
+            if len(parts) > 6 and parts[0].isdigit() and parts[1].split("/")[0] in ("Conv", "ConvChain", "Gemm"):
+                contractions.append((int(parts[0]), float(parts[4]), parts[1], " ".join(parts[5:])))
+        ex.set_profile(False)
+        if not contractions:
+            return []
+        top = max(c[1] for c in contractions)
+        launches += 21 * sum(1 for c in contractions if c[1] == top)
+        return [(ex.time_step(idx, 20), flop, kind, desc) for idx, flop, kind, desc in contractions if flop == top]
+
     # clocks: one sampler (rank 0's GPU), every 50 ms, so that N ranks do not add N polling threads to the host
     sampler = None
     if rank == 0:
@@ -383,6 +403,8 @@ def main():
     ex.synchronize()
 
     launches = args.warmup * launches_per_run
+    # the dominant kernel before the GPU has been under load for seconds (burst clocks); timed again at the end
+    dominant_before_load = time_dominant()
 
     # ---- one executor, one step after the other, L2 flushed before every timed step (`config.one_executor_flushed`)
     barrier()
@@ -525,20 +547,7 @@ def main():
     # whole residual tower in one launch; with chains switched off, the trunk convolutions, which are
     # timed one by one and averaged).  Each is launched 20x back to back between one pair of CUDA events
     # on the executor's stream.
-    ex.set_profile(True)
-    ex.run_async()
-    launches += launches_per_run
-    contractions = []
-    for line in ex.last_profile().splitlines():
-        parts = line.split()
-        if len(parts) > 6 and parts[0].isdigit() and parts[1].split("/")[0] in ("Conv", "ConvChain", "Gemm"):
-            contractions.append((int(parts[0]), float(parts[4]), parts[1], " ".join(parts[5:])))
-    ex.set_profile(False)
-    dominant = []
-    if contractions:
-        top = max(c[1] for c in contractions)
-        dominant = [(ex.time_step(idx, 20), flop, kind, desc) for idx, flop, kind, desc in contractions if flop == top]
-        launches += 21 * len(dominant)
+    dominant = time_dominant()
 
     pipe_ms, e2e_ms, copy_ms = (statistics.median(w) for w in (pipe_windows, e2e_windows, copy_windows))
     mine = torch.tensor([dev_ms, e2e_ms, serial_ms, pipe_ms, copy_ms, pipe_host_us, e2e_host_us], dtype=torch.float64,
@@ -567,7 +576,17 @@ def main():
                         "achieved": achieved, "peak": tensor_peak, "unit": "TFLOP/s", "frac": achieved / tensor_peak,
                         "traffic": CHAIN_DRAM_BYTES if chain else TRUNK_CONV_DRAM_BYTES,
                         "peak_source": f"{peaks['source']} bf16 burst / 2 (tf32)", "us_per_launch": us,
-                        "gflop_per_launch": flop / 1e9, "launches_per_step": len(dominant)}
+                        "gflop_per_launch": flop / 1e9, "launches_per_step": len(dominant),
+                        "when": "20 launches back to back after the timed legs, the GPU under its power cap for seconds; "
+                                "`achieved` and `frac` are this figure against the BURST peak"}
+            if peaks.get("bf16_tflops_sustained"):
+                sustained = peaks["bf16_tflops_sustained"] / 2.0
+                roofline["against_sustained_peak"] = {"peak": sustained, "frac": achieved / sustained}
+            if dominant_before_load:
+                us0 = statistics.mean(u for u, _, _, _ in dominant_before_load)
+                roofline["before_load"] = {"us_per_launch": us0, "achieved": flop / (us0 * 1e-6) / 1e12,
+                                           "frac": flop / (us0 * 1e-6) / 1e12 / tensor_peak,
+                                           "what": "the same 20 launches right after warm-up, at burst clocks, against the burst peak"}
 
         def spread(windows):
             return {"windows": len(windows), "min_ms_per_step": min(windows) / K, "median_ms_per_step": statistics.median(windows) / K,

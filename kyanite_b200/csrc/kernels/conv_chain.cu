@@ -615,10 +615,12 @@ std::shared_ptr<void> chain_prepare(const ConvChainParams& c, uint32_t* status_w
     l->map_tiles = tc_make_map(c.tiles, 3, dims, strides, box, true);
     l->grid = dim3((unsigned)((c.n + g.per_cta - 1) / g.per_cta), 1, 1);
     l->smem_bytes = g.smem_bytes;
-    // Epilogue variants: the accumulator's columns are shared out in chunks among E warps per lane quarter.  Six
-    // warps taking 8-column chunks when the chunk count divides by six (two 8x8 boards: 18 chunks, three each); else
-    // three or two warps taking 16-column chunks.  KN_CHAIN_EPILOGUE=<E> in the environment picks one (measuring).
-    l->epilogue_warps = ((g.n_mma / 8) % 6 == 0) ? 6 : ((g.n_mma / 16) % 3 == 0) ? 3 : 2;
+    // Epilogue variants: the accumulator's columns are shared out in chunks among E warps per lane quarter.  Three
+    // warps taking 16-column chunks when the chunk count divides by three (two 8x8 boards: 9 chunks, three each
+    // instead of five and four), else two.  Four or six warps taking 8-column chunks exist as variants and measured
+    // slower (two boards: 315 / 327 us against 314.5): the epilogue is bound by instruction issue, not by latency.
+    // KN_CHAIN_EPILOGUE=<E> in the environment picks one (measuring).
+    l->epilogue_warps = ((g.n_mma / 16) % 3 == 0) ? 3 : 2;
     if (const char* e = getenv("KN_CHAIN_EPILOGUE")) {
         const int v = atoi(e);
         if (v == 2 || v == 3 || v == 4 || v == 6) l->epilogue_warps = v;
