@@ -330,6 +330,7 @@ def main():
     ap.add_argument("--no-library-proxy", action="store_true")
     ap.add_argument("--no-chain", action="store_true", help="one launch per convolution instead of the merged chain kernel (A/B)")
     ap.add_argument("--e2e-executors", type=int, default=2, help="executors per GPU in the pipelined measurements")
+    ap.add_argument("--no-bind", action="store_true", help="leave the process's CPU affinity alone (A/B)")
     ap.add_argument("--min-seconds", type=float, default=1.5,
                     help="each pipelined leg repeats its window of --steps steps until this much time is covered")
     args = ap.parse_args()
@@ -348,11 +349,16 @@ def main():
 
     from kyanite_b200.configs import resnet_tower, resnet_tower_flops
     from kyanite_b200.executor import FLAG_NO_CONV_CHAIN, MATH_F32, MATH_TF32, CudaExecutor
+    from kyanite_b200.sharding import bind_process_near_gpu
 
     torch.cuda.set_device(local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    # one process per GPU: keep this rank's host buffers and the threads that fill them next to its GPU
+    affinity = bind_process_near_gpu("GPU-" + str(torch.cuda.get_device_properties(local_rank).uuid)) if not args.no_bind else \
+        {"bound": False, "why": "--no-bind"}
 
     graph, make_inputs = resnet_tower()
     math_mode = MATH_TF32 if args.math == "tf32" else MATH_F32
@@ -556,8 +562,11 @@ def main():
         gathered = [torch.zeros_like(mine) for _ in range(world)]
         dist.all_gather(gathered, mine)
         per_rank = torch.stack(gathered).cpu().numpy()
+        affinities = [None] * world
+        dist.all_gather_object(affinities, affinity)
     else:
         per_rank = mine.cpu().numpy()[None]
+        affinities = [affinity]
     dev_ms, e2e_ms, serial_ms, pipe_ms, copy_ms = (float(per_rank[:, c].max()) for c in range(5))   # MAX over ranks
 
     if rank == 0:
@@ -598,6 +607,7 @@ def main():
             "dtype": "tf32 operands, f32 storage and accumulate" if args.math == "tf32" else "f32",
             "data": "synthetic",
             "config": {"workload": WORKLOAD, "batch_per_gpu": BATCH, "parallelism": f"batch-sharded x{world}, no collective",
+                       "cpu_affinity_per_rank": affinities,
                        "executors_per_gpu": args.e2e_executors,
                        "timing": f"steady state: the pipeline is filled with untimed steps, then windows of {K} steps are "
                                  "timed back to back with CUDA events (no drain in between) for at least "

@@ -101,6 +101,40 @@ def merge_outputs(graph: Graph, per_rank_outputs: Sequence[Sequence[np.ndarray]]
     return merged
 
 
+def cpus_from_affinity_words(words: Sequence[int], bits: int = 64) -> List[int]:
+    """CPU numbers of an affinity bit mask given as machine words, least significant word first (the form NVML
+    returns a device's ideal CPU affinity in)."""
+    return [w * bits + b for w, word in enumerate(words) for b in range(bits) if (int(word) >> b) & 1]
+
+
+def bind_process_near_gpu(gpu_uuid: str, allowed: Optional[Sequence[int]] = None, nvml=None) -> dict:
+    """Restricts the calling process to the CPUs the driver names as closest to the GPU (its NUMA node), so that the
+    rank's host buffers (first touch) and the threads that fill them are local to the GPU's PCIe root.  With one
+    process per GPU and the per-step staging copies of `evaluate`, ranks whose process ran on the far socket took
+    twice as long for the same copies.  Changes nothing but this process's own CPU affinity; does nothing (and says
+    so) when NVML is missing, when the ideal set and the CPUs this process may use do not overlap, or when the
+    process is already inside the ideal set.  `nvml`: the pynvml module or a stand-in (tests)."""
+    import os
+    if allowed is None:
+        allowed = sorted(os.sched_getaffinity(0))
+    try:
+        if nvml is None:
+            import pynvml as nvml
+            nvml.nvmlInit()
+        handle = nvml.nvmlDeviceGetHandleByUUID(gpu_uuid.encode())
+        words = nvml.nvmlDeviceGetCpuAffinity(handle, (max(allowed) // 64 + 1) if allowed else 1)
+    except Exception as e:   # no NVML, or the query is not supported here
+        return {"bound": False, "why": f"no ideal affinity from NVML ({type(e).__name__})", "cpus": len(allowed)}
+    ideal = set(cpus_from_affinity_words(words))
+    target = sorted(ideal.intersection(allowed))
+    if not target:
+        return {"bound": False, "why": "the GPU's ideal CPUs are outside this process's CPU set", "cpus": len(allowed)}
+    if len(target) == len(allowed):
+        return {"bound": False, "why": "already inside the GPU's ideal CPU set", "cpus": len(allowed)}
+    os.sched_setaffinity(0, target)
+    return {"bound": True, "cpus": len(target), "of": len(allowed)}
+
+
 def aggregate_throughput(units_per_rank: Sequence[int], ms_per_rank: Sequence[float]) -> float:
     """Whole-job units per second: all units over the slowest rank's time."""
     return sum(units_per_rank) / (max(ms_per_rank) / 1000.0)

@@ -103,3 +103,54 @@ def test_graphs_that_mix_batch_entries_are_refused():
             split_inputs(g, [np.zeros((4, 6), np.float32)], 4, 0, 2)
     # the same operations along a per-sample axis are fine
     check_shardable(graph_with(lambda g, x: g.softmax(g.flip(x, 1), 1)))
+
+
+def test_affinity_words_and_binding_decisions():
+    """Which CPUs a rank is bound to, against a stand-in for NVML (no GPU, and the test leaves the process's own
+    affinity as it found it)."""
+    import os
+
+    from kyanite_b200.sharding import bind_process_near_gpu, cpus_from_affinity_words
+
+    assert cpus_from_affinity_words([0b1011]) == [0, 1, 3]
+    assert cpus_from_affinity_words([0, 1 << 2]) == [66]
+
+    class FakeNvml:
+        def __init__(self, words):
+            self.words = words
+
+        def nvmlDeviceGetHandleByUUID(self, uuid):
+            assert uuid == b"GPU-x"
+            return object()
+
+        def nvmlDeviceGetCpuAffinity(self, handle, n_words):
+            return self.words[:n_words] + [0] * max(0, n_words - len(self.words))
+
+    before = os.sched_getaffinity(0)
+    try:
+        allowed = sorted(before)
+        # the GPU's CPUs lie outside what this process may use: nothing changes
+        far = [0] * (max(allowed) // 64 + 2)
+        far[-1] = 1 << 63
+        r = bind_process_near_gpu("GPU-x", allowed=allowed, nvml=FakeNvml(far))
+        assert r["bound"] is False and os.sched_getaffinity(0) == before
+        # every allowed CPU is ideal: nothing to do
+        every = [(1 << 64) - 1] * (max(allowed) // 64 + 1)
+        r = bind_process_near_gpu("GPU-x", allowed=allowed, nvml=FakeNvml(every))
+        assert r["bound"] is False and os.sched_getaffinity(0) == before
+        # a query that fails is reported, not raised
+        class Broken(FakeNvml):
+            def nvmlDeviceGetCpuAffinity(self, handle, n_words):
+                raise RuntimeError("not supported")
+        assert bind_process_near_gpu("GPU-x", allowed=allowed, nvml=Broken([]))["bound"] is False
+        if len(allowed) >= 2:
+            # half of the allowed CPUs are ideal: the process is restricted to them
+            half = allowed[: len(allowed) // 2]
+            words = [0] * (max(allowed) // 64 + 1)
+            for c in half:
+                words[c // 64] |= 1 << (c % 64)
+            r = bind_process_near_gpu("GPU-x", allowed=allowed, nvml=FakeNvml(words))
+            assert r == {"bound": True, "cpus": len(half), "of": len(allowed)}
+            assert sorted(os.sched_getaffinity(0)) == half
+    finally:
+        os.sched_setaffinity(0, before)
