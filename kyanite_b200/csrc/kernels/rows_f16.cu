@@ -34,11 +34,14 @@ template <int TPR, bool IS_MAX>
 __device__ __forceinline__ float reduce_row(float v, float* smem) {
     v = IS_MAX ? wmax(v) : wsum(v);
     if (TPR == 32) return v;
+    // (a block may hold several rows of TPR threads each: a row's warps are neighbours)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int kWarpsPerRow = TPR >> 5;
+    const int first = (warp / kWarpsPerRow) * kWarpsPerRow;
     __syncthreads();
     if (lane == 0) smem[warp] = v;
     __syncthreads();
-    float r = lane < (TPR >> 5) ? smem[lane] : (IS_MAX ? -INFINITY : 0.0f);
+    float r = lane < kWarpsPerRow ? smem[first + lane] : (IS_MAX ? -INFINITY : 0.0f);
     return IS_MAX ? wmax(r) : wsum(r);
 }
 
@@ -339,13 +342,18 @@ int launch_rows(const RowParams& p, cudaStream_t stream) {
     if (p.rows > 0x7FFFFFFFll) return (int)cudaErrorInvalidValue;
     if (vec_ok(p, SOFTMAX)) {
         const int len8 = (int)(p.len / 8);
-        if (len8 <= 256) {   // one warp per row, eight rows per block
+        if (len8 <= 128) {   // one warp per row, eight rows per block
             const unsigned grid = (unsigned)((p.rows + 7) / 8);
             const int items = (len8 + 31) / 32;
             if (items <= 1) launch_pdl(rows_f16_vec_kernel<SOFTMAX, 32, 1>, dim3(grid), dim3(256), (size_t)0, stream, p);
             else if (items <= 2) launch_pdl(rows_f16_vec_kernel<SOFTMAX, 32, 2>, dim3(grid), dim3(256), (size_t)0, stream, p);
-            else if (items <= 4) launch_pdl(rows_f16_vec_kernel<SOFTMAX, 32, 4>, dim3(grid), dim3(256), (size_t)0, stream, p);
-            else launch_pdl(rows_f16_vec_kernel<SOFTMAX, 32, 8>, dim3(grid), dim3(256), (size_t)0, stream, p);
+            else launch_pdl(rows_f16_vec_kernel<SOFTMAX, 32, 4>, dim3(grid), dim3(256), (size_t)0, stream, p);
+        } else if (len8 <= 256) {
+            // Four warps per row, two rows per block.  One warp per row would hold 64 converted values plus the raw
+            // loads per lane: more than 128 registers, so one block of 8 warps per SM and half the bandwidth
+            // (measured on 2048-element rows: 0.54 of the copy bandwidth).
+            const unsigned grid = (unsigned)((p.rows + 1) / 2);
+            launch_pdl(rows_f16_vec_kernel<SOFTMAX, 128, 2>, dim3(grid), dim3(256), (size_t)0, stream, p);
         } else {             // one block per row
             const unsigned grid = (unsigned)p.rows;
             const int items = (len8 + 255) / 256;
