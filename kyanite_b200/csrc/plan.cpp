@@ -2186,7 +2186,8 @@ std::string Plan::describe() const {
         os << "step " << i << " " << step_kind_name(s.kind) << (s.tensor_core ? "/tc" : "") << " value=" << s.value << " " << s.desc;
         if (s.kind == StepKind::Scalar)
             os << " loads=" << s.scalar.n_loads << " instr=" << s.scalar.n_instr << " rank=" << s.scalar.rank
-               << (s.scalar.vec4 >= 3 ? " vec8" : (s.scalar.vec4 ? " vec4" : ""));
+               << (s.scalar.vec4 >= 3 ? " vec8" : (s.scalar.vec4 ? " vec4" : ""))
+               << ((s.scalar.vec4 == 2 || s.scalar.vec4 == 4) ? " acc" : "");
         os << " bytes=" << (uint64_t)s.alg_bytes << " flops=" << (uint64_t)s.flops << " [";
         for (size_t o = 0; o < s.operands.size(); o++) os << (o ? " " : "") << (s.writes[o] ? "w:" : "r:") << s.operands[o].str();
         os << "]\n";
