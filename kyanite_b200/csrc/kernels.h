@@ -39,7 +39,8 @@ struct ScalarParams {
     int32_t rank, n_operands, n_loads, n_instr, n_stores;
     int32_t vec4;    // 1: every operand is f32 with innermost stride 1 (or 0) and 16-byte aligned rows; 2: the same as an
                      // accumulator program (below); 3: operands and values are f16 or f32, innermost stride 1 (or 0),
-                     // 16-byte aligned rows, eight elements per access; 4: the same as an accumulator program
+                     // 16-byte aligned rows, eight elements per access; 4: the same as an accumulator program; 5: an
+                     // accumulator program whose operands and values are all f16 (runs on packed halves)
     int64_t total;   // element count
     int64_t dims[DEV_MAX_RANK];
     void* ptr[SCALAR_MAX_OPERANDS];

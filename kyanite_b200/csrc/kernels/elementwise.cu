@@ -507,6 +507,211 @@ int launch_acc(const ScalarParams& p, cudaStream_t stream) {
     return (int)cudaGetLastError();
 }
 
+// ---------------------------------------------------------------- accumulator programs over f16 only
+// Every operand and every value of the program is f16.  Values then travel as packed halves (eight per 128-bit
+// register) and add / subtract / multiply / min / max run as half2 instructions: an f16 <-> f32 conversion issues at
+// a fraction of the arithmetic rate, and the f32 route spends several per element (SwiGLU ran at 0.46 of the copy
+// bandwidth on them).  The result is the same bit for bit: an IEEE half operation rounds the exact result once, the
+// oracle rounds it to f32 and then to f16, and for + - x that double rounding is innocuous because 24 >= 2 * 11 + 2
+// significand bits.  Everything else (division, powers, transcendental unaries) converts, computes in f32 and rounds.
+template <int V>
+struct VecH {
+    uint4 v[V];   // 8 halves each
+};
+
+__device__ __forceinline__ uint4 splat_h(uint16_t bits) {
+    const uint32_t w = (uint32_t)bits * 0x00010001u;
+    return make_uint4(w, w, w, w);
+}
+template <typename F>
+__device__ __forceinline__ uint4 map_h2(const uint4& a, const uint4& b, F f) {
+    uint4 r;
+    const __half2* x = (const __half2*)&a;
+    const __half2* y = (const __half2*)&b;
+    __half2* o = (__half2*)&r;
+#pragma unroll
+    for (int i = 0; i < 4; i++) o[i] = f(x[i], y[i]);
+    return r;
+}
+// through f32: 8 halves -> two float4 -> f -> rounded back
+template <typename F>
+__device__ __forceinline__ uint4 via_f32(const uint4& a, const uint4& b, F f) {
+    const __half2* x = (const __half2*)&a;
+    const __half2* y = (const __half2*)&b;
+    uint4 r;
+    __half2* o = (__half2*)&r;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const float2 p = __half22float2(x[i]), q = __half22float2(y[i]);
+        o[i] = __floats2half2_rn(f(p.x, q.x), f(p.y, q.y));
+    }
+    return r;
+}
+
+template <int V>
+__device__ __forceinline__ void unary_h(UnaryOp op, VecH<V>& acc, const VecH<V>& a) {
+#pragma unroll
+    for (int i = 0; i < V; i++) {
+        switch (op) {   // uniform
+            case UnaryOp::Neg: acc.v[i] = map_h2(a.v[i], a.v[i], [](__half2 x, __half2) { return __hneg2(x); }); break;
+            case UnaryOp::Abs: acc.v[i] = map_h2(a.v[i], a.v[i], [](__half2 x, __half2) { return __habs2(x); }); break;
+            // (the hardware exponential and reciprocal, errors near 2^-21: the result is rounded to f16)
+            case UnaryOp::Sigmoid: acc.v[i] = via_f32(a.v[i], a.v[i], [](float x, float) { return __fdividef(1.0f, 1.0f + __expf(-x)); }); break;
+            case UnaryOp::ValueCast: acc.v[i] = a.v[i]; break;
+            default: acc.v[i] = via_f32(a.v[i], a.v[i], [op](float x, float) { return f32_unary(op, x); }); break;
+        }
+    }
+}
+template <int V>
+__device__ __forceinline__ void binary_h(BinaryOp op, VecH<V>& acc, const VecH<V>& a, const VecH<V>& b) {
+#pragma unroll
+    for (int i = 0; i < V; i++) {
+        switch (op) {   // uniform
+            case BinaryOp::Add: acc.v[i] = map_h2(a.v[i], b.v[i], [](__half2 x, __half2 y) { return __hadd2_rn(x, y); }); break;
+            case BinaryOp::Sub: acc.v[i] = map_h2(a.v[i], b.v[i], [](__half2 x, __half2 y) { return __hsub2_rn(x, y); }); break;
+            case BinaryOp::Mul: acc.v[i] = map_h2(a.v[i], b.v[i], [](__half2 x, __half2 y) { return __hmul2_rn(x, y); }); break;
+            case BinaryOp::Min: acc.v[i] = map_h2(a.v[i], b.v[i], [](__half2 x, __half2 y) { return __hmin2(x, y); }); break;
+            case BinaryOp::Max: acc.v[i] = map_h2(a.v[i], b.v[i], [](__half2 x, __half2 y) { return __hmax2(x, y); }); break;
+            case BinaryOp::Div: acc.v[i] = via_f32(a.v[i], b.v[i], [](float x, float y) { return x / y; }); break;
+            default: acc.v[i] = via_f32(a.v[i], b.v[i], [](float x, float y) { return powf(x, y); }); break;
+        }
+    }
+}
+
+template <int V, bool RANK1>
+__global__ void __launch_bounds__(kThreads) scalar_h2_kernel(const __grid_constant__ ScalarParams p) {
+    constexpr int kRegOperands = kRegOperandsMixed;
+    pdl_enter();
+    extern __shared__ float4 spill[];   // [slot][position][thread], 16 bytes = 8 halves per entry
+    uint4* const my_spill = (uint4*)spill + threadIdx.x;
+    const int last = p.rank - 1;
+    const uint32_t inner_v = (uint32_t)(p.dims[last] / (8 * V));   // groups of V positions along the innermost axis
+    const uint32_t total_v = (uint32_t)(p.total / (8 * V));
+    const uint32_t step = gridDim.x * blockDim.x;
+    bool strided[kRegOperands];   // false = broadcast along the innermost axis
+#pragma unroll
+    for (int o = 0; o < kRegOperands; o++) strided[o] = o < p.n_operands && p.strides[o][last] != 0;
+    auto slot_read = [&](int slot, VecH<V>& out) {
+#pragma unroll
+        for (int v = 0; v < V; v++) out.v[v] = my_spill[(slot * V + v) * kThreads];
+    };
+
+    for (uint32_t g = blockIdx.x * blockDim.x + threadIdx.x; g < total_v; g += step) {
+        uint32_t off[kRegOperands];   // element offset of the group's first position
+        if (RANK1) {
+#pragma unroll
+            for (int o = 0; o < kRegOperands; o++) off[o] = strided[o] ? g * (uint32_t)(8 * V) : 0u;
+        } else {
+            uint32_t rem = g / inner_v;
+            const uint32_t inner = (g - rem * inner_v) * (uint32_t)(8 * V);
+#pragma unroll
+            for (int o = 0; o < kRegOperands; o++) off[o] = strided[o] ? inner : 0u;
+            for (int d = last - 1; d >= 0; d--) {
+                const uint32_t dim = (uint32_t)p.dims[d];
+                const uint32_t q = rem / dim;
+                const uint32_t i = rem - q * dim;
+                rem = q;
+#pragma unroll
+                for (int o = 0; o < kRegOperands; o++)
+                    if (o < p.n_operands) off[o] += i * (uint32_t)p.strides[o][d];
+            }
+        }
+        const __half* base[kRegOperands];
+#pragma unroll
+        for (int o = 0; o < kRegOperands; o++) base[o] = o < p.n_operands ? (const __half*)p.ptr[o] + off[o] : nullptr;
+        auto operand = [&](int o, bool* is_strided) -> const __half* {
+            switch (o) {
+                case 0: *is_strided = strided[0]; return base[0];
+                case 1: *is_strided = strided[1]; return base[1];
+                case 2: *is_strided = strided[2]; return base[2];
+                case 3: *is_strided = strided[3]; return base[3];
+                case 4: *is_strided = strided[4]; return base[4];
+                default: *is_strided = strided[5]; return base[5];
+            }
+        };
+
+        VecH<V> acc;
+#pragma unroll
+        for (int v = 0; v < V; v++) acc.v[v] = make_uint4(0u, 0u, 0u, 0u);
+        for (int k = 0; k < p.n_micro; k++) {
+            const ScalarInstr in = p.micro[k];
+            VecH<V> a = acc, b = acc;
+            if (in.kind != 0 && in.kind != 3 && in.a != 255) slot_read(in.a, a);
+            switch (in.kind) {
+                case 0:
+#pragma unroll
+                    for (int v = 0; v < V; v++) acc.v[v] = splat_h((uint16_t)in.imm);
+                    break;
+                case 1:
+                    unary_h<V>((UnaryOp)in.op, acc, a);
+                    break;
+                case 2:
+                    if (in.b != 255) slot_read(in.b, b);
+                    binary_h<V>((BinaryOp)in.op, acc, a, b);
+                    break;
+                case 3: {
+                    bool st;
+                    const __half* src = operand(in.a, &st);
+                    if (st) {
+#pragma unroll
+                        for (int v = 0; v < V; v++) acc.v[v] = __ldg((const uint4*)src + v);
+                    } else {
+                        const uint4 x = splat_h(__half_as_ushort(__ldg(src)));
+#pragma unroll
+                        for (int v = 0; v < V; v++) acc.v[v] = x;
+                    }
+                    break;
+                }
+                case 4: {
+                    bool st;
+                    __half* dst = const_cast<__half*>(operand(in.b, &st));
+#pragma unroll
+                    for (int v = 0; v < V; v++) *((uint4*)dst + v) = a.v[v];
+                    break;
+                }
+                case 5:
+#pragma unroll
+                    for (int v = 0; v < V; v++) b.v[v] = splat_h((uint16_t)in.imm);
+                    binary_h<V>((BinaryOp)in.op, acc, a, b);
+                    break;
+                default:
+#pragma unroll
+                    for (int v = 0; v < V; v++) b.v[v] = splat_h((uint16_t)in.imm);
+                    binary_h<V>((BinaryOp)in.op, acc, b, a);
+                    break;
+            }
+            if ((in.pad & 0xFF) != 255) {
+#pragma unroll
+                for (int v = 0; v < V; v++) my_spill[((int)(in.pad & 0xFF) * V + v) * kThreads] = acc.v[v];
+            }
+        }
+    }
+}
+
+template <int V>
+int launch_h2(const ScalarParams& p, cudaStream_t stream) {
+    const int64_t groups = p.total / (8 * V);
+    const int grid = grid_for(groups);
+    const size_t smem = (size_t)p.n_regs * V * kThreads * sizeof(uint4);
+    static std::mutex mu;
+    static bool done[64] = {false};   // (one set per instantiation of this template)
+    int device = 0;
+    cudaGetDevice(&device);
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (device >= 0 && device < 64 && !done[device]) {
+            cudaError_t e1 = cudaFuncSetAttribute(scalar_h2_kernel<V, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024);
+            cudaError_t e2 = cudaFuncSetAttribute(scalar_h2_kernel<V, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024);
+            if (e1 != cudaSuccess) return (int)e1;
+            if (e2 != cudaSuccess) return (int)e2;
+            done[device] = true;
+        }
+    }
+    if (p.rank == 1) launch_pdl(scalar_h2_kernel<V, true>, dim3(grid), dim3(kThreads), (size_t)(smem), stream, p);
+    else launch_pdl(scalar_h2_kernel<V, false>, dim3(grid), dim3(kThreads), (size_t)(smem), stream, p);
+    return (int)cudaGetLastError();
+}
+
 // ---------------------------------------------------------------- transposing copy
 // A plain copy of 4-byte elements whose source is contiguous along one axis (s) and whose destination is
 // contiguous along another (t): a [batch, k, n] matmul operand rewritten K-contiguous, a head split.
@@ -600,7 +805,7 @@ bool as_transpose(const ScalarParams& p, TransposeParams& q) {
 
 int launch_scalar(const ScalarParams& p, cudaStream_t stream) {
     if (p.total == 0) return 0;
-    if (p.vec4 != 2 && p.vec4 != 4) {
+    if (p.vec4 != 2 && p.vec4 != 4 && p.vec4 != 5) {
         TransposeParams q;
         if (as_transpose(p, q)) {
             int64_t blocks = q.tiles_s * q.tiles_t;
@@ -619,6 +824,13 @@ int launch_scalar(const ScalarParams& p, cudaStream_t stream) {
         if (inner4 % 4 == 0 && p.n_regs <= 4) return launch_acc<4, false>(p, stream);
         if (inner4 % 2 == 0) return launch_acc<2, false>(p, stream);
         return launch_acc<1, false>(p, stream);
+    } else if (p.vec4 == 5) {
+        // an accumulator program over f16 only: packed halves, eight per position (the innermost extent is a multiple
+        // of 8, the planner's condition); four positions per thread when the extent and the spill slots allow
+        const int64_t inner8 = p.dims[p.rank - 1] / 8;
+        if (inner8 % 4 == 0 && p.n_regs <= 4) return launch_h2<4>(p, stream);
+        if (inner8 % 2 == 0) return launch_h2<2>(p, stream);
+        return launch_h2<1>(p, stream);
     } else if (p.vec4 == 4) {
         // f16 / f32 mix as an accumulator program: the innermost extent is a multiple of 8 (the planner's condition)
         const int64_t inner4 = p.dims[p.rank - 1] / 4;

@@ -342,7 +342,15 @@ class Planner {
             }
             if (reach >= (1ll << 31) - 16) small = false;
         }
-        if (small && allocate_registers(p)) p.vec4 = mixed ? 4 : 2;
+        if (small && allocate_registers(p)) {
+            p.vec4 = mixed ? 4 : 2;
+            // every operand and every value f16: the program runs on packed halves (mode 5)
+            bool all_half = mixed;
+            for (int o = 0; o < p.n_operands && all_half; o++) all_half = (DType)p.dtype[o] == DType::F16;
+            for (int k = 0; k < p.n_instr && all_half; k++)
+                all_half = (DType)p.instr[k].dtype == DType::F16 && (DType)p.instr[k].from == DType::F16;
+            if (all_half) p.vec4 = 5;
+        }
         push_step(std::move(s));
     }
 
@@ -2187,7 +2195,7 @@ std::string Plan::describe() const {
         if (s.kind == StepKind::Scalar)
             os << " loads=" << s.scalar.n_loads << " instr=" << s.scalar.n_instr << " rank=" << s.scalar.rank
                << (s.scalar.vec4 >= 3 ? " vec8" : (s.scalar.vec4 ? " vec4" : ""))
-               << ((s.scalar.vec4 == 2 || s.scalar.vec4 == 4) ? " acc" : "");
+               << ((s.scalar.vec4 == 2 || s.scalar.vec4 >= 4) ? " acc" : "") << (s.scalar.vec4 == 5 ? " half2" : "");
         os << " bytes=" << (uint64_t)s.alg_bytes << " flops=" << (uint64_t)s.flops << " [";
         for (size_t o = 0; o < s.operands.size(); o++) os << (o ? " " : "") << (s.writes[o] ? "w:" : "r:") << s.operands[o].str();
         os << "]\n";

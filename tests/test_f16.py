@@ -206,3 +206,88 @@ def test_llama_f16_matches_oracle(name, mode):
         for _ in range(2):
             # two decoder layers: about 30 f16 roundings on the path of a logit; tolerance 1e-2 of the logits' scale
             assert_tensors_match(expected, ex.evaluate(ids), 1e-2, 1e-2, abs_scaled=True)
+
+
+def elementwise_f16_graph(kind, rows, cols, broadcast_row=False):
+    """One fused elementwise step over f16 operands: `kind` picks the expression."""
+    from kyanite_b200.graph import BinaryOp, UnaryOp
+    g = Graph()
+    a = g.input(shape(rows, cols), DType.F16)
+    b = g.input(shape(1, cols) if broadcast_row else shape(rows, cols), DType.F16)
+    if broadcast_row:
+        b = g.broadcast(b, shape(rows, cols))
+    if kind == "add":
+        y = g.add(a, b)
+    elif kind == "sub_mul":
+        y = g.mul(g.sub(a, b), b)
+    elif kind == "min_max":
+        y = g.binary(BinaryOp.MAX, g.binary(BinaryOp.MIN, a, b), g.unary(UnaryOp.NEG, b))
+    elif kind == "rope_like":      # a * b + (-a) * b': two products and a sum, as the rotary embedding step
+        c = g.input(shape(rows, cols), DType.F16)
+        y = g.add(g.mul(a, b), g.mul(g.unary(UnaryOp.NEG, c), b))
+    elif kind == "swiglu":
+        y = g.mul(g.mul(g.unary(UnaryOp.SIGMOID, a), a), b)
+    else:                          # "div_abs"
+        y = g.binary(BinaryOp.DIV, g.unary(UnaryOp.ABS, a), g.add(g.unary(UnaryOp.ABS, b), g.scalar(1.0, DType.F16)))
+    g.output(y)
+    return g
+
+
+def test_f16_elementwise_programs_run_on_packed_halves():
+    for kind in ("add", "sub_mul", "min_max", "rope_like", "swiglu", "div_abs"):
+        d = plan_describe(elementwise_f16_graph(kind, 64, 256), 0)
+        assert " half2" in d, (kind, d)
+    # a cast inside the program keeps the f32 route
+    g = Graph()
+    a = g.input(shape(64, 256), DType.F16)
+    b = g.input(shape(64, 256), DType.F32)
+    g.output(g.add(g.value_cast(a, DType.F32), b))
+    assert " half2" not in plan_describe(g, 0)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("broadcast_row", [False, True], ids=["full", "row_broadcast"])
+@pytest.mark.parametrize("kind", ["add", "sub_mul", "min_max", "rope_like"])
+def test_f16_packed_arithmetic_is_bit_exact(kind, broadcast_row):
+    """add / sub / mul / min / max on packed halves: an IEEE half operation rounds the exact result once; the oracle
+    computes in f32 and rounds to f16, and that double rounding is innocuous for these operations (24 >= 2 * 11 + 2
+    significand bits).  So the comparison is exact, over values that include subnormals, large magnitudes and
+    operands of very different exponents."""
+    from kyanite_b200.executor import CudaExecutor
+    rows, cols = 67, 1000 if kind != "rope_like" else 1024
+    cols -= cols % 8
+    r = rng(21)
+
+    def halves(shape_):
+        x = r.standard_normal(shape_) * np.exp2(r.integers(-20, 12, shape_))
+        return x.astype(np.float16)
+
+    inputs = [halves((rows, cols)), halves((1, cols) if broadcast_row else (rows, cols))]
+    if kind == "rope_like":
+        inputs.append(halves((rows, cols)))
+    g = elementwise_f16_graph(kind, rows, cols, broadcast_row)
+    expected = cpu_eval_graph(g.to_bytes(), 0, inputs)[0]
+    with CudaExecutor(0, g, 0) as ex:
+        got = ex.evaluate(inputs)[0]
+    finite = np.isfinite(expected.astype(np.float32))
+    # (the sign of a zero that min / max pick between +0 and -0 is not defined: both zeros count as equal)
+    both_zero = (got == 0) & (expected == 0)
+    different = (got.view(np.uint16) != expected.view(np.uint16)) & finite & ~both_zero
+    assert not different.any(), (int(different.sum()), got[different][:4], expected[different][:4])
+    np.testing.assert_array_equal(np.isnan(got.astype(np.float32)), np.isnan(expected.astype(np.float32)))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kind", ["swiglu", "div_abs"])
+def test_f16_packed_programs_with_f32_steps_match_oracle(kind):
+    """Sigmoid, division: converted, computed in f32 (hardware exponential and reciprocal for the sigmoid) and rounded
+    once: within one f16 rounding step of the oracle (tolerance 1e-3 of the tensor's scale)."""
+    from kyanite_b200.executor import CudaExecutor
+    rows, cols = 40, 2048
+    r = rng(5)
+    inputs = [r.standard_normal((rows, cols)).astype(np.float16) * np.float16(3), r.standard_normal((rows, cols)).astype(np.float16)]
+    g = elementwise_f16_graph(kind, rows, cols)
+    expected = cpu_eval_graph(g.to_bytes(), 0, inputs)
+    with CudaExecutor(0, g, 0) as ex:
+        got = ex.evaluate(inputs)
+    assert_tensors_match(expected, got, 1e-3, 1e-3, abs_scaled=True)
