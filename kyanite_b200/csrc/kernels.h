@@ -111,6 +111,19 @@ struct GatherParams {
     int64_t out_dims[DEV_MAX_RANK], in_strides[DEV_MAX_RANK], out_strides[DEV_MAX_RANK];
 };
 
+// An operand of a matmul that is a head split or head merge of another tensor (attention): instead of a [batch, rows, k]
+// matrix in memory it is a 4-D tensor (k', rows', x, y) with element strides, of which the operand tile at
+// (K offset k0, row offset r0, batch entry bt) starts at coordinates
+//     (k0 % kd,  r0 % rd,  k0 / kd + bt % bi,  r0 / rd + bt / bi).
+// Head split ([B*S, H*D] read as [B*H, S, D]): dims (D, S, H, B), kd = K = D, rd = rows = S, bi = H.
+// Head merge ([B*H, S, D] read as [B*S, H*D]): dims (D, S, H, B), kd = D, rd = S, bi = 1 (one batch entry).
+// Persistent tensor-core kernel only; `sa` / `sb` are not used for such an operand.
+struct GemmOperand4D {
+    int32_t enabled;
+    int32_t kd, rd, bi;
+    int64_t dims[4], strides[4];
+};
+
 // ---- batched matrix multiply with fused epilogue  C = act(A.B + add1 + add2)
 // replaces cublasSgemmStridedBatched (kn-cuda-sys/src/wrapper/group.rs:120-171) plus the scalar
 // kernel that followed it for bias / activation.
@@ -135,6 +148,7 @@ struct GemmParams {
     // `oy * conv_ow + ox` of batch entry `n` is the window of output position (oy, ox) of image n, K index
     // (tap_y * conv_s + tap_x) * conv_c + channel, zeros outside the image (stride-1 convolution as a matmul
     // without materialising the windows).  `sa` / `sb` are not used for that operand.
+    GemmOperand4D a4, b4;    // head split / merge read in place (above)
     int32_t conv_operand;
     int32_t conv_c, conv_h, conv_w, conv_ow, conv_r, conv_s, conv_pad_y, conv_pad_x;
     int64_t conv_strides[3];   // element strides of the image tensor: image, row, pixel (channels are contiguous)

@@ -898,7 +898,7 @@ void tc_prepare_step(Step& step, uint32_t* status_word, int flags, uint32_t* tra
     int64_t n_cols;
     if (step.kind == StepKind::Gemm) {
         const GemmParams& g = step.gemm;
-        if (g.half || g.conv_operand != 0) {
+        if (g.half || g.conv_operand != 0 || g.a4.enabled || g.b4.enabled) {
             // f16 storage, or an implicit convolution operand: the persistent kernel is the only tensor-core kernel
             // that takes these; the planner marks such a step tensor-core only when that kernel takes it
             int per_slice = 0, splits = 1;
@@ -910,7 +910,8 @@ void tc_prepare_step(Step& step, uint32_t* status_word, int flags, uint32_t* tra
             }
             launch->gemm_p = gemm_persistent_prepare(g, status_word, splits, per_slice, trace_words);
             KN_CHECK(launch->gemm_p != nullptr, KN_ERR_INTERNAL,
-                     g.half ? "f16 matmul planned for the tensor cores does not qualify" : "implicit convolution matmul does not qualify");
+                     g.half ? "f16 matmul planned for the tensor cores does not qualify"
+                            : "matmul with an operand read in place (convolution windows, head split or merge) does not qualify");
             if (splits > 1) {
                 SplitKReduceParams& r = launch->reduce;
                 memset(&r, 0, sizeof(r));

@@ -61,6 +61,8 @@ struct GemmPersistentParams {
     // implicit convolution operand (GemmParams::conv_operand): which operand, 32-channel blocks per filter tap,
     // filter width, padding, output width
     int32_t conv_operand, conv_cblocks, conv_s, conv_pad_y, conv_pad_x, conv_ow;
+    // 4-D operands (GemmOperand4D): kd as a shift (0: the K offset is not split), rd, bi; enabled when rd > 0
+    int32_t a4_kd_shift, a4_rd, a4_bi, b4_kd_shift, b4_rd, b4_bi;
     int32_t out_half;                // f16 storage and no split: the output tile is f16 (else f32: plain C or partial sums)
     uint32_t* status;
     volatile uint32_t* dbg;          // null, or 8 progress words in pinned host memory (KN_FLAG_TRACE_GEMM)
@@ -173,8 +175,24 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                         tma_load_4d(dst + kGpATileBytes, &map_b, bar, cb * 32, tx - p.conv_pad_x, row0 + ty - p.conv_pad_y, bt);
                     }
                 } else {
-                    tma_load_3d(dst, &map_a, bar, k * kBlockKElems, mt * kGpBlockM, bt * p.a_batch);
-                    tma_load_3d(dst + kGpATileBytes, &map_b, bar, k * kBlockKElems, nt * p.bn, bt * p.b_batch);
+                    // (a head split or merge read in place: the tile's coordinates in the 4-D source, see GemmOperand4D;
+                    // the row part does not change along K)
+                    const int k0 = k * kBlockKElems;
+                    if (p.a4_rd > 0) {
+                        const int r0 = mt * kGpBlockM;
+                        const int kh = p.a4_kd_shift ? (k0 >> p.a4_kd_shift) : 0;
+                        tma_load_4d(dst, &map_a, bar, k0 - (kh << p.a4_kd_shift), r0 % p.a4_rd, kh + bt % p.a4_bi, r0 / p.a4_rd + bt / p.a4_bi);
+                    } else {
+                        tma_load_3d(dst, &map_a, bar, k0, mt * kGpBlockM, bt * p.a_batch);
+                    }
+                    if (p.b4_rd > 0) {
+                        const int r0 = nt * p.bn;
+                        const int kh = p.b4_kd_shift ? (k0 >> p.b4_kd_shift) : 0;
+                        tma_load_4d(dst + kGpATileBytes, &map_b, bar, k0 - (kh << p.b4_kd_shift), r0 % p.b4_rd, kh + bt % p.b4_bi,
+                                    r0 / p.b4_rd + bt / p.b4_bi);
+                    } else {
+                        tma_load_3d(dst + kGpATileBytes, &map_b, bar, k0, nt * p.bn, bt * p.b_batch);
+                    }
                 }
                 dbg_mark(p, 1, (uint32_t)(k + 1));
                 if (++s == stages) { s = 0; round++; }
@@ -489,7 +507,34 @@ std::shared_ptr<void> gemm_persistent_prepare(const GemmParams& g, uint32_t* sta
         p.conv_pad_x = g.conv_pad_x;
         p.conv_ow = g.conv_ow;
     }
-    if (half) {
+    // 4-D operands: the box is one K block by the tile's rows inside one (x, y) entry
+    auto operand_4d = [&](const GemmOperand4D& o, const void* base, int rows, int64_t matrix_rows, int32_t* kd_shift, int32_t* rd, int32_t* bi,
+                          CUtensorMap* map) {
+        if (!o.enabled) return true;
+        if (o.kd < 1 || o.rd < 1 || o.bi < 1 || o.strides[0] != 1 || g.conv_operand != 0) return false;
+        int shift = 0;
+        if (o.kd != g.k) {   // the K offset is split: whole K blocks inside one entry, by a shift
+            if (o.kd % block_k != 0 || (o.kd & (o.kd - 1)) != 0) return false;
+            while ((1 << shift) < o.kd) shift++;
+        }
+        // a tile's rows lie inside one entry: an entry's rows are a multiple of the tile's, or the matrix is one entry
+        // tall (then rows past its end are past the tensor's extent: zero fill)
+        if (o.rd % rows != 0 && o.rd < matrix_rows) return false;
+        int box[4] = {block_k, rows, 1, 1};
+        *map = half ? tc_make_map_f16(base, 4, o.dims, o.strides, box, true) : tc_make_map(base, 4, o.dims, o.strides, box, true);
+        *kd_shift = shift;
+        *rd = o.rd;
+        *bi = o.bi;
+        return true;
+    };
+    if (!operand_4d(g.a4, g.a, kGpBlockM, g.m, &p.a4_kd_shift, &p.a4_rd, &p.a4_bi, &l->map_a)) return nullptr;
+    if (!operand_4d(g.b4, g.b, p.bn, g.n, &p.b4_kd_shift, &p.b4_rd, &p.b4_bi, &l->map_b)) return nullptr;
+    if (g.a4.enabled && g.b4.enabled) {
+    } else if (g.a4.enabled) {
+        l->map_b = half ? tc_make_map_f16(g.b, 3, bdims, bstr, bbox, true) : tc_make_map(g.b, 3, bdims, bstr, bbox, true);
+    } else if (g.b4.enabled) {
+        l->map_a = half ? tc_make_map_f16(g.a, 3, adims, astr, abox, true) : tc_make_map(g.a, 3, adims, astr, abox, true);
+    } else if (half) {
         l->map_a = tc_make_map_f16(g.a, 3, adims, astr, abox, true);
         l->map_b = tc_make_map_f16(g.b, 3, bdims, bstr, bbox, true);
     } else {

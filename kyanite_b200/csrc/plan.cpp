@@ -811,6 +811,92 @@ class Planner {
         return e;
     }
 
+    // ---------------------------------------------------------------- attention head split / merge read in place
+    // Attention graphs spell the head split as view [B*S, H*D] -> [B, S, H, D], permute [0, 2, 1, 3], view -> [B*H, S, D]
+    // and the merge as the same three nodes the other way round.  Neither result is expressible with strides (two
+    // batch-like axes of the source with unrelated strides would have to merge), so planned node by node each costs a
+    // copy of the activations.  A matmul operand of that form is instead read in place through a 4-D tensor map
+    // (GemmOperand4D): this finds the source and the four extents.
+    struct HeadChain {
+        int src = -1;
+        int64_t B = 0, S = 0, H = 0, D = 0;
+        bool merge = false;
+    };
+    std::optional<HeadChain> match_head_chain(int v) {
+        auto strip = [](std::vector<int64_t> s) {
+            while (s.size() > 2 && s.front() == 1) s.erase(s.begin());
+            return s;
+        };
+        if (map_[v]) return std::nullopt;                      // already materialised: use that
+        const std::vector<int64_t> target = strip(shape_of(v));
+        int cur = v;
+        while (g_.values[cur].op == OpKind::View && !map_[cur]) cur = g_.values[cur].inputs[0];
+        const ValueInfo& pi = g_.values[cur];
+        if (cur == v || pi.op != OpKind::Permute || map_[cur] || pi.permutation != std::vector<int>{0, 2, 1, 3}) return std::nullopt;
+        const int w = pi.inputs[0];
+        if (g_.values[w].op != OpKind::View) return std::nullopt;
+        const std::vector<int64_t> a = shape_of(w);            // [a0, a1, a2, a3] before the permute
+        if (a.size() != 4) return std::nullopt;
+        int src = w;
+        while (g_.values[src].op == OpKind::View && !map_[src]) src = g_.values[src].inputs[0];
+        const std::vector<int64_t> from = strip(shape_of(src));
+        for (int64_t d : a)
+            if (d < 1) return std::nullopt;
+        HeadChain c;
+        c.src = src;
+        if (from == std::vector<int64_t>{a[0] * a[1], a[2] * a[3]} && target == std::vector<int64_t>{a[0] * a[2], a[1], a[3]}) {
+            c.B = a[0]; c.S = a[1]; c.H = a[2]; c.D = a[3];
+            c.merge = false;
+            return c;
+        }
+        if (from == std::vector<int64_t>{a[0] * a[1], a[2], a[3]} && target == std::vector<int64_t>{a[0] * a[2], a[1] * a[3]}) {
+            c.B = a[0]; c.H = a[1]; c.S = a[2]; c.D = a[3];
+            c.merge = true;
+            return c;
+        }
+        return std::nullopt;
+    }
+    // The 4-D description of a matmul operand that is such a chain (rows x K, K contiguous), or nothing.  `as_b`: the
+    // operand is B, given in the graph as [batch, K, rows], so the chain sits under a permute [0, 2, 1].
+    // Sets `source` to the planned source tensor (visited here) on success.
+    bool head_chain_operand(int value, bool as_b, DType dtype, GemmOperand4D* out, PlanTensor* source, int64_t* batch, int64_t* rows,
+                            int64_t* k) {
+        if (opts_.flags & KN_FLAG_NO_PERSISTENT_GEMM) return false;
+        if (as_b) {
+            const ValueInfo& vi = g_.values[value];
+            if (map_[value] || vi.op != OpKind::Permute || vi.permutation != std::vector<int>{0, 2, 1}) return false;
+            value = vi.inputs[0];
+        }
+        if (shape_of(value).size() != 3) return false;
+        auto c = match_head_chain(value);
+        if (!c) return false;
+        const int64_t block_k = dtype == DType::F16 ? 64 : 32, align = dtype == DType::F16 ? 8 : 4;
+        if (g_.values[c->src].dtype != dtype || c->D % align != 0 || c->B > 65535 || c->H > 65535) return false;
+        GemmOperand4D o{};
+        o.enabled = 1;
+        o.dims[0] = c->D; o.dims[1] = c->S; o.dims[2] = c->H; o.dims[3] = c->B;
+        o.strides[0] = 1;
+        if (!c->merge) {
+            // [B*S, H*D] read as [B*H, S, D]
+            o.strides[1] = c->H * c->D; o.strides[2] = c->D; o.strides[3] = c->S * c->H * c->D;
+            o.kd = (int32_t)c->D; o.rd = (int32_t)c->S; o.bi = (int32_t)c->H;
+            *batch = c->B * c->H; *rows = c->S; *k = c->D;
+            if (c->S < 64) return false;
+        } else {
+            // [B*H, S, D] read as [B*S, H*D]: the K offset is split into (head, offset), whole K blocks per head, and a
+            // tile's rows must lie inside one batch entry
+            if (as_b || c->D % block_k != 0 || (c->D & (c->D - 1)) != 0 || c->S % 128 != 0) return false;
+            o.strides[1] = c->D; o.strides[2] = c->S * c->D; o.strides[3] = c->H * c->S * c->D;
+            o.kd = (int32_t)c->D; o.rd = (int32_t)c->S; o.bi = 1;
+            *batch = 1; *rows = c->B * c->S; *k = c->H * c->D;
+        }
+        PlanTensor t = visit(c->src);
+        if (!t.ss.has_simple_strides() || t.offset % align != 0) return false;   // (the source is planned either way)
+        *out = o;
+        *source = t;
+        return true;
+    }
+
     std::optional<PlanTensor> try_fused_contraction(int root) {
         auto m = match_epilogue(root);
         if (!m) return std::nullopt;
@@ -819,8 +905,20 @@ class Planner {
         std::vector<int64_t> root_shape = shape_of(root);
 
         // operands first (they may emit steps of their own), then this step
-        PlanTensor x = visit(ci.inputs[0]);
-        PlanTensor w = visit(ci.inputs[1]);
+        // (a matmul operand that is an attention head split or merge is read in place: tensor cores only)
+        GemmOperand4D a4{}, b4{};
+        int64_t a4_batch = 0, a4_rows = 0, a4_k = 0, b4_batch = 0, b4_rows = 0, b4_k = 0;
+        PlanTensor x, w;
+        const bool heads_ok = ci.op == OpKind::MatMul && native.size() == 3 && native[2] >= 16 && native[2] % 4 == 0 &&
+                              (ci.dtype == DType::F16 || (ci.dtype == DType::F32 && opts_.math_mode == KN_MATH_TF32));
+        if (!(heads_ok && head_chain_operand(ci.inputs[0], false, ci.dtype, &a4, &x, &a4_batch, &a4_rows, &a4_k) &&
+              a4_batch * 1 == native[0] * 1 && a4_rows == native[1]))
+            a4 = GemmOperand4D{};
+        if (!a4.enabled) x = visit(ci.inputs[0]);
+        if (!(heads_ok && head_chain_operand(ci.inputs[1], true, ci.dtype, &b4, &w, &b4_batch, &b4_rows, &b4_k) && b4_batch == native[0] &&
+              b4_rows == native[2]))
+            b4 = GemmOperand4D{};
+        if (!b4.enabled) w = visit(ci.inputs[1]);
         std::vector<PlanTensor> addends;
         for (int a : m->addends) {
             PlanTensor t = visit(a);
@@ -836,18 +934,41 @@ class Planner {
         PlanTensor conv_view;   // as_gemm: the matmul's output seen as [N, K, OH, OW]
         ConvGemm implicit;      // as_gemm with an implicit operand (implicit.implicit != 0)
         if (opts_.math_mode == KN_MATH_TF32) {
+            if (ci.op == OpKind::MatMul && (a4.enabled || b4.enabled)) {
+                // operands read in place: the other operand must be fine as it is, and the addends ones the persistent
+                // kernel's epilogue takes (per row, per column, or per element with contiguous rows); else back to
+                // materialised operands
+                PlanTensor xc = x, wc = w;   // what the shape checks see
+                if (a4.enabled) xc.ss = StridedShape({a4_batch, a4_rows, a4_k}, {a4_rows * a4_k, a4_k, 1}), xc.offset = 0;
+                if (b4.enabled) wc.ss = StridedShape({b4_batch, b4_k, b4_rows}, {b4_rows * b4_k, 1, b4_k}), wc.offset = 0;
+                bool ok = xc.ss.rank() == 3 && wc.ss.rank() == 3 && xc.ss.shape[2] == wc.ss.shape[1] && gemm_fits_tensor_core(xc, wc);
+                for (const PlanTensor& t : addends) {
+                    const auto& st = t.ss.strides;
+                    if (!(st[1] == 0 || st[2] == 1 || st[2] == 0)) ok = false;
+                }
+                if (ok) {
+                    tensor_core = true;
+                } else {
+                    a4 = GemmOperand4D{};
+                    b4 = GemmOperand4D{};
+                    x = visit(ci.inputs[0]);
+                    w = visit(ci.inputs[1]);
+                }
+            }
             if (ci.op == OpKind::MatMul) {
                 // An operand that is not contiguous along K (the value matrix of an attention head arrives as
                 // [batch, k, n] with n contiguous) gets a transposing copy: the exact-f32 kernel this would
                 // otherwise fall back to is some twenty times slower than copy + tensor cores.
-                if (!gemm_fits_tensor_core(x, w) && gemm_worth_a_copy(x, w)) {
-                    PlanTensor x2 = k_major_a(x, ci.inputs[0]), w2 = k_major_b(w, ci.inputs[1]);
-                    if (gemm_fits_tensor_core(x2, w2)) {
-                        x = x2;
-                        w = w2;
+                if (!a4.enabled && !b4.enabled) {
+                    if (!gemm_fits_tensor_core(x, w) && gemm_worth_a_copy(x, w)) {
+                        PlanTensor x2 = k_major_a(x, ci.inputs[0]), w2 = k_major_b(w, ci.inputs[1]);
+                        if (gemm_fits_tensor_core(x2, w2)) {
+                            x = x2;
+                            w = w2;
+                        }
                     }
+                    tensor_core = gemm_fits_tensor_core(x, w);
                 }
-                tensor_core = gemm_fits_tensor_core(x, w);
             }
             else if (auto g = conv_as_gemm(ci, x, w, native, addends, root)) {
                 // im2col + batched matmul (see conv_as_gemm); from here on this is a matmul step
@@ -905,6 +1026,14 @@ class Planner {
                 p.conv_strides[0] = img.ss.strides[0];
                 p.conv_strides[1] = img.ss.strides[2];
                 p.conv_strides[2] = img.ss.strides[3];
+            } else if (a4.enabled || b4.enabled) {
+                // attention head split / merge read in place: the source tensors stand for the operands
+                p.batch = native[0];
+                p.m = native[1];
+                p.n = native[2];
+                p.k = a4.enabled ? a4_k : x.ss.shape[2];
+                p.a4 = a4;
+                p.b4 = b4;
             } else {
                 KN_CHECK(x.ss.rank() == 3 && w.ss.rank() == 3, KN_ERR_SHAPE, "matmul operands must have rank 3");
                 p.batch = x.ss.shape[0];
@@ -914,8 +1043,8 @@ class Planner {
                 KN_CHECK(w.ss.shape[0] == p.batch && w.ss.shape[1] == p.k, KN_ERR_SHAPE, "matmul operand shapes differ");
             }
             for (int i = 0; i < 3; i++) {
-                if (implicit.implicit != 1) p.sa[i] = x.ss.strides[i];
-                if (implicit.implicit != 2) p.sb[i] = w.ss.strides[i];
+                if (implicit.implicit != 1 && !a4.enabled) p.sa[i] = x.ss.strides[i];
+                if (implicit.implicit != 2 && !b4.enabled) p.sb[i] = w.ss.strides[i];
                 p.sc[i] = out.ss.strides[i];
                 if (addends.size() > 0) p.s1[i] = addends[0].ss.strides[i];
                 if (addends.size() > 1) p.s2[i] = addends[1].ss.strides[i];
@@ -986,6 +1115,9 @@ class Planner {
         if (s.kind == StepKind::Gemm && s.gemm.splits > 1) s.desc += " splitk=" + std::to_string(s.gemm.splits);
         int64_t total = 1;
         for (int64_t d : native) total *= d;
+        if (a4.enabled || b4.enabled)
+            s.desc += std::string(" (head ") + ((a4.enabled && a4.bi == 1) ? "merge" : "split") + " read in place: operand" +
+                      (a4.enabled && b4.enabled ? "s a, b" : (a4.enabled ? " a" : " b")) + ")";
         if (as_gemm && implicit.implicit != 0)
             s.desc += std::string(" (conv, windows read from the image as operand ") + (implicit.implicit == 1 ? "a" : "b") + ")";
         else if (as_gemm) s.desc += " (conv via im2col, stride " + std::to_string(ci.stride_y) + "x" + std::to_string(ci.stride_x) + ")";
