@@ -16,6 +16,10 @@
 //                   waits for that accumulator to be drained, signals it full with tcgen05.commit
 //   warps 2..5      epilogue: thread <-> accumulator lane <-> output row; 32 columns at a time
 //
+// Large matmuls with a long reduction run on CTA PAIRS (template parameter PAIR, clusters of two): `cta_group::2`
+// instructions compute a 256 x BN tile on two SMs, each CTA loading its own 128 rows of A and half of B (see the
+// helpers in front of the kernel).  Same instructions in the same K order: results are bit-identical to one CTA per tile.
+//
 // Tiles are walked column-block-major (all row blocks of one column block before the next), so the CTAs
 // that run at the same time share a B tile in L2.  Row and column tails are the copy engine's zero fill
 // (loads) and clipping (stores).  Every mbarrier wait is bounded as in the other tensor-core kernels.
@@ -89,7 +93,61 @@ __device__ __forceinline__ void mbar_arrive_local(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-template <bool HALF>   // operand storage: f16 (kind::f16) or f32 (kind::tf32)
+// ---- CTA pairs (PAIR): two CTAs of a cluster compute one 256 x BN tile with `cta_group::2` instructions.  Each
+// CTA loads its own 128 rows of A and HALF of the B tile; the tensor cores of both SMs read both halves, so every SM's
+// shared-memory pipe carries a third fewer bytes per multiply-add than with one CTA per tile (that pipe, not the
+// tensor pipe, bounds the one-CTA kernel at about 0.83 of the tensor rate).  CTA 0 of the pair (the leader) issues the
+// MMAs; the loads of both CTAs complete on the leader's barriers; `tcgen05.commit` reaches the barriers of both.
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t cta) {   // shared::cta -> shared::cluster of `cta`
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(cta));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map, uint32_t cluster_bar, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(map), "r"(cluster_bar), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+template <bool HALF>
+__device__ __forceinline__ void mma_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    const uint32_t zero = 0;
+    if (HALF) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+            ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(zero)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+            ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(zero)
+            : "memory");
+    }
+}
+// arrives (once the MMAs issued so far have completed) on the barrier at this shared-memory offset in BOTH CTAs
+__device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((uint16_t)3)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+
+template <bool HALF, bool PAIR>   // operand storage: f16 (kind::f16) or f32 (kind::tf32); one CTA per tile or a CTA pair
 __global__ void __launch_bounds__(kGpThreads, 1)
 gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                        const __grid_constant__ CUtensorMap map_c, const __grid_constant__ GemmPersistentParams p) {
@@ -98,7 +156,10 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
     const int stages = p.stages;
-    const uint32_t b_tile_bytes = (uint32_t)p.bn * 128u;
+    const uint32_t rank = PAIR ? cluster_rank() : 0u;           // 0: the pair's leader
+    const int worker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x, n_workers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+    const int b_rows = PAIR ? p.bn / 2 : p.bn;                   // rows of the B tile this CTA loads
+    const uint32_t b_tile_bytes = (uint32_t)b_rows * 128u;
     const uint32_t stage_bytes = kGpATileBytes + b_tile_bytes;
     const uint32_t staging_base = base + (uint32_t)stages * stage_bytes;          // two staging tiles
     const uint32_t bar_base = staging_base + 2u * kGpStageTileBytes;
@@ -116,16 +177,22 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(acc_full + 8u * b, 1);
-            mbar_init(acc_empty + 8u * b, 128);
+            mbar_init(acc_empty + 8u * b, PAIR ? 256 : 128);   // (pair: the epilogue threads of both CTAs arrive on the leader's)
         }
         *abandon = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
+    if (PAIR) cluster_sync_all();   // the peer's barriers are initialised before anything is sent to them
     const uint32_t tmem_cols = 2u * (uint32_t)p.bn <= 32u ? 32u : (2u * (uint32_t)p.bn <= 64u ? 64u : (2u * (uint32_t)p.bn <= 128u ? 128u : (2u * (uint32_t)p.bn <= 256u ? 256u : 512u)));
     if (warp == 0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_addr), "r"(tmem_cols) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (PAIR) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_addr), "r"(tmem_cols) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_addr), "r"(tmem_cols) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tc_fence_before();
     __syncthreads();
@@ -151,15 +218,24 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
         int s = 0, round = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+        for (int t = worker; t < p.total_tiles && ok; t += n_workers) {
             int mt, nt, bt, sp;
             tile_coords(t, mt, nt, bt, sp);
             const int k_begin = sp * p.k_iters_slice, k_end = k_begin + slice_blocks(sp);
             for (int k = k_begin; k < k_end; k++) {
                 if (round > 0 && !mbar_wait(empty_bar + 8u * s, (uint32_t)((round & 1) ^ 1), abandon, p.status, 21)) { ok = false; break; }
                 const uint32_t bar = full_bar + 8u * s;
-                mbar_expect_tx(bar, stage_bytes);
                 const uint32_t dst = base + (uint32_t)s * stage_bytes;
+                if (PAIR) {
+                    // both CTAs' tiles complete on the LEADER's barrier, which expects the bytes of both
+                    if (rank == 0) mbar_expect_tx(bar, 2u * stage_bytes);
+                    const uint32_t leader_bar = map_to_cta(bar, 0);
+                    tma_load_3d_pair(dst, &map_a, leader_bar, k * kBlockKElems, (2 * mt + (int)rank) * kGpBlockM, bt * p.a_batch);
+                    tma_load_3d_pair(dst + kGpATileBytes, &map_b, leader_bar, k * kBlockKElems, nt * p.bn + (int)rank * b_rows, bt * p.b_batch);
+                    if (++s == stages) { s = 0; round++; }
+                    continue;
+                }
+                mbar_expect_tx(bar, stage_bytes);
                 if (p.conv_operand != 0) {
                     // K block k = (filter tap, 32-channel block); the tile's rows are whole output rows of image `bt`,
                     // so the operand tile is one box of the image tensor (channel, x, y, image) moved by the tap:
@@ -198,15 +274,19 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 if (++s == stages) { s = 0; round++; }
             }
         }
+    } else if (warp == 1 && lane == 0 && PAIR && rank != 0) {
+        // the peer issues no MMAs (the leader's instructions drive both tensor cores)
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     } else if (warp == 1 && lane == 0) {
         // ---------------- MMA issuer
         // instruction descriptor: f32 accumulate; A and B formats 2 = TF32 (kind::tf32) or 0 = F16 (kind::f16); both
         // K-major; N, M
         const uint32_t fmt = HALF ? 0u : 2u;
-        const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(p.bn >> 3) << 17) | ((uint32_t)(kGpBlockM >> 4) << 24);
+        const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(p.bn >> 3) << 17) |
+                               ((uint32_t)((PAIR ? 2 * kGpBlockM : kGpBlockM) >> 4) << 24);
         int s = 0, round = 0, local = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, local++) {
+        for (int t = worker; t < p.total_tiles && ok; t += n_workers, local++) {
             const int buf = local & 1;
             // the epilogue has drained this accumulator (its previous use was tile local - 2)
             if (local >= 2 && !mbar_wait(acc_empty + 8u * buf, (uint32_t)(((local >> 1) - 1) & 1), abandon, p.status, 22)) break;
@@ -216,7 +296,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             tile_coords(t, mt, nt, bt, sp);
             const int k_count = slice_blocks(sp);
             // last tile of this CTA: the next kernel of the stream may be scheduled (once every CTA says so)
-            if (t + (int)gridDim.x >= p.total_tiles) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+            if (t + n_workers >= p.total_tiles) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
             for (int k = 0; k < k_count; k++) {
                 if (!mbar_wait(full_bar + 8u * s, (uint32_t)(round & 1), abandon, p.status, 23)) { ok = false; break; }
                 dbg_mark(p, 2, (uint32_t)(k + 1));
@@ -227,14 +307,19 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 // four instructions of 32 bytes of K each: the start address advances by 2 (16-byte units)
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
-                    if (HALF) mma_f16(acc, da + 2u * j, db + 2u * j, idesc, (k | j) != 0 ? 1u : 0u);
+                    if (PAIR) mma_pair<HALF>(acc, da + 2u * j, db + 2u * j, idesc, (k | j) != 0 ? 1u : 0u);
+                    else if (HALF) mma_f16(acc, da + 2u * j, db + 2u * j, idesc, (k | j) != 0 ? 1u : 0u);
                     else mma_tf32(acc, da + 2u * j, db + 2u * j, idesc, (k | j) != 0 ? 1u : 0u);
                 }
-                mma_commit(empty_bar + 8u * s);
+                if (PAIR) mma_commit_pair(empty_bar + 8u * s);
+                else mma_commit(empty_bar + 8u * s);
                 dbg_mark(p, 3, (uint32_t)(k + 1));
                 if (++s == stages) { s = 0; round++; }
             }
-            if (ok) mma_commit(acc_full + 8u * buf);
+            if (ok) {
+                if (PAIR) mma_commit_pair(acc_full + 8u * buf);
+                else mma_commit(acc_full + 8u * buf);
+            }
         }
     } else if (warp >= 2) {
         // ---------------- epilogue
@@ -247,9 +332,10 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         const uint32_t row_phase = (uint32_t)row_in_tile & 7u;
         int local = 0, stage_buf = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, local++) {
+        for (int t = worker; t < p.total_tiles && ok; t += n_workers, local++) {
             int mt, nt, bt, sp;
             tile_coords(t, mt, nt, bt, sp);
+            if (PAIR) mt = 2 * mt + (int)rank;   // from here on: this CTA's 128-row block
             const int buf = local & 1;
             {
                 uint32_t good = 1;
@@ -392,7 +478,8 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             }
             // every tcgen05.ld of this accumulator has completed (tmem_load_32 waits): the MMA thread may reuse it
             tc_fence_before();
-            mbar_arrive_local(acc_empty + 8u * buf);
+            if (PAIR) mbar_arrive_cluster(map_to_cta(acc_empty + 8u * buf, 0));
+            else mbar_arrive_local(acc_empty + 8u * buf);
         }
         if (issuer) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // shared memory must outlive the stores
         if (issuer) dbg_mark(p, 6, 1);
@@ -400,8 +487,10 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 
     tc_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();   // neither CTA leaves (or frees tensor memory) while the other may still address it
     if (warp == 0) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+        if (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
     }
 }
 
@@ -411,6 +500,7 @@ struct GemmPersistentLaunch {
     dim3 grid;
     int smem_bytes;
     bool half;
+    bool pair;   // CTA pairs (clusters of two, cta_group::2)
 };
 
 // 0 absent, 1 one value per column (row stride 0), 2 a value per element with contiguous rows, 4 one value per
@@ -457,8 +547,18 @@ std::shared_ptr<void> gemm_persistent_prepare(const GemmParams& g, uint32_t* sta
     p.k_iters = (int)((g.k + block_k - 1) / block_k);
     p.out_half = half && !split ? 1 : 0;
     l->half = half;
-    p.m_tiles = (int)((g.m + kGpBlockM - 1) / kGpBlockM);
     p.n_tiles = (int)((g.n + p.bn - 1) / p.bn);
+    // CTA pairs: plain operands, no K slices, at least one 256-row tile per pair of SMs, and a reduction long enough
+    // for the mainloop to matter (measured, f32: 11 % faster at 24 K blocks and more, even at 16, 8 to 17 % slower at
+    // 2 to 10, where a tile is mostly epilogue and the pair's hand-offs cost more than the operand traffic they save).
+    // KN_GEMM_PAIR=0 in the environment switches pairs off, KN_GEMM_PAIR=1 drops the K condition (A/B measurements).
+    bool pair = !split && g.conv_operand == 0 && !g.a4.enabled && !g.b4.enabled && p.bn % 32 == 0 && p.bn >= 64 && g.m >= 256 &&
+                ((g.m + 255) / 256) * p.n_tiles * g.batch >= 74;
+    const char* pair_env = getenv("KN_GEMM_PAIR");
+    if (pair_env && atoi(pair_env) == 0) pair = false;
+    if (!pair_env && p.k_iters < 20) pair = false;
+    l->pair = pair;
+    p.m_tiles = (int)((g.m + (pair ? 2 : 1) * kGpBlockM - 1) / ((pair ? 2 : 1) * kGpBlockM));
     p.batch = (int)g.batch;
     p.splits = splits;
     p.k_iters_slice = split ? k_iters_slice : p.k_iters;
@@ -479,7 +579,7 @@ std::shared_ptr<void> gemm_persistent_prepare(const GemmParams& g, uint32_t* sta
     p.act = split ? 0 : g.act;
     p.status = status_word;
     p.dbg = (volatile uint32_t*)trace_words;
-    const int stage_bytes = kGpATileBytes + p.bn * 128;
+    const int stage_bytes = kGpATileBytes + (pair ? p.bn / 2 : p.bn) * 128;
     const int fixed = 1024 + 2 * kGpStageTileBytes + 16 * 8 + 64 + 64;
     p.stages = std::max(2, std::min(6, (227 * 1024 - fixed) / stage_bytes));
     l->smem_bytes = fixed + p.stages * stage_bytes;
@@ -488,7 +588,7 @@ std::shared_ptr<void> gemm_persistent_prepare(const GemmParams& g, uint32_t* sta
     int abox[3] = {block_k, kGpBlockM, 1};
     p.b_batch = (g.batch > 1 && g.sb[0] == 0) ? 0 : 1;
     int64_t bdims[3] = {g.k, g.n, p.b_batch ? g.batch : 1}, bstr[3] = {1, g.sb[2], p.b_batch ? g.sb[0] : align};
-    int bbox[3] = {block_k, p.bn, 1};
+    int bbox[3] = {block_k, pair ? p.bn / 2 : p.bn, 1};
     // the implicit convolution operand: a 4-D map of the image tensor (channel, x, y, image) whose box is one K
     // block of channels by whole output rows
     int64_t idims[4] = {g.conv_c, g.conv_w, g.conv_h, g.batch}, istr[4] = {1, g.conv_strides[2], g.conv_strides[1], g.conv_strides[0]};
@@ -545,7 +645,7 @@ std::shared_ptr<void> gemm_persistent_prepare(const GemmParams& g, uint32_t* sta
     int cbox[3] = {32, kGpBlockM, 1};
     if (p.out_half) l->map_c = tc_make_map_f16(g.c, 3, cdims, cstr, cbox, false);
     else l->map_c = tc_make_store_map(split ? g.scratch : g.c, 3, cdims, cstr, cbox);
-    l->grid = dim3((unsigned)std::min<int64_t>(total, 148), 1, 1);
+    l->grid = pair ? dim3(2u * (unsigned)std::min<int64_t>(total, 74), 1, 1) : dim3((unsigned)std::min<int64_t>(total, 148), 1, 1);
     return l;
 }
 
@@ -558,15 +658,36 @@ int gemm_persistent_launch(const void* launch, cudaStream_t stream) {
     {
         std::lock_guard<std::mutex> lock(mu);
         if (device >= 0 && device < 64 && !done[device]) {
-            cudaError_t e = cudaFuncSetAttribute(gemm_persistent_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-            if (e != cudaSuccess) return (int)e;
-            e = cudaFuncSetAttribute(gemm_persistent_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-            if (e != cudaSuccess) return (int)e;
+            const void* variants[] = {(const void*)gemm_persistent_kernel<false, false>, (const void*)gemm_persistent_kernel<true, false>,
+                                      (const void*)gemm_persistent_kernel<false, true>, (const void*)gemm_persistent_kernel<true, true>};
+            for (const void* v : variants) {
+                cudaError_t e = cudaFuncSetAttribute(v, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+                if (e != cudaSuccess) return (int)e;
+            }
             done[device] = true;
         }
     }
-    if (l.half) launch_pdl(gemm_persistent_kernel<true>, dim3(l.grid), dim3(kGpThreads), (size_t)(l.smem_bytes), stream, l.map_a, l.map_b, l.map_c, l.p);
-    else launch_pdl(gemm_persistent_kernel<false>, dim3(l.grid), dim3(kGpThreads), (size_t)(l.smem_bytes), stream, l.map_a, l.map_b, l.map_c, l.p);
+    if (l.pair) {
+        // clusters of two CTAs, still with the programmatic edge to the previous kernel
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = l.grid;
+        cfg.blockDim = dim3(kGpThreads);
+        cfg.dynamicSmemBytes = (size_t)l.smem_bytes;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        attr[1].id = cudaLaunchAttributeClusterDimension;
+        attr[1].val.clusterDim.x = 2;
+        attr[1].val.clusterDim.y = 1;
+        attr[1].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 2;
+        if (l.half) return (int)cudaLaunchKernelEx(&cfg, gemm_persistent_kernel<true, true>, l.map_a, l.map_b, l.map_c, l.p);
+        return (int)cudaLaunchKernelEx(&cfg, gemm_persistent_kernel<false, true>, l.map_a, l.map_b, l.map_c, l.p);
+    }
+    if (l.half) launch_pdl(gemm_persistent_kernel<true, false>, dim3(l.grid), dim3(kGpThreads), (size_t)(l.smem_bytes), stream, l.map_a, l.map_b, l.map_c, l.p);
+    else launch_pdl(gemm_persistent_kernel<false, false>, dim3(l.grid), dim3(kGpThreads), (size_t)(l.smem_bytes), stream, l.map_a, l.map_b, l.map_c, l.p);
     return (int)cudaGetLastError();
 }
 

@@ -7,7 +7,7 @@ import pytest
 
 from kyanite_b200.configs import resnet_tower
 from kyanite_b200.executor import MATH_F32, MATH_TF32, CudaExecutor, plan_describe
-from kyanite_b200.graph import BATCH, Graph, shape
+from kyanite_b200.graph import BATCH, Graph, UnaryOp, shape
 from oracle.cpu_eval import assert_tensors_match, cpu_eval_graph
 
 pytestmark = pytest.mark.gpu
@@ -269,3 +269,52 @@ def test_head_split_and_k_major_copy_are_one_step():
     kinds = [l.split()[2] for l in text.splitlines() if l.startswith("step")]
     assert kinds == ["Scalar", "Gemm/tc"], text
     check(g, 0, [rng(1, B * h, s, s) * 0.1, rng(2, B, s, h * d)])
+
+
+PAIR_CASES = {
+    # name: (batch, m, n, k, kwargs): at least 74 tiles of 256 rows, so the planner's matmul runs on CTA pairs
+    "projection": (1, 8192, 1024, 512, {}),
+    "row_tail": (1, 9000, 1024, 264, {"relu": True}),                 # 9000 = 35 x 256 + 40: the last pair's second CTA is past the end
+    "column_tail": (1, 8192, 800, 256, {}),                           # 800 = 4 blocks of 224 > 800 - 3 x 224: clipped stores
+    "batched": (3, 4000, 1000, 264, {"residual": True}),
+    "gelu": (1, 16384, 768, 768, {"gelu": True}),
+    "narrow": (1, 20000, 64, 128, {}),                                # one 64-column block: 32 B rows per CTA
+}
+
+
+def pair_graph(batch, m, n, k, relu=False, gelu=False, residual=False, seed=0):
+    r = np.random.Generator(np.random.PCG64(seed))
+    g = Graph()
+    a = g.input(shape(batch, m, k))
+    w = g.constant_tensor((r.standard_normal((1, n, k)) / np.sqrt(k)).astype(np.float32))
+    y = g.batched_mat_mul(a, g.permute(g.broadcast(w, shape(batch, n, k)), [0, 2, 1]))
+    y = g.add(y, g.constant_tensor(r.standard_normal((1, 1, n)).astype(np.float32)))
+    inputs = [r.standard_normal((batch, m, k)).astype(np.float32)]
+    if residual:
+        y = g.add(y, g.input(shape(batch, m, n)))
+        inputs.append(r.standard_normal((batch, m, n)).astype(np.float32))
+    if relu:
+        y = g.relu(y)
+    if gelu:
+        half = g.scalar(0.5)
+        y = g.mul(g.mul(y, half), g.add(g.scalar(1.0), g.unary(UnaryOp.ERF, g.mul(y, g.scalar(float(np.sqrt(0.5)))))))
+    g.output(y)
+    return g, inputs
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", sorted(PAIR_CASES))
+def test_matmul_on_cta_pairs(name, monkeypatch):
+    """Large matmuls run on CTA pairs (`cta_group::2`: two SMs on one 256-row tile, each loading half of B).  The same
+    instructions in the same K order as the one-CTA kernel: the results are bit-identical to it, and within the TF32
+    tolerance of the oracle."""
+    batch, m, n, k, kw = PAIR_CASES[name]
+    g, inputs = pair_graph(batch, m, n, k, **kw)
+    results = {}
+    for pair in ("1", "0"):
+        monkeypatch.setenv("KN_GEMM_PAIR", pair)
+        with CudaExecutor(0, g, 0, math_mode=MATH_TF32) as ex:
+            results[pair] = ex.evaluate(inputs)[0].copy()
+    np.testing.assert_array_equal(results["1"], results["0"])
+    expected = cpu_eval_graph(g.to_bytes(), 0, inputs)
+    assert_tensors_match(expected, [results["1"]], 4e-3, 4e-3, abs_scaled=True)
