@@ -118,6 +118,12 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap
         ::"r"(dst), "l"(map), "r"(cluster_bar), "r"(c0), "r"(c1), "r"(c2)
         : "memory");
 }
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap* map, uint32_t cluster_bar, int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(cluster_bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
 template <bool HALF>
 __device__ __forceinline__ void mma_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
     const uint32_t zero = 0;
@@ -226,48 +232,49 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 if (round > 0 && !mbar_wait(empty_bar + 8u * s, (uint32_t)((round & 1) ^ 1), abandon, p.status, 21)) { ok = false; break; }
                 const uint32_t bar = full_bar + 8u * s;
                 const uint32_t dst = base + (uint32_t)s * stage_bytes;
-                if (PAIR) {
-                    // both CTAs' tiles complete on the LEADER's barrier, which expects the bytes of both
-                    if (rank == 0) mbar_expect_tx(bar, 2u * stage_bytes);
-                    const uint32_t leader_bar = map_to_cta(bar, 0);
-                    tma_load_3d_pair(dst, &map_a, leader_bar, k * kBlockKElems, (2 * mt + (int)rank) * kGpBlockM, bt * p.a_batch);
-                    tma_load_3d_pair(dst + kGpATileBytes, &map_b, leader_bar, k * kBlockKElems, nt * p.bn + (int)rank * b_rows, bt * p.b_batch);
-                    if (++s == stages) { s = 0; round++; }
-                    continue;
-                }
-                mbar_expect_tx(bar, stage_bytes);
+                // pair: both CTAs' tiles complete on the LEADER's barrier, which expects the bytes of both
+                if (!PAIR || rank == 0) mbar_expect_tx(bar, PAIR ? 2u * stage_bytes : stage_bytes);
+                const uint32_t to_bar = PAIR ? map_to_cta(bar, 0) : bar;
+                auto load3 = [&](uint32_t d, const CUtensorMap* map, int c0, int c1, int c2) {
+                    if (PAIR) tma_load_3d_pair(d, map, to_bar, c0, c1, c2);
+                    else tma_load_3d(d, map, to_bar, c0, c1, c2);
+                };
+                auto load4 = [&](uint32_t d, const CUtensorMap* map, int c0, int c1, int c2, int c3) {
+                    if (PAIR) tma_load_4d_pair(d, map, to_bar, c0, c1, c2, c3);
+                    else tma_load_4d(d, map, to_bar, c0, c1, c2, c3);
+                };
+                const int a_row0 = (PAIR ? 2 * mt + (int)rank : mt) * kGpBlockM;   // this CTA's rows of A
+                const int b_row0 = nt * p.bn + (PAIR ? (int)rank * b_rows : 0);      // and of B (a pair: its half)
                 if (p.conv_operand != 0) {
                     // K block k = (filter tap, 32-channel block); the tile's rows are whole output rows of image `bt`,
                     // so the operand tile is one box of the image tensor (channel, x, y, image) moved by the tap:
                     // positions outside the image are the copy engine's zero fill
                     const int tap = k / p.conv_cblocks, cb = k - tap * p.conv_cblocks;
                     const int ty = tap / p.conv_s, tx = tap - ty * p.conv_s;
-                    const int row0 = (p.conv_operand == 1 ? mt * kGpBlockM : nt * p.bn) / p.conv_ow;
+                    const int row0 = (p.conv_operand == 1 ? a_row0 : b_row0) / p.conv_ow;
                     if (p.conv_operand == 1) {
-                        tma_load_4d(dst, &map_a, bar, cb * 32, tx - p.conv_pad_x, row0 + ty - p.conv_pad_y, bt);
-                        tma_load_3d(dst + kGpATileBytes, &map_b, bar, k * kBlockKElems, nt * p.bn, bt * p.b_batch);
+                        load4(dst, &map_a, cb * 32, tx - p.conv_pad_x, row0 + ty - p.conv_pad_y, bt);
+                        load3(dst + kGpATileBytes, &map_b, k * kBlockKElems, b_row0, bt * p.b_batch);
                     } else {
-                        tma_load_3d(dst, &map_a, bar, k * kBlockKElems, mt * kGpBlockM, bt * p.a_batch);
-                        tma_load_4d(dst + kGpATileBytes, &map_b, bar, cb * 32, tx - p.conv_pad_x, row0 + ty - p.conv_pad_y, bt);
+                        load3(dst, &map_a, k * kBlockKElems, a_row0, bt * p.a_batch);
+                        load4(dst + kGpATileBytes, &map_b, cb * 32, tx - p.conv_pad_x, row0 + ty - p.conv_pad_y, bt);
                     }
                 } else {
                     // (a head split or merge read in place: the tile's coordinates in the 4-D source, see GemmOperand4D;
                     // the row part does not change along K)
                     const int k0 = k * kBlockKElems;
                     if (p.a4_rd > 0) {
-                        const int r0 = mt * kGpBlockM;
                         const int kh = p.a4_kd_shift ? (k0 >> p.a4_kd_shift) : 0;
-                        tma_load_4d(dst, &map_a, bar, k0 - (kh << p.a4_kd_shift), r0 % p.a4_rd, kh + bt % p.a4_bi, r0 / p.a4_rd + bt / p.a4_bi);
+                        load4(dst, &map_a, k0 - (kh << p.a4_kd_shift), a_row0 % p.a4_rd, kh + bt % p.a4_bi, a_row0 / p.a4_rd + bt / p.a4_bi);
                     } else {
-                        tma_load_3d(dst, &map_a, bar, k0, mt * kGpBlockM, bt * p.a_batch);
+                        load3(dst, &map_a, k0, a_row0, bt * p.a_batch);
                     }
                     if (p.b4_rd > 0) {
-                        const int r0 = nt * p.bn;
                         const int kh = p.b4_kd_shift ? (k0 >> p.b4_kd_shift) : 0;
-                        tma_load_4d(dst + kGpATileBytes, &map_b, bar, k0 - (kh << p.b4_kd_shift), r0 % p.b4_rd, kh + bt % p.b4_bi,
-                                    r0 / p.b4_rd + bt / p.b4_bi);
+                        load4(dst + kGpATileBytes, &map_b, k0 - (kh << p.b4_kd_shift), b_row0 % p.b4_rd, kh + bt % p.b4_bi,
+                              b_row0 / p.b4_rd + bt / p.b4_bi);
                     } else {
-                        tma_load_3d(dst + kGpATileBytes, &map_b, bar, k0, nt * p.bn, bt * p.b_batch);
+                        load3(dst + kGpATileBytes, &map_b, k0, b_row0, bt * p.b_batch);
                     }
                 }
                 dbg_mark(p, 1, (uint32_t)(k + 1));
@@ -548,10 +555,13 @@ std::shared_ptr<void> gemm_persistent_prepare(const GemmParams& g, uint32_t* sta
     p.out_half = half && !split ? 1 : 0;
     l->half = half;
     p.n_tiles = (int)((g.n + p.bn - 1) / p.bn);
-    // CTA pairs: plain operands, no K slices, at least one 256-row tile per pair of SMs, and a reduction long enough
+    // CTA pairs: at least one 256-row tile per pair of SMs, and a reduction long enough
     // for the mainloop to matter (measured, f32: 11 % faster at 24 K blocks and more, even at 16, 8 to 17 % slower at
     // 2 to 10, where a tile is mostly epilogue and the pair's hand-offs cost more than the operand traffic they save).
     // KN_GEMM_PAIR=0 in the environment switches pairs off, KN_GEMM_PAIR=1 drops the K condition (A/B measurements).
+    // (plain operands and no K slices: with an A operand read in place, convolution windows or a head merge, pairs
+    // measured no faster than one CTA per tile, 161.5 against 160.5 us and 43.4 against 44.1 us, so those and the
+    // split-K partial tiles stay on the kernel variant that has run them all along)
     bool pair = !split && g.conv_operand == 0 && !g.a4.enabled && !g.b4.enabled && p.bn % 32 == 0 && p.bn >= 64 && g.m >= 256 &&
                 ((g.m + 255) / 256) * p.n_tiles * g.batch >= 74;
     const char* pair_env = getenv("KN_GEMM_PAIR");
