@@ -228,6 +228,23 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             int mt, nt, bt, sp;
             tile_coords(t, mt, nt, bt, sp);
             const int k_begin = sp * p.k_iters_slice, k_end = k_begin + slice_blocks(sp);
+            const int a_row0 = (PAIR ? 2 * mt + (int)rank : mt) * kGpBlockM;   // this CTA's rows of A
+            const int b_row0 = nt * p.bn + (PAIR ? (int)rank * b_rows : 0);      // and of B (a pair: its half)
+            // Everything about an operand read in place that does not change along K is worked out here, and what does
+            // (the filter tap of a K block) is stepped, not divided: this loop runs once per K block in ONE thread,
+            // and three integer divisions by run-time values in it cost more than the four MMAs of the block
+            // (measured: a 3x3 convolution over 320 channels ran at 800 cycles per K block instead of 320).
+            int conv_cb = 0, conv_tx = 0, conv_ty = 0, conv_row0 = 0;
+            if (p.conv_operand != 0) {
+                const int tap = k_begin / p.conv_cblocks;
+                conv_cb = k_begin - tap * p.conv_cblocks;
+                conv_ty = tap / p.conv_s;
+                conv_tx = tap - conv_ty * p.conv_s;
+                conv_row0 = (p.conv_operand == 1 ? a_row0 : b_row0) / p.conv_ow;
+            }
+            int a4_c1 = 0, a4_c2 = 0, a4_c3 = 0, b4_c1 = 0, b4_c2 = 0, b4_c3 = 0;
+            if (p.a4_rd > 0) a4_c1 = a_row0 % p.a4_rd, a4_c2 = bt % p.a4_bi, a4_c3 = a_row0 / p.a4_rd + bt / p.a4_bi;
+            if (p.b4_rd > 0) b4_c1 = b_row0 % p.b4_rd, b4_c2 = bt % p.b4_bi, b4_c3 = b_row0 / p.b4_rd + bt / p.b4_bi;
             for (int k = k_begin; k < k_end; k++) {
                 if (round > 0 && !mbar_wait(empty_bar + 8u * s, (uint32_t)((round & 1) ^ 1), abandon, p.status, 21)) { ok = false; break; }
                 const uint32_t bar = full_bar + 8u * s;
@@ -243,21 +260,20 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                     if (PAIR) tma_load_4d_pair(d, map, to_bar, c0, c1, c2, c3);
                     else tma_load_4d(d, map, to_bar, c0, c1, c2, c3);
                 };
-                const int a_row0 = (PAIR ? 2 * mt + (int)rank : mt) * kGpBlockM;   // this CTA's rows of A
-                const int b_row0 = nt * p.bn + (PAIR ? (int)rank * b_rows : 0);      // and of B (a pair: its half)
                 if (p.conv_operand != 0) {
                     // K block k = (filter tap, 32-channel block); the tile's rows are whole output rows of image `bt`,
                     // so the operand tile is one box of the image tensor (channel, x, y, image) moved by the tap:
                     // positions outside the image are the copy engine's zero fill
-                    const int tap = k / p.conv_cblocks, cb = k - tap * p.conv_cblocks;
-                    const int ty = tap / p.conv_s, tx = tap - ty * p.conv_s;
-                    const int row0 = (p.conv_operand == 1 ? a_row0 : b_row0) / p.conv_ow;
                     if (p.conv_operand == 1) {
-                        load4(dst, &map_a, cb * 32, tx - p.conv_pad_x, row0 + ty - p.conv_pad_y, bt);
+                        load4(dst, &map_a, conv_cb * 32, conv_tx - p.conv_pad_x, conv_row0 + conv_ty - p.conv_pad_y, bt);
                         load3(dst + kGpATileBytes, &map_b, k * kBlockKElems, b_row0, bt * p.b_batch);
                     } else {
                         load3(dst, &map_a, k * kBlockKElems, a_row0, bt * p.a_batch);
-                        load4(dst + kGpATileBytes, &map_b, cb * 32, tx - p.conv_pad_x, row0 + ty - p.conv_pad_y, bt);
+                        load4(dst + kGpATileBytes, &map_b, conv_cb * 32, conv_tx - p.conv_pad_x, conv_row0 + conv_ty - p.conv_pad_y, bt);
+                    }
+                    if (++conv_cb == p.conv_cblocks) {
+                        conv_cb = 0;
+                        if (++conv_tx == p.conv_s) { conv_tx = 0; conv_ty++; }
                     }
                 } else {
                     // (a head split or merge read in place: the tile's coordinates in the 4-D source, see GemmOperand4D;
@@ -265,14 +281,13 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                     const int k0 = k * kBlockKElems;
                     if (p.a4_rd > 0) {
                         const int kh = p.a4_kd_shift ? (k0 >> p.a4_kd_shift) : 0;
-                        load4(dst, &map_a, k0 - (kh << p.a4_kd_shift), a_row0 % p.a4_rd, kh + bt % p.a4_bi, a_row0 / p.a4_rd + bt / p.a4_bi);
+                        load4(dst, &map_a, k0 - (kh << p.a4_kd_shift), a4_c1, kh + a4_c2, a4_c3);
                     } else {
                         load3(dst, &map_a, k0, a_row0, bt * p.a_batch);
                     }
                     if (p.b4_rd > 0) {
                         const int kh = p.b4_kd_shift ? (k0 >> p.b4_kd_shift) : 0;
-                        load4(dst + kGpATileBytes, &map_b, k0 - (kh << p.b4_kd_shift), b_row0 % p.b4_rd, kh + bt % p.b4_bi,
-                              b_row0 / p.b4_rd + bt / p.b4_bi);
+                        load4(dst + kGpATileBytes, &map_b, k0 - (kh << p.b4_kd_shift), b4_c1, kh + b4_c2, b4_c3);
                     } else {
                         load3(dst + kGpATileBytes, &map_b, k0, b_row0, bt * p.b_batch);
                     }
@@ -559,10 +574,10 @@ std::shared_ptr<void> gemm_persistent_prepare(const GemmParams& g, uint32_t* sta
     // for the mainloop to matter (measured, f32: 11 % faster at 24 K blocks and more, even at 16, 8 to 17 % slower at
     // 2 to 10, where a tile is mostly epilogue and the pair's hand-offs cost more than the operand traffic they save).
     // KN_GEMM_PAIR=0 in the environment switches pairs off, KN_GEMM_PAIR=1 drops the K condition (A/B measurements).
-    // (plain operands and no K slices: with an A operand read in place, convolution windows or a head merge, pairs
-    // measured no faster than one CTA per tile, 161.5 against 160.5 us and 43.4 against 44.1 us, so those and the
-    // split-K partial tiles stay on the kernel variant that has run them all along)
-    bool pair = !split && g.conv_operand == 0 && !g.a4.enabled && !g.b4.enabled && p.bn % 32 == 0 && p.bn >= 64 && g.m >= 256 &&
+    // (no K slices; the A operand may be a head split or merge read in place, 42.3 -> 38.5 us on the BERT output
+    // projection; with convolution windows as the A operand pairs measured no faster, 127.4 against 126.3 us, and a B
+    // operand read in place would need its box halved: those stay on one CTA per tile)
+    bool pair = !split && g.conv_operand == 0 && !g.b4.enabled && p.bn % 32 == 0 && p.bn >= 64 && g.m >= 256 &&
                 ((g.m + 255) / 256) * p.n_tiles * g.batch >= 74;
     const char* pair_env = getenv("KN_GEMM_PAIR");
     if (pair_env && atoi(pair_env) == 0) pair = false;
