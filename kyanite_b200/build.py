@@ -33,6 +33,7 @@ SOURCES = [
     "kernels/contract_tc.cu",
     "kernels/conv_chain.cu",
     "kernels/gemm_persistent.cu",
+    "kernels/attn_softmax.cu",
 ]
 
 NVCC_FLAGS = [

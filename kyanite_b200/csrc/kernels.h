@@ -149,6 +149,10 @@ struct GemmParams {
     // (tap_y * conv_s + tap_x) * conv_c + channel, zeros outside the image (stride-1 convolution as a matmul
     // without materialising the windows).  `sa` / `sb` are not used for that operand.
     GemmOperand4D a4, b4;    // head split / merge read in place (above)
+    // Row softmax fused into the matmul (attention scores): C = softmax over each row of (softmax_scale * A.B), rows of
+    // at most 512 columns, no addends, no activation (kernels/attn_softmax.cu; tensor cores only).
+    int32_t row_softmax;
+    float softmax_scale;
     int32_t conv_operand;
     int32_t conv_c, conv_h, conv_w, conv_ow, conv_r, conv_s, conv_pad_y, conv_pad_x;
     int64_t conv_strides[3];   // element strides of the image tensor: image, row, pixel (channels are contiguous)

@@ -700,6 +700,7 @@ struct TcLaunch {
     int smem_bytes;
     std::shared_ptr<void> chain;  // ConvChain step: launch data of kernels/conv_chain.cu
     std::shared_ptr<void> gemm_p; // matmul taken by the persistent kernel (kernels/gemm_persistent.cu)
+    std::shared_ptr<void> attn;   // matmul with a row softmax (kernels/attn_softmax.cu)
 };
 
 CUtensorMap tc_make_store_map(const void* base, int rank, const int64_t* dims, const int64_t* strides, const int* box) {
@@ -898,6 +899,12 @@ void tc_prepare_step(Step& step, uint32_t* status_word, int flags, uint32_t* tra
     int64_t n_cols;
     if (step.kind == StepKind::Gemm) {
         const GemmParams& g = step.gemm;
+        if (g.row_softmax) {
+            launch->attn = attn_softmax_prepare(g, status_word);
+            KN_CHECK(launch->attn != nullptr, KN_ERR_INTERNAL, "matmul with a row softmax does not qualify");
+            step.tc = launch;
+            return;
+        }
         if (g.half || g.conv_operand != 0 || g.a4.enabled || g.b4.enabled) {
             // f16 storage, or an implicit convolution operand: the persistent kernel is the only tensor-core kernel
             // that takes these; the planner marks such a step tensor-core only when that kernel takes it
@@ -1092,6 +1099,7 @@ static int launch_splitk_reduce(const SplitKReduceParams& r, cudaStream_t stream
 int tc_launch_step(const Step& step, cudaStream_t stream) {
     const TcLaunch& l = *step.tc;
     if (l.chain) return chain_launch(l.chain.get(), stream);
+    if (l.attn) return attn_softmax_launch(l.attn.get(), stream);
     if (l.gemm_p) {
         const int err = gemm_persistent_launch(l.gemm_p.get(), stream);
         if (err != 0 || !l.split_k) return err;

@@ -30,6 +30,11 @@ std::shared_ptr<void> gemm_persistent_prepare(const GemmParams& g, uint32_t* sta
                                               uint32_t* trace_words = nullptr);
 int gemm_persistent_launch(const void* launch, cudaStream_t stream);
 
+// Matmul with a row softmax (attention scores, kernels/attn_softmax.cu): null if the step does not qualify.
+bool attn_softmax_fits(int64_t batch, int64_t m, int64_t n, int64_t k);
+std::shared_ptr<void> attn_softmax_prepare(const GemmParams& g, uint32_t* status_word);
+int attn_softmax_launch(const void* launch, cudaStream_t stream);
+
 // Convolution chain (kernels/conv_chain.cu): launch data built once the device pointers are known.
 std::shared_ptr<void> chain_prepare(const ConvChainParams& c, uint32_t* status_word);
 int chain_launch(const void* launch, cudaStream_t stream);

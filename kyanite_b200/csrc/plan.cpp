@@ -3,6 +3,7 @@
 #include <pthread.h>
 
 #include <algorithm>
+#include <cmath>
 #include <cstdio>
 #include <map>
 #include <optional>
@@ -580,7 +581,9 @@ class Planner {
             case OpKind::Conv:
                 fail(KN_ERR_UNSUPPORTED, "Conv is only supported for f32 operands");
             case OpKind::Unary: case OpKind::Binary: return visit_scalar(v);
-            case OpKind::Softmax: return visit_softmax(v);
+            case OpKind::Softmax:
+                if (auto fused = try_fused_attention_scores(v)) return *fused;
+                return visit_softmax(v);
             case OpKind::Layernorm: return visit_layernorm(v);
             case OpKind::Reduce: return visit_reduce(v);
             case OpKind::AllReduce: {
@@ -895,6 +898,82 @@ class Planner {
         *out = o;
         *source = t;
         return true;
+    }
+
+    // ---------------------------------------------------------------- attention scores + softmax as one step
+    // softmax over the last axis of (scale *) a batched matmul whose rows are at most 512 long (the scores of an
+    // attention head over up to 512 keys), every node in between used by this expression only: ONE tensor-core step
+    // that keeps the scores in tensor memory and writes the probabilities (kernels/attn_softmax.cu), instead of a
+    // matmul that writes the scores and a softmax that reads and writes them again.
+    std::optional<PlanTensor> try_fused_attention_scores(int v) {
+        const ValueInfo& si = g_.values[v];
+        if (si.dtype != DType::F32 || opts_.math_mode != KN_MATH_TF32 || (opts_.flags & KN_FLAG_NO_PERSISTENT_GEMM)) return std::nullopt;
+        const std::vector<int64_t> shape = shape_of(v);
+        if (shape.size() != 3 || si.axis != 2) return std::nullopt;
+        int y = si.inputs[0];
+        float scale = 1.0f;
+        if (g_.values[y].op == OpKind::Binary && g_.values[y].binary_op == BinaryOp::Mul && fusable(y) && !map_[y]) {
+            const ValueInfo& mi = g_.values[y];
+            int other = -1;
+            for (int side = 0; side < 2; side++) {
+                auto c = g_.as_single_const(mi.inputs[side]);
+                if (c && other < 0) {
+                    scale = c->as_f32();
+                    other = mi.inputs[1 - side];
+                }
+            }
+            if (other < 0 || !(scale > 0.0f) || !std::isfinite(scale)) return std::nullopt;   // (the kernel takes the maximum before scaling)
+            y = other;
+        }
+        const ValueInfo& ci = g_.values[y];
+        if (ci.op != OpKind::MatMul || ci.dtype != DType::F32 || !fusable(y) || map_[y] || shape_of(y) != shape) return std::nullopt;
+        const int64_t batch = shape[0], m = shape[1], n = shape[2];
+        const int64_t k = shape_of(ci.inputs[0])[2];
+        if (!attn_softmax_fits(batch, m, n, k)) return std::nullopt;
+        // operands: head splits read in place, or K-contiguous matrices as they are
+        GemmOperand4D a4{}, b4{};
+        int64_t ob = 0, orows = 0, ok_ = 0;
+        PlanTensor x, w;
+        if (!(head_chain_operand(ci.inputs[0], false, DType::F32, &a4, &x, &ob, &orows, &ok_) && a4.kd == k && ob == batch && orows == m))
+            a4 = GemmOperand4D{};
+        if (!a4.enabled) x = visit(ci.inputs[0]);
+        if (!(head_chain_operand(ci.inputs[1], true, DType::F32, &b4, &w, &ob, &orows, &ok_) && b4.kd == k && ob == batch && orows == n))
+            b4 = GemmOperand4D{};
+        if (!b4.enabled) w = visit(ci.inputs[1]);
+        PlanTensor xc = x, wc = w;   // what the shape checks see
+        if (a4.enabled) xc.ss = StridedShape({batch, m, k}, {m * k, k, 1}), xc.offset = 0;
+        if (b4.enabled) wc.ss = StridedShape({batch, k, n}, {n * k, 1, k}), wc.offset = 0;
+        if (xc.ss.rank() != 3 || wc.ss.rank() != 3 || !gemm_fits_tensor_core(xc, wc) || xc.ss.strides[0] == 0 || wc.ss.strides[0] == 0)
+            return std::nullopt;   // (the operands are planned either way; the matmul and the softmax stay two steps)
+        PlanTensor out = alloc_shared(shape, DType::F32, v);
+        Step s;
+        s.kind = StepKind::Gemm;
+        s.value = v;
+        s.tensor_core = true;
+        s.operands = {x, w, out};
+        s.writes = {0, 0, 1};
+        GemmParams& p = s.gemm;
+        p.batch = batch;
+        p.m = m;
+        p.n = n;
+        p.k = k;
+        p.a4 = a4;
+        p.b4 = b4;
+        for (int i = 0; i < 3; i++) {
+            if (!a4.enabled) p.sa[i] = x.ss.strides[i];
+            if (!b4.enabled) p.sb[i] = w.ss.strides[i];
+            p.sc[i] = out.ss.strides[i];
+        }
+        p.splits = 1;
+        p.row_softmax = 1;
+        p.softmax_scale = scale;
+        s.flops = 2.0 * (double)batch * (double)m * (double)n * (double)k;
+        s.desc = "matmul b=" + std::to_string(batch) + " m=" + std::to_string(m) + " n=" + std::to_string(n) + " k=" + std::to_string(k) +
+                 " +0 tf32 row softmax";
+        if (a4.enabled || b4.enabled)
+            s.desc += std::string(" (head split read in place: operand") + (a4.enabled && b4.enabled ? "s a, b" : (a4.enabled ? " a" : " b")) + ")";
+        push_step(std::move(s));
+        return out;
     }
 
     std::optional<PlanTensor> try_fused_contraction(int root) {

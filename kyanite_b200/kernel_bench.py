@@ -125,6 +125,16 @@ def case_attention_scores(rng):
     return g, 0, [rng.standard_normal((384, 512, 64)).astype(np.float32) for _ in range(2)]
 
 
+def case_attention_softmax(rng):
+    """BERT attention scores with their softmax: 384 x softmax([512, 64] . [64, 512] / 8), one fused step."""
+    g = Graph()
+    q = g.input(shape(384, 512, 64))
+    k = g.input(shape(384, 512, 64))
+    scores = g.mul(g.batched_mat_mul(q, g.permute(k, [0, 2, 1])), g.scalar(0.125))
+    g.output(g.softmax(scores, 2))
+    return g, 0, [rng.standard_normal((384, 512, 64)).astype(np.float32) for _ in range(2)]
+
+
 def case_conv_trunk(rng):
     """One trunk convolution of the tower on its own: 3x3, 128 -> 128, batch 256, 8x8, + bias + relu."""
     g = Graph()
@@ -234,6 +244,7 @@ CASES = {
     "linear_llama_proj": _linear_case(2048, 4096, 4096, bias=False),
     "linear_llama_ffn": _linear_case(2048, 11008, 4096, bias=False),
     "attention_scores": case_attention_scores,
+    "attention_softmax": case_attention_softmax,
     "tower": case_tower,
     "conv_trunk": case_conv_trunk,
     "conv_unet": case_conv_unet,

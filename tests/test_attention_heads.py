@@ -86,3 +86,130 @@ def test_matches_oracle(name, project):
     with CudaExecutor(0, g, 0, math_mode=MATH_TF32, flags=FLAG_NO_PERSISTENT_GEMM) as ex:
         other = ex.evaluate(inputs)
     assert_tensors_match(other, got, 2e-3, 2e-3, abs_scaled=True)
+
+
+# ---------------------------------------------------------------- scores and their softmax in one step
+# (kernels/attn_softmax.cu: the scores stay in tensor memory.  The reference runs the matmul, the scaling and the
+# softmax as three operations: kn-cuda-eval/src/planner.rs:300-330 and 560-600.)
+
+def scores_graph(b, m, n, k, scale=0.125, seed=0, constant_keys=False):
+    """softmax(scale * q . keys^T) over the last axis: q [b, m, k] and keys [b, n, k] (K-contiguous, as attention has them)."""
+    g = Graph()
+    q = g.input(shape(b, m, k))
+    if constant_keys:
+        keys = g.constant_tensor(rng(seed).standard_normal((b, n, k)).astype(np.float32))
+    else:
+        keys = g.input(shape(b, n, k))
+    scores = g.batched_mat_mul(q, g.permute(keys, [0, 2, 1]))
+    if scale is not None:
+        scores = g.mul(scores, g.scalar(scale))
+    g.output(g.softmax(scores, 2))
+    return g
+
+
+def fused_steps(g, mode=MATH_TF32, flags=0):
+    return [l for l in steps(plan_describe(g, 0, mode, flags=flags)) if "row softmax" in l]
+
+
+def test_bert_layer_scores_never_reach_memory():
+    g, _ = bert_encoder(layers=1)
+    lines = steps(plan_describe(g, 4, MATH_TF32))
+    fused = [l for l in lines if "row softmax" in l]
+    assert len(fused) == 1 and "head split read in place: operands a, b" in fused[0], lines
+    assert not any(l.split()[2].startswith("softmax") for l in lines), lines
+    for mode, flags in ((MATH_F32, 0), (MATH_TF32, FLAG_NO_PERSISTENT_GEMM)):
+        assert not any("row softmax" in l for l in steps(plan_describe(g, 4, mode, flags=flags)))
+
+
+SCORE_SHAPES = {
+    # name: (b, m, n, k, scale)
+    "one_chunk": (3, 128, 32, 32, 0.2),
+    "three_chunks": (2, 256, 96, 64, 0.125),
+    "odd_chunk_count_per_group": (2, 128, 160, 64, 0.125),
+    "two_halves": (2, 128, 320, 64, 0.125),
+    "full_width": (2, 256, 512, 64, 0.125),
+    "ragged_rows": (3, 200, 192, 64, 0.125),       # the last row block of an entry is partial
+    "long_reduction": (1, 384, 128, 128, 0.09),
+    "no_scale": (2, 128, 64, 32, None),
+}
+
+
+@pytest.mark.parametrize("name", sorted(SCORE_SHAPES))
+def test_scores_route(name):
+    b, m, n, k, scale = SCORE_SHAPES[name]
+    assert len(fused_steps(scores_graph(b, m, n, k, scale))) == 1
+    assert len(fused_steps(scores_graph(b, m, n, k, scale, constant_keys=True))) == 1
+
+
+@pytest.mark.parametrize("case", ["negative_scale", "few_rows", "too_many_keys", "keys_not_a_chunk_multiple", "masked", "softmax_over_rows",
+                                  "scores_read_twice"])
+def test_scores_stay_two_steps(case):
+    b, m, n, k, scale = 2, 128, 128, 64, 0.125
+    if case == "negative_scale":
+        g = scores_graph(b, m, n, k, -0.125)
+    elif case == "few_rows":
+        g = scores_graph(b, 64, n, k, scale)
+    elif case == "too_many_keys":
+        g = scores_graph(b, m, 1024, k, scale)
+    elif case == "keys_not_a_chunk_multiple":
+        g = scores_graph(b, m, 100, k, scale)
+    else:
+        g = Graph()
+        q, keys = g.input(shape(b, m, k)), g.input(shape(b, n, k))
+        scores = g.mul(g.batched_mat_mul(q, g.permute(keys, [0, 2, 1])), g.scalar(scale))
+        if case == "masked":
+            g.output(g.softmax(g.add(scores, g.input(shape(1, m, n))), 2))
+        elif case == "softmax_over_rows":
+            g.output(g.softmax(scores, 1))
+        else:
+            g.output(g.softmax(scores, 2))
+            g.output(scores)
+    assert fused_steps(g) == []
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("constant_keys", [False, True], ids=["input_keys", "constant_keys"])
+@pytest.mark.parametrize("name", sorted(SCORE_SHAPES))
+def test_scores_match_oracle(name, constant_keys):
+    from kyanite_b200.executor import CudaExecutor
+    b, m, n, k, scale = SCORE_SHAPES[name]
+    g = scores_graph(b, m, n, k, scale, seed=5, constant_keys=constant_keys)
+    r = rng(21)
+    q = r.standard_normal((b, m, k)).astype(np.float32)
+    if scale is None:
+        q *= 0.2   # unscaled scores of standard normal operands would make every row one-hot
+    inputs = [q] if constant_keys else [q, r.standard_normal((b, n, k)).astype(np.float32)]
+    expected = cpu_eval_graph(g.to_bytes(), 0, inputs)
+    with CudaExecutor(0, g, 0, math_mode=MATH_TF32) as ex:
+        assert "row softmax" in plan_describe(g, 0, MATH_TF32)
+        got = ex.evaluate(inputs)
+        again = ex.evaluate(inputs)
+    # TF32 operands: a score is off by up to ~1e-2 absolute here, a probability by that relative amount
+    assert_tensors_match(expected, got, 2e-2, 2e-2, abs_scaled=True)
+    np.testing.assert_allclose(got[0].sum(axis=2), 1.0, rtol=0, atol=1e-5)
+    assert np.array_equal(got[0], again[0])
+    # the two-step plan rounds the same operands the same way: only the exponential differs (ex2.approx against expf)
+    with CudaExecutor(0, g, 0, math_mode=MATH_TF32, flags=FLAG_NO_PERSISTENT_GEMM) as ex:
+        other = ex.evaluate(inputs)
+    assert_tensors_match(other, got, 1e-5, 1e-4, abs_scaled=True)
+
+
+@pytest.mark.gpu
+def test_scores_softmax_is_stable_for_large_scores():
+    """Rows whose scores are far outside the range of exp: the maximum is subtracted first, as the oracle does."""
+    from kyanite_b200.executor import CudaExecutor
+    b, m, n, k = 1, 128, 64, 32
+    g = scores_graph(b, m, n, k, 1.0)
+    r = rng(2)
+    q = (30.0 * r.standard_normal((b, m, k))).astype(np.float32)
+    keys = (30.0 * r.standard_normal((b, n, k))).astype(np.float32)
+    with CudaExecutor(0, g, 0, math_mode=MATH_TF32) as ex:
+        got = ex.evaluate([q, keys])[0]
+    assert np.isfinite(got).all()
+    np.testing.assert_allclose(got.sum(axis=2), 1.0, rtol=0, atol=1e-5)
+    # scores of magnitude ~5000: the winner of a row is the oracle's wherever its margin exceeds the TF32 error
+    exact = np.einsum("bmk,bnk->bmn", q.astype(np.float64), keys.astype(np.float64))
+    top2 = np.sort(exact, axis=2)[:, :, -2:]
+    clear = (top2[:, :, 1] - top2[:, :, 0]) > 50.0
+    assert clear.sum() > m // 2
+    assert np.array_equal(got.argmax(axis=2)[clear], exact.argmax(axis=2)[clear])
