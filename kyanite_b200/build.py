@@ -34,6 +34,7 @@ SOURCES = [
     "kernels/conv_chain.cu",
     "kernels/gemm_persistent.cu",
     "kernels/attn_softmax.cu",
+    "kernels/attention.cu",
 ]
 
 NVCC_FLAGS = [

@@ -145,6 +145,10 @@ struct Executor {
                     }
                     s.gemm.add1 = ptr.size() > 3 ? (const float*)ptr[3] : nullptr;
                     s.gemm.add2 = ptr.size() > 4 ? (const float*)ptr[4] : nullptr;
+                    if (s.gemm.row_softmax == 2) {   // fused attention: the fourth operand is V^T, there are no addends
+                        s.gemm.values = s.gemm.add1;
+                        s.gemm.add1 = nullptr;
+                    }
                     break;
                 case StepKind::Conv:
                     s.conv.in = (const float*)ptr[0];

@@ -151,8 +151,13 @@ struct GemmParams {
     GemmOperand4D a4, b4;    // head split / merge read in place (above)
     // Row softmax fused into the matmul (attention scores): C = softmax over each row of (softmax_scale * A.B), rows of
     // at most 512 columns, no addends, no activation (kernels/attn_softmax.cu; tensor cores only).
+    // 2: the step goes on to C = softmax(...) . V without writing the probabilities: `values` is V^T, [batch][values_cols][n]
+    // with element strides `values_strides` (the last is 1), C is [batch][m][values_cols] (kernels/attention.cu).
     int32_t row_softmax;
     float softmax_scale;
+    const float* values;
+    int64_t values_strides[3];
+    int64_t values_cols;
     int32_t conv_operand;
     int32_t conv_c, conv_h, conv_w, conv_ow, conv_r, conv_s, conv_pad_y, conv_pad_x;
     int64_t conv_strides[3];   // element strides of the image tensor: image, row, pixel (channels are contiguous)

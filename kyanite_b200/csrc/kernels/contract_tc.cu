@@ -701,6 +701,7 @@ struct TcLaunch {
     std::shared_ptr<void> chain;  // ConvChain step: launch data of kernels/conv_chain.cu
     std::shared_ptr<void> gemm_p; // matmul taken by the persistent kernel (kernels/gemm_persistent.cu)
     std::shared_ptr<void> attn;   // matmul with a row softmax (kernels/attn_softmax.cu)
+    std::shared_ptr<void> attention;   // scores, softmax and probabilities . V (kernels/attention.cu)
 };
 
 CUtensorMap tc_make_store_map(const void* base, int rank, const int64_t* dims, const int64_t* strides, const int* box) {
@@ -899,6 +900,12 @@ void tc_prepare_step(Step& step, uint32_t* status_word, int flags, uint32_t* tra
     int64_t n_cols;
     if (step.kind == StepKind::Gemm) {
         const GemmParams& g = step.gemm;
+        if (g.row_softmax == 2) {
+            launch->attention = attention_prepare(g, status_word);
+            KN_CHECK(launch->attention != nullptr, KN_ERR_INTERNAL, "fused attention step does not qualify");
+            step.tc = launch;
+            return;
+        }
         if (g.row_softmax) {
             launch->attn = attn_softmax_prepare(g, status_word);
             KN_CHECK(launch->attn != nullptr, KN_ERR_INTERNAL, "matmul with a row softmax does not qualify");
@@ -1099,6 +1106,7 @@ static int launch_splitk_reduce(const SplitKReduceParams& r, cudaStream_t stream
 int tc_launch_step(const Step& step, cudaStream_t stream) {
     const TcLaunch& l = *step.tc;
     if (l.chain) return chain_launch(l.chain.get(), stream);
+    if (l.attention) return attention_launch(l.attention.get(), stream);
     if (l.attn) return attn_softmax_launch(l.attn.get(), stream);
     if (l.gemm_p) {
         const int err = gemm_persistent_launch(l.gemm_p.get(), stream);

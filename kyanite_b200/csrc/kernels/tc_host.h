@@ -34,6 +34,10 @@ int gemm_persistent_launch(const void* launch, cudaStream_t stream);
 bool attn_softmax_fits(int64_t batch, int64_t m, int64_t n, int64_t k);
 std::shared_ptr<void> attn_softmax_prepare(const GemmParams& g, uint32_t* status_word);
 int attn_softmax_launch(const void* launch, cudaStream_t stream);
+// Scores, softmax and probabilities . V in one kernel (kernels/attention.cu): null if the step does not qualify.
+bool attention_fits(int64_t batch, int64_t m, int64_t n, int64_t k, int64_t dv);
+std::shared_ptr<void> attention_prepare(const GemmParams& g, uint32_t* status_word);
+int attention_launch(const void* launch, cudaStream_t stream);
 
 // Convolution chain (kernels/conv_chain.cu): launch data built once the device pointers are known.
 std::shared_ptr<void> chain_prepare(const ConvChainParams& c, uint32_t* status_word);

@@ -523,6 +523,7 @@ class Planner {
     }
 
     PlanTensor visit_new(int v) {
+        if (auto fused = try_fused_attention_context(v)) return *fused;
         if (auto fused = try_fused_contraction(v)) return *fused;
         if (auto fused = try_fused_rmsnorm(v)) return *fused;
         const ValueInfo& info = g_.values[v];
@@ -905,7 +906,41 @@ class Planner {
     // attention head over up to 512 keys), every node in between used by this expression only: ONE tensor-core step
     // that keeps the scores in tensor memory and writes the probabilities (kernels/attn_softmax.cu), instead of a
     // matmul that writes the scores and a softmax that reads and writes them again.
-    std::optional<PlanTensor> try_fused_attention_scores(int v) {
+    //
+    // With `context` (a matmul whose left operand is that softmax and nothing else reads it, V of 32 or 64 columns) the
+    // step goes on to probabilities . V: the probabilities never reach memory either (kernels/attention.cu).
+    std::optional<PlanTensor> try_fused_attention_scores(int v) { return plan_attention(v, -1); }
+
+    std::optional<PlanTensor> try_fused_attention_context(int v) {
+        const ValueInfo& mi = g_.values[v];
+        if (mi.op != OpKind::MatMul || mi.dtype != DType::F32 || shape_of(v).size() != 3) return std::nullopt;
+        const int sv = mi.inputs[0];
+        if (g_.values[sv].op != OpKind::Softmax || !fusable(sv) || map_[sv] || mi.inputs[1] == sv) return std::nullopt;
+        const std::vector<int64_t> ps = shape_of(sv), vs = shape_of(mi.inputs[1]);
+        if (ps.size() != 3 || vs.size() != 3 || vs[0] != ps[0]) return std::nullopt;
+        const int q = plan_attention_query(sv);
+        if (q < 0 || !attention_fits(ps[0], ps[1], ps[2], shape_of(q)[2], vs[2])) return std::nullopt;
+        return plan_attention(sv, v);
+    }
+
+    // the left operand of the scores matmul if `v` is a softmax the fused attention steps take, else -1
+    int plan_attention_query(int v) {
+        const ValueInfo& si = g_.values[v];
+        if (si.dtype != DType::F32 || opts_.math_mode != KN_MATH_TF32 || (opts_.flags & KN_FLAG_NO_PERSISTENT_GEMM)) return -1;
+        if (shape_of(v).size() != 3 || si.axis != 2) return -1;
+        int y = si.inputs[0];
+        if (g_.values[y].op == OpKind::Binary && g_.values[y].binary_op == BinaryOp::Mul && fusable(y) && !map_[y]) {
+            const ValueInfo& mi = g_.values[y];
+            auto c0 = g_.as_single_const(mi.inputs[0]), c1 = g_.as_single_const(mi.inputs[1]);
+            if (!c0 && !c1) return -1;
+            y = c0 ? mi.inputs[1] : mi.inputs[0];
+        }
+        const ValueInfo& ci = g_.values[y];
+        if (ci.op != OpKind::MatMul || ci.dtype != DType::F32 || !fusable(y) || map_[y] || shape_of(y) != shape_of(v)) return -1;
+        return ci.inputs[0];
+    }
+
+    std::optional<PlanTensor> plan_attention(int v, int context) {
         const ValueInfo& si = g_.values[v];
         if (si.dtype != DType::F32 || opts_.math_mode != KN_MATH_TF32 || (opts_.flags & KN_FLAG_NO_PERSISTENT_GEMM)) return std::nullopt;
         const std::vector<int64_t> shape = shape_of(v);
@@ -945,6 +980,53 @@ class Planner {
         if (b4.enabled) wc.ss = StridedShape({batch, k, n}, {n * k, 1, k}), wc.offset = 0;
         if (xc.ss.rank() != 3 || wc.ss.rank() != 3 || !gemm_fits_tensor_core(xc, wc) || xc.ss.strides[0] == 0 || wc.ss.strides[0] == 0)
             return std::nullopt;   // (the operands are planned either way; the matmul and the softmax stay two steps)
+        PlanTensor values;
+        int64_t dv = 0;
+        if (context >= 0) {
+            // V as [batch, keys, dv] with the keys contiguous (a transposed copy unless it is stored that way)
+            const int vin = g_.values[context].inputs[1];
+            values = k_major_b(visit(vin), vin);
+            dv = values.ss.shape[2];
+            const auto& st = values.ss.strides;
+            if (st[1] != 1 || st[2] % 4 != 0 || st[0] % 4 != 0 || (batch > 1 && st[0] == 0) || values.offset % 4 != 0)
+                return std::nullopt;   // (planned as separate steps; V stays planned)
+        }
+        if (context >= 0) {
+            // the softmax and its matmul are part of this step: nothing else reads them (checked by the caller)
+            PlanTensor out = alloc_shared({batch, m, dv}, DType::F32, context);
+            Step s;
+            s.kind = StepKind::Gemm;
+            s.value = context;
+            s.tensor_core = true;
+            s.operands = {x, w, out, values};
+            s.writes = {0, 0, 1, 0};
+            GemmParams& p = s.gemm;
+            p.batch = batch;
+            p.m = m;
+            p.n = n;
+            p.k = k;
+            p.a4 = a4;
+            p.b4 = b4;
+            for (int i = 0; i < 3; i++) {
+                if (!a4.enabled) p.sa[i] = x.ss.strides[i];
+                if (!b4.enabled) p.sb[i] = w.ss.strides[i];
+                p.sc[i] = out.ss.strides[i];
+            }
+            p.values_strides[0] = values.ss.strides[0];   // V^T [batch][dv][keys]
+            p.values_strides[1] = values.ss.strides[2];
+            p.values_strides[2] = values.ss.strides[1];
+            p.values_cols = dv;
+            p.splits = 1;
+            p.row_softmax = 2;
+            p.softmax_scale = scale;
+            s.flops = 2.0 * (double)batch * (double)m * (double)n * (double)(k + dv);
+            s.desc = "attention b=" + std::to_string(batch) + " m=" + std::to_string(m) + " keys=" + std::to_string(n) + " k=" + std::to_string(k) +
+                     " dv=" + std::to_string(dv) + " tf32 (scores and probabilities stay in tensor memory)";
+            if (a4.enabled || b4.enabled)
+                s.desc += std::string(" (head split read in place: operand") + (a4.enabled && b4.enabled ? "s a, b" : (a4.enabled ? " a" : " b")) + ")";
+            push_step(std::move(s));
+            return out;
+        }
         PlanTensor out = alloc_shared(shape, DType::F32, v);
         Step s;
         s.kind = StepKind::Gemm;

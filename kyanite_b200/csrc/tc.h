@@ -21,6 +21,7 @@ int gemm_persistent_bn(int64_t n);
 
 // Shapes the fused attention-scores kernel takes (kernels/attn_softmax.cu): pure host arithmetic.
 bool attn_softmax_fits(int64_t batch, int64_t m, int64_t n, int64_t k);
+bool attention_fits(int64_t batch, int64_t m, int64_t n, int64_t k, int64_t dv);   // (kernels/attention.cu)
 
 // Output tile of the convolution kernel: wb x hb x nb output positions (product 128).
 bool tc_conv_tile(int oh, int ow, int* wb, int* hb, int* nb);

@@ -135,6 +135,20 @@ def case_attention_softmax(rng):
     return g, 0, [rng.standard_normal((384, 512, 64)).astype(np.float32) for _ in range(2)]
 
 
+def case_attention(rng):
+    """BERT attention for 384 heads of 512 tokens: softmax([512, 64] . [64, 512] / 8) . [512, 64] as one fused step
+    (V arrives as [384, 64, 512], keys contiguous, as the planner's transposing copy leaves it).  With KN_ATTN_TRACE=1
+    in the environment the kernel's per-item phase clocks are printed at exit."""
+    g = Graph()
+    q = g.input(shape(384, 512, 64))
+    k = g.input(shape(384, 512, 64))
+    vt = g.input(shape(384, 64, 512))
+    scores = g.mul(g.batched_mat_mul(q, g.permute(k, [0, 2, 1])), g.scalar(0.125))
+    g.output(g.batched_mat_mul(g.softmax(scores, 2), g.permute(vt, [0, 2, 1])))
+    r = [rng.standard_normal((384, 512, 64)).astype(np.float32) for _ in range(2)]
+    return g, 0, r + [rng.standard_normal((384, 64, 512)).astype(np.float32)]
+
+
 def case_conv_trunk(rng):
     """One trunk convolution of the tower on its own: 3x3, 128 -> 128, batch 256, 8x8, + bias + relu."""
     g = Graph()
@@ -245,6 +259,7 @@ CASES = {
     "linear_llama_ffn": _linear_case(2048, 11008, 4096, bias=False),
     "attention_scores": case_attention_scores,
     "attention_softmax": case_attention_softmax,
+    "attention": case_attention,
     "tower": case_tower,
     "conv_trunk": case_conv_trunk,
     "conv_unet": case_conv_unet,

@@ -114,11 +114,15 @@ def fused_steps(g, mode=MATH_TF32, flags=0):
 def test_bert_layer_scores_never_reach_memory():
     g, _ = bert_encoder(layers=1)
     lines = steps(plan_describe(g, 4, MATH_TF32))
-    fused = [l for l in lines if "row softmax" in l]
+    fused = [l for l in lines if " attention " in l]
     assert len(fused) == 1 and "head split read in place: operands a, b" in fused[0], lines
-    assert not any(l.split()[2].startswith("softmax") for l in lines), lines
+    assert "keys=512 k=64 dv=64" in fused[0]
+    # neither a softmax step nor a matmul over the probabilities is left
+    assert not any("softmax" in l for l in lines), lines
+    assert not any("matmul b=48" in l for l in lines), lines
     for mode, flags in ((MATH_F32, 0), (MATH_TF32, FLAG_NO_PERSISTENT_GEMM)):
-        assert not any("row softmax" in l for l in steps(plan_describe(g, 4, mode, flags=flags)))
+        other = steps(plan_describe(g, 4, mode, flags=flags))
+        assert not any("row softmax" in l or " attention " in l for l in other)
 
 
 SCORE_SHAPES = {
@@ -131,6 +135,8 @@ SCORE_SHAPES = {
     "ragged_rows": (3, 200, 192, 64, 0.125),       # the last row block of an entry is partial
     "long_reduction": (1, 384, 128, 128, 0.09),
     "no_scale": (2, 128, 64, 32, None),
+    "more_items_than_ctas": (170, 128, 64, 32, 0.2),   # every CTA walks several items
+    "more_items_than_ctas_full_width": (80, 512, 512, 64, 0.125),
 }
 
 
@@ -213,3 +219,102 @@ def test_scores_softmax_is_stable_for_large_scores():
     clear = (top2[:, :, 1] - top2[:, :, 0]) > 50.0
     assert clear.sum() > m // 2
     assert np.array_equal(got.argmax(axis=2)[clear], exact.argmax(axis=2)[clear])
+
+
+# ---------------------------------------------------------------- scores, softmax and probabilities . V in one step
+# (kernels/attention.cu: the probabilities stay in tensor memory as the A operand of the second matmul.)
+
+def context_graph(b, m, n, k, dv, scale=0.125, values_keys_contiguous=True, probabilities_output=False):
+    """softmax(scale * q . keys^T) . v: q [b, m, k], keys [b, n, k], v [b, n, dv] (stored as [b, dv, n] if asked)."""
+    g = Graph()
+    q, keys = g.input(shape(b, m, k)), g.input(shape(b, n, k))
+    v = g.permute(g.input(shape(b, dv, n)), [0, 2, 1]) if values_keys_contiguous else g.input(shape(b, n, dv))
+    probs = g.softmax(g.mul(g.batched_mat_mul(q, g.permute(keys, [0, 2, 1])), g.scalar(scale)), 2)
+    g.output(g.batched_mat_mul(probs, v))
+    if probabilities_output:
+        g.output(probs)
+    return g
+
+
+CONTEXT_SHAPES = {
+    # name: (b, m, n, k, dv)
+    "bert_head": (3, 256, 512, 64, 64),
+    "narrow_values": (2, 256, 256, 64, 32),
+    "narrow_head": (2, 256, 128, 32, 32),
+    "one_row_block": (2, 128, 128, 64, 64),
+    "keys_only_through_shared_memory": (2, 256, 64, 64, 64),
+    "one_chunk_of_keys": (2, 256, 32, 32, 32),
+    "three_chunks": (2, 256, 96, 64, 64),
+    "ragged_rows": (3, 200, 192, 64, 64),
+    "three_row_blocks": (2, 384, 128, 64, 64),
+    "long_reduction": (1, 512, 128, 128, 64),
+    "more_items_than_ctas": (90, 256, 64, 32, 32),     # every CTA walks several items
+    "more_items_than_ctas_full_width": (40, 512, 512, 64, 64),
+}
+
+
+@pytest.mark.parametrize("name", sorted(CONTEXT_SHAPES))
+def test_context_route(name):
+    b, m, n, k, dv = CONTEXT_SHAPES[name]
+    for contiguous in (True, False):
+        lines = steps(plan_describe(context_graph(b, m, n, k, dv, values_keys_contiguous=contiguous), 0, MATH_TF32))
+        assert sum(" attention " in l for l in lines) == 1 and not any("row softmax" in l for l in lines), lines
+        # V with its columns contiguous gets the transposing copy the plain matmul would need as well
+        assert sum(" copy " in l for l in lines) == (0 if contiguous else 1), lines
+
+
+@pytest.mark.parametrize("case", ["wide_values", "values_wider_than_head", "probabilities_read_elsewhere", "few_rows"])
+def test_context_stays_a_matmul(case):
+    if case == "wide_values":
+        g = context_graph(2, 256, 128, 128, 128)
+    elif case == "probabilities_read_elsewhere":
+        g = context_graph(2, 256, 128, 64, 64, probabilities_output=True)
+    elif case == "values_wider_than_head":
+        g = context_graph(2, 256, 128, 32, 64)    # V^T takes the place of the keys in shared memory
+    else:
+        g = context_graph(2, 64, 128, 64, 64)
+    lines = steps(plan_describe(g, 0, MATH_TF32))
+    assert not any(" attention " in l for l in lines), lines
+    if case != "few_rows":
+        assert sum("row softmax" in l for l in lines) == 1, lines
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("contiguous", [True, False], ids=["keys_contiguous", "columns_contiguous"])
+@pytest.mark.parametrize("name", sorted(CONTEXT_SHAPES))
+def test_context_matches_oracle(name, contiguous):
+    from kyanite_b200.executor import CudaExecutor
+    b, m, n, k, dv = CONTEXT_SHAPES[name]
+    g = context_graph(b, m, n, k, dv, scale=1.0 / math.sqrt(k), values_keys_contiguous=contiguous)
+    r = rng(33)
+    inputs = [r.standard_normal((b, m, k)).astype(np.float32), r.standard_normal((b, n, k)).astype(np.float32),
+              r.standard_normal((b, dv, n) if contiguous else (b, n, dv)).astype(np.float32)]
+    expected = cpu_eval_graph(g.to_bytes(), 0, inputs)
+    with CudaExecutor(0, g, 0, math_mode=MATH_TF32) as ex:
+        got = ex.evaluate(inputs)
+        again = ex.evaluate(inputs)
+    # two chained TF32 contractions: 4e-3 of the largest expected magnitude
+    assert_tensors_match(expected, got, 4e-3, 4e-3, abs_scaled=True)
+    assert np.array_equal(got[0], again[0])
+    # against the same graph planned as separate tensor-core steps (same operand rounding; the probabilities are
+    # rounded to TF32 there too, but from their normalised values)
+    with CudaExecutor(0, g, 0, math_mode=MATH_TF32, flags=FLAG_NO_PERSISTENT_GEMM) as ex:
+        other = ex.evaluate(inputs)
+    assert_tensors_match(other, got, 2e-3, 2e-3, abs_scaled=True)
+
+
+@pytest.mark.gpu
+def test_context_of_one_hot_rows_copies_values():
+    """Scores so far apart that every row's softmax is one-hot: the context rows are rows of V (rounded to TF32)."""
+    from kyanite_b200.executor import CudaExecutor
+    b, m, n, k, dv = 2, 256, 128, 64, 64
+    g = context_graph(b, m, n, k, dv, scale=1.0)
+    r = rng(4)
+    keys = r.standard_normal((b, n, k)).astype(np.float32)
+    pick = r.integers(0, n, size=(b, m))
+    q = np.stack([40.0 * keys[i][pick[i]] for i in range(b)]).astype(np.float32)
+    v = r.standard_normal((b, dv, n)).astype(np.float32)
+    with CudaExecutor(0, g, 0, math_mode=MATH_TF32) as ex:
+        got = ex.evaluate([q, keys, v])[0]
+    want = np.stack([v[i].T[pick[i]] for i in range(b)])
+    np.testing.assert_allclose(got, want, rtol=0, atol=2e-3)
