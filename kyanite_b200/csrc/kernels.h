@@ -155,9 +155,13 @@ struct GemmParams {
     // with element strides `values_strides` (the last is 1), C is [batch][m][values_cols] (kernels/attention.cu).
     int32_t row_softmax;
     float softmax_scale;
+    // `values_mn`: `values` is V itself, [batch][n][values_cols] with the columns contiguous (strides as above), or, with
+    // `v4`, a head split read in place (rows = keys, K = columns).
     const float* values;
     int64_t values_strides[3];
     int64_t values_cols;
+    int32_t values_mn;
+    GemmOperand4D v4;
     int32_t conv_operand;
     int32_t conv_c, conv_h, conv_w, conv_ow, conv_r, conv_s, conv_pad_y, conv_pad_x;
     int64_t conv_strides[3];   // element strides of the image tensor: image, row, pixel (channels are contiguous)

@@ -55,7 +55,9 @@ struct AttentionParams {
     int32_t k_blocks;                // 32-element K blocks of the scores' reduction (the head dimension / 32)
     int32_t dv;                      // columns of V and of the output: 32 or 64
     int32_t m, m_tiles, total;       // rows per batch entry; 128-row blocks per batch entry; work items
-    int32_t a_bi, b_bi;              // batch entry bt -> map coordinates (bt % bi, bt / bi) of Q and of the keys
+    int32_t a_bi, b_bi, v_bi;        // batch entry bt -> map coordinates (bt % bi, bt / bi) of Q, of the keys and of V
+    int32_t v_mn;                    // 1: V is given with its columns contiguous ([keys][dv], possibly a head split read in place)
+                                     // and is the MN-major B operand of the context MMAs; 0: V^T ([dv][keys]), K-major
     int32_t tmem_cols;
     float scale;
     float* out;                      // [batch][m][dv]: strides out_s0, out_s1 (elements), 1
@@ -136,12 +138,28 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             // the score MMAs have read the keys: V^T takes their place while the epilogue works on the scores
             if (!mbar_wait(s_done, (uint32_t)(local & 1), abandon, p.status, 42, kWaitCycles, kAtSleepNs)) break;
             mbar_expect_tx(full_v, v_bytes);
-            for (int c = 0; c < chunks; c++) tma_load_4d(k_base + (uint32_t)c * v_block_bytes, &map_v, full_v, c * 32, 0, bt, 0);
+            if (p.v_mn) {
+                // per 32 columns of V a tile [keys][128 B] (at most 256 rows per request)
+                const int v2 = bt % p.v_bi, v3 = bt / p.v_bi;
+                const int rows_per = p.n > 256 ? p.n >> 1 : p.n;
+                for (int cb = 0; cb < e_chunks; cb++)
+                    for (int r0 = 0; r0 < p.n; r0 += rows_per)
+                        tma_load_4d(k_base + (uint32_t)(cb * p.n + r0) * 128u, &map_v, full_v, cb * 32, r0, v2, v3);
+            } else {
+                for (int c = 0; c < chunks; c++) tma_load_4d(k_base + (uint32_t)c * v_block_bytes, &map_v, full_v, c * 32, 0, bt, 0);
+            }
         }
     } else if (warp == 1 && lane == 0) {
         // ---------------- MMA issuer: f32 accumulate, TF32 x TF32, both K-major, M = 128
         const uint32_t idesc_s = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(p.half_n >> 3) << 17) | ((uint32_t)(kAtBlockM >> 4) << 24);
-        const uint32_t idesc_o = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(p.dv >> 3) << 17) | ((uint32_t)(kAtBlockM >> 4) << 24);
+        // (bit 16: the B operand is MN-major, its N index contiguous)
+        const uint32_t idesc_o = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(p.v_mn ? 1 : 0) << 16) | ((uint32_t)(p.dv >> 3) << 17) |
+                                 ((uint32_t)(kAtBlockM >> 4) << 24);
+        // MN-major B of 32-bit elements: the 128-byte swizzle in 32-byte pieces (layout type 1; the copy engine's
+        // SWIZZLE_128B_ATOM_32B).  4 K rows (keys) of 128 bytes (32 columns of V) make an atom, the next 4 keys are
+        // `stride byte offset` = 512 bytes further on, the next 32 columns `leading byte offset` (their own
+        // [keys][128 B] tile).
+        const uint64_t v_mn_desc = ((uint64_t)(((uint32_t)p.n * 128u) >> 4) << 16) | ((uint64_t)(512 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)1 << 61);
         int local = 0;
         for (int t = blockIdx.x; t < p.total; t += gridDim.x, local++) {
             if (!mbar_wait(full_qk, (uint32_t)(local & 1), abandon, p.status, 43, kWaitCycles, kAtSleepNs)) break;
@@ -166,14 +184,18 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             if (!mbar_wait(e_ready, (uint32_t)(local & 1), abandon, p.status, 46, kWaitCycles, kAtSleepNs)) break;
             tc_fence_after();
             for (int c = 0; c < chunks; c++) {
-                const uint64_t db = smem_desc_sw128(k_base + (uint32_t)c * v_block_bytes);
+                // B of the j-th instruction of the chunk (8 keys): K-major, 32 bytes along the rows of the chunk's block
+                // of V^T; MN-major, 8 rows of 128 bytes further on in the tiles of V
+                const uint64_t db = p.v_mn ? (v_mn_desc | (uint64_t)(((k_base + (uint32_t)c * 4096u) & 0x3FFFFu) >> 4))
+                                           : smem_desc_sw128(k_base + (uint32_t)c * v_block_bytes);
+                const uint32_t db_step = p.v_mn ? (1024u >> 4) : 2u;
                 if (c < e_chunks) {
                     const uint64_t da = smem_desc_sw128(e_base + (uint32_t)c * kAtChunkTileBytes);
 #pragma unroll
-                    for (int j = 0; j < 4; j++) mma_tf32(tmem_base, da + 2u * j, db + 2u * j, idesc_o, (c | j) != 0 ? 1u : 0u);
+                    for (int j = 0; j < 4; j++) mma_tf32(tmem_base, da + 2u * j, db + db_step * j, idesc_o, (c | j) != 0 ? 1u : 0u);
                 } else {
 #pragma unroll
-                    for (int j = 0; j < 4; j++) mma_tf32_a_tmem(tmem_base, tmem_base + (uint32_t)(c * 32 + j * 8), db + 2u * j, idesc_o, 1u);
+                    for (int j = 0; j < 4; j++) mma_tf32_a_tmem(tmem_base, tmem_base + (uint32_t)(c * 32 + j * 8), db + db_step * j, idesc_o, 1u);
                 }
             }
             mma_commit(pv_done);
@@ -369,10 +391,12 @@ std::shared_ptr<void> attention_prepare(const GemmParams& g, uint32_t* status_wo
     if (g.half || g.conv_operand != 0 || g.splits > 1 || g.add1 || g.add2 || g.act != 0 || g.row_softmax != 2 || !g.values) return nullptr;
     if (!attention_fits(g.batch, g.m, g.n, g.k, g.values_cols)) return nullptr;
     if (g.sc[2] != 1 || g.sc[1] % 4 != 0 || (g.batch > 1 && g.sc[0] % 4 != 0) || ((uintptr_t)g.c & 15) != 0) return nullptr;
-    // V^T: [batch][dv][n] with the keys contiguous
-    if (g.values_strides[2] != 1 || g.values_strides[1] % 4 != 0 || (g.batch > 1 && (g.values_strides[0] % 4 != 0 || g.values_strides[0] == 0)) ||
-        ((uintptr_t)g.values & 15) != 0)
+    // V^T [batch][dv][n] with the keys contiguous, or (values_mn) V [batch][n][dv] with its columns contiguous / a head split
+    if (((uintptr_t)g.values & 15) != 0) return nullptr;
+    if (!g.v4.enabled && (g.values_strides[2] != 1 || g.values_strides[1] % 4 != 0 ||
+                          (g.batch > 1 && (g.values_strides[0] % 4 != 0 || g.values_strides[0] == 0))))
         return nullptr;
+    if (g.v4.enabled && (!g.values_mn || g.v4.kd != g.values_cols || g.v4.rd < g.n || g.v4.strides[0] != 1)) return nullptr;
     auto l = std::make_shared<AttentionLaunch>();
     AttentionParams& p = l->p;
     memset(&p, 0, sizeof(p));
@@ -420,10 +444,22 @@ std::shared_ptr<void> attention_prepare(const GemmParams& g, uint32_t* status_wo
             p.b_bi = (int)g.batch + 1;
         }
     }
-    {
+    p.v_mn = g.values_mn ? 1 : 0;
+    if (g.values_mn) {
+        int box[4] = {32, (int)(g.n > 256 ? g.n / 2 : g.n), 1, 1};
+        if (g.v4.enabled) {
+            l->map_v = tc_make_map_mn_major(g.values, 4, g.v4.dims, g.v4.strides, box);
+            p.v_bi = g.v4.bi;
+        } else {
+            int64_t dims[4] = {g.values_cols, g.n, g.batch, 1}, strides[4] = {1, g.values_strides[1], g.batch > 1 ? g.values_strides[0] : g.values_strides[1] * g.n, 4};
+            l->map_v = tc_make_map_mn_major(g.values, 4, dims, strides, box);
+            p.v_bi = (int)g.batch + 1;
+        }
+    } else {
         int box[4] = {32, p.dv, 1, 1};
         int64_t dims[4] = {g.n, g.values_cols, g.batch, 1}, strides[4] = {1, g.values_strides[1], g.batch > 1 ? g.values_strides[0] : g.values_strides[1] * g.values_cols, 4};
         l->map_v = tc_make_map(g.values, 4, dims, strides, box, true);
+        p.v_bi = (int)g.batch + 1;
     }
     // KN_ATTN_TRACE=1 in the environment: CTA 0 stamps clock64 per work item (producer: loads issued; MMA thread:
     // operands landed, tensor memory free; first epilogue warp: scores ready, after the maximum, after the

@@ -646,7 +646,7 @@ EncodeTiledFn encode_tiled_fn() {
 
 // dims / strides innermost first; strides in elements (dims[0] has stride 1)
 CUtensorMap make_map(const void* base, int rank, const int64_t* dims, const int64_t* strides, const int* box,
-                     bool operand = true) {
+                     bool operand = true, bool atom_32b = false) {
     KN_CHECK(((uintptr_t)base & 15) == 0, KN_ERR_INTERNAL, "TMA base address is not 16-byte aligned");
     cuuint64_t gdim[5], gstride[4];
     cuuint32_t gbox[5], estride[5];
@@ -667,7 +667,8 @@ CUtensorMap make_map(const void* base, int rank, const int64_t* dims, const int6
     // (epilogue tiles, `operand == false`, are plain f32 rows without swizzle)
     CUresult res = encode_tiled_fn()(&map, operand ? CU_TENSOR_MAP_DATA_TYPE_TFLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
                                      (cuuint32_t)rank, const_cast<void*>(base), gdim, gstride, gbox, estride,
-                                     CU_TENSOR_MAP_INTERLEAVE_NONE, operand ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                                     CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                     operand ? (atom_32b ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B) : CU_TENSOR_MAP_SWIZZLE_NONE,
                                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     KN_CHECK(res == CUDA_SUCCESS, KN_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)res));
     return map;
@@ -729,6 +730,9 @@ CUtensorMap tc_make_store_map(const void* base, int rank, const int64_t* dims, c
 
 CUtensorMap tc_make_map(const void* base, int rank, const int64_t* dims, const int64_t* strides, const int* box, bool operand) {
     return make_map(base, rank, dims, strides, box, operand);
+}
+CUtensorMap tc_make_map_mn_major(const void* base, int rank, const int64_t* dims, const int64_t* strides, const int* box) {
+    return make_map(base, rank, dims, strides, box, true, true);
 }
 
 CUtensorMap tc_make_map_f16(const void* base, int rank, const int64_t* dims, const int64_t* strides, const int* box, bool operand) {

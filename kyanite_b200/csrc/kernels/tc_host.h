@@ -14,6 +14,9 @@ namespace kn {
 // stride 1).  `operand`: 128-byte swizzle and round-to-TF32 on load (an MMA operand tile); otherwise a
 // plain f32 tile without swizzle (an epilogue tile).
 CUtensorMap tc_make_map(const void* base, int rank, const int64_t* dims, const int64_t* strides, const int* box, bool operand);
+// The same for a TF32 operand whose M / N index is the contiguous one (MN-major): the 128-byte swizzle in 32-byte
+// pieces, the only shared-memory layout the tensor cores take for such an operand of 32-bit elements.
+CUtensorMap tc_make_map_mn_major(const void* base, int rank, const int64_t* dims, const int64_t* strides, const int* box);
 
 // Tiled tensor map for bulk tensor STORES of plain f32 from a 128-byte-swizzled staging tile (inner box
 // extent 32 floats).

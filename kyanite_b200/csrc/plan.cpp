@@ -981,15 +981,29 @@ class Planner {
         if (xc.ss.rank() != 3 || wc.ss.rank() != 3 || !gemm_fits_tensor_core(xc, wc) || xc.ss.strides[0] == 0 || wc.ss.strides[0] == 0)
             return std::nullopt;   // (the operands are planned either way; the matmul and the softmax stay two steps)
         PlanTensor values;
+        GemmOperand4D v4{};
+        bool values_mn = false;
         int64_t dv = 0;
         if (context >= 0) {
-            // V as [batch, keys, dv] with the keys contiguous (a transposed copy unless it is stored that way)
+            // V [batch, keys, dv]: a head split read in place or a tensor with its columns contiguous (the MN-major B
+            // operand of the context MMAs), or one with its keys contiguous (K-major); anything else gets a copy
             const int vin = g_.values[context].inputs[1];
-            values = k_major_b(visit(vin), vin);
-            dv = values.ss.shape[2];
-            const auto& st = values.ss.strides;
-            if (st[1] != 1 || st[2] % 4 != 0 || st[0] % 4 != 0 || (batch > 1 && st[0] == 0) || values.offset % 4 != 0)
-                return std::nullopt;   // (planned as separate steps; V stays planned)
+            dv = shape_of(vin)[2];
+            if (head_chain_operand(vin, false, DType::F32, &v4, &values, &ob, &orows, &ok_) && v4.kd == dv && ob == batch && orows == n) {
+                values_mn = true;
+            } else {
+                v4 = GemmOperand4D{};
+                values = visit(vin);
+                const auto& vs = values.ss.strides;
+                if (vs[2] == 1 && vs[1] % 4 == 0 && vs[0] % 4 == 0 && (batch == 1 || vs[0] != 0) && values.offset % 4 == 0) {
+                    values_mn = true;
+                } else {
+                    values = k_major_b(values, vin);
+                    const auto& st = values.ss.strides;
+                    if (st[1] != 1 || st[2] % 4 != 0 || st[0] % 4 != 0 || (batch > 1 && st[0] == 0) || values.offset % 4 != 0)
+                        return std::nullopt;   // (planned as separate steps; V stays planned)
+                }
+            }
         }
         if (context >= 0) {
             // the softmax and its matmul are part of this step: nothing else reads them (checked by the caller)
@@ -1012,9 +1026,15 @@ class Planner {
                 if (!b4.enabled) p.sb[i] = w.ss.strides[i];
                 p.sc[i] = out.ss.strides[i];
             }
-            p.values_strides[0] = values.ss.strides[0];   // V^T [batch][dv][keys]
-            p.values_strides[1] = values.ss.strides[2];
-            p.values_strides[2] = values.ss.strides[1];
+            p.values_mn = values_mn ? 1 : 0;
+            p.v4 = v4;
+            if (values_mn && !v4.enabled) {
+                for (int i = 0; i < 3; i++) p.values_strides[i] = values.ss.strides[i];   // V [batch][keys][dv]
+            } else if (!values_mn) {
+                p.values_strides[0] = values.ss.strides[0];   // V^T [batch][dv][keys]
+                p.values_strides[1] = values.ss.strides[2];
+                p.values_strides[2] = values.ss.strides[1];
+            }
             p.values_cols = dv;
             p.splits = 1;
             p.row_softmax = 2;
@@ -1022,8 +1042,12 @@ class Planner {
             s.flops = 2.0 * (double)batch * (double)m * (double)n * (double)(k + dv);
             s.desc = "attention b=" + std::to_string(batch) + " m=" + std::to_string(m) + " keys=" + std::to_string(n) + " k=" + std::to_string(k) +
                      " dv=" + std::to_string(dv) + " tf32 (scores and probabilities stay in tensor memory)";
-            if (a4.enabled || b4.enabled)
-                s.desc += std::string(" (head split read in place: operand") + (a4.enabled && b4.enabled ? "s a, b" : (a4.enabled ? " a" : " b")) + ")";
+            if (a4.enabled || b4.enabled || v4.enabled) {
+                std::string which;
+                for (const char* name : {a4.enabled ? "a" : "", b4.enabled ? "b" : "", v4.enabled ? "v" : ""})
+                    if (*name) which += (which.empty() ? "" : ", ") + std::string(name);
+                s.desc += std::string(" (head split read in place: operand") + (which.size() > 1 ? "s " : " ") + which + ")";
+            }
             push_step(std::move(s));
             return out;
         }
