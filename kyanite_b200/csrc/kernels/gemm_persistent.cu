@@ -406,7 +406,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                     for (int j = 0; j < 32; j++) v[j] = __float_as_uint(fmaxf(__uint_as_float(v[j]), 0.f));
                 } else if (p.act == (int)Activation::Gelu) {
 #pragma unroll
-                    for (int j = 0; j < 32; j++) v[j] = __float_as_uint(apply_activation(__uint_as_float(v[j]), (int)Activation::Gelu));
+                    for (int j = 0; j < 32; j++) v[j] = __float_as_uint(gelu_erf_tensor_core(__uint_as_float(v[j])));
                 }
                 // the staging tile about to be written was handed to the copy engine two chunks ago
                 if (issuer) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
