@@ -28,6 +28,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <memory>
 #include <mutex>
@@ -484,6 +485,10 @@ int classify_addend(const float* ptr, const int64_t* st) {
 
 // Column blocks of equal width: n = 320 is two blocks of 160, not 256 + 64 with three quarters of the second empty.
 int gemm_persistent_bn(int64_t n) {
+    if (const char* e = getenv("KN_GEMM_BN")) {   // (measuring: a fixed block width, a multiple of 32)
+        const int v = atoi(e);
+        if (v >= 32 && v <= 256 && v % 32 == 0 && n >= v) return v;
+    }
     const int64_t blocks = (n + 255) / 256;
     // (several blocks: a multiple of 32, the width of an epilogue chunk, so that no chunk reaches into the
     // next block's columns; a single block is clipped by the store's tensor bounds)

@@ -928,16 +928,30 @@ class Planner {
         const ValueInfo& si = g_.values[v];
         if (si.dtype != DType::F32 || opts_.math_mode != KN_MATH_TF32 || (opts_.flags & KN_FLAG_NO_PERSISTENT_GEMM)) return -1;
         if (shape_of(v).size() != 3 || si.axis != 2) return -1;
-        int y = si.inputs[0];
-        if (g_.values[y].op == OpKind::Binary && g_.values[y].binary_op == BinaryOp::Mul && fusable(y) && !map_[y]) {
-            const ValueInfo& mi = g_.values[y];
-            auto c0 = g_.as_single_const(mi.inputs[0]), c1 = g_.as_single_const(mi.inputs[1]);
-            if (!c0 && !c1) return -1;
-            y = c0 ? mi.inputs[1] : mi.inputs[0];
-        }
+        float scale = 1.0f;
+        const int y = peel_positive_scale(si.inputs[0], &scale);
+        if (y < 0) return -1;
         const ValueInfo& ci = g_.values[y];
         if (ci.op != OpKind::MatMul || ci.dtype != DType::F32 || !fusable(y) || map_[y] || shape_of(y) != shape_of(v)) return -1;
         return ci.inputs[0];
+    }
+
+    // `y`, or what `y` scales if it is x * c, c * x or x / c with a positive finite constant c that only this expression
+    // reads (the attention kernels take the row maximum before scaling); -1 if it scales by anything else.
+    int peel_positive_scale(int y, float* scale) {
+        const ValueInfo& mi = g_.values[y];
+        if (mi.op != OpKind::Binary || !fusable(y) || map_[y]) return y;
+        if (mi.binary_op != BinaryOp::Mul && mi.binary_op != BinaryOp::Div) return y;
+        auto c0 = g_.as_single_const(mi.inputs[0]), c1 = g_.as_single_const(mi.inputs[1]);
+        float c;
+        int other;
+        if (c1) c = c1->as_f32(), other = mi.inputs[0];
+        else if (c0 && mi.binary_op == BinaryOp::Mul) c = c0->as_f32(), other = mi.inputs[1];
+        else return -1;
+        if (mi.binary_op == BinaryOp::Div) c = 1.0f / c;
+        if (!(c > 0.0f) || !std::isfinite(c)) return -1;
+        *scale = c;
+        return other;
     }
 
     std::optional<PlanTensor> plan_attention(int v, int context) {
@@ -945,21 +959,9 @@ class Planner {
         if (si.dtype != DType::F32 || opts_.math_mode != KN_MATH_TF32 || (opts_.flags & KN_FLAG_NO_PERSISTENT_GEMM)) return std::nullopt;
         const std::vector<int64_t> shape = shape_of(v);
         if (shape.size() != 3 || si.axis != 2) return std::nullopt;
-        int y = si.inputs[0];
         float scale = 1.0f;
-        if (g_.values[y].op == OpKind::Binary && g_.values[y].binary_op == BinaryOp::Mul && fusable(y) && !map_[y]) {
-            const ValueInfo& mi = g_.values[y];
-            int other = -1;
-            for (int side = 0; side < 2; side++) {
-                auto c = g_.as_single_const(mi.inputs[side]);
-                if (c && other < 0) {
-                    scale = c->as_f32();
-                    other = mi.inputs[1 - side];
-                }
-            }
-            if (other < 0 || !(scale > 0.0f) || !std::isfinite(scale)) return std::nullopt;   // (the kernel takes the maximum before scaling)
-            y = other;
-        }
+        const int y = peel_positive_scale(si.inputs[0], &scale);
+        if (y < 0) return std::nullopt;
         const ValueInfo& ci = g_.values[y];
         if (ci.op != OpKind::MatMul || ci.dtype != DType::F32 || !fusable(y) || map_[y] || shape_of(y) != shape) return std::nullopt;
         const int64_t batch = shape[0], m = shape[1], n = shape[2];

@@ -92,7 +92,7 @@ def test_matches_oracle(name, project):
 # (kernels/attn_softmax.cu: the scores stay in tensor memory.  The reference runs the matmul, the scaling and the
 # softmax as three operations: kn-cuda-eval/src/planner.rs:300-330 and 560-600.)
 
-def scores_graph(b, m, n, k, scale=0.125, seed=0, constant_keys=False):
+def scores_graph(b, m, n, k, scale=0.125, seed=0, constant_keys=False, divide=False):
     """softmax(scale * q . keys^T) over the last axis: q [b, m, k] and keys [b, n, k] (K-contiguous, as attention has them)."""
     g = Graph()
     q = g.input(shape(b, m, k))
@@ -102,7 +102,7 @@ def scores_graph(b, m, n, k, scale=0.125, seed=0, constant_keys=False):
         keys = g.input(shape(b, n, k))
     scores = g.batched_mat_mul(q, g.permute(keys, [0, 2, 1]))
     if scale is not None:
-        scores = g.mul(scores, g.scalar(scale))
+        scores = g.div(scores, g.scalar(1.0 / scale)) if divide else g.mul(scores, g.scalar(scale))
     g.output(g.softmax(scores, 2))
     return g
 
@@ -145,6 +145,8 @@ def test_scores_route(name):
     b, m, n, k, scale = SCORE_SHAPES[name]
     assert len(fused_steps(scores_graph(b, m, n, k, scale))) == 1
     assert len(fused_steps(scores_graph(b, m, n, k, scale, constant_keys=True))) == 1
+    if scale is not None:
+        assert len(fused_steps(scores_graph(b, m, n, k, scale, divide=True))) == 1   # scores / sqrt(d), as exported graphs spell it
 
 
 @pytest.mark.parametrize("case", ["negative_scale", "few_rows", "too_many_keys", "keys_not_a_chunk_multiple", "masked", "softmax_over_rows",
@@ -198,6 +200,19 @@ def test_scores_match_oracle(name, constant_keys):
     with CudaExecutor(0, g, 0, math_mode=MATH_TF32, flags=FLAG_NO_PERSISTENT_GEMM) as ex:
         other = ex.evaluate(inputs)
     assert_tensors_match(other, got, 1e-5, 1e-4, abs_scaled=True)
+
+
+@pytest.mark.gpu
+def test_scores_divided_by_a_constant_match_oracle():
+    from kyanite_b200.executor import CudaExecutor
+    b, m, n, k = 2, 256, 192, 64
+    g = scores_graph(b, m, n, k, 0.125, divide=True)
+    r = rng(8)
+    inputs = [r.standard_normal((b, m, k)).astype(np.float32), r.standard_normal((b, n, k)).astype(np.float32)]
+    expected = cpu_eval_graph(g.to_bytes(), 0, inputs)
+    with CudaExecutor(0, g, 0, math_mode=MATH_TF32) as ex:
+        got = ex.evaluate(inputs)
+    assert_tensors_match(expected, got, 2e-2, 2e-2, abs_scaled=True)
 
 
 @pytest.mark.gpu
