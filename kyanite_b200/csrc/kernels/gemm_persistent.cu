@@ -28,6 +28,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <memory>
@@ -49,6 +50,7 @@ constexpr int kGpThreads = 192;
 constexpr int kGpBlockM = 128;
 constexpr int kGpBlockK = 32;
 constexpr int kGpATileBytes = kGpBlockM * 128;
+constexpr int kGpClockTiles = 16;
 constexpr int kGpStageTileBytes = 128 * 128;   // epilogue staging: 128 rows x 32 columns of f32
 
 struct GemmPersistentParams {
@@ -71,6 +73,7 @@ struct GemmPersistentParams {
     int32_t out_half;                // f16 storage and no split: the output tile is f16 (else f32: plain C or partial sums)
     uint32_t* status;
     volatile uint32_t* dbg;          // null, or 8 progress words in pinned host memory (KN_FLAG_TRACE_GEMM)
+    long long* clocks;               // KN_GEMM_CLOCKS only: 8 clock64 stamps per tile of CTA 0, in pinned host memory
 };
 
 // Post-mortem aid: with KN_FLAG_TRACE_GEMM the first CTA records how far each role got (words: 0 kernel entered,
@@ -256,9 +259,12 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         bool ok = true;
         for (int t = worker; t < p.total_tiles && ok; t += n_workers, local++) {
             const int buf = local & 1;
+            const bool clk = p.clocks != nullptr && blockIdx.x == 0 && local < kGpClockTiles;
+            if (clk) p.clocks[local * 8 + 0] = clock64();
             // the epilogue has drained this accumulator (its previous use was tile local - 2)
             if (local >= 2 && !mbar_wait(acc_empty + 8u * buf, (uint32_t)(((local >> 1) - 1) & 1), abandon, p.status, 22)) break;
             tc_fence_after();
+            if (clk) p.clocks[local * 8 + 1] = clock64();
             const uint32_t acc = tmem_base + (uint32_t)(buf * p.bn);
             int mt, nt, bt, sp;
             tile_coords(t, mt, nt, bt, sp);
@@ -267,6 +273,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             if (t + n_workers >= p.total_tiles) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
             for (int k = 0; k < k_count; k++) {
                 if (!mbar_wait(full_bar + 8u * s, (uint32_t)(round & 1), abandon, p.status, 23)) { ok = false; break; }
+                if (clk && k == 0) p.clocks[local * 8 + 2] = clock64();
                 dbg_mark(p, 2, (uint32_t)(k + 1));
                 tc_fence_after();
                 const uint32_t a_addr = base + (uint32_t)s * stage_bytes;
@@ -287,6 +294,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             if (ok) {
                 if (PAIR) mma_commit_pair(acc_full + 8u * buf);
                 else mma_commit(acc_full + 8u * buf);
+                if (clk) p.clocks[local * 8 + 3] = clock64();
             }
         }
     } else if (warp >= 2) {
@@ -324,6 +332,9 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 while (!mbar_try_wait(acc_full + 8u * buf, (uint32_t)((local >> 1) & 1))) {}
             }
             tc_fence_after();
+            const bool eclk = p.clocks != nullptr && blockIdx.x == 0 && local < kGpClockTiles && issuer;
+            long long store_wait = 0;
+            if (eclk) p.clocks[local * 8 + 4] = clock64();
             if (issuer) dbg_mark(p, 4, 1);
             const int64_t row = (int64_t)mt * kGpBlockM + row_in_tile;
             const bool row_ok = row < p.m;
@@ -410,7 +421,11 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                     for (int j = 0; j < 32; j++) v[j] = __float_as_uint(gelu_erf_tensor_core(__uint_as_float(v[j])));
                 }
                 // the staging tile about to be written was handed to the copy engine two chunks ago
-                if (issuer) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                if (issuer) {
+                    const long long t0 = eclk ? clock64() : 0;
+                    asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                    if (eclk) store_wait += clock64() - t0;
+                }
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (HALF && p.out_half) {
                     // f16 output: rows of 32 halves = 64 bytes, plain row-major (the store map has no swizzle)
@@ -444,6 +459,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 }
                 stage_buf ^= 1;
             }
+            if (eclk) p.clocks[local * 8 + 5] = clock64(), p.clocks[local * 8 + 6] = store_wait;
             // every tcgen05.ld of this accumulator has completed (tmem_load_32 waits): the MMA thread may reuse it
             tc_fence_before();
             if (PAIR) mbar_arrive_cluster(map_to_cta(acc_empty + 8u * buf, 0));
@@ -554,6 +570,24 @@ std::shared_ptr<void> gemm_persistent_prepare(const GemmParams& g, uint32_t* sta
     p.act = split ? 0 : g.act;
     p.status = status_word;
     p.dbg = (volatile uint32_t*)trace_words;
+    // KN_GEMM_CLOCKS=1 in the environment: CTA 0 stamps clock64 per tile (MMA thread: tile reached, accumulator free,
+    // first K block landed, all MMAs issued; copy-engine thread of the epilogue: accumulator ready, tile stored, cycles
+    // spent waiting for staging tiles) and the table of the last launch is printed when the process exits.
+    if (getenv("KN_GEMM_CLOCKS")) {
+        static long long* table = nullptr;
+        if (!table && cudaHostAlloc((void**)&table, (size_t)kGpClockTiles * 64, cudaHostAllocMapped) == cudaSuccess) {
+            atexit([] {
+                const long long* d = table;
+                fprintf(stderr, "gemm_persistent_kernel, CTA 0, SM clock cycles since the MMA thread reached the tile\n"
+                                "tile  accumulator_free  first_block_landed  mmas_issued  | accumulator_ready  tile_stored  (staging waits)  | period\n");
+                for (int i = 0; i < kGpClockTiles && d[i * 8 + 3]; i++)
+                    fprintf(stderr, "%4d  %16lld  %18lld  %11lld  | %17lld  %11lld  %15lld  | %6lld\n", i, d[i * 8 + 1] - d[i * 8], d[i * 8 + 2] - d[i * 8],
+                            d[i * 8 + 3] - d[i * 8], d[i * 8 + 4] - d[i * 8], d[i * 8 + 5] - d[i * 8], d[i * 8 + 6], i ? d[i * 8] - d[(i - 1) * 8] : 0);
+            });
+        }
+        if (table) memset(table, 0, (size_t)kGpClockTiles * 64);
+        p.clocks = table;
+    }
     const int stage_bytes = kGpATileBytes + (pair ? p.bn / 2 : p.bn) * 128;
     const int fixed = 1024 + 2 * kGpStageTileBytes + 16 * 8 + 64 + 64;
     p.stages = std::max(2, std::min(6, (227 * 1024 - fixed) / stage_bytes));
