@@ -315,6 +315,103 @@ __global__ void __launch_bounds__(TPR > 256 ? TPR : 256) layernorm_vec4_kernel(c
     }
 }
 
+// A row too long for one block's registers (a group norm over a few groups of a large feature map: 64 rows of 81 920
+// or 122 880 elements in the UNet-shaped graph): a thread-block cluster of CL CTAs takes the row, each CTA keeps a
+// CL-th of it in registers, and the two statistics meet through distributed shared memory (every CTA publishes its
+// partial sum in its own shared memory, a cluster barrier, every CTA adds the CL partials in the same order).  One
+// read and one write of the row on CL times as many SMs as rows, where the streaming kernel sweeps global memory three
+// times with one CTA per row (64 CTAs on 148 SMs: 218 GB/s measured).
+template <int CL, int ITEMS4>
+__global__ void __launch_bounds__(512) layernorm_cluster_kernel(const __grid_constant__ RowParams p) {
+    pdl_enter();
+    __shared__ float smem[32];
+    __shared__ float partial[2];
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    const int64_t row = (int64_t)(blockIdx.x / CL);
+    const int t = threadIdx.x;
+    int64_t oi = 0, oo = 0;
+    decode_offsets(row, p.outer_rank, p.outer_dims, p.in_strides, p.out_strides, oi, oo);
+    const int len4 = (int)(p.len >> 2);
+    const int part4 = (len4 + CL - 1) / CL;                 // float4s per CTA
+    const int begin = (int)rank * part4, end = min(len4, begin + part4);
+    const float4* in0 = (const float4*)(p.in0 + oi);
+    const float4* in1 = p.in1 ? (const float4*)(p.in1 + oi) : nullptr;
+    float4* out = (float4*)(p.out + oo);
+    // the sum of the CL partials, identical in every CTA of the cluster
+    auto cluster_sum = [&](float mine, int slot) -> float {
+        if (t == 0) partial[slot] = mine;
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        float total = 0.f;
+        const uint32_t local = (uint32_t)__cvta_generic_to_shared(&partial[slot]);
+#pragma unroll
+        for (uint32_t c = 0; c < (uint32_t)CL; c++) {
+            uint32_t remote;
+            float v;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(c));
+            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+            total += v;
+        }
+        return total;
+    };
+
+    float4 v[ITEMS4];
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < ITEMS4; i++) {
+        const int e = begin + i * 512 + t;
+        v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (e < end) {
+            const float4 a = __ldg(in0 + e);
+            v[i] = make_float4(p.alpha0 * a.x, p.alpha0 * a.y, p.alpha0 * a.z, p.alpha0 * a.w);
+            if (in1 != nullptr) {
+                const float4 b = __ldg(in1 + e);
+                v[i].x += p.alpha1 * b.x; v[i].y += p.alpha1 * b.y; v[i].z += p.alpha1 * b.z; v[i].w += p.alpha1 * b.w;
+            }
+        }
+        sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    }
+    const float n = (float)p.len;
+    const float mean = cluster_sum(row_reduce<512, false>(sum, smem), 0) / n;
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < ITEMS4; i++) {
+        const int e = begin + i * 512 + t;
+        v[i].x -= mean; v[i].y -= mean; v[i].z -= mean; v[i].w -= mean;
+        if (e < end) sq += (v[i].x * v[i].x + v[i].y * v[i].y) + (v[i].z * v[i].z + v[i].w * v[i].w);
+    }
+    const float var = cluster_sum(row_reduce<512, false>(sq, smem), 1) / n;
+    const float denom = sqrtf(var + p.eps);
+#pragma unroll
+    for (int i = 0; i < ITEMS4; i++) {
+        const int e = begin + i * 512 + t;
+        if (e < end) out[e] = make_float4(v[i].x / denom, v[i].y / denom, v[i].z / denom, v[i].w / denom);
+    }
+    // no CTA leaves while another may still read its partial sums
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+template <int CL, int ITEMS4>
+static int launch_layernorm_cluster(const RowParams& p, cudaStream_t stream) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(p.rows * CL));
+    cfg.blockDim = dim3(512);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = CL;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    return (int)cudaLaunchKernelEx(&cfg, layernorm_cluster_kernel<CL, ITEMS4>, p);
+}
+
 // Sum / mean of f32 over a contiguous innermost axis: TPO threads per output, float4 loads.
 template <int TPO>
 __global__ void __launch_bounds__(256) reduce_f32_rows_kernel(const __grid_constant__ ReduceParams p) {
@@ -528,6 +625,13 @@ int launch_layernorm(const RowParams& p, cudaStream_t stream) {
         else if (items <= 20) launch_pdl(layernorm_vec4_kernel<512, 20>, dim3(grid), dim3(512), (size_t)0, stream, p);
         else launch_pdl(layernorm_vec4_kernel<512, 24>, dim3(grid), dim3(512), (size_t)0, stream, p);
         return (int)cudaGetLastError();
+    }
+    // Longer rows, up to 8 x 49152 elements: a cluster of eight CTAs per row (see layernorm_cluster_kernel).
+    if (p.rows > 0 && p.rows <= (1 << 24) && p.len > 49152 && p.len <= 8 * 49152 && row_vec4_ok_len(p, 8 * 49152)) {
+        const int items = (int)(((p.len / 4 + 7) / 8 + 511) / 512);
+        if (items <= 8) return launch_layernorm_cluster<8, 8>(p, stream);
+        if (items <= 16) return launch_layernorm_cluster<8, 16>(p, stream);
+        return launch_layernorm_cluster<8, 24>(p, stream);
     }
     KN_ROW_DISPATCH(layernorm_cached_kernel, layernorm_vec4_kernel, layernorm_streaming_kernel, row_vec4_ok)
 }

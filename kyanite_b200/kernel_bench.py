@@ -72,6 +72,15 @@ def case_layernorm(rng):
     return g, 0, [rng.standard_normal((262144, 768)).astype(np.float32) for _ in range(2)]
 
 
+def case_layernorm_group(rng):
+    """A group norm of the UNet-shaped graph as the layernorm it is planned as: rows of 81 920
+    elements (64 per tensor there: 2 images x 32 groups; 1024 here, so that the 336 MB working set exceeds L2)."""
+    g = Graph()
+    x = g.input(shape(1024, 81920))
+    g.output(g.layernorm(x, 1, 1e-5))
+    return g, 0, [rng.standard_normal((1024, 81920)).astype(np.float32)]
+
+
 def case_reduce(rng):
     """RMSNorm statistic: mean of squares over the last axis of [65536, 4096]."""
     g = Graph()
@@ -249,6 +258,7 @@ CASES = {
     "softmax": case_softmax,
     "softmax_long": case_softmax_long,
     "layernorm": case_layernorm,
+    "layernorm_group": case_layernorm_group,
     "reduce": case_reduce,
     "gather": case_gather,
     "permute_copy": case_permute_copy,
