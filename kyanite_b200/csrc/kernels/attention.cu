@@ -9,8 +9,11 @@
 //
 //   warp 0 lane 0   producer: Q tile [128 x K] and the key matrix [n x K] as 128-byte-wide K blocks (128-byte swizzle,
 //                   rounded to TF32 by the copy engine) through 4-D tensor maps (an operand may be an attention head
-//                   split read in place, GemmOperand4D in kernels.h); when the score MMAs have completed, V^T
-//                   ([dv x n], keys contiguous) as 32-key blocks into the buffer the keys occupied
+//                   split read in place, GemmOperand4D in kernels.h); when the score MMAs have completed, V into the
+//                   buffer the keys occupied: either V itself ([n x dv], columns contiguous, possibly a head split
+//                   read in place too) as one [keys][128 B] tile per 32 columns, the MN-major B operand, which for
+//                   32-bit elements takes the 128-byte swizzle in 32-byte pieces; or V^T ([dv x n], keys contiguous)
+//                   as 32-key blocks, the K-major operand with the usual 128-byte swizzle
 //   warp 1 lane 0   MMA issuer.  Scores: per half of the keys and K block four tcgen05.mma.kind::tf32 (M 128, N <= 256).
 //                   Context: per 32 keys four MMAs (M 128, N dv, K 8) into columns [0, dv) of tensor memory, A = e.
 //                   Those columns held the scores of the first dv keys: their e goes through shared memory instead
