@@ -626,12 +626,22 @@ int launch_layernorm(const RowParams& p, cudaStream_t stream) {
         else launch_pdl(layernorm_vec4_kernel<512, 24>, dim3(grid), dim3(512), (size_t)0, stream, p);
         return (int)cudaGetLastError();
     }
-    // Longer rows, up to 8 x 49152 elements: a cluster of eight CTAs per row (see layernorm_cluster_kernel).
+    // Longer rows, up to 8 x 49152 elements: a cluster of two, four or eight CTAs per row (see layernorm_cluster_kernel).
+    // The smallest cluster whose slices fit in registers, unless that leaves SMs without a CTA (few rows: the group
+    // norms of a small batch), in which case a larger one.
     if (p.rows > 0 && p.rows <= (1 << 24) && p.len > 49152 && p.len <= 8 * 49152 && row_vec4_ok_len(p, 8 * 49152)) {
-        const int items = (int)(((p.len / 4 + 7) / 8 + 511) / 512);
-        if (items <= 8) return launch_layernorm_cluster<8, 8>(p, stream);
-        if (items <= 16) return launch_layernorm_cluster<8, 16>(p, stream);
-        return launch_layernorm_cluster<8, 24>(p, stream);
+        int cl = 8;
+        for (int c : {4, 2})
+            if ((p.len + c - 1) / c <= 49152 && p.rows * c >= 2 * 148) cl = c;
+        const int items = (int)(((p.len / 4 + cl - 1) / cl + 511) / 512);
+#define KN_LN_CLUSTER(CL)                                                          \
+        if (cl == CL) {                                                            \
+            if (items <= 8) return launch_layernorm_cluster<CL, 8>(p, stream);     \
+            if (items <= 16) return launch_layernorm_cluster<CL, 16>(p, stream);   \
+            return launch_layernorm_cluster<CL, 24>(p, stream);                    \
+        }
+        KN_LN_CLUSTER(2) KN_LN_CLUSTER(4) KN_LN_CLUSTER(8)
+#undef KN_LN_CLUSTER
     }
     KN_ROW_DISPATCH(layernorm_cached_kernel, layernorm_vec4_kernel, layernorm_streaming_kernel, row_vec4_ok)
 }

@@ -150,7 +150,7 @@ def test_softmax_with_scale_and_additive_term(rows, length, mask_kind):
 
 
 @pytest.mark.parametrize("rows,length", [(5, 8196), (64, 20480), (3, 40960), (2, 49152), (2, 49156), (2, 81920), (64, 81920), (3, 122880),
-                                         (5, 131076), (2, 393216), (2, 393220), (1, 49154)])
+                                         (5, 131076), (2, 393216), (2, 393220), (1, 49154), (160, 81920), (80, 122880), (300, 81920)])
 def test_layernorm_over_long_rows(rows, length):
     """Group-norm sized rows: 8193..49152 elements run on the one-block-per-row kernel with the row in
     registers (with a second input scaled into the first), up to eight times that on a cluster of eight CTAs per row
