@@ -333,3 +333,42 @@ def test_context_of_one_hot_rows_copies_values():
         got = ex.evaluate([q, keys, v])[0]
     want = np.stack([v[i].T[pick[i]] for i in range(b)])
     np.testing.assert_allclose(got, want, rtol=0, atol=2e-3)
+
+
+# ---------------------------------------------------------------- seeded random shapes through both attention kernels
+
+def _random_attention_shapes(count, seed):
+    r = rng(seed)
+    out = []
+    while len(out) < count:
+        b = int(r.integers(1, 7))
+        m = int(r.choice([128, 129, 160, 200, 256, 300, 384, 511, 640]))
+        n = 32 * int(r.integers(1, 17))
+        k = int(r.choice([32, 64, 96, 128]))
+        dv = int(r.choice([32, 64]))
+        if (128 + n) * k * 4 + 32768 + 3584 > 227 * 1024:
+            continue    # the kernels hold the Q tile and all keys of a head in shared memory
+        out.append((b, m, n, k, dv, float(r.choice([0.05, 0.125, 0.3, 1.0])), bool(r.integers(0, 2))))
+    return out
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("b,m,n,k,dv,scale,keys_contiguous", _random_attention_shapes(24, 77))
+def test_random_shapes_match_oracle(b, m, n, k, dv, scale, keys_contiguous):
+    """Both kernels on shapes nobody picked: the fused attention step where V fits (dv <= k), else scores + softmax
+    followed by a matmul; probabilities as a second output force the scores-only kernel."""
+    from kyanite_b200.executor import CudaExecutor
+    r = rng(b * 1000003 + m * 1009 + n * 31 + k + dv)
+    q = (r.standard_normal((b, m, k)) / math.sqrt(math.sqrt(k))).astype(np.float32)
+    keys = (r.standard_normal((b, n, k)) / math.sqrt(math.sqrt(k))).astype(np.float32)
+    v = r.standard_normal((b, dv, n) if keys_contiguous else (b, n, dv)).astype(np.float32)
+    for probabilities_output in (False, True):
+        g = context_graph(b, m, n, k, dv, scale=scale, values_keys_contiguous=keys_contiguous, probabilities_output=probabilities_output)
+        lines = steps(plan_describe(g, 0, MATH_TF32))
+        fused = any(" attention " in l for l in lines)
+        assert fused == (not probabilities_output and dv <= k), lines
+        assert fused or any("row softmax" in l for l in lines), lines
+        expected = cpu_eval_graph(g.to_bytes(), 0, [q, keys, v])
+        with CudaExecutor(0, g, 0, math_mode=MATH_TF32) as ex:
+            got = ex.evaluate([q, keys, v])
+        assert_tensors_match(expected, got, 6e-3, 6e-3, abs_scaled=True)
