@@ -222,7 +222,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         // that can give up: one lane waits, then all vote.
         auto wait_agreed = [&](uint32_t bar, uint32_t parity, uint32_t code) -> bool {
             uint32_t good = 1;
-            if (lane == 0) good = mbar_wait(bar, parity, abandon, p.status, code) ? 1u : 0u;
+            if (lane == 0) good = mbar_wait(bar, parity, abandon, p.status, code, kWaitCycles, kAtSleepNs) ? 1u : 0u;
             good = __shfl_sync(0xffffffffu, good, 0);
             uint32_t all_good;
             asm volatile(
