@@ -124,20 +124,26 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
         const uint32_t qk_bytes = q_bytes + (uint32_t)p.k_blocks * k_block_bytes;
         const uint32_t v_bytes = (uint32_t)chunks * v_block_bytes;
+        // Q of an item is requested a phase ahead of its keys: its buffer is free once the previous item's score MMAs
+        // have read it, the keys' only when that item's context MMAs have read V.  One barrier takes both.
+        auto request_q = [&](int item) {
+            const int ibt = item / p.m_tiles, imt = item - ibt * p.m_tiles;
+            mbar_expect_tx(full_qk, qk_bytes);
+            for (int kb = 0; kb < p.k_blocks; kb++)
+                tma_load_4d(base + (uint32_t)kb * (uint32_t)kAtBlockM * 128u, &map_q, full_qk, kb * 32, imt * kAtBlockM, ibt % p.a_bi, ibt / p.a_bi);
+        };
+        if ((int)blockIdx.x < p.total) request_q((int)blockIdx.x);
         int local = 0;
         for (int t = blockIdx.x; t < p.total; t += gridDim.x, local++) {
-            const int bt = t / p.m_tiles, mt = t - bt * p.m_tiles;
-            // the context MMAs of the previous item have read V^T (and the score MMAs before them Q)
+            const int bt = t / p.m_tiles;
+            // the context MMAs of the previous item have read V
             if (local > 0 && !mbar_wait(pv_done, (uint32_t)((local - 1) & 1), abandon, p.status, 41, kWaitCycles, kAtSleepNs)) break;
             if (p.trace && blockIdx.x == 0 && local < kAtTraceItems) p.trace[local * 8 + 0] = clock64();
-            mbar_expect_tx(full_qk, qk_bytes);
-            const int a2 = bt % p.a_bi, a3 = bt / p.a_bi, b2 = bt % p.b_bi, b3 = bt / p.b_bi;
-            for (int kb = 0; kb < p.k_blocks; kb++) {
-                tma_load_4d(base + (uint32_t)kb * (uint32_t)kAtBlockM * 128u, &map_q, full_qk, kb * 32, mt * kAtBlockM, a2, a3);
+            const int b2 = bt % p.b_bi, b3 = bt / p.b_bi;
+            for (int kb = 0; kb < p.k_blocks; kb++)
                 for (int h = 0; h < p.halves; h++)
                     tma_load_4d(k_base + (uint32_t)kb * k_block_bytes + (uint32_t)(h * p.half_n) * 128u, &map_k, full_qk, kb * 32,
                                 h * p.half_n, b2, b3);
-            }
             // the score MMAs have read the keys: V^T takes their place while the epilogue works on the scores
             if (!mbar_wait(s_done, (uint32_t)(local & 1), abandon, p.status, 42, kWaitCycles, kAtSleepNs)) break;
             mbar_expect_tx(full_v, v_bytes);
@@ -151,6 +157,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             } else {
                 for (int c = 0; c < chunks; c++) tma_load_4d(k_base + (uint32_t)c * v_block_bytes, &map_v, full_v, c * 32, 0, bt, 0);
             }
+            if (t + (int)gridDim.x < p.total) request_q(t + (int)gridDim.x);
         }
     } else if (warp == 1 && lane == 0) {
         // ---------------- MMA issuer: f32 accumulate, TF32 x TF32, both K-major, M = 128
