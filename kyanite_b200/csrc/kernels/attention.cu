@@ -86,8 +86,8 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     const uint32_t e_base = k_base + (uint32_t)p.k_blocks * k_block_bytes;           // e of the first dv keys / transposing tiles
     const uint32_t bar_base = e_base + (uint32_t)kAtStagingBytes;
     const uint32_t full_qk = bar_base, s_done = bar_base + 8u, full_v = bar_base + 16u, e_ready = bar_base + 24u;
-    const uint32_t pv_done = bar_base + 32u, acc_empty = bar_base + 40u;
-    const uint32_t slot_addr = bar_base + 48u;
+    const uint32_t pv_done = bar_base + 32u, acc_empty = bar_base + 40u, full_k1 = bar_base + 48u;
+    const uint32_t slot_addr = bar_base + 64u;
     volatile uint32_t* tmem_slot = (volatile uint32_t*)(gen_base + (slot_addr - base));
     volatile int* abandon = (volatile int*)(gen_base + (slot_addr + 4u - base));
     float* exchange_max = (float*)(gen_base + (slot_addr + 16u - base));   // [2 groups][128 rows]: the maximum over a group's columns
@@ -96,6 +96,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         mbar_init(full_qk, 1);
+        mbar_init(full_k1, 1);
         mbar_init(s_done, 1);
         mbar_init(full_v, 1);
         mbar_init(e_ready, 256);
@@ -122,7 +123,10 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
-        const uint32_t qk_bytes = q_bytes + (uint32_t)p.k_blocks * k_block_bytes;
+        // (the second half of the keys, if the score MMAs take them in two halves, has a barrier of its own: the MMAs over
+        // the first half run while it lands)
+        const uint32_t half_bytes = (uint32_t)p.k_blocks * (uint32_t)p.half_n * 128u;
+        const uint32_t qk_bytes = q_bytes + half_bytes;
         const uint32_t v_bytes = (uint32_t)chunks * v_block_bytes;
         // Q of an item is requested a phase ahead of its keys: its buffer is free once the previous item's score MMAs
         // have read it, the keys' only when that item's context MMAs have read V.  One barrier takes both.
@@ -140,10 +144,11 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             if (local > 0 && !mbar_wait(pv_done, (uint32_t)((local - 1) & 1), abandon, p.status, 41, kWaitCycles, kAtSleepNs)) break;
             if (p.trace && blockIdx.x == 0 && local < kAtTraceItems) p.trace[local * 8 + 0] = clock64();
             const int b2 = bt % p.b_bi, b3 = bt / p.b_bi;
-            for (int kb = 0; kb < p.k_blocks; kb++)
-                for (int h = 0; h < p.halves; h++)
-                    tma_load_4d(k_base + (uint32_t)kb * k_block_bytes + (uint32_t)(h * p.half_n) * 128u, &map_k, full_qk, kb * 32,
-                                h * p.half_n, b2, b3);
+            if (p.halves > 1) mbar_expect_tx(full_k1, half_bytes);
+            for (int h = 0; h < p.halves; h++)
+                for (int kb = 0; kb < p.k_blocks; kb++)
+                    tma_load_4d(k_base + (uint32_t)kb * k_block_bytes + (uint32_t)(h * p.half_n) * 128u, &map_k, h == 0 ? full_qk : full_k1,
+                                kb * 32, h * p.half_n, b2, b3);
             // the score MMAs have read the keys: V^T takes their place while the epilogue works on the scores
             if (!mbar_wait(s_done, (uint32_t)(local & 1), abandon, p.status, 42, kWaitCycles, kAtSleepNs)) break;
             mbar_expect_tx(full_v, v_bytes);
@@ -179,7 +184,13 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             tc_fence_after();
             if (p.trace && blockIdx.x == 0 && local < kAtTraceItems) p.trace[local * 8 + 2] = clock64();
             if (t + (int)gridDim.x >= p.total) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-            for (int h = 0; h < p.halves; h++) {
+            bool landed = true;
+            for (int h = 0; h < p.halves && landed; h++) {
+                if (h == 1) {
+                    landed = mbar_wait(full_k1, (uint32_t)(local & 1), abandon, p.status, 43, kWaitCycles, kAtSleepNs);
+                    if (!landed) break;
+                    tc_fence_after();
+                }
                 const uint32_t acc = tmem_base + (uint32_t)(h * p.half_n);
                 for (int kb = 0; kb < p.k_blocks; kb++) {
                     const uint64_t da = smem_desc_sw128(base + (uint32_t)kb * (uint32_t)kAtBlockM * 128u);
@@ -188,6 +199,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     for (int j = 0; j < 4; j++) mma_tf32(acc, da + 2u * j, db + 2u * j, idesc_s, (kb | j) != 0 ? 1u : 0u);
                 }
             }
+            if (!landed) break;
             mma_commit(s_done);
             // context: O[128 x dv] = e[128 x n] . V[n x dv]
             if (!mbar_wait(full_v, (uint32_t)(local & 1), abandon, p.status, 45, kWaitCycles, kAtSleepNs)) break;
