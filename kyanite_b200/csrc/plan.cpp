@@ -798,6 +798,9 @@ class Planner {
         }
         if (chain_end(curr) < 0) return std::nullopt;
         while (!is_contraction(curr)) {
+            // (a node below the root that is planned already, as one of several projections computed by one matmul,
+            // is read, not recomputed)
+            if (curr != root && map_[curr]) return std::nullopt;
             const ValueInfo& ci = g_.values[curr];
             if (ci.op == OpKind::View) {
                 curr = ci.inputs[0];
@@ -811,6 +814,7 @@ class Planner {
                 curr = cont;
             }
         }
+        if (curr != root && map_[curr]) return std::nullopt;
         e.contraction = curr;
         return e;
     }
@@ -895,7 +899,14 @@ class Planner {
             *batch = 1; *rows = c->B * c->S; *k = c->H * c->D;
         }
         PlanTensor t = visit(c->src);
-        if (!t.ss.has_simple_strides() || t.offset % align != 0) return false;   // (the source is planned either way)
+        if (t.offset % align != 0) return false;   // (the source is planned either way)
+        if (!t.ss.has_simple_strides()) {
+            // a head split of a column slice of a wider matrix (one of several projections computed as one matmul):
+            // the rows are further apart, nothing else changes
+            if (c->merge || t.ss.rank() != 2 || t.ss.strides[1] != 1 || t.ss.strides[0] < c->H * c->D || t.ss.strides[0] % align != 0) return false;
+            o.strides[1] = t.ss.strides[0];
+            o.strides[3] = c->S * t.ss.strides[0];
+        }
         *out = o;
         *source = t;
         return true;
@@ -1084,7 +1095,152 @@ class Planner {
         return out;
     }
 
+    // ---------------------------------------------------------------- projections of one tensor as one matmul
+    // x . W1 + b1, x . W2 + b2, ... (the query / key / value projections of an attention block) with constant weights
+    // and biases: ONE matmul x . [W1 W2 ...] + [b1 b2 ...] into one buffer of which every projection is a column
+    // slice.  Three matmuls of 16384 x 768 x 768 are 2.6 rounds of tiles each on 74 CTA pairs, with the first loads and
+    // the last epilogue exposed three times; one of 16384 x 2304 x 768 is 7.8 rounds.  The weights and biases are
+    // concatenated here, on the host, once.
+    struct Projection {
+        int root, matmul;
+        PlanTensor weight, bias;   // constants: [1, K, N] and anything that broadcasts to [1, 1, N]
+        int64_t n;
+    };
+    // a constant seen through operations that only edit strides: planning it emits no step
+    bool is_constant_view(int v) const {
+        for (;;) {
+            const ValueInfo& vi = g_.values[v];
+            if (vi.op == OpKind::Constant) return true;
+            if (vi.op != OpKind::View && vi.op != OpKind::Permute && vi.op != OpKind::Broadcast && vi.op != OpKind::Slice && vi.op != OpKind::Flip)
+                return false;
+            v = vi.inputs[0];
+        }
+    }
+    std::optional<Projection> as_projection(int root, int x) {
+        if (map_[root] || g_.values[root].dtype != DType::F32) return std::nullopt;
+        auto e = match_epilogue(root);
+        if (!e || e->act != Activation::None || e->addends.size() != 1 || e->contraction == root) return std::nullopt;
+        const ValueInfo& ci = g_.values[e->contraction];
+        if (ci.op != OpKind::MatMul || ci.dtype != DType::F32 || map_[e->contraction] || ci.inputs[0] != x) return std::nullopt;
+        // [1, M, N] out of the matmul; the sum may be over a view of it that keeps the columns ([M, N])
+        const std::vector<int64_t> shape = shape_of(e->contraction), rs = shape_of(root);
+        int64_t root_elems = 1;
+        for (int64_t d : rs) root_elems *= d;
+        if (shape.size() != 3 || shape[0] != 1 || rs.empty() || rs.back() != shape[2] || root_elems != shape[1] * shape[2]) return std::nullopt;
+        if (!is_constant_view(ci.inputs[1]) || !is_constant_view(e->addends[0])) return std::nullopt;
+        Projection p;
+        p.root = root;
+        p.matmul = e->contraction;
+        p.n = shape[2];
+        p.weight = visit(ci.inputs[1]);
+        p.bias = visit(e->addends[0]);
+        auto is_host_const = [&](const PlanTensor& t) {
+            const BufferInfo& b = plan_.buffers[t.buf];
+            return b.kind == BufKind::Const && b.host_data != nullptr && t.dtype == DType::F32;
+        };
+        if (!is_host_const(p.weight) || !is_host_const(p.bias) || p.weight.ss.rank() != 3 || p.n % 4 != 0) return std::nullopt;
+        // the bias must be one value per column
+        const std::vector<int64_t>& bs = p.bias.ss.shape;
+        if (bs.empty() || bs.back() != p.n) return std::nullopt;
+        for (size_t d = 0; d + 1 < bs.size(); d++)
+            if (bs[d] != 1 && p.bias.ss.strides[d] != 0) return std::nullopt;
+        return p;
+    }
+
+    std::optional<PlanTensor> try_merged_projections(int root) {
+        if (opts_.math_mode != KN_MATH_TF32 || (opts_.flags & KN_FLAG_NO_PERSISTENT_GEMM)) return std::nullopt;
+        auto head = match_epilogue(root);
+        if (!head || head->contraction == root || g_.values[head->contraction].op != OpKind::MatMul) return std::nullopt;
+        const int x = g_.values[head->contraction].inputs[0];
+        auto first = as_projection(root, x);
+        if (!first) return std::nullopt;
+        const std::vector<int64_t> xs = shape_of(x);
+        const int64_t m = xs[1], k = xs[2];
+        if (m < 256 || k % 4 != 0) return std::nullopt;
+        // the other projections of x: an Add over a MatMul of x that nothing else reads
+        std::vector<Projection> all{*first};
+        for (int v = 0; v < (int)g_.values.size() && all.size() < 8; v++) {
+            const ValueInfo& vi = g_.values[v];
+            if (v == root || vi.op != OpKind::Binary || vi.binary_op != BinaryOp::Add || map_[v]) continue;
+            // (the same matmul seen from a view above its sum is not another projection)
+            bool seen = false;
+            if (auto e = match_epilogue(v))
+                for (auto& have : all) seen = seen || have.matmul == e->contraction;
+            if (seen) continue;
+            if (auto p = as_projection(v, x)) all.push_back(*p);
+        }
+        if (all.size() < 2) return std::nullopt;
+        int64_t n_total = 0;
+        for (auto& p : all) n_total += p.n;
+        // only where the separate matmuls leave CTA pairs idle in their last round of 256 x 256 tiles
+        auto rounds = [&](int64_t n) { return (double)(((m + 255) / 256) * ((n + 255) / 256)) / 74.0; };
+        double separate = 0;
+        for (auto& p : all) separate += std::ceil(rounds(p.n));
+        if (std::ceil(rounds(n_total)) >= separate || n_total > (1 << 20)) return std::nullopt;
+        PlanTensor xt = visit(x);
+        if (xt.ss.rank() != 3 || xt.ss.strides[2] != 1 || !tma_stride_ok(m, xt.ss.strides[1]) || xt.offset % 4 != 0) return std::nullopt;
+        // [n_total][k] with k contiguous, and the biases side by side
+        auto wdata = std::make_shared<std::vector<uint8_t>>((size_t)(n_total * k) * 4);
+        auto bdata = std::make_shared<std::vector<uint8_t>>((size_t)n_total * 4);
+        float* wd = (float*)wdata->data();
+        float* bd = (float*)bdata->data();
+        int64_t col = 0;
+        for (auto& p : all) {
+            if (p.weight.ss.shape[1] != k || p.weight.ss.shape[2] != p.n) return std::nullopt;
+            const float* ws = (const float*)plan_.buffers[p.weight.buf].host_data + p.weight.offset;
+            const float* bs = (const float*)plan_.buffers[p.bias.buf].host_data + p.bias.offset;
+            const int64_t sk = p.weight.ss.strides[1], sn = p.weight.ss.strides[2], sb = p.bias.ss.strides.back();
+            for (int64_t j = 0; j < p.n; j++) {
+                for (int64_t i = 0; i < k; i++) wd[(col + j) * k + i] = ws[i * sk + j * sn];
+                bd[col + j] = bs[j * sb];
+            }
+            col += p.n;
+        }
+        PlanTensor w = alloc_const({1, n_total, k}, DType::F32, all[0].matmul, nullptr, wdata);
+        w = w.with(w.ss.permute({0, 2, 1}));                                  // logical [1, k, n_total], k contiguous
+        PlanTensor bias = alloc_const({1, 1, n_total}, DType::F32, all[0].root, nullptr, bdata);
+        bias = bias.with(StridedShape({1, m, n_total}, {0, 0, 1}));
+        PlanTensor out = alloc_shared({1, m, n_total}, DType::F32, root);
+        if (!gemm_fits_tensor_core(xt, w)) return std::nullopt;
+        Step s;
+        s.kind = StepKind::Gemm;
+        s.value = root;
+        s.tensor_core = true;
+        s.operands = {xt, w, out, bias};
+        s.writes = {0, 0, 1, 0};
+        GemmParams& p = s.gemm;
+        p.batch = 1;
+        p.m = m;
+        p.n = n_total;
+        p.k = k;
+        for (int i = 0; i < 3; i++) {
+            p.sa[i] = xt.ss.strides[i];
+            p.sb[i] = w.ss.strides[i];
+            p.sc[i] = out.ss.strides[i];
+            p.s1[i] = bias.ss.strides[i];
+        }
+        p.splits = 1;
+        s.flops = 2.0 * (double)m * (double)n_total * (double)k;
+        s.desc = "matmul b=1 m=" + std::to_string(m) + " n=" + std::to_string(n_total) + " k=" + std::to_string(k) + " +1 tf32 (" +
+                 std::to_string(all.size()) + " projections of one tensor)";
+        push_step(std::move(s));
+        // every projection is a column slice of the result, seen in the shape of its sum
+        col = 0;
+        PlanTensor mine;
+        for (auto& pr : all) {
+            PlanTensor slice = out.slice(2, col, col + pr.n, 1);
+            auto shaped = slice.ss.view(shape_of(pr.root));
+            KN_CHECK(shaped.has_value(), KN_ERR_INTERNAL, "column slice of merged projections is not viewable");
+            slice = slice.with(*shaped);
+            if (pr.root == root) mine = slice;
+            else map_[pr.root] = slice;
+            col += pr.n;
+        }
+        return mine;
+    }
+
     std::optional<PlanTensor> try_fused_contraction(int root) {
+        if (auto merged = try_merged_projections(root)) return *merged;
         auto m = match_epilogue(root);
         if (!m) return std::nullopt;
         const ValueInfo& ci = g_.values[m->contraction];
