@@ -903,9 +903,11 @@ class Planner {
         if (!t.ss.has_simple_strides()) {
             // a head split of a column slice of a wider matrix (one of several projections computed as one matmul):
             // the rows are further apart, nothing else changes
-            if (c->merge || t.ss.rank() != 2 || t.ss.strides[1] != 1 || t.ss.strides[0] < c->H * c->D || t.ss.strides[0] % align != 0) return false;
-            o.strides[1] = t.ss.strides[0];
-            o.strides[3] = c->S * t.ss.strides[0];
+            if (c->merge) return false;
+            auto rows = t.ss.view({c->B * c->S, c->H * c->D});   // (whatever leading axes the source has)
+            if (!rows || rows->strides[1] != 1 || rows->strides[0] < c->H * c->D || rows->strides[0] % align != 0) return false;
+            o.strides[1] = rows->strides[0];
+            o.strides[3] = c->S * rows->strides[0];
         }
         *out = o;
         *source = t;
@@ -1104,8 +1106,28 @@ class Planner {
     struct Projection {
         int root, matmul;
         PlanTensor weight, bias;   // constants: [1, K, N] and anything that broadcasts to [1, 1, N]
+        bool has_bias;
         int64_t n;
     };
+    // `v` is read, through any views / permutes / slices (the head split of an attention block), by matmuls only: no
+    // bias, residual or activation that would have been its epilogue
+    bool only_contraction_readers(int v) {
+        if (readers_.empty()) {
+            readers_.resize(g_.values.size());
+            for (int u = 0; u < (int)g_.values.size(); u++)
+                for (int in : g_.values[u].inputs) readers_[in].push_back(u);
+        }
+        for (int u : readers_[v]) {
+            const OpKind op = g_.values[u].op;
+            if (op == OpKind::View || op == OpKind::Permute || op == OpKind::Slice) {
+                if (!only_contraction_readers(u)) return false;
+            } else if (op != OpKind::MatMul) {
+                return false;
+            }
+        }
+        return true;
+    }
+    std::vector<std::vector<int>> readers_;
     // a constant seen through operations that only edit strides: planning it emits no step
     bool is_constant_view(int v) const {
         for (;;) {
@@ -1119,7 +1141,7 @@ class Planner {
     std::optional<Projection> as_projection(int root, int x) {
         if (map_[root] || g_.values[root].dtype != DType::F32) return std::nullopt;
         auto e = match_epilogue(root);
-        if (!e || e->act != Activation::None || e->addends.size() != 1 || e->contraction == root) return std::nullopt;
+        if (!e || e->act != Activation::None || e->addends.size() > 1) return std::nullopt;
         const ValueInfo& ci = g_.values[e->contraction];
         if (ci.op != OpKind::MatMul || ci.dtype != DType::F32 || map_[e->contraction] || ci.inputs[0] != x) return std::nullopt;
         // [1, M, N] out of the matmul; the sum may be over a view of it that keeps the columns ([M, N])
@@ -1127,18 +1149,21 @@ class Planner {
         int64_t root_elems = 1;
         for (int64_t d : rs) root_elems *= d;
         if (shape.size() != 3 || shape[0] != 1 || rs.empty() || rs.back() != shape[2] || root_elems != shape[1] * shape[2]) return std::nullopt;
-        if (!is_constant_view(ci.inputs[1]) || !is_constant_view(e->addends[0])) return std::nullopt;
         Projection p;
+        p.has_bias = !e->addends.empty();
+        if (!is_constant_view(ci.inputs[1]) || (p.has_bias && !is_constant_view(e->addends[0]))) return std::nullopt;
         p.root = root;
         p.matmul = e->contraction;
         p.n = shape[2];
         p.weight = visit(ci.inputs[1]);
-        p.bias = visit(e->addends[0]);
         auto is_host_const = [&](const PlanTensor& t) {
             const BufferInfo& b = plan_.buffers[t.buf];
             return b.kind == BufKind::Const && b.host_data != nullptr && t.dtype == DType::F32;
         };
-        if (!is_host_const(p.weight) || !is_host_const(p.bias) || p.weight.ss.rank() != 3 || p.n % 4 != 0) return std::nullopt;
+        if (!is_host_const(p.weight) || p.weight.ss.rank() != 3 || p.n % 4 != 0) return std::nullopt;
+        if (!p.has_bias) return p;
+        p.bias = visit(e->addends[0]);
+        if (!is_host_const(p.bias)) return std::nullopt;
         // the bias must be one value per column
         const std::vector<int64_t>& bs = p.bias.ss.shape;
         if (bs.empty() || bs.back() != p.n) return std::nullopt;
@@ -1150,7 +1175,7 @@ class Planner {
     std::optional<PlanTensor> try_merged_projections(int root) {
         if (opts_.math_mode != KN_MATH_TF32 || (opts_.flags & KN_FLAG_NO_PERSISTENT_GEMM)) return std::nullopt;
         auto head = match_epilogue(root);
-        if (!head || head->contraction == root || g_.values[head->contraction].op != OpKind::MatMul) return std::nullopt;
+        if (!head || g_.values[head->contraction].op != OpKind::MatMul) return std::nullopt;
         const int x = g_.values[head->contraction].inputs[0];
         auto first = as_projection(root, x);
         if (!first) return std::nullopt;
@@ -1161,7 +1186,10 @@ class Planner {
         std::vector<Projection> all{*first};
         for (int v = 0; v < (int)g_.values.size() && all.size() < 8; v++) {
             const ValueInfo& vi = g_.values[v];
-            if (v == root || vi.op != OpKind::Binary || vi.binary_op != BinaryOp::Add || map_[v]) continue;
+            // a sum over a matmul of x, or a matmul of x that is only re-described by its readers (no epilogue to lose)
+            const bool sum = vi.op == OpKind::Binary && vi.binary_op == BinaryOp::Add;
+            const bool bare = vi.op == OpKind::MatMul && vi.inputs[0] == x && only_contraction_readers(v);
+            if (v == root || !(sum || bare) || map_[v]) continue;
             // (the same matmul seen from a view above its sum is not another projection)
             bool seen = false;
             if (auto e = match_epilogue(v))
@@ -1177,6 +1205,10 @@ class Planner {
         double separate = 0;
         for (auto& p : all) separate += std::ceil(rounds(p.n));
         if (std::ceil(rounds(n_total)) >= separate || n_total > (1 << 20)) return std::nullopt;
+        // (a result of few tiles under a long reduction is cut along K by the planner: not here)
+        if (((m + 127) / 128) * ((n_total + 255) / 256) < 74 && k >= 512) return std::nullopt;
+        bool any_bias = false;
+        for (auto& p : all) any_bias = any_bias || p.has_bias;
         PlanTensor xt = visit(x);
         if (xt.ss.rank() != 3 || xt.ss.strides[2] != 1 || !tma_stride_ok(m, xt.ss.strides[1]) || xt.offset % 4 != 0) return std::nullopt;
         // [n_total][k] with k contiguous, and the biases side by side
@@ -1188,26 +1220,33 @@ class Planner {
         for (auto& p : all) {
             if (p.weight.ss.shape[1] != k || p.weight.ss.shape[2] != p.n) return std::nullopt;
             const float* ws = (const float*)plan_.buffers[p.weight.buf].host_data + p.weight.offset;
-            const float* bs = (const float*)plan_.buffers[p.bias.buf].host_data + p.bias.offset;
-            const int64_t sk = p.weight.ss.strides[1], sn = p.weight.ss.strides[2], sb = p.bias.ss.strides.back();
+            const float* bs = p.has_bias ? (const float*)plan_.buffers[p.bias.buf].host_data + p.bias.offset : nullptr;
+            const int64_t sk = p.weight.ss.strides[1], sn = p.weight.ss.strides[2], sb = p.has_bias ? p.bias.ss.strides.back() : 0;
             for (int64_t j = 0; j < p.n; j++) {
                 for (int64_t i = 0; i < k; i++) wd[(col + j) * k + i] = ws[i * sk + j * sn];
-                bd[col + j] = bs[j * sb];
+                bd[col + j] = bs ? bs[j * sb] : 0.0f;
             }
             col += p.n;
         }
         PlanTensor w = alloc_const({1, n_total, k}, DType::F32, all[0].matmul, nullptr, wdata);
         w = w.with(w.ss.permute({0, 2, 1}));                                  // logical [1, k, n_total], k contiguous
-        PlanTensor bias = alloc_const({1, 1, n_total}, DType::F32, all[0].root, nullptr, bdata);
-        bias = bias.with(StridedShape({1, m, n_total}, {0, 0, 1}));
+        PlanTensor bias;
+        if (any_bias) {
+            bias = alloc_const({1, 1, n_total}, DType::F32, all[0].root, nullptr, bdata);
+            bias = bias.with(StridedShape({1, m, n_total}, {0, 0, 1}));
+        }
         PlanTensor out = alloc_shared({1, m, n_total}, DType::F32, root);
         if (!gemm_fits_tensor_core(xt, w)) return std::nullopt;
         Step s;
         s.kind = StepKind::Gemm;
         s.value = root;
         s.tensor_core = true;
-        s.operands = {xt, w, out, bias};
-        s.writes = {0, 0, 1, 0};
+        s.operands = {xt, w, out};
+        s.writes = {0, 0, 1};
+        if (any_bias) {
+            s.operands.push_back(bias);
+            s.writes.push_back(0);
+        }
         GemmParams& p = s.gemm;
         p.batch = 1;
         p.m = m;
@@ -1217,11 +1256,11 @@ class Planner {
             p.sa[i] = xt.ss.strides[i];
             p.sb[i] = w.ss.strides[i];
             p.sc[i] = out.ss.strides[i];
-            p.s1[i] = bias.ss.strides[i];
+            if (any_bias) p.s1[i] = bias.ss.strides[i];
         }
         p.splits = 1;
         s.flops = 2.0 * (double)m * (double)n_total * (double)k;
-        s.desc = "matmul b=1 m=" + std::to_string(m) + " n=" + std::to_string(n_total) + " k=" + std::to_string(k) + " +1 tf32 (" +
+        s.desc = "matmul b=1 m=" + std::to_string(m) + " n=" + std::to_string(n_total) + " k=" + std::to_string(k) + (any_bias ? " +1" : " +0") + " tf32 (" +
                  std::to_string(all.size()) + " projections of one tensor)";
         push_step(std::move(s));
         // every projection is a column slice of the result, seen in the shape of its sum

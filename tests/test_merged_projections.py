@@ -40,7 +40,7 @@ def projections_graph(m, k, widths, seed=0, with_bias=True, second_input=False, 
     else:
         acc = None
         for y in outs:
-            t = g.mul(y, y)
+            t = g.relu(y) if consume == "relu" else g.mul(y, y)
             acc = t if acc is None else g.add(acc, t)
         g.output(acc)
     return g
@@ -55,6 +55,8 @@ def test_bert_layer_projects_queries_keys_and_values_at_once():
     lines = steps(plan_describe(g, 32, MATH_TF32))
     one = merged(lines)
     assert len(one) == 1 and "n=2304 k=768" in one[0] and "(3 projections of one tensor)" in one[0], lines
+    # with their biases: no elementwise step adds one afterwards (only the embedding sum is left as such a step)
+    assert sum(l.split()[2] == "Scalar" for l in lines) == 1, lines
     # the attention step reads the three column slices in place
     assert sum("head split read in place: operands a, b, v" in l for l in lines) == 1
     assert sum(" copy " in l for l in lines) == 0
@@ -62,9 +64,11 @@ def test_bert_layer_projects_queries_keys_and_values_at_once():
         assert not merged(steps(plan_describe(g, 32, mode, flags=flags)))
 
 
-@pytest.mark.parametrize("case", ["three_equal", "three_different", "two", "consumed_as_slices"])
+@pytest.mark.parametrize("case", ["three_equal", "three_different", "two", "consumed_as_slices", "no_bias"])
 def test_route(case):
-    if case == "three_equal":
+    if case == "no_bias":
+        g = projections_graph(2048, 256, [256, 256, 256], with_bias=False)    # (read through views only: nothing to fuse into)
+    elif case == "three_equal":
         g = projections_graph(2048, 256, [256, 256, 256])
     elif case == "three_different":
         g = projections_graph(2048, 256, [128, 256, 64])
@@ -77,10 +81,10 @@ def test_route(case):
     assert sum(l.split()[2].startswith("Gemm") for l in lines) == 1, lines
 
 
-@pytest.mark.parametrize("case", ["no_bias", "different_inputs", "one_projection", "few_rows", "no_gain"])
+@pytest.mark.parametrize("case", ["no_bias_into_an_activation", "different_inputs", "one_projection", "few_rows", "no_gain"])
 def test_stays_separate(case):
-    if case == "no_bias":
-        g = projections_graph(2048, 256, [256, 256, 256], with_bias=False)
+    if case == "no_bias_into_an_activation":
+        g = projections_graph(2048, 256, [256, 256, 256], with_bias=False, consume="relu")    # relu is each matmul's epilogue
     elif case == "different_inputs":
         g = projections_graph(2048, 256, [256, 256], second_input=True)
     elif case == "one_projection":
@@ -93,14 +97,15 @@ def test_stays_separate(case):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("with_bias", [True, False], ids=["bias", "no_bias"])
 @pytest.mark.parametrize("consume", ["outputs", "sum"])
 @pytest.mark.parametrize("m,k,widths", [(2048, 256, [256, 256, 256]), (2048, 256, [128, 256, 64]), (1000, 96, [32, 100, 64, 36]),
                                         (4096, 128, [256, 256])])
-def test_matches_oracle(m, k, widths, consume):
+def test_matches_oracle(m, k, widths, consume, with_bias):
     from kyanite_b200.executor import CudaExecutor
-    if consume == "sum" and len(set(widths)) > 1:
-        pytest.skip("the sum needs projections of equal width")
-    g = projections_graph(m, k, widths, seed=5, consume=consume)
+    if consume == "sum" and (len(set(widths)) > 1 or not with_bias):
+        pytest.skip("the sum needs projections of equal width (and reads the matmuls themselves when there is no bias)")
+    g = projections_graph(m, k, widths, seed=5, consume=consume, with_bias=with_bias)
     assert merged(steps(plan_describe(g, 0, MATH_TF32)))
     x = rng(6).standard_normal((m, k)).astype(np.float32)
     expected = cpu_eval_graph(g.to_bytes(), 0, [x])
