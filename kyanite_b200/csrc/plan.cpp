@@ -1111,12 +1111,17 @@ class Planner {
     };
     // `v` is read, through any views / permutes / slices (the head split of an attention block), by matmuls only: no
     // bias, residual or activation that would have been its epilogue
-    bool only_contraction_readers(int v) {
-        if (readers_.empty()) {
-            readers_.resize(g_.values.size());
-            for (int u = 0; u < (int)g_.values.size(); u++)
-                for (int in : g_.values[u].inputs) readers_[in].push_back(u);
+    void ensure_readers() {
+        if (!readers_.empty()) return;
+        readers_.resize(g_.values.size());
+        matmuls_of_.resize(g_.values.size());
+        for (int u = 0; u < (int)g_.values.size(); u++) {
+            for (int in : g_.values[u].inputs) readers_[in].push_back(u);
+            if (g_.values[u].op == OpKind::MatMul) matmuls_of_[g_.values[u].inputs[0]].push_back(u);
         }
+    }
+    bool only_contraction_readers(int v) {
+        ensure_readers();
         for (int u : readers_[v]) {
             const OpKind op = g_.values[u].op;
             if (op == OpKind::View || op == OpKind::Permute || op == OpKind::Slice) {
@@ -1127,7 +1132,7 @@ class Planner {
         }
         return true;
     }
-    std::vector<std::vector<int>> readers_;
+    std::vector<std::vector<int>> readers_, matmuls_of_;   // per value: the values that read it; the matmuls whose left operand it is
     // a constant seen through operations that only edit strides: planning it emits no step
     bool is_constant_view(int v) const {
         for (;;) {
@@ -1184,18 +1189,25 @@ class Planner {
         if (m < 256 || k % 4 != 0) return std::nullopt;
         // the other projections of x: an Add over a MatMul of x that nothing else reads
         std::vector<Projection> all{*first};
-        for (int v = 0; v < (int)g_.values.size() && all.size() < 8; v++) {
-            const ValueInfo& vi = g_.values[v];
-            // a sum over a matmul of x, or a matmul of x that is only re-described by its readers (no epilogue to lose)
-            const bool sum = vi.op == OpKind::Binary && vi.binary_op == BinaryOp::Add;
-            const bool bare = vi.op == OpKind::MatMul && vi.inputs[0] == x && only_contraction_readers(v);
-            if (v == root || !(sum || bare) || map_[v]) continue;
-            // (the same matmul seen from a view above its sum is not another projection)
+        ensure_readers();
+        for (int mm : matmuls_of_[x]) {
+            if (all.size() >= 8) break;
+            if (map_[mm]) continue;
             bool seen = false;
-            if (auto e = match_epilogue(v))
-                for (auto& have : all) seen = seen || have.matmul == e->contraction;
+            for (auto& have : all) seen = seen || have.matmul == mm;
             if (seen) continue;
-            if (auto p = as_projection(v, x)) all.push_back(*p);
+            // the sum over it (through views that nothing else reads), or the matmul itself if only matmuls read it
+            int cur = mm;
+            while (readers_[cur].size() == 1 && g_.values[readers_[cur][0]].op == OpKind::View && fusable(cur)) cur = readers_[cur][0];
+            int candidate = -1;
+            if (readers_[cur].size() == 1 && fusable(cur)) {
+                const ValueInfo& ri = g_.values[readers_[cur][0]];
+                if (ri.op == OpKind::Binary && ri.binary_op == BinaryOp::Add) candidate = readers_[cur][0];
+            }
+            if (candidate < 0 && only_contraction_readers(mm)) candidate = mm;
+            if (candidate < 0 || candidate == root || map_[candidate]) continue;
+            if (auto p = as_projection(candidate, x))
+                if (p->matmul == mm) all.push_back(*p);
         }
         if (all.size() < 2) return std::nullopt;
         int64_t n_total = 0;
