@@ -59,7 +59,6 @@ struct AttnSoftmaxParams {
     int64_t out_s0, out_s1;
     float scale;
     uint32_t* status;
-    int32_t stagger;                 // SM clock cycles by which every second CTA starts late (see attn_softmax_prepare)
     long long* trace;                // KN_ATTN_TRACE only: 8 clock64 stamps per work item of CTA 0, in pinned host memory
 };
 constexpr int kAsTraceItems = 16;
@@ -111,10 +110,6 @@ attn_softmax_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
         const uint32_t bytes = q_bytes + (uint32_t)p.k_blocks * k_block_bytes;
-        if (p.stagger > 0 && (blockIdx.x & 1)) {
-            const long long t0 = clock64();
-            while (clock64() - t0 < (long long)p.stagger) __nanosleep(500);
-        }
         int local = 0;
         for (int t = blockIdx.x; t < p.total; t += gridDim.x, local++) {
             const int bt = t / p.m_tiles, mt = t - bt * p.m_tiles;
@@ -412,9 +407,9 @@ std::shared_ptr<void> attn_softmax_prepare(const GemmParams& g, uint32_t* status
         }
         p.trace = table;
     }
-    if (const char* e = getenv("KN_ATTN_STAGGER")) p.stagger = atoi(e);
     l->smem_bytes = operands + kAsStagingBytes;
     l->grid = dim3((unsigned)std::min<int64_t>(total, 148), 1, 1);
+    // KN_ATTN_GRID=<n> in the environment: at most n CTAs (measuring: how the store sweep depends on how many SMs store)
     if (const char* e = getenv("KN_ATTN_GRID")) l->grid.x = (unsigned)std::max(1, std::min(atoi(e), (int)l->grid.x));
     return l;
 }
